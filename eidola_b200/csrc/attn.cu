@@ -1,0 +1,578 @@
+// Paged KV-cache append and paged sink attention (decode / speculative verify) for sm_100a.
+//
+// Cache layout of one layer: [num_pages][2 (K,V)][n_kv][16 tokens][64 dims] bf16.  Seen as a 2-D tensor of
+// 128-byte rows, a page is 32*n_kv consecutive rows, so one tiled TMA copy (128-byte swizzle) brings a whole
+// page -- every KV head of 16 tokens, K and V -- into shared memory, and ldmatrix reads it without bank
+// conflicts.
+//
+// attn_kernel: one CTA per work item (a run of logical pages of one sequence, planned on the host by
+// eb_attn_plan).  Eight compute warps and one producer warp.  A pipeline stage holds 256 rows (32 KiB):
+// one page when the rank holds 8 KV heads, 8/n_kv pages otherwise.  Compute warp w owns KV head w % n_kv of
+// page w / n_kv of each stage: S = Q K^T and O += P V on mma.sync m16n8k16 (bf16 in, fp32 accumulate), rows of
+// the M tile = (query position, query head of the GQA group), online softmax in base 2 with quad shuffles.
+// The kernel is HBM-bound: per 2 KiB of K and 2 KiB of V a warp issues 16 MMAs.
+//
+// The sink logit enters the softmax denominator exactly once: in the kernel epilogue when a sequence has a
+// single partial, otherwise in attn_merge_kernel, which combines split-K partials (m, l, acc) by log-sum-exp.
+//
+// The reference project has no attention code (its inference runs in a `llama-server` child process,
+// crates/eidola-app-core/src/local_models.rs:1612-1626).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "common.h"
+
+namespace {
+
+constexpr int kHeadDim = 64;
+constexpr int kPage = 16;
+constexpr int kGroup = 8;            // query heads per KV head
+constexpr int kComputeWarps = 8;
+constexpr int kThreads = (kComputeWarps + 1) * 32;
+constexpr int kStageBytes = 32768;   // 256 rows of 128 bytes
+constexpr int kMaxItemPages = 512;
+constexpr uint32_t kWaitTries = 1u << 22;
+constexpr float kNegBig = -1.0e30f;
+
+struct AttnParams {
+  const uint16_t* q;
+  int64_t q_stride;
+  uint16_t* out;
+  int64_t out_stride;
+  const int32_t* block_tables;
+  int32_t bt_stride;
+  const int32_t* seq_slots;
+  const int32_t* q_off;
+  const int32_t* ctx_lens;
+  const float* sinks;
+  int32_t window, n_q, max_q_len, num_pages;
+  float scale_log2;
+  const eb_attn_item* items;
+  const int32_t* seq_part;
+  float* part_acc;
+  float* part_ml;
+  int32_t* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after kWaitTries polls, raises the CTA's abort flag and the device status word.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+  for (uint32_t i = 0; i < kWaitTries; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) {
+      __nanosleep(64);
+      if (*abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  atomicOr(status, EB_DEV_WAIT_TIMEOUT);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// MT  : 16-row M tiles = ceil(max_q_len * 8 / 16)
+// HKV : KV heads held by this rank (8, 4, 2 or 1)
+template <int MT, int HKV, int STAGES>
+__global__ void __launch_bounds__(kThreads, (MT == 1) ? 2 : 1)
+attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
+  constexpr int PPS = kComputeWarps / HKV;       // pages per stage
+  constexpr int kPageRows = 2 * HKV * kPage;     // 128-byte rows per page
+  constexpr int kPageBytes = kPageRows * 128;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t stage0 = (raw + 1023u) & ~1023u;
+  uint8_t* after = smem_raw + (stage0 - raw) + STAGES * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after);  // full[STAGES], empty[STAGES]
+  int32_t* page_ids = reinterpret_cast<int32_t*>(after + 2 * STAGES * sizeof(uint64_t));
+  __shared__ int abort_flag;
+  __shared__ int n_issued;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const eb_attn_item item = p.items[blockIdx.x];
+  const int seq = item.seq;
+  const int slot = p.seq_slots[seq];
+  const int L = p.ctx_lens[seq];
+  const int q0 = p.q_off[seq];
+  const int ql = p.q_off[seq + 1] - q0;
+  int n_pages = item.page_end - item.page_begin;
+  if (n_pages > kMaxItemPages) {  // the planner never emits this; refuse instead of overrunning page_ids
+    if (tid == 0) atomicOr(p.status, EB_DEV_BAD_INDEX);
+    n_pages = kMaxItemPages;
+  }
+
+  for (int j = tid; j < n_pages; j += kThreads) {
+    int32_t id = p.block_tables[(int64_t)slot * p.bt_stride + item.page_begin + j];
+    if (id < 0 || id >= p.num_pages) {
+      atomicOr(p.status, EB_DEV_BAD_INDEX);
+      id = 0;
+    }
+    page_ids[j] = id;
+  }
+  if (tid == 0) {
+    abort_flag = 0;
+    n_issued = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bars[s]), 1);
+      mbar_init(smem_u32(&bars[STAGES + s]), kComputeWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int n_iters = (n_pages + PPS - 1) / PPS;
+
+  if (warp == kComputeWarps) {
+    // ---------------- producer: one thread feeds the stage ring with whole pages
+    if (lane == 0) {
+      for (int it = 0; it < n_iters; ++it) {
+        const int s = it % STAGES;
+        if (it >= STAGES) {
+          if (!mbar_wait(smem_u32(&bars[STAGES + s]), ((it / STAGES) - 1) & 1, &abort_flag, p.status)) break;
+        }
+        const int np = min(PPS, n_pages - it * PPS);
+        const uint32_t full = smem_u32(&bars[s]);
+        mbar_arrive_expect_tx(full, (uint32_t)(np * kPageBytes));
+        for (int j = 0; j < np; ++j)
+          tma_load_2d(stage0 + s * kStageBytes + j * kPageBytes, &tmap, 0, page_ids[it * PPS + j] * kPageRows, full);
+        n_issued = it + 1;
+      }
+    }
+  } else {
+    // ---------------- consumers
+    const int hk = warp % HKV;   // KV head of this warp
+    const int sub = warp / HKV;  // page of the stage this warp takes
+    const int g = lane >> 2, tq = lane & 3;
+
+    // Q fragments (A operand): rows = (query position, head of the group), kept in registers.
+    uint32_t qf[MT][4][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int qi = mt * 2 + half;
+        const uint16_t* qrow = p.q + (int64_t)(q0 + qi) * p.q_stride + (int64_t)(hk * kGroup + g) * kHeadDim;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          uint32_t lo = 0, hi = 0;
+          if (qi < ql) {
+            lo = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + tq * 2);
+            hi = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + tq * 2 + 8);
+          }
+          qf[mt][ks][half] = lo;       // a0 (row g) / a1 (row g+8)
+          qf[mt][ks][2 + half] = hi;   // a2 / a3
+        }
+      }
+    }
+
+    float o[MT][8][4];
+    float m_run[MT][2], l_run[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      m_run[mt][0] = m_run[mt][1] = kNegBig;
+      l_run[mt][0] = l_run[mt][1] = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) o[mt][nt][0] = o[mt][nt][1] = o[mt][nt][2] = o[mt][nt][3] = 0.f;
+    }
+
+    // per-lane constant parts of the ldmatrix addresses
+    const int mj = lane >> 3, mr = lane & 7;
+    const int k_tok = (mj >> 1) * 8 + mr, k_chunk = mj & 1;  // K: matrices (tok 0-7 | 8-15) x (dims lo | hi)
+    const int v_tok = (mj & 1) * 8 + mr, v_chunk = mj >> 1;  // V: matrices (dims lo | hi) x (tok 0-7 | 8-15)
+
+    for (int it = 0; it < n_iters; ++it) {
+      const int s = it % STAGES;
+      if (!mbar_wait(smem_u32(&bars[s]), (it / STAGES) & 1, &abort_flag, p.status)) break;
+      const int pl = it * PPS + sub;
+      if (pl < n_pages) {
+        const uint32_t page_base = stage0 + s * kStageBytes + sub * kPageBytes;
+        const uint32_t kbase = page_base + hk * (kPage * 128);
+        const uint32_t vbase = page_base + (HKV + hk) * (kPage * 128);
+        const int t0 = (item.page_begin + pl) * kPage;
+
+        float sc[MT][2][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) sc[mt][nt][0] = sc[mt][nt][1] = sc[mt][nt][2] = sc[mt][nt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          uint32_t b[4];
+          ldsm_x4(b, kbase + k_tok * 128 + (((ks * 2 + k_chunk) ^ (k_tok & 7)) << 4));
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_bf16(sc[mt][0], qf[mt][ks], b[0], b[1]);
+            mma_bf16(sc[mt][1], qf[mt][ks], b[2], b[3]);
+          }
+        }
+
+        uint32_t pa[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int pq = L - ql + mt * 2 + half;  // absolute position of this row's query
+            const int lo = p.window > 0 ? pq - p.window + 1 : 0;
+            float v[2][2];
+            float mx = kNegBig;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int t = t0 + nt * 8 + tq * 2 + e;
+                float x = sc[mt][nt][half * 2 + e] * p.scale_log2;
+                if (t > pq || t < lo) x = -INFINITY;
+                v[nt][e] = x;
+                mx = fmaxf(mx, x);
+              }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[mt][half], mx);
+            const float alpha = exp2f(m_run[mt][half] - m_new);
+            m_run[mt][half] = m_new;
+            float ps = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                v[nt][e] = exp2f(v[nt][e] - m_new);
+                ps += v[nt][e];
+              }
+            l_run[mt][half] = l_run[mt][half] * alpha + ps;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+              o[mt][nt][half * 2 + 0] *= alpha;
+              o[mt][nt][half * 2 + 1] *= alpha;
+            }
+            pa[mt][half] = pack_bf16(v[0][0], v[0][1]);      // a0 / a1: tokens 0-7
+            pa[mt][2 + half] = pack_bf16(v[1][0], v[1][1]);  // a2 / a3: tokens 8-15
+          }
+        }
+
+#pragma unroll
+        for (int dp = 0; dp < 4; ++dp) {
+          uint32_t b[4];
+          ldsm_x4_t(b, vbase + v_tok * 128 + (((dp * 2 + v_chunk) ^ (v_tok & 7)) << 4));
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_bf16(o[mt][dp * 2], pa[mt], b[0], b[1]);
+            mma_bf16(o[mt][dp * 2 + 1], pa[mt], b[2], b[3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[STAGES + s]));
+    }
+
+    // ---------------- epilogue
+    const int n_parts_seq = p.seq_part[seq + 1] - p.seq_part[seq];
+    const bool direct = (n_parts_seq == 1);
+    const int part = item.part + sub;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int qi = mt * 2 + half;
+        float l = l_run[mt][half];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (qi >= ql) continue;
+        const int head = hk * kGroup + g;
+        const float m = m_run[mt][half];
+        if (direct) {
+          const float sk = p.sinks[head] * 1.4426950408889634f;
+          const float mf = fmaxf(m, sk);
+          const float w = exp2f(m - mf);
+          const float inv = w / (l * w + exp2f(sk - mf));
+          uint16_t* orow = p.out + (int64_t)(q0 + qi) * p.out_stride + (int64_t)head * kHeadDim;
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt)
+            *reinterpret_cast<uint32_t*>(orow + nt * 8 + tq * 2) =
+                pack_bf16(o[mt][nt][half * 2] * inv, o[mt][nt][half * 2 + 1] * inv);
+        } else {
+          const int64_t row = ((int64_t)part * p.max_q_len + qi) * p.n_q + head;
+          float* arow = p.part_acc + row * kHeadDim;
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt)
+            *reinterpret_cast<float2*>(arow + nt * 8 + tq * 2) = make_float2(o[mt][nt][half * 2], o[mt][nt][half * 2 + 1]);
+          if (tq == 0) *reinterpret_cast<float2*>(p.part_ml + row * 2) = make_float2(m, l);
+        }
+      }
+    }
+  }
+
+  __syncthreads();
+  if (abort_flag && tid == 0) {
+    // A wait gave up.  Before the CTA releases its shared memory, wait (bounded) for the copies still in flight.
+    const int issued = n_issued;
+    for (int it = max(0, issued - STAGES); it < issued; ++it) {
+      const uint32_t bar = smem_u32(&bars[it % STAGES]);
+      for (uint32_t i = 0; i < kWaitTries; ++i) {
+        if (mbar_try_wait(bar, (it / STAGES) & 1)) break;
+        __nanosleep(64);
+      }
+    }
+  }
+}
+
+// Combine the split-K partials of one (sequence, KV group): warp = query head, lane = two dims.
+__global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
+  const int seq = blockIdx.x;
+  const int pb = p.seq_part[seq], pe = p.seq_part[seq + 1];
+  if (pe - pb <= 1) return;  // written directly by attn_kernel
+  const int head = blockIdx.y * kGroup + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int q0 = p.q_off[seq], ql = p.q_off[seq + 1] - q0;
+  const float sk = p.sinks[head] * 1.4426950408889634f;
+  for (int qi = 0; qi < ql; ++qi) {
+    float mf = sk;
+    for (int j = pb + lane; j < pe; j += 32) {
+      const int64_t row = ((int64_t)j * p.max_q_len + qi) * p.n_q + head;
+      mf = fmaxf(mf, p.part_ml[row * 2]);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mf = fmaxf(mf, __shfl_xor_sync(0xffffffffu, mf, o));
+    float den = exp2f(sk - mf);
+    float ax = 0.f, ay = 0.f;
+    for (int j = pb; j < pe; ++j) {
+      const int64_t row = ((int64_t)j * p.max_q_len + qi) * p.n_q + head;
+      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + row * 2);
+      const float w = exp2f(ml.x - mf);
+      den += w * ml.y;
+      const float2 a = *reinterpret_cast<const float2*>(p.part_acc + row * kHeadDim + lane * 2);
+      ax += w * a.x;
+      ay += w * a.y;
+    }
+    const float inv = 1.0f / den;
+    uint16_t* orow = p.out + (int64_t)(q0 + qi) * p.out_stride + (int64_t)head * kHeadDim;
+    *reinterpret_cast<uint32_t*>(orow + lane * 2) = pack_bf16(ax * inv, ay * inv);
+  }
+}
+
+// One thread per 16-byte chunk of a new K or V row.
+__global__ void kv_append_kernel(uint4* cache, int32_t num_pages, int32_t n_kv, const uint4* k_new, const uint4* v_new,
+                                 int64_t row_stride16, const int32_t* block_tables, int32_t bt_stride,
+                                 const int32_t* tok_slot, const int32_t* positions, int32_t n_tokens, int32_t* status) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int chunks_per_tok = 2 * n_kv * 8;  // K and V, 8 chunks of 16 bytes per head row
+  if (idx >= (int64_t)n_tokens * chunks_per_tok) return;
+  const int t = (int)(idx / chunks_per_tok);
+  const int r = (int)(idx % chunks_per_tok);
+  const int kv = r / (n_kv * 8), h = (r / 8) % n_kv, c = r % 8;
+  const int pos = positions[t];
+  const int32_t page = block_tables[(int64_t)tok_slot[t] * bt_stride + pos / kPage];
+  if (page < 0 || page >= num_pages || pos < 0) {
+    atomicOr(status, EB_DEV_BAD_INDEX);
+    return;
+  }
+  const uint4* src = (kv ? v_new : k_new) + (int64_t)t * row_stride16 + h * 8 + c;
+  // page = 2*n_kv head blocks of 16 rows of 8 chunks
+  uint4* dst = cache + (((int64_t)page * 2 * n_kv + kv * n_kv + h) * kPage + pos % kPage) * 8 + c;
+  *dst = *src;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+template <int MT, int HKV, int STAGES>
+int32_t launch_attn(const CUtensorMap& tm, const AttnParams& p, int n_items, cudaStream_t st) {
+  const size_t smem = 1024 + (size_t)STAGES * kStageBytes + 2 * STAGES * sizeof(uint64_t) + kMaxItemPages * sizeof(int32_t);
+  auto kfn = attn_kernel<MT, HKV, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  kfn<<<n_items, kThreads, smem, st>>>(tm, p);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+template <int MT>
+int32_t dispatch_hkv(int n_kv, const CUtensorMap& tm, const AttnParams& p, int n_items, cudaStream_t st) {
+  constexpr int ST = (MT == 1) ? 3 : 6;
+  switch (n_kv) {
+    case 8: return launch_attn<MT, 8, ST>(tm, p, n_items, st);
+    case 4: return launch_attn<MT, 4, ST>(tm, p, n_items, st);
+    case 2: return launch_attn<MT, 2, ST>(tm, p, n_items, st);
+    case 1: return launch_attn<MT, 1, ST>(tm, p, n_items, st);
+  }
+  return eb::fail(EB_ERR_UNSUPPORTED, "attention: n_kv %d not in {1,2,4,8}", n_kv);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t eb_kv_append(void* d_cache, int32_t num_pages, int32_t n_kv, int32_t head_dim, int32_t page_size,
+                     const void* d_k_new, const void* d_v_new, int64_t row_stride, const int32_t* d_block_tables,
+                     int32_t bt_stride, const int32_t* d_tok_slot, const int32_t* d_positions, int32_t n_tokens,
+                     void* stream) {
+  EB_REQUIRE(d_cache && d_k_new && d_v_new && d_block_tables && d_tok_slot && d_positions, EB_ERR_ARG,
+             "eb_kv_append: null pointer");
+  EB_REQUIRE(head_dim == kHeadDim && page_size == kPage, EB_ERR_UNSUPPORTED,
+             "eb_kv_append: head_dim %d / page_size %d (built for 64 / 16)", head_dim, page_size);
+  EB_REQUIRE(n_kv >= 1 && num_pages >= 1 && n_tokens >= 0 && bt_stride >= 1, EB_ERR_ARG, "eb_kv_append: bad size");
+  EB_REQUIRE(row_stride >= (int64_t)n_kv * head_dim && row_stride % 8 == 0, EB_ERR_ARG,
+             "eb_kv_append: row stride %lld (needs >= %d, multiple of 8)", (long long)row_stride, n_kv * head_dim);
+  EB_REQUIRE(((uintptr_t)d_k_new % 16 == 0) && ((uintptr_t)d_v_new % 16 == 0) && ((uintptr_t)d_cache % 16 == 0),
+             EB_ERR_ARG, "eb_kv_append: pointers must be 16-byte aligned");
+  if (n_tokens == 0) return EB_OK;
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_kv_append: no device");
+  const int64_t total = (int64_t)n_tokens * 2 * n_kv * 8;
+  kv_append_kernel<<<(unsigned)eb::cdiv(total, 256), 256, 0, eb::as_stream(stream)>>>(
+      (uint4*)d_cache, num_pages, n_kv, (const uint4*)d_k_new, (const uint4*)d_v_new, row_stride / 8, d_block_tables,
+      bt_stride, d_tok_slot, d_positions, n_tokens, status);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_attn_workspace(int32_t n_parts, int32_t max_q_len, int32_t n_q, int32_t head_dim, size_t* acc_bytes,
+                          size_t* ml_bytes) {
+  EB_REQUIRE(acc_bytes && ml_bytes && n_parts >= 0 && max_q_len >= 1 && n_q >= 1 && head_dim >= 1, EB_ERR_ARG,
+             "eb_attn_workspace: bad argument");
+  const size_t rows = (size_t)n_parts * max_q_len * n_q;
+  *acc_bytes = rows * head_dim * sizeof(float);
+  *ml_bytes = rows * 2 * sizeof(float);
+  return EB_OK;
+}
+
+int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
+  EB_REQUIRE(a, EB_ERR_ARG, "eb_attn_paged_sink: null args");
+  EB_REQUIRE(a->d_q && a->d_out && a->d_cache && a->d_block_tables && a->d_seq_slots && a->d_q_off && a->d_ctx_lens &&
+                 a->d_sinks && a->d_items && a->d_seq_part,
+             EB_ERR_ARG, "eb_attn_paged_sink: null pointer");
+  EB_REQUIRE(a->head_dim == kHeadDim && a->page_size == kPage, EB_ERR_UNSUPPORTED,
+             "eb_attn_paged_sink: head_dim %d / page_size %d (built for 64 / 16)", a->head_dim, a->page_size);
+  EB_REQUIRE(a->n_kv >= 1 && a->n_q == a->n_kv * kGroup, EB_ERR_UNSUPPORTED,
+             "eb_attn_paged_sink: %d query heads over %d KV heads (built for groups of 8)", a->n_q, a->n_kv);
+  EB_REQUIRE(a->max_q_len >= 1 && a->max_q_len <= 6, EB_ERR_UNSUPPORTED, "eb_attn_paged_sink: max_q_len %d not in 1..6",
+             a->max_q_len);
+  EB_REQUIRE(a->n_seqs >= 0 && a->n_items >= 0 && a->n_parts >= 0 && a->num_pages >= 1 && a->window >= 0, EB_ERR_ARG,
+             "eb_attn_paged_sink: negative size");
+  EB_REQUIRE(a->q_stride % 2 == 0 && a->out_stride % 2 == 0 && (uintptr_t)a->d_q % 4 == 0 && (uintptr_t)a->d_out % 4 == 0,
+             EB_ERR_ARG, "eb_attn_paged_sink: q/out must be 4-byte aligned with even strides");
+  EB_REQUIRE((uintptr_t)a->d_cache % 1024 == 0, EB_ERR_ARG, "eb_attn_paged_sink: cache must be 1024-byte aligned");
+  EB_REQUIRE(a->n_parts == 0 || (a->d_part_acc && a->d_part_ml), EB_ERR_ARG, "eb_attn_paged_sink: null workspace");
+  if (a->n_seqs == 0 || a->n_items == 0) return EB_OK;
+  const int64_t rows = (int64_t)a->num_pages * 2 * a->n_kv * kPage;
+  EB_REQUIRE(rows < (1ll << 31), EB_ERR_UNSUPPORTED, "eb_attn_paged_sink: cache of %lld rows exceeds a tensor map",
+             (long long)rows);
+
+  EncodeTiledFn enc = encode_tiled_fn();
+  EB_REQUIRE(enc, EB_ERR_NODEVICE, "eb_attn_paged_sink: driver entry point cuTensorMapEncodeTiled not found");
+  CUtensorMap tm;
+  const cuuint64_t gdim[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows};
+  const cuuint64_t gstr[1] = {128};
+  const cuuint32_t box[2] = {(cuuint32_t)kHeadDim, (cuuint32_t)(2 * a->n_kv * kPage)};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult cr = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a->d_cache), gdim, gstr, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  EB_REQUIRE(cr == CUDA_SUCCESS, EB_ERR_ARG, "eb_attn_paged_sink: cuTensorMapEncodeTiled failed (%d)", (int)cr);
+
+  AttnParams p;
+  p.q = (const uint16_t*)a->d_q;
+  p.q_stride = a->q_stride;
+  p.out = (uint16_t*)a->d_out;
+  p.out_stride = a->out_stride;
+  p.block_tables = a->d_block_tables;
+  p.bt_stride = a->bt_stride;
+  p.seq_slots = a->d_seq_slots;
+  p.q_off = a->d_q_off;
+  p.ctx_lens = a->d_ctx_lens;
+  p.sinks = a->d_sinks;
+  p.window = a->window;
+  p.n_q = a->n_q;
+  p.max_q_len = a->max_q_len;
+  p.num_pages = a->num_pages;
+  p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.items = a->d_items;
+  p.seq_part = a->d_seq_part;
+  p.part_acc = (float*)a->d_part_acc;
+  p.part_ml = (float*)a->d_part_ml;
+  p.status = eb::status_word();
+  EB_REQUIRE(p.status, EB_ERR_NODEVICE, "eb_attn_paged_sink: no device");
+
+  cudaStream_t st = eb::as_stream(stream);
+  const int mt = (a->max_q_len * kGroup + 15) / 16;
+  int32_t rc;
+  if (mt == 1)
+    rc = dispatch_hkv<1>(a->n_kv, tm, p, a->n_items, st);
+  else if (mt == 2)
+    rc = dispatch_hkv<2>(a->n_kv, tm, p, a->n_items, st);
+  else
+    rc = dispatch_hkv<3>(a->n_kv, tm, p, a->n_items, st);
+  if (rc != EB_OK) return rc;
+  if (a->n_parts > a->n_seqs) {  // at least one sequence has more than one partial
+    attn_merge_kernel<<<dim3((unsigned)a->n_seqs, (unsigned)a->n_kv), 256, 0, st>>>(p);
+    EB_LAUNCH_CHECK();
+  }
+  return EB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,284 @@
+// Device-memory plumbing, the status word, and the seeded tensor generators of libeidola_b200.
+#include <string.h>
+
+#include <mutex>
+#include <string>
+
+#include "../../include/eb_synth.h"
+#include "common.h"
+
+namespace eb {
+
+static thread_local std::string g_last_error;
+
+int32_t fail(int32_t code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+static std::mutex g_status_mu;
+static int32_t* g_status_ptr[64] = {nullptr};
+
+int32_t* status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_status_mu);
+  if (!g_status_ptr[dev]) {
+    int32_t* p = nullptr;
+    if (cudaMalloc(&p, sizeof(int32_t)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int32_t));
+    g_status_ptr[dev] = p;
+  }
+  return g_status_ptr[dev];
+}
+
+}  // namespace eb
+
+using eb::as_stream;
+
+extern "C" {
+
+int32_t eb_version(int32_t* abi) {
+  if (abi) *abi = EB_ABI_VERSION;
+  return EB_OK;
+}
+
+int32_t eb_last_error(char* buf, size_t n) {
+  if (!buf || n == 0) return EB_ERR_ARG;
+  strncpy(buf, eb::g_last_error.c_str(), n - 1);
+  buf[n - 1] = 0;
+  return EB_OK;
+}
+
+int32_t eb_device_count(int32_t* n) {
+  EB_REQUIRE(n, EB_ERR_ARG, "eb_device_count: null");
+  int c = 0;
+  cudaError_t e = cudaGetDeviceCount(&c);
+  if (e != cudaSuccess) {
+    *n = 0;
+    return eb::fail(EB_ERR_NODEVICE, "cudaGetDeviceCount: %s", cudaGetErrorString(e));
+  }
+  *n = c;
+  return EB_OK;
+}
+
+int32_t eb_device_set(int32_t device) {
+  EB_CUDA(cudaSetDevice(device));
+  return EB_OK;
+}
+
+int32_t eb_device_info(int32_t device, int32_t* sm_count, int64_t* l2_bytes, int64_t* hbm_bytes, int32_t* cc_major,
+                       int32_t* cc_minor) {
+  cudaDeviceProp p;
+  EB_CUDA(cudaGetDeviceProperties(&p, device));
+  if (sm_count) *sm_count = p.multiProcessorCount;
+  if (l2_bytes) *l2_bytes = p.l2CacheSize;
+  if (hbm_bytes) *hbm_bytes = (int64_t)p.totalGlobalMem;
+  if (cc_major) *cc_major = p.major;
+  if (cc_minor) *cc_minor = p.minor;
+  return EB_OK;
+}
+
+int32_t eb_malloc(void** d_ptr, size_t bytes) {
+  EB_REQUIRE(d_ptr, EB_ERR_ARG, "eb_malloc: null");
+  EB_CUDA(cudaMalloc(d_ptr, bytes ? bytes : 1));
+  return EB_OK;
+}
+int32_t eb_free(void* d_ptr) {
+  EB_CUDA(cudaFree(d_ptr));
+  return EB_OK;
+}
+int32_t eb_host_alloc(void** h_ptr, size_t bytes) {
+  EB_REQUIRE(h_ptr, EB_ERR_ARG, "eb_host_alloc: null");
+  EB_CUDA(cudaMallocHost(h_ptr, bytes ? bytes : 1));
+  return EB_OK;
+}
+int32_t eb_host_free(void* h_ptr) {
+  EB_CUDA(cudaFreeHost(h_ptr));
+  return EB_OK;
+}
+int32_t eb_memset(void* d_ptr, int32_t value, size_t bytes, void* stream) {
+  EB_CUDA(cudaMemsetAsync(d_ptr, value, bytes, as_stream(stream)));
+  return EB_OK;
+}
+int32_t eb_copy_h2d(void* d_dst, const void* h_src, size_t bytes, void* stream) {
+  EB_CUDA(cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, as_stream(stream)));
+  return EB_OK;
+}
+int32_t eb_copy_d2h(void* h_dst, const void* d_src, size_t bytes, void* stream) {
+  EB_CUDA(cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, as_stream(stream)));
+  return EB_OK;
+}
+int32_t eb_copy_d2d(void* d_dst, const void* d_src, size_t bytes, void* stream) {
+  EB_CUDA(cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDeviceToDevice, as_stream(stream)));
+  return EB_OK;
+}
+int32_t eb_stream_create(void** stream) {
+  EB_REQUIRE(stream, EB_ERR_ARG, "eb_stream_create: null");
+  cudaStream_t s;
+  EB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  *stream = s;
+  return EB_OK;
+}
+int32_t eb_stream_destroy(void* stream) {
+  EB_CUDA(cudaStreamDestroy(as_stream(stream)));
+  return EB_OK;
+}
+int32_t eb_stream_sync(void* stream) {
+  EB_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  return EB_OK;
+}
+int32_t eb_device_sync(void) {
+  EB_CUDA(cudaDeviceSynchronize());
+  return EB_OK;
+}
+int32_t eb_event_create(void** ev) {
+  EB_REQUIRE(ev, EB_ERR_ARG, "eb_event_create: null");
+  cudaEvent_t e;
+  EB_CUDA(cudaEventCreate(&e));
+  *ev = e;
+  return EB_OK;
+}
+int32_t eb_event_destroy(void* ev) {
+  EB_CUDA(cudaEventDestroy((cudaEvent_t)ev));
+  return EB_OK;
+}
+int32_t eb_event_record(void* ev, void* stream) {
+  EB_CUDA(cudaEventRecord((cudaEvent_t)ev, as_stream(stream)));
+  return EB_OK;
+}
+int32_t eb_event_elapsed_ms(void* ev_start, void* ev_stop, float* ms) {
+  EB_REQUIRE(ms, EB_ERR_ARG, "eb_event_elapsed_ms: null");
+  EB_CUDA(cudaEventSynchronize((cudaEvent_t)ev_stop));
+  EB_CUDA(cudaEventElapsedTime(ms, (cudaEvent_t)ev_start, (cudaEvent_t)ev_stop));
+  return EB_OK;
+}
+
+int32_t eb_status_read(int32_t* status) {
+  EB_REQUIRE(status, EB_ERR_ARG, "eb_status_read: null");
+  int32_t* p = eb::status_word();
+  EB_REQUIRE(p, EB_ERR_NODEVICE, "eb_status_read: no device status word");
+  EB_CUDA(cudaMemcpy(status, p, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  EB_CUDA(cudaMemset(p, 0, sizeof(int32_t)));
+  return EB_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// kernels
+
+namespace {
+
+__global__ void l2_flush_kernel(uint4* p, size_t n16, uint32_t v) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n16; i += stride) p[i] = make_uint4(v, v, v, v);
+}
+
+template <int KIND>  // 0 bf16 normal, 1 f32 normal, 2 e4m3 normal, 3 f32 uniform
+__global__ void synth_kernel(void* out, int64_t n, uint64_t seed, uint64_t sid, uint64_t idx0, float a, float b) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    if (KIND == 3) {
+      ((float*)out)[i] = eb_uniform(seed, sid, idx0 + (uint64_t)i, a, b);
+    } else {
+      const float v = __fmul_rn(eb_normal(seed, sid, idx0 + (uint64_t)i), a);
+      if (KIND == 0) ((uint16_t*)out)[i] = eb_f32_to_bf16(v);
+      if (KIND == 1) ((float*)out)[i] = v;
+      if (KIND == 2) ((uint8_t*)out)[i] = eb_f32_to_e4m3(v);
+    }
+  }
+}
+
+// One CTA per 128x128 block: generate, block amax, scale, quantise.  256 threads, thread t owns column
+// pair-of-bytes positions; values are regenerated for the second pass instead of being held.
+__global__ void synth_weight_fp8_kernel(uint8_t* codes, float* scales, int64_t cols, int64_t row0, int64_t nrows,
+                                        uint64_t seed, uint64_t sid, float std) {
+  const int64_t cb = (cols + 127) / 128;
+  const int64_t br = blockIdx.x / cb, bc = blockIdx.x % cb;
+  const int64_t r_lo = br * 128, c_lo = bc * 128;
+  const int r_n = (int)min((int64_t)128, nrows - r_lo), c_n = (int)min((int64_t)128, cols - c_lo);
+  __shared__ float red[8];
+  float amax = 0.f;
+  for (int e = threadIdx.x; e < r_n * c_n; e += blockDim.x) {
+    const int r = e / c_n, c = e % c_n;
+    const float v = __fmul_rn(eb_normal(seed, sid, (uint64_t)((row0 + r_lo + r) * cols + c_lo + c)), std);
+    amax = fmaxf(amax, fabsf(v));
+  }
+  for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
+  const float s = amax > 0.f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+  if (threadIdx.x == 0) scales[br * cb + bc] = s;
+  for (int e = threadIdx.x; e < r_n * c_n; e += blockDim.x) {
+    const int r = e / c_n, c = e % c_n;
+    const float v = __fmul_rn(eb_normal(seed, sid, (uint64_t)((row0 + r_lo + r) * cols + c_lo + c)), std);
+    codes[(r_lo + r) * cols + c_lo + c] = eb_f32_to_e4m3(__fdiv_rn(v, s));
+  }
+}
+
+template <int KIND>
+int32_t launch_synth(void* d_out, int64_t n, uint64_t seed, uint64_t sid, uint64_t idx0, float a, float b, void* st) {
+  EB_REQUIRE(d_out && n >= 0, EB_ERR_ARG, "eb_synth: null or negative size");
+  if (n == 0) return EB_OK;
+  const int threads = 256;
+  const int64_t blocks = std::min<int64_t>(eb::cdiv(n, threads), 148 * 32);
+  synth_kernel<KIND><<<(unsigned)blocks, threads, 0, as_stream(st)>>>(d_out, n, seed, sid, idx0, a, b);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t eb_l2_flush(void* d_scratch, size_t bytes, void* stream) {
+  EB_REQUIRE(d_scratch && bytes >= 16, EB_ERR_ARG, "eb_l2_flush: null or too small");
+  static uint32_t v = 0;
+  l2_flush_kernel<<<148 * 8, 256, 0, as_stream(stream)>>>((uint4*)d_scratch, bytes / 16, ++v);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_synth_normal_bf16(void* d_out, int64_t n, uint64_t seed, uint64_t sid, uint64_t idx0, float scale,
+                             void* stream) {
+  return launch_synth<0>(d_out, n, seed, sid, idx0, scale, 0.f, stream);
+}
+int32_t eb_synth_normal_f32(void* d_out, int64_t n, uint64_t seed, uint64_t sid, uint64_t idx0, float scale,
+                            void* stream) {
+  return launch_synth<1>(d_out, n, seed, sid, idx0, scale, 0.f, stream);
+}
+int32_t eb_synth_normal_e4m3(void* d_out, int64_t n, uint64_t seed, uint64_t sid, uint64_t idx0, float scale,
+                             void* stream) {
+  return launch_synth<2>(d_out, n, seed, sid, idx0, scale, 0.f, stream);
+}
+int32_t eb_synth_uniform_f32(void* d_out, int64_t n, uint64_t seed, uint64_t sid, uint64_t idx0, float lo, float hi,
+                             void* stream) {
+  return launch_synth<3>(d_out, n, seed, sid, idx0, lo, hi, stream);
+}
+
+int32_t eb_synth_weight_fp8(void* d_codes, void* d_scales, int64_t rows_total, int64_t cols, int64_t row0,
+                            int64_t nrows, uint64_t seed, uint64_t sid, float std, void* stream) {
+  EB_REQUIRE(d_codes && d_scales, EB_ERR_ARG, "eb_synth_weight_fp8: null");
+  EB_REQUIRE(rows_total > 0 && cols > 0 && nrows > 0 && row0 >= 0 && row0 + nrows <= rows_total, EB_ERR_ARG,
+             "eb_synth_weight_fp8: band [%lld,+%lld) outside %lld rows", (long long)row0, (long long)nrows,
+             (long long)rows_total);
+  EB_REQUIRE(row0 % 128 == 0, EB_ERR_ARG, "eb_synth_weight_fp8: row0 %lld not a multiple of 128", (long long)row0);
+  const int64_t blocks = eb::cdiv(nrows, 128) * eb::cdiv(cols, 128);
+  EB_REQUIRE(blocks < (1ll << 31), EB_ERR_ARG, "eb_synth_weight_fp8: too many blocks");
+  synth_weight_fp8_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>((uint8_t*)d_codes, (float*)d_scales, cols,
+                                                                           row0, nrows, seed, sid, std);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+}  // extern "C"

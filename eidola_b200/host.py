@@ -1,0 +1,145 @@
+"""Typed wrappers over the C ABI: one Python function per entry point, arguments in the header's order."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from .capi import (AttnArgs, AttnItem, DeviceBuffer, call, c_f32, c_i32, c_i64, c_sz, c_u64, c_vp, ptr)
+
+I32 = np.int32
+
+
+def _i32(a) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(a, dtype=I32))
+
+
+class Scheduler:
+    """eb_sched_*: page pool + block tables + ragged packing (host only)."""
+
+    def __init__(self, num_pages: int, page_size: int, max_seqs: int, max_pages_per_seq: int, seed: int):
+        self._h = c_vp()
+        call("eb_sched_create", c_i32(num_pages), c_i32(page_size), c_i32(max_seqs), c_i32(max_pages_per_seq),
+             c_u64(seed), C.byref(self._h))
+        self.num_pages, self.page_size, self.max_seqs, self.max_pages = num_pages, page_size, max_seqs, max_pages_per_seq
+
+    def close(self):
+        if self._h:
+            call("eb_sched_destroy", self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def admit(self, context_len: int) -> int:
+        slot = c_i32(-1)
+        call("eb_sched_admit", self._h, c_i32(context_len), C.byref(slot))
+        return int(slot.value)
+
+    def extend(self, slot: int, new_len: int) -> None:
+        call("eb_sched_extend", self._h, c_i32(slot), c_i32(new_len))
+
+    def truncate(self, slot: int, new_len: int) -> None:
+        call("eb_sched_truncate", self._h, c_i32(slot), c_i32(new_len))
+
+    def release(self, slot: int) -> None:
+        call("eb_sched_release", self._h, c_i32(slot))
+
+    def free_pages(self) -> int:
+        n = c_i32(0)
+        call("eb_sched_free_pages", self._h, C.byref(n))
+        return int(n.value)
+
+    def seq_len(self, slot: int) -> int:
+        n = c_i32(0)
+        call("eb_sched_seq_len", self._h, c_i32(slot), C.byref(n))
+        return int(n.value)
+
+    def block_tables(self) -> np.ndarray:
+        """A copy of the [max_seqs][max_pages_per_seq] table."""
+        p = C.POINTER(c_i32)()
+        stride = c_i32(0)
+        call("eb_sched_block_tables", self._h, C.byref(p), C.byref(stride))
+        return np.ctypeslib.as_array(p, shape=(self.max_seqs, int(stride.value))).copy()
+
+    def pack(self, slots, q_lens) -> dict:
+        slots, q_lens = _i32(slots), _i32(q_lens)
+        n = len(slots)
+        cap = int(q_lens.sum()) if n else 0
+        q_off = np.zeros(n + 1, I32)
+        ctx = np.zeros(n, I32)
+        tok_seq, tok_slot, pos = np.zeros(cap, I32), np.zeros(cap, I32), np.zeros(cap, I32)
+        nt = c_i32(0)
+        call("eb_sched_pack", self._h, ptr(slots), ptr(q_lens), c_i32(n), ptr(q_off), ptr(ctx), ptr(tok_seq),
+             ptr(tok_slot), ptr(pos), C.byref(nt))
+        assert nt.value == cap
+        return {"slots": slots, "q_lens": q_lens, "q_off": q_off, "ctx_lens": ctx, "tok_seq": tok_seq,
+                "tok_slot": tok_slot, "positions": pos, "n_tokens": cap}
+
+
+def attn_plan(ctx_lens, q_lens, page_size: int, window: int, sm_count: int, chunk_pages: int = 0,
+              parts_per_item: int = 1) -> dict:
+    ctx_lens, q_lens = _i32(ctx_lens), _i32(q_lens)
+    n = len(ctx_lens)
+    cap = int(((ctx_lens.astype(np.int64) + page_size - 1) // page_size).sum()) + n + 1
+    items = (AttnItem * cap)()
+    n_items, n_parts = c_i32(0), c_i32(0)
+    seq_part = np.zeros(n + 1, I32)
+    call("eb_attn_plan", ptr(ctx_lens), ptr(q_lens), c_i32(n), c_i32(page_size), c_i32(window), c_i32(sm_count),
+         c_i32(chunk_pages), c_i32(parts_per_item), items, c_i32(cap), C.byref(n_items), ptr(seq_part),
+         C.byref(n_parts))
+    arr = np.frombuffer(items, dtype=I32).reshape(cap, 4)[: n_items.value].copy()
+    return {"items": arr, "seq_part": seq_part, "n_items": int(n_items.value), "n_parts": int(n_parts.value)}
+
+
+def kv_append(d_cache, num_pages, n_kv, head_dim, page_size, d_k_new, d_v_new, row_stride, d_block_tables, bt_stride,
+              d_tok_slot, d_positions, n_tokens, stream=None) -> None:
+    call("eb_kv_append", c_vp(d_cache), c_i32(num_pages), c_i32(n_kv), c_i32(head_dim), c_i32(page_size),
+         c_vp(d_k_new), c_vp(d_v_new), c_i64(row_stride), c_vp(d_block_tables), c_i32(bt_stride), c_vp(d_tok_slot),
+         c_vp(d_positions), c_i32(n_tokens), c_vp(stream))
+
+
+def attn_workspace(n_parts, max_q_len, n_q, head_dim) -> tuple[int, int]:
+    a, m = c_sz(0), c_sz(0)
+    call("eb_attn_workspace", c_i32(n_parts), c_i32(max_q_len), c_i32(n_q), c_i32(head_dim), C.byref(a), C.byref(m))
+    return int(a.value), int(m.value)
+
+
+def attn_paged_sink(args: AttnArgs, stream=None) -> None:
+    call("eb_attn_paged_sink", C.byref(args), c_vp(stream))
+
+
+class AttnLaunch:
+    """Device-resident arguments of one attention launch, built from a packed step and a plan."""
+
+    def __init__(self, *, d_q, q_stride, d_out, out_stride, d_cache, num_pages, d_block_tables, bt_stride, packed,
+                 plan, d_sinks, window, n_q, n_kv, head_dim=64, page_size=16, scale=0.125):
+        self.max_q_len = int(packed["q_lens"].max()) if len(packed["q_lens"]) else 1
+        self.bufs = {
+            "seq_slots": DeviceBuffer.from_array(_i32(packed["slots"])),
+            "q_off": DeviceBuffer.from_array(_i32(packed["q_off"])),
+            "ctx_lens": DeviceBuffer.from_array(_i32(packed["ctx_lens"])),
+            "items": DeviceBuffer.from_array(_i32(plan["items"])),
+            "seq_part": DeviceBuffer.from_array(_i32(plan["seq_part"])),
+        }
+        acc_b, ml_b = attn_workspace(plan["n_parts"], self.max_q_len, n_q, head_dim)
+        self.bufs["acc"] = DeviceBuffer(acc_b)
+        self.bufs["ml"] = DeviceBuffer(ml_b)
+        a = AttnArgs()
+        a.d_q, a.q_stride, a.d_out, a.out_stride = d_q, q_stride, d_out, out_stride
+        a.d_cache, a.num_pages = d_cache, num_pages
+        a.d_block_tables, a.bt_stride = d_block_tables, bt_stride
+        a.d_seq_slots, a.d_q_off, a.d_ctx_lens = (self.bufs[k].ptr for k in ("seq_slots", "q_off", "ctx_lens"))
+        a.n_seqs, a.max_q_len = len(packed["slots"]), self.max_q_len
+        a.d_sinks, a.window = d_sinks, window
+        a.n_q, a.n_kv, a.head_dim, a.page_size, a.scale = n_q, n_kv, head_dim, page_size, scale
+        a.d_items, a.n_items = self.bufs["items"].ptr, plan["n_items"]
+        a.d_seq_part, a.n_parts = self.bufs["seq_part"].ptr, plan["n_parts"]
+        a.d_part_acc, a.d_part_ml = self.bufs["acc"].ptr, self.bufs["ml"].ptr
+        self.args = a
+
+    def run(self, stream=None) -> None:
+        attn_paged_sink(self.args, stream)

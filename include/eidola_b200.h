@@ -1,0 +1,204 @@
+/*
+ * eidola_b200.h -- C ABI of libeidola_b200.so: the decode step of a paged-KV,
+ * sink-attention, FP8 block-scaled, mixture-of-experts decoder on NVIDIA B200
+ * (sm_100a).
+ *
+ * THIS SURFACE IS NEW.  The reference project (eidola-ai/eidola) has no operator
+ * API: its only engine boundaries are text-in/text-out --
+ *   * server side: `trait ChatBackend { send, list_models, send_stream }`
+ *     (crates/eidola-server/src/backend.rs:87-108), sole implementation an HTTPS
+ *     client (`TinfoilBackend`, backend.rs:413-615);
+ *   * client side: a `llama-server` child process started with the argv at
+ *     crates/eidola-app-core/src/local_models.rs:1612-1626 and spoken to over
+ *     loopback HTTP (crates/eidola-app-core/src/lib.rs:7155-7163).
+ * Everything below is what an in-process engine behind either of those would
+ * call every decode step.  Each entry point cites the reference code that would
+ * sit above it; none replaces reference arithmetic, because there is none.
+ *
+ * Conventions
+ *   * every function returns an int32 status: 0 = ok, negative = host-side
+ *     validation error (nothing was launched), positive = CUDA runtime error
+ *     code or a device status word read back by eb_status_read();
+ *   * no exception crosses the boundary; eb_last_error() gives a log-safe
+ *     message (sizes and indices only, never tensor contents -- the reference
+ *     keeps payloads out of its logs, crates/eidola-server/AGENTS.md:65-66);
+ *   * buffers are caller-owned unless an eb_engine owns them; pointers named
+ *     d_* are device pointers, h_* are host pointers; `stream` is a
+ *     cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   * one thread drives one handle at a time (the reference gives each engine
+ *     a single owning supervisor task, local_models.rs:1633-1638).
+ *
+ * Tensor formats
+ *   bf16   : uint16 bit patterns, round-to-nearest-even
+ *   e4m3   : 1-4-3, bias 7, max 448, no infinity, saturating RNE
+ *   scales : one fp32 per 128x128 block, row-major [ceil(rows/128)][ceil(cols/128)]
+ *   KV page: [2 (K,V)][n_kv][page_size=16][head_dim=64] bf16, pages contiguous per layer
+ */
+#ifndef EIDOLA_B200_H_
+#define EIDOLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EB_ABI_VERSION 1
+
+/* status codes (negative: host validation) */
+#define EB_OK 0
+#define EB_ERR_ARG (-1)        /* null pointer, size out of range, misaligned */
+#define EB_ERR_UNSUPPORTED (-2) /* shape outside what the kernels are built for */
+#define EB_ERR_NOMEM (-3)       /* page pool or sequence slots exhausted (scheduler) */
+#define EB_ERR_NODEVICE (-4)    /* no sm_100 device / driver entry point missing */
+#define EB_ERR_STATE (-5)       /* call order (e.g. unknown sequence slot) */
+/* device status word bits (positive, OR-ed) */
+#define EB_DEV_WAIT_TIMEOUT 0x1000 /* a bounded wait inside a kernel gave up */
+#define EB_DEV_BAD_INDEX 0x2000    /* a page id / expert id / row index was out of range and skipped */
+
+int32_t eb_version(int32_t* abi);
+/* Message for the last non-zero return on this thread. */
+int32_t eb_last_error(char* buf, size_t n);
+
+/* ---- device memory plumbing for callers without a CUDA binding ------------------
+ * A Rust or C host needs these to own buffers without linking the CUDA runtime itself. */
+int32_t eb_device_count(int32_t* n);
+int32_t eb_device_set(int32_t device);
+int32_t eb_device_info(int32_t device, int32_t* sm_count, int64_t* l2_bytes, int64_t* hbm_bytes, int32_t* cc_major,
+                       int32_t* cc_minor);
+int32_t eb_malloc(void** d_ptr, size_t bytes);
+int32_t eb_free(void* d_ptr);
+int32_t eb_host_alloc(void** h_ptr, size_t bytes); /* pinned */
+int32_t eb_host_free(void* h_ptr);
+int32_t eb_memset(void* d_ptr, int32_t value, size_t bytes, void* stream);
+int32_t eb_copy_h2d(void* d_dst, const void* h_src, size_t bytes, void* stream);
+int32_t eb_copy_d2h(void* h_dst, const void* d_src, size_t bytes, void* stream);
+int32_t eb_copy_d2d(void* d_dst, const void* d_src, size_t bytes, void* stream);
+int32_t eb_stream_create(void** stream);
+int32_t eb_stream_destroy(void* stream);
+int32_t eb_stream_sync(void* stream);
+int32_t eb_device_sync(void);
+int32_t eb_event_create(void** ev);
+int32_t eb_event_destroy(void* ev);
+int32_t eb_event_record(void* ev, void* stream);
+int32_t eb_event_elapsed_ms(void* ev_start, void* ev_stop, float* ms); /* synchronises on ev_stop */
+/* Writes `bytes` of a scratch buffer so that the L2 holds none of the caller's tensors. */
+int32_t eb_l2_flush(void* d_scratch, size_t bytes, void* stream);
+/* Device status word (EB_DEV_* bits) accumulated by kernels since the last read; reading clears it. */
+int32_t eb_status_read(int32_t* status);
+
+/* ---- synthetic tensors (definition: eb_synth.h) ------------------------------------
+ * Fill device buffers with the seeded tensors the benchmark configurations describe. */
+int32_t eb_synth_normal_bf16(void* d_out, int64_t n, uint64_t seed, uint64_t stream_id, uint64_t idx0, float scale,
+                             void* stream);
+int32_t eb_synth_normal_f32(void* d_out, int64_t n, uint64_t seed, uint64_t stream_id, uint64_t idx0, float scale,
+                            void* stream);
+int32_t eb_synth_normal_e4m3(void* d_out, int64_t n, uint64_t seed, uint64_t stream_id, uint64_t idx0, float scale,
+                             void* stream);
+int32_t eb_synth_uniform_f32(void* d_out, int64_t n, uint64_t seed, uint64_t stream_id, uint64_t idx0, float lo,
+                             float hi, void* stream);
+/* Random-init weight band [row0, row0+nrows) x cols of a [rows_total x cols] tensor ~ N(0, std), quantised to
+ * e4m3 with per-128x128 scales.  row0 must be a multiple of 128. */
+int32_t eb_synth_weight_fp8(void* d_codes, void* d_scales, int64_t rows_total, int64_t cols, int64_t row0,
+                            int64_t nrows, uint64_t seed, uint64_t stream_id, float std, void* stream);
+
+/* ---- scheduler: continuous batching over a page pool (host only, no CUDA call) ------
+ * Nearest reference analogue: the whole-engine admission planner `plan_evictions` /
+ * `reserve_engine` (crates/eidola-app-core/src/local_models.rs:441-485, 653-701), which admits
+ * engines against a byte budget in one critical section; here the unit is a 16-token page. */
+typedef struct eb_sched eb_sched;
+
+int32_t eb_sched_create(int32_t num_pages, int32_t page_size, int32_t max_seqs, int32_t max_pages_per_seq,
+                        uint64_t seed, eb_sched** out);
+int32_t eb_sched_destroy(eb_sched* s);
+/* Admit a sequence with `context_len` tokens already to be held; returns its slot.  EB_ERR_NOMEM when the pool
+ * cannot hold it (nothing is changed, like the reference planner's refusal without eviction). */
+int32_t eb_sched_admit(eb_sched* s, int32_t context_len, int32_t* slot);
+/* Grow a sequence to `new_len` tokens, taking pages from the shuffled free list as needed. */
+int32_t eb_sched_extend(eb_sched* s, int32_t slot, int32_t new_len);
+/* Roll a sequence back to `new_len` tokens (rejected draft tokens); whole pages past the end are returned. */
+int32_t eb_sched_truncate(eb_sched* s, int32_t slot, int32_t new_len);
+int32_t eb_sched_release(eb_sched* s, int32_t slot);
+int32_t eb_sched_free_pages(const eb_sched* s, int32_t* n);
+int32_t eb_sched_seq_len(const eb_sched* s, int32_t slot, int32_t* len);
+/* Block table of all slots: [max_seqs][max_pages_per_seq] int32, unused entries -1.  The pointer stays valid
+ * until the scheduler is destroyed. */
+int32_t eb_sched_block_tables(const eb_sched* s, const int32_t** h_tables, int32_t* stride);
+/*
+ * Pack a ragged step.  For each of n_seqs sequences (slots[i], q_lens[i] new tokens, already counted in the
+ * sequence length by eb_sched_extend) write:
+ *   q_off[n_seqs+1]   exclusive prefix sum of q_lens (row offsets into the flat token arrays)
+ *   ctx_lens[n_seqs]  sequence length including the new tokens
+ *   tok_seq[T]        index i of the sequence each token row belongs to
+ *   tok_slot[T]       scheduler slot of each token row
+ *   positions[T]      absolute position of each token row
+ * Returns T through n_tokens.
+ */
+int32_t eb_sched_pack(const eb_sched* s, const int32_t* slots, const int32_t* q_lens, int32_t n_seqs, int32_t* q_off,
+                      int32_t* ctx_lens, int32_t* tok_seq, int32_t* tok_slot, int32_t* positions, int32_t* n_tokens);
+
+/* One unit of attention work: a run of logical pages of one sequence. */
+typedef struct eb_attn_item {
+  int32_t seq;        /* index into the step's sequence arrays */
+  int32_t page_begin; /* first logical page (index into the block-table row) */
+  int32_t page_end;   /* one past the last logical page */
+  int32_t part;       /* first partial-result slot this item writes */
+} eb_attn_item;
+
+/*
+ * Split-K plan for one attention launch.  Long contexts are cut into runs of at most `chunk_pages` pages
+ * (0 = choose so that about 4 items per SM exist); items are ordered longest first.
+ *   items[cap_items], seq_part[n_seqs+1] (partial-slot range of each sequence)
+ * window = 0 plans a full layer, otherwise only the pages a `window`-token sliding window can see.
+ * parts_per_item = 8 / n_kv_local (warps that share a KV head write separate partials).
+ */
+int32_t eb_attn_plan(const int32_t* ctx_lens, const int32_t* q_lens, int32_t n_seqs, int32_t page_size,
+                     int32_t window, int32_t sm_count, int32_t chunk_pages, int32_t parts_per_item,
+                     eb_attn_item* items, int32_t cap_items, int32_t* n_items, int32_t* seq_part, int32_t* n_parts);
+
+/* ---- operators (device pointers) ------------------------------------------------------ */
+
+/* K1.  Scatter new K,V rows into one layer's paged cache.
+ * d_k_new/d_v_new: [T][n_kv][head_dim] bf16, row stride in elements (>= n_kv*head_dim, multiple of 8). */
+int32_t eb_kv_append(void* d_cache, int32_t num_pages, int32_t n_kv, int32_t head_dim, int32_t page_size,
+                     const void* d_k_new, const void* d_v_new, int64_t row_stride, const int32_t* d_block_tables,
+                     int32_t bt_stride, const int32_t* d_tok_slot, const int32_t* d_positions, int32_t n_tokens,
+                     void* stream);
+
+typedef struct eb_attn_args {
+  const void* d_q;    /* [T][n_q][head_dim] bf16 */
+  int64_t q_stride;   /* elements between token rows of q */
+  void* d_out;        /* [T][n_q][head_dim] bf16 */
+  int64_t out_stride; /* elements between token rows of out */
+  const void* d_cache;
+  int32_t num_pages;
+  const int32_t* d_block_tables;
+  int32_t bt_stride;
+  const int32_t* d_seq_slots; /* [n_seqs] block-table row of each sequence */
+  const int32_t* d_q_off;     /* [n_seqs+1] */
+  const int32_t* d_ctx_lens;  /* [n_seqs] */
+  int32_t n_seqs;
+  int32_t max_q_len; /* largest q_len in the batch, 1..6 */
+  const float* d_sinks; /* [n_q] learned sink logit per query head */
+  int32_t window;       /* 0 = full attention */
+  int32_t n_q, n_kv, head_dim, page_size;
+  float scale; /* 1/sqrt(head_dim) */
+  const eb_attn_item* d_items;
+  int32_t n_items;
+  const int32_t* d_seq_part; /* [n_seqs+1] */
+  int32_t n_parts;
+  void* d_part_acc; /* fp32 [n_parts][max_q_len][n_q][head_dim] */
+  void* d_part_ml;  /* fp32 [n_parts][max_q_len][n_q][2] */
+} eb_attn_args;
+
+/* K2+K3.  Paged sink attention (decode and k>1 verify) with split-K and log-sum-exp merge. */
+int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream);
+/* Workspace sizes for the two partial buffers of eb_attn_args. */
+int32_t eb_attn_workspace(int32_t n_parts, int32_t max_q_len, int32_t n_q, int32_t head_dim, size_t* acc_bytes,
+                          size_t* ml_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EIDOLA_B200_H_ */

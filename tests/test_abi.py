@@ -1,0 +1,39 @@
+"""The C-ABI library loads on a machine without a GPU and exports every symbol the public header declares."""
+import ctypes as C
+
+import eidola_b200 as eb
+from eidola_b200 import capi
+
+
+def test_header_symbols_are_exported():
+    names = capi.declared_symbols()
+    assert len(names) >= 30
+    missing = [n for n in names if not hasattr(capi.lib(), n)]
+    assert not missing, missing
+
+
+def test_version_and_error_text():
+    v = C.c_int32(0)
+    capi.call("eb_version", C.byref(v))
+    assert v.value == 1
+    rc = capi.call_rc("eb_sched_create", C.c_int32(0), C.c_int32(16), C.c_int32(1), C.c_int32(1), C.c_uint64(0),
+                      C.byref(C.c_void_p()))
+    assert rc == -1
+    assert "eb_sched_create" in capi.last_error()
+
+
+def test_no_cpu_fallback_when_library_missing(tmp_path):
+    import pytest
+    with pytest.raises(ImportError, match="no CPU fallback"):
+        capi.load_library(tmp_path / "libeidola_b200.so")
+
+
+def test_validation_happens_before_any_launch():
+    """Host validation errors are negative and need no device."""
+    a = capi.AttnArgs()
+    rc = capi.call_rc("eb_attn_paged_sink", C.byref(a), C.c_void_p())
+    assert rc == -1 and "null" in capi.last_error()
+    rc = capi.call_rc("eb_kv_append", C.c_void_p(16), C.c_int32(4), C.c_int32(8), C.c_int32(128), C.c_int32(16),
+                      C.c_void_p(16), C.c_void_p(16), C.c_int64(512), C.c_void_p(16), C.c_int32(4), C.c_void_p(16),
+                      C.c_void_p(16), C.c_int32(1), C.c_void_p())
+    assert rc == -2 and "head_dim" in capi.last_error()
