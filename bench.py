@@ -31,6 +31,9 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 HEAD_DIM, PAGE = 64, 16
+# dram bytes read+written per launch / algorithmic bytes, from the ncu capture summarised in
+# profiles/attn_kernel_paged_sink_decode.md (64-sequence case, scaled by the bytes processed)
+NCU_TRAFFIC_RATIO_ATTN = 1.028
 S_KV, S_Q, S_SINK = 101, 102, 103
 
 
@@ -63,7 +66,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -200,7 +203,7 @@ def run_ours(args) -> dict:
     import eidola_b200 as eb
     from eidola_b200 import capi
     capi.call("eb_device_set", capi.c_i32(rank_device(rank)))
-    wl = AttnWorkload(rank)
+    wl = AttnWorkload(rank, n_seqs=args.seqs)
     K, W = args.steps, args.warmup
 
     def barrier():
@@ -210,12 +213,12 @@ def run_ours(args) -> dict:
             capi.call("eb_device_sync")
 
     # ---- device-resident throughput (value) + per-launch durations (roofline)
-    for _ in range(W):
-        wl.step()
-    barrier()
     sampler = ClockSampler(rank_device(rank))
     if rank == 0:
         sampler.start()
+    for _ in range(W):
+        wl.step()
+    barrier()
     timers = [eb.Timer() for _ in range(K)]
     total = eb.Timer()
     barrier()
@@ -271,7 +274,7 @@ def run_ours(args) -> dict:
                 "d2h_bytes_per_step": wl.e2e_d2h},
         "gpu_launches": wl.launches_per_step * K,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "traffic": None, "kernel": "attn_kernel (+ attn_merge_kernel)",
+                     "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_RATIO_ATTN * wl.alg_bytes, "kernel": "attn_kernel (+ attn_merge_kernel)",
                      "alg_bytes_per_launch": wl.alg_bytes, "avg_launch_ms": avg_launch_ms,
                      "frac_of_nominal_8TBs": achieved / 8000.0},
         "clocks": clocks,
@@ -337,10 +340,11 @@ def run_reference(args) -> dict:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--seqs", type=int, default=256, help="sequences in the batch (smaller values are for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     out = run_reference(args) if args.impl == "reference" else run_ours(args)

@@ -1,0 +1,573 @@
+// Block-scaled FP8 (e4m3) GEMM on the sm_100a tensor cores (tcgen05.mma, accumulators in tensor memory),
+// dense and grouped (one weight matrix per expert), plus the activation quantiser that feeds it.
+//
+//   Y[m][n] = bf16( sum_kb sx[blk(m)][kb] * sw[n/128][kb] * sum_{k in kb} X8[m][k] * W8[n][k] )
+//
+// Decode-shaped: the weight tile is the M operand of the MMA (128 weight rows), the tokens are the N operand
+// (TN = 16..128 columns), so a few tokens still fill a 128-wide instruction and every CTA streams a
+// 128-row band of W exactly once.  One pipeline stage is one 128-byte K block of both operands (TMA, 128-byte
+// swizzle) = one scale block: its four K=32 MMAs start a fresh accumulator in tensor memory, and four epilogue
+// warps fold finished blocks into registers with acc += (sx*sw) * block while the tensor core works on the
+// next block in the other accumulator buffer.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = tensor-memory owner and MMA issuer,
+// warps 2..5 = epilogue (tensor-memory lane quarter = warp % 4).  All waits are bounded.
+//
+// The reference project has no GEMM (inference is delegated, crates/eidola-server/src/backend.rs:421-433).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "common.h"
+#include "tmap.h"
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kTileN = 128;       // weight rows per CTA (MMA M)
+constexpr int kBlockK = 128;      // bytes = e4m3 elements per K block
+constexpr int kMaxKB = 128;       // K blocks per GEMM (K <= 16384)
+constexpr int kMaxSplitRows = 512;  // split K only for decode-sized activations
+constexpr uint32_t kWaitTries = 1u << 22;
+
+struct GemmParams {
+  const float* sx;
+  const float* sw;
+  uint16_t* y;
+  float* y_part;  // fp32 partials [splits][rows][N] when splits > 1
+  int64_t ldy;
+  int32_t rows, N, K, n_groups, splits;
+  const int32_t* seg_off;     // grouped: [n_groups+1]
+  const int32_t* blk_off;     // grouped: [n_groups+1]
+  const int32_t* tile_group;  // grouped: [max_tiles]
+  const int32_t* tile_row0;   // grouped: [max_tiles]
+  const int32_t* n_tiles;     // grouped: device scalar
+  int32_t* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+  for (uint32_t i = 0; i < kWaitTries; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) {
+      __nanosleep(64);
+      if (*abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  atomicOr(status, EB_DEV_WAIT_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// ---- tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], e4m3 x e4m3 -> fp32, M=128, N from the instruction descriptor, K=32.
+__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Shared-memory matrix descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(1024u >> 4) << 32;  // stride byte offset
+  d |= (uint64_t)1 << 46;             // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;             // SWIZZLE_128B
+  return d;
+}
+// 32 lanes x 16 consecutive 32-bit columns of tensor memory -> 16 registers per thread.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int TN>
+struct Cfg {
+  static constexpr int kStageBytes = kTileN * kBlockK + TN * kBlockK;
+  static constexpr int kStages = (TN == 128) ? 6 : 8;
+  static constexpr uint32_t kTmemCols = (2 * TN < 32) ? 32 : 2 * TN;
+  static constexpr size_t kSmem = 1024 + (size_t)kStages * kStageBytes + 256 + kMaxKB * sizeof(float);
+};
+
+template <int TN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
+  using C = Cfg<TN>;
+  constexpr int S = C::kStages;
+
+  // ---- which tile
+  int g = 0, row0, row_end, xblk;
+  if (p.n_groups > 1 || p.seg_off) {
+    const int t = blockIdx.y;
+    if (t >= *p.n_tiles) return;
+    g = p.tile_group[t];
+    row0 = p.tile_row0[t];
+    row_end = p.seg_off[g + 1];
+    xblk = p.blk_off[g] + (row0 - p.seg_off[g]) / 128;
+  } else {
+    row0 = blockIdx.y * TN;
+    row_end = p.rows;
+    xblk = row0 / 128;
+  }
+  const int nb = blockIdx.x, n0 = nb * kTileN;
+  const int KB = (p.K + kBlockK - 1) / kBlockK;
+  const int NB = (p.N + kTileN - 1) / kTileN;
+  const int split = blockIdx.z;
+  const int kb_per = (KB + p.splits - 1) / p.splits;
+  const int kb0 = split * kb_per, kb1 = min(KB, kb0 + kb_per);
+  const int nkb = max(0, kb1 - kb0);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t stage0 = (raw + 1023u) & ~1023u;
+  uint8_t* after = smem_raw + (stage0 - raw) + S * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after);  // full[S], empty[S], tfull[2], tempty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(after + (2 * S + 4) * sizeof(uint64_t));
+  float* sprod = reinterpret_cast<float*>(after + 256);
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[S]);
+  const uint32_t bar_tfull = smem_u32(&bars[2 * S]), bar_tempty = smem_u32(&bars[2 * S + 2]);
+
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+  if (tid >= 64) {
+    const float* swr = p.sw + ((int64_t)g * NB + nb) * KB;
+    const float* sxr = p.sx + (int64_t)xblk * KB;
+    for (int kb = tid - 64; kb < nkb; kb += 128) sprod[kb] = swr[kb0 + kb] * sxr[kb0 + kb];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int wy = g * p.N + n0;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % S;
+        if (i >= S && !mbar_wait(bar_empty + 8 * s, ((i / S) - 1) & 1, &abort_flag, p.status)) break;
+        const uint32_t a_dst = stage0 + s * C::kStageBytes, b_dst = a_dst + kTileN * kBlockK;
+        mbar_arrive_expect_tx(bar_full + 8 * s, C::kStageBytes);
+        tma_load_2d(a_dst, &tm_w, (kb0 + i) * kBlockK, wy, bar_full + 8 * s);
+        tma_load_2d(b_dst, &tm_x, (kb0 + i) * kBlockK, row0, bar_full + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, A and B e4m3, both K-major, N = TN, M = 128
+      constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % S, b = i & 1;
+        if (!mbar_wait(bar_full + 8 * s, (i / S) & 1, &abort_flag, p.status)) break;
+        if (i >= 2 && !mbar_wait(bar_tempty + 8 * b, ((i >> 1) - 1) & 1, &abort_flag, p.status)) break;
+        tc_fence_after();
+        const uint32_t a_addr = stage0 + s * C::kStageBytes, b_addr = a_addr + kTileN * kBlockK;
+        const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)  // 32 bytes of K per instruction: advance the start address field by 32 >> 4
+          tc_mma_f8(tmem_base + b * TN, da + 2 * k, db + 2 * k, idesc, k > 0 ? 1u : 0u);
+        tc_commit(bar_empty + 8 * s);  // stage reusable once these MMAs have read it
+        tc_commit(bar_tfull + 8 * b);  // accumulator buffer complete
+      }
+    }
+  } else {
+    // ---------------- epilogue warps: lanes [32q, 32q+32) of tensor memory = weight rows n0 + 32q + lane
+    const int q = warp & 3;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    float acc[TN];
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[j] = 0.f;
+    for (int i = 0; i < nkb; ++i) {
+      const int b = i & 1;
+      if (!mbar_wait(bar_tfull + 8 * b, (i >> 1) & 1, &abort_flag, p.status)) break;
+      tc_fence_after();
+      const float sc = sprod[i];
+#pragma unroll
+      for (int c = 0; c < TN / 16; ++c) {
+        float v[16];
+        tmem_ld16(lane_base + b * TN + c * 16, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(sc, v[j], acc[c * 16 + j]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+    }
+    const int n = n0 + q * 32 + lane;
+    if (n < p.N && !abort_flag) {
+      if (p.splits > 1) {
+        float* yp = p.y_part + ((int64_t)split * p.rows) * p.N;
+#pragma unroll
+        for (int j = 0; j < TN; ++j)
+          if (row0 + j < row_end) yp[(int64_t)(row0 + j) * p.N + n] = acc[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < TN; ++j)
+          if (row0 + j < row_end) {
+            uint32_t h;
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(0.f), "f"(acc[j]));
+            p.y[(int64_t)(row0 + j) * p.ldy + n] = (uint16_t)(h & 0xFFFFu);
+          }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
+}
+
+// Sum split-K partials in split order and round to bf16.
+__global__ void gemm_splitk_reduce_kernel(const float* part, uint16_t* y, int64_t ldy, int rows, int N, int splits) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)rows * N) return;
+  float a = 0.f;
+  for (int s = 0; s < splits; ++s) a += part[(int64_t)s * rows * N + idx];
+  uint32_t h;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(0.f), "f"(a));
+  y[(idx / N) * ldy + idx % N] = (uint16_t)(h & 0xFFFFu);
+}
+
+// Token-tile table of a grouped GEMM: for group g with rows [seg_off[g], seg_off[g+1]) emit one tile per TN rows.
+// Also the exclusive prefix of 128-row scale blocks.  One CTA; n_groups <= 1024.
+__global__ void gemm_tiles_kernel(const int32_t* seg_off, int n_groups, int tn, int max_tiles, int32_t* blk_off,
+                                  int32_t* tile_group, int32_t* tile_row0, int32_t* n_tiles, int32_t* status) {
+  __shared__ int32_t t_off[1025], b_off[1025];
+  for (int g = threadIdx.x; g < n_groups; g += blockDim.x) {
+    const int len = seg_off[g + 1] - seg_off[g];
+    t_off[g + 1] = (len + tn - 1) / tn;
+    b_off[g + 1] = (len + 127) / 128;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    t_off[0] = b_off[0] = 0;
+    for (int g = 0; g < n_groups; ++g) {
+      t_off[g + 1] += t_off[g];
+      b_off[g + 1] += b_off[g];
+    }
+    int nt = t_off[n_groups];
+    if (nt > max_tiles) {
+      atomicOr(status, EB_DEV_BAD_INDEX);
+      nt = max_tiles;
+    }
+    *n_tiles = nt;
+  }
+  __syncthreads();
+  for (int g = threadIdx.x; g <= n_groups; g += blockDim.x) blk_off[g] = b_off[g];
+  for (int g = threadIdx.x; g < n_groups; g += blockDim.x)
+    for (int t = t_off[g]; t < t_off[g + 1] && t < max_tiles; ++t) {
+      tile_group[t] = g;
+      tile_row0[t] = seg_off[g] + (t - t_off[g]) * tn;
+    }
+}
+
+// Activation quantiser: one CTA per (128-row block, 128-column block) of a bf16 matrix.
+// Thread t holds 8 rows x one 16-byte chunk; block amax -> scale -> e4m3.
+__global__ void __launch_bounds__(256)
+quant_act_kernel(const uint16_t* x, int64_t ldx, int rows, int cols, const int32_t* seg_off, int n_groups,
+                 uint8_t* codes, float* scales) {
+  const int blk = blockIdx.y, cb = blockIdx.x, n_cb = gridDim.x;
+  int r0, r1;
+  if (seg_off) {
+    // Row range of scale block `blk`: blocks restart at every segment start.  Warp 0 scans the segments 32 at a time.
+    __shared__ int s_r0, s_r1;
+    if (threadIdx.x < 32) {
+      const int lane = threadIdx.x;
+      int base = 0;
+      bool found = false;
+      for (int g0 = 0; g0 < n_groups && !found; g0 += 32) {
+        const int g = g0 + lane;
+        const int lo = g < n_groups ? seg_off[g] : 0, hi = g < n_groups ? seg_off[g + 1] : 0;
+        const int cnt = (hi - lo + 127) / 128;
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += v;
+        }
+        const int first = base + incl - cnt;
+        const bool hit = cnt > 0 && blk >= first && blk < base + incl;
+        if (hit) {
+          s_r0 = lo + (blk - first) * 128;
+          s_r1 = min(lo + (blk - first) * 128 + 128, hi);
+        }
+        found = __any_sync(0xffffffffu, hit);
+        base += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (!found && lane == 0) s_r0 = -1;
+    }
+    __syncthreads();
+    if (s_r0 < 0) return;
+    r0 = s_r0;
+    r1 = s_r1;
+  } else {
+    r0 = blk * 128;
+    r1 = min(r0 + 128, rows);
+    if (r0 >= rows) return;
+  }
+  const int c0 = cb * 128;
+  const int chunk = threadIdx.x & 15, rsub = threadIdx.x >> 4;
+  const int col = c0 + chunk * 8;
+  const bool col_ok = col < cols;  // cols is a multiple of 8
+  uint4 v[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = r0 + rsub + i * 16;
+    v[i] = make_uint4(0, 0, 0, 0);
+    if (col_ok && r < r1) v[i] = *reinterpret_cast<const uint4*>(x + (int64_t)r * ldx + col);
+    const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      amax = fmaxf(amax, fabsf(__uint_as_float(w[k] << 16)));
+      amax = fmaxf(amax, fabsf(__uint_as_float(w[k] & 0xFFFF0000u)));
+    }
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+  const float s = amax > 0.f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+  if (threadIdx.x == 0) scales[(int64_t)blk * n_cb + cb] = s;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = r0 + rsub + i * 16;
+    if (!(col_ok && r < r1)) continue;
+    const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+    uint32_t o[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      uint16_t lo16, hi16;
+      const float a0 = __fdiv_rn(__uint_as_float(w[2 * k] << 16), s);
+      const float a1 = __fdiv_rn(__uint_as_float(w[2 * k] & 0xFFFF0000u), s);
+      const float a2 = __fdiv_rn(__uint_as_float(w[2 * k + 1] << 16), s);
+      const float a3 = __fdiv_rn(__uint_as_float(w[2 * k + 1] & 0xFFFF0000u), s);
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo16) : "f"(a1), "f"(a0));
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi16) : "f"(a3), "f"(a2));
+      o[k] = (uint32_t)lo16 | ((uint32_t)hi16 << 16);
+    }
+    *reinterpret_cast<uint2*>(codes + (int64_t)r * cols + col) = make_uint2(o[0], o[1]);
+  }
+}
+
+template <int TN>
+int32_t launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, dim3 grid, cudaStream_t st) {
+  auto kfn = gemm_fp8_kernel<TN>;
+  static bool configured = false;
+  if (!configured) {
+    EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<TN>::kSmem));
+    configured = true;
+  }
+  kfn<<<grid, kThreads, Cfg<TN>::kSmem, st>>>(tw, tx, p);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int pick_tn(int64_t rows_per_group) {
+  if (rows_per_group <= 16) return 16;
+  if (rows_per_group <= 32) return 32;
+  if (rows_per_group <= 64) return 64;
+  return 128;
+}
+
+int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st) {
+  EB_REQUIRE(a->d_x8 && a->d_sx && a->d_w8 && a->d_sw && a->d_y, EB_ERR_ARG, "gemm: null pointer");
+  EB_REQUIRE(a->rows >= 0 && a->N >= 1 && a->K >= 16 && a->n_groups >= 1, EB_ERR_ARG, "gemm: bad size");
+  EB_REQUIRE(a->K % 16 == 0, EB_ERR_UNSUPPORTED, "gemm: K %d must be a multiple of 16", a->K);
+  EB_REQUIRE(a->K <= kMaxKB * kBlockK, EB_ERR_UNSUPPORTED, "gemm: K %d exceeds %d", a->K, kMaxKB * kBlockK);
+  EB_REQUIRE(a->ldy >= a->N, EB_ERR_ARG, "gemm: ldy %lld < N %d", (long long)a->ldy, a->N);
+  EB_REQUIRE(a->n_groups <= 1024, EB_ERR_UNSUPPORTED, "gemm: %d groups (at most 1024)", a->n_groups);
+  EB_REQUIRE((int64_t)a->n_groups * a->N < (1ll << 31), EB_ERR_UNSUPPORTED, "gemm: weight rows exceed a tensor map");
+  if (a->rows == 0) return EB_OK;
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "gemm: no device");
+
+  GemmParams p = {};
+  p.sx = a->d_sx;
+  p.sw = a->d_sw;
+  p.y = (uint16_t*)a->d_y;
+  p.ldy = a->ldy;
+  p.rows = a->rows;
+  p.N = a->N;
+  p.K = a->K;
+  p.n_groups = a->n_groups;
+  p.status = status;
+  p.splits = 1;
+
+  const int KB = (a->K + kBlockK - 1) / kBlockK;
+  const int nb = (a->N + kTileN - 1) / kTileN;
+  int tn, token_tiles;
+  if (grouped) {
+    EB_REQUIRE(a->d_seg_off && a->d_work, EB_ERR_ARG, "grouped gemm: null segment offsets or workspace");
+    tn = a->tile_tokens ? a->tile_tokens : pick_tn((a->rows + a->n_groups - 1) / a->n_groups);
+    EB_REQUIRE(tn == 16 || tn == 32 || tn == 64 || tn == 128, EB_ERR_ARG, "gemm: tile_tokens %d not in {16,32,64,128}", tn);
+    token_tiles = a->rows / tn + a->n_groups;
+    int32_t* w = (int32_t*)a->d_work;
+    int32_t* blk_off = w;
+    int32_t* n_tiles = w + (a->n_groups + 1);
+    int32_t* tile_group = n_tiles + 1;
+    int32_t* tile_row0 = tile_group + token_tiles;
+    gemm_tiles_kernel<<<1, 256, 0, st>>>(a->d_seg_off, a->n_groups, tn, token_tiles, blk_off, tile_group, tile_row0,
+                                         n_tiles, status);
+    EB_LAUNCH_CHECK();
+    p.seg_off = a->d_seg_off;
+    p.blk_off = blk_off;
+    p.tile_group = tile_group;
+    p.tile_row0 = tile_row0;
+    p.n_tiles = n_tiles;
+  } else {
+    tn = a->tile_tokens ? a->tile_tokens : pick_tn(a->rows);
+    EB_REQUIRE(tn == 16 || tn == 32 || tn == 64 || tn == 128, EB_ERR_ARG, "gemm: tile_tokens %d not in {16,32,64,128}", tn);
+    token_tiles = (a->rows + tn - 1) / tn;
+    // split K when the tiles alone cannot fill the GPU and the caller lent a partial buffer
+    int splits = a->splits;
+    if (splits == 0) {
+      splits = 1;
+      if (a->d_work && a->rows <= kMaxSplitRows) {
+        const int tiles = nb * token_tiles;
+        while (tiles * splits < 120 && splits * 2 <= 8 && KB / (splits * 2) >= 4) splits *= 2;
+      }
+    }
+    EB_REQUIRE(splits >= 1 && splits <= KB, EB_ERR_ARG, "gemm: splits %d outside 1..%d", splits, KB);
+    EB_REQUIRE(splits == 1 || (a->d_work && a->rows <= kMaxSplitRows && splits <= 8), EB_ERR_ARG,
+               "gemm: split K needs a workspace, at most %d rows and at most 8 splits", kMaxSplitRows);
+    p.splits = splits;
+    p.y_part = (float*)a->d_work;
+  }
+  EB_REQUIRE(token_tiles <= 65535, EB_ERR_UNSUPPORTED, "gemm: %d token tiles exceed the grid", token_tiles);
+
+  CUtensorMap tw, tx;
+  int32_t rc = eb::make_tmap_2d_sw128(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, (uint64_t)a->n_groups * a->N,
+                                      (uint64_t)a->K, (uint64_t)a->K, kTileN);
+  if (rc != EB_OK) return rc;
+  rc = eb::make_tmap_2d_sw128(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_x8, (uint64_t)a->rows, (uint64_t)a->K,
+                              (uint64_t)a->K, (uint32_t)tn);
+  if (rc != EB_OK) return rc;
+
+  const dim3 grid((unsigned)nb, (unsigned)token_tiles, (unsigned)p.splits);
+  switch (tn) {
+    case 16: rc = launch_gemm<16>(tw, tx, p, grid, st); break;
+    case 32: rc = launch_gemm<32>(tw, tx, p, grid, st); break;
+    case 64: rc = launch_gemm<64>(tw, tx, p, grid, st); break;
+    default: rc = launch_gemm<128>(tw, tx, p, grid, st); break;
+  }
+  if (rc != EB_OK) return rc;
+  if (p.splits > 1) {
+    const int64_t total = (int64_t)a->rows * a->N;
+    gemm_splitk_reduce_kernel<<<(unsigned)eb::cdiv(total, 256), 256, 0, st>>>(p.y_part, p.y, p.ldy, a->rows, a->N,
+                                                                              p.splits);
+    EB_LAUNCH_CHECK();
+  }
+  return EB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t eb_gemm_workspace(int32_t rows, int32_t N, int32_t n_groups, size_t* bytes) {
+  EB_REQUIRE(bytes && rows >= 0 && N >= 1 && n_groups >= 1, EB_ERR_ARG, "eb_gemm_workspace: bad argument");
+  // grouped: blk_off[n_groups+1], n_tiles, tile_group[max], tile_row0[max] with max = rows/16 + n_groups
+  const size_t max_tiles = (size_t)rows / 16 + n_groups;
+  const size_t tiles_bytes = sizeof(int32_t) * ((size_t)n_groups + 2 + 2 * max_tiles);
+  // dense: up to 8 split-K partials, only offered for decode-sized row counts
+  const size_t split_bytes = (n_groups == 1 && rows <= kMaxSplitRows) ? sizeof(float) * 8 * (size_t)rows * N : 0;
+  *bytes = tiles_bytes > split_bytes ? tiles_bytes : split_bytes;
+  return EB_OK;
+}
+
+int32_t eb_gemm_fp8_block(const eb_gemm_args* a, void* stream) {
+  EB_REQUIRE(a, EB_ERR_ARG, "eb_gemm_fp8_block: null args");
+  EB_REQUIRE(a->n_groups == 1, EB_ERR_ARG, "eb_gemm_fp8_block: n_groups must be 1 (use eb_gemm_fp8_grouped)");
+  return run_gemm(a, false, eb::as_stream(stream));
+}
+
+int32_t eb_gemm_fp8_grouped(const eb_gemm_args* a, void* stream) {
+  EB_REQUIRE(a, EB_ERR_ARG, "eb_gemm_fp8_grouped: null args");
+  return run_gemm(a, true, eb::as_stream(stream));
+}
+
+int32_t eb_quant_act_block128(const void* d_x, int64_t ldx, int32_t rows, int32_t cols, const int32_t* d_seg_off,
+                              int32_t n_groups, void* d_codes, void* d_scales, void* stream) {
+  EB_REQUIRE(d_x && d_codes && d_scales, EB_ERR_ARG, "eb_quant_act_block128: null pointer");
+  EB_REQUIRE(rows >= 0 && cols >= 8 && cols % 8 == 0 && ldx >= cols && ldx % 8 == 0, EB_ERR_ARG,
+             "eb_quant_act_block128: cols %d / ldx %lld must be multiples of 8", cols, (long long)ldx);
+  EB_REQUIRE(n_groups >= 1, EB_ERR_ARG, "eb_quant_act_block128: n_groups %d", n_groups);
+  EB_REQUIRE(((uintptr_t)d_x % 16 == 0) && ((uintptr_t)d_codes % 8 == 0), EB_ERR_ARG, "eb_quant_act_block128: alignment");
+  if (rows == 0) return EB_OK;
+  const int n_blk = d_seg_off ? rows / 128 + n_groups : (rows + 127) / 128;
+  EB_REQUIRE(n_blk <= 65535, EB_ERR_UNSUPPORTED, "eb_quant_act_block128: %d row blocks exceed the grid", n_blk);
+  const dim3 grid((unsigned)((cols + 127) / 128), (unsigned)n_blk);
+  quant_act_kernel<<<grid, 256, 0, eb::as_stream(stream)>>>((const uint16_t*)d_x, ldx, rows, cols, d_seg_off,
+                                                            n_groups, (uint8_t*)d_codes, (float*)d_scales);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+}  // extern "C"

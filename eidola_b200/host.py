@@ -5,7 +5,7 @@ import ctypes as C
 
 import numpy as np
 
-from .capi import (AttnArgs, AttnItem, DeviceBuffer, call, c_f32, c_i32, c_i64, c_sz, c_u64, c_vp, ptr)
+from .capi import (AttnArgs, AttnItem, GemmArgs, DeviceBuffer, call, c_f32, c_i32, c_i64, c_sz, c_u64, c_vp, ptr)
 
 I32 = np.int32
 
@@ -143,3 +143,25 @@ class AttnLaunch:
 
     def run(self, stream=None) -> None:
         attn_paged_sink(self.args, stream)
+
+
+def quant_act_block128(d_x, ldx, rows, cols, d_codes, d_scales, d_seg_off=None, n_groups=1, stream=None) -> None:
+    call("eb_quant_act_block128", c_vp(d_x), c_i64(ldx), c_i32(rows), c_i32(cols), c_vp(d_seg_off), c_i32(n_groups),
+         c_vp(d_codes), c_vp(d_scales), c_vp(stream))
+
+
+def gemm_workspace(rows, N, n_groups) -> int:
+    b = c_sz(0)
+    call("eb_gemm_workspace", c_i32(rows), c_i32(N), c_i32(n_groups), C.byref(b))
+    return int(b.value)
+
+
+def gemm_fp8(d_x8, d_sx, d_w8, d_sw, d_y, rows, N, K, *, ldy=None, n_groups=1, d_seg_off=None, d_work=None,
+             tile_tokens=0, splits=0, stream=None) -> None:
+    """eb_gemm_fp8_block (n_groups == 1, no segments) or eb_gemm_fp8_grouped."""
+    a = GemmArgs()
+    a.d_x8, a.d_sx, a.d_w8, a.d_sw, a.d_y = d_x8, d_sx, d_w8, d_sw, d_y
+    a.ldy = N if ldy is None else ldy
+    a.rows, a.N, a.K, a.n_groups = rows, N, K, n_groups
+    a.d_seg_off, a.d_work, a.tile_tokens, a.splits = d_seg_off, d_work, tile_tokens, splits
+    call("eb_gemm_fp8_grouped" if d_seg_off is not None else "eb_gemm_fp8_block", C.byref(a), c_vp(stream))

@@ -198,6 +198,35 @@ int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream);
 int32_t eb_attn_workspace(int32_t n_parts, int32_t max_q_len, int32_t n_q, int32_t head_dim, size_t* acc_bytes,
                           size_t* ml_bytes);
 
+/* K8 (part).  Quantise bf16 activations to e4m3 with one fp32 scale per (128-row block, 128-column block).
+ * Dense: d_seg_off = NULL, blocks are rows [128b, 128b+128).  Grouped: rows are grouped in n_groups segments
+ * d_seg_off[n_groups+1] (device) and blocks restart at every segment start, numbered consecutively over the
+ * segments.  d_scales: [n_blocks][ceil(cols/128)], n_blocks <= rows/128 + n_groups. */
+int32_t eb_quant_act_block128(const void* d_x, int64_t ldx, int32_t rows, int32_t cols, const int32_t* d_seg_off,
+                              int32_t n_groups, void* d_codes, void* d_scales, void* stream);
+
+typedef struct eb_gemm_args {
+  const void* d_x8;  /* [rows][K] e4m3 activations */
+  const float* d_sx; /* [row blocks][ceil(K/128)] */
+  const void* d_w8;  /* [n_groups][N][K] e4m3 weights */
+  const float* d_sw; /* [n_groups][ceil(N/128)][ceil(K/128)] */
+  void* d_y;         /* [rows][N] bf16 */
+  int64_t ldy;       /* elements between rows of y */
+  int32_t rows, N, K;
+  int32_t n_groups;           /* 1 = dense */
+  const int32_t* d_seg_off;   /* grouped: [n_groups+1] row range of each group (device) */
+  void* d_work;               /* eb_gemm_workspace() bytes; dense: optional (enables split K) */
+  int32_t tile_tokens;        /* 0 = choose; else 16, 32, 64 or 128 tokens per tile */
+  int32_t splits;             /* dense: 0 = choose, else K splits (needs d_work) */
+} eb_gemm_args;
+
+/* K4.  Y = X * W^T, e4m3 x e4m3 -> fp32 with per-128x128 block scales, bf16 out (tcgen05 tensor cores). */
+int32_t eb_gemm_fp8_block(const eb_gemm_args* a, void* stream);
+/* K6.  The same per group g on rows [d_seg_off[g], d_seg_off[g+1]) with weights W[g]; activation scale blocks
+ * restart at each segment start (the numbering eb_quant_act_block128 uses). */
+int32_t eb_gemm_fp8_grouped(const eb_gemm_args* a, void* stream);
+int32_t eb_gemm_workspace(int32_t rows, int32_t N, int32_t n_groups, size_t* bytes);
+
 #ifdef __cplusplus
 }
 #endif
