@@ -53,6 +53,31 @@ class GemmArgs(C.Structure):
     ]
 
 
+class Config(C.Structure):
+    """eb_config."""
+    _fields_ = [
+        ("n_layers", c_i32), ("hidden", c_i32), ("n_q_heads", c_i32), ("n_kv_heads", c_i32), ("head_dim", c_i32),
+        ("window", c_i32),
+        ("n_experts", c_i32), ("top_k", c_i32), ("inter", c_i32), ("vocab", c_i32),
+        ("page_size", c_i32), ("num_pages", c_i32), ("max_seqs", c_i32), ("max_pages_per_seq", c_i32),
+        ("max_tokens", c_i32), ("max_q_len", c_i32),
+        ("rope_theta", c_f32), ("rms_eps", c_f32), ("init_std", c_f32),
+        ("seed", c_u64),
+        ("debug", c_i32),
+    ]
+
+
+def make_config(**kw) -> "Config":
+    """eb_config with the defaults of the benchmark family (head_dim 64, page 16, window 128, top-4, std 0.02)."""
+    d = dict(head_dim=64, window=128, top_k=4, page_size=16, max_q_len=1, rope_theta=150000.0, rms_eps=1e-5,
+             init_std=0.02, seed=0, debug=0)
+    d.update(kw)
+    c = Config()
+    for k, v in d.items():
+        setattr(c, k, v)
+    return c
+
+
 def declared_symbols(header: Path = HEADER) -> list[str]:
     """Every function the public header declares."""
     text = header.read_text()

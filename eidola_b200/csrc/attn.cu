@@ -10,7 +10,8 @@
 // one page when the rank holds 8 KV heads, 8/n_kv pages otherwise.  Compute warp w owns KV head w % n_kv of
 // page w / n_kv of each stage: S = Q K^T and O += P V on mma.sync m16n8k16 (bf16 in, fp32 accumulate), rows of
 // the M tile = (query position, query head of the GQA group), online softmax in base 2 with quad shuffles.
-// The kernel is HBM-bound: per 2 KiB of K and 2 KiB of V a warp issues 16 MMAs.
+// P is fed to the second MMA as a bf16 head plus a bf16 remainder (two MMAs), so the result carries about 16
+// bits of the softmax weights.  The kernel is HBM-bound: per 2 KiB of K and 2 KiB of V a warp issues 24 MMAs.
 //
 // The sink logit enters the softmax denominator exactly once: in the kernel epilogue when a sequence has a
 // single partial, otherwise in attn_merge_kernel, which combines split-K partials (m, l, acc) by log-sum-exp.
@@ -26,7 +27,6 @@ namespace {
 
 constexpr int kHeadDim = 64;
 constexpr int kPage = 16;
-constexpr int kGroup = 8;            // query heads per KV head
 constexpr int kComputeWarps = 8;
 constexpr int kThreads = (kComputeWarps + 1) * 32;
 constexpr int kStageBytes = 32768;   // 256 rows of 128 bytes
@@ -119,9 +119,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return r;
 }
 
-// MT  : 16-row M tiles = ceil(max_q_len * 8 / 16)
+// MT  : 16-row M tiles = ceil(max_q_len * G / 16)
 // HKV : KV heads held by this rank (8, 4, 2 or 1)
-template <int MT, int HKV, int STAGES>
+// G   : query heads per KV head (8 or 4); row r of the M tiles = (query position r / G, head r % G of the group)
+template <int MT, int HKV, int STAGES, int G>
 __global__ void __launch_bounds__(kThreads, (MT == 1) ? 2 : 1)
 attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
   constexpr int PPS = kComputeWarps / HKV;       // pages per stage
@@ -192,7 +193,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     // ---------------- consumers
     const int hk = warp % HKV;   // KV head of this warp
     const int sub = warp / HKV;  // page of the stage this warp takes
-    const int g = lane >> 2, tq = lane & 3;
+    const int tq = lane & 3;
 
     // Q fragments (A operand): rows = (query position, head of the group), kept in registers.
     uint32_t qf[MT][4][4];
@@ -200,8 +201,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int qi = mt * 2 + half;
-        const uint16_t* qrow = p.q + (int64_t)(q0 + qi) * p.q_stride + (int64_t)(hk * kGroup + g) * kHeadDim;
+        const int row = mt * 16 + half * 8 + (lane >> 2);
+        const int qi = row / G;
+        const uint16_t* qrow = p.q + (int64_t)(q0 + qi) * p.q_stride + (int64_t)(hk * G + row % G) * kHeadDim;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           uint32_t lo = 0, hi = 0;
@@ -256,12 +258,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
           }
         }
 
-        uint32_t pa[MT][4];
+        uint32_t pa[MT][4], pb[MT][4];  // P = pa + pb: bf16 head and bf16 remainder, so P V keeps ~16 bits of P
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
-            const int pq = L - ql + mt * 2 + half;  // absolute position of this row's query
+            const int pq = L - ql + (mt * 16 + half * 8 + (lane >> 2)) / G;  // absolute position of this row's query
             const int lo = p.window > 0 ? pq - p.window + 1 : 0;
             float v[2][2];
             float mx = kNegBig;
@@ -294,8 +296,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
               o[mt][nt][half * 2 + 0] *= alpha;
               o[mt][nt][half * 2 + 1] *= alpha;
             }
-            pa[mt][half] = pack_bf16(v[0][0], v[0][1]);      // a0 / a1: tokens 0-7
-            pa[mt][2 + half] = pack_bf16(v[1][0], v[1][1]);  // a2 / a3: tokens 8-15
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {  // a0 / a1: tokens 0-7, a2 / a3: tokens 8-15
+              const uint32_t hi = pack_bf16(v[nt][0], v[nt][1]);
+              pa[mt][2 * nt + half] = hi;
+              pb[mt][2 * nt + half] = pack_bf16(v[nt][0] - __uint_as_float(hi << 16), v[nt][1] - __uint_as_float(hi & 0xFFFF0000u));
+            }
           }
         }
 
@@ -307,6 +313,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
           for (int mt = 0; mt < MT; ++mt) {
             mma_bf16(o[mt][dp * 2], pa[mt], b[0], b[1]);
             mma_bf16(o[mt][dp * 2 + 1], pa[mt], b[2], b[3]);
+            mma_bf16(o[mt][dp * 2], pb[mt], b[0], b[1]);
+            mma_bf16(o[mt][dp * 2 + 1], pb[mt], b[2], b[3]);
           }
         }
       }
@@ -322,12 +330,13 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int qi = mt * 2 + half;
+        const int row = mt * 16 + half * 8 + (lane >> 2);
+        const int qi = row / G;
         float l = l_run[mt][half];
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         if (qi >= ql) continue;
-        const int head = hk * kGroup + g;
+        const int head = hk * G + row % G;
         const float m = m_run[mt][half];
         if (direct) {
           const float sk = p.sinks[head] * 1.4426950408889634f;
@@ -370,7 +379,8 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
   const int seq = blockIdx.x;
   const int pb = p.seq_part[seq], pe = p.seq_part[seq + 1];
   if (pe - pb <= 1) return;  // written directly by attn_kernel
-  const int head = blockIdx.y * kGroup + (threadIdx.x >> 5);
+  const int head = blockIdx.y * 8 + (threadIdx.x >> 5);
+  if (head >= p.n_q) return;
   const int lane = threadIdx.x & 31;
   const int q0 = p.q_off[seq], ql = p.q_off[seq + 1] - q0;
   const float sk = p.sinks[head] * 1.4426950408889634f;
@@ -437,10 +447,10 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int MT, int HKV, int STAGES>
+template <int MT, int HKV, int STAGES, int G>
 int32_t launch_attn(const CUtensorMap& tm, const AttnParams& p, int n_items, cudaStream_t st) {
   const size_t smem = 1024 + (size_t)STAGES * kStageBytes + 2 * STAGES * sizeof(uint64_t) + kMaxItemPages * sizeof(int32_t);
-  auto kfn = attn_kernel<MT, HKV, STAGES>;
+  auto kfn = attn_kernel<MT, HKV, STAGES, G>;
   static bool configured = false;
   if (!configured) {
     EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -451,14 +461,14 @@ int32_t launch_attn(const CUtensorMap& tm, const AttnParams& p, int n_items, cud
   return EB_OK;
 }
 
-template <int MT>
+template <int MT, int G>
 int32_t dispatch_hkv(int n_kv, const CUtensorMap& tm, const AttnParams& p, int n_items, cudaStream_t st) {
   constexpr int ST = (MT == 1) ? 3 : 6;
   switch (n_kv) {
-    case 8: return launch_attn<MT, 8, ST>(tm, p, n_items, st);
-    case 4: return launch_attn<MT, 4, ST>(tm, p, n_items, st);
-    case 2: return launch_attn<MT, 2, ST>(tm, p, n_items, st);
-    case 1: return launch_attn<MT, 1, ST>(tm, p, n_items, st);
+    case 8: return launch_attn<MT, 8, ST, G>(tm, p, n_items, st);
+    case 4: return launch_attn<MT, 4, ST, G>(tm, p, n_items, st);
+    case 2: return launch_attn<MT, 2, ST, G>(tm, p, n_items, st);
+    case 1: return launch_attn<MT, 1, ST, G>(tm, p, n_items, st);
   }
   return eb::fail(EB_ERR_UNSUPPORTED, "attention: n_kv %d not in {1,2,4,8}", n_kv);
 }
@@ -508,10 +518,11 @@ int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
              EB_ERR_ARG, "eb_attn_paged_sink: null pointer");
   EB_REQUIRE(a->head_dim == kHeadDim && a->page_size == kPage, EB_ERR_UNSUPPORTED,
              "eb_attn_paged_sink: head_dim %d / page_size %d (built for 64 / 16)", a->head_dim, a->page_size);
-  EB_REQUIRE(a->n_kv >= 1 && a->n_q == a->n_kv * kGroup, EB_ERR_UNSUPPORTED,
-             "eb_attn_paged_sink: %d query heads over %d KV heads (built for groups of 8)", a->n_q, a->n_kv);
-  EB_REQUIRE(a->max_q_len >= 1 && a->max_q_len <= 6, EB_ERR_UNSUPPORTED, "eb_attn_paged_sink: max_q_len %d not in 1..6",
-             a->max_q_len);
+  EB_REQUIRE(a->n_kv >= 1 && (a->n_q == a->n_kv * 8 || a->n_q == a->n_kv * 4), EB_ERR_UNSUPPORTED,
+             "eb_attn_paged_sink: %d query heads over %d KV heads (built for groups of 8 or 4)", a->n_q, a->n_kv);
+  const int group = a->n_q / a->n_kv;
+  EB_REQUIRE(a->max_q_len >= 1 && a->max_q_len * group <= 48, EB_ERR_UNSUPPORTED,
+             "eb_attn_paged_sink: max_q_len %d exceeds %d", a->max_q_len, 48 / group);
   EB_REQUIRE(a->n_seqs >= 0 && a->n_items >= 0 && a->n_parts >= 0 && a->num_pages >= 1 && a->window >= 0, EB_ERR_ARG,
              "eb_attn_paged_sink: negative size");
   EB_REQUIRE(a->q_stride % 2 == 0 && a->out_stride % 2 == 0 && (uintptr_t)a->d_q % 4 == 0 && (uintptr_t)a->d_out % 4 == 0,
@@ -559,17 +570,26 @@ int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
   EB_REQUIRE(p.status, EB_ERR_NODEVICE, "eb_attn_paged_sink: no device");
 
   cudaStream_t st = eb::as_stream(stream);
-  const int mt = (a->max_q_len * kGroup + 15) / 16;
+  const int mt = (a->max_q_len * group + 15) / 16;
   int32_t rc;
-  if (mt == 1)
-    rc = dispatch_hkv<1>(a->n_kv, tm, p, a->n_items, st);
-  else if (mt == 2)
-    rc = dispatch_hkv<2>(a->n_kv, tm, p, a->n_items, st);
-  else
-    rc = dispatch_hkv<3>(a->n_kv, tm, p, a->n_items, st);
+  if (group == 8) {
+    if (mt == 1)
+      rc = dispatch_hkv<1, 8>(a->n_kv, tm, p, a->n_items, st);
+    else if (mt == 2)
+      rc = dispatch_hkv<2, 8>(a->n_kv, tm, p, a->n_items, st);
+    else
+      rc = dispatch_hkv<3, 8>(a->n_kv, tm, p, a->n_items, st);
+  } else {
+    if (mt == 1)
+      rc = dispatch_hkv<1, 4>(a->n_kv, tm, p, a->n_items, st);
+    else if (mt == 2)
+      rc = dispatch_hkv<2, 4>(a->n_kv, tm, p, a->n_items, st);
+    else
+      rc = dispatch_hkv<3, 4>(a->n_kv, tm, p, a->n_items, st);
+  }
   if (rc != EB_OK) return rc;
   if (a->n_parts > a->n_seqs) {  // at least one sequence has more than one partial
-    attn_merge_kernel<<<dim3((unsigned)a->n_seqs, (unsigned)a->n_kv), 256, 0, st>>>(p);
+    attn_merge_kernel<<<dim3((unsigned)a->n_seqs, (unsigned)((a->n_q + 7) / 8)), 256, 0, st>>>(p);
     EB_LAUNCH_CHECK();
   }
   return EB_OK;

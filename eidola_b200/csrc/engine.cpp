@@ -1,0 +1,698 @@
+// The decode engine: owns weights (random-init from a seed, generated on the device), the paged KV cache of
+// every layer, the page scheduler and the step workspaces, and runs one ragged decode / verify step through the
+// library's own kernels.  Host code only; every kernel is reached through the operator entry points.
+//
+// Layer (l even: sliding window, l odd: full attention):
+//   h = rmsnorm(x) -> e4m3 -> QKV GEMM -> rotary(q, k) -> KV append -> paged sink attention -> e4m3 -> O GEMM
+//   -> x += o -> h = rmsnorm(x) -> router top-k -> permute -> gather+e4m3 -> W1 grouped GEMM -> silu(gate)*up
+//   -> e4m3 -> W2 grouped GEMM -> x += combine.   After the last layer: rmsnorm -> e4m3 -> LM head -> argmax.
+//
+// Per step the host builds ONE pinned staging block (token ids, packing arrays, block-table patches, the two
+// attention plans) and copies it with one transfer; results come back in one transfer.
+//
+// What would sit above this in the reference: the loopback HTTP client of a local engine
+// (crates/eidola-app-core/src/lib.rs:7155-7163) or a `ChatBackend` (crates/eidola-server/src/backend.rs:87-108).
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+#include <vector>
+
+#include "common.h"
+
+namespace {
+
+inline uint64_t sid(int layer, int kind, int expert) {
+  return ((uint64_t)(layer + 1) << 20) | ((uint64_t)kind << 12) | (uint64_t)expert;
+}
+enum { K_WQKV = 1, K_WO = 2, K_ROUTER = 3, K_W1 = 4, K_W2 = 5, K_SINK = 6, K_EMBED = 1, K_LMHEAD = 2 };
+
+struct Fp8Weight {
+  uint8_t* codes = nullptr;
+  float* scales = nullptr;
+};
+
+struct Layer {
+  Fp8Weight wqkv, wo, w1, w2;
+  uint16_t* wr = nullptr;
+  float* sinks = nullptr;
+  float *g_attn = nullptr, *g_mlp = nullptr;
+  uint16_t* cache = nullptr;
+};
+
+struct Plan {
+  std::vector<eb_attn_item> items;
+  std::vector<int32_t> seq_part;
+  int32_t n_items = 0, n_parts = 0;
+};
+
+}  // namespace
+
+struct eb_engine {
+  eb_config c;
+  int sm_count = 0;
+  int nqkv = 0, hqd = 0, kbH = 0, kbI = 0, kbA = 0;
+  std::vector<Layer> layers;
+  uint16_t* embed = nullptr;
+  Fp8Weight lm;
+  float* g_final = nullptr;
+  float *rope_cos = nullptr, *rope_sin = nullptr;
+  eb_sched* sched = nullptr;
+  std::vector<int32_t> uploaded_pages;  // block-table entries of each slot already on the device
+  int32_t* d_bt = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  std::vector<void*> allocs;
+  int64_t weight_bytes = 0, kv_bytes = 0, work_bytes = 0;
+
+  // step workspaces
+  uint16_t *x = nullptr, *h = nullptr, *qkv = nullptr, *attn = nullptr, *o = nullptr, *gu = nullptr, *y = nullptr,
+           *logits = nullptr;
+  uint8_t *h8 = nullptr, *a8 = nullptr, *xp8 = nullptr, *act8 = nullptr;
+  float *sh = nullptr, *sa = nullptr, *sxp = nullptr, *sact = nullptr;
+  int32_t *r_idx = nullptr, *seg_off = nullptr, *perm_row = nullptr, *row_token = nullptr;
+  float* r_wts = nullptr;
+  void *gemm_ws = nullptr, *group_ws = nullptr;
+  float *part_acc = nullptr, *part_ml = nullptr;
+  int32_t* d_next = nullptr;
+  float* d_margin = nullptr;
+  int32_t *h_stage = nullptr, *d_stage = nullptr;
+  size_t stage_words = 0;
+  int32_t* h_result = nullptr;  // pinned: next[T] then margin[T]
+  int32_t cap_items = 0;
+  // debug
+  int32_t* dbg_route = nullptr;
+  uint16_t* dbg_hidden = nullptr;
+  uint16_t* dbg_force = nullptr;       // [n_layers+1][max_tokens][hidden]: residual stream to impose before a layer
+  std::vector<int32_t> force_rows;     // rows imposed before each layer (0 = none)
+
+  // state of the step in flight
+  int32_t cur_T = 0;
+  bool in_flight = false;
+  int32_t launches = 0;
+  float last_ms = 0.f;
+};
+
+namespace {
+
+#define EB_TRY(expr)            \
+  do {                          \
+    int32_t _rc = (expr);       \
+    if (_rc != EB_OK) return _rc; \
+  } while (0)
+
+template <typename T>
+int32_t dev_alloc(eb_engine* e, T** p, size_t count, int64_t* tally) {
+  void* q = nullptr;
+  const size_t bytes = std::max<size_t>(count * sizeof(T), 16);
+  cudaError_t err = cudaMalloc(&q, bytes);
+  if (err != cudaSuccess) return eb::fail((int32_t)err, "engine: cudaMalloc of %zu bytes: %s", bytes, cudaGetErrorString(err));
+  e->allocs.push_back(q);
+  *p = (T*)q;
+  *tally += (int64_t)bytes;
+  return EB_OK;
+}
+
+int32_t alloc_fp8(eb_engine* e, Fp8Weight* w, int64_t groups, int64_t rows, int64_t cols) {
+  EB_TRY(dev_alloc(e, &w->codes, (size_t)(groups * rows * cols), &e->weight_bytes));
+  EB_TRY(dev_alloc(e, &w->scales, (size_t)(groups * eb::cdiv(rows, 128) * eb::cdiv(cols, 128)), &e->weight_bytes));
+  return EB_OK;
+}
+
+int32_t fill_ones(eb_engine* e, float* d, int n) {
+  std::vector<float> ones((size_t)n, 1.0f);
+  EB_CUDA(cudaMemcpyAsync(d, ones.data(), (size_t)n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+  EB_CUDA(cudaStreamSynchronize(e->stream));
+  return EB_OK;
+}
+
+int32_t init_weights(eb_engine* e) {
+  const eb_config& c = e->c;
+  const int H = c.hidden, I = c.inter, E = c.n_experts;
+  void* st = e->stream;
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer& L = e->layers[(size_t)l];
+    EB_TRY(alloc_fp8(e, &L.wqkv, 1, e->nqkv, H));
+    EB_TRY(alloc_fp8(e, &L.wo, 1, H, e->hqd));
+    EB_TRY(alloc_fp8(e, &L.w1, E, 2 * I, H));
+    EB_TRY(alloc_fp8(e, &L.w2, E, H, I));
+    EB_TRY(dev_alloc(e, &L.wr, (size_t)E * H, &e->weight_bytes));
+    EB_TRY(dev_alloc(e, &L.sinks, (size_t)c.n_q_heads, &e->weight_bytes));
+    EB_TRY(dev_alloc(e, &L.g_attn, (size_t)H, &e->weight_bytes));
+    EB_TRY(dev_alloc(e, &L.g_mlp, (size_t)H, &e->weight_bytes));
+    EB_TRY(eb_synth_weight_fp8(L.wqkv.codes, L.wqkv.scales, e->nqkv, H, 0, e->nqkv, c.seed, sid(l, K_WQKV, 0), c.init_std, st));
+    EB_TRY(eb_synth_weight_fp8(L.wo.codes, L.wo.scales, H, e->hqd, 0, H, c.seed, sid(l, K_WO, 0), c.init_std, st));
+    const int64_t s1 = eb::cdiv(2 * I, 128) * e->kbH, s2 = eb::cdiv(H, 128) * e->kbI;
+    for (int x = 0; x < E; ++x) {
+      EB_TRY(eb_synth_weight_fp8(L.w1.codes + (int64_t)x * 2 * I * H, L.w1.scales + x * s1, 2 * I, H, 0, 2 * I, c.seed,
+                                 sid(l, K_W1, x), c.init_std, st));
+      EB_TRY(eb_synth_weight_fp8(L.w2.codes + (int64_t)x * H * I, L.w2.scales + x * s2, H, I, 0, H, c.seed,
+                                 sid(l, K_W2, x), c.init_std, st));
+    }
+    EB_TRY(eb_synth_normal_bf16(L.wr, (int64_t)E * H, c.seed, sid(l, K_ROUTER, 0), 0, c.init_std, st));
+    EB_TRY(eb_synth_normal_f32(L.sinks, c.n_q_heads, c.seed, sid(l, K_SINK, 0), 0, 1.0f, st));
+    EB_TRY(fill_ones(e, L.g_attn, H));
+    EB_TRY(fill_ones(e, L.g_mlp, H));
+  }
+  EB_TRY(dev_alloc(e, &e->embed, (size_t)c.vocab * H, &e->weight_bytes));
+  EB_TRY(eb_synth_normal_bf16(e->embed, (int64_t)c.vocab * H, c.seed, sid(-1, K_EMBED, 0), 0, c.init_std, st));
+  EB_TRY(alloc_fp8(e, &e->lm, 1, c.vocab, H));
+  EB_TRY(eb_synth_weight_fp8(e->lm.codes, e->lm.scales, c.vocab, H, 0, c.vocab, c.seed, sid(-1, K_LMHEAD, 0), c.init_std, st));
+  EB_TRY(dev_alloc(e, &e->g_final, (size_t)H, &e->weight_bytes));
+  EB_TRY(fill_ones(e, e->g_final, H));
+  // rotary table
+  const int max_pos = c.max_pages_per_seq * c.page_size;
+  const size_t n = (size_t)max_pos * (c.head_dim / 2);
+  std::vector<float> hc(n), hs(n);
+  EB_TRY(eb_rope_table(max_pos, c.head_dim, (double)c.rope_theta, hc.data(), hs.data()));
+  EB_TRY(dev_alloc(e, &e->rope_cos, n, &e->weight_bytes));
+  EB_TRY(dev_alloc(e, &e->rope_sin, n, &e->weight_bytes));
+  EB_CUDA(cudaMemcpyAsync(e->rope_cos, hc.data(), n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+  EB_CUDA(cudaMemcpyAsync(e->rope_sin, hs.data(), n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+  EB_CUDA(cudaStreamSynchronize(e->stream));
+  return EB_OK;
+}
+
+int32_t init_work(eb_engine* e) {
+  const eb_config& c = e->c;
+  const int H = c.hidden, I = c.inter, E = c.n_experts, T = c.max_tokens;
+  const int64_t R = (int64_t)T * c.top_k;
+  int64_t* w = &e->work_bytes;
+  EB_TRY(dev_alloc(e, &e->x, (size_t)T * H, w));
+  EB_TRY(dev_alloc(e, &e->h, (size_t)T * H, w));
+  EB_TRY(dev_alloc(e, &e->qkv, (size_t)T * e->nqkv, w));
+  EB_TRY(dev_alloc(e, &e->attn, (size_t)T * e->hqd, w));
+  EB_TRY(dev_alloc(e, &e->o, (size_t)T * H, w));
+  EB_TRY(dev_alloc(e, &e->gu, (size_t)R * 2 * I, w));
+  EB_TRY(dev_alloc(e, &e->y, (size_t)R * H, w));
+  EB_TRY(dev_alloc(e, &e->logits, (size_t)T * c.vocab, w));
+  EB_TRY(dev_alloc(e, &e->h8, (size_t)T * H, w));
+  EB_TRY(dev_alloc(e, &e->a8, (size_t)T * e->hqd, w));
+  EB_TRY(dev_alloc(e, &e->xp8, (size_t)R * H, w));
+  EB_TRY(dev_alloc(e, &e->act8, (size_t)R * I, w));
+  const int64_t tb = eb::cdiv(T, 128), rb = R / 128 + E;
+  EB_TRY(dev_alloc(e, &e->sh, (size_t)(tb * e->kbH), w));
+  EB_TRY(dev_alloc(e, &e->sa, (size_t)(tb * e->kbA), w));
+  EB_TRY(dev_alloc(e, &e->sxp, (size_t)(rb * e->kbH), w));
+  EB_TRY(dev_alloc(e, &e->sact, (size_t)(rb * e->kbI), w));
+  EB_TRY(dev_alloc(e, &e->r_idx, (size_t)R, w));
+  EB_TRY(dev_alloc(e, &e->r_wts, (size_t)R, w));
+  EB_TRY(dev_alloc(e, &e->seg_off, (size_t)E + 1, w));
+  EB_TRY(dev_alloc(e, &e->perm_row, (size_t)R, w));
+  EB_TRY(dev_alloc(e, &e->row_token, (size_t)R, w));
+  size_t ws = 0, ws2 = 0;
+  const int nmax = std::max(std::max(e->nqkv, H), 1);
+  EB_TRY(eb_gemm_workspace(T, nmax, 1, &ws));
+  uint8_t* p8 = nullptr;
+  EB_TRY(dev_alloc(e, &p8, ws, w));
+  e->gemm_ws = p8;
+  EB_TRY(eb_gemm_workspace((int32_t)R, 2 * I, std::max(E, 2), &ws2));
+  EB_TRY(dev_alloc(e, &p8, ws2, w));
+  e->group_ws = p8;
+  e->cap_items = 4 * e->sm_count + c.max_seqs + 16;
+  const int ppi = 8 / c.n_kv_heads;
+  size_t acc_b = 0, ml_b = 0;
+  EB_TRY(eb_attn_workspace(e->cap_items * ppi, c.max_q_len, c.n_q_heads, c.head_dim, &acc_b, &ml_b));
+  EB_TRY(dev_alloc(e, &e->part_acc, acc_b / sizeof(float), w));
+  EB_TRY(dev_alloc(e, &e->part_ml, ml_b / sizeof(float), w));
+  EB_TRY(dev_alloc(e, &e->d_next, (size_t)T, w));
+  EB_TRY(dev_alloc(e, &e->d_margin, (size_t)T, w));
+  EB_TRY(dev_alloc(e, &e->d_bt, (size_t)c.max_seqs * c.max_pages_per_seq, w));
+  EB_CUDA(cudaMemsetAsync(e->d_bt, 0xFF, (size_t)c.max_seqs * c.max_pages_per_seq * sizeof(int32_t), e->stream));
+  // staging: tokens, tok_slot, positions [T each]; slots, ctx_lens [S]; q_off [S+1]; patches 3*P (P <= all pages of
+  // newly admitted sequences: bounded by max_seqs*max_pages); two plans (items 4 words each + seq_part)
+  const size_t S = (size_t)c.max_seqs;
+  e->stage_words = 3 * (size_t)T + 3 * S + 1 + 3 * S * (size_t)c.max_pages_per_seq + 2 * (4 * (size_t)e->cap_items + S + 1) + 64;
+  EB_CUDA(cudaMallocHost((void**)&e->h_stage, e->stage_words * sizeof(int32_t)));
+  EB_TRY(dev_alloc(e, &e->d_stage, e->stage_words, w));
+  EB_CUDA(cudaMallocHost((void**)&e->h_result, 2 * (size_t)T * sizeof(int32_t)));
+  if (c.debug) {
+    EB_TRY(dev_alloc(e, &e->dbg_route, (size_t)c.n_layers * R, w));
+    EB_TRY(dev_alloc(e, &e->dbg_hidden, (size_t)(c.n_layers + 1) * T * H, w));
+    EB_TRY(dev_alloc(e, &e->dbg_force, (size_t)(c.n_layers + 1) * T * H, w));
+    e->force_rows.assign((size_t)c.n_layers + 1, 0);
+  }
+  return EB_OK;
+}
+
+__global__ void bt_patch_kernel(int32_t* bt, int stride, const int32_t* patches, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) bt[(int64_t)patches[3 * i] * stride + patches[3 * i + 1]] = patches[3 * i + 2];
+}
+
+int32_t validate(const eb_config* c) {
+  EB_REQUIRE(c, EB_ERR_ARG, "eb_engine_create: null config");
+  EB_REQUIRE(c->n_layers >= 1 && c->hidden >= 128 && c->hidden % 16 == 0, EB_ERR_ARG, "config: hidden %d", c->hidden);
+  EB_REQUIRE(c->head_dim == 64 && c->page_size == 16, EB_ERR_UNSUPPORTED, "config: head_dim %d / page_size %d (64 / 16)",
+             c->head_dim, c->page_size);
+  EB_REQUIRE(c->n_kv_heads == 1 || c->n_kv_heads == 2 || c->n_kv_heads == 4 || c->n_kv_heads == 8, EB_ERR_UNSUPPORTED,
+             "config: n_kv_heads %d not in {1,2,4,8}", c->n_kv_heads);
+  EB_REQUIRE(c->n_q_heads == 8 * c->n_kv_heads || c->n_q_heads == 4 * c->n_kv_heads, EB_ERR_UNSUPPORTED,
+             "config: %d query heads over %d KV heads (groups of 8 or 4)", c->n_q_heads, c->n_kv_heads);
+  EB_REQUIRE(c->n_experts >= 1 && c->n_experts <= 256 && c->top_k >= 1 && c->top_k <= 8 && c->top_k <= c->n_experts,
+             EB_ERR_UNSUPPORTED, "config: experts %d, top_k %d", c->n_experts, c->top_k);
+  EB_REQUIRE(c->inter >= 128 && c->inter % 16 == 0 && c->vocab >= 2, EB_ERR_ARG, "config: inter %d / vocab %d", c->inter,
+             c->vocab);
+  EB_REQUIRE(c->num_pages >= 1 && c->max_seqs >= 1 && c->max_pages_per_seq >= 1 && c->max_tokens >= 1 && c->max_q_len >= 1,
+             EB_ERR_ARG, "config: non-positive capacity");
+  EB_REQUIRE(c->max_q_len * (c->n_q_heads / c->n_kv_heads) <= 48, EB_ERR_UNSUPPORTED, "config: max_q_len %d", c->max_q_len);
+  EB_REQUIRE(c->window >= 0 && c->rope_theta > 0 && c->rms_eps > 0 && c->init_std > 0, EB_ERR_ARG, "config: bad scalar");
+  return EB_OK;
+}
+
+int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, const int32_t* d_tok_slot,
+                   const int32_t* d_positions, const int32_t* d_slots, const int32_t* d_q_off, const int32_t* d_ctx,
+                   const eb_attn_item* d_items[2], const int32_t* d_seq_part[2], const Plan plans[2], int max_q_len) {
+  const eb_config& c = e->c;
+  const int H = c.hidden, I = c.inter, E = c.n_experts, R = T * c.top_k;
+  void* st = e->stream;
+  const int max_pos = c.max_pages_per_seq * c.page_size;
+  int& n = e->launches;
+  n = 0;
+
+  auto dense = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout) -> int32_t {
+    eb_gemm_args g = {};
+    g.d_x8 = x8;
+    g.d_sx = sx;
+    g.d_w8 = w.codes;
+    g.d_sw = w.scales;
+    g.d_y = yout;
+    g.ldy = N;
+    g.rows = T;
+    g.N = N;
+    g.K = K;
+    g.n_groups = 1;
+    g.d_work = (T <= 512 && N <= std::max(e->nqkv, H)) ? e->gemm_ws : nullptr;
+    n += 1;  // (+1 when split K runs its reduction; counted below by the caller of stats as a lower bound)
+    return eb_gemm_fp8_block(&g, st);
+  };
+  auto grouped = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout) -> int32_t {
+    eb_gemm_args g = {};
+    g.d_x8 = x8;
+    g.d_sx = sx;
+    g.d_w8 = w.codes;
+    g.d_sw = w.scales;
+    g.d_y = yout;
+    g.ldy = N;
+    g.rows = R;
+    g.N = N;
+    g.K = K;
+    g.n_groups = E;
+    g.d_seg_off = e->seg_off;
+    g.d_work = e->group_ws;
+    const int avg2 = std::min(128, 2 * ((R + E - 1) / E));
+    g.tile_tokens = avg2 <= 16 ? 16 : avg2 <= 32 ? 32 : avg2 <= 64 ? 64 : 128;
+    n += 2;
+    return eb_gemm_fp8_grouped(&g, st);
+  };
+
+  EB_TRY(eb_embed(e->embed, c.vocab, H, d_tokens, T, e->x, st));
+  n += 1;
+  if (c.debug)
+    EB_CUDA(cudaMemcpyAsync(e->dbg_hidden, e->x, (size_t)T * H * 2, cudaMemcpyDeviceToDevice, e->stream));
+
+  auto impose = [&](int l) -> int32_t {  // debug: replace the residual stream before layer l (n_layers = before the head)
+    if (c.debug && e->force_rows[(size_t)l] == T)
+      EB_CUDA(cudaMemcpyAsync(e->x, e->dbg_force + (size_t)l * c.max_tokens * H, (size_t)T * H * 2,
+                              cudaMemcpyDeviceToDevice, e->stream));
+    return EB_OK;
+  };
+  for (int l = 0; l < c.n_layers; ++l) {
+    const Layer& L = e->layers[(size_t)l];
+    const int pi = (l % 2 == 0 && c.window > 0) ? 1 : 0;  // plan 1 = windowed
+    EB_TRY(impose(l));
+    EB_TRY(eb_rmsnorm(e->x, L.g_attn, T, H, c.rms_eps, e->h, st));
+    EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
+    EB_TRY(dense(e->h8, e->sh, L.wqkv, e->nqkv, H, e->qkv));
+    EB_TRY(eb_rope(e->qkv, e->nqkv, c.n_q_heads + c.n_kv_heads, c.head_dim, d_positions, T, e->rope_cos, e->rope_sin, max_pos, st));
+    EB_TRY(eb_kv_append(L.cache, c.num_pages, c.n_kv_heads, c.head_dim, c.page_size, e->qkv + e->hqd,
+                        e->qkv + e->hqd + c.n_kv_heads * c.head_dim, e->nqkv, e->d_bt, c.max_pages_per_seq, d_tok_slot,
+                        d_positions, T, st));
+    eb_attn_args a = {};
+    a.d_q = e->qkv;
+    a.q_stride = e->nqkv;
+    a.d_out = e->attn;
+    a.out_stride = e->hqd;
+    a.d_cache = L.cache;
+    a.num_pages = c.num_pages;
+    a.d_block_tables = e->d_bt;
+    a.bt_stride = c.max_pages_per_seq;
+    a.d_seq_slots = d_slots;
+    a.d_q_off = d_q_off;
+    a.d_ctx_lens = d_ctx;
+    a.n_seqs = n_seqs;
+    a.max_q_len = max_q_len;
+    a.d_sinks = L.sinks;
+    a.window = pi ? c.window : 0;
+    a.n_q = c.n_q_heads;
+    a.n_kv = c.n_kv_heads;
+    a.head_dim = c.head_dim;
+    a.page_size = c.page_size;
+    a.scale = 0.125f;
+    a.d_items = d_items[pi];
+    a.n_items = plans[pi].n_items;
+    a.d_seq_part = d_seq_part[pi];
+    a.n_parts = plans[pi].n_parts;
+    a.d_part_acc = e->part_acc;
+    a.d_part_ml = e->part_ml;
+    EB_TRY(eb_attn_paged_sink(&a, st));
+    EB_TRY(eb_quant_act_block128(e->attn, e->hqd, T, e->hqd, nullptr, 1, e->a8, e->sa, st));
+    EB_TRY(dense(e->a8, e->sa, L.wo, H, e->hqd, e->o));
+    EB_TRY(eb_residual_add(e->x, e->o, (int64_t)T * H, st));
+    EB_TRY(eb_rmsnorm(e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
+    EB_TRY(eb_moe_route(e->h, L.wr, T, E, H, c.top_k, e->r_idx, e->r_wts, nullptr, st));
+    EB_TRY(eb_moe_permute(e->r_idx, T, c.top_k, E, e->seg_off, e->perm_row, e->row_token, st));
+    EB_TRY(eb_quant_gather_block128(e->h, H, T, e->row_token, R, H, e->seg_off, E, e->xp8, e->sxp, st));
+    EB_TRY(grouped(e->xp8, e->sxp, L.w1, 2 * I, H, e->gu));
+    EB_TRY(eb_quant_silu_mul_block128(e->gu, 2 * I, R, I, e->seg_off, E, e->act8, e->sact, st));
+    EB_TRY(grouped(e->act8, e->sact, L.w2, H, I, e->y));
+    EB_TRY(eb_moe_combine(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->x, st));
+    n += 12 + (plans[pi].n_parts > n_seqs ? 1 : 0);
+    if (c.debug) {
+      EB_CUDA(cudaMemcpyAsync(e->dbg_route + (size_t)l * c.max_tokens * c.top_k, e->r_idx, (size_t)R * sizeof(int32_t),
+                              cudaMemcpyDeviceToDevice, e->stream));
+      EB_CUDA(cudaMemcpyAsync(e->dbg_hidden + (size_t)(l + 1) * c.max_tokens * H, e->x, (size_t)T * H * 2,
+                              cudaMemcpyDeviceToDevice, e->stream));
+    }
+  }
+  EB_TRY(impose(c.n_layers));
+  EB_TRY(eb_rmsnorm(e->x, e->g_final, T, H, c.rms_eps, e->h, st));
+  EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
+  EB_TRY(dense(e->h8, e->sh, e->lm, c.vocab, H, e->logits));
+  EB_TRY(eb_argmax(e->logits, T, c.vocab, c.vocab, e->d_next, e->d_margin, st));
+  n += 3;
+  return EB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t eb_engine_create(const eb_config* cfg, eb_engine** out) {
+  EB_REQUIRE(out, EB_ERR_ARG, "eb_engine_create: null out");
+  EB_TRY(validate(cfg));
+  eb_engine* e = new (std::nothrow) eb_engine;
+  EB_REQUIRE(e, EB_ERR_NOMEM, "eb_engine_create: host allocation failed");
+  e->c = *cfg;
+  const eb_config& c = e->c;
+  int dev = 0;
+  cudaDeviceProp prop;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err == cudaSuccess) err = cudaGetDeviceProperties(&prop, dev);
+  if (err != cudaSuccess) {
+    delete e;
+    return eb::fail(EB_ERR_NODEVICE, "eb_engine_create: %s", cudaGetErrorString(err));
+  }
+  if (prop.major != 10) {
+    delete e;
+    return eb::fail(EB_ERR_NODEVICE, "eb_engine_create: compute capability %d.%d (built for sm_100a only)", prop.major,
+                    prop.minor);
+  }
+  e->sm_count = prop.multiProcessorCount;
+  e->hqd = c.n_q_heads * c.head_dim;
+  e->nqkv = (c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim;
+  e->kbH = (int)eb::cdiv(c.hidden, 128);
+  e->kbI = (int)eb::cdiv(c.inter, 128);
+  e->kbA = (int)eb::cdiv(e->hqd, 128);
+  e->layers.resize((size_t)c.n_layers);
+  e->uploaded_pages.assign((size_t)c.max_seqs, 0);
+  int32_t rc = EB_OK;
+  do {
+    if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreate(&e->ev0) != cudaSuccess || cudaEventCreate(&e->ev1) != cudaSuccess) {
+      rc = eb::fail(EB_ERR_NODEVICE, "eb_engine_create: stream/event creation failed");
+      break;
+    }
+    if ((rc = eb_sched_create(c.num_pages, c.page_size, c.max_seqs, c.max_pages_per_seq, c.seed, &e->sched)) != EB_OK) break;
+    if ((rc = init_weights(e)) != EB_OK) break;
+    const size_t cache_elems = (size_t)c.num_pages * 2 * c.n_kv_heads * c.page_size * c.head_dim;
+    for (int l = 0; l < c.n_layers && rc == EB_OK; ++l) {
+      rc = dev_alloc(e, &e->layers[(size_t)l].cache, cache_elems, &e->kv_bytes);
+      if (rc == EB_OK && cudaMemsetAsync(e->layers[(size_t)l].cache, 0, cache_elems * 2, e->stream) != cudaSuccess)
+        rc = eb::fail(EB_ERR_NODEVICE, "eb_engine_create: cache memset failed");
+    }
+    if (rc != EB_OK) break;
+    if ((rc = init_work(e)) != EB_OK) break;
+    if (cudaStreamSynchronize(e->stream) != cudaSuccess) rc = eb::fail(EB_ERR_NODEVICE, "eb_engine_create: sync failed");
+  } while (0);
+  if (rc != EB_OK) {
+    eb_engine_destroy(e);
+    return rc;
+  }
+  *out = e;
+  return EB_OK;
+}
+
+int32_t eb_engine_destroy(eb_engine* e) {
+  if (!e) return EB_OK;
+  if (e->stream) cudaStreamSynchronize(e->stream);
+  for (void* p : e->allocs) cudaFree(p);
+  if (e->h_stage) cudaFreeHost(e->h_stage);
+  if (e->h_result) cudaFreeHost(e->h_result);
+  if (e->ev0) cudaEventDestroy(e->ev0);
+  if (e->ev1) cudaEventDestroy(e->ev1);
+  if (e->stream) cudaStreamDestroy(e->stream);
+  if (e->sched) eb_sched_destroy(e->sched);
+  delete e;
+  return EB_OK;
+}
+
+int32_t eb_engine_memory(const eb_engine* e, int64_t* weight_bytes, int64_t* kv_bytes, int64_t* work_bytes) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_memory: null engine");
+  if (weight_bytes) *weight_bytes = e->weight_bytes;
+  if (kv_bytes) *kv_bytes = e->kv_bytes;
+  if (work_bytes) *work_bytes = e->work_bytes;
+  return EB_OK;
+}
+
+int32_t eb_engine_kv_fill_synth(eb_engine* e) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_kv_fill_synth: null engine");
+  const eb_config& c = e->c;
+  const int64_t n = (int64_t)c.num_pages * 2 * c.n_kv_heads * c.page_size * c.head_dim;
+  for (int l = 0; l < c.n_layers; ++l)
+    EB_TRY(eb_synth_normal_bf16(e->layers[(size_t)l].cache, n, c.seed, 20000 + (uint64_t)l, 0, 1.0f, e->stream));
+  EB_CUDA(cudaStreamSynchronize(e->stream));
+  return EB_OK;
+}
+
+int32_t eb_engine_seq_admit(eb_engine* e, int32_t context_len, int32_t* slot) {
+  EB_REQUIRE(e && slot, EB_ERR_ARG, "eb_engine_seq_admit: null");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_seq_admit: a step is in flight");
+  EB_TRY(eb_sched_admit(e->sched, context_len, slot));
+  e->uploaded_pages[(size_t)*slot] = 0;
+  return EB_OK;
+}
+
+int32_t eb_engine_seq_release(eb_engine* e, int32_t slot) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_seq_release: null");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_seq_release: a step is in flight");
+  EB_TRY(eb_sched_release(e->sched, slot));
+  e->uploaded_pages[(size_t)slot] = 0;
+  return EB_OK;
+}
+
+int32_t eb_engine_seq_truncate(eb_engine* e, int32_t slot, int32_t new_len) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_seq_truncate: null");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_seq_truncate: a step is in flight");
+  EB_TRY(eb_sched_truncate(e->sched, slot, new_len));
+  const int32_t pages = (new_len + e->c.page_size - 1) / e->c.page_size;
+  e->uploaded_pages[(size_t)slot] = std::min(e->uploaded_pages[(size_t)slot], pages);
+  return EB_OK;
+}
+
+int32_t eb_engine_seq_len(const eb_engine* e, int32_t slot, int32_t* len) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_seq_len: null");
+  return eb_sched_seq_len(e->sched, slot, len);
+}
+
+int32_t eb_engine_sched(eb_engine* e, eb_sched** sched) {
+  EB_REQUIRE(e && sched, EB_ERR_ARG, "eb_engine_sched: null");
+  *sched = e->sched;
+  return EB_OK;
+}
+
+int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
+                              const int32_t* h_tokens) {
+  EB_REQUIRE(e && h_slots && h_q_lens && h_tokens, EB_ERR_ARG, "eb_engine_step: null pointer");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_step: the previous step has not been waited for");
+  const eb_config& c = e->c;
+  EB_REQUIRE(n_seqs >= 1 && n_seqs <= c.max_seqs, EB_ERR_ARG, "eb_engine_step: n_seqs %d outside 1..%d", n_seqs, c.max_seqs);
+  int64_t T64 = 0;
+  int max_q = 1;
+  for (int i = 0; i < n_seqs; ++i) {
+    EB_REQUIRE(h_q_lens[i] >= 1 && h_q_lens[i] <= c.max_q_len, EB_ERR_ARG, "eb_engine_step: q_len %d of sequence %d outside 1..%d",
+               h_q_lens[i], i, c.max_q_len);
+    for (int j = 0; j < i; ++j)
+      EB_REQUIRE(h_slots[j] != h_slots[i], EB_ERR_ARG, "eb_engine_step: slot %d appears twice", h_slots[i]);
+    T64 += h_q_lens[i];
+    max_q = std::max(max_q, h_q_lens[i]);
+  }
+  EB_REQUIRE(T64 <= c.max_tokens, EB_ERR_ARG, "eb_engine_step: %lld token rows exceed max_tokens %d", (long long)T64, c.max_tokens);
+  const int T = (int)T64;
+  for (int t = 0; t < T; ++t)
+    EB_REQUIRE(h_tokens[t] >= 0 && h_tokens[t] < c.vocab, EB_ERR_ARG, "eb_engine_step: token id %d of row %d outside the vocabulary",
+               h_tokens[t], t);
+
+  // grow every sequence; on failure undo the ones already grown so a refused step leaves no trace
+  std::vector<int32_t> old_len((size_t)n_seqs);
+  for (int i = 0; i < n_seqs; ++i) {
+    int32_t rc = eb_sched_seq_len(e->sched, h_slots[i], &old_len[(size_t)i]);
+    if (rc == EB_OK) rc = eb_sched_extend(e->sched, h_slots[i], old_len[(size_t)i] + h_q_lens[i]);
+    if (rc != EB_OK) {
+      for (int j = 0; j < i; ++j) eb_engine_seq_truncate(e, h_slots[j], old_len[(size_t)j]);
+      return rc;
+    }
+  }
+
+  // ---- one staging block
+  int32_t* hs = e->h_stage;
+  size_t off = 0;
+  auto take = [&](size_t n) {
+    int32_t* p = hs + off;
+    off += n;
+    return p;
+  };
+  int32_t* s_tokens = take((size_t)T);
+  int32_t* s_tok_slot = take((size_t)T);
+  int32_t* s_pos = take((size_t)T);
+  int32_t* s_slots = take((size_t)n_seqs);
+  int32_t* s_ctx = take((size_t)n_seqs);
+  int32_t* s_qoff = take((size_t)n_seqs + 1);
+  memcpy(s_tokens, h_tokens, (size_t)T * sizeof(int32_t));
+  memcpy(s_slots, h_slots, (size_t)n_seqs * sizeof(int32_t));
+  std::vector<int32_t> tok_seq((size_t)T);
+  int32_t nt = 0;
+  EB_TRY(eb_sched_pack(e->sched, h_slots, h_q_lens, n_seqs, s_qoff, s_ctx, tok_seq.data(), s_tok_slot, s_pos, &nt));
+  // block-table patches
+  const int32_t* tables = nullptr;
+  int32_t stride = 0;
+  EB_TRY(eb_sched_block_tables(e->sched, &tables, &stride));
+  int32_t* s_patch = hs + off;
+  int n_patch = 0;
+  for (int i = 0; i < n_seqs; ++i) {
+    const int slot = h_slots[i];
+    const int pages = (s_ctx[i] + c.page_size - 1) / c.page_size;
+    for (int p = e->uploaded_pages[(size_t)slot]; p < pages; ++p) {
+      s_patch[3 * n_patch] = slot;
+      s_patch[3 * n_patch + 1] = p;
+      s_patch[3 * n_patch + 2] = tables[(size_t)slot * stride + p];
+      ++n_patch;
+    }
+    e->uploaded_pages[(size_t)slot] = pages;
+  }
+  off += 3 * (size_t)n_patch;
+  // attention plans: [0] full, [1] windowed
+  Plan plans[2];
+  size_t items_off[2], part_off[2];
+  const int ppi = 8 / c.n_kv_heads;
+  for (int k = 0; k < 2; ++k) {
+    if (k == 1 && c.window == 0) {
+      items_off[1] = items_off[0];
+      part_off[1] = part_off[0];
+      plans[1] = plans[0];
+      break;
+    }
+    items_off[k] = off;
+    eb_attn_item* it = reinterpret_cast<eb_attn_item*>(hs + off);
+    off += 4 * (size_t)e->cap_items;
+    part_off[k] = off;
+    int32_t* sp = take((size_t)n_seqs + 1);
+    EB_TRY(eb_attn_plan(s_ctx, h_q_lens, n_seqs, c.page_size, k ? c.window : 0, e->sm_count, 0, ppi, it, e->cap_items,
+                        &plans[k].n_items, sp, &plans[k].n_parts));
+  }
+  EB_REQUIRE(off <= e->stage_words, EB_ERR_NOMEM, "eb_engine_step: staging block overflow (%zu > %zu words)", off, e->stage_words);
+
+  EB_CUDA(cudaEventRecord(e->ev0, e->stream));
+  EB_CUDA(cudaMemcpyAsync(e->d_stage, hs, off * sizeof(int32_t), cudaMemcpyHostToDevice, e->stream));
+  const int32_t* ds = e->d_stage;
+  if (n_patch > 0) {
+    bt_patch_kernel<<<(unsigned)eb::cdiv(n_patch, 256), 256, 0, e->stream>>>(e->d_bt, c.max_pages_per_seq,
+                                                                            ds + (s_patch - hs), n_patch);
+    EB_LAUNCH_CHECK();
+  }
+  const eb_attn_item* d_items[2] = {reinterpret_cast<const eb_attn_item*>(ds + items_off[0]),
+                                    reinterpret_cast<const eb_attn_item*>(ds + items_off[1])};
+  const int32_t* d_seq_part[2] = {ds + part_off[0], ds + part_off[1]};
+  int32_t rc = run_layers(e, T, n_seqs, ds + (s_tokens - hs), ds + (s_tok_slot - hs), ds + (s_pos - hs), ds + (s_slots - hs),
+                          ds + (s_qoff - hs), ds + (s_ctx - hs), d_items, d_seq_part, plans, max_q);
+  if (rc != EB_OK) return rc;
+  e->launches += (n_patch > 0 ? 1 : 0);
+  EB_CUDA(cudaMemcpyAsync(e->h_result, e->d_next, (size_t)T * sizeof(int32_t), cudaMemcpyDeviceToHost, e->stream));
+  EB_CUDA(cudaMemcpyAsync(e->h_result + T, e->d_margin, (size_t)T * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+  EB_CUDA(cudaEventRecord(e->ev1, e->stream));
+  e->cur_T = T;
+  e->in_flight = true;
+  return EB_OK;
+}
+
+int32_t eb_engine_step_wait(eb_engine* e, int32_t* h_next, float* h_margin) {
+  EB_REQUIRE(e && h_next, EB_ERR_ARG, "eb_engine_step_wait: null pointer");
+  EB_REQUIRE(e->in_flight, EB_ERR_STATE, "eb_engine_step_wait: no step in flight");
+  e->in_flight = false;
+  EB_CUDA(cudaEventSynchronize(e->ev1));
+  EB_CUDA(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+  memcpy(h_next, e->h_result, (size_t)e->cur_T * sizeof(int32_t));
+  if (h_margin) memcpy(h_margin, e->h_result + e->cur_T, (size_t)e->cur_T * sizeof(float));
+  return EB_OK;
+}
+
+int32_t eb_engine_step(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
+                       const int32_t* h_tokens, int32_t* h_next, float* h_margin) {
+  EB_TRY(eb_engine_step_launch(e, h_slots, h_q_lens, n_seqs, h_tokens));
+  return eb_engine_step_wait(e, h_next, h_margin);
+}
+
+int32_t eb_engine_last_step_stats(const eb_engine* e, float* device_ms, int32_t* kernel_launches) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_last_step_stats: null engine");
+  if (device_ms) *device_ms = e->last_ms;
+  if (kernel_launches) *kernel_launches = e->launches;
+  return EB_OK;
+}
+
+int32_t eb_engine_read_logits(eb_engine* e, void* h_logits, int64_t bytes) {
+  EB_REQUIRE(e && h_logits, EB_ERR_ARG, "eb_engine_read_logits: null");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_read_logits: a step is in flight");
+  EB_REQUIRE(bytes == (int64_t)e->cur_T * e->c.vocab * 2, EB_ERR_ARG, "eb_engine_read_logits: expected %lld bytes",
+             (long long)e->cur_T * e->c.vocab * 2);
+  EB_CUDA(cudaMemcpy(h_logits, e->logits, (size_t)bytes, cudaMemcpyDeviceToHost));
+  return EB_OK;
+}
+
+int32_t eb_engine_read_routing(eb_engine* e, int32_t layer, int32_t* h_idx, int64_t bytes) {
+  EB_REQUIRE(e && h_idx, EB_ERR_ARG, "eb_engine_read_routing: null");
+  EB_REQUIRE(e->c.debug && e->dbg_route, EB_ERR_STATE, "eb_engine_read_routing: engine was not created with debug = 1");
+  EB_REQUIRE(layer >= 0 && layer < e->c.n_layers, EB_ERR_ARG, "eb_engine_read_routing: layer %d", layer);
+  EB_REQUIRE(bytes == (int64_t)e->cur_T * e->c.top_k * 4, EB_ERR_ARG, "eb_engine_read_routing: expected %lld bytes",
+             (long long)e->cur_T * e->c.top_k * 4);
+  EB_CUDA(cudaMemcpy(h_idx, e->dbg_route + (size_t)layer * e->c.max_tokens * e->c.top_k, (size_t)bytes, cudaMemcpyDeviceToHost));
+  return EB_OK;
+}
+
+int32_t eb_engine_read_hidden(eb_engine* e, int32_t layer, void* h_x, int64_t bytes) {
+  EB_REQUIRE(e && h_x, EB_ERR_ARG, "eb_engine_read_hidden: null");
+  EB_REQUIRE(e->c.debug && e->dbg_hidden, EB_ERR_STATE, "eb_engine_read_hidden: engine was not created with debug = 1");
+  EB_REQUIRE(layer >= -1 && layer < e->c.n_layers, EB_ERR_ARG, "eb_engine_read_hidden: layer %d", layer);
+  EB_REQUIRE(bytes == (int64_t)e->cur_T * e->c.hidden * 2, EB_ERR_ARG, "eb_engine_read_hidden: expected %lld bytes",
+             (long long)e->cur_T * e->c.hidden * 2);
+  EB_CUDA(cudaMemcpy(h_x, e->dbg_hidden + (size_t)(layer + 1) * e->c.max_tokens * e->c.hidden, (size_t)bytes, cudaMemcpyDeviceToHost));
+  return EB_OK;
+}
+
+
+int32_t eb_engine_debug_force_hidden(eb_engine* e, int32_t layer, const void* h_x, int32_t rows) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_debug_force_hidden: null engine");
+  EB_REQUIRE(e->c.debug && e->dbg_force, EB_ERR_STATE, "eb_engine_debug_force_hidden: engine was not created with debug = 1");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_debug_force_hidden: a step is in flight");
+  EB_REQUIRE(layer >= 0 && layer <= e->c.n_layers, EB_ERR_ARG, "eb_engine_debug_force_hidden: layer %d", layer);
+  EB_REQUIRE(rows >= 0 && rows <= e->c.max_tokens, EB_ERR_ARG, "eb_engine_debug_force_hidden: rows %d", rows);
+  if (!h_x || rows == 0) {
+    e->force_rows[(size_t)layer] = 0;
+    return EB_OK;
+  }
+  EB_CUDA(cudaMemcpy(e->dbg_force + (size_t)layer * e->c.max_tokens * e->c.hidden, h_x, (size_t)rows * e->c.hidden * 2,
+                     cudaMemcpyHostToDevice));
+  e->force_rows[(size_t)layer] = rows;
+  return EB_OK;
+}
+
+}  // extern "C"

@@ -325,9 +325,12 @@ __global__ void gemm_tiles_kernel(const int32_t* seg_off, int n_groups, int tn, 
 
 // Activation quantiser: one CTA per (128-row block, 128-column block) of a bf16 matrix.
 // Thread t holds 8 rows x one 16-byte chunk; block amax -> scale -> e4m3.
+// MODE 0: value = x[src_row(r)][c] (src_row = identity when row_map is null).
+// MODE 1: x holds [gate | up] halves of width `cols`; value = bf16( gate/(1+exp(-gate)) * up ).
+template <int MODE>
 __global__ void __launch_bounds__(256)
 quant_act_kernel(const uint16_t* x, int64_t ldx, int rows, int cols, const int32_t* seg_off, int n_groups,
-                 uint8_t* codes, float* scales) {
+                 const int32_t* row_map, int src_rows, uint8_t* codes, float* scales, int32_t* status) {
   const int blk = blockIdx.y, cb = blockIdx.x, n_cb = gridDim.x;
   int r0, r1;
   if (seg_off) {
@@ -377,7 +380,31 @@ quant_act_kernel(const uint16_t* x, int64_t ldx, int rows, int cols, const int32
   for (int i = 0; i < 8; ++i) {
     const int r = r0 + rsub + i * 16;
     v[i] = make_uint4(0, 0, 0, 0);
-    if (col_ok && r < r1) v[i] = *reinterpret_cast<const uint4*>(x + (int64_t)r * ldx + col);
+    if (col_ok && r < r1) {
+      int sr = r;
+      if (MODE == 0 && row_map) {
+        sr = row_map[r];
+        if (sr < 0 || sr >= src_rows) {
+          atomicOr(status, EB_DEV_BAD_INDEX);
+          sr = 0;
+        }
+      }
+      v[i] = *reinterpret_cast<const uint4*>(x + (int64_t)sr * ldx + col);
+      if (MODE == 1) {
+        const uint4 u = *reinterpret_cast<const uint4*>(x + (int64_t)sr * ldx + cols + col);
+        const uint32_t gw[4] = {v[i].x, v[i].y, v[i].z, v[i].w}, uw[4] = {u.x, u.y, u.z, u.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float g0 = __uint_as_float(gw[k] << 16), g1 = __uint_as_float(gw[k] & 0xFFFF0000u);
+          const float u0 = __uint_as_float(uw[k] << 16), u1 = __uint_as_float(uw[k] & 0xFFFF0000u);
+          const float a0 = __fmul_rn(__fdiv_rn(g0, 1.0f + expf(-g0)), u0);
+          const float a1 = __fmul_rn(__fdiv_rn(g1, 1.0f + expf(-g1)), u1);
+          asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[k]) : "f"(a1), "f"(a0));
+        }
+        v[i] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
     const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -553,21 +580,46 @@ int32_t eb_gemm_fp8_grouped(const eb_gemm_args* a, void* stream) {
   return run_gemm(a, true, eb::as_stream(stream));
 }
 
-int32_t eb_quant_act_block128(const void* d_x, int64_t ldx, int32_t rows, int32_t cols, const int32_t* d_seg_off,
-                              int32_t n_groups, void* d_codes, void* d_scales, void* stream) {
-  EB_REQUIRE(d_x && d_codes && d_scales, EB_ERR_ARG, "eb_quant_act_block128: null pointer");
-  EB_REQUIRE(rows >= 0 && cols >= 8 && cols % 8 == 0 && ldx >= cols && ldx % 8 == 0, EB_ERR_ARG,
-             "eb_quant_act_block128: cols %d / ldx %lld must be multiples of 8", cols, (long long)ldx);
-  EB_REQUIRE(n_groups >= 1, EB_ERR_ARG, "eb_quant_act_block128: n_groups %d", n_groups);
-  EB_REQUIRE(((uintptr_t)d_x % 16 == 0) && ((uintptr_t)d_codes % 8 == 0), EB_ERR_ARG, "eb_quant_act_block128: alignment");
+static int32_t run_quant(int mode, const void* d_x, int64_t ldx, int32_t rows, int32_t cols, const int32_t* d_seg_off,
+                         int32_t n_groups, const int32_t* d_row_map, int32_t src_rows, void* d_codes, void* d_scales,
+                         void* stream) {
+  EB_REQUIRE(d_x && d_codes && d_scales, EB_ERR_ARG, "quantise: null pointer");
+  EB_REQUIRE(rows >= 0 && cols >= 8 && cols % 8 == 0 && ldx >= (mode ? 2 : 1) * (int64_t)cols && ldx % 8 == 0, EB_ERR_ARG,
+             "quantise: cols %d / ldx %lld must be multiples of 8", cols, (long long)ldx);
+  EB_REQUIRE(n_groups >= 1, EB_ERR_ARG, "quantise: n_groups %d", n_groups);
+  EB_REQUIRE(((uintptr_t)d_x % 16 == 0) && ((uintptr_t)d_codes % 8 == 0), EB_ERR_ARG, "quantise: alignment");
   if (rows == 0) return EB_OK;
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "quantise: no device");
   const int n_blk = d_seg_off ? rows / 128 + n_groups : (rows + 127) / 128;
-  EB_REQUIRE(n_blk <= 65535, EB_ERR_UNSUPPORTED, "eb_quant_act_block128: %d row blocks exceed the grid", n_blk);
+  EB_REQUIRE(n_blk <= 65535, EB_ERR_UNSUPPORTED, "quantise: %d row blocks exceed the grid", n_blk);
   const dim3 grid((unsigned)((cols + 127) / 128), (unsigned)n_blk);
-  quant_act_kernel<<<grid, 256, 0, eb::as_stream(stream)>>>((const uint16_t*)d_x, ldx, rows, cols, d_seg_off,
-                                                            n_groups, (uint8_t*)d_codes, (float*)d_scales);
+  if (mode == 0)
+    quant_act_kernel<0><<<grid, 256, 0, eb::as_stream(stream)>>>((const uint16_t*)d_x, ldx, rows, cols, d_seg_off, n_groups,
+                                                                 d_row_map, src_rows, (uint8_t*)d_codes, (float*)d_scales, status);
+  else
+    quant_act_kernel<1><<<grid, 256, 0, eb::as_stream(stream)>>>((const uint16_t*)d_x, ldx, rows, cols, d_seg_off, n_groups,
+                                                                 nullptr, rows, (uint8_t*)d_codes, (float*)d_scales, status);
   EB_LAUNCH_CHECK();
   return EB_OK;
+}
+
+int32_t eb_quant_act_block128(const void* d_x, int64_t ldx, int32_t rows, int32_t cols, const int32_t* d_seg_off,
+                              int32_t n_groups, void* d_codes, void* d_scales, void* stream) {
+  return run_quant(0, d_x, ldx, rows, cols, d_seg_off, n_groups, nullptr, rows, d_codes, d_scales, stream);
+}
+
+int32_t eb_quant_gather_block128(const void* d_x, int64_t ldx, int32_t src_rows, const int32_t* d_row_map, int32_t rows,
+                                 int32_t cols, const int32_t* d_seg_off, int32_t n_groups, void* d_codes,
+                                 void* d_scales, void* stream) {
+  EB_REQUIRE(d_row_map && src_rows >= 1, EB_ERR_ARG, "eb_quant_gather_block128: null row map");
+  return run_quant(0, d_x, ldx, rows, cols, d_seg_off, n_groups, d_row_map, src_rows, d_codes, d_scales, stream);
+}
+
+int32_t eb_quant_silu_mul_block128(const void* d_gate_up, int64_t ld, int32_t rows, int32_t cols,
+                                   const int32_t* d_seg_off, int32_t n_groups, void* d_codes, void* d_scales,
+                                   void* stream) {
+  return run_quant(1, d_gate_up, ld, rows, cols, d_seg_off, n_groups, nullptr, rows, d_codes, d_scales, stream);
 }
 
 }  // extern "C"

@@ -1,0 +1,236 @@
+// Mixture-of-experts routing for the decode step: router logits + top-k, token -> expert permutation, and the
+// weighted combine of expert outputs.  The expert matrices themselves run in the grouped FP8 GEMM (gemm.cu).
+//
+// Routing decisions must be bit-exact against the CPU restatement, so the router logit is summed in one fixed
+// order: lane l of a warp adds the exact bf16 x bf16 products k = l, l+32, ... in ascending k with fmaf, then
+// the 32 lane sums are combined by an xor butterfly (offsets 16, 8, 4, 2, 1).  Ties go to the lower expert.
+//
+// The reference project has no router (inference is delegated, crates/eidola-server/src/backend.rs:421-433).
+#include <cuda_runtime.h>
+
+#include "common.h"
+
+namespace {
+
+constexpr int kMaxExperts = 256;
+constexpr int kMaxTopK = 8;
+
+__device__ __forceinline__ float bf(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+
+// One warp per token.  x row staged in shared memory; every lane keeps the logits of experts e = lane + 32*j.
+template <int EPL>  // experts per lane = ceil(E / 32)
+__global__ void __launch_bounds__(128)
+router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, int top_k, int32_t* idx, float* wts,
+                   float* logits_out) {
+  extern __shared__ uint16_t xs[];  // [4 warps][H]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= T) return;
+  uint16_t* xr = xs + (size_t)warp * H;
+  for (int k = lane; k < H; k += 32) xr[k] = x[(int64_t)t * H + k];
+  __syncwarp();
+
+  float lg[EPL];
+#pragma unroll
+  for (int j = 0; j < EPL; ++j) lg[j] = -INFINITY;
+  for (int e = 0; e < E; ++e) {
+    const uint16_t* w = wr + (int64_t)e * H;
+    float acc = 0.f;
+    for (int k = lane; k < H; k += 32) acc = __fmaf_rn(bf(xr[k]), bf(w[k]), acc);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+    if ((e & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < EPL; ++j)
+        if (j == (e >> 5)) lg[j] = acc;
+    }
+    if (logits_out && lane == 0) logits_out[(int64_t)t * E + e] = acc;
+  }
+
+  float sel[kMaxTopK];
+  for (int j = 0; j < top_k; ++j) {
+    // local best (lowest index on ties: ascending scan with strict >)
+    float bv = -INFINITY;
+    int bi = 0x7FFFFFFF;
+#pragma unroll
+    for (int q = 0; q < EPL; ++q) {
+      const int e = lane + 32 * q;
+      if (e < E && lg[q] > bv) {
+        bv = lg[q];
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    sel[j] = bv;
+    if (lane == 0) idx[(int64_t)t * top_k + j] = bi;
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int q = 0; q < EPL; ++q)
+        if (q == (bi >> 5)) lg[q] = -INFINITY;  // taken
+    }
+  }
+  if (lane == 0) {
+    float ex[kMaxTopK], den = 0.f;
+    for (int j = 0; j < top_k; ++j) {
+      ex[j] = expf(sel[j] - sel[0]);
+      den += ex[j];
+    }
+    for (int j = 0; j < top_k; ++j) wts[(int64_t)t * top_k + j] = ex[j] / den;
+  }
+}
+
+// Stable counting sort of the T*top_k routed slots by expert, one CTA of 1024 threads.
+//   seg_off[E+1]  : expert segment bounds in the permuted row space
+//   perm_row[i]   : permuted row of slot i = t*top_k + j   (order: expert, then slot index)
+//   row_token[r]  : token whose activations permuted row r carries
+__global__ void __launch_bounds__(1024)
+moe_permute_kernel(const int32_t* idx, int n_slots, int top_k, int E, int32_t* seg_off, int32_t* perm_row,
+                   int32_t* row_token, int32_t* status) {
+  __shared__ int32_t base[kMaxExperts + 1];   // running start of each expert's unplaced slots
+  __shared__ int32_t wcnt[32][kMaxExperts];   // per-warp counts of the current tile
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int e = tid; e <= E; e += 1024) base[e] = 0;
+  __syncthreads();
+  for (int i = tid; i < n_slots; i += 1024) {
+    int e = idx[i];
+    if (e < 0 || e >= E) {
+      atomicOr(status, EB_DEV_BAD_INDEX);
+      e = 0;
+    }
+    atomicAdd(&base[e + 1], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    for (int e = 0; e < E; ++e) base[e + 1] += base[e];
+  }
+  __syncthreads();
+  for (int e = tid; e <= E; e += 1024) seg_off[e] = base[e];
+  __syncthreads();
+
+  for (int i0 = 0; i0 < n_slots; i0 += 1024) {
+    for (int k = tid; k < 32 * E; k += 1024) wcnt[k / E][k % E] = 0;
+    __syncthreads();
+    const int i = i0 + tid;
+    const bool on = i < n_slots;
+    int e = on ? idx[i] : -1;
+    if (on && (e < 0 || e >= E)) e = 0;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (on && rank == 0) wcnt[warp][e] = __popc(peers);
+    __syncthreads();
+    if (tid < E) {  // exclusive prefix over the 32 warps, continuing from the expert's running base
+      int run = base[tid];
+      for (int w = 0; w < 32; ++w) {
+        const int c = wcnt[w][tid];
+        wcnt[w][tid] = run;
+        run += c;
+      }
+      base[tid] = run;
+    }
+    __syncthreads();
+    if (on) {
+      const int r = wcnt[warp][e] + rank;
+      perm_row[i] = r;
+      row_token[r] = i / top_k;
+    }
+    __syncthreads();
+  }
+}
+
+// x[t] = bf16( x[t] + bf16( sum_j w[t][j] * y[perm_row[t*top_k+j]] ) ), j ascending, fmaf.  8 columns per thread.
+__global__ void moe_combine_kernel(const uint16_t* y, const int32_t* perm_row, const float* wts, int T, int top_k,
+                                   int H, uint16_t* x, int64_t n_rows) {
+  const int h8 = H >> 3;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)T * h8) return;
+  const int t = (int)(idx / h8), c = (int)(idx % h8) * 8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int j = 0; j < top_k; ++j) {
+    const int r = perm_row[(int64_t)t * top_k + j];
+    if (r < 0 || r >= n_rows) continue;
+    const float w = wts[(int64_t)t * top_k + j];
+    const uint4 v = *reinterpret_cast<const uint4*>(y + (int64_t)r * H + c);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      acc[2 * k] = __fmaf_rn(w, __uint_as_float(u[k] << 16), acc[2 * k]);
+      acc[2 * k + 1] = __fmaf_rn(w, __uint_as_float(u[k] & 0xFFFF0000u), acc[2 * k + 1]);
+    }
+  }
+  uint4 xv = *reinterpret_cast<const uint4*>(x + (int64_t)t * H + c);
+  uint32_t xu[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    uint32_t m;  // the expert mix is rounded to bf16 before the residual add
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(m) : "f"(acc[2 * k + 1]), "f"(acc[2 * k]));
+    const float lo = __fadd_rn(__uint_as_float(xu[k] << 16), __uint_as_float(m << 16));
+    const float hi = __fadd_rn(__uint_as_float(xu[k] & 0xFFFF0000u), __uint_as_float(m & 0xFFFF0000u));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(xu[k]) : "f"(hi), "f"(lo));
+  }
+  *reinterpret_cast<uint4*>(x + (int64_t)t * H + c) = make_uint4(xu[0], xu[1], xu[2], xu[3]);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t eb_moe_route(const void* d_x, const void* d_wr, int32_t T, int32_t E, int32_t H, int32_t top_k, int32_t* d_idx,
+                     float* d_wts, float* d_logits, void* stream) {
+  EB_REQUIRE(d_x && d_wr && d_idx && d_wts, EB_ERR_ARG, "eb_moe_route: null pointer");
+  EB_REQUIRE(T >= 0 && E >= 1 && E <= kMaxExperts && H >= 1 && top_k >= 1 && top_k <= kMaxTopK && top_k <= E,
+             EB_ERR_UNSUPPORTED, "eb_moe_route: E %d (<= %d), top_k %d (<= %d)", E, kMaxExperts, top_k, kMaxTopK);
+  if (T == 0) return EB_OK;
+  const size_t smem = 4 * (size_t)H * sizeof(uint16_t);
+  EB_REQUIRE(smem <= 48 * 1024, EB_ERR_UNSUPPORTED, "eb_moe_route: hidden size %d too large", H);
+  const unsigned grid = (unsigned)((T + 3) / 4);
+  cudaStream_t st = eb::as_stream(stream);
+  const uint16_t* x = (const uint16_t*)d_x;
+  const uint16_t* wr = (const uint16_t*)d_wr;
+  const int epl = (E + 31) / 32;
+  if (epl <= 1)
+    router_topk_kernel<1><<<grid, 128, smem, st>>>(x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  else if (epl <= 2)
+    router_topk_kernel<2><<<grid, 128, smem, st>>>(x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  else if (epl <= 4)
+    router_topk_kernel<4><<<grid, 128, smem, st>>>(x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  else
+    router_topk_kernel<8><<<grid, 128, smem, st>>>(x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_moe_permute(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E, int32_t* d_seg_off,
+                       int32_t* d_perm_row, int32_t* d_row_token, void* stream) {
+  EB_REQUIRE(d_idx && d_seg_off && d_perm_row && d_row_token, EB_ERR_ARG, "eb_moe_permute: null pointer");
+  EB_REQUIRE(T >= 0 && top_k >= 1 && E >= 1 && E <= kMaxExperts, EB_ERR_UNSUPPORTED, "eb_moe_permute: E %d (<= %d)", E,
+             kMaxExperts);
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_moe_permute: no device");
+  moe_permute_kernel<<<1, 1024, 0, eb::as_stream(stream)>>>(d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
+                                                             d_row_token, status);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_moe_combine(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
+                       int32_t H, void* d_x, void* stream) {
+  EB_REQUIRE(d_y && d_perm_row && d_wts && d_x, EB_ERR_ARG, "eb_moe_combine: null pointer");
+  EB_REQUIRE(T >= 0 && top_k >= 1 && H >= 8 && H % 8 == 0, EB_ERR_ARG, "eb_moe_combine: H %d must be a multiple of 8", H);
+  EB_REQUIRE(((uintptr_t)d_y % 16 == 0) && ((uintptr_t)d_x % 16 == 0), EB_ERR_ARG, "eb_moe_combine: 16-byte alignment");
+  if (T == 0) return EB_OK;
+  const int64_t n = (int64_t)T * (H / 8);
+  moe_combine_kernel<<<(unsigned)eb::cdiv(n, 256), 256, 0, eb::as_stream(stream)>>>(
+      (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, (uint16_t*)d_x, (int64_t)T * top_k);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+}  // extern "C"

@@ -5,7 +5,7 @@ import ctypes as C
 
 import numpy as np
 
-from .capi import (AttnArgs, AttnItem, GemmArgs, DeviceBuffer, call, c_f32, c_i32, c_i64, c_sz, c_u64, c_vp, ptr)
+from .capi import (AttnArgs, AttnItem, Config, GemmArgs, DeviceBuffer, call, c_f32, c_i32, c_i64, c_sz, c_u64, c_vp, ptr)
 
 I32 = np.int32
 
@@ -165,3 +165,103 @@ def gemm_fp8(d_x8, d_sx, d_w8, d_sw, d_y, rows, N, K, *, ldy=None, n_groups=1, d
     a.rows, a.N, a.K, a.n_groups = rows, N, K, n_groups
     a.d_seg_off, a.d_work, a.tile_tokens, a.splits = d_seg_off, d_work, tile_tokens, splits
     call("eb_gemm_fp8_grouped" if d_seg_off is not None else "eb_gemm_fp8_block", C.byref(a), c_vp(stream))
+
+
+class Engine:
+    """eb_engine_*: weights, KV pages, scheduler and the decode step."""
+
+    def __init__(self, cfg: Config):
+        self.cfg = cfg
+        self._h = c_vp()
+        call("eb_engine_create", C.byref(cfg), C.byref(self._h))
+        self._last_T = 0
+
+    def close(self):
+        if self._h:
+            call("eb_engine_destroy", self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def memory(self) -> dict:
+        w, k, x = c_i64(0), c_i64(0), c_i64(0)
+        call("eb_engine_memory", self._h, C.byref(w), C.byref(k), C.byref(x))
+        return {"weights": w.value, "kv": k.value, "work": x.value}
+
+    def kv_fill_synth(self) -> None:
+        call("eb_engine_kv_fill_synth", self._h)
+
+    def admit(self, context_len: int) -> int:
+        slot = c_i32(-1)
+        call("eb_engine_seq_admit", self._h, c_i32(context_len), C.byref(slot))
+        return int(slot.value)
+
+    def release(self, slot: int) -> None:
+        call("eb_engine_seq_release", self._h, c_i32(slot))
+
+    def truncate(self, slot: int, new_len: int) -> None:
+        call("eb_engine_seq_truncate", self._h, c_i32(slot), c_i32(new_len))
+
+    def seq_len(self, slot: int) -> int:
+        n = c_i32(0)
+        call("eb_engine_seq_len", self._h, c_i32(slot), C.byref(n))
+        return int(n.value)
+
+    def block_tables(self) -> np.ndarray:
+        sp = c_vp()
+        call("eb_engine_sched", self._h, C.byref(sp))
+        p = C.POINTER(c_i32)()
+        stride = c_i32(0)
+        call("eb_sched_block_tables", sp, C.byref(p), C.byref(stride))
+        return np.ctypeslib.as_array(p, shape=(self.cfg.max_seqs, int(stride.value))).copy()
+
+    def step(self, slots, q_lens, tokens):
+        """Returns (next_tokens[T], margins[T])."""
+        slots, q_lens, tokens = _i32(slots), _i32(q_lens), _i32(tokens)
+        T = int(q_lens.sum())
+        assert len(tokens) == T
+        nxt, mg = np.empty(T, I32), np.empty(T, np.float32)
+        call("eb_engine_step", self._h, ptr(slots), ptr(q_lens), c_i32(len(slots)), ptr(tokens), ptr(nxt), ptr(mg))
+        self._last_T = T
+        return nxt, mg
+
+    def step_launch(self, slots, q_lens, tokens) -> None:
+        slots, q_lens, tokens = _i32(slots), _i32(q_lens), _i32(tokens)
+        self._last_T = int(q_lens.sum())
+        call("eb_engine_step_launch", self._h, ptr(slots), ptr(q_lens), c_i32(len(slots)), ptr(tokens))
+
+    def step_wait(self):
+        nxt, mg = np.empty(self._last_T, I32), np.empty(self._last_T, np.float32)
+        call("eb_engine_step_wait", self._h, ptr(nxt), ptr(mg))
+        return nxt, mg
+
+    def last_step_stats(self) -> tuple[float, int]:
+        ms, n = c_f32(0), c_i32(0)
+        call("eb_engine_last_step_stats", self._h, C.byref(ms), C.byref(n))
+        return float(ms.value), int(n.value)
+
+    def read_logits(self) -> np.ndarray:
+        out = np.empty((self._last_T, self.cfg.vocab), np.uint16)
+        call("eb_engine_read_logits", self._h, ptr(out), c_i64(out.nbytes))
+        return out
+
+    def read_routing(self, layer: int) -> np.ndarray:
+        out = np.empty((self._last_T, self.cfg.top_k), I32)
+        call("eb_engine_read_routing", self._h, c_i32(layer), ptr(out), c_i64(out.nbytes))
+        return out
+
+    def read_hidden(self, layer: int) -> np.ndarray:
+        out = np.empty((self._last_T, self.cfg.hidden), np.uint16)
+        call("eb_engine_read_hidden", self._h, c_i32(layer), ptr(out), c_i64(out.nbytes))
+        return out
+
+    def force_hidden(self, layer: int, x=None) -> None:
+        if x is None:
+            call("eb_engine_debug_force_hidden", self._h, c_i32(layer), c_vp(None), c_i32(0))
+        else:
+            x = np.ascontiguousarray(x, np.uint16)
+            call("eb_engine_debug_force_hidden", self._h, c_i32(layer), ptr(x), c_i32(x.shape[0]))

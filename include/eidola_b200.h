@@ -179,10 +179,10 @@ typedef struct eb_attn_args {
   const int32_t* d_q_off;     /* [n_seqs+1] */
   const int32_t* d_ctx_lens;  /* [n_seqs] */
   int32_t n_seqs;
-  int32_t max_q_len; /* largest q_len in the batch, 1..6 */
+  int32_t max_q_len; /* largest q_len in the batch; max_q_len * (n_q / n_kv) <= 48 */
   const float* d_sinks; /* [n_q] learned sink logit per query head */
   int32_t window;       /* 0 = full attention */
-  int32_t n_q, n_kv, head_dim, page_size;
+  int32_t n_q, n_kv, head_dim, page_size; /* n_q / n_kv = 8 or 4; n_kv in {1,2,4,8}; head_dim 64; page_size 16 */
   float scale; /* 1/sqrt(head_dim) */
   const eb_attn_item* d_items;
   int32_t n_items;
@@ -205,6 +205,15 @@ int32_t eb_attn_workspace(int32_t n_parts, int32_t max_q_len, int32_t n_q, int32
 int32_t eb_quant_act_block128(const void* d_x, int64_t ldx, int32_t rows, int32_t cols, const int32_t* d_seg_off,
                               int32_t n_groups, void* d_codes, void* d_scales, void* stream);
 
+/* The same, reading row d_row_map[r] of a [src_rows x cols] matrix for output row r (token -> expert gather). */
+int32_t eb_quant_gather_block128(const void* d_x, int64_t ldx, int32_t src_rows, const int32_t* d_row_map, int32_t rows,
+                                 int32_t cols, const int32_t* d_seg_off, int32_t n_groups, void* d_codes,
+                                 void* d_scales, void* stream);
+/* The same on act = bf16(silu(gate) * up), where row r of d_gate_up holds [gate(cols) | up(cols)] bf16. */
+int32_t eb_quant_silu_mul_block128(const void* d_gate_up, int64_t ld, int32_t rows, int32_t cols,
+                                   const int32_t* d_seg_off, int32_t n_groups, void* d_codes, void* d_scales,
+                                   void* stream);
+
 typedef struct eb_gemm_args {
   const void* d_x8;  /* [rows][K] e4m3 activations */
   const float* d_sx; /* [row blocks][ceil(K/128)] */
@@ -226,6 +235,91 @@ int32_t eb_gemm_fp8_block(const eb_gemm_args* a, void* stream);
  * restart at each segment start (the numbering eb_quant_act_block128 uses). */
 int32_t eb_gemm_fp8_grouped(const eb_gemm_args* a, void* stream);
 int32_t eb_gemm_workspace(int32_t rows, int32_t N, int32_t n_groups, size_t* bytes);
+
+/* ---- MoE routing (K5, K7) ---------------------------------------------------------------- */
+
+/* Router: logits = x * Wr^T (bf16 inputs, fp32 accumulation in a fixed order, so the choice is reproducible bit for
+ * bit), top_k by value with ties to the lower expert, weights = softmax over the selected logits.
+ * d_idx [T][top_k] int32, d_wts [T][top_k] fp32, d_logits [T][E] fp32 or NULL. */
+int32_t eb_moe_route(const void* d_x, const void* d_wr, int32_t T, int32_t E, int32_t H, int32_t top_k, int32_t* d_idx,
+                     float* d_wts, float* d_logits, void* stream);
+/* Token -> expert permutation (stable by expert, then token, then slot): d_seg_off[E+1], d_perm_row[T*top_k] (row
+ * of slot (t,j) in expert order), d_row_token[T*top_k] (token of each permuted row). */
+int32_t eb_moe_permute(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E, int32_t* d_seg_off,
+                       int32_t* d_perm_row, int32_t* d_row_token, void* stream);
+/* x[t] = bf16(x[t] + bf16(sum_j w[t][j] * y[perm_row[t][j]])): weighted combine fused with the residual add. */
+int32_t eb_moe_combine(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
+                       int32_t H, void* d_x, void* stream);
+
+/* ---- per-token glue (K8) ---------------------------------------------------------------- */
+
+int32_t eb_rmsnorm(const void* d_x, const float* d_g, int32_t T, int32_t H, float eps, void* d_y, void* stream);
+/* cos/sin table [max_pos][head_dim/2], angle = pos * theta^(-2i/head_dim) evaluated in double (host buffers). */
+int32_t eb_rope_table(int32_t max_pos, int32_t head_dim, double theta, float* h_cos, float* h_sin);
+/* Rotate-half rotary embedding, in place, of n_heads heads starting at d_x in each token row. */
+int32_t eb_rope(void* d_x, int64_t row_stride, int32_t n_heads, int32_t head_dim, const int32_t* d_positions, int32_t T,
+                const float* d_cos, const float* d_sin, int32_t max_pos, void* stream);
+int32_t eb_residual_add(void* d_x, const void* d_y, int64_t n, void* stream);
+int32_t eb_embed(const void* d_table, int32_t V, int32_t H, const int32_t* d_tokens, int32_t T, void* d_x, void* stream);
+/* Greedy argmax over bf16 logits [T][ld], ties to the lower id; d_margin (top1 - top2) may be NULL. */
+int32_t eb_argmax(const void* d_logits, int32_t T, int64_t V, int64_t ld, int32_t* d_tok, float* d_margin, void* stream);
+
+/* ---- engine: the whole decode step ------------------------------------------------------------
+ * What an in-process implementation of the reference's engine boundary would drive once per generated token:
+ * the reference client posts to `llama-server` and reads tokens back as SSE chunks
+ * (crates/eidola-app-core/src/lib.rs:7155-7163, 7232-7340); the server relays a provider's chunks
+ * (crates/eidola-server/src/backend.rs:481-615).  Tokenisation, chat templating and sampling policy stay above
+ * this call; the engine takes token ids and returns the greedy next token of every row. */
+typedef struct eb_config {
+  int32_t n_layers, hidden, n_q_heads, n_kv_heads, head_dim;
+  int32_t window;       /* sliding window of even layers (odd layers attend to everything) */
+  int32_t n_experts, top_k, inter, vocab;
+  int32_t page_size, num_pages, max_seqs, max_pages_per_seq;
+  int32_t max_tokens;   /* token rows per step (sum of q_len) */
+  int32_t max_q_len;    /* new tokens per sequence per step: 1 = decode, k+1 = verify k drafts */
+  float rope_theta, rms_eps, init_std;
+  uint64_t seed;        /* weights are a pure function of (shape, seed) */
+  int32_t debug;        /* 1: keep per-layer routing indices and the last logits readable */
+} eb_config;
+
+typedef struct eb_engine eb_engine;
+
+int32_t eb_engine_create(const eb_config* cfg, eb_engine** out);
+int32_t eb_engine_destroy(eb_engine* e);
+/* Device bytes held by weights, KV pages and workspaces. */
+int32_t eb_engine_memory(const eb_engine* e, int64_t* weight_bytes, int64_t* kv_bytes, int64_t* work_bytes);
+/* Stand-in for prefill: fill every KV page of every layer with seeded N(0,1) values (element i of layer l is
+ * eb_normal(seed, 20000 + l, i)), so a sequence admitted with a context length has keys and values to attend to. */
+int32_t eb_engine_kv_fill_synth(eb_engine* e);
+/* Scheduler of this engine (continuous batching): admit / release between steps. */
+int32_t eb_engine_seq_admit(eb_engine* e, int32_t context_len, int32_t* slot);
+int32_t eb_engine_seq_release(eb_engine* e, int32_t slot);
+int32_t eb_engine_seq_truncate(eb_engine* e, int32_t slot, int32_t new_len);
+int32_t eb_engine_seq_len(const eb_engine* e, int32_t slot, int32_t* len);
+int32_t eb_engine_sched(eb_engine* e, eb_sched** sched); /* borrowed; lives as long as the engine */
+/*
+ * One step for n_seqs sequences: sequence i appends q_lens[i] tokens (h_tokens, flat, in sequence order), every
+ * layer runs, and h_next[row] receives the greedy token after each of the T = sum(q_lens) rows (h_margin: top-1
+ * minus top-2 logit, may be NULL).  Host buffers; the call returns after the results have arrived.
+ */
+int32_t eb_engine_step(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
+                       const int32_t* h_tokens, int32_t* h_next, float* h_margin);
+/* The same split in two so a caller can overlap host work: launch, then wait for the results. */
+int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
+                              const int32_t* h_tokens);
+int32_t eb_engine_step_wait(eb_engine* e, int32_t* h_next, float* h_margin);
+/* Milliseconds the last step spent on the device (CUDA events around its kernels) and kernels it launched. */
+int32_t eb_engine_last_step_stats(const eb_engine* e, float* device_ms, int32_t* kernel_launches);
+/* debug = 1 only: copy out the last step's logits [T][vocab] bf16 and layer routing indices [T][top_k]. */
+int32_t eb_engine_read_logits(eb_engine* e, void* h_logits, int64_t bytes);
+int32_t eb_engine_read_routing(eb_engine* e, int32_t layer, int32_t* h_idx, int64_t bytes);
+/* Copy out the residual stream [T][hidden] bf16 as it stood after `layer` (debug = 1; layer = -1: embeddings). */
+int32_t eb_engine_read_hidden(eb_engine* e, int32_t layer, void* h_x, int64_t bytes);
+/* Teacher forcing for parity tests (debug = 1): before `layer` runs (layer = n_layers: before the final norm) the
+ * residual stream of the next steps with exactly `rows` token rows is replaced by h_x [rows][hidden] bf16.  FP8
+ * activation quantisation amplifies a one-ulp difference into percent-level differences a layer later, so a
+ * layer is compared with a CPU restatement on identical inputs.  h_x = NULL clears the override. */
+int32_t eb_engine_debug_force_hidden(eb_engine* e, int32_t layer, const void* h_x, int32_t rows);
 
 #ifdef __cplusplus
 }

@@ -233,3 +233,53 @@ def argmax(logits):
     margin = np.empty(T, np.float32)
     _void("orc_argmax", _p(logits), c_i32(T), c_i64(V), _p(tok), _p(margin))
     return tok, margin
+
+
+# ---- whole decoder
+
+class Model:
+    """orc_model_*: the CPU decoder.  `cfg` is the ctypes eb_config the engine is created with."""
+
+    def __init__(self, cfg):
+        self.cfg = cfg
+        _lib.orc_model_create.restype = c_vp
+        self._h = c_vp(_lib.orc_model_create(C.byref(cfg)))
+
+    def close(self):
+        if self._h:
+            _void("orc_model_destroy", self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def kv_fill_synth(self):
+        _void("orc_model_kv_fill_synth", self._h)
+
+    def embed_table(self) -> np.ndarray:
+        """A writable view of the embedding table [vocab][hidden] (uint16 bf16 bits)."""
+        _lib.orc_model_embed.restype = C.POINTER(C.c_uint16)
+        p = _lib.orc_model_embed(self._h)
+        return np.ctypeslib.as_array(p, shape=(self.cfg.vocab, self.cfg.hidden))
+
+    def step(self, packed, tokens, block_tables, n_layers_run=None, want_logits=True, want_debug=False):
+        """packed: the dict eb_sched_pack produces.  Returns a dict of outputs."""
+        c = self.cfg
+        T, n = int(packed["n_tokens"]), len(packed["slots"])
+        bt = _i32(block_tables)
+        nl = c.n_layers if n_layers_run is None else n_layers_run
+        out = {"next": np.empty(T, np.int32), "margin": np.empty(T, np.float32)}
+        logits = np.empty((T, c.vocab), np.uint16) if want_logits else None
+        ridx = np.zeros((c.n_layers, T, c.top_k), np.int32) if want_debug else None
+        rlog = np.zeros((c.n_layers, T, c.n_experts), np.float32) if want_debug else None
+        hid = np.zeros((c.n_layers + 1, T, c.hidden), np.uint16) if want_debug else None
+        opt = lambda a: _p(a) if a is not None else c_vp(None)  # noqa: E731
+        _void("orc_model_step", self._h, c_i32(T), c_i32(n), _p(_i32(tokens)), _p(_i32(packed["tok_slot"])),
+              _p(_i32(packed["positions"])), _p(_i32(packed["slots"])), _p(_i32(packed["q_off"])),
+              _p(_i32(packed["ctx_lens"])), _p(bt), c_i32(bt.shape[1]), c_i32(nl), _p(out["next"]), _p(out["margin"]),
+              opt(logits), opt(ridx), opt(rlog), opt(hid))
+        out.update(logits=logits, route_idx=ridx, route_logits=rlog, hidden=hid)
+        return out

@@ -2,8 +2,9 @@
 
 There is no reference implementation of this path to compile (the reference project
 delegates inference to a third-party process), so there is no oracle/_ref here.
-synth.cpp is compiled with -ffp-contract=off: its arithmetic must round exactly like
-the device intrinsics.  -march=x86-64-v3 (AVX2+FMA) keeps the library runnable on a
+Everything is compiled with -ffp-contract=off: a*b+c rounds twice unless the source says
+fmaf(), so the arithmetic does not depend on the compiler's contraction choices and matches
+the device intrinsics operation for operation.  -march=x86-64-v3 (AVX2+FMA) keeps the library runnable on a
 host other than the one that built it.
 """
 from __future__ import annotations
@@ -14,11 +15,11 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "liboracle.so"
-COMMON = ["-O3", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-std=c++17", "-Wall"]
+COMMON = ["-O3", "-march=x86-64-v3", "-ffp-contract=off", "-fopenmp", "-fPIC", "-std=c++17", "-Wall"]
 
 
 def build(force: bool = False) -> Path:
-    srcs = {"synth.cpp": ["-ffp-contract=off"], "oracle.cpp": [], "model.cpp": []}
+    srcs = {"synth.cpp": [], "oracle.cpp": [], "model.cpp": []}
     deps = [HERE / s for s in srcs if (HERE / s).exists()] + sorted((HERE.parent / "include").glob("*.h"))
     if not force and LIB_PATH.exists() and all(d.stat().st_mtime <= LIB_PATH.stat().st_mtime for d in deps):
         return LIB_PATH

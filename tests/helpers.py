@@ -60,12 +60,12 @@ def make_sinks_host(n_q, seed):
 class AttnCase:
     """A ragged paged-attention problem resident on the device, built through the C ABI only."""
 
-    def __init__(self, ctx_lens, q_lens, n_kv, seed, sm_count, extra_pages=3, device_synth=False):
+    def __init__(self, ctx_lens, q_lens, n_kv, seed, sm_count, extra_pages=3, device_synth=False, group=8):
         import eidola_b200 as eb
         from eidola_b200 import capi
         from eidola_b200.capi import DeviceBuffer
         self.eb = eb
-        self.n_kv, self.n_q, self.seed, self.sm_count = n_kv, n_kv * 8, seed, sm_count
+        self.n_kv, self.n_q, self.seed, self.sm_count = n_kv, n_kv * group, seed, sm_count
         ctx_lens = np.asarray(ctx_lens, np.int32)
         q_lens = np.asarray(q_lens, np.int32)
         n = len(ctx_lens)

@@ -81,6 +81,19 @@ def test_attention_small_matches_oracle(gpu, n_kv, window, q_mode):
     assert plan["n_items"] > len(ctx) or window  # chunk 3 really split something
 
 
+@pytest.mark.parametrize("n_kv", [2, 8])
+@pytest.mark.parametrize("window", [0, 128])
+def test_attention_group_of_four(gpu, n_kv, window):
+    """8 query heads over 2 KV heads (the tiny decode configuration) and 32 over 8: GQA groups of 4."""
+    ctx = np.array(CTX_SMALL, np.int32)
+    ql = np.minimum(ctx, np.array([1, 2, 3, 4, 5, 1, 12, 2, 1, 7], np.int32))
+    case = AttnCase(ctx, ql, n_kv, seed=3, sm_count=gpu["sm_count"], group=4)
+    want = case.oracle(window)
+    for chunk in (0, 5):
+        got, _ = case.run(window, chunk)
+        assert_close_bf16(got, want, what=f"group 4, n_kv={n_kv} window={window} chunk={chunk}")
+
+
 def test_attention_benchmark_shape_matches_oracle(gpu):
     """256 ragged sequences, lognormal(median 2048, sigma 1) clipped to [16, 32768], 64 q / 8 kv heads, seed 1."""
     ctx = lognormal_lengths(256, 2048, 1.0, 16, 32768, seed=1)
