@@ -1,21 +1,29 @@
 #!/usr/bin/env python
 """Benchmark of the decode hot path on B200 through the C ABI of libeidola_b200.so.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decoder|attn]
 
-Prints ONE JSON line.  Workloads:
-  attn   paged sink-attention decode of one layer: 256 ragged sequences, 64 query / 8 KV heads, head_dim 64,
-         bf16 KV cache in 16-token pages, context lengths lognormal(median 2048, sigma 1) clipped to [16, 32768],
-         per-head sink logits ~ N(0,1), Q/K/V ~ N(0,1), seed 1 (+rank).  One step = one decode token per sequence.
-Inputs are synthetic (seeded, generated on the device); the KV working set (~1.5 GB) is an order of magnitude
-larger than the L2, so no flush is needed between iterations.
+Prints ONE JSON line.
 
---impl reference times the CPU oracle (the reference project has no implementation of this path) on a bounded
-sample of the same workload with all host threads.
+decoder (default): the gpt-oss-20b-shaped random-init FP8 decoder -- 24 layers (even: 128-token sliding window,
+    odd: full attention), hidden 2880, 64 query / 8 KV heads, head_dim 64, 32 experts top-4 (intermediate 2880),
+    vocabulary 201088 -- decoding 256 concurrent ragged sequences greedily, prompt lengths uniform in [128, 8192]
+    (seed 4 + rank).  Prefill is stood in for by filling the KV pages with seeded N(0,1) values.  One step = one
+    new token for every sequence, through eb_engine_step: token ids go in from host memory, greedy tokens come
+    back to host memory and are fed to the next step.
+attn: one layer of paged sink-attention decode on 256 ragged sequences with lognormal(median 2048, sigma 1)
+    context lengths clipped to [16, 32768] (seed 1 + rank); the kernel-level benchmark of the attention path.
+
+Inputs are synthetic (seeded, generated on the device).  The per-step working set (weights 20 GB + KV 28 GB for
+the decoder, 1.5 GB of KV for attn) is far larger than the L2, so nothing is flushed between iterations.
+
+--impl reference times the CPU oracle on the host cores: the reference project has no implementation of this path
+(it delegates inference to a third-party process), so the committed CPU restatement is the CPU arm.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import json
 import os
 import statistics
@@ -31,10 +39,11 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 HEAD_DIM, PAGE = 64, 16
-# dram bytes read+written per launch / algorithmic bytes, from the ncu capture summarised in
+S_KV, S_Q, S_SINK = 101, 102, 103
+# dram bytes read+written per launch / algorithmic bytes of attn_kernel, from the ncu capture summarised in
 # profiles/attn_kernel_paged_sink_decode.md (64-sequence case, scaled by the bytes processed)
 NCU_TRAFFIC_RATIO_ATTN = 1.028
-S_KV, S_Q, S_SINK = 101, 102, 103
+METRIC = "decode tokens/s @256 ragged seqs"
 
 
 def lognormal_lengths(n, median, sigma, lo, hi, seed):
@@ -51,6 +60,10 @@ def measured_peaks() -> tuple[float, str]:
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def rank_device(rank: int) -> int:
+    return int(os.environ.get("LOCAL_RANK", rank))
 
 
 class ClockSampler:
@@ -85,18 +98,122 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             pass
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         for r in self.rows:
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
+                pw.append(float(r[2]))
             except Exception:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------ decoder workload
+
+def decoder_config(n_layers=24, n_seqs=256, max_ctx=8192, steps=0, n_experts=32, debug=0, seed=4):
+    from eidola_b200.capi import make_config
+    pages_per_seq = (max_ctx + steps + PAGE) // PAGE + 1
+    return make_config(n_layers=n_layers, hidden=2880, n_q_heads=64, n_kv_heads=8, window=128, n_experts=n_experts,
+                       top_k=4, inter=2880, vocab=201088, num_pages=1, max_seqs=n_seqs,
+                       max_pages_per_seq=pages_per_seq, max_tokens=n_seqs, max_q_len=1, seed=seed, debug=debug)
+
+
+class DecoderWorkload:
+    name = ("gpt-oss-20b-shaped random-init FP8 decoder: 24 layers (even 128-window, odd full), hidden 2880, 64q/8kv "
+            "heads d64, 32 experts top-4 inter 2880, vocab 201088; 256 ragged seqs, prompts U[128,8192], greedy decode")
+
+    def __init__(self, rank: int, total_steps: int, n_seqs=256, n_layers=24, profile=False):
+        import eidola_b200 as eb
+        self.eb = eb
+        seed = 4 + rank
+        rng = np.random.default_rng(seed)
+        self.ctx0 = rng.integers(128, 8193, size=n_seqs).astype(np.int32)
+        cfg = decoder_config(n_layers=n_layers, n_seqs=n_seqs, steps=total_steps, debug=2 if profile else 0, seed=seed)
+        cfg.num_pages = int(((self.ctx0.astype(np.int64) + total_steps + PAGE) // PAGE + 1).sum()) + 64
+        self.cfg = cfg
+        self.eng = eb.Engine(cfg)
+        self.eng.kv_fill_synth()
+        self.slots = np.array([self.eng.admit(int(L)) for L in self.ctx0], np.int32)
+        self.q_lens = np.ones(n_seqs, np.int32)
+        self.tokens = rng.integers(0, cfg.vocab, size=n_seqs).astype(np.int32)
+        self.steps_done = 0
+        self.units_per_step = n_seqs
+        self.mem = self.eng.memory()
+
+    def step(self):
+        """One greedy decode step through the host-buffer API: the returned tokens feed the next step."""
+        nxt, _ = self.eng.step(self.slots, self.q_lens, self.tokens)
+        self.tokens = nxt
+        self.steps_done += 1
+        return nxt
+
+    def ctx_now(self) -> np.ndarray:
+        return self.ctx0.astype(np.int64) + self.steps_done
+
+    def attn_alg_bytes_full_layer(self) -> int:
+        """Algorithmic bytes of one full-attention layer launch at the current lengths: K and V of every context
+        token for 8 KV heads (2 KiB per token), Q in and O out, one block-table entry per page."""
+        ctx = self.ctx_now() + 1
+        n = len(ctx)
+        return int(ctx.sum()) * 2048 + 2 * n * 64 * HEAD_DIM * 2 + 4 * int(((ctx + PAGE - 1) // PAGE).sum())
+
+    def step_alg_bytes(self) -> dict:
+        c = self.cfg
+        ctx = self.ctx_now() + 1
+        per_layer_dense = (64 + 16) * 64 * 2880 + 2880 * 4096          # QKV + O, e4m3
+        per_layer_experts = c.n_experts * 3 * 2880 * 2880                # all experts are hit at 1024 routed slots
+        weights = c.n_layers * (per_layer_dense + per_layer_experts + c.n_experts * 2880 * 2) + c.vocab * 2880
+        kv_full = (c.n_layers // 2) * int(ctx.sum()) * 2048
+        kv_win = (c.n_layers - c.n_layers // 2) * int(np.minimum(ctx, 128 + PAGE).sum()) * 2048
+        return {"weights": weights, "kv_full": kv_full, "kv_window": kv_win, "total": weights + kv_full + kv_win}
+
+    def config(self) -> dict:
+        return {"workload": self.name, "n_seqs": int(len(self.ctx0)), "n_layers": int(self.cfg.n_layers),
+                "mean_context": float(self.ctx_now().mean()),
+                "device_bytes": self.mem,
+                "prefill": "KV pages filled with seeded N(0,1) values (stand-in for prefill)",
+                "l2": "per-step working set ~%.0f GB >> L2, no flush" % (self.step_alg_bytes()["total"] / 1e9)}
+
+
+def decoder_cpu_sample(n_seqs=32, seed=4):
+    """CPU oracle on a bounded sample of the decoder workload: the first two layers (one windowed, one full) and the
+    LM head, one step, n_seqs of the 256 sequences.  Returns (tokens_per_second_extrapolated, description, seconds)."""
+    from oracle import binding as orc
+    from oracle import sched as osched
+    cfg = decoder_config(n_layers=2, n_seqs=n_seqs, steps=2, seed=seed)
+    rng = np.random.default_rng(seed)
+    ctx = rng.integers(128, 8193, size=256).astype(np.int32)[:: 256 // n_seqs][:n_seqs]
+    cfg.num_pages = int(((ctx.astype(np.int64) + 2 + PAGE) // PAGE + 1).sum()) + 8
+    model = orc.Model(cfg)
+    model.kv_fill_synth()
+    sch = osched.Sched(cfg.num_pages, PAGE, n_seqs, cfg.max_pages_per_seq, seed)
+    slots = [sch.admit(int(L)) for L in ctx]
+    for s in slots:
+        sch.extend(s, sch.len[s] + 1)
+    p = sch.pack(slots, [1] * n_seqs)
+    p.update(slots=slots, n_tokens=n_seqs)
+    bt = np.array(sch.tables, np.int32)
+    toks = rng.integers(0, cfg.vocab, size=n_seqs).astype(np.int32)
+    t0 = time.perf_counter()
+    model.step(p, toks, bt, n_layers_run=2, want_logits=False)           # 2 layers + head
+    t_full = time.perf_counter() - t0
+    for s in slots:
+        sch.extend(s, sch.len[s] + 1)
+    p = sch.pack(slots, [1] * n_seqs)
+    p.update(slots=slots, n_tokens=n_seqs)
+    bt = np.array(sch.tables, np.int32)
+    t0 = time.perf_counter()
+    model.step(p, toks, bt, n_layers_run=0, want_logits=False)           # embedding + head only
+    t_head = time.perf_counter() - t0
+    t_step = (t_full - t_head) * 12 + t_head                               # 24 layers = 12 (windowed, full) pairs
+    desc = ("CPU oracle, %d of 256 sequences, one step: 2 of 24 layers (one windowed, one full) + LM head timed "
+            "(%.1f s), layer time x12 + head -> %.1f s per step" % (n_seqs, t_full + t_head, t_step))
+    return n_seqs / t_step, desc, t_full + t_head
 
 
 # ------------------------------------------------------------------------------------------ attention workload
@@ -138,16 +255,13 @@ class AttnWorkload:
                                  out_stride=self.n_q * HEAD_DIM, d_cache=self.d_cache.ptr, num_pages=self.num_pages,
                                  d_block_tables=self.d_bt.ptr, bt_stride=self.bt.shape[1], packed=self.packed,
                                  plan=self.plan, d_sinks=self.d_sinks.ptr, window=window, n_q=self.n_q, n_kv=self.n_kv)
-        # pinned host staging for the end-to-end leg
-        self.h_q, self.h_out = c_vp(), c_vp()
-        capi.call("eb_host_alloc", __import__("ctypes").byref(self.h_q), capi.c_sz(self.q_bytes))
-        capi.call("eb_host_alloc", __import__("ctypes").byref(self.h_out), capi.c_sz(self.q_bytes))
+        self.h_q, self.h_out = c_vp(), c_vp()  # pinned host staging for the end-to-end leg
+        capi.call("eb_host_alloc", C.byref(self.h_q), capi.c_sz(self.q_bytes))
+        capi.call("eb_host_alloc", C.byref(self.h_out), capi.c_sz(self.q_bytes))
         capi.call("eb_copy_d2h", self.h_q, c_vp(self.d_q.ptr), capi.c_sz(self.q_bytes), None)
         capi.call("eb_device_sync")
-        self.units_per_step = T  # decode tokens
+        self.units_per_step = T
         visible = np.minimum(self.ctx, window) if window else self.ctx
-        # algorithmic bytes of one launch: K and V of every visible token for all 8 KV heads (2 KiB per token),
-        # Q in and O out (bf16), and one int32 block-table entry per visible page
         self.alg_bytes = int(visible.astype(np.int64).sum()) * 2 * self.n_kv * HEAD_DIM * 2 + 2 * self.q_bytes \
             + 4 * int(((visible.astype(np.int64) + PAGE - 1) // PAGE).sum())
         self.launches_per_step = 2 if self.plan["n_parts"] > n else 1
@@ -162,36 +276,28 @@ class AttnWorkload:
         capi.call("eb_copy_d2h", self.h_out, c_vp(self.d_out.ptr), c_sz(self.q_bytes), c_vp(stream))
         capi.call("eb_stream_sync", c_vp(stream))
 
-    e2e_h2d = property(lambda self: self.q_bytes)
-    e2e_d2h = property(lambda self: self.q_bytes)
-
     def config(self) -> dict:
         return {"workload": self.name, "n_seqs": len(self.ctx), "sum_context_tokens": int(self.ctx.sum()),
                 "attn_items": self.plan["n_items"], "split_parts": self.plan["n_parts"],
                 "l2": "working set %.2f GB >> L2 %.0f MB, no flush" % (self.alg_bytes / 1e9, self.info["l2_bytes"] / 1e6)}
 
-    def cpu_sample(self, n_sample=24):
-        """Oracle on every (256/n_sample)-th sequence; returns (tokens, seconds, description)."""
+    def cpu_sample(self, reps=20):
         from oracle import binding as orc
-        idx = list(range(0, len(self.ctx), max(1, len(self.ctx) // n_sample)))[:n_sample]
         cache = self.d_cache.to_array(np.uint16, (self.num_pages, 2, self.n_kv, PAGE, HEAD_DIM))
         q = self.d_q.to_array(np.uint16, (self.T, self.n_q * HEAD_DIM))
         sinks = self.d_sinks.to_array(np.float32, self.n_q)
         p = self.packed
-        sel = np.array(idx, np.int32)
-        q_off = np.arange(len(sel) + 1, dtype=np.int32)
         t0 = time.perf_counter()
-        out = orc.attn_paged_sink(q[sel], cache, self.bt, p["slots"][sel], q_off, p["ctx_lens"][sel], sinks,
-                                  self.window, self.n_q, self.n_kv)
+        for _ in range(reps):
+            out = orc.attn_paged_sink(q, cache, self.bt, p["slots"], p["q_off"], p["ctx_lens"], sinks, self.window,
+                                      self.n_q, self.n_kv)
         dt = time.perf_counter() - t0
-        return len(sel), dt, out, sel
+        return self.T * reps / dt, dt, out
 
 
-def rank_device(rank: int) -> int:
-    return int(os.environ.get("LOCAL_RANK", rank))
+# ------------------------------------------------------------------------------------------ drivers
 
-
-def run_ours(args) -> dict:
+def setup_dist():
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     dist = None
@@ -200,6 +306,121 @@ def run_ours(args) -> dict:
         import torch.distributed as dist  # plumbing only: barrier and max-over-ranks of the timings
         torch.cuda.set_device(rank_device(rank))
         dist.init_process_group("nccl", device_id=torch.device("cuda", rank_device(rank)))
+    return rank, world, dist
+
+
+def reduce_max(dist, values):
+    if dist is None:
+        return values
+    import torch
+    t = torch.tensor(values, device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def run_decoder(args) -> dict:
+    rank, world, dist = setup_dist()
+    import eidola_b200 as eb
+    from eidola_b200 import capi
+    capi.call("eb_device_set", capi.c_i32(rank_device(rank)))
+    K, W = args.steps, args.warmup
+    n_prof = 3
+    wl = DecoderWorkload(rank, total_steps=K + W + n_prof + 2, n_seqs=args.seqs, n_layers=args.layers)
+    stream = wl.eng.stream()
+
+    def barrier():
+        capi.call("eb_device_sync")
+        if dist is not None:
+            dist.barrier()
+            capi.call("eb_device_sync")
+
+    sampler = ClockSampler(rank_device(rank))
+    if rank == 0:
+        sampler.start()
+    for _ in range(W):
+        wl.step()
+    barrier()
+    timer = eb.Timer(stream)
+    dev_ms = 0.0
+    launches = 0
+    ctx_mid = None
+    barrier()
+    timer.start()
+    for i in range(K):
+        wl.step()
+        ms, nl = wl.eng.last_step_stats()
+        dev_ms += ms
+        launches += nl
+        if i == K // 2:
+            ctx_mid = wl.step_alg_bytes()
+    e2e_ms = timer.stop()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    status = eb.status_read()
+    dev_ms, e2e_ms = reduce_max(dist, [dev_ms, e2e_ms])
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return {}
+
+    units = wl.units_per_step * world
+    peak, peak_kind = measured_peaks()
+    out = {
+        "metric": METRIC,
+        "value": units * K / (dev_ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8 e4m3 x e4m3 -> fp32 (GEMMs), bf16 (attention, activations)", "data": "synthetic",
+        "config": dict(wl.config(), parallelism=("%d independent replicas (data parallel over sequences)" % world) if world > 1 else "single GPU",
+                       value_is="sum of per-step device time (CUDA events around the step's copies and kernels)",
+                       e2e_is="CUDA events on the engine stream around K calls of eb_engine_step with host token buffers"),
+        "e2e": {"value": units * K / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms / K,
+                "h2d_bytes_per_step": 4 * (3 * args.seqs + 3 * args.seqs + 1) + 16 * 1300,
+                "d2h_bytes_per_step": 8 * args.seqs},
+        "gpu_launches": launches,
+        "step_bytes": ctx_mid,
+        "step_hbm_bound": {"bytes": ctx_mid["total"], "floor_ms": ctx_mid["total"] / (peak * 1e6),
+                           "frac_of_floor": (ctx_mid["total"] / (peak * 1e6)) / (dev_ms / K), "peak_gbs": peak, "peak_kind": peak_kind},
+        "clocks": clocks, "device_status": status,
+    }
+    # ---- roofline of the dominant kernel (paged sink attention on the full layers), measured with CUDA events
+    # around each call in a few extra steps of the same run on a second engine handle that has per-call timing on
+    wl.eng.close()
+    wl2 = DecoderWorkload(rank, total_steps=W + n_prof + 2, n_seqs=args.seqs, n_layers=args.layers, profile=True)
+    for _ in range(3):
+        wl2.step()
+    acc = {}
+    alg = 0
+    step_ms_prof = 0.0
+    for _ in range(n_prof):
+        alg_bytes = wl2.attn_alg_bytes_full_layer()
+        wl2.step()
+        for k, v in wl2.eng.last_step_breakdown().items():
+            acc[k] = acc.get(k, 0.0) + v / n_prof
+        alg += alg_bytes / n_prof
+        step_ms_prof = wl2.eng.last_step_stats()[0]
+    n_full = wl2.cfg.n_layers // 2
+    per_launch_ms = acc["attn_full"] / max(n_full, 1)
+    achieved = alg / (per_launch_ms * 1e-3) / 1e9 if per_launch_ms > 0 else 0.0
+    out["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                       "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_RATIO_ATTN * alg,
+                       "kernel": "attn_kernel (+ attn_merge_kernel), full-attention layers",
+                       "alg_bytes_per_launch": alg, "avg_launch_ms": per_launch_ms, "launches_timed": n_prof * n_full,
+                       "frac_of_nominal_8TBs": achieved / 8000.0}
+    out["step_breakdown_ms"] = dict(acc, step_total=step_ms_prof,
+                                    other=step_ms_prof - sum(acc.values()),
+                                    note="%d steps with CUDA events around each call (adds event overhead)" % n_prof)
+    wl2.eng.close()
+    if world == 1 and not args.no_cpu:
+        v, desc, secs = decoder_cpu_sample()
+        out["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port", "sample": desc}
+    if dist is not None:
+        dist.destroy_process_group()
+    return out
+
+
+def run_attn(args) -> dict:
+    rank, world, dist = setup_dist()
     import eidola_b200 as eb
     from eidola_b200 import capi
     capi.call("eb_device_set", capi.c_i32(rank_device(rank)))
@@ -212,7 +433,6 @@ def run_ours(args) -> dict:
             dist.barrier()
             capi.call("eb_device_sync")
 
-    # ---- device-resident throughput (value) + per-launch durations (roofline)
     sampler = ClockSampler(rank_device(rank))
     if rank == 0:
         sampler.start()
@@ -226,15 +446,14 @@ def run_ours(args) -> dict:
     for t in timers:
         t.start()
         wl.step()
-        t.e1_recorded = capi.call("eb_event_record", t.e1, None)
+        capi.call("eb_event_record", t.e1, None)
     total_ms = total.stop()
     per_launch = []
     for t in timers:
         ms = capi.c_f32(0)
-        capi.call("eb_event_elapsed_ms", t.e0, t.e1, __import__("ctypes").byref(ms))
+        capi.call("eb_event_elapsed_ms", t.e0, t.e1, C.byref(ms))
         per_launch.append(ms.value)
     barrier()
-    # ---- end to end through the C ABI with host buffers
     for _ in range(min(W, 3)):
         wl.step_e2e()
     barrier()
@@ -246,48 +465,35 @@ def run_ours(args) -> dict:
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     status = eb.status_read()
-
-    if dist is not None:
-        import torch
-        t = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms = t.tolist()
+    total_ms, e2e_ms = reduce_max(dist, [total_ms, e2e_ms])
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return {}
-
     peak, peak_kind = measured_peaks()
     avg_launch_ms = sum(per_launch) / len(per_launch)
     achieved = wl.alg_bytes / (avg_launch_ms * 1e-3) / 1e9
     units = wl.units_per_step * world
     out = {
-        "metric": "decode tokens/s @256 ragged seqs",
-        "value": units * K / (total_ms * 1e-3),
-        "unit": "tokens/s",
-        "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": total_ms / K,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
+        "metric": METRIC, "value": units * K / (total_ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": total_ms / K,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": dict(wl.config(), parallelism=("replicas x%d (independent sequence sets)" % world) if world > 1 else "single GPU"),
-        "e2e": {"value": units * K / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": wl.e2e_h2d,
-                "d2h_bytes_per_step": wl.e2e_d2h},
+        "e2e": {"value": units * K / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": wl.q_bytes,
+                "d2h_bytes_per_step": wl.q_bytes},
         "gpu_launches": wl.launches_per_step * K,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_RATIO_ATTN * wl.alg_bytes, "kernel": "attn_kernel (+ attn_merge_kernel)",
-                     "alg_bytes_per_launch": wl.alg_bytes, "avg_launch_ms": avg_launch_ms,
-                     "frac_of_nominal_8TBs": achieved / 8000.0},
-        "clocks": clocks,
-        "device_status": status,
+                     "peak_kind": peak_kind, "traffic": NCU_TRAFFIC_RATIO_ATTN * wl.alg_bytes,
+                     "kernel": "attn_kernel (+ attn_merge_kernel)", "alg_bytes_per_launch": wl.alg_bytes,
+                     "avg_launch_ms": avg_launch_ms, "frac_of_nominal_8TBs": achieved / 8000.0},
+        "clocks": clocks, "device_status": status,
     }
-    # ---- CPU baseline on this box's host cores (rank 0, N=1 only)
     if world == 1 and not args.no_cpu:
-        n, dt, cpu_out, sel = wl.cpu_sample()
-        gpu_out = wl.d_out.to_array(np.uint16, (wl.T, wl.n_q * HEAD_DIM))[sel]
-        g = (gpu_out.astype(np.uint32) << 16).view(np.float32)
+        v, dt, cpu_out = wl.cpu_sample()
+        g = (wl.d_out.to_array(np.uint16, (wl.T, wl.n_q * HEAD_DIM)).astype(np.uint32) << 16).view(np.float32)
         c = (cpu_out.astype(np.uint32) << 16).view(np.float32)
-        out["cpu_baseline"] = {"value": n / dt, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
-                               "sample": "%d of 256 sequences (every %dth), one decode token each, %.1f s" % (n, 256 // n, dt),
+        out["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+                               "sample": "all 256 sequences, 20 repetitions, %.1f s" % dt,
                                "max_abs_diff_vs_gpu": float(np.abs(g - c).max())}
     if dist is not None:
         dist.destroy_process_group()
@@ -295,43 +501,24 @@ def run_ours(args) -> dict:
 
 
 def run_reference(args) -> dict:
-    """The reference arm: the CPU oracle (no reference implementation of this path exists) on all host threads."""
+    """The reference arm: the CPU oracle (the reference project has no implementation of this path), all host threads."""
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return {}
-    from oracle import binding as orc
-    n_sample = 16
-    ctx = lognormal_lengths(256, 2048, 1.0, 16, 32768, 1)
-    sel = np.arange(0, 256, 256 // n_sample)[:n_sample]
-    ctx_s = ctx[sel]
-    pages = ((ctx_s.astype(np.int64) + PAGE - 1) // PAGE)
-    num_pages = int(pages.sum())
-    bt = np.full((n_sample, int(pages.max())), -1, np.int32)
-    perm = np.random.default_rng(1).permutation(num_pages)
-    k = 0
-    for i, n in enumerate(pages):
-        bt[i, :n] = perm[k:k + n]
-        k += int(n)
-    cache = orc.synth_normal_bf16(1, S_KV, 0, num_pages * 2 * 8 * PAGE * HEAD_DIM).reshape(num_pages, 2, 8, PAGE, HEAD_DIM)
-    q = orc.synth_normal_bf16(1, S_Q, 0, n_sample * 64 * HEAD_DIM).reshape(n_sample, 64 * HEAD_DIM)
-    sinks = orc.synth_normal_f32(1, S_SINK, 0, 64)
-    q_off = np.arange(n_sample + 1, dtype=np.int32)
-    slots = np.arange(n_sample, dtype=np.int32)
-    K, W = args.steps, args.warmup
-    for _ in range(min(W, 1)):
-        orc.attn_paged_sink(q, cache, bt, slots, q_off, ctx_s, sinks, 0, 64, 8)
-    K = max(1, min(K, 5))
+    K = max(1, min(args.steps, 2))
+    vals, desc = [], ""
     t0 = time.perf_counter()
     for _ in range(K):
-        orc.attn_paged_sink(q, cache, bt, slots, q_off, ctx_s, sinks, 0, 64, 8)
+        v, desc, _ = decoder_cpu_sample()
+        vals.append(v)
     dt = time.perf_counter() - t0
-    v = n_sample * K / dt
-    sample = "CPU oracle (port; the reference has no implementation of this path), %d of 256 sequences per step" % n_sample
+    v = float(np.mean(vals))
+    sample = desc + "; the reference project has no implementation of this path, so this is the committed CPU port"
     return {
-        "impl": "reference", "metric": "decode tokens/s @256 ragged seqs", "value": v, "unit": "tokens/s",
-        "n_gpus": int(os.environ.get("WORLD_SIZE", 1)), "steps": K, "warmup": min(W, 1), "ms_per_step": dt / K * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": AttnWorkload.name, "sample": sample},
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", 1)), "steps": K, "warmup": 0, "ms_per_step": 1e3 * 32 / v,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8 weights/activations decoded to fp32",
+        "data": "synthetic", "config": {"workload": DecoderWorkload.name, "sample": sample, "wall_s": dt},
         "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -340,14 +527,22 @@ def run_reference(args) -> dict:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decoder", choices=["decoder", "attn"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--seqs", type=int, default=256, help="sequences in the batch (smaller values are for profiler captures)")
+    ap.add_argument("--layers", type=int, default=24, help="decoder layers (smaller values are for profiler captures)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "ours":
+        args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        out = run_reference(args)
+    elif args.workload == "attn":
+        out = run_attn(args)
+    else:
+        out = run_decoder(args)
     if out:
         print(json.dumps(out), flush=True)
 

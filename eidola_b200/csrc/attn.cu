@@ -527,7 +527,7 @@ int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
              "eb_attn_paged_sink: negative size");
   EB_REQUIRE(a->q_stride % 2 == 0 && a->out_stride % 2 == 0 && (uintptr_t)a->d_q % 4 == 0 && (uintptr_t)a->d_out % 4 == 0,
              EB_ERR_ARG, "eb_attn_paged_sink: q/out must be 4-byte aligned with even strides");
-  EB_REQUIRE((uintptr_t)a->d_cache % 1024 == 0, EB_ERR_ARG, "eb_attn_paged_sink: cache must be 1024-byte aligned");
+  EB_REQUIRE((uintptr_t)a->d_cache % 16 == 0, EB_ERR_ARG, "eb_attn_paged_sink: cache must be 16-byte aligned");
   EB_REQUIRE(a->n_parts == 0 || (a->d_part_acc && a->d_part_ml), EB_ERR_ARG, "eb_attn_paged_sink: null workspace");
   if (a->n_seqs == 0 || a->n_items == 0) return EB_OK;
   const int64_t rows = (int64_t)a->num_pages * 2 * a->n_kv * kPage;

@@ -86,6 +86,12 @@ struct eb_engine {
   uint16_t* dbg_force = nullptr;       // [n_layers+1][max_tokens][hidden]: residual stream to impose before a layer
   std::vector<int32_t> force_rows;     // rows imposed before each layer (0 = none)
 
+  // per-category device time of the last step (debug & 2): 0 attention full, 1 attention windowed, 2 dense GEMMs,
+  // 3 expert GEMMs, 4 LM head
+  std::vector<cudaEvent_t> prof_ev;
+  std::vector<int> prof_cat;
+  float prof_ms[8] = {0};
+
   // state of the step in flight
   int32_t cur_T = 0;
   bool in_flight = false;
@@ -226,7 +232,7 @@ int32_t init_work(eb_engine* e) {
   EB_CUDA(cudaMallocHost((void**)&e->h_stage, e->stage_words * sizeof(int32_t)));
   EB_TRY(dev_alloc(e, &e->d_stage, e->stage_words, w));
   EB_CUDA(cudaMallocHost((void**)&e->h_result, 2 * (size_t)T * sizeof(int32_t)));
-  if (c.debug) {
+  if (c.debug & 1) {
     EB_TRY(dev_alloc(e, &e->dbg_route, (size_t)c.n_layers * R, w));
     EB_TRY(dev_alloc(e, &e->dbg_hidden, (size_t)(c.n_layers + 1) * T * H, w));
     EB_TRY(dev_alloc(e, &e->dbg_force, (size_t)(c.n_layers + 1) * T * H, w));
@@ -270,6 +276,19 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   int& n = e->launches;
   n = 0;
 
+  const bool prof = (c.debug & 2) != 0;
+  size_t prof_used = 0;
+  e->prof_cat.clear();
+  auto mark = [&](int cat) {  // one event before and one after a call; cat < 0 closes the open interval
+    if (!prof) return;
+    if (prof_used == e->prof_ev.size()) {
+      cudaEvent_t ev;
+      if (cudaEventCreate(&ev) != cudaSuccess) return;
+      e->prof_ev.push_back(ev);
+    }
+    cudaEventRecord(e->prof_ev[prof_used++], e->stream);
+    e->prof_cat.push_back(cat);
+  };
   auto dense = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout) -> int32_t {
     eb_gemm_args g = {};
     g.d_x8 = x8;
@@ -308,11 +327,11 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
 
   EB_TRY(eb_embed(e->embed, c.vocab, H, d_tokens, T, e->x, st));
   n += 1;
-  if (c.debug)
+  if (c.debug & 1)
     EB_CUDA(cudaMemcpyAsync(e->dbg_hidden, e->x, (size_t)T * H * 2, cudaMemcpyDeviceToDevice, e->stream));
 
   auto impose = [&](int l) -> int32_t {  // debug: replace the residual stream before layer l (n_layers = before the head)
-    if (c.debug && e->force_rows[(size_t)l] == T)
+    if ((c.debug & 1) && e->force_rows[(size_t)l] == T)
       EB_CUDA(cudaMemcpyAsync(e->x, e->dbg_force + (size_t)l * c.max_tokens * H, (size_t)T * H * 2,
                               cudaMemcpyDeviceToDevice, e->stream));
     return EB_OK;
@@ -323,7 +342,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     EB_TRY(impose(l));
     EB_TRY(eb_rmsnorm(e->x, L.g_attn, T, H, c.rms_eps, e->h, st));
     EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
+    mark(2);
     EB_TRY(dense(e->h8, e->sh, L.wqkv, e->nqkv, H, e->qkv));
+    mark(-1);
     EB_TRY(eb_rope(e->qkv, e->nqkv, c.n_q_heads + c.n_kv_heads, c.head_dim, d_positions, T, e->rope_cos, e->rope_sin, max_pos, st));
     EB_TRY(eb_kv_append(L.cache, c.num_pages, c.n_kv_heads, c.head_dim, c.page_size, e->qkv + e->hqd,
                         e->qkv + e->hqd + c.n_kv_heads * c.head_dim, e->nqkv, e->d_bt, c.max_pages_per_seq, d_tok_slot,
@@ -355,20 +376,28 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     a.n_parts = plans[pi].n_parts;
     a.d_part_acc = e->part_acc;
     a.d_part_ml = e->part_ml;
+    mark(pi ? 1 : 0);
     EB_TRY(eb_attn_paged_sink(&a, st));
+    mark(-1);
     EB_TRY(eb_quant_act_block128(e->attn, e->hqd, T, e->hqd, nullptr, 1, e->a8, e->sa, st));
+    mark(2);
     EB_TRY(dense(e->a8, e->sa, L.wo, H, e->hqd, e->o));
+    mark(-1);
     EB_TRY(eb_residual_add(e->x, e->o, (int64_t)T * H, st));
     EB_TRY(eb_rmsnorm(e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
     EB_TRY(eb_moe_route(e->h, L.wr, T, E, H, c.top_k, e->r_idx, e->r_wts, nullptr, st));
     EB_TRY(eb_moe_permute(e->r_idx, T, c.top_k, E, e->seg_off, e->perm_row, e->row_token, st));
     EB_TRY(eb_quant_gather_block128(e->h, H, T, e->row_token, R, H, e->seg_off, E, e->xp8, e->sxp, st));
+    mark(3);
     EB_TRY(grouped(e->xp8, e->sxp, L.w1, 2 * I, H, e->gu));
+    mark(-1);
     EB_TRY(eb_quant_silu_mul_block128(e->gu, 2 * I, R, I, e->seg_off, E, e->act8, e->sact, st));
+    mark(3);
     EB_TRY(grouped(e->act8, e->sact, L.w2, H, I, e->y));
+    mark(-1);
     EB_TRY(eb_moe_combine(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->x, st));
     n += 12 + (plans[pi].n_parts > n_seqs ? 1 : 0);
-    if (c.debug) {
+    if (c.debug & 1) {
       EB_CUDA(cudaMemcpyAsync(e->dbg_route + (size_t)l * c.max_tokens * c.top_k, e->r_idx, (size_t)R * sizeof(int32_t),
                               cudaMemcpyDeviceToDevice, e->stream));
       EB_CUDA(cudaMemcpyAsync(e->dbg_hidden + (size_t)(l + 1) * c.max_tokens * H, e->x, (size_t)T * H * 2,
@@ -378,7 +407,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   EB_TRY(impose(c.n_layers));
   EB_TRY(eb_rmsnorm(e->x, e->g_final, T, H, c.rms_eps, e->h, st));
   EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
+  mark(4);
   EB_TRY(dense(e->h8, e->sh, e->lm, c.vocab, H, e->logits));
+  mark(-1);
   EB_TRY(eb_argmax(e->logits, T, c.vocab, c.vocab, e->d_next, e->d_margin, st));
   n += 3;
   return EB_OK;
@@ -447,6 +478,7 @@ int32_t eb_engine_destroy(eb_engine* e) {
   if (!e) return EB_OK;
   if (e->stream) cudaStreamSynchronize(e->stream);
   for (void* p : e->allocs) cudaFree(p);
+  for (cudaEvent_t ev : e->prof_ev) cudaEventDestroy(ev);
   if (e->h_stage) cudaFreeHost(e->h_stage);
   if (e->h_result) cudaFreeHost(e->h_result);
   if (e->ev0) cudaEventDestroy(e->ev0);
@@ -631,6 +663,12 @@ int32_t eb_engine_step_wait(eb_engine* e, int32_t* h_next, float* h_margin) {
   e->in_flight = false;
   EB_CUDA(cudaEventSynchronize(e->ev1));
   EB_CUDA(cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1));
+  for (float& v : e->prof_ms) v = 0.f;
+  for (size_t i = 0; i + 1 < e->prof_cat.size(); i += 2) {
+    float ms = 0.f;
+    if (e->prof_cat[i] >= 0 && cudaEventElapsedTime(&ms, e->prof_ev[i], e->prof_ev[i + 1]) == cudaSuccess)
+      e->prof_ms[e->prof_cat[i]] += ms;
+  }
   memcpy(h_next, e->h_result, (size_t)e->cur_T * sizeof(int32_t));
   if (h_margin) memcpy(h_margin, e->h_result + e->cur_T, (size_t)e->cur_T * sizeof(float));
   return EB_OK;
@@ -646,6 +684,19 @@ int32_t eb_engine_last_step_stats(const eb_engine* e, float* device_ms, int32_t*
   EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_last_step_stats: null engine");
   if (device_ms) *device_ms = e->last_ms;
   if (kernel_launches) *kernel_launches = e->launches;
+  return EB_OK;
+}
+
+int32_t eb_engine_last_step_breakdown(const eb_engine* e, float* ms5) {
+  EB_REQUIRE(e && ms5, EB_ERR_ARG, "eb_engine_last_step_breakdown: null");
+  EB_REQUIRE(e->c.debug & 2, EB_ERR_STATE, "eb_engine_last_step_breakdown: engine was not created with debug & 2");
+  for (int i = 0; i < 5; ++i) ms5[i] = e->prof_ms[i];
+  return EB_OK;
+}
+
+int32_t eb_engine_stream(eb_engine* e, void** stream) {
+  EB_REQUIRE(e && stream, EB_ERR_ARG, "eb_engine_stream: null");
+  *stream = e->stream;
   return EB_OK;
 }
 

@@ -131,13 +131,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 template <int TN>
 struct Cfg {
   static constexpr int kStageBytes = kTileN * kBlockK + TN * kBlockK;
-  static constexpr int kStages = (TN == 128) ? 6 : 8;
+  // two CTAs share an SM (one streams while the other starts up or drains): <= 113 KB of shared memory and
+  // <= 256 tensor-memory columns each
+  static constexpr int kStages = (TN == 128) ? 3 : (TN == 64) ? 4 : 5;
   static constexpr uint32_t kTmemCols = (2 * TN < 32) ? 32 : 2 * TN;
   static constexpr size_t kSmem = 1024 + (size_t)kStages * kStageBytes + 256 + kMaxKB * sizeof(float);
 };
 
 template <int TN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
   using C = Cfg<TN>;
   constexpr int S = C::kStages;

@@ -17,26 +17,45 @@ constexpr int kMaxTopK = 8;
 
 __device__ __forceinline__ float bf(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
 
-// One warp per token.  x row staged in shared memory; every lane keeps the logits of experts e = lane + 32*j.
-template <int EPL>  // experts per lane = ceil(E / 32)
-__global__ void __launch_bounds__(128)
+// One warp per token, eight tokens per CTA.  Lane l keeps its slice of the token row (x[k], k = l mod 32) in
+// registers; the CTA streams the router matrix through shared memory one expert row at a time (double
+// buffered, 16-byte loads), so every row is fetched once per CTA instead of once per warp and the inner loop
+// reads only shared memory.  Every lane keeps the logits of experts e = lane + 32*j.
+template <int EPL, int HPL>  // experts per lane = ceil(E / 32), hidden elements per lane = ceil(H / 32)
+__global__ void __launch_bounds__(256)
 router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, int top_k, int32_t* idx, float* wts,
                    float* logits_out) {
-  extern __shared__ uint16_t xs[];  // [4 warps][H]
+  extern __shared__ __align__(16) uint16_t wrow[];  // [2][H8 * 8]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= T) return;
-  uint16_t* xr = xs + (size_t)warp * H;
-  for (int k = lane; k < H; k += 32) xr[k] = x[(int64_t)t * H + k];
-  __syncwarp();
+  const int t = blockIdx.x * 8 + warp;
+  const bool on = t < T;
+  const int H8 = (H + 7) >> 3;  // H is a multiple of 8
+  float xr[HPL];
+#pragma unroll
+  for (int j = 0; j < HPL; ++j) {
+    const int k = lane + 32 * j;
+    xr[j] = (on && k < H) ? bf(x[(int64_t)t * H + k]) : 0.f;
+  }
+  auto stage = [&](int e, int buf) {
+    const uint4* src = reinterpret_cast<const uint4*>(wr + (int64_t)e * H);
+    uint4* dst = reinterpret_cast<uint4*>(wrow + (size_t)buf * H8 * 8);
+    for (int c = threadIdx.x; c < H8; c += 256) dst[c] = src[c];
+  };
+  stage(0, 0);
+  __syncthreads();
 
   float lg[EPL];
 #pragma unroll
   for (int j = 0; j < EPL; ++j) lg[j] = -INFINITY;
   for (int e = 0; e < E; ++e) {
-    const uint16_t* w = wr + (int64_t)e * H;
+    if (e + 1 < E) stage(e + 1, (e + 1) & 1);
+    const uint16_t* w = wrow + (size_t)(e & 1) * H8 * 8;
     float acc = 0.f;
-    for (int k = lane; k < H; k += 32) acc = __fmaf_rn(bf(xr[k]), bf(w[k]), acc);
+#pragma unroll
+    for (int j = 0; j < HPL; ++j) {
+      const int k = lane + 32 * j;
+      if (k < H) acc = __fmaf_rn(xr[j], bf(w[k]), acc);
+    }
 #pragma unroll
     for (int o = 16; o; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
     if ((e & 31) == lane) {
@@ -44,8 +63,10 @@ router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, i
       for (int j = 0; j < EPL; ++j)
         if (j == (e >> 5)) lg[j] = acc;
     }
-    if (logits_out && lane == 0) logits_out[(int64_t)t * E + e] = acc;
+    if (logits_out && on && lane == 0) logits_out[(int64_t)t * E + e] = acc;
+    __syncthreads();
   }
+  if (!on) return;
 
   float sel[kMaxTopK];
   for (int j = 0; j < top_k; ++j) {
@@ -178,6 +199,19 @@ __global__ void moe_combine_kernel(const uint16_t* y, const int32_t* perm_row, c
   *reinterpret_cast<uint4*>(x + (int64_t)t * H + c) = make_uint4(xu[0], xu[1], xu[2], xu[3]);
 }
 
+template <int HPL>
+void launch_router(int epl, unsigned grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wr, int T,
+                          int E, int H, int top_k, int32_t* idx, float* wts, float* logits) {
+  if (epl <= 1)
+    router_topk_kernel<1, HPL><<<grid, 256, smem, st>>>(x, wr, T, E, H, top_k, idx, wts, logits);
+  else if (epl <= 2)
+    router_topk_kernel<2, HPL><<<grid, 256, smem, st>>>(x, wr, T, E, H, top_k, idx, wts, logits);
+  else if (epl <= 4)
+    router_topk_kernel<4, HPL><<<grid, 256, smem, st>>>(x, wr, T, E, H, top_k, idx, wts, logits);
+  else
+    router_topk_kernel<8, HPL><<<grid, 256, smem, st>>>(x, wr, T, E, H, top_k, idx, wts, logits);
+}
+
 }  // namespace
 
 extern "C" {
@@ -185,24 +219,27 @@ extern "C" {
 int32_t eb_moe_route(const void* d_x, const void* d_wr, int32_t T, int32_t E, int32_t H, int32_t top_k, int32_t* d_idx,
                      float* d_wts, float* d_logits, void* stream) {
   EB_REQUIRE(d_x && d_wr && d_idx && d_wts, EB_ERR_ARG, "eb_moe_route: null pointer");
-  EB_REQUIRE(T >= 0 && E >= 1 && E <= kMaxExperts && H >= 1 && top_k >= 1 && top_k <= kMaxTopK && top_k <= E,
-             EB_ERR_UNSUPPORTED, "eb_moe_route: E %d (<= %d), top_k %d (<= %d)", E, kMaxExperts, top_k, kMaxTopK);
+  EB_REQUIRE(T >= 0 && E >= 1 && E <= kMaxExperts && top_k >= 1 && top_k <= kMaxTopK && top_k <= E, EB_ERR_UNSUPPORTED,
+             "eb_moe_route: E %d (<= %d), top_k %d (<= %d)", E, kMaxExperts, top_k, kMaxTopK);
+  EB_REQUIRE(H >= 8 && H % 8 == 0 && H <= 4096, EB_ERR_UNSUPPORTED, "eb_moe_route: hidden size %d (multiple of 8, <= 4096)", H);
+  EB_REQUIRE((uintptr_t)d_wr % 16 == 0, EB_ERR_ARG, "eb_moe_route: router matrix must be 16-byte aligned");
   if (T == 0) return EB_OK;
-  const size_t smem = 4 * (size_t)H * sizeof(uint16_t);
-  EB_REQUIRE(smem <= 48 * 1024, EB_ERR_UNSUPPORTED, "eb_moe_route: hidden size %d too large", H);
-  const unsigned grid = (unsigned)((T + 3) / 4);
+  const size_t smem = 2 * (size_t)H * sizeof(uint16_t);
+  const unsigned grid = (unsigned)((T + 7) / 8);
   cudaStream_t st = eb::as_stream(stream);
   const uint16_t* x = (const uint16_t*)d_x;
   const uint16_t* wr = (const uint16_t*)d_wr;
-  const int epl = (E + 31) / 32;
-  if (epl <= 1)
-    router_topk_kernel<1><<<grid, 128, smem, st>>>(x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
-  else if (epl <= 2)
-    router_topk_kernel<2><<<grid, 128, smem, st>>>(x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
-  else if (epl <= 4)
-    router_topk_kernel<4><<<grid, 128, smem, st>>>(x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  const int epl = (E + 31) / 32, hpl = (H + 31) / 32;
+  if (hpl <= 16)
+    launch_router<16>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  else if (hpl <= 32)
+    launch_router<32>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  else if (hpl <= 64)
+    launch_router<64>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  else if (hpl <= 96)
+    launch_router<96>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
   else
-    router_topk_kernel<8><<<grid, 128, smem, st>>>(x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+    launch_router<128>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

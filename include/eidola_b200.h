@@ -279,7 +279,8 @@ typedef struct eb_config {
   int32_t max_q_len;    /* new tokens per sequence per step: 1 = decode, k+1 = verify k drafts */
   float rope_theta, rms_eps, init_std;
   uint64_t seed;        /* weights are a pure function of (shape, seed) */
-  int32_t debug;        /* 1: keep per-layer routing indices and the last logits readable */
+  int32_t debug;        /* bit 0: keep per-layer routing indices / hidden states readable and allow teacher forcing;
+                           bit 1: time attention, GEMM and LM-head calls of each step with CUDA events */
 } eb_config;
 
 typedef struct eb_engine eb_engine;
@@ -310,7 +311,12 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
 int32_t eb_engine_step_wait(eb_engine* e, int32_t* h_next, float* h_margin);
 /* Milliseconds the last step spent on the device (CUDA events around its kernels) and kernels it launched. */
 int32_t eb_engine_last_step_stats(const eb_engine* e, float* device_ms, int32_t* kernel_launches);
-/* debug = 1 only: copy out the last step's logits [T][vocab] bf16 and layer routing indices [T][top_k]. */
+/* debug bit 1: device milliseconds of the last step by category: [0] attention on full layers, [1] attention on
+ * windowed layers, [2] QKV and O projections, [3] expert GEMMs, [4] LM head. */
+int32_t eb_engine_last_step_breakdown(const eb_engine* e, float* ms5);
+/* The stream the engine launches on (borrowed), so a caller can record its own events around steps. */
+int32_t eb_engine_stream(eb_engine* e, void** stream);
+/* debug bit 0 only: copy out the last step's logits [T][vocab] bf16 and layer routing indices [T][top_k]. */
 int32_t eb_engine_read_logits(eb_engine* e, void* h_logits, int64_t bytes);
 int32_t eb_engine_read_routing(eb_engine* e, int32_t layer, int32_t* h_idx, int64_t bytes);
 /* Copy out the residual stream [T][hidden] bf16 as it stood after `layer` (debug = 1; layer = -1: embeddings). */
