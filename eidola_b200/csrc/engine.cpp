@@ -289,7 +289,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     cudaEventRecord(e->prof_ev[prof_used++], e->stream);
     e->prof_cat.push_back(cat);
   };
-  auto dense = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout) -> int32_t {
+  // Dense GEMM; when `splits` is given the split-K partials are left in gemm_ws for a fused consumer.
+  auto dense = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout,
+                   int32_t* splits) -> int32_t {
     eb_gemm_args g = {};
     g.d_x8 = x8;
     g.d_sx = sx;
@@ -302,9 +304,11 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     g.K = K;
     g.n_groups = 1;
     g.d_work = (T <= 512 && N <= std::max(e->nqkv, H)) ? e->gemm_ws : nullptr;
-    n += 1;  // (+1 when split K runs its reduction; counted below by the caller of stats as a lower bound)
-    return eb_gemm_fp8_block(&g, st);
+    n += 1;
+    return splits ? eb_gemm_fp8_block_partial(&g, splits, st) : eb_gemm_fp8_block(&g, st);
   };
+  const int avg2 = std::min(128, 2 * ((R + E - 1) / E));
+  const int group_tn = avg2 <= 16 ? 16 : avg2 <= 32 ? 32 : avg2 <= 64 ? 64 : 128;
   auto grouped = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout) -> int32_t {
     eb_gemm_args g = {};
     g.d_x8 = x8;
@@ -319,9 +323,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     g.n_groups = E;
     g.d_seg_off = e->seg_off;
     g.d_work = e->group_ws;
-    const int avg2 = std::min(128, 2 * ((R + E - 1) / E));
-    g.tile_tokens = avg2 <= 16 ? 16 : avg2 <= 32 ? 32 : avg2 <= 64 ? 64 : 128;
-    n += 2;
+    g.tile_tokens = group_tn;
+    g.tiles_ready = 1;
+    n += 1;
     return eb_gemm_fp8_grouped(&g, st);
   };
 
@@ -336,19 +340,24 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
                               cudaMemcpyDeviceToDevice, e->stream));
     return EB_OK;
   };
+  // h = rmsnorm(x) of the first layer; later layers get it from the fused combine of the layer before
+  EB_TRY(eb_rmsnorm(e->x, e->layers[0].g_attn, T, H, c.rms_eps, e->h, st));
+  n += 1;
   for (int l = 0; l < c.n_layers; ++l) {
     const Layer& L = e->layers[(size_t)l];
     const int pi = (l % 2 == 0 && c.window > 0) ? 1 : 0;  // plan 1 = windowed
-    EB_TRY(impose(l));
-    EB_TRY(eb_rmsnorm(e->x, L.g_attn, T, H, c.rms_eps, e->h, st));
+    if ((c.debug & 1) && e->force_rows[(size_t)l] == T) {
+      EB_TRY(impose(l));
+      EB_TRY(eb_rmsnorm(e->x, L.g_attn, T, H, c.rms_eps, e->h, st));
+    }
+    int32_t splits = 1;
     EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
     mark(2);
-    EB_TRY(dense(e->h8, e->sh, L.wqkv, e->nqkv, H, e->qkv));
+    EB_TRY(dense(e->h8, e->sh, L.wqkv, e->nqkv, H, e->qkv, &splits));
     mark(-1);
-    EB_TRY(eb_rope(e->qkv, e->nqkv, c.n_q_heads + c.n_kv_heads, c.head_dim, d_positions, T, e->rope_cos, e->rope_sin, max_pos, st));
-    EB_TRY(eb_kv_append(L.cache, c.num_pages, c.n_kv_heads, c.head_dim, c.page_size, e->qkv + e->hqd,
-                        e->qkv + e->hqd + c.n_kv_heads * c.head_dim, e->nqkv, e->d_bt, c.max_pages_per_seq, d_tok_slot,
-                        d_positions, T, st));
+    EB_TRY(eb_qkv_rope_append((const float*)e->gemm_ws, splits, e->qkv, T, c.n_q_heads, c.n_kv_heads, c.head_dim,
+                              d_positions, e->rope_cos, e->rope_sin, max_pos, L.cache, c.num_pages, c.page_size, e->d_bt,
+                              c.max_pages_per_seq, d_tok_slot, st));
     eb_attn_args a = {};
     a.d_q = e->qkv;
     a.q_stride = e->nqkv;
@@ -381,12 +390,11 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     mark(-1);
     EB_TRY(eb_quant_act_block128(e->attn, e->hqd, T, e->hqd, nullptr, 1, e->a8, e->sa, st));
     mark(2);
-    EB_TRY(dense(e->a8, e->sa, L.wo, H, e->hqd, e->o));
+    EB_TRY(dense(e->a8, e->sa, L.wo, H, e->hqd, e->o, &splits));
     mark(-1);
-    EB_TRY(eb_residual_add(e->x, e->o, (int64_t)T * H, st));
-    EB_TRY(eb_rmsnorm(e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
+    EB_TRY(eb_oproj_residual_rmsnorm((const float*)e->gemm_ws, splits, e->o, e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
     EB_TRY(eb_moe_route(e->h, L.wr, T, E, H, c.top_k, e->r_idx, e->r_wts, nullptr, st));
-    EB_TRY(eb_moe_permute(e->r_idx, T, c.top_k, E, e->seg_off, e->perm_row, e->row_token, st));
+    EB_TRY(eb_moe_permute_tiles(e->r_idx, T, c.top_k, E, e->seg_off, e->perm_row, e->row_token, group_tn, e->group_ws, st));
     EB_TRY(eb_quant_gather_block128(e->h, H, T, e->row_token, R, H, e->seg_off, E, e->xp8, e->sxp, st));
     mark(3);
     EB_TRY(grouped(e->xp8, e->sxp, L.w1, 2 * I, H, e->gu));
@@ -395,8 +403,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     mark(3);
     EB_TRY(grouped(e->act8, e->sact, L.w2, H, I, e->y));
     mark(-1);
-    EB_TRY(eb_moe_combine(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->x, st));
-    n += 12 + (plans[pi].n_parts > n_seqs ? 1 : 0);
+    const float* g_next = (l + 1 < c.n_layers) ? e->layers[(size_t)l + 1].g_attn : e->g_final;
+    EB_TRY(eb_moe_combine_rmsnorm(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->x, g_next, c.rms_eps, e->h, st));
+    n += 9 + (plans[pi].n_parts > n_seqs ? 1 : 0);
     if (c.debug & 1) {
       EB_CUDA(cudaMemcpyAsync(e->dbg_route + (size_t)l * c.max_tokens * c.top_k, e->r_idx, (size_t)R * sizeof(int32_t),
                               cudaMemcpyDeviceToDevice, e->stream));
@@ -404,11 +413,13 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
                               cudaMemcpyDeviceToDevice, e->stream));
     }
   }
-  EB_TRY(impose(c.n_layers));
-  EB_TRY(eb_rmsnorm(e->x, e->g_final, T, H, c.rms_eps, e->h, st));
+  if ((c.debug & 1) && e->force_rows[(size_t)c.n_layers] == T) {
+    EB_TRY(impose(c.n_layers));
+    EB_TRY(eb_rmsnorm(e->x, e->g_final, T, H, c.rms_eps, e->h, st));
+  }
   EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
   mark(4);
-  EB_TRY(dense(e->h8, e->sh, e->lm, c.vocab, H, e->logits));
+  EB_TRY(dense(e->h8, e->sh, e->lm, c.vocab, H, e->logits, nullptr));
   mark(-1);
   EB_TRY(eb_argmax(e->logits, T, c.vocab, c.vocab, e->d_next, e->d_margin, st));
   n += 3;

@@ -147,18 +147,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   // ---- which tile
   int g = 0, row0, row_end, xblk;
   if (p.n_groups > 1 || p.seg_off) {
-    const int t = blockIdx.y;
+    const int t = blockIdx.x;
     if (t >= *p.n_tiles) return;
     g = p.tile_group[t];
     row0 = p.tile_row0[t];
     row_end = p.seg_off[g + 1];
     xblk = p.blk_off[g] + (row0 - p.seg_off[g]) / 128;
   } else {
-    row0 = blockIdx.y * TN;
+    row0 = blockIdx.x * TN;
     row_end = p.rows;
     xblk = row0 / 128;
   }
-  const int nb = blockIdx.x, n0 = nb * kTileN;
+  const int nb = blockIdx.y, n0 = nb * kTileN;
   const int KB = (p.K + kBlockK - 1) / kBlockK;
   const int NB = (p.N + kTileN - 1) / kTileN;
   const int split = blockIdx.z;
@@ -465,7 +465,7 @@ int pick_tn(int64_t rows_per_group) {
   return 128;
 }
 
-int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st) {
+int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* splits_used = nullptr) {
   EB_REQUIRE(a->d_x8 && a->d_sx && a->d_w8 && a->d_sw && a->d_y, EB_ERR_ARG, "gemm: null pointer");
   EB_REQUIRE(a->rows >= 0 && a->N >= 1 && a->K >= 16 && a->n_groups >= 1, EB_ERR_ARG, "gemm: bad size");
   EB_REQUIRE(a->K % 16 == 0, EB_ERR_UNSUPPORTED, "gemm: K %d must be a multiple of 16", a->K);
@@ -502,9 +502,11 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st) {
     int32_t* n_tiles = w + (a->n_groups + 1);
     int32_t* tile_group = n_tiles + 1;
     int32_t* tile_row0 = tile_group + token_tiles;
-    gemm_tiles_kernel<<<1, 256, 0, st>>>(a->d_seg_off, a->n_groups, tn, token_tiles, blk_off, tile_group, tile_row0,
-                                         n_tiles, status);
-    EB_LAUNCH_CHECK();
+    if (!a->tiles_ready) {
+      gemm_tiles_kernel<<<1, 256, 0, st>>>(a->d_seg_off, a->n_groups, tn, token_tiles, blk_off, tile_group, tile_row0,
+                                           n_tiles, status);
+      EB_LAUNCH_CHECK();
+    }
     p.seg_off = a->d_seg_off;
     p.blk_off = blk_off;
     p.tile_group = tile_group;
@@ -529,7 +531,7 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st) {
     p.splits = splits;
     p.y_part = (float*)a->d_work;
   }
-  EB_REQUIRE(token_tiles <= 65535, EB_ERR_UNSUPPORTED, "gemm: %d token tiles exceed the grid", token_tiles);
+  EB_REQUIRE(nb <= 65535, EB_ERR_UNSUPPORTED, "gemm: %d weight tiles exceed the grid", nb);
 
   CUtensorMap tw, tx;
   int32_t rc = eb::make_tmap_2d_sw128(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, (uint64_t)a->n_groups * a->N,
@@ -539,7 +541,7 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st) {
                               (uint64_t)a->K, (uint32_t)tn);
   if (rc != EB_OK) return rc;
 
-  const dim3 grid((unsigned)nb, (unsigned)token_tiles, (unsigned)p.splits);
+  const dim3 grid((unsigned)token_tiles, (unsigned)nb, (unsigned)p.splits);  // token tile fastest: CTAs sharing a weight tile run together
   switch (tn) {
     case 16: rc = launch_gemm<16>(tw, tx, p, grid, st); break;
     case 32: rc = launch_gemm<32>(tw, tx, p, grid, st); break;
@@ -547,7 +549,8 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st) {
     default: rc = launch_gemm<128>(tw, tx, p, grid, st); break;
   }
   if (rc != EB_OK) return rc;
-  if (p.splits > 1) {
+  if (splits_used) *splits_used = p.splits;
+  if (p.splits > 1 && !splits_used) {
     const int64_t total = (int64_t)a->rows * a->N;
     gemm_splitk_reduce_kernel<<<(unsigned)eb::cdiv(total, 256), 256, 0, st>>>(p.y_part, p.y, p.ldy, a->rows, a->N,
                                                                               p.splits);
@@ -575,6 +578,30 @@ int32_t eb_gemm_fp8_block(const eb_gemm_args* a, void* stream) {
   EB_REQUIRE(a, EB_ERR_ARG, "eb_gemm_fp8_block: null args");
   EB_REQUIRE(a->n_groups == 1, EB_ERR_ARG, "eb_gemm_fp8_block: n_groups must be 1 (use eb_gemm_fp8_grouped)");
   return run_gemm(a, false, eb::as_stream(stream));
+}
+
+int32_t eb_gemm_fp8_block_partial(const eb_gemm_args* a, int32_t* splits_used, void* stream) {
+  EB_REQUIRE(a && splits_used, EB_ERR_ARG, "eb_gemm_fp8_block_partial: null args");
+  EB_REQUIRE(a->n_groups == 1, EB_ERR_ARG, "eb_gemm_fp8_block_partial: n_groups must be 1");
+  return run_gemm(a, false, eb::as_stream(stream), splits_used);
+}
+
+int32_t eb_gemm_group_tiles(const int32_t* d_seg_off, int32_t n_groups, int32_t rows, int32_t tile_tokens, void* d_work,
+                            void* stream) {
+  EB_REQUIRE(d_seg_off && d_work, EB_ERR_ARG, "eb_gemm_group_tiles: null pointer");
+  EB_REQUIRE(n_groups >= 1 && n_groups <= 1024 && rows >= 0, EB_ERR_ARG, "eb_gemm_group_tiles: bad size");
+  EB_REQUIRE(tile_tokens == 16 || tile_tokens == 32 || tile_tokens == 64 || tile_tokens == 128, EB_ERR_ARG,
+             "eb_gemm_group_tiles: tile_tokens %d not in {16,32,64,128}", tile_tokens);
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_gemm_group_tiles: no device");
+  const int token_tiles = rows / tile_tokens + n_groups;
+  int32_t* w = (int32_t*)d_work;
+  int32_t* n_tiles = w + (n_groups + 1);
+  int32_t* tile_group = n_tiles + 1;
+  gemm_tiles_kernel<<<1, 256, 0, eb::as_stream(stream)>>>(d_seg_off, n_groups, tile_tokens, token_tiles, w, tile_group,
+                                                          tile_group + token_tiles, n_tiles, status);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
 }
 
 int32_t eb_gemm_fp8_grouped(const eb_gemm_args* a, void* stream) {

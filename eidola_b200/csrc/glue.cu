@@ -109,15 +109,29 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const uint16_t* logits, in
   const uint16_t* r = logits + (int64_t)blockIdx.x * ld;
   float b1 = -INFINITY, b2 = -INFINITY;
   int64_t i1 = V;
-  for (int64_t v = threadIdx.x; v < V; v += blockDim.x) {
-    const float x = __uint_as_float((uint32_t)r[v] << 16);
-    if (x > b1) {  // ascending v within a thread: strict > keeps the lower id
+  auto take = [&](float x, int64_t v) {  // ascending v within a thread: strict > keeps the lower id
+    if (x > b1) {
       b2 = b1;
       b1 = x;
       i1 = v;
     } else if (x > b2) {
       b2 = x;
     }
+  };
+  if ((((uintptr_t)r) & 15) == 0) {
+    const int64_t V8 = V >> 3;
+    for (int64_t c = threadIdx.x; c < V8; c += blockDim.x) {
+      const uint4 q = *reinterpret_cast<const uint4*>(r + c * 8);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        take(bf_lo(w[k]), c * 8 + 2 * k);
+        take(bf_hi(w[k]), c * 8 + 2 * k + 1);
+      }
+    }
+    for (int64_t v = V8 * 8 + threadIdx.x; v < V; v += blockDim.x) take(__uint_as_float((uint32_t)r[v] << 16), v);
+  } else {
+    for (int64_t v = threadIdx.x; v < V; v += blockDim.x) take(__uint_as_float((uint32_t)r[v] << 16), v);
   }
   __shared__ float s1[1024], s2[1024];
   __shared__ int64_t si[1024];
@@ -216,6 +230,243 @@ int32_t eb_argmax(const void* d_logits, int32_t T, int64_t V, int64_t ld, int32_
   EB_REQUIRE(T >= 0 && V >= 1 && ld >= V, EB_ERR_ARG, "eb_argmax: bad size");
   if (T == 0) return EB_OK;
   argmax_kernel<<<T, 1024, 0, eb::as_stream(stream)>>>((const uint16_t*)d_logits, V, ld, d_tok, d_margin);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Fused consumers of the dense GEMMs and of the expert combine (fewer, fatter launches per layer).
+
+namespace {
+
+__device__ __forceinline__ float sum_partials(const float* part, int splits, int64_t plane, int64_t idx) {
+  float a = 0.f;
+  for (int s = 0; s < splits; ++s) a += part[(int64_t)s * plane + idx];
+  return a;
+}
+__device__ __forceinline__ float round_bf16(float v) { return __uint_as_float(pack_bf16(v, 0.f) << 16); }
+
+// One thread per (token, head, 8 consecutive i < D/2): elements [i, i+8) and [i + D/2, i + D/2 + 8) of a q, k or v
+// head, moved with 16-byte accesses.
+__global__ void qkv_rope_append_kernel(const float* part, int splits, uint16_t* qkv, int T, int n_q, int n_kv, int head_dim,
+                                       const int32_t* positions, const float* cos_t, const float* sin_t, int max_pos,
+                                       uint16_t* cache, int num_pages, int page_size, const int32_t* block_tables,
+                                       int bt_stride, const int32_t* tok_slot, int32_t* status) {
+  const int half = head_dim >> 1;
+  const int groups = half >> 3;  // threads per head
+  const int n_heads = n_q + 2 * n_kv;
+  const int N = n_heads * head_dim;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)T * n_heads * groups) return;
+  const int i = (int)(idx % groups) * 8;
+  const int h = (int)((idx / groups) % n_heads);
+  const int t = (int)(idx / ((int64_t)groups * n_heads));
+  const int pos = positions[t];
+  if (pos < 0 || pos >= max_pos) {
+    atomicOr(status, EB_DEV_BAD_INDEX);
+    return;
+  }
+  const int64_t e0 = (int64_t)t * N + (int64_t)h * head_dim + i;
+  float a[8], b[8];
+  if (splits > 1) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = b[k] = 0.f;
+    const int64_t plane = (int64_t)T * N;
+    for (int s = 0; s < splits; ++s) {
+      const float4* pa = reinterpret_cast<const float4*>(part + s * plane + e0);
+      const float4* pb = reinterpret_cast<const float4*>(part + s * plane + e0 + half);
+      const float4 a0 = pa[0], a1 = pa[1], b0 = pb[0], b1 = pb[1];
+      a[0] += a0.x; a[1] += a0.y; a[2] += a0.z; a[3] += a0.w; a[4] += a1.x; a[5] += a1.y; a[6] += a1.z; a[7] += a1.w;
+      b[0] += b0.x; b[1] += b0.y; b[2] += b0.z; b[3] += b0.w; b[4] += b1.x; b[5] += b1.y; b[6] += b1.z; b[7] += b1.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      a[k] = round_bf16(a[k]);
+      b[k] = round_bf16(b[k]);
+    }
+  } else {
+    const uint4 va = *reinterpret_cast<const uint4*>(qkv + e0), vb = *reinterpret_cast<const uint4*>(qkv + e0 + half);
+    const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      a[2 * k] = bf_lo(wa[k]);
+      a[2 * k + 1] = bf_hi(wa[k]);
+      b[2 * k] = bf_lo(wb[k]);
+      b[2 * k + 1] = bf_hi(wb[k]);
+    }
+  }
+  if (h < n_q + n_kv) {  // q and k heads rotate
+    const float4* pc = reinterpret_cast<const float4*>(cos_t + (int64_t)pos * half + i);
+    const float4* ps = reinterpret_cast<const float4*>(sin_t + (int64_t)pos * half + i);
+    const float4 c0 = pc[0], c1 = pc[1], s0 = ps[0], s1 = ps[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float ra = __fsub_rn(__fmul_rn(a[k], c[k]), __fmul_rn(b[k], sn[k]));
+      const float rb = __fadd_rn(__fmul_rn(b[k], c[k]), __fmul_rn(a[k], sn[k]));
+      a[k] = ra;
+      b[k] = rb;
+    }
+  }
+  const uint4 oa = make_uint4(pack_bf16(a[0], a[1]), pack_bf16(a[2], a[3]), pack_bf16(a[4], a[5]), pack_bf16(a[6], a[7]));
+  const uint4 ob = make_uint4(pack_bf16(b[0], b[1]), pack_bf16(b[2], b[3]), pack_bf16(b[4], b[5]), pack_bf16(b[6], b[7]));
+  if (h < n_q) {
+    *reinterpret_cast<uint4*>(qkv + e0) = oa;
+    *reinterpret_cast<uint4*>(qkv + e0 + half) = ob;
+    return;
+  }
+  const int kv = (h >= n_q + n_kv) ? 1 : 0;
+  const int hk = h - n_q - kv * n_kv;
+  const int32_t page = block_tables[(int64_t)tok_slot[t] * bt_stride + pos / page_size];
+  if (page < 0 || page >= num_pages) {
+    atomicOr(status, EB_DEV_BAD_INDEX);
+    return;
+  }
+  uint16_t* dst = cache + ((((int64_t)page * 2 + kv) * n_kv + hk) * page_size + pos % page_size) * head_dim;
+  *reinterpret_cast<uint4*>(dst + i) = oa;
+  *reinterpret_cast<uint4*>(dst + i + half) = ob;
+}
+
+// One CTA per token row; a thread owns chunks of 8 consecutive columns (16-byte accesses), at most two (H <= 4096):
+//   MODE 0: v = bf16(sum of split-K partials) or the bf16 GEMM output    (O projection)
+//   MODE 1: v = bf16(sum_j w_j * y[perm_row_j])                          (expert combine)
+// then x = bf16(x + v), h = bf16(x * rsqrt(mean(x^2) + eps) * g).
+template <int MODE>
+__global__ void __launch_bounds__(256)
+row_residual_rmsnorm_kernel(const float* part, int splits, const uint16_t* o_bf16, const uint16_t* y, const int32_t* perm_row,
+                            const float* wts, int top_k, int64_t n_rows, uint16_t* x, const float* g, int T, int H, float eps,
+                            uint16_t* hout) {
+  __shared__ float red[8];
+  const int t = blockIdx.x;
+  const int H8 = H >> 3;
+  float xv[2][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int ch = threadIdx.x + 256 * q;
+    if (ch >= H8) continue;
+    const int64_t e = (int64_t)t * H + ch * 8;
+    float v[8];
+    if (MODE == 0) {
+      if (splits > 1) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = 0.f;
+        const int64_t plane = (int64_t)T * H;
+        for (int s = 0; s < splits; ++s) {
+          const float4* pp = reinterpret_cast<const float4*>(part + s * plane + e);
+          const float4 p0 = pp[0], p1 = pp[1];
+          v[0] += p0.x; v[1] += p0.y; v[2] += p0.z; v[3] += p0.w; v[4] += p1.x; v[5] += p1.y; v[6] += p1.z; v[7] += p1.w;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = round_bf16(v[k]);
+      } else {
+        const uint4 ov = *reinterpret_cast<const uint4*>(o_bf16 + e);
+        const uint32_t w[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          v[2 * k] = bf_lo(w[k]);
+          v[2 * k + 1] = bf_hi(w[k]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = 0.f;
+      for (int j = 0; j < top_k; ++j) {
+        const int r = perm_row[(int64_t)t * top_k + j];
+        if (r < 0 || r >= n_rows) continue;
+        const float wj = wts[(int64_t)t * top_k + j];
+        const uint4 yv = *reinterpret_cast<const uint4*>(y + (int64_t)r * H + ch * 8);
+        const uint32_t w[4] = {yv.x, yv.y, yv.z, yv.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          v[2 * k] = __fmaf_rn(wj, bf_lo(w[k]), v[2 * k]);
+          v[2 * k + 1] = __fmaf_rn(wj, bf_hi(w[k]), v[2 * k + 1]);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = round_bf16(v[k]);
+    }
+    const uint4 xin = *reinterpret_cast<const uint4*>(x + e);
+    const uint32_t xw[4] = {xin.x, xin.y, xin.z, xin.w};
+    uint32_t xo[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      xo[k] = pack_bf16(__fadd_rn(bf_lo(xw[k]), v[2 * k]), __fadd_rn(bf_hi(xw[k]), v[2 * k + 1]));
+      xv[q][2 * k] = bf_lo(xo[k]);
+      xv[q][2 * k + 1] = bf_hi(xo[k]);
+      ss += xv[q][2 * k] * xv[q][2 * k] + xv[q][2 * k + 1] * xv[q][2 * k + 1];
+    }
+    *reinterpret_cast<uint4*>(x + e) = make_uint4(xo[0], xo[1], xo[2], xo[3]);
+  }
+  ss = block_sum(ss, red);
+  const float r = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int ch = threadIdx.x + 256 * q;
+    if (ch >= H8) continue;
+    const float4 g0 = *reinterpret_cast<const float4*>(g + ch * 8), g1 = *reinterpret_cast<const float4*>(g + ch * 8 + 4);
+    uint4 o;
+    o.x = pack_bf16(xv[q][0] * r * g0.x, xv[q][1] * r * g0.y);
+    o.y = pack_bf16(xv[q][2] * r * g0.z, xv[q][3] * r * g0.w);
+    o.z = pack_bf16(xv[q][4] * r * g1.x, xv[q][5] * r * g1.y);
+    o.w = pack_bf16(xv[q][6] * r * g1.z, xv[q][7] * r * g1.w);
+    *reinterpret_cast<uint4*>(hout + (int64_t)t * H + ch * 8) = o;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t eb_qkv_rope_append(const float* d_part, int32_t splits, void* d_qkv, int32_t T, int32_t n_q, int32_t n_kv,
+                           int32_t head_dim, const int32_t* d_positions, const float* d_cos, const float* d_sin,
+                           int32_t max_pos, void* d_cache, int32_t num_pages, int32_t page_size,
+                           const int32_t* d_block_tables, int32_t bt_stride, const int32_t* d_tok_slot, void* stream) {
+  EB_REQUIRE(d_qkv && d_positions && d_cos && d_sin && d_cache && d_block_tables && d_tok_slot, EB_ERR_ARG,
+             "eb_qkv_rope_append: null pointer");
+  EB_REQUIRE(splits >= 1 && (splits == 1 || d_part), EB_ERR_ARG, "eb_qkv_rope_append: splits %d without partials", splits);
+  EB_REQUIRE(T >= 0 && n_q >= 1 && n_kv >= 1 && head_dim >= 16 && head_dim % 16 == 0 && max_pos >= 1 && num_pages >= 1 &&
+                 page_size >= 1 && bt_stride >= 1,
+             EB_ERR_ARG, "eb_qkv_rope_append: bad size (head_dim must be a multiple of 16)");
+  EB_REQUIRE(((uintptr_t)d_qkv % 16 == 0) && ((uintptr_t)d_cache % 16 == 0) && ((uintptr_t)d_cos % 16 == 0) &&
+                 ((uintptr_t)d_sin % 16 == 0) && ((uintptr_t)d_part % 16 == 0),
+             EB_ERR_ARG, "eb_qkv_rope_append: 16-byte alignment");
+  if (T == 0) return EB_OK;
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_qkv_rope_append: no device");
+  const int64_t n = (int64_t)T * (n_q + 2 * n_kv) * (head_dim / 16);
+  qkv_rope_append_kernel<<<(unsigned)eb::cdiv(n, 256), 256, 0, eb::as_stream(stream)>>>(
+      d_part, splits, (uint16_t*)d_qkv, T, n_q, n_kv, head_dim, d_positions, d_cos, d_sin, max_pos, (uint16_t*)d_cache,
+      num_pages, page_size, d_block_tables, bt_stride, d_tok_slot, status);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_oproj_residual_rmsnorm(const float* d_part, int32_t splits, const void* d_o_bf16, void* d_x, const float* d_g,
+                                  int32_t T, int32_t H, float eps, void* d_h, void* stream) {
+  EB_REQUIRE(d_x && d_g && d_h, EB_ERR_ARG, "eb_oproj_residual_rmsnorm: null pointer");
+  EB_REQUIRE(splits >= 1 && ((splits > 1 && d_part) || (splits == 1 && d_o_bf16)), EB_ERR_ARG,
+             "eb_oproj_residual_rmsnorm: splits %d without its input", splits);
+  EB_REQUIRE(T >= 0 && H >= 8 && H % 8 == 0 && H <= 4096, EB_ERR_UNSUPPORTED, "eb_oproj_residual_rmsnorm: H %d (multiple of 8, <= 4096)", H);
+  if (T == 0) return EB_OK;
+  row_residual_rmsnorm_kernel<0><<<T, 256, 0, eb::as_stream(stream)>>>(d_part, splits, (const uint16_t*)d_o_bf16, nullptr,
+                                                                       nullptr, nullptr, 0, 0, (uint16_t*)d_x, d_g, T, H, eps,
+                                                                       (uint16_t*)d_h);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_moe_combine_rmsnorm(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
+                               int32_t H, void* d_x, const float* d_g, float eps, void* d_h, void* stream) {
+  EB_REQUIRE(d_y && d_perm_row && d_wts && d_x && d_g && d_h, EB_ERR_ARG, "eb_moe_combine_rmsnorm: null pointer");
+  EB_REQUIRE(T >= 0 && top_k >= 1 && H >= 8 && H % 8 == 0 && H <= 4096, EB_ERR_UNSUPPORTED, "eb_moe_combine_rmsnorm: H %d (multiple of 8, <= 4096)", H);
+  if (T == 0) return EB_OK;
+  row_residual_rmsnorm_kernel<1><<<T, 256, 0, eb::as_stream(stream)>>>(nullptr, 1, nullptr, (const uint16_t*)d_y, d_perm_row,
+                                                                       d_wts, top_k, (int64_t)T * top_k, (uint16_t*)d_x, d_g, T,
+                                                                       H, eps, (uint16_t*)d_h);
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

@@ -18,52 +18,77 @@ constexpr int kMaxTopK = 8;
 __device__ __forceinline__ float bf(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
 
 // One warp per token, eight tokens per CTA.  Lane l keeps its slice of the token row (x[k], k = l mod 32) in
-// registers; the CTA streams the router matrix through shared memory one expert row at a time (double
-// buffered, 16-byte loads), so every row is fetched once per CTA instead of once per warp and the inner loop
-// reads only shared memory.  Every lane keeps the logits of experts e = lane + 32*j.
+// registers; the CTA streams the router matrix through shared memory eight expert rows at a time (double
+// buffered: the next chunk's 16-byte loads are in flight while the current chunk is reduced), so every row is
+// fetched once per CTA and the inner loop reads only shared memory.  Lane l keeps the logits of experts
+// e = l + 32*j.
+constexpr int kRouterChunk = 8;
+
 template <int EPL, int HPL>  // experts per lane = ceil(E / 32), hidden elements per lane = ceil(H / 32)
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 1)
 router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, int top_k, int32_t* idx, float* wts,
                    float* logits_out) {
-  extern __shared__ __align__(16) uint16_t wrow[];  // [2][H8 * 8]
+  extern __shared__ __align__(16) uint16_t wrow[];  // [2][kRouterChunk][H]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 8 + warp;
   const bool on = t < T;
-  const int H8 = (H + 7) >> 3;  // H is a multiple of 8
+  const int H8 = H >> 3;  // H is a multiple of 8
   float xr[HPL];
 #pragma unroll
   for (int j = 0; j < HPL; ++j) {
     const int k = lane + 32 * j;
     xr[j] = (on && k < H) ? bf(x[(int64_t)t * H + k]) : 0.f;
   }
-  auto stage = [&](int e, int buf) {
-    const uint4* src = reinterpret_cast<const uint4*>(wr + (int64_t)e * H);
-    uint4* dst = reinterpret_cast<uint4*>(wrow + (size_t)buf * H8 * 8);
-    for (int c = threadIdx.x; c < H8; c += 256) dst[c] = src[c];
+  constexpr int kPerThread = (kRouterChunk * (HPL * 32 / 8) + 255) / 256;  // 16-byte loads per thread per chunk
+  uint4 pre[kPerThread];
+  auto fetch = [&](int e0) {  // rows [e0, e0 + chunk) are contiguous in the router matrix
+    const int n16 = min(kRouterChunk, E - e0) * H8;
+    const uint4* src = reinterpret_cast<const uint4*>(wr + (int64_t)e0 * H);
+#pragma unroll
+    for (int q = 0; q < kPerThread; ++q) {
+      const int c = threadIdx.x + 256 * q;
+      if (c < n16) pre[q] = src[c];
+    }
   };
-  stage(0, 0);
+  auto commit = [&](int e0, int buf) {
+    const int n16 = min(kRouterChunk, E - e0) * H8;
+    uint4* dst = reinterpret_cast<uint4*>(wrow + (size_t)buf * kRouterChunk * H);
+#pragma unroll
+    for (int q = 0; q < kPerThread; ++q) {
+      const int c = threadIdx.x + 256 * q;
+      if (c < n16) dst[c] = pre[q];
+    }
+  };
+  fetch(0);
+  commit(0, 0);
   __syncthreads();
 
   float lg[EPL];
 #pragma unroll
   for (int j = 0; j < EPL; ++j) lg[j] = -INFINITY;
-  for (int e = 0; e < E; ++e) {
-    if (e + 1 < E) stage(e + 1, (e + 1) & 1);
-    const uint16_t* w = wrow + (size_t)(e & 1) * H8 * 8;
-    float acc = 0.f;
+  for (int e0 = 0, buf = 0; e0 < E; e0 += kRouterChunk, buf ^= 1) {
+    const bool more = e0 + kRouterChunk < E;
+    if (more) fetch(e0 + kRouterChunk);
+    const int ne = min(kRouterChunk, E - e0);
+    for (int r = 0; r < ne; ++r) {
+      const int e = e0 + r;
+      const uint16_t* w = wrow + ((size_t)buf * kRouterChunk + r) * H;
+      float acc = 0.f;
 #pragma unroll
-    for (int j = 0; j < HPL; ++j) {
-      const int k = lane + 32 * j;
-      if (k < H) acc = __fmaf_rn(xr[j], bf(w[k]), acc);
+      for (int j = 0; j < HPL; ++j) {
+        const int k = lane + 32 * j;
+        if (k < H) acc = __fmaf_rn(xr[j], bf(w[k]), acc);
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
+      if ((e & 31) == lane) {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j)
+          if (j == (e >> 5)) lg[j] = acc;
+      }
+      if (logits_out && on && lane == 0) logits_out[(int64_t)t * E + e] = acc;
     }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
-    if ((e & 31) == lane) {
-#pragma unroll
-      for (int j = 0; j < EPL; ++j)
-        if (j == (e >> 5)) lg[j] = acc;
-    }
-    if (logits_out && on && lane == 0) logits_out[(int64_t)t * E + e] = acc;
+    if (more) commit(e0 + kRouterChunk, buf ^ 1);  // that buffer was last read one iteration ago, before a barrier
     __syncthreads();
   }
   if (!on) return;
@@ -114,7 +139,7 @@ router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, i
 //   row_token[r]  : token whose activations permuted row r carries
 __global__ void __launch_bounds__(1024)
 moe_permute_kernel(const int32_t* idx, int n_slots, int top_k, int E, int32_t* seg_off, int32_t* perm_row,
-                   int32_t* row_token, int32_t* status) {
+                   int32_t* row_token, int tn, int max_tiles, int32_t* tile_ws, int32_t* status) {
   __shared__ int32_t base[kMaxExperts + 1];   // running start of each expert's unplaced slots
   __shared__ int32_t wcnt[32][kMaxExperts];   // per-warp counts of the current tile
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -134,6 +159,38 @@ moe_permute_kernel(const int32_t* idx, int n_slots, int top_k, int E, int32_t* s
   }
   __syncthreads();
   for (int e = tid; e <= E; e += 1024) seg_off[e] = base[e];
+  if (tile_ws) {
+    // token-tile table of the grouped GEMMs over these segments (layout of eb_gemm_group_tiles):
+    // blk_off[E+1], n_tiles, tile_group[max_tiles], tile_row0[max_tiles]
+    __shared__ int32_t t_off[kMaxExperts + 1];
+    int32_t* blk_off = tile_ws;
+    int32_t* n_tiles = tile_ws + (E + 1);
+    int32_t* tile_group = n_tiles + 1;
+    int32_t* tile_row0 = tile_group + max_tiles;
+    if (tid == 0) {
+      int tt = 0, bb = 0;
+      for (int e = 0; e < E; ++e) {
+        const int len = base[e + 1] - base[e];
+        t_off[e] = tt;
+        blk_off[e] = bb;
+        tt += (len + tn - 1) / tn;
+        bb += (len + 127) / 128;
+      }
+      t_off[E] = tt;
+      blk_off[E] = bb;
+      if (tt > max_tiles) {
+        atomicOr(status, EB_DEV_BAD_INDEX);
+        tt = max_tiles;
+      }
+      *n_tiles = tt;
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += 1024)
+      for (int t = t_off[e]; t < t_off[e + 1] && t < max_tiles; ++t) {
+        tile_group[t] = e;
+        tile_row0[t] = base[e] + (t - t_off[e]) * tn;
+      }
+  }
   __syncthreads();
 
   for (int i0 = 0; i0 < n_slots; i0 += 1024) {
@@ -199,17 +256,29 @@ __global__ void moe_combine_kernel(const uint16_t* y, const int32_t* perm_row, c
   *reinterpret_cast<uint4*>(x + (int64_t)t * H + c) = make_uint4(xu[0], xu[1], xu[2], xu[3]);
 }
 
+template <int EPL, int HPL>
+void launch_router2(unsigned grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wr, int T, int E, int H,
+                    int top_k, int32_t* idx, float* wts, float* logits) {
+  auto kfn = router_topk_kernel<EPL, HPL>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kRouterChunk * HPL * 32 * (int)sizeof(uint16_t));
+    configured = true;
+  }
+  kfn<<<grid, 256, smem, st>>>(x, wr, T, E, H, top_k, idx, wts, logits);
+}
+
 template <int HPL>
 void launch_router(int epl, unsigned grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wr, int T,
-                          int E, int H, int top_k, int32_t* idx, float* wts, float* logits) {
+                   int E, int H, int top_k, int32_t* idx, float* wts, float* logits) {
   if (epl <= 1)
-    router_topk_kernel<1, HPL><<<grid, 256, smem, st>>>(x, wr, T, E, H, top_k, idx, wts, logits);
+    launch_router2<1, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
   else if (epl <= 2)
-    router_topk_kernel<2, HPL><<<grid, 256, smem, st>>>(x, wr, T, E, H, top_k, idx, wts, logits);
+    launch_router2<2, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
   else if (epl <= 4)
-    router_topk_kernel<4, HPL><<<grid, 256, smem, st>>>(x, wr, T, E, H, top_k, idx, wts, logits);
+    launch_router2<4, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
   else
-    router_topk_kernel<8, HPL><<<grid, 256, smem, st>>>(x, wr, T, E, H, top_k, idx, wts, logits);
+    launch_router2<8, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
 }
 
 }  // namespace
@@ -223,8 +292,9 @@ int32_t eb_moe_route(const void* d_x, const void* d_wr, int32_t T, int32_t E, in
              "eb_moe_route: E %d (<= %d), top_k %d (<= %d)", E, kMaxExperts, top_k, kMaxTopK);
   EB_REQUIRE(H >= 8 && H % 8 == 0 && H <= 4096, EB_ERR_UNSUPPORTED, "eb_moe_route: hidden size %d (multiple of 8, <= 4096)", H);
   EB_REQUIRE((uintptr_t)d_wr % 16 == 0, EB_ERR_ARG, "eb_moe_route: router matrix must be 16-byte aligned");
+  EB_REQUIRE((uintptr_t)d_wr % 16 == 0, EB_ERR_ARG, "eb_moe_route: router matrix must be 16-byte aligned");
   if (T == 0) return EB_OK;
-  const size_t smem = 2 * (size_t)H * sizeof(uint16_t);
+  const size_t smem = 2 * (size_t)kRouterChunk * H * sizeof(uint16_t);
   const unsigned grid = (unsigned)((T + 7) / 8);
   cudaStream_t st = eb::as_stream(stream);
   const uint16_t* x = (const uint16_t*)d_x;
@@ -252,7 +322,24 @@ int32_t eb_moe_permute(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_moe_permute: no device");
   moe_permute_kernel<<<1, 1024, 0, eb::as_stream(stream)>>>(d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
-                                                             d_row_token, status);
+                                                             d_row_token, 0, 0, nullptr, status);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_moe_permute_tiles(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E, int32_t* d_seg_off,
+                             int32_t* d_perm_row, int32_t* d_row_token, int32_t tile_tokens, void* d_group_work,
+                             void* stream) {
+  EB_REQUIRE(d_idx && d_seg_off && d_perm_row && d_row_token && d_group_work, EB_ERR_ARG, "eb_moe_permute_tiles: null pointer");
+  EB_REQUIRE(T >= 0 && top_k >= 1 && E >= 1 && E <= kMaxExperts, EB_ERR_UNSUPPORTED, "eb_moe_permute_tiles: E %d (<= %d)",
+             E, kMaxExperts);
+  EB_REQUIRE(tile_tokens == 16 || tile_tokens == 32 || tile_tokens == 64 || tile_tokens == 128, EB_ERR_ARG,
+             "eb_moe_permute_tiles: tile_tokens %d not in {16,32,64,128}", tile_tokens);
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_moe_permute_tiles: no device");
+  const int max_tiles = (T * top_k) / tile_tokens + E;
+  moe_permute_kernel<<<1, 1024, 0, eb::as_stream(stream)>>>(d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
+                                                             d_row_token, tile_tokens, max_tiles, (int32_t*)d_group_work, status);
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

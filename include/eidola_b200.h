@@ -227,6 +227,7 @@ typedef struct eb_gemm_args {
   void* d_work;               /* eb_gemm_workspace() bytes; dense: optional (enables split K) */
   int32_t tile_tokens;        /* 0 = choose; else 16, 32, 64 or 128 tokens per tile */
   int32_t splits;             /* dense: 0 = choose, else K splits (needs d_work) */
+  int32_t tiles_ready;        /* grouped: 1 = d_work already holds eb_gemm_group_tiles() output for these segments */
 } eb_gemm_args;
 
 /* K4.  Y = X * W^T, e4m3 x e4m3 -> fp32 with per-128x128 block scales, bf16 out (tcgen05 tensor cores). */
@@ -235,6 +236,12 @@ int32_t eb_gemm_fp8_block(const eb_gemm_args* a, void* stream);
  * restart at each segment start (the numbering eb_quant_act_block128 uses). */
 int32_t eb_gemm_fp8_grouped(const eb_gemm_args* a, void* stream);
 int32_t eb_gemm_workspace(int32_t rows, int32_t N, int32_t n_groups, size_t* bytes);
+/* Dense GEMM that leaves split-K partials for a fused consumer: when it chose splits_used > 1 the fp32 partials
+ * [splits_used][rows][N] are in d_work and d_y is untouched; when splits_used == 1 d_y holds the bf16 result. */
+int32_t eb_gemm_fp8_block_partial(const eb_gemm_args* a, int32_t* splits_used, void* stream);
+/* Token-tile table of a grouped GEMM, built once and shared by GEMMs over the same segments (tiles_ready = 1). */
+int32_t eb_gemm_group_tiles(const int32_t* d_seg_off, int32_t n_groups, int32_t rows, int32_t tile_tokens, void* d_work,
+                            void* stream);
 
 /* ---- MoE routing (K5, K7) ---------------------------------------------------------------- */
 
@@ -247,6 +254,11 @@ int32_t eb_moe_route(const void* d_x, const void* d_wr, int32_t T, int32_t E, in
  * of slot (t,j) in expert order), d_row_token[T*top_k] (token of each permuted row). */
 int32_t eb_moe_permute(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E, int32_t* d_seg_off,
                        int32_t* d_perm_row, int32_t* d_row_token, void* stream);
+/* The same, also writing the token-tile table of the grouped GEMMs over these segments into d_group_work
+ * (what eb_gemm_group_tiles would build for rows = T*top_k and tile_tokens), so they run with tiles_ready = 1. */
+int32_t eb_moe_permute_tiles(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E, int32_t* d_seg_off,
+                             int32_t* d_perm_row, int32_t* d_row_token, int32_t tile_tokens, void* d_group_work,
+                             void* stream);
 /* x[t] = bf16(x[t] + bf16(sum_j w[t][j] * y[perm_row[t][j]])): weighted combine fused with the residual add. */
 int32_t eb_moe_combine(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
                        int32_t H, void* d_x, void* stream);
@@ -260,6 +272,20 @@ int32_t eb_rope_table(int32_t max_pos, int32_t head_dim, double theta, float* h_
 int32_t eb_rope(void* d_x, int64_t row_stride, int32_t n_heads, int32_t head_dim, const int32_t* d_positions, int32_t T,
                 const float* d_cos, const float* d_sin, int32_t max_pos, void* stream);
 int32_t eb_residual_add(void* d_x, const void* d_y, int64_t n, void* stream);
+/* Fused consumers of a dense GEMM.  `d_part`/`splits`: fp32 split-K partials [splits][T][N] summed in split order
+ * and rounded to bf16 first (splits = 1: d_y_bf16 is read instead).
+ * eb_qkv_rope_append: rotary embedding of the q and k heads of the fused [q | k | v] row, q written to d_qkv (row
+ * stride N), k and v appended to the paged cache.
+ * eb_oproj_residual_rmsnorm: x = bf16(x + o); h = rmsnorm(x) * g. */
+int32_t eb_qkv_rope_append(const float* d_part, int32_t splits, void* d_qkv, int32_t T, int32_t n_q, int32_t n_kv,
+                           int32_t head_dim, const int32_t* d_positions, const float* d_cos, const float* d_sin,
+                           int32_t max_pos, void* d_cache, int32_t num_pages, int32_t page_size,
+                           const int32_t* d_block_tables, int32_t bt_stride, const int32_t* d_tok_slot, void* stream);
+int32_t eb_oproj_residual_rmsnorm(const float* d_part, int32_t splits, const void* d_o_bf16, void* d_x, const float* d_g,
+                                  int32_t T, int32_t H, float eps, void* d_h, void* stream);
+/* x = bf16(x + bf16(sum_j w_j y[perm_row])) as eb_moe_combine, then h = rmsnorm(x) * g for the next consumer. */
+int32_t eb_moe_combine_rmsnorm(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
+                               int32_t H, void* d_x, const float* d_g, float eps, void* d_h, void* stream);
 int32_t eb_embed(const void* d_table, int32_t V, int32_t H, const int32_t* d_tokens, int32_t T, void* d_x, void* stream);
 /* Greedy argmax over bf16 logits [T][ld], ties to the lower id; d_margin (top1 - top2) may be NULL. */
 int32_t eb_argmax(const void* d_logits, int32_t T, int64_t V, int64_t ld, int32_t* d_tok, float* d_margin, void* stream);
