@@ -125,6 +125,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int MT, int HKV, int STAGES, int G>
 __global__ void __launch_bounds__(kThreads, (MT == 1) ? 2 : 1)
 attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   constexpr int PPS = kComputeWarps / HKV;       // pages per stage
   constexpr int kPageRows = 2 * HKV * kPage;     // 128-byte rows per page
   constexpr int kPageBytes = kPageRows * 128;
@@ -376,6 +378,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
 
 // Combine the split-K partials of one (sequence, KV group): warp = query head, lane = two dims.
 __global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const int seq = blockIdx.x;
   const int pb = p.seq_part[seq], pe = p.seq_part[seq + 1];
   if (pe - pb <= 1) return;  // written directly by attn_kernel
@@ -413,6 +417,8 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
 __global__ void kv_append_kernel(uint4* cache, int32_t num_pages, int32_t n_kv, const uint4* k_new, const uint4* v_new,
                                  int64_t row_stride16, const int32_t* block_tables, int32_t bt_stride,
                                  const int32_t* tok_slot, const int32_t* positions, int32_t n_tokens, int32_t* status) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int chunks_per_tok = 2 * n_kv * 8;  // K and V, 8 chunks of 16 bytes per head row
   if (idx >= (int64_t)n_tokens * chunks_per_tok) return;
@@ -456,7 +462,7 @@ int32_t launch_attn(const CUtensorMap& tm, const AttnParams& p, int n_items, cud
     EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  kfn<<<n_items, kThreads, smem, st>>>(tm, p);
+  EB_CUDA(eb::launch(kfn, dim3(n_items), dim3(kThreads), smem, st, tm, p));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -494,9 +500,9 @@ int32_t eb_kv_append(void* d_cache, int32_t num_pages, int32_t n_kv, int32_t hea
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_kv_append: no device");
   const int64_t total = (int64_t)n_tokens * 2 * n_kv * 8;
-  kv_append_kernel<<<(unsigned)eb::cdiv(total, 256), 256, 0, eb::as_stream(stream)>>>(
+  EB_CUDA(eb::launch(kv_append_kernel, dim3((unsigned)eb::cdiv(total, 256)), dim3(256), 0, eb::as_stream(stream), 
       (uint4*)d_cache, num_pages, n_kv, (const uint4*)d_k_new, (const uint4*)d_v_new, row_stride / 8, d_block_tables,
-      bt_stride, d_tok_slot, d_positions, n_tokens, status);
+      bt_stride, d_tok_slot, d_positions, n_tokens, status));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -589,7 +595,7 @@ int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
   }
   if (rc != EB_OK) return rc;
   if (a->n_parts > a->n_seqs) {  // at least one sequence has more than one partial
-    attn_merge_kernel<<<dim3((unsigned)a->n_seqs, (unsigned)((a->n_q + 7) / 8)), 256, 0, st>>>(p);
+    EB_CUDA(eb::launch(attn_merge_kernel, dim3(dim3((unsigned)a->n_seqs, (unsigned)((a->n_q + 7) / 8))), dim3(256), 0, st, p));
     EB_LAUNCH_CHECK();
   }
   return EB_OK;

@@ -22,6 +22,33 @@ inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 }  // namespace eb
 
+#ifdef __CUDACC__
+#include <utility>
+namespace eb {
+// Programmatic dependent launch: a kernel launched through eb::launch may start (be scheduled, run its prologue)
+// while its predecessor in the stream drains; it must call pdl_wait() before it touches any global memory and may
+// call pdl_trigger() once its own successor is allowed to be scheduled.  EIDOLA_B200_NO_PDL=1 turns the launch
+// attribute off (the device calls are then no-ops).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+}  // namespace eb
+#endif
+
 #define EB_CUDA(expr)                                                                              \
   do {                                                                                             \
     cudaError_t _e = (expr);                                                                       \

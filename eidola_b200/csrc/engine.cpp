@@ -242,6 +242,8 @@ int32_t init_work(eb_engine* e) {
 }
 
 __global__ void bt_patch_kernel(int32_t* bt, int stride, const int32_t* patches, int n) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) bt[(int64_t)patches[3 * i] * stride + patches[3 * i + 1]] = patches[3 * i + 2];
 }
@@ -649,8 +651,8 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
   EB_CUDA(cudaMemcpyAsync(e->d_stage, hs, off * sizeof(int32_t), cudaMemcpyHostToDevice, e->stream));
   const int32_t* ds = e->d_stage;
   if (n_patch > 0) {
-    bt_patch_kernel<<<(unsigned)eb::cdiv(n_patch, 256), 256, 0, e->stream>>>(e->d_bt, c.max_pages_per_seq,
-                                                                            ds + (s_patch - hs), n_patch);
+    EB_CUDA(eb::launch(bt_patch_kernel, dim3((unsigned)eb::cdiv(n_patch, 256)), dim3(256), 0, e->stream, e->d_bt, c.max_pages_per_seq,
+                                                                            ds + (s_patch - hs), n_patch));
     EB_LAUNCH_CHECK();
   }
   const eb_attn_item* d_items[2] = {reinterpret_cast<const eb_attn_item*>(ds + items_off[0]),

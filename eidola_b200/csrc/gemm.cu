@@ -141,6 +141,8 @@ struct Cfg {
 template <int TN>
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   using C = Cfg<TN>;
   constexpr int S = C::kStages;
 
@@ -283,6 +285,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 
 // Sum split-K partials in split order and round to bf16.
 __global__ void gemm_splitk_reduce_kernel(const float* part, uint16_t* y, int64_t ldy, int rows, int N, int splits) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)rows * N) return;
   float a = 0.f;
@@ -296,6 +300,8 @@ __global__ void gemm_splitk_reduce_kernel(const float* part, uint16_t* y, int64_
 // Also the exclusive prefix of 128-row scale blocks.  One CTA; n_groups <= 1024.
 __global__ void gemm_tiles_kernel(const int32_t* seg_off, int n_groups, int tn, int max_tiles, int32_t* blk_off,
                                   int32_t* tile_group, int32_t* tile_row0, int32_t* n_tiles, int32_t* status) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   __shared__ int32_t t_off[1025], b_off[1025];
   for (int g = threadIdx.x; g < n_groups; g += blockDim.x) {
     const int len = seg_off[g + 1] - seg_off[g];
@@ -333,6 +339,8 @@ template <int MODE>
 __global__ void __launch_bounds__(256)
 quant_act_kernel(const uint16_t* x, int64_t ldx, int rows, int cols, const int32_t* seg_off, int n_groups,
                  const int32_t* row_map, int src_rows, uint8_t* codes, float* scales, int32_t* status) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const int blk = blockIdx.y, cb = blockIdx.x, n_cb = gridDim.x;
   int r0, r1;
   if (seg_off) {
@@ -453,7 +461,7 @@ int32_t launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmPara
     EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<TN>::kSmem));
     configured = true;
   }
-  kfn<<<grid, kThreads, Cfg<TN>::kSmem, st>>>(tw, tx, p);
+  EB_CUDA(eb::launch(kfn, dim3(grid), dim3(kThreads), Cfg<TN>::kSmem, st, tw, tx, p));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -503,8 +511,8 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
     int32_t* tile_group = n_tiles + 1;
     int32_t* tile_row0 = tile_group + token_tiles;
     if (!a->tiles_ready) {
-      gemm_tiles_kernel<<<1, 256, 0, st>>>(a->d_seg_off, a->n_groups, tn, token_tiles, blk_off, tile_group, tile_row0,
-                                           n_tiles, status);
+      EB_CUDA(eb::launch(gemm_tiles_kernel, dim3(1), dim3(256), 0, st, a->d_seg_off, a->n_groups, tn, token_tiles, blk_off, tile_group, tile_row0,
+                                           n_tiles, status));
       EB_LAUNCH_CHECK();
     }
     p.seg_off = a->d_seg_off;
@@ -552,8 +560,8 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
   if (splits_used) *splits_used = p.splits;
   if (p.splits > 1 && !splits_used) {
     const int64_t total = (int64_t)a->rows * a->N;
-    gemm_splitk_reduce_kernel<<<(unsigned)eb::cdiv(total, 256), 256, 0, st>>>(p.y_part, p.y, p.ldy, a->rows, a->N,
-                                                                              p.splits);
+    EB_CUDA(eb::launch(gemm_splitk_reduce_kernel, dim3((unsigned)eb::cdiv(total, 256)), dim3(256), 0, st, p.y_part, p.y, p.ldy, a->rows, a->N,
+                                                                              p.splits));
     EB_LAUNCH_CHECK();
   }
   return EB_OK;
@@ -598,8 +606,8 @@ int32_t eb_gemm_group_tiles(const int32_t* d_seg_off, int32_t n_groups, int32_t 
   int32_t* w = (int32_t*)d_work;
   int32_t* n_tiles = w + (n_groups + 1);
   int32_t* tile_group = n_tiles + 1;
-  gemm_tiles_kernel<<<1, 256, 0, eb::as_stream(stream)>>>(d_seg_off, n_groups, tile_tokens, token_tiles, w, tile_group,
-                                                          tile_group + token_tiles, n_tiles, status);
+  EB_CUDA(eb::launch(gemm_tiles_kernel, dim3(1), dim3(256), 0, eb::as_stream(stream), d_seg_off, n_groups, tile_tokens, token_tiles, w, tile_group,
+                                                          tile_group + token_tiles, n_tiles, status));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -624,11 +632,11 @@ static int32_t run_quant(int mode, const void* d_x, int64_t ldx, int32_t rows, i
   EB_REQUIRE(n_blk <= 65535, EB_ERR_UNSUPPORTED, "quantise: %d row blocks exceed the grid", n_blk);
   const dim3 grid((unsigned)((cols + 127) / 128), (unsigned)n_blk);
   if (mode == 0)
-    quant_act_kernel<0><<<grid, 256, 0, eb::as_stream(stream)>>>((const uint16_t*)d_x, ldx, rows, cols, d_seg_off, n_groups,
-                                                                 d_row_map, src_rows, (uint8_t*)d_codes, (float*)d_scales, status);
+    EB_CUDA(eb::launch(quant_act_kernel<0>, dim3(grid), dim3(256), 0, eb::as_stream(stream), (const uint16_t*)d_x, ldx, rows, cols, d_seg_off, n_groups,
+                                                                 d_row_map, src_rows, (uint8_t*)d_codes, (float*)d_scales, status));
   else
-    quant_act_kernel<1><<<grid, 256, 0, eb::as_stream(stream)>>>((const uint16_t*)d_x, ldx, rows, cols, d_seg_off, n_groups,
-                                                                 nullptr, rows, (uint8_t*)d_codes, (float*)d_scales, status);
+    EB_CUDA(eb::launch(quant_act_kernel<1>, dim3(grid), dim3(256), 0, eb::as_stream(stream), (const uint16_t*)d_x, ldx, rows, cols, d_seg_off, n_groups,
+                                                                 nullptr, rows, (uint8_t*)d_codes, (float*)d_scales, status));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

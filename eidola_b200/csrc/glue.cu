@@ -32,6 +32,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 // One CTA per token row: y = bf16(x * rsqrt(mean(x^2) + eps) * g).  H is a multiple of 8.
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* x, const float* g, int H, float eps, uint16_t* y) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   __shared__ float red[8];
   const uint16_t* xr = x + (int64_t)blockIdx.x * H;
   uint16_t* yr = y + (int64_t)blockIdx.x * H;
@@ -60,6 +62,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* x, const f
 // Rotate-half rotary embedding in place: one thread per (token, head, pair i < D/2).
 __global__ void rope_kernel(uint16_t* x, int64_t row_stride, int n_heads, int head_dim, const int32_t* positions, int T,
                             const float* cos_t, const float* sin_t, int max_pos, int32_t* status) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const int half = head_dim >> 1;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)T * n_heads * half) return;
@@ -83,6 +87,8 @@ __global__ void rope_kernel(uint16_t* x, int64_t row_stride, int n_heads, int he
 
 // x = bf16(x + y), 8 elements per thread.
 __global__ void residual_add_kernel(uint4* x, const uint4* y, int64_t n8) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n8) return;
   uint4 a = x[i];
@@ -95,6 +101,8 @@ __global__ void residual_add_kernel(uint4* x, const uint4* y, int64_t n8) {
 }
 
 __global__ void embed_kernel(const uint4* table, int V, int H8, const int32_t* tokens, uint4* x, int32_t* status) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const int t = blockIdx.x;
   int tok = tokens[t];
   if (tok < 0 || tok >= V) {
@@ -106,6 +114,8 @@ __global__ void embed_kernel(const uint4* table, int V, int H8, const int32_t* t
 
 // Greedy argmax over bf16 logits, one CTA per token; ties go to the lower id.  Also the top-1 minus top-2 margin.
 __global__ void __launch_bounds__(1024) argmax_kernel(const uint16_t* logits, int64_t V, int64_t ld, int32_t* tok, float* margin) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const uint16_t* r = logits + (int64_t)blockIdx.x * ld;
   float b1 = -INFINITY, b2 = -INFINITY;
   int64_t i1 = V;
@@ -169,7 +179,7 @@ int32_t eb_rmsnorm(const void* d_x, const float* d_g, int32_t T, int32_t H, floa
   EB_REQUIRE(((uintptr_t)d_x % 16 == 0) && ((uintptr_t)d_y % 16 == 0) && ((uintptr_t)d_g % 16 == 0), EB_ERR_ARG,
              "eb_rmsnorm: 16-byte alignment");
   if (T == 0) return EB_OK;
-  rmsnorm_kernel<<<T, 256, 0, eb::as_stream(stream)>>>((const uint16_t*)d_x, d_g, H, eps, (uint16_t*)d_y);
+  EB_CUDA(eb::launch(rmsnorm_kernel, dim3(T), dim3(256), 0, eb::as_stream(stream), (const uint16_t*)d_x, d_g, H, eps, (uint16_t*)d_y));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -199,8 +209,8 @@ int32_t eb_rope(void* d_x, int64_t row_stride, int32_t n_heads, int32_t head_dim
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_rope: no device");
   const int64_t n = (int64_t)T * n_heads * (head_dim / 2);
-  rope_kernel<<<(unsigned)eb::cdiv(n, 256), 256, 0, eb::as_stream(stream)>>>((uint16_t*)d_x, row_stride, n_heads, head_dim,
-                                                                             d_positions, T, d_cos, d_sin, max_pos, status);
+  EB_CUDA(eb::launch(rope_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream), (uint16_t*)d_x, row_stride, n_heads, head_dim,
+                                                                             d_positions, T, d_cos, d_sin, max_pos, status));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -209,7 +219,7 @@ int32_t eb_residual_add(void* d_x, const void* d_y, int64_t n, void* stream) {
   EB_REQUIRE(d_x && d_y && n >= 0 && n % 8 == 0, EB_ERR_ARG, "eb_residual_add: n %lld must be a multiple of 8", (long long)n);
   EB_REQUIRE(((uintptr_t)d_x % 16 == 0) && ((uintptr_t)d_y % 16 == 0), EB_ERR_ARG, "eb_residual_add: 16-byte alignment");
   if (n == 0) return EB_OK;
-  residual_add_kernel<<<(unsigned)eb::cdiv(n / 8, 256), 256, 0, eb::as_stream(stream)>>>((uint4*)d_x, (const uint4*)d_y, n / 8);
+  EB_CUDA(eb::launch(residual_add_kernel, dim3((unsigned)eb::cdiv(n / 8, 256)), dim3(256), 0, eb::as_stream(stream), (uint4*)d_x, (const uint4*)d_y, n / 8));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -220,7 +230,7 @@ int32_t eb_embed(const void* d_table, int32_t V, int32_t H, const int32_t* d_tok
   if (T == 0) return EB_OK;
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_embed: no device");
-  embed_kernel<<<T, 128, 0, eb::as_stream(stream)>>>((const uint4*)d_table, V, H / 8, d_tokens, (uint4*)d_x, status);
+  EB_CUDA(eb::launch(embed_kernel, dim3(T), dim3(128), 0, eb::as_stream(stream), (const uint4*)d_table, V, H / 8, d_tokens, (uint4*)d_x, status));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -229,7 +239,7 @@ int32_t eb_argmax(const void* d_logits, int32_t T, int64_t V, int64_t ld, int32_
   EB_REQUIRE(d_logits && d_tok, EB_ERR_ARG, "eb_argmax: null pointer");
   EB_REQUIRE(T >= 0 && V >= 1 && ld >= V, EB_ERR_ARG, "eb_argmax: bad size");
   if (T == 0) return EB_OK;
-  argmax_kernel<<<T, 1024, 0, eb::as_stream(stream)>>>((const uint16_t*)d_logits, V, ld, d_tok, d_margin);
+  EB_CUDA(eb::launch(argmax_kernel, dim3(T), dim3(1024), 0, eb::as_stream(stream), (const uint16_t*)d_logits, V, ld, d_tok, d_margin));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -254,6 +264,8 @@ __global__ void qkv_rope_append_kernel(const float* part, int splits, uint16_t* 
                                        const int32_t* positions, const float* cos_t, const float* sin_t, int max_pos,
                                        uint16_t* cache, int num_pages, int page_size, const int32_t* block_tables,
                                        int bt_stride, const int32_t* tok_slot, int32_t* status) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const int half = head_dim >> 1;
   const int groups = half >> 3;  // threads per head
   const int n_heads = n_q + 2 * n_kv;
@@ -339,6 +351,8 @@ __global__ void __launch_bounds__(256)
 row_residual_rmsnorm_kernel(const float* part, int splits, const uint16_t* o_bf16, const uint16_t* y, const int32_t* perm_row,
                             const float* wts, int top_k, int64_t n_rows, uint16_t* x, const float* g, int T, int H, float eps,
                             uint16_t* hout) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   __shared__ float red[8];
   const int t = blockIdx.x;
   const int H8 = H >> 3;
@@ -438,9 +452,9 @@ int32_t eb_qkv_rope_append(const float* d_part, int32_t splits, void* d_qkv, int
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_qkv_rope_append: no device");
   const int64_t n = (int64_t)T * (n_q + 2 * n_kv) * (head_dim / 16);
-  qkv_rope_append_kernel<<<(unsigned)eb::cdiv(n, 256), 256, 0, eb::as_stream(stream)>>>(
+  EB_CUDA(eb::launch(qkv_rope_append_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream), 
       d_part, splits, (uint16_t*)d_qkv, T, n_q, n_kv, head_dim, d_positions, d_cos, d_sin, max_pos, (uint16_t*)d_cache,
-      num_pages, page_size, d_block_tables, bt_stride, d_tok_slot, status);
+      num_pages, page_size, d_block_tables, bt_stride, d_tok_slot, status));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -452,9 +466,9 @@ int32_t eb_oproj_residual_rmsnorm(const float* d_part, int32_t splits, const voi
              "eb_oproj_residual_rmsnorm: splits %d without its input", splits);
   EB_REQUIRE(T >= 0 && H >= 8 && H % 8 == 0 && H <= 4096, EB_ERR_UNSUPPORTED, "eb_oproj_residual_rmsnorm: H %d (multiple of 8, <= 4096)", H);
   if (T == 0) return EB_OK;
-  row_residual_rmsnorm_kernel<0><<<T, 256, 0, eb::as_stream(stream)>>>(d_part, splits, (const uint16_t*)d_o_bf16, nullptr,
+  EB_CUDA(eb::launch(row_residual_rmsnorm_kernel<0>, dim3(T), dim3(256), 0, eb::as_stream(stream), d_part, splits, (const uint16_t*)d_o_bf16, nullptr,
                                                                        nullptr, nullptr, 0, 0, (uint16_t*)d_x, d_g, T, H, eps,
-                                                                       (uint16_t*)d_h);
+                                                                       (uint16_t*)d_h));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -464,9 +478,9 @@ int32_t eb_moe_combine_rmsnorm(const void* d_y, const int32_t* d_perm_row, const
   EB_REQUIRE(d_y && d_perm_row && d_wts && d_x && d_g && d_h, EB_ERR_ARG, "eb_moe_combine_rmsnorm: null pointer");
   EB_REQUIRE(T >= 0 && top_k >= 1 && H >= 8 && H % 8 == 0 && H <= 4096, EB_ERR_UNSUPPORTED, "eb_moe_combine_rmsnorm: H %d (multiple of 8, <= 4096)", H);
   if (T == 0) return EB_OK;
-  row_residual_rmsnorm_kernel<1><<<T, 256, 0, eb::as_stream(stream)>>>(nullptr, 1, nullptr, (const uint16_t*)d_y, d_perm_row,
+  EB_CUDA(eb::launch(row_residual_rmsnorm_kernel<1>, dim3(T), dim3(256), 0, eb::as_stream(stream), nullptr, 1, nullptr, (const uint16_t*)d_y, d_perm_row,
                                                                        d_wts, top_k, (int64_t)T * top_k, (uint16_t*)d_x, d_g, T,
-                                                                       H, eps, (uint16_t*)d_h);
+                                                                       H, eps, (uint16_t*)d_h));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

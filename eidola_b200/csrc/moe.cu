@@ -28,6 +28,8 @@ template <int EPL, int HPL>  // experts per lane = ceil(E / 32), hidden elements
 __global__ void __launch_bounds__(256, 1)
 router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, int top_k, int32_t* idx, float* wts,
                    float* logits_out) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   extern __shared__ __align__(16) uint16_t wrow[];  // [2][kRouterChunk][H]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 8 + warp;
@@ -140,6 +142,8 @@ router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, i
 __global__ void __launch_bounds__(1024)
 moe_permute_kernel(const int32_t* idx, int n_slots, int top_k, int E, int32_t* seg_off, int32_t* perm_row,
                    int32_t* row_token, int tn, int max_tiles, int32_t* tile_ws, int32_t* status) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   __shared__ int32_t base[kMaxExperts + 1];   // running start of each expert's unplaced slots
   __shared__ int32_t wcnt[32][kMaxExperts];   // per-warp counts of the current tile
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -226,6 +230,8 @@ moe_permute_kernel(const int32_t* idx, int n_slots, int top_k, int E, int32_t* s
 // x[t] = bf16( x[t] + bf16( sum_j w[t][j] * y[perm_row[t*top_k+j]] ) ), j ascending, fmaf.  8 columns per thread.
 __global__ void moe_combine_kernel(const uint16_t* y, const int32_t* perm_row, const float* wts, int T, int top_k,
                                    int H, uint16_t* x, int64_t n_rows) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
   const int h8 = H >> 3;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)T * h8) return;
@@ -257,7 +263,7 @@ __global__ void moe_combine_kernel(const uint16_t* y, const int32_t* perm_row, c
 }
 
 template <int EPL, int HPL>
-void launch_router2(unsigned grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wr, int T, int E, int H,
+int32_t launch_router2(unsigned grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wr, int T, int E, int H,
                     int top_k, int32_t* idx, float* wts, float* logits) {
   auto kfn = router_topk_kernel<EPL, HPL>;
   static bool configured = false;
@@ -265,20 +271,21 @@ void launch_router2(unsigned grid, size_t smem, cudaStream_t st, const uint16_t*
     cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kRouterChunk * HPL * 32 * (int)sizeof(uint16_t));
     configured = true;
   }
-  kfn<<<grid, 256, smem, st>>>(x, wr, T, E, H, top_k, idx, wts, logits);
+  EB_CUDA(eb::launch(kfn, dim3(grid), dim3(256), smem, st, x, wr, T, E, H, top_k, idx, wts, logits));
+  return EB_OK;
 }
 
 template <int HPL>
-void launch_router(int epl, unsigned grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wr, int T,
+int32_t launch_router(int epl, unsigned grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wr, int T,
                    int E, int H, int top_k, int32_t* idx, float* wts, float* logits) {
   if (epl <= 1)
-    launch_router2<1, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
+    return launch_router2<1, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
   else if (epl <= 2)
-    launch_router2<2, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
+    return launch_router2<2, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
   else if (epl <= 4)
-    launch_router2<4, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
+    return launch_router2<4, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
   else
-    launch_router2<8, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
+    return launch_router2<8, HPL>(grid, smem, st, x, wr, T, E, H, top_k, idx, wts, logits);
 }
 
 }  // namespace
@@ -301,17 +308,15 @@ int32_t eb_moe_route(const void* d_x, const void* d_wr, int32_t T, int32_t E, in
   const uint16_t* wr = (const uint16_t*)d_wr;
   const int epl = (E + 31) / 32, hpl = (H + 31) / 32;
   if (hpl <= 16)
-    launch_router<16>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+    return launch_router<16>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
   else if (hpl <= 32)
-    launch_router<32>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+    return launch_router<32>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
   else if (hpl <= 64)
-    launch_router<64>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+    return launch_router<64>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
   else if (hpl <= 96)
-    launch_router<96>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+    return launch_router<96>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
   else
-    launch_router<128>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
-  EB_LAUNCH_CHECK();
-  return EB_OK;
+    return launch_router<128>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
 }
 
 int32_t eb_moe_permute(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E, int32_t* d_seg_off,
@@ -321,8 +326,8 @@ int32_t eb_moe_permute(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E
              kMaxExperts);
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_moe_permute: no device");
-  moe_permute_kernel<<<1, 1024, 0, eb::as_stream(stream)>>>(d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
-                                                             d_row_token, 0, 0, nullptr, status);
+  EB_CUDA(eb::launch(moe_permute_kernel, dim3(1), dim3(1024), 0, eb::as_stream(stream), d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
+                                                             d_row_token, 0, 0, nullptr, status));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -338,8 +343,8 @@ int32_t eb_moe_permute_tiles(const int32_t* d_idx, int32_t T, int32_t top_k, int
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_moe_permute_tiles: no device");
   const int max_tiles = (T * top_k) / tile_tokens + E;
-  moe_permute_kernel<<<1, 1024, 0, eb::as_stream(stream)>>>(d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
-                                                             d_row_token, tile_tokens, max_tiles, (int32_t*)d_group_work, status);
+  EB_CUDA(eb::launch(moe_permute_kernel, dim3(1), dim3(1024), 0, eb::as_stream(stream), d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
+                                                             d_row_token, tile_tokens, max_tiles, (int32_t*)d_group_work, status));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -351,8 +356,8 @@ int32_t eb_moe_combine(const void* d_y, const int32_t* d_perm_row, const float* 
   EB_REQUIRE(((uintptr_t)d_y % 16 == 0) && ((uintptr_t)d_x % 16 == 0), EB_ERR_ARG, "eb_moe_combine: 16-byte alignment");
   if (T == 0) return EB_OK;
   const int64_t n = (int64_t)T * (H / 8);
-  moe_combine_kernel<<<(unsigned)eb::cdiv(n, 256), 256, 0, eb::as_stream(stream)>>>(
-      (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, (uint16_t*)d_x, (int64_t)T * top_k);
+  EB_CUDA(eb::launch(moe_combine_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream), 
+      (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, (uint16_t*)d_x, (int64_t)T * top_k));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

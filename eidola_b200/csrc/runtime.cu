@@ -1,4 +1,5 @@
 // Device-memory plumbing, the status word, and the seeded tensor generators of libeidola_b200.
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -19,6 +20,14 @@ int32_t fail(int32_t code, const char* fmt, ...) {
   va_end(ap);
   g_last_error = buf;
   return code;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("EIDOLA_B200_NO_PDL");
+    return !(v && v[0] == '1');
+  }();
+  return on;
 }
 
 static std::mutex g_status_mu;
