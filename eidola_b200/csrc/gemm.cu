@@ -181,6 +181,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[S]);
   const uint32_t bar_tfull = smem_u32(&bars[2 * S]), bar_tempty = smem_u32(&bars[2 * S + 2]);
 
+  const int wy = g * p.N + n0;
+  int prefilled = 0;
   if (tid == 0) {
     abort_flag = 0;
     for (int s = 0; s < S; ++s) {
@@ -193,6 +195,15 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // Fill the pipeline before the rest of the CTA has finished setting up (tensor-memory allocation, scale
+    // products): the first stages are in flight one barrier round trip earlier.
+    prefilled = min(S, nkb);
+    for (int i = 0; i < prefilled; ++i) {
+      const uint32_t a_dst = stage0 + i * C::kStageBytes, b_dst = a_dst + kTileN * kBlockK;
+      mbar_arrive_expect_tx(bar_full + 8 * i, C::kStageBytes);
+      tma_load_2d(a_dst, &tm_w, (kb0 + i) * kBlockK, wy, bar_full + 8 * i);
+      tma_load_2d(b_dst, &tm_x, (kb0 + i) * kBlockK, row0, bar_full + 8 * i);
+    }
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
   if (tid >= 64) {
@@ -207,8 +218,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      const int wy = g * p.N + n0;
-      for (int i = 0; i < nkb; ++i) {
+      for (int i = prefilled; i < nkb; ++i) {
         const int s = i % S;
         if (i >= S && !mbar_wait(bar_empty + 8 * s, ((i / S) - 1) & 1, &abort_flag, p.status)) break;
         const uint32_t a_dst = stage0 + s * C::kStageBytes, b_dst = a_dst + kTileN * kBlockK;
