@@ -602,3 +602,133 @@ int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Paged sink attention for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc where they need attention: a host that has handed all device
+// memory to its own pool, a plugin that runs inside another runtime's allocator arena, a latency-critical thread
+// that must not take the allocator's lock.  For them the split-K scratch (partial accumulators and their
+// (max, sum) pairs) lives in the two file-scope device arrays below, which every GPU that loads the library holds
+// until the process exits (16.5 MiB together).  The caller still owns every input and output.
+
+namespace {
+
+constexpr int64_t kStaticRows = 65536;  // (partial slot, query position, query head) rows the scratch can hold
+
+static __device__ __align__(256) float g_static_part_acc[kStaticRows * kHeadDim];  // 16 MiB
+static __device__ __align__(256) float g_static_part_ml[kStaticRows * 2];          // 512 KiB
+static __device__ __align__(256) int32_t g_static_status[64];                       // status word when the caller passes none
+
+struct StaticScratch {
+  bool ready = false;
+  float* acc = nullptr;
+  float* ml = nullptr;
+  int32_t* status = nullptr;
+};
+StaticScratch g_static_scratch[64];  // per device: in host code the array names above are only host-side stand-ins,
+                                     // the device addresses come from cudaGetSymbolAddress with that device current
+
+}  // namespace
+
+extern "C" {
+
+int32_t eb_attn_paged_sink_static(const eb_attn_args* a, int32_t* d_status, void* stream) {
+  EB_REQUIRE(a, EB_ERR_ARG, "eb_attn_paged_sink_static: null args");
+  EB_REQUIRE(a->d_q && a->d_out && a->d_cache && a->d_block_tables && a->d_seq_slots && a->d_q_off && a->d_ctx_lens &&
+                 a->d_sinks && a->d_items && a->d_seq_part,
+             EB_ERR_ARG, "eb_attn_paged_sink_static: null pointer");
+  EB_REQUIRE(a->head_dim == kHeadDim && a->page_size == kPage, EB_ERR_UNSUPPORTED,
+             "eb_attn_paged_sink_static: head_dim %d / page_size %d (built for 64 / 16)", a->head_dim, a->page_size);
+  EB_REQUIRE(a->n_kv >= 1 && (a->n_q == a->n_kv * 8 || a->n_q == a->n_kv * 4), EB_ERR_UNSUPPORTED,
+             "eb_attn_paged_sink_static: %d query heads over %d KV heads (built for groups of 8 or 4)", a->n_q, a->n_kv);
+  const int group = a->n_q / a->n_kv;
+  EB_REQUIRE(a->max_q_len >= 1 && a->max_q_len * group <= 48, EB_ERR_UNSUPPORTED,
+             "eb_attn_paged_sink_static: max_q_len %d exceeds %d", a->max_q_len, 48 / group);
+  EB_REQUIRE(a->n_seqs >= 0 && a->n_items >= 0 && a->n_parts >= 0 && a->num_pages >= 1 && a->window >= 0, EB_ERR_ARG,
+             "eb_attn_paged_sink_static: negative size");
+  EB_REQUIRE(a->q_stride % 2 == 0 && a->out_stride % 2 == 0 && (uintptr_t)a->d_q % 4 == 0 && (uintptr_t)a->d_out % 4 == 0,
+             EB_ERR_ARG, "eb_attn_paged_sink_static: q/out must be 4-byte aligned with even strides");
+  EB_REQUIRE((uintptr_t)a->d_cache % 16 == 0, EB_ERR_ARG, "eb_attn_paged_sink_static: cache must be 16-byte aligned");
+  const int64_t need_rows = (int64_t)a->n_parts * a->max_q_len * a->n_q;
+  EB_REQUIRE(need_rows <= kStaticRows, EB_ERR_NOMEM,
+             "eb_attn_paged_sink_static: %d partial slots x %d query positions x %d heads = %lld rows exceed the built-in "
+             "scratch of %lld rows; plan with a larger chunk_pages or use eb_attn_paged_sink with a caller workspace",
+             a->n_parts, a->max_q_len, a->n_q, (long long)need_rows, (long long)kStaticRows);
+  if (a->n_seqs == 0 || a->n_items == 0) return EB_OK;
+  const int64_t rows = (int64_t)a->num_pages * 2 * a->n_kv * kPage;
+  EB_REQUIRE(rows < (1ll << 31), EB_ERR_UNSUPPORTED, "eb_attn_paged_sink_static: cache of %lld rows exceeds a tensor map",
+             (long long)rows);
+
+  // Set-up, once per device, with that device current: resolve the device addresses of the scratch arrays.
+  int dev = -1;
+  EB_CUDA(cudaGetDevice(&dev));
+  EB_REQUIRE(dev >= 0 && dev < 64, EB_ERR_UNSUPPORTED, "eb_attn_paged_sink_static: device ordinal %d", dev);
+  StaticScratch& sc = g_static_scratch[dev];
+  if (!sc.ready) {
+    EB_CUDA(cudaGetSymbolAddress((void**)&sc.acc, g_static_part_acc));
+    EB_CUDA(cudaGetSymbolAddress((void**)&sc.ml, g_static_part_ml));
+    EB_CUDA(cudaGetSymbolAddress((void**)&sc.status, g_static_status));
+    sc.ready = true;
+  }
+
+  EncodeTiledFn enc = encode_tiled_fn();
+  EB_REQUIRE(enc, EB_ERR_NODEVICE, "eb_attn_paged_sink_static: driver entry point cuTensorMapEncodeTiled not found");
+  CUtensorMap tm;
+  const cuuint64_t gdim[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows};
+  const cuuint64_t gstr[1] = {128};
+  const cuuint32_t box[2] = {(cuuint32_t)kHeadDim, (cuuint32_t)(2 * a->n_kv * kPage)};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult cr = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a->d_cache), gdim, gstr, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  EB_REQUIRE(cr == CUDA_SUCCESS, EB_ERR_ARG, "eb_attn_paged_sink_static: cuTensorMapEncodeTiled failed (%d)", (int)cr);
+
+  AttnParams p;
+  p.q = (const uint16_t*)a->d_q;
+  p.q_stride = a->q_stride;
+  p.out = (uint16_t*)a->d_out;
+  p.out_stride = a->out_stride;
+  p.block_tables = a->d_block_tables;
+  p.bt_stride = a->bt_stride;
+  p.seq_slots = a->d_seq_slots;
+  p.q_off = a->d_q_off;
+  p.ctx_lens = a->d_ctx_lens;
+  p.sinks = a->d_sinks;
+  p.window = a->window;
+  p.n_q = a->n_q;
+  p.max_q_len = a->max_q_len;
+  p.num_pages = a->num_pages;
+  p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.items = a->d_items;
+  p.seq_part = a->d_seq_part;
+  p.part_acc = sc.acc;  // every partial row that the merge reads is written by this call first: nothing to clear
+  p.part_ml = sc.ml;
+  p.status = d_status ? d_status : sc.status;
+
+  cudaStream_t st = eb::as_stream(stream);
+  const int mt = (a->max_q_len * group + 15) / 16;
+  int32_t rc;
+  if (group == 8) {
+    if (mt == 1)
+      rc = dispatch_hkv<1, 8>(a->n_kv, tm, p, a->n_items, st);
+    else if (mt == 2)
+      rc = dispatch_hkv<2, 8>(a->n_kv, tm, p, a->n_items, st);
+    else
+      rc = dispatch_hkv<3, 8>(a->n_kv, tm, p, a->n_items, st);
+  } else {
+    if (mt == 1)
+      rc = dispatch_hkv<1, 4>(a->n_kv, tm, p, a->n_items, st);
+    else if (mt == 2)
+      rc = dispatch_hkv<2, 4>(a->n_kv, tm, p, a->n_items, st);
+    else
+      rc = dispatch_hkv<3, 4>(a->n_kv, tm, p, a->n_items, st);
+  }
+  if (rc != EB_OK) return rc;
+  if (a->n_parts > a->n_seqs) {
+    EB_CUDA(eb::launch(attn_merge_kernel, dim3((unsigned)a->n_seqs, (unsigned)((a->n_q + 7) / 8)), dim3(256), 0, st, p));
+  }
+  return EB_OK;
+}
+
+}  // extern "C"

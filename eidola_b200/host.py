@@ -112,6 +112,11 @@ def attn_paged_sink(args: AttnArgs, stream=None) -> None:
     call("eb_attn_paged_sink", C.byref(args), c_vp(stream))
 
 
+def attn_paged_sink_static(args: AttnArgs, d_status=None, stream=None) -> None:
+    """The variant that allocates nothing: split-K scratch lives in arrays built into the library."""
+    call("eb_attn_paged_sink_static", C.byref(args), c_vp(d_status), c_vp(stream))
+
+
 class AttnLaunch:
     """Device-resident arguments of one attention launch, built from a packed step and a plan."""
 

@@ -194,6 +194,23 @@ typedef struct eb_attn_args {
 
 /* K2+K3.  Paged sink attention (decode and k>1 verify) with split-K and log-sum-exp merge. */
 int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream);
+/*
+ * K2+K3 for callers that cannot allocate device memory (this entry point has no counterpart in the reference
+ * project).  A host that has given all device memory to its own pool, a plugin living inside another runtime's
+ * allocator arena, or a thread that must never take the allocator's lock cannot hand eb_attn_paged_sink a
+ * workspace; here the split-K scratch is two device arrays built into the library (16 MiB + 512 KiB, held by every
+ * GPU that loads the library until the process exits).  d_part_acc / d_part_ml of the arguments are ignored.
+ *   limit    : n_parts * max_q_len * n_q <= 65536 rows, else EB_ERR_NOMEM and nothing is launched (plan with a
+ *              larger chunk_pages, or use eb_attn_paged_sink);
+ *   d_status : caller-owned device int32 that receives EB_DEV_* bits (OR-ed in; NULL = a word inside the library);
+ *   calls no cudaMalloc, cudaFree or other allocating routine.  The first call on a device resolves the addresses
+ *   of the built-in arrays (cudaGetSymbolAddress, once per device, with that device current): make that first call
+ *   before any stream capture begins;
+ *   every call on a device shares the same scratch, which keeps the previous call's contents.  Nothing in it has
+ *   to start at zero (each partial row is written before it is read), but two calls that overlap on the GPU --
+ *   different streams, or the same scratch from two threads -- race on it: serialise them.
+ */
+int32_t eb_attn_paged_sink_static(const eb_attn_args* a, int32_t* d_status, void* stream);
 /* Workspace sizes for the two partial buffers of eb_attn_args. */
 int32_t eb_attn_workspace(int32_t n_parts, int32_t max_q_len, int32_t n_q, int32_t head_dim, size_t* acc_bytes,
                           size_t* ml_bytes);
