@@ -74,7 +74,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                     print(r.stderr, file=sys.stderr)
     if jobs or not LIB_PATH.exists():
         cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a",
-               "-Xcompiler", "-fPIC", "-cudart", "static"]
+               "-Xcompiler", "-fPIC", "-cudart", "static", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

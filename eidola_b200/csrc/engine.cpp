@@ -51,6 +51,15 @@ struct Plan {
 struct eb_engine {
   eb_config c;
   int sm_count = 0;
+  // tensor / expert parallelism: this rank holds query heads [rank*hq_l, +hq_l), KV heads [rank*hkv_l, +hkv_l) and
+  // experts [e0, e0 + e_l); hqd and nqkv below are the LOCAL widths
+  int tp_rank = 0, tp_size = 1;
+  eb_comm* comm = nullptr;
+  int hq_l = 0, hkv_l = 0, e_l = 0, e0 = 0;
+  int kv_band = 0, k_col0 = 0, v_col0 = 0;  // the K and V bands of the local QKV row start on 128-row scale blocks
+  float* ar_buf = nullptr;                   // fp32 [max_tokens][hidden] summed across ranks
+  int32_t* r_idx_local = nullptr;
+  float* sinks_all = nullptr;
   int nqkv = 0, hqd = 0, kbH = 0, kbI = 0, kbA = 0;
   std::vector<Layer> layers;
   uint16_t* embed = nullptr;
@@ -134,28 +143,39 @@ int32_t fill_ones(eb_engine* e, float* d, int n) {
 
 int32_t init_weights(eb_engine* e) {
   const eb_config& c = e->c;
-  const int H = c.hidden, I = c.inter, E = c.n_experts;
+  const int H = c.hidden, I = c.inter, E = e->e_l;  // E: experts held by this rank
   void* st = e->stream;
+  const int hqd_g = c.n_q_heads * c.head_dim, hkd_g = c.n_kv_heads * c.head_dim, nqkv_g = hqd_g + 2 * hkd_g;
+  const int kv_row0 = (e->tp_rank * e->hkv_l * c.head_dim) / 128 * 128;  // start of this rank's K (and V) band
   for (int l = 0; l < c.n_layers; ++l) {
     Layer& L = e->layers[(size_t)l];
     EB_TRY(alloc_fp8(e, &L.wqkv, 1, e->nqkv, H));
     EB_TRY(alloc_fp8(e, &L.wo, 1, H, e->hqd));
     EB_TRY(alloc_fp8(e, &L.w1, E, 2 * I, H));
     EB_TRY(alloc_fp8(e, &L.w2, E, H, I));
-    EB_TRY(dev_alloc(e, &L.wr, (size_t)E * H, &e->weight_bytes));
+    EB_TRY(dev_alloc(e, &L.wr, (size_t)c.n_experts * H, &e->weight_bytes));
     EB_TRY(dev_alloc(e, &L.sinks, (size_t)c.n_q_heads, &e->weight_bytes));
     EB_TRY(dev_alloc(e, &L.g_attn, (size_t)H, &e->weight_bytes));
     EB_TRY(dev_alloc(e, &L.g_mlp, (size_t)H, &e->weight_bytes));
-    EB_TRY(eb_synth_weight_fp8(L.wqkv.codes, L.wqkv.scales, e->nqkv, H, 0, e->nqkv, c.seed, sid(l, K_WQKV, 0), c.init_std, st));
-    EB_TRY(eb_synth_weight_fp8(L.wo.codes, L.wo.scales, H, e->hqd, 0, H, c.seed, sid(l, K_WO, 0), c.init_std, st));
+    // local QKV rows = [q heads | K band | V band], each a row band of the global [q | k | v] tensor
+    const int64_t band_rows[3] = {e->hqd, e->kv_band, e->kv_band};
+    const int64_t band_src[3] = {(int64_t)e->tp_rank * e->hqd, hqd_g + kv_row0, hqd_g + hkd_g + kv_row0};
+    int64_t dst_row = 0;
+    for (int b = 0; b < 3; ++b) {
+      EB_TRY(eb_synth_weight_fp8(L.wqkv.codes + dst_row * H, L.wqkv.scales + (dst_row / 128) * e->kbH, nqkv_g, H, band_src[b],
+                                 band_rows[b], c.seed, sid(l, K_WQKV, 0), c.init_std, st));
+      dst_row += band_rows[b];
+    }
+    EB_TRY(eb_synth_weight_fp8_slice(L.wo.codes, L.wo.scales, H, hqd_g, 0, H, (int64_t)e->tp_rank * e->hqd, e->hqd, c.seed,
+                                     sid(l, K_WO, 0), c.init_std, st));
     const int64_t s1 = eb::cdiv(2 * I, 128) * e->kbH, s2 = eb::cdiv(H, 128) * e->kbI;
     for (int x = 0; x < E; ++x) {
       EB_TRY(eb_synth_weight_fp8(L.w1.codes + (int64_t)x * 2 * I * H, L.w1.scales + x * s1, 2 * I, H, 0, 2 * I, c.seed,
-                                 sid(l, K_W1, x), c.init_std, st));
+                                 sid(l, K_W1, e->e0 + x), c.init_std, st));
       EB_TRY(eb_synth_weight_fp8(L.w2.codes + (int64_t)x * H * I, L.w2.scales + x * s2, H, I, 0, H, c.seed,
-                                 sid(l, K_W2, x), c.init_std, st));
+                                 sid(l, K_W2, e->e0 + x), c.init_std, st));
     }
-    EB_TRY(eb_synth_normal_bf16(L.wr, (int64_t)E * H, c.seed, sid(l, K_ROUTER, 0), 0, c.init_std, st));
+    EB_TRY(eb_synth_normal_bf16(L.wr, (int64_t)c.n_experts * H, c.seed, sid(l, K_ROUTER, 0), 0, c.init_std, st));
     EB_TRY(eb_synth_normal_f32(L.sinks, c.n_q_heads, c.seed, sid(l, K_SINK, 0), 0, 1.0f, st));
     EB_TRY(fill_ones(e, L.g_attn, H));
     EB_TRY(fill_ones(e, L.g_mlp, H));
@@ -181,7 +201,7 @@ int32_t init_weights(eb_engine* e) {
 
 int32_t init_work(eb_engine* e) {
   const eb_config& c = e->c;
-  const int H = c.hidden, I = c.inter, E = c.n_experts, T = c.max_tokens;
+  const int H = c.hidden, I = c.inter, E = e->e_l, T = c.max_tokens;
   const int64_t R = (int64_t)T * c.top_k;
   int64_t* w = &e->work_bytes;
   EB_TRY(dev_alloc(e, &e->x, (size_t)T * H, w));
@@ -202,6 +222,8 @@ int32_t init_work(eb_engine* e) {
   EB_TRY(dev_alloc(e, &e->sxp, (size_t)(rb * e->kbH), w));
   EB_TRY(dev_alloc(e, &e->sact, (size_t)(rb * e->kbI), w));
   EB_TRY(dev_alloc(e, &e->r_idx, (size_t)R, w));
+  EB_TRY(dev_alloc(e, &e->r_idx_local, (size_t)R, w));
+  if (e->tp_size > 1) EB_TRY(dev_alloc(e, &e->ar_buf, (size_t)T * H, w));
   EB_TRY(dev_alloc(e, &e->r_wts, (size_t)R, w));
   EB_TRY(dev_alloc(e, &e->seg_off, (size_t)E + 1, w));
   EB_TRY(dev_alloc(e, &e->perm_row, (size_t)R, w));
@@ -216,9 +238,9 @@ int32_t init_work(eb_engine* e) {
   EB_TRY(dev_alloc(e, &p8, ws2, w));
   e->group_ws = p8;
   e->cap_items = 4 * e->sm_count + c.max_seqs + 16;
-  const int ppi = 8 / c.n_kv_heads;
+  const int ppi = 8 / e->hkv_l;
   size_t acc_b = 0, ml_b = 0;
-  EB_TRY(eb_attn_workspace(e->cap_items * ppi, c.max_q_len, c.n_q_heads, c.head_dim, &acc_b, &ml_b));
+  EB_TRY(eb_attn_workspace(e->cap_items * ppi, c.max_q_len, e->hq_l, c.head_dim, &acc_b, &ml_b));
   EB_TRY(dev_alloc(e, &e->part_acc, acc_b / sizeof(float), w));
   EB_TRY(dev_alloc(e, &e->part_ml, ml_b / sizeof(float), w));
   EB_TRY(dev_alloc(e, &e->d_next, (size_t)T, w));
@@ -272,7 +294,8 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
                    const int32_t* d_positions, const int32_t* d_slots, const int32_t* d_q_off, const int32_t* d_ctx,
                    const eb_attn_item* d_items[2], const int32_t* d_seq_part[2], const Plan plans[2], int max_q_len) {
   const eb_config& c = e->c;
-  const int H = c.hidden, I = c.inter, E = c.n_experts, R = T * c.top_k;
+  const int H = c.hidden, I = c.inter, E = e->e_l, R = T * c.top_k;  // E: local experts; R: upper bound of local rows
+  const bool tp = e->tp_size > 1;
   void* st = e->stream;
   const int max_pos = c.max_pages_per_seq * c.page_size;
   int& n = e->launches;
@@ -309,7 +332,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     n += 1;
     return splits ? eb_gemm_fp8_block_partial(&g, splits, st) : eb_gemm_fp8_block(&g, st);
   };
-  const int avg2 = std::min(128, 2 * ((R + E - 1) / E));
+  const int avg2 = std::min(128, 2 * ((R / e->tp_size + E - 1) / E));
   const int group_tn = avg2 <= 16 ? 16 : avg2 <= 32 ? 32 : avg2 <= 64 ? 64 : 128;
   auto grouped = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout) -> int32_t {
     eb_gemm_args g = {};
@@ -357,9 +380,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     mark(2);
     EB_TRY(dense(e->h8, e->sh, L.wqkv, e->nqkv, H, e->qkv, &splits));
     mark(-1);
-    EB_TRY(eb_qkv_rope_append((const float*)e->gemm_ws, splits, e->qkv, T, c.n_q_heads, c.n_kv_heads, c.head_dim,
-                              d_positions, e->rope_cos, e->rope_sin, max_pos, L.cache, c.num_pages, c.page_size, e->d_bt,
-                              c.max_pages_per_seq, d_tok_slot, st));
+    EB_TRY(eb_qkv_rope_append_ex((const float*)e->gemm_ws, splits, e->qkv, e->nqkv, e->k_col0, e->v_col0, T, e->hq_l,
+                                 e->hkv_l, c.head_dim, d_positions, e->rope_cos, e->rope_sin, max_pos, L.cache,
+                                 c.num_pages, c.page_size, e->d_bt, c.max_pages_per_seq, d_tok_slot, st));
     eb_attn_args a = {};
     a.d_q = e->qkv;
     a.q_stride = e->nqkv;
@@ -374,10 +397,10 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     a.d_ctx_lens = d_ctx;
     a.n_seqs = n_seqs;
     a.max_q_len = max_q_len;
-    a.d_sinks = L.sinks;
+    a.d_sinks = L.sinks + e->tp_rank * e->hq_l;
     a.window = pi ? c.window : 0;
-    a.n_q = c.n_q_heads;
-    a.n_kv = c.n_kv_heads;
+    a.n_q = e->hq_l;
+    a.n_kv = e->hkv_l;
     a.head_dim = c.head_dim;
     a.page_size = c.page_size;
     a.scale = 0.125f;
@@ -394,9 +417,25 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     mark(2);
     EB_TRY(dense(e->a8, e->sa, L.wo, H, e->hqd, e->o, &splits));
     mark(-1);
-    EB_TRY(eb_oproj_residual_rmsnorm((const float*)e->gemm_ws, splits, e->o, e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
-    EB_TRY(eb_moe_route(e->h, L.wr, T, E, H, c.top_k, e->r_idx, e->r_wts, nullptr, st));
-    EB_TRY(eb_moe_permute_tiles(e->r_idx, T, c.top_k, E, e->seg_off, e->perm_row, e->row_token, group_tn, e->group_ws, st));
+    if (!tp) {
+      EB_TRY(eb_oproj_residual_rmsnorm((const float*)e->gemm_ws, splits, e->o, e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
+    } else {
+      // C1: this rank's heads contributed a partial [T, H]; sum the partials of all ranks in fp32, then round once
+      EB_TRY(eb_sum_planes_f32(splits > 1 ? (const float*)e->gemm_ws : nullptr, splits, e->o, (int64_t)T * H, e->ar_buf, st));
+      EB_TRY(eb_comm_allreduce_f32(e->comm, e->ar_buf, (int64_t)T * H, st));
+      EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf, 1, nullptr, e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
+      n += 2;
+    }
+    EB_TRY(eb_moe_route(e->h, L.wr, T, c.n_experts, H, c.top_k, e->r_idx, e->r_wts, nullptr, st));
+    if (!tp) {
+      EB_TRY(eb_moe_permute_tiles(e->r_idx, T, c.top_k, E, e->seg_off, e->perm_row, e->row_token, group_tn, e->group_ws, st));
+    } else {
+      // routing is replicated; keep the slots of this rank's experts only
+      EB_TRY(eb_moe_localize(e->r_idx, T * c.top_k, e->e0, E, e->r_idx_local, st));
+      EB_TRY(eb_moe_permute_tiles_local(e->r_idx_local, T, c.top_k, E, e->seg_off, e->perm_row, e->row_token, group_tn,
+                                        e->group_ws, st));
+      n += 1;
+    }
     EB_TRY(eb_quant_gather_block128(e->h, H, T, e->row_token, R, H, e->seg_off, E, e->xp8, e->sxp, st));
     mark(3);
     EB_TRY(grouped(e->xp8, e->sxp, L.w1, 2 * I, H, e->gu));
@@ -406,7 +445,16 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     EB_TRY(grouped(e->act8, e->sact, L.w2, H, I, e->y));
     mark(-1);
     const float* g_next = (l + 1 < c.n_layers) ? e->layers[(size_t)l + 1].g_attn : e->g_final;
-    EB_TRY(eb_moe_combine_rmsnorm(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->x, g_next, c.rms_eps, e->h, st));
+    if (!tp) {
+      EB_TRY(eb_moe_combine_rmsnorm(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->x, g_next, c.rms_eps, e->h, st));
+    } else {
+      // C2: partial mix of this rank's experts, summed across ranks (tokens are replicated, so the combine of an
+      // expert-parallel layer is an all-reduce and the dispatch needs no exchange)
+      EB_TRY(eb_moe_combine_f32(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->ar_buf, st));
+      EB_TRY(eb_comm_allreduce_f32(e->comm, e->ar_buf, (int64_t)T * H, st));
+      EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf, 1, nullptr, e->x, g_next, T, H, c.rms_eps, e->h, st));
+      n += 2;
+    }
     n += 9 + (plans[pi].n_parts > n_seqs ? 1 : 0);
     if (c.debug & 1) {
       EB_CUDA(cudaMemcpyAsync(e->dbg_route + (size_t)l * c.max_tokens * c.top_k, e->r_idx, (size_t)R * sizeof(int32_t),
@@ -432,9 +480,19 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
 
 extern "C" {
 
-int32_t eb_engine_create(const eb_config* cfg, eb_engine** out) {
+int32_t eb_engine_create(const eb_config* cfg, eb_engine** out) { return eb_engine_create_tp(cfg, 0, 1, nullptr, out); }
+
+int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_size, eb_comm* comm, eb_engine** out) {
   EB_REQUIRE(out, EB_ERR_ARG, "eb_engine_create: null out");
   EB_TRY(validate(cfg));
+  EB_REQUIRE(tp_size >= 1 && tp_rank >= 0 && tp_rank < tp_size, EB_ERR_ARG, "eb_engine_create_tp: rank %d of %d", tp_rank, tp_size);
+  EB_REQUIRE(tp_size == 1 || comm, EB_ERR_ARG, "eb_engine_create_tp: %d ranks need a communicator", tp_size);
+  EB_REQUIRE(cfg->n_kv_heads % tp_size == 0 && cfg->n_experts % tp_size == 0, EB_ERR_UNSUPPORTED,
+             "eb_engine_create_tp: %d KV heads / %d experts do not divide over %d ranks", cfg->n_kv_heads, cfg->n_experts, tp_size);
+  EB_REQUIRE(tp_size == 1 || cfg->n_q_heads == 8 * cfg->n_kv_heads, EB_ERR_UNSUPPORTED,
+             "eb_engine_create_tp: tensor parallelism is built for groups of 8 query heads per KV head");
+  EB_REQUIRE(tp_size == 1 || ((cfg->n_q_heads / tp_size) * cfg->head_dim) % 128 == 0, EB_ERR_UNSUPPORTED,
+             "eb_engine_create_tp: the query heads of a rank must fill whole 128-row scale blocks");
   eb_engine* e = new (std::nothrow) eb_engine;
   EB_REQUIRE(e, EB_ERR_NOMEM, "eb_engine_create: host allocation failed");
   e->c = *cfg;
@@ -453,8 +511,25 @@ int32_t eb_engine_create(const eb_config* cfg, eb_engine** out) {
                     prop.minor);
   }
   e->sm_count = prop.multiProcessorCount;
-  e->hqd = c.n_q_heads * c.head_dim;
-  e->nqkv = (c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim;
+  e->tp_rank = tp_rank;
+  e->tp_size = tp_size;
+  e->comm = comm;
+  e->hq_l = c.n_q_heads / tp_size;
+  e->hkv_l = c.n_kv_heads / tp_size;
+  e->e_l = c.n_experts / tp_size;
+  e->e0 = tp_rank * e->e_l;
+  e->hqd = e->hq_l * c.head_dim;
+  if (tp_size == 1) {
+    e->kv_band = e->hkv_l * c.head_dim;  // the fused [q | k | v] row as it is
+    e->k_col0 = e->hqd;
+    e->v_col0 = e->hqd + e->kv_band;
+  } else {
+    e->kv_band = (int)eb::cdiv(e->hkv_l * c.head_dim, 128) * 128;
+    const int koff = (tp_rank * e->hkv_l * c.head_dim) % 128;  // this rank's heads inside a shared 128-row block
+    e->k_col0 = e->hqd + koff;
+    e->v_col0 = e->hqd + e->kv_band + koff;
+  }
+  e->nqkv = e->hqd + 2 * e->kv_band;
   e->kbH = (int)eb::cdiv(c.hidden, 128);
   e->kbI = (int)eb::cdiv(c.inter, 128);
   e->kbA = (int)eb::cdiv(e->hqd, 128);
@@ -469,7 +544,7 @@ int32_t eb_engine_create(const eb_config* cfg, eb_engine** out) {
     }
     if ((rc = eb_sched_create(c.num_pages, c.page_size, c.max_seqs, c.max_pages_per_seq, c.seed, &e->sched)) != EB_OK) break;
     if ((rc = init_weights(e)) != EB_OK) break;
-    const size_t cache_elems = (size_t)c.num_pages * 2 * c.n_kv_heads * c.page_size * c.head_dim;
+    const size_t cache_elems = (size_t)c.num_pages * 2 * e->hkv_l * c.page_size * c.head_dim;
     for (int l = 0; l < c.n_layers && rc == EB_OK; ++l) {
       rc = dev_alloc(e, &e->layers[(size_t)l].cache, cache_elems, &e->kv_bytes);
       if (rc == EB_OK && cudaMemsetAsync(e->layers[(size_t)l].cache, 0, cache_elems * 2, e->stream) != cudaSuccess)
@@ -513,9 +588,9 @@ int32_t eb_engine_memory(const eb_engine* e, int64_t* weight_bytes, int64_t* kv_
 int32_t eb_engine_kv_fill_synth(eb_engine* e) {
   EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_kv_fill_synth: null engine");
   const eb_config& c = e->c;
-  const int64_t n = (int64_t)c.num_pages * 2 * c.n_kv_heads * c.page_size * c.head_dim;
   for (int l = 0; l < c.n_layers; ++l)
-    EB_TRY(eb_synth_normal_bf16(e->layers[(size_t)l].cache, n, c.seed, 20000 + (uint64_t)l, 0, 1.0f, e->stream));
+    EB_TRY(eb_synth_kv_heads_bf16(e->layers[(size_t)l].cache, c.num_pages, c.n_kv_heads, e->tp_rank * e->hkv_l, e->hkv_l,
+                                  c.page_size, c.head_dim, c.seed, 20000 + (uint64_t)l, e->stream));
   EB_CUDA(cudaStreamSynchronize(e->stream));
   return EB_OK;
 }
@@ -629,7 +704,7 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
   // attention plans: [0] full, [1] windowed
   Plan plans[2];
   size_t items_off[2], part_off[2];
-  const int ppi = 8 / c.n_kv_heads;
+  const int ppi = 8 / e->hkv_l;
   for (int k = 0; k < 2; ++k) {
     if (k == 1 && c.window == 0) {
       items_off[1] = items_off[0];

@@ -263,13 +263,13 @@ __device__ __forceinline__ float round_bf16(float v) { return __uint_as_float(pa
 __global__ void qkv_rope_append_kernel(const float* part, int splits, uint16_t* qkv, int T, int n_q, int n_kv, int head_dim,
                                        const int32_t* positions, const float* cos_t, const float* sin_t, int max_pos,
                                        uint16_t* cache, int num_pages, int page_size, const int32_t* block_tables,
-                                       int bt_stride, const int32_t* tok_slot, int32_t* status) {
+                                       int bt_stride, const int32_t* tok_slot, int32_t* status, int N, int k_col0,
+                                       int v_col0) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
   const int half = head_dim >> 1;
   const int groups = half >> 3;  // threads per head
   const int n_heads = n_q + 2 * n_kv;
-  const int N = n_heads * head_dim;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (int64_t)T * n_heads * groups) return;
   const int i = (int)(idx % groups) * 8;
@@ -280,7 +280,10 @@ __global__ void qkv_rope_append_kernel(const float* part, int splits, uint16_t* 
     atomicOr(status, EB_DEV_BAD_INDEX);
     return;
   }
-  const int64_t e0 = (int64_t)t * N + (int64_t)h * head_dim + i;
+  // column of this head in the row: q heads first, then the K band and the V band (under tensor parallelism a band
+  // may start before this rank's first head, when 128-row scale blocks of the weight straddle ranks)
+  const int col = h < n_q ? h * head_dim : h < n_q + n_kv ? k_col0 + (h - n_q) * head_dim : v_col0 + (h - n_q - n_kv) * head_dim;
+  const int64_t e0 = (int64_t)t * N + col + i;
   float a[8], b[8];
   if (splits > 1) {
 #pragma unroll
@@ -365,7 +368,7 @@ row_residual_rmsnorm_kernel(const float* part, int splits, const uint16_t* o_bf1
     const int64_t e = (int64_t)t * H + ch * 8;
     float v[8];
     if (MODE == 0) {
-      if (splits > 1) {
+      if (part) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[k] = 0.f;
         const int64_t plane = (int64_t)T * H;
@@ -454,7 +457,8 @@ int32_t eb_qkv_rope_append(const float* d_part, int32_t splits, void* d_qkv, int
   const int64_t n = (int64_t)T * (n_q + 2 * n_kv) * (head_dim / 16);
   EB_CUDA(eb::launch(qkv_rope_append_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream), 
       d_part, splits, (uint16_t*)d_qkv, T, n_q, n_kv, head_dim, d_positions, d_cos, d_sin, max_pos, (uint16_t*)d_cache,
-      num_pages, page_size, d_block_tables, bt_stride, d_tok_slot, status));
+      num_pages, page_size, d_block_tables, bt_stride, d_tok_slot, status, (n_q + 2 * n_kv) * head_dim, n_q * head_dim,
+      (n_q + n_kv) * head_dim));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -462,10 +466,11 @@ int32_t eb_qkv_rope_append(const float* d_part, int32_t splits, void* d_qkv, int
 int32_t eb_oproj_residual_rmsnorm(const float* d_part, int32_t splits, const void* d_o_bf16, void* d_x, const float* d_g,
                                   int32_t T, int32_t H, float eps, void* d_h, void* stream) {
   EB_REQUIRE(d_x && d_g && d_h, EB_ERR_ARG, "eb_oproj_residual_rmsnorm: null pointer");
-  EB_REQUIRE(splits >= 1 && ((splits > 1 && d_part) || (splits == 1 && d_o_bf16)), EB_ERR_ARG,
+  EB_REQUIRE(splits >= 1 && (d_part || (splits == 1 && d_o_bf16)), EB_ERR_ARG,
              "eb_oproj_residual_rmsnorm: splits %d without its input", splits);
   EB_REQUIRE(T >= 0 && H >= 8 && H % 8 == 0 && H <= 4096, EB_ERR_UNSUPPORTED, "eb_oproj_residual_rmsnorm: H %d (multiple of 8, <= 4096)", H);
   if (T == 0) return EB_OK;
+  if (splits > 1 && !d_part) return eb::fail(EB_ERR_ARG, "eb_oproj_residual_rmsnorm: partials missing");
   EB_CUDA(eb::launch(row_residual_rmsnorm_kernel<0>, dim3(T), dim3(256), 0, eb::as_stream(stream), d_part, splits, (const uint16_t*)d_o_bf16, nullptr,
                                                                        nullptr, nullptr, 0, 0, (uint16_t*)d_x, d_g, T, H, eps,
                                                                        (uint16_t*)d_h));
@@ -482,6 +487,80 @@ int32_t eb_moe_combine_rmsnorm(const void* d_y, const int32_t* d_perm_row, const
                                                                        d_wts, top_k, (int64_t)T * top_k, (uint16_t*)d_x, d_g, T,
                                                                        H, eps, (uint16_t*)d_h));
   EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-/expert-parallel helpers: fp32 buffers that an all-reduce sums across ranks.
+
+namespace {
+
+__global__ void sum_planes_kernel(const float4* part, int splits, int64_t n4, float4* out) {
+  eb::pdl_wait();
+  eb::pdl_trigger();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 a = part[i];
+  for (int s = 1; s < splits; ++s) {
+    const float4 b = part[(int64_t)s * n4 + i];
+    a.x += b.x;
+    a.y += b.y;
+    a.z += b.z;
+    a.w += b.w;
+  }
+  out[i] = a;
+}
+
+__global__ void bf16_to_f32_kernel(const uint16_t* in, int64_t n, float* out) {
+  eb::pdl_wait();
+  eb::pdl_trigger();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __uint_as_float((uint32_t)in[i] << 16);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t eb_qkv_rope_append_ex(const float* d_part, int32_t splits, void* d_qkv, int32_t row_elems, int32_t k_col0,
+                              int32_t v_col0, int32_t T, int32_t n_q, int32_t n_kv, int32_t head_dim,
+                              const int32_t* d_positions, const float* d_cos, const float* d_sin, int32_t max_pos,
+                              void* d_cache, int32_t num_pages, int32_t page_size, const int32_t* d_block_tables,
+                              int32_t bt_stride, const int32_t* d_tok_slot, void* stream) {
+  EB_REQUIRE(d_qkv && d_positions && d_cos && d_sin && d_cache && d_block_tables && d_tok_slot, EB_ERR_ARG,
+             "eb_qkv_rope_append_ex: null pointer");
+  EB_REQUIRE(splits >= 1 && (splits == 1 || d_part), EB_ERR_ARG, "eb_qkv_rope_append_ex: splits %d without partials", splits);
+  EB_REQUIRE(T >= 0 && n_q >= 1 && n_kv >= 1 && head_dim >= 16 && head_dim % 16 == 0 && max_pos >= 1 && num_pages >= 1 &&
+                 page_size >= 1 && bt_stride >= 1,
+             EB_ERR_ARG, "eb_qkv_rope_append_ex: bad size (head_dim must be a multiple of 16)");
+  EB_REQUIRE(k_col0 >= n_q * head_dim && v_col0 >= k_col0 + n_kv * head_dim && v_col0 + n_kv * head_dim <= row_elems &&
+                 k_col0 % 8 == 0 && v_col0 % 8 == 0 && row_elems % 8 == 0,
+             EB_ERR_ARG, "eb_qkv_rope_append_ex: K/V bands at %d/%d do not fit a row of %d", k_col0, v_col0, row_elems);
+  EB_REQUIRE(((uintptr_t)d_qkv % 16 == 0) && ((uintptr_t)d_cache % 16 == 0) && ((uintptr_t)d_cos % 16 == 0) &&
+                 ((uintptr_t)d_sin % 16 == 0) && ((uintptr_t)d_part % 16 == 0),
+             EB_ERR_ARG, "eb_qkv_rope_append_ex: 16-byte alignment");
+  if (T == 0) return EB_OK;
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_qkv_rope_append_ex: no device");
+  const int64_t n = (int64_t)T * (n_q + 2 * n_kv) * (head_dim / 16);
+  EB_CUDA(eb::launch(qkv_rope_append_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream), d_part,
+                     splits, (uint16_t*)d_qkv, T, n_q, n_kv, head_dim, d_positions, d_cos, d_sin, max_pos, (uint16_t*)d_cache,
+                     num_pages, page_size, d_block_tables, bt_stride, d_tok_slot, status, row_elems, k_col0, v_col0));
+  return EB_OK;
+}
+
+int32_t eb_sum_planes_f32(const float* d_part, int32_t splits, const void* d_bf16, int64_t n, float* d_out, void* stream) {
+  EB_REQUIRE(d_out && n >= 0 && n % 4 == 0 && splits >= 1 && (d_part || (splits == 1 && d_bf16)), EB_ERR_ARG,
+             "eb_sum_planes_f32: bad argument");
+  if (n == 0) return EB_OK;
+  if (d_part)
+    EB_CUDA(eb::launch(sum_planes_kernel, dim3((unsigned)eb::cdiv(n / 4, 256)), dim3(256), 0, eb::as_stream(stream),
+                       (const float4*)d_part, splits, n / 4, (float4*)d_out));
+  else
+    EB_CUDA(eb::launch(bf16_to_f32_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream),
+                       (const uint16_t*)d_bf16, n, d_out));
   return EB_OK;
 }
 

@@ -141,7 +141,7 @@ router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, i
 //   row_token[r]  : token whose activations permuted row r carries
 __global__ void __launch_bounds__(1024)
 moe_permute_kernel(const int32_t* idx, int n_slots, int top_k, int E, int32_t* seg_off, int32_t* perm_row,
-                   int32_t* row_token, int tn, int max_tiles, int32_t* tile_ws, int32_t* status) {
+                   int32_t* row_token, int tn, int max_tiles, int32_t* tile_ws, int32_t* status, int skip_foreign) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
   __shared__ int32_t base[kMaxExperts + 1];   // running start of each expert's unplaced slots
@@ -152,6 +152,7 @@ moe_permute_kernel(const int32_t* idx, int n_slots, int top_k, int E, int32_t* s
   for (int i = tid; i < n_slots; i += 1024) {
     int e = idx[i];
     if (e < 0 || e >= E) {
+      if (skip_foreign) continue;  // expert parallel: the slot belongs to another rank's expert
       atomicOr(status, EB_DEV_BAD_INDEX);
       e = 0;
     }
@@ -201,9 +202,18 @@ moe_permute_kernel(const int32_t* idx, int n_slots, int top_k, int E, int32_t* s
     for (int k = tid; k < 32 * E; k += 1024) wcnt[k / E][k % E] = 0;
     __syncthreads();
     const int i = i0 + tid;
-    const bool on = i < n_slots;
-    int e = on ? idx[i] : -1;
-    if (on && (e < 0 || e >= E)) e = 0;
+    const bool on0 = i < n_slots;
+    int e = on0 ? idx[i] : -1;
+    bool on = on0;
+    if (on && (e < 0 || e >= E)) {
+      if (skip_foreign) {
+        on = false;
+        e = -1;
+        perm_row[i] = -1;
+      } else {
+        e = 0;
+      }
+    }
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const int rank = __popc(peers & ((1u << lane) - 1u));
     if (on && rank == 0) wcnt[warp][e] = __popc(peers);
@@ -327,14 +337,24 @@ int32_t eb_moe_permute(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_moe_permute: no device");
   EB_CUDA(eb::launch(moe_permute_kernel, dim3(1), dim3(1024), 0, eb::as_stream(stream), d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
-                                                             d_row_token, 0, 0, nullptr, status));
+                                                             d_row_token, 0, 0, nullptr, status, 0));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
 
+static int32_t permute_tiles(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E, int32_t* d_seg_off,
+                             int32_t* d_perm_row, int32_t* d_row_token, int32_t tile_tokens, void* d_group_work,
+                             void* stream, int skip_foreign);
+
 int32_t eb_moe_permute_tiles(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E, int32_t* d_seg_off,
                              int32_t* d_perm_row, int32_t* d_row_token, int32_t tile_tokens, void* d_group_work,
                              void* stream) {
+  return permute_tiles(d_idx, T, top_k, E, d_seg_off, d_perm_row, d_row_token, tile_tokens, d_group_work, stream, 0);
+}
+
+static int32_t permute_tiles(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E, int32_t* d_seg_off,
+                             int32_t* d_perm_row, int32_t* d_row_token, int32_t tile_tokens, void* d_group_work,
+                             void* stream, int skip_foreign) {
   EB_REQUIRE(d_idx && d_seg_off && d_perm_row && d_row_token && d_group_work, EB_ERR_ARG, "eb_moe_permute_tiles: null pointer");
   EB_REQUIRE(T >= 0 && top_k >= 1 && E >= 1 && E <= kMaxExperts, EB_ERR_UNSUPPORTED, "eb_moe_permute_tiles: E %d (<= %d)",
              E, kMaxExperts);
@@ -344,7 +364,7 @@ int32_t eb_moe_permute_tiles(const int32_t* d_idx, int32_t T, int32_t top_k, int
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_moe_permute_tiles: no device");
   const int max_tiles = (T * top_k) / tile_tokens + E;
   EB_CUDA(eb::launch(moe_permute_kernel, dim3(1), dim3(1024), 0, eb::as_stream(stream), d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
-                                                             d_row_token, tile_tokens, max_tiles, (int32_t*)d_group_work, status));
+                                                             d_row_token, tile_tokens, max_tiles, (int32_t*)d_group_work, status, skip_foreign));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -359,6 +379,80 @@ int32_t eb_moe_combine(const void* d_y, const int32_t* d_perm_row, const float* 
   EB_CUDA(eb::launch(moe_combine_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream), 
       (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, (uint16_t*)d_x, (int64_t)T * top_k));
   EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Expert parallelism: a rank owns experts [e0, e0 + E_local).  Routing is replicated (every rank sees the same
+// activations after the tensor-parallel all-reduce), so no index exchange is needed: each rank keeps the slots of
+// its own experts, and the per-rank partial mixes are summed by an all-reduce.
+
+namespace {
+
+__global__ void localize_experts_kernel(const int32_t* idx, int n, int e0, int e_local, int32_t* out) {
+  eb::pdl_wait();
+  eb::pdl_trigger();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int e = idx[i] - e0;
+  out[i] = (e >= 0 && e < e_local) ? e : -1;
+}
+
+// out[t] = sum over this rank's slots j of w[t][j] * y[perm_row[t][j]]  (fp32, slots in ascending j)
+__global__ void moe_combine_f32_kernel(const uint16_t* y, const int32_t* perm_row, const float* wts, int T, int top_k, int H,
+                                       float* out, int64_t n_rows) {
+  eb::pdl_wait();
+  eb::pdl_trigger();
+  const int h8 = H >> 3;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)T * h8) return;
+  const int t = (int)(idx / h8), c = (int)(idx % h8) * 8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int j = 0; j < top_k; ++j) {
+    const int r = perm_row[(int64_t)t * top_k + j];
+    if (r < 0 || r >= n_rows) continue;
+    const float w = wts[(int64_t)t * top_k + j];
+    const uint4 v = *reinterpret_cast<const uint4*>(y + (int64_t)r * H + c);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      acc[2 * k] = __fmaf_rn(w, __uint_as_float(u[k] << 16), acc[2 * k]);
+      acc[2 * k + 1] = __fmaf_rn(w, __uint_as_float(u[k] & 0xFFFF0000u), acc[2 * k + 1]);
+    }
+  }
+  float4* o = reinterpret_cast<float4*>(out + (int64_t)t * H + c);
+  o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t eb_moe_localize(const int32_t* d_idx, int32_t n, int32_t e0, int32_t e_local, int32_t* d_out, void* stream) {
+  EB_REQUIRE(d_idx && d_out && n >= 0 && e0 >= 0 && e_local >= 1, EB_ERR_ARG, "eb_moe_localize: bad argument");
+  if (n == 0) return EB_OK;
+  EB_CUDA(eb::launch(localize_experts_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream), d_idx, n, e0,
+                     e_local, d_out));
+  return EB_OK;
+}
+
+int32_t eb_moe_permute_tiles_local(const int32_t* d_idx_local, int32_t T, int32_t top_k, int32_t e_local, int32_t* d_seg_off,
+                                   int32_t* d_perm_row, int32_t* d_row_token, int32_t tile_tokens, void* d_group_work,
+                                   void* stream) {
+  return permute_tiles(d_idx_local, T, top_k, e_local, d_seg_off, d_perm_row, d_row_token, tile_tokens, d_group_work, stream, 1);
+}
+
+int32_t eb_moe_combine_f32(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k, int32_t H,
+                           float* d_out, void* stream) {
+  EB_REQUIRE(d_y && d_perm_row && d_wts && d_out, EB_ERR_ARG, "eb_moe_combine_f32: null pointer");
+  EB_REQUIRE(T >= 0 && top_k >= 1 && H >= 8 && H % 8 == 0, EB_ERR_ARG, "eb_moe_combine_f32: H %d must be a multiple of 8", H);
+  if (T == 0) return EB_OK;
+  const int64_t n = (int64_t)T * (H / 8);
+  EB_CUDA(eb::launch(moe_combine_f32_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream),
+                     (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, d_out, (int64_t)T * top_k));
   return EB_OK;
 }
 

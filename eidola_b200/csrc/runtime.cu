@@ -208,8 +208,9 @@ __global__ void synth_kernel(void* out, int64_t n, uint64_t seed, uint64_t sid, 
 
 // One CTA per 128x128 block: generate, block amax, scale, quantise.  256 threads, thread t owns column
 // pair-of-bytes positions; values are regenerated for the second pass instead of being held.
+// `cols` columns starting at col0 of a tensor with cols_total columns; element index = row * cols_total + column.
 __global__ void synth_weight_fp8_kernel(uint8_t* codes, float* scales, int64_t cols, int64_t row0, int64_t nrows,
-                                        uint64_t seed, uint64_t sid, float std) {
+                                        uint64_t seed, uint64_t sid, float std, int64_t cols_total, int64_t col0) {
   const int64_t cb = (cols + 127) / 128;
   const int64_t br = blockIdx.x / cb, bc = blockIdx.x % cb;
   const int64_t r_lo = br * 128, c_lo = bc * 128;
@@ -218,7 +219,7 @@ __global__ void synth_weight_fp8_kernel(uint8_t* codes, float* scales, int64_t c
   float amax = 0.f;
   for (int e = threadIdx.x; e < r_n * c_n; e += blockDim.x) {
     const int r = e / c_n, c = e % c_n;
-    const float v = __fmul_rn(eb_normal(seed, sid, (uint64_t)((row0 + r_lo + r) * cols + c_lo + c)), std);
+    const float v = __fmul_rn(eb_normal(seed, sid, (uint64_t)((row0 + r_lo + r) * cols_total + col0 + c_lo + c)), std);
     amax = fmaxf(amax, fabsf(v));
   }
   for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -230,8 +231,23 @@ __global__ void synth_weight_fp8_kernel(uint8_t* codes, float* scales, int64_t c
   if (threadIdx.x == 0) scales[br * cb + bc] = s;
   for (int e = threadIdx.x; e < r_n * c_n; e += blockDim.x) {
     const int r = e / c_n, c = e % c_n;
-    const float v = __fmul_rn(eb_normal(seed, sid, (uint64_t)((row0 + r_lo + r) * cols + c_lo + c)), std);
+    const float v = __fmul_rn(eb_normal(seed, sid, (uint64_t)((row0 + r_lo + r) * cols_total + col0 + c_lo + c)), std);
     codes[(r_lo + r) * cols + c_lo + c] = eb_f32_to_e4m3(__fdiv_rn(v, s));
+  }
+}
+
+// Local KV heads [head0, head0 + n_local) of a cache whose global layout is [pages][2][n_total][page][dim]:
+// element i of the local cache takes the value of its global index, so every rank fills the same global tensor.
+__global__ void synth_kv_heads_kernel(uint16_t* out, int64_t n, int n_total, int head0, int n_local, int head_elems,
+                                      uint64_t seed, uint64_t sid) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) {
+    const int64_t e = i % head_elems;
+    const int64_t h = (i / head_elems) % n_local;
+    const int64_t pk = i / ((int64_t)head_elems * n_local);  // page * 2 + (K or V)
+    const uint64_t g = (uint64_t)((pk * n_total + head0 + h) * head_elems + e);
+    out[i] = eb_f32_to_bf16(eb_normal(seed, sid, g));
   }
 }
 
@@ -285,7 +301,37 @@ int32_t eb_synth_weight_fp8(void* d_codes, void* d_scales, int64_t rows_total, i
   const int64_t blocks = eb::cdiv(nrows, 128) * eb::cdiv(cols, 128);
   EB_REQUIRE(blocks < (1ll << 31), EB_ERR_ARG, "eb_synth_weight_fp8: too many blocks");
   synth_weight_fp8_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>((uint8_t*)d_codes, (float*)d_scales, cols,
-                                                                           row0, nrows, seed, sid, std);
+                                                                           row0, nrows, seed, sid, std, cols, 0);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_synth_weight_fp8_slice(void* d_codes, void* d_scales, int64_t rows_total, int64_t cols_total, int64_t row0,
+                                  int64_t nrows, int64_t col0, int64_t ncols, uint64_t seed, uint64_t sid, float std,
+                                  void* stream) {
+  EB_REQUIRE(d_codes && d_scales, EB_ERR_ARG, "eb_synth_weight_fp8_slice: null");
+  EB_REQUIRE(rows_total > 0 && cols_total > 0 && nrows > 0 && ncols > 0 && row0 >= 0 && col0 >= 0 &&
+                 row0 + nrows <= rows_total && col0 + ncols <= cols_total,
+             EB_ERR_ARG, "eb_synth_weight_fp8_slice: slice outside the tensor");
+  EB_REQUIRE(row0 % 128 == 0 && col0 % 128 == 0, EB_ERR_ARG, "eb_synth_weight_fp8_slice: row0 and col0 must be multiples of 128");
+  const int64_t blocks = eb::cdiv(nrows, 128) * eb::cdiv(ncols, 128);
+  EB_REQUIRE(blocks < (1ll << 31), EB_ERR_ARG, "eb_synth_weight_fp8_slice: too many blocks");
+  synth_weight_fp8_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>((uint8_t*)d_codes, (float*)d_scales, ncols,
+                                                                           row0, nrows, seed, sid, std, cols_total, col0);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_synth_kv_heads_bf16(void* d_cache, int64_t num_pages, int32_t n_kv_total, int32_t head0, int32_t n_kv_local,
+                               int32_t page_size, int32_t head_dim, uint64_t seed, uint64_t sid, void* stream) {
+  EB_REQUIRE(d_cache && num_pages >= 0 && n_kv_total >= 1 && head0 >= 0 && n_kv_local >= 1 &&
+                 head0 + n_kv_local <= n_kv_total && page_size >= 1 && head_dim >= 1,
+             EB_ERR_ARG, "eb_synth_kv_heads_bf16: bad argument");
+  const int64_t n = num_pages * 2 * n_kv_local * page_size * head_dim;
+  if (n == 0) return EB_OK;
+  const int64_t blocks = std::min<int64_t>(eb::cdiv(n, 256), 148 * 32);
+  synth_kv_heads_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>((uint16_t*)d_cache, n, n_kv_total, head0, n_kv_local,
+                                                                         page_size * head_dim, seed, sid);
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

@@ -172,13 +172,41 @@ def gemm_fp8(d_x8, d_sx, d_w8, d_sw, d_y, rows, N, K, *, ldy=None, n_groups=1, d
     call("eb_gemm_fp8_grouped" if d_seg_off is not None else "eb_gemm_fp8_block", C.byref(a), c_vp(stream))
 
 
+class Comm:
+    """eb_comm_*: the NCCL communicator of a tensor-/expert-parallel engine (one process per GPU)."""
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        call("eb_comm_unique_id", buf)
+        return buf.raw
+
+    def __init__(self, unique_id: bytes, rank: int, size: int):
+        assert len(unique_id) == 128
+        self._h = c_vp()
+        self.rank, self.size = rank, size
+        call("eb_comm_create", C.c_char_p(unique_id), c_i32(rank), c_i32(size), C.byref(self._h))
+
+    def allreduce_f32(self, d_buf, count, stream=None) -> None:
+        call("eb_comm_allreduce_f32", self._h, c_vp(d_buf), c_i64(count), c_vp(stream))
+
+    def close(self):
+        if self._h:
+            call("eb_comm_destroy", self._h)
+            self._h = None
+
+
 class Engine:
     """eb_engine_*: weights, KV pages, scheduler and the decode step."""
 
-    def __init__(self, cfg: Config):
+    def __init__(self, cfg: Config, tp_rank: int = 0, tp_size: int = 1, comm: "Comm | None" = None):
         self.cfg = cfg
         self._h = c_vp()
-        call("eb_engine_create", C.byref(cfg), C.byref(self._h))
+        self._comm = comm  # keep the communicator alive as long as the engine
+        if tp_size == 1:
+            call("eb_engine_create", C.byref(cfg), C.byref(self._h))
+        else:
+            call("eb_engine_create_tp", C.byref(cfg), c_i32(tp_rank), c_i32(tp_size), comm._h, C.byref(self._h))
         self._last_T = 0
 
     def close(self):

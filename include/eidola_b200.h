@@ -103,6 +103,16 @@ int32_t eb_synth_uniform_f32(void* d_out, int64_t n, uint64_t seed, uint64_t str
 int32_t eb_synth_weight_fp8(void* d_codes, void* d_scales, int64_t rows_total, int64_t cols, int64_t row0,
                             int64_t nrows, uint64_t seed, uint64_t stream_id, float std, void* stream);
 
+/* The block [row0, +nrows) x [col0, +ncols) of the same tensor (row0 and col0 multiples of 128, so its scale blocks
+ * are the tensor's own): what a tensor-parallel rank holds of a column-sharded weight. */
+int32_t eb_synth_weight_fp8_slice(void* d_codes, void* d_scales, int64_t rows_total, int64_t cols_total, int64_t row0,
+                                  int64_t nrows, int64_t col0, int64_t ncols, uint64_t seed, uint64_t stream_id,
+                                  float std, void* stream);
+/* KV heads [head0, head0+n_kv_local) of a cache filled with N(0,1) values indexed by their position in the global
+ * layout [pages][2][n_kv_total][page_size][head_dim], so every rank holds its slice of one global tensor. */
+int32_t eb_synth_kv_heads_bf16(void* d_cache, int64_t num_pages, int32_t n_kv_total, int32_t head0, int32_t n_kv_local,
+                               int32_t page_size, int32_t head_dim, uint64_t seed, uint64_t stream_id, void* stream);
+
 /* ---- scheduler: continuous batching over a page pool (host only, no CUDA call) ------
  * Nearest reference analogue: the whole-engine admission planner `plan_evictions` /
  * `reserve_engine` (crates/eidola-app-core/src/local_models.rs:441-485, 653-701), which admits
@@ -300,6 +310,25 @@ int32_t eb_qkv_rope_append(const float* d_part, int32_t splits, void* d_qkv, int
                            const int32_t* d_block_tables, int32_t bt_stride, const int32_t* d_tok_slot, void* stream);
 int32_t eb_oproj_residual_rmsnorm(const float* d_part, int32_t splits, const void* d_o_bf16, void* d_x, const float* d_g,
                                   int32_t T, int32_t H, float eps, void* d_h, void* stream);
+/* The same with explicit row geometry: a row of d_qkv has row_elems elements, the K heads start at k_col0 and the V
+ * heads at v_col0 (a tensor-parallel rank whose K/V heads share a 128-row scale block with a neighbour computes the
+ * whole block and uses its part). */
+int32_t eb_qkv_rope_append_ex(const float* d_part, int32_t splits, void* d_qkv, int32_t row_elems, int32_t k_col0,
+                              int32_t v_col0, int32_t T, int32_t n_q, int32_t n_kv, int32_t head_dim,
+                              const int32_t* d_positions, const float* d_cos, const float* d_sin, int32_t max_pos,
+                              void* d_cache, int32_t num_pages, int32_t page_size, const int32_t* d_block_tables,
+                              int32_t bt_stride, const int32_t* d_tok_slot, void* stream);
+/* d_out[i] = sum over splits of d_part[s][i] (fp32), or the fp32 image of d_bf16 when d_part is NULL: the buffer an
+ * all-reduce sums across ranks. */
+int32_t eb_sum_planes_f32(const float* d_part, int32_t splits, const void* d_bf16, int64_t n, float* d_out, void* stream);
+/* Expert parallelism: d_out[i] = d_idx[i] - e0 when that is one of this rank's e_local experts, else -1;
+ * the permutation that skips the -1 slots (perm_row = -1); the fp32 partial mix of this rank's experts. */
+int32_t eb_moe_localize(const int32_t* d_idx, int32_t n, int32_t e0, int32_t e_local, int32_t* d_out, void* stream);
+int32_t eb_moe_permute_tiles_local(const int32_t* d_idx_local, int32_t T, int32_t top_k, int32_t e_local, int32_t* d_seg_off,
+                                   int32_t* d_perm_row, int32_t* d_row_token, int32_t tile_tokens, void* d_group_work,
+                                   void* stream);
+int32_t eb_moe_combine_f32(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k, int32_t H,
+                           float* d_out, void* stream);
 /* x = bf16(x + bf16(sum_j w_j y[perm_row])) as eb_moe_combine, then h = rmsnorm(x) * g for the next consumer. */
 int32_t eb_moe_combine_rmsnorm(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
                                int32_t H, void* d_x, const float* d_g, float eps, void* d_h, void* stream);
@@ -328,7 +357,26 @@ typedef struct eb_config {
 
 typedef struct eb_engine eb_engine;
 
+/* ---- communicator (NCCL, bound at run time with dlopen) ---------------------------------------
+ * Rank 0 makes a 128-byte id, hands it to the other ranks by any channel, every rank (its device current) creates. */
+typedef struct eb_comm eb_comm;
+int32_t eb_comm_unique_id(void* h_id128);
+int32_t eb_comm_create(const void* h_id128, int32_t rank, int32_t size, eb_comm** out);
+int32_t eb_comm_destroy(eb_comm* c);
+int32_t eb_comm_info(const eb_comm* c, int32_t* rank, int32_t* size);
+int32_t eb_comm_allreduce_f32(eb_comm* c, void* d_buf, int64_t count, void* stream);
+/* 0 = healthy.  A host whose step does not return within its own deadline, or that reads a non-zero value, aborts
+ * the communicator and rebuilds it (failure handling stays on the host; kernels never wait on a peer). */
+int32_t eb_comm_async_error(eb_comm* c, int32_t* err);
+int32_t eb_comm_abort(eb_comm* c);
+
 int32_t eb_engine_create(const eb_config* cfg, eb_engine** out);
+/* Tensor-parallel heads + expert-parallel experts over tp_size ranks (one process per GPU): rank r holds query heads
+ * [r*n_q/tp, ...), KV heads [r*n_kv/tp, ...) with their slice of every KV page, and experts [r*E/tp, ...); the
+ * router, embeddings and LM head are replicated, and every rank is given the same steps and returns the same
+ * tokens.  Two fp32 all-reduces of [tokens, hidden] per layer (after the O projection and after the experts)
+ * run on `comm`.  The model is the same tensor for every tp_size (weights are slices of the single-GPU tensors). */
+int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_size, eb_comm* comm, eb_engine** out);
 int32_t eb_engine_destroy(eb_engine* e);
 /* Device bytes held by weights, KV pages and workspaces. */
 int32_t eb_engine_memory(const eb_engine* e, int64_t* weight_bytes, int64_t* kv_bytes, int64_t* work_bytes);

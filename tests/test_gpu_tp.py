@@ -1,0 +1,94 @@
+"""GPU (needs two devices): tensor-parallel heads + expert-parallel experts over NCCL against the single-GPU engine
+and the CPU oracle.  One process per GPU, started here as children; skipped on a box with one GPU."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import binding as orc
+from oracle import sched as osched
+from tests.decoder_cases import compare_forced_step, free_running_error
+from tests.tp_worker import CONTEXTS, run_steps, tp_config
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _spawn(world, name, tmp_path, force_file=None):
+    import uuid
+    id_file = str(tmp_path / f"nccl_id_{uuid.uuid4().hex}")
+    procs, outs = [], []
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    for r in range(world):
+        out = str(tmp_path / f"rank{r}.npz")
+        outs.append(out)
+        cmd = [sys.executable, str(ROOT / "tests" / "tp_worker.py"), str(r), str(world), id_file, out, name]
+        if force_file:
+            cmd.append(force_file)
+        procs.append(subprocess.Popen(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    logs = []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        logs.append(o)
+    for r, p in enumerate(procs):
+        assert p.returncode == 0, f"rank {r} failed:\n{logs[r][-3000:]}"
+    return [np.load(o) for o in outs]
+
+
+def _oracle_steps(name):
+    cfg = tp_config(name)
+    model = orc.Model(cfg)
+    model.kv_fill_synth()
+    sch = osched.Sched(cfg.num_pages, cfg.page_size, cfg.max_seqs, cfg.max_pages_per_seq, cfg.seed)
+    ctx = CONTEXTS[name]
+    slots = [sch.admit(L) for L in ctx]
+    rng = np.random.default_rng(0)
+    refs = []
+    for q_lens in ([1] * len(ctx), [(i % 5) + 1 for i in range(len(ctx))]):
+        T = sum(q_lens)
+        toks = rng.integers(0, cfg.vocab, size=T).astype(np.int32)
+        for s, q in zip(slots, q_lens):
+            sch.extend(s, sch.len[s] + q)
+        p = sch.pack(slots, q_lens)
+        p.update(slots=slots, n_tokens=T)
+        refs.append(model.step(p, toks, np.array(sch.tables, np.int32), want_debug=True))
+    return cfg, refs
+
+
+@pytest.mark.parametrize("name", ["tp_small", "tp_mid"])
+def test_two_rank_engine_matches_oracle_and_single_gpu(gpu, tmp_path, name):
+    import eidola_b200 as eb
+    if eb.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cfg, refs = _oracle_steps(name)
+    force_file = str(tmp_path / "force.npz")
+    np.savez(force_file, **{f"s{s}_l{l}": refs[s]["hidden"][l] for s in range(2) for l in range(cfg.n_layers + 1)})
+    # (1) teacher-forced against the oracle, layer by layer
+    ranks = _spawn(2, name, tmp_path, force_file)
+    for s in range(2):
+        got = [{k: r[f"s{s}_{k}"] for k in ("next", "margin", "logits", "route_idx", "hidden")} for r in ranks]
+        assert np.array_equal(got[0]["logits"], got[1]["logits"]) and np.array_equal(got[0]["next"], got[1]["next"])
+        assert np.array_equal(got[0]["hidden"], got[1]["hidden"])  # ranks stay in lockstep bit for bit
+        g = dict(got[0], route_idx=list(got[0]["route_idx"]), hidden=list(got[0]["hidden"]))
+        wh, wl = compare_forced_step(g, refs[s], cfg, what=f"{name} tp=2 step {s}")
+        print(f"{name} tp=2 step {s}: forced hidden err {wh:.4f} logits err {wl:.4f}")
+    assert all(int(r["status"][0]) == 0 for r in ranks)
+    # (2) free-running against the single-GPU engine on the same steps
+    ranks = _spawn(2, name, tmp_path)
+    eng = eb.Engine(cfg)
+    eng.kv_fill_synth()
+    _, single = run_steps(eng, name)
+    for s in range(2):
+        got = {k: ranks[0][f"s{s}_{k}"] for k in ("logits", "hidden")}
+        dl, rel = free_running_error({"logits": got["logits"], "hidden": list(got["hidden"])},
+                                     {"logits": single[s]["logits"], "hidden": list(single[s]["hidden"])})
+        print(f"{name} tp=2 vs single GPU step {s}: logits err {dl.max():.4f} hidden rel {rel:.4f}")
+        assert rel <= 0.15
