@@ -64,13 +64,14 @@ class Config(C.Structure):
         ("rope_theta", c_f32), ("rms_eps", c_f32), ("init_std", c_f32),
         ("seed", c_u64),
         ("debug", c_i32),
+        ("window_ring", c_i32),
     ]
 
 
 def make_config(**kw) -> "Config":
     """eb_config with the defaults of the benchmark family (head_dim 64, page 16, window 128, top-4, std 0.02)."""
     d = dict(head_dim=64, window=128, top_k=4, page_size=16, max_q_len=1, rope_theta=150000.0, rms_eps=1e-5,
-             init_std=0.02, seed=0, debug=0)
+             init_std=0.02, seed=0, debug=0, window_ring=0)
     d.update(kw)
     c = Config()
     for k, v in d.items():

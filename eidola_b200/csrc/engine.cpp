@@ -69,6 +69,8 @@ struct eb_engine {
   eb_sched* sched = nullptr;
   std::vector<int32_t> uploaded_pages;  // block-table entries of each slot already on the device
   int32_t* d_bt = nullptr;
+  int32_t* d_bt_ring = nullptr;  // window_ring: [max_seqs][max_pages_per_seq], logical page p -> slot*ring + p % ring
+  int ring = 0;
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::vector<void*> allocs;
@@ -115,6 +117,12 @@ namespace {
     int32_t _rc = (expr);       \
     if (_rc != EB_OK) return _rc; \
   } while (0)
+
+// Pages of layer l's cache: sliding-window layers keep a ring per sequence when the engine was asked to.
+inline bool layer_windowed(const eb_engine* e, int l) { return l % 2 == 0 && e->c.window > 0; }
+inline int32_t layer_pages(const eb_engine* e, int l) {
+  return (e->ring && layer_windowed(e, l)) ? e->c.max_seqs * e->ring : e->c.num_pages;
+}
 
 template <typename T>
 int32_t dev_alloc(eb_engine* e, T** p, size_t count, int64_t* tally) {
@@ -371,6 +379,8 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   for (int l = 0; l < c.n_layers; ++l) {
     const Layer& L = e->layers[(size_t)l];
     const int pi = (l % 2 == 0 && c.window > 0) ? 1 : 0;  // plan 1 = windowed
+    const int32_t* bt = (pi && e->ring) ? e->d_bt_ring : e->d_bt;
+    const int32_t n_pages = layer_pages(e, l);
     if ((c.debug & 1) && e->force_rows[(size_t)l] == T) {
       EB_TRY(impose(l));
       EB_TRY(eb_rmsnorm(e->x, L.g_attn, T, H, c.rms_eps, e->h, st));
@@ -382,15 +392,15 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     mark(-1);
     EB_TRY(eb_qkv_rope_append_ex((const float*)e->gemm_ws, splits, e->qkv, e->nqkv, e->k_col0, e->v_col0, T, e->hq_l,
                                  e->hkv_l, c.head_dim, d_positions, e->rope_cos, e->rope_sin, max_pos, L.cache,
-                                 c.num_pages, c.page_size, e->d_bt, c.max_pages_per_seq, d_tok_slot, st));
+                                 n_pages, c.page_size, bt, c.max_pages_per_seq, d_tok_slot, st));
     eb_attn_args a = {};
     a.d_q = e->qkv;
     a.q_stride = e->nqkv;
     a.d_out = e->attn;
     a.out_stride = e->hqd;
     a.d_cache = L.cache;
-    a.num_pages = c.num_pages;
-    a.d_block_tables = e->d_bt;
+    a.num_pages = n_pages;
+    a.d_block_tables = bt;
     a.bt_stride = c.max_pages_per_seq;
     a.d_seq_slots = d_slots;
     a.d_q_off = d_q_off;
@@ -418,7 +428,8 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     EB_TRY(dense(e->a8, e->sa, L.wo, H, e->hqd, e->o, &splits));
     mark(-1);
     if (!tp) {
-      EB_TRY(eb_oproj_residual_rmsnorm((const float*)e->gemm_ws, splits, e->o, e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
+      EB_TRY(eb_oproj_residual_rmsnorm(splits > 1 ? (const float*)e->gemm_ws : nullptr, splits, e->o, e->x, L.g_mlp, T, H,
+                                       c.rms_eps, e->h, st));
     } else {
       // C1: this rank's heads contributed a partial [T, H]; sum the partials of all ranks in fp32, then round once
       EB_TRY(eb_sum_planes_f32(splits > 1 ? (const float*)e->gemm_ws : nullptr, splits, e->o, (int64_t)T * H, e->ar_buf, st));
@@ -544,11 +555,20 @@ int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_si
     }
     if ((rc = eb_sched_create(c.num_pages, c.page_size, c.max_seqs, c.max_pages_per_seq, c.seed, &e->sched)) != EB_OK) break;
     if ((rc = init_weights(e)) != EB_OK) break;
-    const size_t cache_elems = (size_t)c.num_pages * 2 * e->hkv_l * c.page_size * c.head_dim;
+    e->ring = (c.window_ring && c.window > 0) ? (c.window + c.max_q_len + c.page_size - 1) / c.page_size + 1 : 0;
     for (int l = 0; l < c.n_layers && rc == EB_OK; ++l) {
+      const size_t cache_elems = (size_t)layer_pages(e, l) * 2 * e->hkv_l * c.page_size * c.head_dim;
       rc = dev_alloc(e, &e->layers[(size_t)l].cache, cache_elems, &e->kv_bytes);
       if (rc == EB_OK && cudaMemsetAsync(e->layers[(size_t)l].cache, 0, cache_elems * 2, e->stream) != cudaSuccess)
         rc = eb::fail(EB_ERR_NODEVICE, "eb_engine_create: cache memset failed");
+    }
+    if (rc == EB_OK && e->ring) {
+      std::vector<int32_t> t((size_t)c.max_seqs * c.max_pages_per_seq);
+      for (int s_ = 0; s_ < c.max_seqs; ++s_)
+        for (int p_ = 0; p_ < c.max_pages_per_seq; ++p_) t[(size_t)s_ * c.max_pages_per_seq + p_] = s_ * e->ring + p_ % e->ring;
+      rc = dev_alloc(e, &e->d_bt_ring, t.size(), &e->work_bytes);
+      if (rc == EB_OK && cudaMemcpy(e->d_bt_ring, t.data(), t.size() * sizeof(int32_t), cudaMemcpyHostToDevice) != cudaSuccess)
+        rc = eb::fail(EB_ERR_NODEVICE, "eb_engine_create: ring table upload failed");
     }
     if (rc != EB_OK) break;
     if ((rc = init_work(e)) != EB_OK) break;
@@ -589,7 +609,7 @@ int32_t eb_engine_kv_fill_synth(eb_engine* e) {
   EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_kv_fill_synth: null engine");
   const eb_config& c = e->c;
   for (int l = 0; l < c.n_layers; ++l)
-    EB_TRY(eb_synth_kv_heads_bf16(e->layers[(size_t)l].cache, c.num_pages, c.n_kv_heads, e->tp_rank * e->hkv_l, e->hkv_l,
+    EB_TRY(eb_synth_kv_heads_bf16(e->layers[(size_t)l].cache, layer_pages(e, l), c.n_kv_heads, e->tp_rank * e->hkv_l, e->hkv_l,
                                   c.page_size, c.head_dim, c.seed, 20000 + (uint64_t)l, e->stream));
   EB_CUDA(cudaStreamSynchronize(e->stream));
   return EB_OK;

@@ -44,7 +44,7 @@
 extern "C" {
 #endif
 
-#define EB_ABI_VERSION 1
+#define EB_ABI_VERSION 2
 
 /* status codes (negative: host validation) */
 #define EB_OK 0
@@ -353,6 +353,8 @@ typedef struct eb_config {
   uint64_t seed;        /* weights are a pure function of (shape, seed) */
   int32_t debug;        /* bit 0: keep per-layer routing indices / hidden states readable and allow teacher forcing;
                            bit 1: time attention, GEMM and LM-head calls of each step with CUDA events */
+  int32_t window_ring;  /* 1: sliding-window layers keep only a ring of ceil((window + max_q_len)/page_size) + 1 pages
+                           per sequence (logical page p lives in ring page p mod ring) instead of the whole context */
 } eb_config;
 
 typedef struct eb_engine eb_engine;

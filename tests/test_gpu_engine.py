@@ -158,3 +158,33 @@ def test_refused_step_leaves_no_trace(gpu):
         eng.step([a], [1], [cfg.vocab])
     eng.step([a], [1], [5])
     assert eng.seq_len(a) == 41
+
+
+def test_window_ring_is_bit_identical_to_full_pages(gpu):
+    """Sliding-window layers that keep only a ring of pages per sequence produce the same tokens and logits as
+    layers that keep the whole context: 170 decode steps from empty contexts (the ring of 10 pages wraps) and
+    verify steps with rollbacks in between."""
+    import eidola_b200 as eb
+    engines = []
+    for ring in (0, 1):
+        cfg = tiny_config(window_ring=ring, num_pages=96, max_pages_per_seq=24)
+        eng = eb.Engine(cfg)
+        slots = [eng.admit(0) for _ in range(4)]
+        engines.append((eng, slots))
+    toks = np.array([1, 2, 3, 4], np.int32)
+    for step in range(170):
+        outs = []
+        for eng, slots in engines:
+            if step % 23 == 7:  # a verify step with 5 tokens per sequence, then reject three of them
+                nxt, _ = eng.step(slots, [5] * 4, np.repeat(toks, 5))
+                for s in slots:
+                    eng.truncate(s, eng.seq_len(s) - 3)
+                nxt = nxt[4::5]
+            else:
+                nxt, _ = eng.step(slots, [1] * 4, toks)
+            outs.append((nxt.copy(), eng.read_logits()))
+        assert np.array_equal(outs[0][0], outs[1][0]), f"step {step}"
+        assert np.array_equal(outs[0][1], outs[1][1]), f"step {step}"
+        toks = outs[0][0]
+    mem_full, mem_ring = engines[0][0].memory()["kv"], engines[1][0].memory()["kv"]
+    assert mem_ring < mem_full
