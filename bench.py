@@ -11,6 +11,8 @@ decoder (default): the gpt-oss-20b-shaped random-init FP8 decoder -- 24 layers (
     (seed 4 + rank).  Prefill is stood in for by filling the KV pages with seeded N(0,1) values.  One step = one
     new token for every sequence, through eb_engine_step: token ids go in from host memory, greedy tokens come
     back to host memory and are fed to the next step.
+spec120b: the gpt-oss-120b-shaped decoder (36 layers, 128 experts) with tensor-parallel heads and expert-parallel
+    experts over 2, 4 or 8 GPUs (torchrun), verifying k=4 draft tokens per sequence on 512 ragged sequences.
 attn: one layer of paged sink-attention decode on 256 ragged sequences with lognormal(median 2048, sigma 1)
     context lengths clipped to [16, 32768] (seed 1 + rank); the kernel-level benchmark of the attention path.
 
@@ -216,6 +218,73 @@ def decoder_cpu_sample(n_seqs=32, seed=4):
     return n_seqs / t_step, desc, t_full + t_head
 
 
+# ------------------------------------------------------------------------------------------ 120b-shaped TP x EP verify
+
+class Spec120bWorkload:
+    name = ("gpt-oss-120b-shaped random-init FP8 decoder: 36 layers, hidden 2880, 64q/8kv heads d64, 128 experts top-4 "
+            "inter 2880, vocab 201088; heads tensor-parallel, experts expert-parallel; speculative verification of k=4 "
+            "draft tokens (+1 bonus position, q_len 5) per sequence, acceptance Bernoulli(0.7) per draft, 512 ragged "
+            "seqs, context lognormal(median 4096, sigma 1) in [16,131072]")
+
+    def __init__(self, rank, world, dist, total_steps, n_seqs=512, n_layers=36, n_experts=128, profile=False):
+        import eidola_b200 as eb
+        from eidola_b200.capi import make_config
+        self.eb, self.rank, self.world = eb, rank, world
+        seed = 5
+        self.ctx0 = lognormal_lengths(n_seqs, 4096, 1.0, 16, 131072, seed)
+        grow = 5 * total_steps + 16
+        max_pages = int((int(self.ctx0.max()) + grow) // PAGE + 2)
+        cfg = make_config(n_layers=n_layers, hidden=2880, n_q_heads=64, n_kv_heads=8, window=128, n_experts=n_experts,
+                          top_k=4, inter=2880, vocab=201088, num_pages=1, max_seqs=n_seqs, max_pages_per_seq=max_pages,
+                          max_tokens=5 * n_seqs, max_q_len=5, seed=seed, debug=2 if profile else 0, window_ring=1)
+        cfg.num_pages = int(((self.ctx0.astype(np.int64) + grow) // PAGE + 1).sum()) + 64
+        self.cfg = cfg
+        uid = [eb.Comm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        self.comm = eb.Comm(uid[0], rank, world)
+        self.eng = eb.Engine(cfg, rank, world, self.comm)
+        self.eng.kv_fill_synth()
+        self.slots = np.array([self.eng.admit(int(L)) for L in self.ctx0], np.int32)
+        self.lens = self.ctx0.astype(np.int64).copy()
+        self.q_lens = np.full(n_seqs, 5, np.int32)
+        self.rng = np.random.default_rng(seed)       # same stream on every rank: identical drafts and acceptances
+        self.last = self.rng.integers(0, cfg.vocab, size=n_seqs).astype(np.int32)
+        self.mem = self.eng.memory()
+        self.accepted_total = 0
+
+    def step(self):
+        """Verify 4 random draft tokens per sequence; accept a Bernoulli(0.7) prefix, keep the bonus token."""
+        n = len(self.slots)
+        drafts = self.rng.integers(0, self.cfg.vocab, size=(n, 4)).astype(np.int32)
+        toks = np.concatenate([self.last[:, None], drafts], axis=1).reshape(-1)
+        nxt, _ = self.eng.step(self.slots, self.q_lens, toks)
+        ok = self.rng.random((n, 4)) < 0.7
+        a = np.where(ok.all(axis=1), 4, np.argmin(ok, axis=1)).astype(np.int64)   # accepted drafts per sequence
+        self.last = nxt.reshape(n, 5)[np.arange(n), a].astype(np.int32)           # the model's token after the last accepted
+        self.lens = self.lens + a + 1
+        self.eng.truncate_many(self.slots, self.lens)
+        adv = int((a + 1).sum())
+        self.accepted_total += adv
+        return adv
+
+    def step_alg_bytes(self) -> dict:
+        c, G = self.cfg, self.world
+        ctx = self.lens + 5
+        dense = (64 + 16) * 64 * 2880 + 2880 * 4096
+        experts = c.n_experts * 3 * 2880 * 2880
+        weights = c.n_layers * (dense + experts) // G + c.n_layers * c.n_experts * 2880 * 2 + c.vocab * 2880
+        kv_full = (c.n_layers // 2) * int(ctx.sum()) * 2048 // G
+        kv_win = (c.n_layers - c.n_layers // 2) * int(np.minimum(ctx, 128 + 5 + PAGE).sum()) * 2048 // G
+        return {"weights": weights, "kv_full": kv_full, "kv_window": kv_win, "total": weights + kv_full + kv_win,
+                "allreduce_bytes_per_layer": 2 * 5 * len(ctx) * 2880 * 4}
+
+    def config(self) -> dict:
+        return {"workload": self.name, "n_seqs": int(len(self.ctx0)), "n_layers": int(self.cfg.n_layers),
+                "mean_context": float(self.lens.mean()), "device_bytes_per_rank": self.mem,
+                "prefill": "KV pages filled with seeded N(0,1) values (stand-in for prefill)",
+                "parallelism": "tp%d (heads) x ep%d (experts), 2 fp32 all-reduces of [2560, 2880] per layer" % (self.world, self.world)}
+
+
 # ------------------------------------------------------------------------------------------ attention workload
 
 class AttnWorkload:
@@ -302,10 +371,8 @@ def setup_dist():
     world = int(os.environ.get("WORLD_SIZE", 1))
     dist = None
     if world > 1:
-        import torch
-        import torch.distributed as dist  # plumbing only: barrier and max-over-ranks of the timings
-        torch.cuda.set_device(rank_device(rank))
-        dist.init_process_group("nccl", device_id=torch.device("cuda", rank_device(rank)))
+        import torch.distributed as dist  # plumbing only (gloo, host tensors): barrier, max over ranks, NCCL id hand-off
+        dist.init_process_group("gloo")
     return rank, world, dist
 
 
@@ -313,7 +380,7 @@ def reduce_max(dist, values):
     if dist is None:
         return values
     import torch
-    t = torch.tensor(values, device="cuda", dtype=torch.float64)
+    t = torch.tensor(values, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return t.tolist()
 
@@ -416,6 +483,76 @@ def run_decoder(args) -> dict:
         out["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port", "sample": desc}
     if dist is not None:
         dist.destroy_process_group()
+    return out
+
+
+def run_spec120b(args) -> dict:
+    rank, world, dist = setup_dist()
+    if world < 2:
+        return {"metric": "accepted tokens/s, 120b-shaped TP x EP verify", "unavailable":
+                "the 120b-shaped configuration needs at least 2 GPUs (116 GB of weights + KV); launch with torchrun"}
+    import eidola_b200 as eb
+    from eidola_b200 import capi
+    capi.call("eb_device_set", capi.c_i32(rank_device(rank)))
+    K, W = args.steps, args.warmup
+    wl = Spec120bWorkload(rank, world, dist, total_steps=K + W + 2, n_seqs=args.seqs if args.seqs != 256 else 512,
+                          n_layers=args.layers if args.layers != 24 else 36, profile=args.profile)
+    stream = wl.eng.stream()
+
+    def barrier():
+        capi.call("eb_device_sync")
+        dist.barrier()
+
+    sampler = ClockSampler(rank_device(rank))
+    if rank == 0:
+        sampler.start()
+    for _ in range(W):
+        wl.step()
+    barrier()
+    timer = eb.Timer(stream)
+    dev_ms, accepted, launches = 0.0, 0, 0
+    acc = {}
+    barrier()
+    timer.start()
+    for i in range(K):
+        accepted += wl.step()
+        ms, nl = wl.eng.last_step_stats()
+        dev_ms += ms
+        launches += nl
+        if args.profile:
+            for k, v in wl.eng.last_step_breakdown().items():
+                acc[k] = acc.get(k, 0.0) + v / K
+    e2e_ms = timer.stop()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    status = eb.status_read()
+    dev_ms, e2e_ms = reduce_max(dist, [dev_ms, e2e_ms])
+    bytes_now = wl.step_alg_bytes()
+    peak, peak_kind = measured_peaks()
+    out = {}
+    if rank == 0:
+        out = {
+            "metric": "accepted tokens/s, 120b-shaped TP x EP speculative verify", "value": accepted / (dev_ms * 1e-3),
+            "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp8 e4m3 x e4m3 -> fp32 (GEMMs), bf16 (attention, activations)", "data": "synthetic",
+            "config": wl.config(),
+            "e2e": {"value": accepted / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms / K,
+                    "h2d_bytes_per_step": 4 * (3 * 2560 + 3 * 512 + 1) + 16 * 1500, "d2h_bytes_per_step": 8 * 2560},
+            "accepted_per_seq_per_step": accepted / (K * len(wl.slots)),
+            "verified_rows_per_s": 5 * len(wl.slots) * K / (dev_ms * 1e-3),
+            "gpu_launches": launches,
+            "step_bytes_per_rank": bytes_now,
+            "step_hbm_bound_per_rank": {"floor_ms": bytes_now["total"] / (peak * 1e6),
+                                        "frac_of_floor": (bytes_now["total"] / (peak * 1e6)) / (dev_ms / K), "peak_gbs": peak,
+                                        "peak_kind": peak_kind},
+            "clocks": clocks, "device_status": status,
+        }
+        if args.profile:
+            out["step_breakdown_ms"] = dict(acc, note="CUDA events around each call in every timed step (adds overhead)")
+    wl.eng.close()
+    wl.comm.close()
+    dist.destroy_process_group()
     return out
 
 
@@ -530,7 +667,8 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decoder", choices=["decoder", "attn"])
+    ap.add_argument("--workload", default="decoder", choices=["decoder", "attn", "spec120b"])
+    ap.add_argument("--profile", action="store_true", help="spec120b: time attention/GEMM calls with CUDA events in every step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--seqs", type=int, default=256, help="sequences in the batch (smaller values are for profiler captures)")
     ap.add_argument("--layers", type=int, default=24, help="decoder layers (smaller values are for profiler captures)")
@@ -541,6 +679,8 @@ def main():
         out = run_reference(args)
     elif args.workload == "attn":
         out = run_attn(args)
+    elif args.workload == "spec120b":
+        out = run_spec120b(args)
     else:
         out = run_decoder(args)
     if out:

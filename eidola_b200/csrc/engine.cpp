@@ -640,6 +640,12 @@ int32_t eb_engine_seq_truncate(eb_engine* e, int32_t slot, int32_t new_len) {
   return EB_OK;
 }
 
+int32_t eb_engine_seq_truncate_many(eb_engine* e, const int32_t* h_slots, const int32_t* h_new_lens, int32_t n) {
+  EB_REQUIRE(e && h_slots && h_new_lens && n >= 0, EB_ERR_ARG, "eb_engine_seq_truncate_many: bad argument");
+  for (int i = 0; i < n; ++i) EB_TRY(eb_engine_seq_truncate(e, h_slots[i], h_new_lens[i]));
+  return EB_OK;
+}
+
 int32_t eb_engine_seq_len(const eb_engine* e, int32_t slot, int32_t* len) {
   EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_seq_len: null");
   return eb_sched_seq_len(e->sched, slot, len);

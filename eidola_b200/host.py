@@ -239,6 +239,10 @@ class Engine:
     def truncate(self, slot: int, new_len: int) -> None:
         call("eb_engine_seq_truncate", self._h, c_i32(slot), c_i32(new_len))
 
+    def truncate_many(self, slots, new_lens) -> None:
+        slots, new_lens = _i32(slots), _i32(new_lens)
+        call("eb_engine_seq_truncate_many", self._h, ptr(slots), ptr(new_lens), c_i32(len(slots)))
+
     def seq_len(self, slot: int) -> int:
         n = c_i32(0)
         call("eb_engine_seq_len", self._h, c_i32(slot), C.byref(n))

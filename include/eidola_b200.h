@@ -389,6 +389,8 @@ int32_t eb_engine_kv_fill_synth(eb_engine* e);
 int32_t eb_engine_seq_admit(eb_engine* e, int32_t context_len, int32_t* slot);
 int32_t eb_engine_seq_release(eb_engine* e, int32_t slot);
 int32_t eb_engine_seq_truncate(eb_engine* e, int32_t slot, int32_t new_len);
+/* Roll n sequences back in one call (after a verify step: new length = old length + accepted drafts + 1). */
+int32_t eb_engine_seq_truncate_many(eb_engine* e, const int32_t* h_slots, const int32_t* h_new_lens, int32_t n);
 int32_t eb_engine_seq_len(const eb_engine* e, int32_t slot, int32_t* len);
 int32_t eb_engine_sched(eb_engine* e, eb_sched** sched); /* borrowed; lives as long as the engine */
 /*
