@@ -239,9 +239,11 @@ class Spec120bWorkload:
                           max_tokens=5 * n_seqs, max_q_len=5, seed=seed, debug=2 if profile else 0, window_ring=1)
         cfg.num_pages = int(((self.ctx0.astype(np.int64) + grow) // PAGE + 1).sum()) + 64
         self.cfg = cfg
-        uid = [eb.Comm.unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(uid, src=0)
-        self.comm = eb.Comm(uid[0], rank, world)
+        self.comm = None
+        if world > 1:
+            uid = [eb.Comm.unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(uid, src=0)
+            self.comm = eb.Comm(uid[0], rank, world)
         self.eng = eb.Engine(cfg, rank, world, self.comm)
         self.eng.kv_fill_synth()
         self.slots = np.array([self.eng.admit(int(L)) for L in self.ctx0], np.int32)
@@ -488,9 +490,10 @@ def run_decoder(args) -> dict:
 
 def run_spec120b(args) -> dict:
     rank, world, dist = setup_dist()
-    if world < 2:
+    if world < 2 and (args.layers == 24 or args.layers > 8):
         return {"metric": "accepted tokens/s, 120b-shaped TP x EP verify", "unavailable":
-                "the 120b-shaped configuration needs at least 2 GPUs (116 GB of weights + KV); launch with torchrun"}
+                "the 120b-shaped configuration needs at least 2 GPUs (116 GB of weights + KV); launch with torchrun, "
+                "or pass --layers <= 8 for a single-GPU profile of its layer shapes"}
     import eidola_b200 as eb
     from eidola_b200 import capi
     capi.call("eb_device_set", capi.c_i32(rank_device(rank)))
@@ -501,7 +504,8 @@ def run_spec120b(args) -> dict:
 
     def barrier():
         capi.call("eb_device_sync")
-        dist.barrier()
+        if dist is not None:
+            dist.barrier()
 
     sampler = ClockSampler(rank_device(rank))
     if rank == 0:
@@ -551,8 +555,10 @@ def run_spec120b(args) -> dict:
         if args.profile:
             out["step_breakdown_ms"] = dict(acc, note="CUDA events around each call in every timed step (adds overhead)")
     wl.eng.close()
-    wl.comm.close()
-    dist.destroy_process_group()
+    if wl.comm is not None:
+        wl.comm.close()
+    if dist is not None:
+        dist.destroy_process_group()
     return out
 
 
