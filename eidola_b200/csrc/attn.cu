@@ -113,6 +113,12 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x for x <= 0 (or -inf): one MUFU instruction, relative error about 2^-22.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -260,6 +266,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
           }
         }
 
+        // Only the pages at the ends of the visible range need the causal / window mask (warp-uniform test).
+        const bool edge = (t0 + kPage - 1 > L - ql) || (p.window > 0 && t0 < L - p.window);
         uint32_t pa[MT][4], pb[MT][4];  // P = pa + pb: bf16 head and bf16 remainder, so P V keeps ~16 bits of P
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
@@ -275,21 +283,21 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
               for (int e = 0; e < 2; ++e) {
                 const int t = t0 + nt * 8 + tq * 2 + e;
                 float x = sc[mt][nt][half * 2 + e] * p.scale_log2;
-                if (t > pq || t < lo) x = -INFINITY;
+                if (edge && (t > pq || t < lo)) x = -INFINITY;
                 v[nt][e] = x;
                 mx = fmaxf(mx, x);
               }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float m_new = fmaxf(m_run[mt][half], mx);
-            const float alpha = exp2f(m_run[mt][half] - m_new);
+            const float alpha = fast_exp2(m_run[mt][half] - m_new);
             m_run[mt][half] = m_new;
             float ps = 0.f;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
-                v[nt][e] = exp2f(v[nt][e] - m_new);
+                v[nt][e] = fast_exp2(v[nt][e] - m_new);
                 ps += v[nt][e];
               }
             l_run[mt][half] = l_run[mt][half] * alpha + ps;

@@ -2,8 +2,9 @@
 // weighted combine of expert outputs.  The expert matrices themselves run in the grouped FP8 GEMM (gemm.cu).
 //
 // Routing decisions must be bit-exact against the CPU restatement, so the router logit is summed in one fixed
-// order: lane l of a warp adds the exact bf16 x bf16 products k = l, l+32, ... in ascending k with fmaf, then
-// the 32 lane sums are combined by an xor butterfly (offsets 16, 8, 4, 2, 1).  Ties go to the lower expert.
+// order: the row is cut in groups of 8 consecutive elements, lane l of a warp owns groups l, l+32, ... and adds
+// their exact bf16 x bf16 products in ascending k with fmaf, then the 32 lane sums are combined by an xor
+// butterfly (offsets 16, 8, 4, 2, 1).  Ties go to the lower expert.
 //
 // The reference project has no router (inference is delegated, crates/eidola-server/src/backend.rs:421-433).
 #include <cuda_runtime.h>
@@ -24,8 +25,8 @@ __device__ __forceinline__ float bf(uint16_t h) { return __uint_as_float((uint32
 // e = l + 32*j.
 constexpr int kRouterChunk = 8;
 
-template <int EPL, int HPL>  // experts per lane = ceil(E / 32), hidden elements per lane = ceil(H / 32)
-__global__ void __launch_bounds__(256, 1)
+template <int EPL, int GPL>  // experts per lane = ceil(E / 32), 8-element groups per lane = ceil(H / 256)
+__global__ void __launch_bounds__(256, 2)
 router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, int top_k, int32_t* idx, float* wts,
                    float* logits_out) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
@@ -34,35 +35,31 @@ router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, i
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 8 + warp;
   const bool on = t < T;
-  const int H8 = H >> 3;  // H is a multiple of 8
-  float xr[HPL];
+  const int H8 = H >> 3;  // groups of 8 elements = 16-byte words per row
+  float xr[GPL][8];
 #pragma unroll
-  for (int j = 0; j < HPL; ++j) {
-    const int k = lane + 32 * j;
-    xr[j] = (on && k < H) ? bf(x[(int64_t)t * H + k]) : 0.f;
+  for (int j = 0; j < GPL; ++j) {
+    const int g = lane + 32 * j;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (on && g < H8) v = *reinterpret_cast<const uint4*>(x + (int64_t)t * H + 8 * g);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      xr[j][2 * q] = __uint_as_float(w[q] << 16);
+      xr[j][2 * q + 1] = __uint_as_float(w[q] & 0xFFFF0000u);
+    }
   }
-  constexpr int kPerThread = (kRouterChunk * (HPL * 32 / 8) + 255) / 256;  // 16-byte loads per thread per chunk
-  uint4 pre[kPerThread];
-  auto fetch = [&](int e0) {  // rows [e0, e0 + chunk) are contiguous in the router matrix
+  // Rows [e0, e0 + chunk) are contiguous in the router matrix: copy them with 16-byte cp.async, no registers held.
+  auto stage = [&](int e0, int buf) {
     const int n16 = min(kRouterChunk, E - e0) * H8;
     const uint4* src = reinterpret_cast<const uint4*>(wr + (int64_t)e0 * H);
-#pragma unroll
-    for (int q = 0; q < kPerThread; ++q) {
-      const int c = threadIdx.x + 256 * q;
-      if (c < n16) pre[q] = src[c];
-    }
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(wrow + (size_t)buf * kRouterChunk * H);
+    for (int c = threadIdx.x; c < n16; c += 256)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + c * 16), "l"(src + c) : "memory");
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  auto commit = [&](int e0, int buf) {
-    const int n16 = min(kRouterChunk, E - e0) * H8;
-    uint4* dst = reinterpret_cast<uint4*>(wrow + (size_t)buf * kRouterChunk * H);
-#pragma unroll
-    for (int q = 0; q < kPerThread; ++q) {
-      const int c = threadIdx.x + 256 * q;
-      if (c < n16) dst[c] = pre[q];
-    }
-  };
-  fetch(0);
-  commit(0, 0);
+  stage(0, 0);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
 
   float lg[EPL];
@@ -70,27 +67,47 @@ router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, i
   for (int j = 0; j < EPL; ++j) lg[j] = -INFINITY;
   for (int e0 = 0, buf = 0; e0 < E; e0 += kRouterChunk, buf ^= 1) {
     const bool more = e0 + kRouterChunk < E;
-    if (more) fetch(e0 + kRouterChunk);
+    if (more) stage(e0 + kRouterChunk, buf ^ 1);  // that buffer was last read one iteration ago, before a barrier
     const int ne = min(kRouterChunk, E - e0);
-    for (int r = 0; r < ne; ++r) {
-      const int e = e0 + r;
-      const uint16_t* w = wrow + ((size_t)buf * kRouterChunk + r) * H;
-      float acc = 0.f;
+    for (int r0 = 0; r0 < ne; r0 += 2) {
+      // two experts at a time (two independent fmaf chains); one 16-byte shared-memory load feeds eight fmaf
+      const uint4* w0 = reinterpret_cast<const uint4*>(wrow + ((size_t)buf * kRouterChunk + r0) * H);
+      const uint4* w1 = w0 + (r0 + 1 < ne ? H8 : 0);
+      float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-      for (int j = 0; j < HPL; ++j) {
-        const int k = lane + 32 * j;
-        if (k < H) acc = __fmaf_rn(xr[j], bf(w[k]), acc);
+      for (int j = 0; j < GPL; ++j) {
+        const int g = lane + 32 * j;
+        if (g < H8) {
+          const uint4 u0 = w0[g], u1 = w1[g];
+          const uint32_t p0[4] = {u0.x, u0.y, u0.z, u0.w}, p1[4] = {u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            a0 = __fmaf_rn(xr[j][2 * q], __uint_as_float(p0[q] << 16), a0);
+            a0 = __fmaf_rn(xr[j][2 * q + 1], __uint_as_float(p0[q] & 0xFFFF0000u), a0);
+            a1 = __fmaf_rn(xr[j][2 * q], __uint_as_float(p1[q] << 16), a1);
+            a1 = __fmaf_rn(xr[j][2 * q + 1], __uint_as_float(p1[q] & 0xFFFF0000u), a1);
+          }
+        }
       }
 #pragma unroll
-      for (int o = 16; o; o >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, o));
-      if ((e & 31) == lane) {
-#pragma unroll
-        for (int j = 0; j < EPL; ++j)
-          if (j == (e >> 5)) lg[j] = acc;
+      for (int o = 16; o; o >>= 1) {
+        a0 = __fadd_rn(a0, __shfl_xor_sync(0xffffffffu, a0, o));
+        a1 = __fadd_rn(a1, __shfl_xor_sync(0xffffffffu, a1, o));
       }
-      if (logits_out && on && lane == 0) logits_out[(int64_t)t * E + e] = acc;
+      const float av[2] = {a0, a1};
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int e = e0 + r0 + q;
+        if (r0 + q >= ne) break;
+        if ((e & 31) == lane) {
+#pragma unroll
+          for (int j = 0; j < EPL; ++j)
+            if (j == (e >> 5)) lg[j] = av[q];
+        }
+        if (logits_out && on && lane == 0) logits_out[(int64_t)t * E + e] = av[q];
+      }
     }
-    if (more) commit(e0 + kRouterChunk, buf ^ 1);  // that buffer was last read one iteration ago, before a barrier
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
   }
   if (!on) return;
@@ -278,7 +295,7 @@ int32_t launch_router2(unsigned grid, size_t smem, cudaStream_t st, const uint16
   auto kfn = router_topk_kernel<EPL, HPL>;
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kRouterChunk * HPL * 32 * (int)sizeof(uint16_t));
+    cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kRouterChunk * HPL * 256 * (int)sizeof(uint16_t));
     configured = true;
   }
   EB_CUDA(eb::launch(kfn, dim3(grid), dim3(256), smem, st, x, wr, T, E, H, top_k, idx, wts, logits));
@@ -316,17 +333,17 @@ int32_t eb_moe_route(const void* d_x, const void* d_wr, int32_t T, int32_t E, in
   cudaStream_t st = eb::as_stream(stream);
   const uint16_t* x = (const uint16_t*)d_x;
   const uint16_t* wr = (const uint16_t*)d_wr;
-  const int epl = (E + 31) / 32, hpl = (H + 31) / 32;
-  if (hpl <= 16)
-    return launch_router<16>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
-  else if (hpl <= 32)
-    return launch_router<32>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
-  else if (hpl <= 64)
-    return launch_router<64>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
-  else if (hpl <= 96)
-    return launch_router<96>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  const int epl = (E + 31) / 32, hpl = (H + 255) / 256;  // 8-element groups per lane
+  if (hpl <= 2)
+    return launch_router<2>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  else if (hpl <= 4)
+    return launch_router<4>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  else if (hpl <= 8)
+    return launch_router<8>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+  else if (hpl <= 12)
+    return launch_router<12>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
   else
-    return launch_router<128>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
+    return launch_router<16>(epl, grid, smem, st, x, wr, T, E, H, top_k, d_idx, d_wts, d_logits);
 }
 
 int32_t eb_moe_permute(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E, int32_t* d_seg_off,

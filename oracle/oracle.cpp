@@ -264,10 +264,11 @@ void orc_embed(const uint16_t* table, int64_t H, const int32_t* tokens, int32_t 
 /* ----------------------------------------------------------------- MoE */
 
 /*
- * Router.  logit[t][e] = sum_k x[t][k]*wr[e][k] in fp32 with this exact order: lane l (0..31) adds the
- * products k = l, l+32, l+64, ... in ascending k (each product of two bf16 is exact in fp32), then the 32
- * lane sums are combined by a butterfly: for off in 16,8,4,2,1: a[l] += a[l ^ off].  top_k by value, ties to
- * the lower expert index; weights = softmax over the selected logits.
+ * Router.  logit[t][e] = sum_k x[t][k]*wr[e][k] in fp32 with this exact order: the row is cut in groups of 8
+ * consecutive elements; lane l (0..31) owns groups l, l+32, l+64, ... and adds their products in ascending k with
+ * fmaf (each product of two bf16 is exact in fp32); then the 32 lane sums are combined by a butterfly:
+ * for off in 16,8,4,2,1: a[l] += a[l ^ off].  top_k by value, ties to the lower expert index; weights = softmax
+ * over the selected logits.  H must be a multiple of 8.
  */
 void orc_router_topk(const uint16_t* x, const uint16_t* wr, int32_t T, int32_t E, int32_t H, int32_t top_k,
                      int32_t* idx, float* wts, float* logits_out) {
@@ -278,7 +279,8 @@ void orc_router_topk(const uint16_t* x, const uint16_t* wr, int32_t T, int32_t E
       float a[32];
       for (int l = 0; l < 32; ++l) {
         float acc = 0.f;
-        for (int32_t k = l; k < H; k += 32) acc = fmaf(bf(x[(int64_t)t * H + k]), bf(wr[(int64_t)e * H + k]), acc);
+        for (int32_t g = l; g < H / 8; g += 32)
+          for (int32_t k = 8 * g; k < 8 * g + 8; ++k) acc = fmaf(bf(x[(int64_t)t * H + k]), bf(wr[(int64_t)e * H + k]), acc);
         a[l] = acc;
       }
       for (int off = 16; off >= 1; off >>= 1) {
