@@ -187,6 +187,7 @@ def decoder_cpu_sample(n_seqs=32, seed=4):
     LM head, one step, n_seqs of the 256 sequences.  Returns (tokens_per_second_extrapolated, description, seconds)."""
     from oracle import binding as orc
     from oracle import sched as osched
+    threads = orc.set_threads(os.cpu_count() or 1)  # all host cores, whatever OMP_NUM_THREADS the launcher exported
     cfg = decoder_config(n_layers=2, n_seqs=n_seqs, steps=2, seed=seed)
     rng = np.random.default_rng(seed)
     ctx = rng.integers(128, 8193, size=256).astype(np.int32)[:: 256 // n_seqs][:n_seqs]
@@ -213,8 +214,8 @@ def decoder_cpu_sample(n_seqs=32, seed=4):
     model.step(p, toks, bt, n_layers_run=0, want_logits=False)           # embedding + head only
     t_head = time.perf_counter() - t0
     t_step = (t_full - t_head) * 12 + t_head                               # 24 layers = 12 (windowed, full) pairs
-    desc = ("CPU oracle, %d of 256 sequences, one step: 2 of 24 layers (one windowed, one full) + LM head timed "
-            "(%.1f s), layer time x12 + head -> %.1f s per step" % (n_seqs, t_full + t_head, t_step))
+    desc = ("CPU oracle on %d threads, %d of 256 sequences, one step: 2 of 24 layers (one windowed, one full) + LM head "
+            "timed (%.1f s), layer time x12 + head -> %.1f s per step" % (threads, n_seqs, t_full + t_head, t_step))
     return n_seqs / t_step, desc, t_full + t_head
 
 

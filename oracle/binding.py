@@ -40,6 +40,12 @@ def _void(name, *args):
     f(*args)
 
 
+def set_threads(n: int) -> int:
+    """Use n OpenMP threads (0 = leave as is); returns the number in effect."""
+    _lib.orc_set_threads.restype = C.c_int
+    return int(_lib.orc_set_threads(C.c_int(n)))
+
+
 # ---- formats / synthetic tensors
 
 def synth_normal_f32(seed, stream, idx0, n, scale=1.0) -> np.ndarray:

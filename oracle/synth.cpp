@@ -12,9 +12,17 @@
 #include <stdint.h>
 #include <stddef.h>
 
+#include <omp.h>
+
 #include "../include/eb_synth.h"
 
 extern "C" {
+
+/* Threads the oracle may use (launchers such as torchrun export OMP_NUM_THREADS=1); returns the value in effect. */
+int orc_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+}
 
 /* out[i] = scale * N(0,1)(seed, stream, idx0 + i) */
 void orc_synth_normal_f32(uint64_t seed, uint64_t stream, uint64_t idx0, int64_t n, float scale, float* out) {
