@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the decode hot path on B200 through the C ABI of libeidola_b200.so.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decoder|attn]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decoder|attn|spec120b|gemm]
 
 Prints ONE JSON line.
 
@@ -644,6 +644,203 @@ def run_attn(args) -> dict:
     return out
 
 
+# ------------------------------------------------------------------------------------------ GEMM sweep workload
+
+def measured_tensor_peak() -> tuple[float, str]:
+    """FP8 dense peak estimate in TFLOP/s: twice the measured bf16 cuBLAS burst figure (the tensor pipe runs e4m3 at
+    twice the bf16 rate; no FP8 figure was measured on this pool), else twice the fallback bf16 figure."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return 2.0 * float(json.loads(p.read_text())["bf16_tflops"]), "2 x measured bf16"
+        except Exception:
+            pass
+    return 2.0 * 1590.0, "2 x fallback bf16"
+
+
+class GemmSweep:
+    """Y = X W^T, X [M,2880] e4m3, W [5120,2880] e4m3, fp32 scales per 128x128 block uniform in [0.5,2), bf16 output.
+    Entries are N(0,1) rounded to e4m3.  Each M rotates over enough distinct copies of W and X that consecutive
+    launches never find their operands in L2."""
+    name = "FP8 block-scaled GEMM sweep: X[M,2880] x W[5120,2880]^T, e4m3 operands, fp32 128x128 block scales, bf16 out"
+    N, K = 5120, 2880
+    MS = (1, 8, 64, 256, 1024, 4096)
+
+    def __init__(self, rank: int, seed=2):
+        import eidola_b200 as eb
+        from eidola_b200 import capi, host
+        from eidola_b200.capi import DeviceBuffer, c_f32, c_i64, c_u64, c_vp
+        self.eb, self.capi, self.host = eb, capi, host
+        self.info = eb.device_info(rank_device(rank))
+        N, K = self.N, self.K
+        kb = (K + 127) // 128
+        self.copies = int(1.5 * self.info["l2_bytes"] // (N * K)) + 1
+        self.w, self.sw = [], []
+        for c in range(self.copies):
+            w8, sw = DeviceBuffer(N * K), DeviceBuffer(((N + 127) // 128) * kb * 4)
+            capi.call("eb_synth_normal_e4m3", c_vp(w8.ptr), c_i64(N * K), c_u64(seed), c_u64(100 + c), c_u64(0), c_f32(1.0), None)
+            capi.call("eb_synth_uniform_f32", c_vp(sw.ptr), c_i64(((N + 127) // 128) * kb), c_u64(seed), c_u64(200 + c),
+                      c_u64(0), c_f32(0.5), c_f32(2.0), None)
+            self.w.append(w8)
+            self.sw.append(sw)
+        Mmax = max(self.MS)
+        self.x, self.sx, self.y = [], [], []
+        self.x_copies = 4
+        for c in range(self.x_copies):
+            x8, sx = DeviceBuffer(Mmax * K), DeviceBuffer(((Mmax + 127) // 128) * kb * 4)
+            capi.call("eb_synth_normal_e4m3", c_vp(x8.ptr), c_i64(Mmax * K), c_u64(seed), c_u64(300 + c), c_u64(0), c_f32(1.0), None)
+            capi.call("eb_synth_uniform_f32", c_vp(sx.ptr), c_i64(((Mmax + 127) // 128) * kb), c_u64(seed), c_u64(400 + c),
+                      c_u64(0), c_f32(0.5), c_f32(2.0), None)
+            self.x.append(x8)
+            self.sx.append(sx)
+            self.y.append(DeviceBuffer(Mmax * N * 2))
+        self.work = DeviceBuffer(max(host.gemm_workspace(M, N, 1) for M in self.MS))
+        capi.call("eb_device_sync")
+        self.i = 0
+
+    def launch(self, M: int, stream=None):
+        c, xc = self.i % self.copies, self.i % self.x_copies
+        self.i += 1
+        self.host.gemm_fp8(self.x[xc].ptr, self.sx[xc].ptr, self.w[c].ptr, self.sw[c].ptr, self.y[xc].ptr, M, self.N,
+                           self.K, work=self.work, stream=stream)
+
+    def alg_bytes(self, M: int) -> int:
+        N, K = self.N, self.K
+        kb = (K + 127) // 128
+        return N * K + M * K + M * N * 2 + 4 * kb * (((N + 127) // 128) + ((M + 127) // 128))
+
+    def flops(self, M: int) -> float:
+        return 2.0 * M * self.N * self.K
+
+    def time_m(self, M: int, reps: int, warm: int) -> float:
+        """Average device milliseconds per launch over `reps` back-to-back launches."""
+        for _ in range(warm):
+            self.launch(M)
+        t = self.eb.Timer()
+        self.capi.call("eb_device_sync")
+        t.start()
+        for _ in range(reps):
+            self.launch(M)
+        return t.stop() / reps
+
+    def cpu_sample(self, M=64):
+        from oracle import binding as orc
+        N, K = self.N, self.K
+        kb = (K + 127) // 128
+        x8 = self.x[0].to_array(np.uint8, (max(self.MS), K))[:M].copy()
+        sx = self.sx[0].to_array(np.float32, ((max(self.MS) + 127) // 128, kb))[: (M + 127) // 128].copy()
+        w8 = self.w[0].to_array(np.uint8, (N, K))
+        sw = self.sw[0].to_array(np.float32, ((N + 127) // 128, kb))
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 10.0:
+            out = orc.gemm_fp8_block(x8, sx, w8, sw)
+            reps += 1
+        dt = time.perf_counter() - t0
+        return self.flops(M) * reps / dt / 1e12, dt, reps, out
+
+
+def run_gemm(args) -> dict:
+    rank, world, dist = setup_dist()
+    import eidola_b200 as eb
+    from eidola_b200 import capi
+    capi.call("eb_device_set", capi.c_i32(rank_device(rank)))
+    wl = GemmSweep(rank)
+    K, W = args.steps, args.warmup
+
+    def barrier():
+        capi.call("eb_device_sync")
+        if dist is not None:
+            dist.barrier()
+            capi.call("eb_device_sync")
+
+    sampler = ClockSampler(rank_device(rank))
+    if rank == 0:
+        sampler.start()
+    for _ in range(W):
+        for M in wl.MS:
+            wl.launch(M)
+    barrier()
+    total = eb.Timer()
+    total.start()
+    for _ in range(K):  # one step = one pass over the sweep
+        for M in wl.MS:
+            wl.launch(M)
+    total_ms = total.stop()
+    barrier()
+    per_m = {}
+    for M in wl.MS:
+        ms = wl.time_m(M, reps=max(20, K), warm=3)
+        per_m[M] = ms
+    barrier()
+    # end to end: host X in, host Y out, for the largest M
+    Mbig = max(wl.MS)
+    xb, yb = Mbig * wl.K, Mbig * wl.N * 2
+    h_x, h_y = capi.c_vp(), capi.c_vp()
+    capi.call("eb_host_alloc", C.byref(h_x), capi.c_sz(xb))
+    capi.call("eb_host_alloc", C.byref(h_y), capi.c_sz(yb))
+    capi.call("eb_copy_d2h", h_x, capi.c_vp(wl.x[0].ptr), capi.c_sz(xb), None)
+    capi.call("eb_device_sync")
+
+    def e2e_step():
+        xc = wl.i % wl.x_copies
+        capi.call("eb_copy_h2d", capi.c_vp(wl.x[xc].ptr), h_x, capi.c_sz(xb), None)
+        wl.launch(Mbig)
+        capi.call("eb_copy_d2h", h_y, capi.c_vp(wl.y[xc].ptr), capi.c_sz(yb), None)
+        capi.call("eb_device_sync")
+
+    for _ in range(3):
+        e2e_step()
+    e2e_t = eb.Timer()
+    e2e_t.start()
+    for _ in range(K):
+        e2e_step()
+    e2e_ms = e2e_t.stop()
+    clocks = sampler.stop() if rank == 0 else None
+    status = eb.status_read()
+    total_ms, e2e_ms = reduce_max(dist, [total_ms, e2e_ms])
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return {}
+    hbm_peak, hbm_kind = measured_peaks()
+    t_peak, t_kind = measured_tensor_peak()
+    sweep = {}
+    for M, ms in per_m.items():
+        tf = wl.flops(M) / (ms * 1e-3) / 1e12
+        gbs = wl.alg_bytes(M) / (ms * 1e-3) / 1e9
+        sweep[str(M)] = {"us": ms * 1e3, "tflops": tf, "gbs": gbs, "frac_tensor": tf / t_peak, "frac_hbm": gbs / hbm_peak}
+    flops_step = sum(wl.flops(M) for M in wl.MS)
+    big = sweep[str(Mbig)]
+    out = {
+        "metric": "FP8 GEMM TFLOPS vs peak", "value": world * flops_step * K / (total_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": total_ms / K, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8 e4m3 x e4m3 -> fp32 accumulate, fp32 block scales, bf16 out",
+        "data": "synthetic",
+        "config": {"workload": wl.name, "M": list(wl.MS), "step": "one launch per M of the sweep",
+                   "l2": "%d weight copies (%.0f MB) rotate so no launch finds W in L2" % (wl.copies, wl.copies * wl.N * wl.K / 1e6),
+                   "parallelism": ("replicas x%d" % world) if world > 1 else "single GPU"},
+        "e2e": {"value": world * wl.flops(Mbig) * K / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "M": Mbig,
+                "h2d_bytes_per_step": xb, "d2h_bytes_per_step": yb},
+        "gpu_launches": len(wl.MS) * K,
+        "sweep": sweep,
+        "roofline": {"bound": "tensor", "achieved": big["tflops"], "peak": t_peak, "unit": "TFLOP/s",
+                     "frac": big["tflops"] / t_peak, "peak_kind": t_kind, "traffic": None,
+                     "kernel": "gemm_fp8 kernel, M=%d" % Mbig, "alg_flops_per_launch": wl.flops(Mbig),
+                     "avg_launch_ms": per_m[Mbig], "frac_of_nominal_4500": big["tflops"] / 4500.0,
+                     "small_m_hbm": {"M": 8, "achieved_gbs": sweep["8"]["gbs"], "peak_gbs": hbm_peak, "peak_kind": hbm_kind,
+                                     "frac": sweep["8"]["frac_hbm"]}},
+        "clocks": clocks, "device_status": status,
+    }
+    if world == 1 and not args.no_cpu:
+        v, dt, reps, cpu_out = wl.cpu_sample(64)
+        out["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                               "sample": "M=64 of the sweep, %d repetitions, %.1f s" % (reps, dt)}
+    if dist is not None:
+        dist.destroy_process_group()
+    return out
+
+
 def run_reference(args) -> dict:
     """The reference arm: the CPU oracle (the reference project has no implementation of this path), all host threads."""
     rank = int(os.environ.get("RANK", 0))
@@ -674,7 +871,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decoder", choices=["decoder", "attn", "spec120b"])
+    ap.add_argument("--workload", default="decoder", choices=["decoder", "attn", "spec120b", "gemm"])
     ap.add_argument("--profile", action="store_true", help="spec120b: time attention/GEMM calls with CUDA events in every step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--seqs", type=int, default=256, help="sequences in the batch (smaller values are for profiler captures)")
@@ -688,6 +885,8 @@ def main():
         out = run_attn(args)
     elif args.workload == "spec120b":
         out = run_spec120b(args)
+    elif args.workload == "gemm":
+        out = run_gemm(args)
     else:
         out = run_decoder(args)
     if out:

@@ -84,6 +84,7 @@ struct eb_engine {
   int32_t *r_idx = nullptr, *seg_off = nullptr, *perm_row = nullptr, *row_token = nullptr;
   float* r_wts = nullptr;
   void *gemm_ws = nullptr, *group_ws = nullptr;
+  size_t gemm_ws_bytes = 0, group_ws_bytes = 0;
   float *part_acc = nullptr, *part_ml = nullptr;
   int32_t* d_next = nullptr;
   float* d_margin = nullptr;
@@ -242,9 +243,11 @@ int32_t init_work(eb_engine* e) {
   uint8_t* p8 = nullptr;
   EB_TRY(dev_alloc(e, &p8, ws, w));
   e->gemm_ws = p8;
+  e->gemm_ws_bytes = ws;
   EB_TRY(eb_gemm_workspace((int32_t)R, 2 * I, std::max(E, 2), &ws2));
   EB_TRY(dev_alloc(e, &p8, ws2, w));
   e->group_ws = p8;
+  e->group_ws_bytes = ws2;
   e->cap_items = 4 * e->sm_count + c.max_seqs + 16;
   const int ppi = 8 / e->hkv_l;
   size_t acc_b = 0, ml_b = 0;
@@ -337,6 +340,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     g.K = K;
     g.n_groups = 1;
     g.d_work = (T <= 512 && N <= std::max(e->nqkv, H)) ? e->gemm_ws : nullptr;
+    g.work_bytes = g.d_work ? e->gemm_ws_bytes : 0;
     n += 1;
     return splits ? eb_gemm_fp8_block_partial(&g, splits, st) : eb_gemm_fp8_block(&g, st);
   };
@@ -356,6 +360,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     g.n_groups = E;
     g.d_seg_off = e->seg_off;
     g.d_work = e->group_ws;
+    g.work_bytes = e->group_ws_bytes;
     g.tile_tokens = group_tn;
     g.tiles_ready = 1;
     n += 1;

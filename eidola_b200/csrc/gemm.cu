@@ -15,6 +15,9 @@
 //
 // The reference project has no GEMM (inference is delegated, crates/eidola-server/src/backend.rs:421-433).
 #include <cuda.h>
+#include <stdlib.h>
+
+#include <algorithm>
 #include <cuda_runtime.h>
 
 #include "common.h"
@@ -293,6 +296,204 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Persistent variant: at most two CTAs per SM walk the work list (token tile fastest, then weight tile, then K
+// split) with a stride of the grid size.  The stage ring and the tensor-memory buffers keep rotating across
+// tiles, so the producer is already loading the next tile while the epilogue warps store the current one, and the
+// per-CTA set-up (barriers, tensor-memory allocation) is paid once per SM instead of once per tile.
+template <int TN>
+struct PCfg {
+  static constexpr int kStageBytes = kTileN * kBlockK + TN * kBlockK;
+  static constexpr int kStages = (TN == 128) ? 3 : (TN == 64) ? 4 : 5;
+  static constexpr int kBufs = (TN == 128) ? 2 : 4;  // accumulator buffers in tensor memory
+  static constexpr uint32_t kTmemCols = (kBufs * TN < 32) ? 32 : kBufs * TN;
+  static constexpr size_t kSmem = 1024 + (size_t)kStages * kStageBytes + 256;
+};
+
+struct TileInfo {
+  int g, row0, row_end, xblk, nb, n0, split, kb0, nkb;
+};
+
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int w, int TT, int NB, int KB, int tn) {
+  TileInfo t;
+  const int tt = w % TT;
+  t.nb = (w / TT) % NB;
+  t.split = w / (TT * NB);
+  t.n0 = t.nb * kTileN;
+  if (p.seg_off) {
+    t.g = p.tile_group[tt];
+    t.row0 = p.tile_row0[tt];
+    t.row_end = p.seg_off[t.g + 1];
+    t.xblk = p.blk_off[t.g] + (t.row0 - p.seg_off[t.g]) / 128;
+  } else {
+    t.g = 0;
+    t.row0 = tt * tn;
+    t.row_end = p.rows;
+    t.xblk = t.row0 / 128;
+  }
+  const int kb_per = (KB + p.splits - 1) / p.splits;
+  t.kb0 = t.split * kb_per;
+  t.nkb = max(0, min(KB, t.kb0 + kb_per) - t.kb0);
+  return t;
+}
+
+template <int TN>
+__global__ void __launch_bounds__(kThreads, 2)
+gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                           const GemmParams p) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
+  using C = PCfg<TN>;
+  constexpr int S = C::kStages, NBUF = C::kBufs;
+  const int KB = (p.K + kBlockK - 1) / kBlockK;
+  const int NB = (p.N + kTileN - 1) / kTileN;
+  const int TT = p.seg_off ? *p.n_tiles : (p.rows + TN - 1) / TN;
+  const int n_work = TT * NB * p.splits;
+  if ((int)blockIdx.x >= n_work) return;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t stage0 = (raw + 1023u) & ~1023u;
+  uint8_t* after = smem_raw + (stage0 - raw) + S * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after);  // full[S], empty[S], tfull[NBUF], tempty[NBUF]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(after + (2 * S + 2 * NBUF) * sizeof(uint64_t));
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[S]);
+  const uint32_t bar_tfull = smem_u32(&bars[2 * S]), bar_tempty = smem_u32(&bars[2 * S + NBUF]);
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < NBUF; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;  // K blocks issued by this CTA so far, over all its tiles
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const TileInfo t = decode_tile(p, w, TT, NB, KB, TN);
+        const int wy = t.g * p.N + t.n0;
+        for (int i = 0; i < t.nkb; ++i, ++it) {
+          const uint32_t s = it % S;
+          if (it >= (uint32_t)S && !mbar_wait(bar_empty + 8 * s, ((it / S) - 1) & 1, &abort_flag, p.status)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = stage0 + s * C::kStageBytes, b_dst = a_dst + kTileN * kBlockK;
+          mbar_arrive_expect_tx(bar_full + 8 * s, C::kStageBytes);
+          tma_load_2d(a_dst, &tm_w, (t.kb0 + i) * kBlockK, wy, bar_full + 8 * s);
+          tma_load_2d(b_dst, &tm_x, (t.kb0 + i) * kBlockK, t.row0, bar_full + 8 * s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const TileInfo t = decode_tile(p, w, TT, NB, KB, TN);
+        for (int i = 0; i < t.nkb; ++i, ++it) {
+          const uint32_t s = it % S, b = it % NBUF;
+          if (!mbar_wait(bar_full + 8 * s, (it / S) & 1, &abort_flag, p.status) ||
+              (it >= (uint32_t)NBUF && !mbar_wait(bar_tempty + 8 * b, ((it / NBUF) - 1) & 1, &abort_flag, p.status))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = stage0 + s * C::kStageBytes, b_addr = a_addr + kTileN * kBlockK;
+          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_f8(tmem_base + b * TN, da + 2 * k, db + 2 * k, idesc, k > 0 ? 1u : 0u);
+          tc_commit(bar_empty + 8 * s);
+          tc_commit(bar_tfull + 8 * b);
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+      const TileInfo t = decode_tile(p, w, TT, NB, KB, TN);
+      // scale products of this tile's K blocks, block kb held by lane kb % 32 in register kb / 32
+      float sreg[kMaxKB / 32];
+      {
+        const float* swr = p.sw + ((int64_t)t.g * NB + t.nb) * KB + t.kb0;
+        const float* sxr = p.sx + (int64_t)t.xblk * KB + t.kb0;
+#pragma unroll
+        for (int j = 0; j < kMaxKB / 32; ++j) {
+          const int kb = lane + 32 * j;
+          sreg[j] = kb < t.nkb ? swr[kb] * sxr[kb] : 0.f;
+        }
+      }
+      float acc[TN];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[j] = 0.f;
+      for (int i = 0; i < t.nkb; ++i, ++it) {
+        const uint32_t b = it % NBUF;
+        if (!mbar_wait(bar_tfull + 8 * b, (it / NBUF) & 1, &abort_flag, p.status)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const int jr = i >> 5;
+        const float mine = jr == 0 ? sreg[0] : jr == 1 ? sreg[1] : jr == 2 ? sreg[2] : sreg[3];
+        const float sc = __shfl_sync(0xffffffffu, mine, i & 31);
+#pragma unroll
+        for (int c = 0; c < TN / 16; ++c) {
+          float v[16];
+          tmem_ld16(lane_base + b * TN + c * 16, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(sc, v[j], acc[c * 16 + j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+      }
+      const int n = t.n0 + q * 32 + lane;
+      if (ok && n < p.N) {
+        if (p.splits > 1) {
+          float* yp = p.y_part + ((int64_t)t.split * p.rows) * p.N;
+#pragma unroll
+          for (int j = 0; j < TN; ++j)
+            if (t.row0 + j < t.row_end) yp[(int64_t)(t.row0 + j) * p.N + n] = acc[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < TN; ++j)
+            if (t.row0 + j < t.row_end) {
+              uint32_t h;
+              asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(0.f), "f"(acc[j]));
+              p.y[(int64_t)(t.row0 + j) * p.ldy + n] = (uint16_t)(h & 0xFFFFu);
+            }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
+}
+
 // Sum split-K partials in split order and round to bf16.
 __global__ void gemm_splitk_reduce_kernel(const float* part, uint16_t* y, int64_t ldy, int rows, int N, int splits) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
@@ -466,13 +667,56 @@ quant_act_kernel(const uint16_t* x, int64_t ldx, int rows, int cols, const int32
 template <int TN>
 int32_t launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, dim3 grid, cudaStream_t st) {
   auto kfn = gemm_fp8_kernel<TN>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {false};  // the attribute is per device
+  int dev = 0;
+  EB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<TN>::kSmem));
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   EB_CUDA(eb::launch(kfn, dim3(grid), dim3(kThreads), Cfg<TN>::kSmem, st, tw, tx, p));
   EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int sm_count_now() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 148;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// Which kernel runs a GEMM: the persistent one pays off once the tiles exceed what the GPU holds at a time (two CTAs
+// per SM); below that the one-tile-per-CTA kernel starts its loads sooner.  EIDOLA_B200_GEMM_LEGACY=1 forces the
+// one-tile kernel, =0 the persistent one (for A/B timing).
+bool gemm_persistent(int64_t work_upper, int sms) {
+  static const int mode = [] {
+    const char* v = getenv("EIDOLA_B200_GEMM_LEGACY");
+    return !v ? -1 : (v[0] == '1' ? 1 : 0);
+  }();
+  if (mode >= 0) return mode == 0;
+  return work_upper > 2ll * sms;
+}
+
+template <int TN>
+int32_t launch_gemm_persistent(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int64_t work_upper,
+                               cudaStream_t st) {
+  auto kfn = gemm_fp8_persistent_kernel<TN>;
+  static bool configured[64] = {false};  // the attribute is per device
+  int dev = 0;
+  EB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PCfg<TN>::kSmem));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int sms = sm_count_now();
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(work_upper, 2ll * sms));
+  EB_CUDA(eb::launch(kfn, dim3(grid), dim3(kThreads), PCfg<TN>::kSmem, st, tw, tx, p));
   return EB_OK;
 }
 
@@ -515,6 +759,9 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
     tn = a->tile_tokens ? a->tile_tokens : pick_tn((a->rows + a->n_groups - 1) / a->n_groups);
     EB_REQUIRE(tn == 16 || tn == 32 || tn == 64 || tn == 128, EB_ERR_ARG, "gemm: tile_tokens %d not in {16,32,64,128}", tn);
     token_tiles = a->rows / tn + a->n_groups;
+    const size_t need = sizeof(int32_t) * ((size_t)a->n_groups + 2 + 2 * (size_t)token_tiles);
+    EB_REQUIRE(a->work_bytes >= need, EB_ERR_ARG, "grouped gemm: workspace of %zu bytes, %zu needed (eb_gemm_workspace)",
+               a->work_bytes, need);
     int32_t* w = (int32_t*)a->d_work;
     int32_t* blk_off = w;
     int32_t* n_tiles = w + (a->n_groups + 1);
@@ -540,12 +787,17 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
       splits = 1;
       if (a->d_work && a->rows <= kMaxSplitRows) {
         const int tiles = nb * token_tiles;
-        while (tiles * splits < 120 && splits * 2 <= 8 && KB / (splits * 2) >= 4) splits *= 2;
+        const size_t per_split = sizeof(float) * (size_t)a->rows * a->N;
+        while (tiles * splits < 120 && splits * 2 <= 8 && KB / (splits * 2) >= 4 && per_split * (splits * 2) <= a->work_bytes)
+          splits *= 2;
       }
     }
     EB_REQUIRE(splits >= 1 && splits <= KB, EB_ERR_ARG, "gemm: splits %d outside 1..%d", splits, KB);
     EB_REQUIRE(splits == 1 || (a->d_work && a->rows <= kMaxSplitRows && splits <= 8), EB_ERR_ARG,
                "gemm: split K needs a workspace, at most %d rows and at most 8 splits", kMaxSplitRows);
+    EB_REQUIRE(splits == 1 || sizeof(float) * (size_t)splits * a->rows * a->N <= a->work_bytes, EB_ERR_ARG,
+               "gemm: %d K splits need %zu workspace bytes, the caller lent %zu", splits,
+               sizeof(float) * (size_t)splits * a->rows * a->N, a->work_bytes);
     p.splits = splits;
     p.y_part = (float*)a->d_work;
   }
@@ -559,6 +811,23 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
                               (uint64_t)a->K, (uint32_t)tn);
   if (rc != EB_OK) return rc;
 
+  const int64_t work_upper = (int64_t)token_tiles * nb * p.splits;
+  if (gemm_persistent(work_upper, sm_count_now())) {
+    switch (tn) {
+      case 16: rc = launch_gemm_persistent<16>(tw, tx, p, work_upper, st); break;
+      case 32: rc = launch_gemm_persistent<32>(tw, tx, p, work_upper, st); break;
+      case 64: rc = launch_gemm_persistent<64>(tw, tx, p, work_upper, st); break;
+      default: rc = launch_gemm_persistent<128>(tw, tx, p, work_upper, st); break;
+    }
+    if (rc != EB_OK) return rc;
+    if (splits_used) *splits_used = p.splits;
+    if (p.splits > 1 && !splits_used) {
+      const int64_t total = (int64_t)a->rows * a->N;
+      EB_CUDA(eb::launch(gemm_splitk_reduce_kernel, dim3((unsigned)eb::cdiv(total, 256)), dim3(256), 0, st, p.y_part, p.y, p.ldy,
+                         a->rows, a->N, p.splits));
+    }
+    return EB_OK;
+  }
   const dim3 grid((unsigned)token_tiles, (unsigned)nb, (unsigned)p.splits);  // token tile fastest: CTAs sharing a weight tile run together
   switch (tn) {
     case 16: rc = launch_gemm<16>(tw, tx, p, grid, st); break;

@@ -161,14 +161,17 @@ def gemm_workspace(rows, N, n_groups) -> int:
     return int(b.value)
 
 
-def gemm_fp8(d_x8, d_sx, d_w8, d_sw, d_y, rows, N, K, *, ldy=None, n_groups=1, d_seg_off=None, d_work=None,
+def gemm_fp8(d_x8, d_sx, d_w8, d_sw, d_y, rows, N, K, *, ldy=None, n_groups=1, d_seg_off=None, work=None,
              tile_tokens=0, splits=0, stream=None) -> None:
-    """eb_gemm_fp8_block (n_groups == 1, no segments) or eb_gemm_fp8_grouped."""
+    """eb_gemm_fp8_block (n_groups == 1, no segments) or eb_gemm_fp8_grouped.  `work` is the DeviceBuffer lent as
+    workspace (its size travels with the call, the library refuses what would not fit)."""
+    d_work, work_bytes = (work.ptr, work.nbytes) if work is not None else (None, 0)
     a = GemmArgs()
     a.d_x8, a.d_sx, a.d_w8, a.d_sw, a.d_y = d_x8, d_sx, d_w8, d_sw, d_y
     a.ldy = N if ldy is None else ldy
     a.rows, a.N, a.K, a.n_groups = rows, N, K, n_groups
     a.d_seg_off, a.d_work, a.tile_tokens, a.splits = d_seg_off, d_work, tile_tokens, splits
+    a.work_bytes = work_bytes
     call("eb_gemm_fp8_grouped" if d_seg_off is not None else "eb_gemm_fp8_block", C.byref(a), c_vp(stream))
 
 

@@ -44,7 +44,7 @@
 extern "C" {
 #endif
 
-#define EB_ABI_VERSION 2
+#define EB_ABI_VERSION 3
 
 /* status codes (negative: host validation) */
 #define EB_OK 0
@@ -255,6 +255,8 @@ typedef struct eb_gemm_args {
   int32_t tile_tokens;        /* 0 = choose; else 16, 32, 64 or 128 tokens per tile */
   int32_t splits;             /* dense: 0 = choose, else K splits (needs d_work) */
   int32_t tiles_ready;        /* grouped: 1 = d_work already holds eb_gemm_group_tiles() output for these segments */
+  size_t work_bytes;          /* bytes the caller owns at d_work; a call that would need more is refused (explicit
+                                 splits, grouped) or falls back to fewer K splits (splits = 0) */
 } eb_gemm_args;
 
 /* K4.  Y = X * W^T, e4m3 x e4m3 -> fp32 with per-128x128 block scales, bf16 out (tcgen05 tensor cores). */

@@ -53,7 +53,7 @@ def test_gemm_dense_small_m_matches_oracle(gpu, M):
     d_work = DeviceBuffer(host.gemm_workspace(M, N, 1))
     for splits, tn in ((1, 0), (0, 0), (4, 0), (1, 128), (1, 16)):
         d_y.zero()
-        host.gemm_fp8(d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d_y.ptr, M, N, K, d_work=d_work.ptr, splits=splits,
+        host.gemm_fp8(d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d_y.ptr, M, N, K, work=d_work, splits=splits,
                       tile_tokens=tn)
         got = d_y.to_array(np.uint16, (M, N))
         # outputs are O(100): compare relative to the bf16 grid of the value
@@ -122,6 +122,28 @@ def test_gemm_grouped_matches_oracle(gpu, tn):
     assert np.array_equal(d_sx.to_array(np.float32, sx.shape), sx)
     d_y.zero()
     host.gemm_fp8(d_x8.ptr, d_sx.ptr, d_w8.ptr, d_sw.ptr, d_y.ptr, R, N, K, n_groups=G, d_seg_off=d_seg.ptr,
-                  d_work=d_work.ptr, tile_tokens=tn)
+                  work=d_work, tile_tokens=tn)
     got = d_y.to_array(np.uint16, (R, N))
     assert_close_bf16(got, want, atol=1e-3, rtol=G_RTOL, what=f"grouped tn={tn}")
+
+
+def test_gemm_workspace_too_small_is_refused_or_degrades(gpu):
+    """The workspace size travels with the call: explicit K splits that would not fit are refused before any launch,
+    automatic splitting falls back to what fits, and a grouped call with too little room for its tile table is refused."""
+    import eidola_b200.host as host
+    from eidola_b200.capi import DeviceBuffer, EbError
+    M, N, K = 8, 5120, 2880
+    x8, sx, w8, sw = _sweep_inputs(M, N, K, seed=5)
+    want = orc.gemm_fp8_block(x8, sx, w8, sw)
+    d = [_dev(a) for a in (x8, sx, w8, sw)]
+    d_y = DeviceBuffer(M * N * 2)
+    small = DeviceBuffer(M * N * 4)  # room for one partial plane only
+    with pytest.raises(EbError):
+        host.gemm_fp8(d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d_y.ptr, M, N, K, work=small, splits=4)
+    host.gemm_fp8(d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d_y.ptr, M, N, K, work=small, splits=0)
+    assert_close_bf16(d_y.to_array(np.uint16, (M, N)), want, atol=G_ATOL, rtol=G_RTOL, what="auto splits, small workspace")
+    seg = _dev(np.array([0, 3, 8], np.int32))
+    w2 = _dev(np.concatenate([w8[:256], w8[256:512]]))
+    with pytest.raises(EbError):
+        host.gemm_fp8(d[0].ptr, d[1].ptr, w2.ptr, d[3].ptr, d_y.ptr, M, 256, K, n_groups=2, d_seg_off=seg.ptr,
+                      work=DeviceBuffer(8))

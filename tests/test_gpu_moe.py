@@ -91,11 +91,11 @@ def test_moe_pipeline_matches_oracle(gpu):
     assert np.array_equal(d_xp8.to_array(np.uint8, (R, H)), want_xp8)
     assert np.array_equal(d_sxp.to_array(np.float32, want_sxp.shape), want_sxp)
     host.gemm_fp8(d_xp8.ptr, d_sxp.ptr, d_w1c.ptr, d_w1s.ptr, d_gu.ptr, R, 2 * I, H, n_groups=E, d_seg_off=d_seg.ptr,
-                  d_work=d_ws.ptr)
+                  work=d_ws)
     _call("eb_quant_silu_mul_block128", c_vp(d_gu.ptr), c_i64(2 * I), c_i32(R), c_i32(I), c_vp(d_seg.ptr), c_i32(E),
           c_vp(d_a8.ptr), c_vp(d_sa.ptr), None)
     host.gemm_fp8(d_a8.ptr, d_sa.ptr, d_w2c.ptr, d_w2s.ptr, d_y.ptr, R, H, I, n_groups=E, d_seg_off=d_seg.ptr,
-                  d_work=d_ws.ptr)
+                  work=d_ws)
     _call("eb_moe_combine", c_vp(d_y.ptr), c_vp(d_perm.ptr), c_vp(d_w.ptr), c_i32(T), c_i32(k), c_i32(H), c_vp(d_x.ptr), None)
     got_x = d_x.to_array(np.uint16, (T, H))
     # expert outputs are O(0.01); the residual stream is O(1): compare the stream with the usual bf16 bound and the
