@@ -494,6 +494,225 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
   if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Prefill-sized dense GEMM (hundreds of tokens and more): compute bound, so the tile is as large as one CTA's
+// tensor memory allows.  Tokens are the MMA's M operand here (128 per tile) and 256 weight rows its N operand:
+// a thread of the epilogue then owns one token and 128 consecutive outputs, which it stores as 16-byte vectors.
+// One persistent CTA per SM, 384 threads in three warpgroups: warpgroup 0 holds the TMA producer (warp 0) and the
+// MMA issuer (warp 1) and gives its registers away; warpgroups 1 and 2 are the epilogue (tensor-memory lane
+// quarter = warp % 4, warpgroup 1 takes accumulator columns 0..127 and warpgroup 2 columns 128..255) and claim
+// 232 registers per thread for the 128 running sums plus two 32-column loads in flight.
+constexpr int kBigThreads = 384;
+constexpr int kBigTokens = 128;  // MMA M
+constexpr int kBigRows = 256;    // weight rows per tile, MMA N
+constexpr int kBigStages = 4;
+constexpr int kBigStageBytes = (kBigTokens + kBigRows) * kBlockK;
+constexpr size_t kBigSmem = 1024 + (size_t)kBigStages * kBigStageBytes + 256;
+
+// 32 lanes x 32 consecutive columns, issued without waiting; tmem_wait32 makes the registers valid.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+// Waits for this thread's tensor-memory loads; the registers pass through so that no use is scheduled before it.
+__device__ __forceinline__ void tmem_wait32(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+#define EB_R8(a, o) "=r"(a[o]), "=r"(a[o + 1]), "=r"(a[o + 2]), "=r"(a[o + 3]), "=r"(a[o + 4]), "=r"(a[o + 5]), "=r"(a[o + 6]), "=r"(a[o + 7])
+#define EB_RW8(a, o) "+r"(a[o]), "+r"(a[o + 1]), "+r"(a[o + 2]), "+r"(a[o + 3]), "+r"(a[o + 4]), "+r"(a[o + 5]), "+r"(a[o + 6]), "+r"(a[o + 7])
+// 32 lanes x 64 consecutive columns, issued without waiting; tmem_wait64 makes the registers valid.
+__device__ __forceinline__ void tmem_ld64_issue(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,"
+      "%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+      : EB_R8(r, 0), EB_R8(r, 8), EB_R8(r, 16), EB_R8(r, 24), EB_R8(r, 32), EB_R8(r, 40), EB_R8(r, 48), EB_R8(r, 56)
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait64(uint32_t (&r)[64]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : EB_RW8(r, 0), EB_RW8(r, 8), EB_RW8(r, 16), EB_RW8(r, 24), EB_RW8(r, 32), EB_RW8(r, 40), EB_RW8(r, 48),
+                 EB_RW8(r, 56)
+               :
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kBigThreads, 1)
+gemm_fp8_big_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
+  constexpr int S = kBigStages, NBUF = 2;
+  const int KB = (p.K + kBlockK - 1) / kBlockK;
+  const int NB2 = (p.N + kBigRows - 1) / kBigRows;
+  const int NB = (p.N + kTileN - 1) / kTileN;  // scale blocks along N
+  const int TT = (p.rows + kBigTokens - 1) / kBigTokens;
+  const int n_work = TT * NB2;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t stage0 = (raw + 1023u) & ~1023u;
+  uint8_t* after = smem_raw + (stage0 - raw) + S * kBigStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after);  // full[S], empty[S], tfull[NBUF], tempty[NBUF]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(after + (2 * S + 2 * NBUF) * sizeof(uint64_t));
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[S]);
+  const uint32_t bar_tfull = smem_u32(&bars[2 * S]), bar_tempty = smem_u32(&bars[2 * S + NBUF]);
+  if (tid == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < NBUF; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, 8);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0 && lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const int row0 = (w % TT) * kBigTokens, n0 = (w / TT) * kBigRows;
+        for (int i = 0; i < KB; ++i, ++it) {
+          const uint32_t s = it % S;
+          if (it >= (uint32_t)S && !mbar_wait(bar_empty + 8 * s, ((it / S) - 1) & 1, &abort_flag, p.status)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = stage0 + s * kBigStageBytes, b_dst = a_dst + kBigTokens * kBlockK;
+          mbar_arrive_expect_tx(bar_full + 8 * s, kBigStageBytes);
+          tma_load_2d(a_dst, &tm_x, i * kBlockK, row0, bar_full + 8 * s);
+          tma_load_2d(b_dst, &tm_w, i * kBlockK, n0, bar_full + 8 * s);
+        }
+      }
+    } else if (warp == 1 && lane == 0) {
+      constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(kBigRows >> 3) << 17) | ((uint32_t)(kBigTokens >> 4) << 24);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        for (int i = 0; i < KB; ++i, ++it) {
+          const uint32_t s = it % S, b = it % NBUF;
+          if (!mbar_wait(bar_full + 8 * s, (it / S) & 1, &abort_flag, p.status) ||
+              (it >= (uint32_t)NBUF && !mbar_wait(bar_tempty + 8 * b, ((it / NBUF) - 1) & 1, &abort_flag, p.status))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = stage0 + s * kBigStageBytes, b_addr = a_addr + kBigTokens * kBlockK;
+          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            tc_mma_f8(tmem_base + b * kBigRows, da + 2 * k, db + 2 * k, idesc, k > 0 ? 1u : 0u);
+          tc_commit(bar_empty + 8 * s);
+          tc_commit(bar_tfull + 8 * b);
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int q = warp & 3, h = (warp - 4) >> 2;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + h * 128;
+    const bool vec_ok = (p.ldy % 8 == 0) && (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+      const int tt = w % TT, row0 = tt * kBigTokens, n0 = (w / TT) * kBigRows + h * 128;
+      float sreg[kMaxKB / 32];
+      {
+        const int nblk = min(n0 / kTileN, NB - 1);
+        const float* swr = p.sw + (int64_t)nblk * KB;
+        const float* sxr = p.sx + (int64_t)tt * KB;
+#pragma unroll
+        for (int j = 0; j < kMaxKB / 32; ++j) {
+          const int kb = lane + 32 * j;
+          sreg[j] = kb < KB ? swr[kb] * sxr[kb] : 0.f;
+        }
+      }
+      float acc[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      for (int i = 0; i < KB; ++i, ++it) {
+        const uint32_t b = it % NBUF;
+        if (!mbar_wait(bar_tfull + 8 * b, (it / NBUF) & 1, &abort_flag, p.status)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const int jr = i >> 5;
+        const float mine = jr == 0 ? sreg[0] : jr == 1 ? sreg[1] : jr == 2 ? sreg[2] : sreg[3];
+        const float sc = __shfl_sync(0xffffffffu, mine, i & 31);
+        const uint32_t src = lane_base + b * kBigRows;
+        uint32_t v[64];
+        tmem_ld64_issue(src, v);
+        tmem_wait64(v);
+#pragma unroll
+        for (int j = 0; j < 64; ++j) acc[j] = fmaf(sc, __uint_as_float(v[j]), acc[j]);
+        tmem_ld64_issue(src + 64, v);
+        tmem_wait64(v);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * b);  // the accumulator buffer is free before the last 64 sums
+#pragma unroll
+        for (int j = 0; j < 64; ++j) acc[64 + j] = fmaf(sc, __uint_as_float(v[j]), acc[64 + j]);
+      }
+      const int r = row0 + q * 32 + lane;
+      if (ok && r < p.rows && n0 < p.N) {
+        uint16_t* yr = p.y + (int64_t)r * p.ldy + n0;
+        if (vec_ok) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            if (n0 + c * 8 < p.N) {
+              uint32_t h4[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(h4[j]) : "f"(acc[c * 8 + 2 * j + 1]), "f"(acc[c * 8 + 2 * j]));
+              *reinterpret_cast<uint4*>(yr + c * 8) = make_uint4(h4[0], h4[1], h4[2], h4[3]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 128; ++j)
+            if (n0 + j < p.N) {
+              uint32_t hh;
+              asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hh) : "f"(0.f), "f"(acc[j]));
+              yr[j] = (uint16_t)(hh & 0xFFFFu);
+            }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
 // Sum split-K partials in split order and round to bf16.
 __global__ void gemm_splitk_reduce_kernel(const float* part, uint16_t* y, int64_t ldy, int rows, int N, int splits) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
@@ -720,6 +939,16 @@ int32_t launch_gemm_persistent(const CUtensorMap& tw, const CUtensorMap& tx, con
   return EB_OK;
 }
 
+// Dense GEMMs of 512 tokens and more take the 128-token x 256-row kernel unless the caller fixed a tile or a split.
+// EIDOLA_B200_GEMM_BIG=0 keeps them on the decode kernels (for A/B timing).
+bool gemm_big(int rows, int tile_tokens, int splits) {
+  static const bool on = [] {
+    const char* v = getenv("EIDOLA_B200_GEMM_BIG");
+    return !(v && v[0] == '0');
+  }();
+  return on && rows >= 512 && tile_tokens == 0 && splits <= 1;
+}
+
 int pick_tn(int64_t rows_per_group) {
   if (rows_per_group <= 16) return 16;
   if (rows_per_group <= 32) return 32;
@@ -780,6 +1009,8 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
   } else {
     tn = a->tile_tokens ? a->tile_tokens : pick_tn(a->rows);
     EB_REQUIRE(tn == 16 || tn == 32 || tn == 64 || tn == 128, EB_ERR_ARG, "gemm: tile_tokens %d not in {16,32,64,128}", tn);
+    // a GEMM too small to fill the GPU with 128-token tiles runs 64-token tiles before it splits K: no partial planes
+    if (!a->tile_tokens && a->splits == 0 && tn == 128 && nb * ((a->rows + 127) / 128) < 120 && a->rows > 64) tn = 64;
     token_tiles = (a->rows + tn - 1) / tn;
     // split K when the tiles alone cannot fill the GPU and the caller lent a partial buffer
     int splits = a->splits;
@@ -802,6 +1033,29 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
     p.y_part = (float*)a->d_work;
   }
   EB_REQUIRE(nb <= 65535, EB_ERR_UNSUPPORTED, "gemm: %d weight tiles exceed the grid", nb);
+
+  if (!grouped && gemm_big(a->rows, a->tile_tokens, a->splits)) {
+    CUtensorMap bw, bx;
+    int32_t brc = eb::make_tmap_2d_sw128(&bw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, (uint64_t)a->N, (uint64_t)a->K,
+                                         (uint64_t)a->K, kBigRows);
+    if (brc != EB_OK) return brc;
+    brc = eb::make_tmap_2d_sw128(&bx, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_x8, (uint64_t)a->rows, (uint64_t)a->K, (uint64_t)a->K,
+                                 kBigTokens);
+    if (brc != EB_OK) return brc;
+    static bool configured[64] = {false};  // the attribute is per device
+    int dev = 0;
+    EB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+      EB_CUDA(cudaFuncSetAttribute(gemm_fp8_big_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBigSmem));
+      if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    const int64_t work = (int64_t)((a->rows + kBigTokens - 1) / kBigTokens) * ((a->N + kBigRows - 1) / kBigRows);
+    const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(work, sm_count_now()));
+    p.splits = 1;
+    EB_CUDA(eb::launch(gemm_fp8_big_kernel, dim3(grid), dim3(kBigThreads), kBigSmem, st, bw, bx, p));
+    if (splits_used) *splits_used = 1;
+    return EB_OK;
+  }
 
   CUtensorMap tw, tx;
   int32_t rc = eb::make_tmap_2d_sw128(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, (uint64_t)a->n_groups * a->N,

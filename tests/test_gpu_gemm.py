@@ -147,3 +147,40 @@ def test_gemm_workspace_too_small_is_refused_or_degrades(gpu):
     with pytest.raises(EbError):
         host.gemm_fp8(d[0].ptr, d[1].ptr, w2.ptr, d[3].ptr, d_y.ptr, M, 256, K, n_groups=2, d_seg_off=seg.ptr,
                       work=DeviceBuffer(8))
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 5120, 2880), (600, 2880, 512), (513, 200, 4096)])
+def test_gemm_dense_prefill_sized_matches_oracle(gpu, M, N, K):
+    """512 tokens and more run on the 128-token x 256-row kernel: ragged token and weight-row edges included."""
+    import eidola_b200.host as host
+    from eidola_b200.capi import DeviceBuffer
+    x8, sx, w8, sw = _sweep_inputs(M, N, K, seed=6)
+    want = orc.gemm_fp8_block(x8, sx, w8, sw)
+    d = [_dev(a) for a in (x8, sx, w8, sw)]
+    d_y = DeviceBuffer(M * N * 2)
+    host.gemm_fp8(d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d_y.ptr, M, N, K)
+    assert_close_bf16(d_y.to_array(np.uint16, (M, N)), want, atol=G_ATOL, rtol=G_RTOL, what=f"M={M} N={N} K={K}")
+    # a row pitch that rules out 16-byte stores
+    ldy = N + 3
+    d_y2 = DeviceBuffer(M * ldy * 2)
+    d_y2.zero()
+    host.gemm_fp8(d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d_y2.ptr, M, N, K, ldy=ldy)
+    got = d_y2.to_array(np.uint16, (M, ldy))
+    assert np.array_equal(got[:, :N], d_y.to_array(np.uint16, (M, N)))
+    assert not got[:, N:].any()
+
+
+def test_gemm_prefill_sized_power_of_two_scales_exact(gpu):
+    import eidola_b200.host as host
+    from eidola_b200.capi import DeviceBuffer
+    rng = np.random.default_rng(4)
+    M, N, K = 640, 384, 320
+    x8 = orc.e4m3_encode(rng.integers(-3, 4, size=(M, K)).astype(np.float32))
+    w8 = orc.e4m3_encode(rng.integers(-3, 4, size=(N, K)).astype(np.float32))
+    sx = (2.0 ** rng.integers(-2, 3, size=(5, 3))).astype(np.float32)
+    sw = (2.0 ** rng.integers(-2, 3, size=(3, 3))).astype(np.float32)
+    want = orc.gemm_fp8_block(x8, sx, w8, sw)
+    d = [_dev(a) for a in (x8, sx, w8, sw)]
+    d_y = DeviceBuffer(M * N * 2)
+    host.gemm_fp8(d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d_y.ptr, M, N, K)
+    assert np.array_equal(d_y.to_array(np.uint16, (M, N)), want)
