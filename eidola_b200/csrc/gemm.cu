@@ -144,32 +144,20 @@ struct Cfg {
 template <int TN>
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
-  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  // Programmatic dependent launch: this grid may start while its predecessor in the stream drains.  Everything up
+  // to pdl_wait() touches no memory the predecessor writes: barriers, tensor memory and (dense mode) the first
+  // stages' weight tiles, which no kernel of the step produces.
   eb::pdl_trigger();
   using C = Cfg<TN>;
   constexpr int S = C::kStages;
-
-  // ---- which tile
-  int g = 0, row0, row_end, xblk;
-  if (p.n_groups > 1 || p.seg_off) {
-    const int t = blockIdx.x;
-    if (t >= *p.n_tiles) return;
-    g = p.tile_group[t];
-    row0 = p.tile_row0[t];
-    row_end = p.seg_off[g + 1];
-    xblk = p.blk_off[g] + (row0 - p.seg_off[g]) / 128;
-  } else {
-    row0 = blockIdx.x * TN;
-    row_end = p.rows;
-    xblk = row0 / 128;
-  }
+  const bool grouped = p.n_groups > 1 || p.seg_off;
   const int nb = blockIdx.y, n0 = nb * kTileN;
   const int KB = (p.K + kBlockK - 1) / kBlockK;
   const int NB = (p.N + kTileN - 1) / kTileN;
   const int split = blockIdx.z;
   const int kb_per = (KB + p.splits - 1) / p.splits;
   const int kb0 = split * kb_per, kb1 = min(KB, kb0 + kb_per);
-  const int nkb = max(0, kb1 - kb0);
+  int nkb = max(0, kb1 - kb0);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -184,7 +172,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
   const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[S]);
   const uint32_t bar_tfull = smem_u32(&bars[2 * S]), bar_tempty = smem_u32(&bars[2 * S + 2]);
 
-  const int wy = g * p.N + n0;
   int prefilled = 0;
   if (tid == 0) {
     abort_flag = 0;
@@ -198,17 +185,48 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    // Fill the pipeline before the rest of the CTA has finished setting up (tensor-memory allocation, scale
-    // products): the first stages are in flight one barrier round trip earlier.
-    prefilled = min(S, nkb);
-    for (int i = 0; i < prefilled; ++i) {
-      const uint32_t a_dst = stage0 + i * C::kStageBytes, b_dst = a_dst + kTileN * kBlockK;
-      mbar_arrive_expect_tx(bar_full + 8 * i, C::kStageBytes);
-      tma_load_2d(a_dst, &tm_w, (kb0 + i) * kBlockK, wy, bar_full + 8 * i);
-      tma_load_2d(b_dst, &tm_x, (kb0 + i) * kBlockK, row0, bar_full + 8 * i);
+    if (!grouped) {  // the weight half of the first stages, ahead of the predecessor's completion
+      prefilled = min(S, nkb);
+      for (int i = 0; i < prefilled; ++i) {
+        mbar_arrive_expect_tx(bar_full + 8 * i, C::kStageBytes);
+        tma_load_2d(stage0 + i * C::kStageBytes, &tm_w, (kb0 + i) * kBlockK, n0, bar_full + 8 * i);
+      }
     }
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+  eb::pdl_wait();  // the predecessor in the stream has completed and its writes are visible
+
+  // ---- which tile
+  int g = 0, row0 = 0, row_end = 0, xblk = 0;
+  if (grouped) {
+    const int t = blockIdx.x;
+    if (t < *p.n_tiles) {
+      g = p.tile_group[t];
+      row0 = p.tile_row0[t];
+      row_end = p.seg_off[g + 1];
+      xblk = p.blk_off[g] + (row0 - p.seg_off[g]) / 128;
+    } else {
+      nkb = 0;  // no such tile: fall through to the common exit
+    }
+  } else {
+    row0 = blockIdx.x * TN;
+    row_end = p.rows;
+    xblk = row0 / 128;
+  }
+  const int wy = g * p.N + n0;
+  if (tid == 0) {
+    // Fill the pipeline before the rest of the CTA has finished setting up (scale products, the set-up barrier):
+    // the first stages are in flight one barrier round trip earlier.
+    if (grouped) {
+      prefilled = min(S, nkb);
+      for (int i = 0; i < prefilled; ++i) {
+        mbar_arrive_expect_tx(bar_full + 8 * i, C::kStageBytes);
+        tma_load_2d(stage0 + i * C::kStageBytes, &tm_w, (kb0 + i) * kBlockK, wy, bar_full + 8 * i);
+      }
+    }
+    for (int i = 0; i < prefilled; ++i)
+      tma_load_2d(stage0 + i * C::kStageBytes + kTileN * kBlockK, &tm_x, (kb0 + i) * kBlockK, row0, bar_full + 8 * i);
+  }
   if (tid >= 64) {
     const float* swr = p.sw + ((int64_t)g * NB + nb) * KB;
     const float* sxr = p.sx + (int64_t)xblk * KB;
@@ -341,15 +359,11 @@ template <int TN>
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                            const GemmParams p) {
-  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
-  eb::pdl_trigger();
+  eb::pdl_trigger();  // programmatic dependent launch: set-up below overlaps the predecessor's tail
   using C = PCfg<TN>;
   constexpr int S = C::kStages, NBUF = C::kBufs;
   const int KB = (p.K + kBlockK - 1) / kBlockK;
   const int NB = (p.N + kTileN - 1) / kTileN;
-  const int TT = p.seg_off ? *p.n_tiles : (p.rows + TN - 1) / TN;
-  const int n_work = TT * NB * p.splits;
-  if ((int)blockIdx.x >= n_work) return;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -380,6 +394,9 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  eb::pdl_wait();  // the predecessor in the stream has completed and its writes are visible
+  const int TT = p.seg_off ? *p.n_tiles : (p.rows + TN - 1) / TN;
+  const int n_work = TT * NB * p.splits;  // a CTA beyond the work list runs no loop iteration and leaves below
 
   if (warp == 0) {
     if (lane == 0) {
@@ -509,28 +526,6 @@ constexpr int kBigStages = 4;
 constexpr int kBigStageBytes = (kBigTokens + kBigRows) * kBlockK;
 constexpr size_t kBigSmem = 1024 + (size_t)kBigStages * kBigStageBytes + 256;
 
-// 32 lanes x 32 consecutive columns, issued without waiting; tmem_wait32 makes the registers valid.
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
-      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-// Waits for this thread's tensor-memory loads; the registers pass through so that no use is scheduled before it.
-__device__ __forceinline__ void tmem_wait32(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
-                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
-                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
-                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
-}
-
 #define EB_R8(a, o) "=r"(a[o]), "=r"(a[o + 1]), "=r"(a[o + 2]), "=r"(a[o + 3]), "=r"(a[o + 4]), "=r"(a[o + 5]), "=r"(a[o + 6]), "=r"(a[o + 7])
 #define EB_RW8(a, o) "+r"(a[o]), "+r"(a[o + 1]), "+r"(a[o + 2]), "+r"(a[o + 3]), "+r"(a[o + 4]), "+r"(a[o + 5]), "+r"(a[o + 6]), "+r"(a[o + 7])
 // 32 lanes x 64 consecutive columns, issued without waiting; tmem_wait64 makes the registers valid.
@@ -552,8 +547,7 @@ __device__ __forceinline__ void tmem_wait64(uint32_t (&r)[64]) {
 
 __global__ void __launch_bounds__(kBigThreads, 1)
 gemm_fp8_big_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const GemmParams p) {
-  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
-  eb::pdl_trigger();
+  eb::pdl_trigger();  // programmatic dependent launch: set-up below overlaps the predecessor's tail
   constexpr int S = kBigStages, NBUF = 2;
   const int KB = (p.K + kBlockK - 1) / kBlockK;
   const int NB2 = (p.N + kBigRows - 1) / kBigRows;
@@ -590,6 +584,7 @@ gemm_fp8_big_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  eb::pdl_wait();  // the predecessor in the stream has completed and its writes are visible
 
   if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");

@@ -259,7 +259,9 @@ typedef struct eb_gemm_args {
                                  splits, grouped) or falls back to fewer K splits (splits = 0) */
 } eb_gemm_args;
 
-/* K4.  Y = X * W^T, e4m3 x e4m3 -> fp32 with per-128x128 block scales, bf16 out (tcgen05 tensor cores). */
+/* K4.  Y = X * W^T, e4m3 x e4m3 -> fp32 with per-128x128 block scales, bf16 out (tcgen05 tensor cores).
+ * The weights (d_w8, d_sw) must be complete when the call is made: the kernel may fetch them before the work queued
+ * ahead of it on the stream has finished (activations and scales of X are read only after it has). */
 int32_t eb_gemm_fp8_block(const eb_gemm_args* a, void* stream);
 /* K6.  The same per group g on rows [d_seg_off[g], d_seg_off[g+1]) with weights W[g]; activation scale blocks
  * restart at each segment start (the numbering eb_quant_act_block128 uses). */
