@@ -275,7 +275,7 @@ class Spec120bWorkload:
         ctx = self.lens + 5
         dense = (64 + 16) * 64 * 2880 + 2880 * 4096
         experts = c.n_experts * 3 * 2880 * 2880
-        weights = c.n_layers * (dense + experts) // G + c.n_layers * c.n_experts * 2880 * 2 + c.vocab * 2880
+        weights = c.n_layers * (dense + experts) // G + c.n_layers * c.n_experts * 2880 * 2 // G + c.vocab * 2880 // G
         kv_full = (c.n_layers // 2) * int(ctx.sum()) * 2048 // G
         kv_win = (c.n_layers - c.n_layers // 2) * int(np.minimum(ctx, 128 + 5 + PAGE).sum()) * 2048 // G
         return {"weights": weights, "kv_full": kv_full, "kv_window": kv_win, "total": weights + kv_full + kv_win,
@@ -285,7 +285,8 @@ class Spec120bWorkload:
         return {"workload": self.name, "n_seqs": int(len(self.ctx0)), "n_layers": int(self.cfg.n_layers),
                 "mean_context": float(self.lens.mean()), "device_bytes_per_rank": self.mem,
                 "prefill": "KV pages filled with seeded N(0,1) values (stand-in for prefill)",
-                "parallelism": "tp%d (heads) x ep%d (experts), 2 fp32 all-reduces of [2560, 2880] per layer" % (self.world, self.world)}
+                "parallelism": "tp%d (heads) x ep%d (experts); per layer 2 fp32 all-reduces of [2560, 2880] and one all-gather of the "
+                               "token-sharded routing; vocabulary-parallel LM head with an all-gather of argmax candidates" % (self.world, self.world)}
 
 
 # ------------------------------------------------------------------------------------------ attention workload

@@ -23,6 +23,9 @@ struct NcclApi {
   ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
   ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
   bool ok = false;
 };
@@ -41,10 +44,13 @@ NcclApi& api() {
     EB_SYM(CommAbort, "ncclCommAbort");
     EB_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
     EB_SYM(AllReduce, "ncclAllReduce");
+    EB_SYM(AllGather, "ncclAllGather");
+    EB_SYM(GroupStart, "ncclGroupStart");
+    EB_SYM(GroupEnd, "ncclGroupEnd");
     EB_SYM(GetErrorString, "ncclGetErrorString");
 #undef EB_SYM
     a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.CommAbort && a.CommGetAsyncError && a.AllReduce &&
-           a.GetErrorString;
+           a.AllGather && a.GroupStart && a.GroupEnd && a.GetErrorString;
   });
   return a;
 }
@@ -111,6 +117,25 @@ int32_t eb_comm_allreduce_f32(eb_comm* c, void* d_buf, int64_t count, void* stre
   EB_REQUIRE(c && d_buf && count >= 0, EB_ERR_ARG, "eb_comm_allreduce_f32: bad argument");
   if (count == 0 || c->size == 1) return EB_OK;
   EB_NCCL(api().AllReduce(d_buf, d_buf, (size_t)count, ncclFloat32, ncclSum, c->comm, eb::as_stream(stream)));
+  return EB_OK;
+}
+
+// In-place all-gather of up to two buffers in one NCCL group: rank r's `bytes_per_rank` bytes already sit at offset
+// r * bytes_per_rank of each buffer; on return every rank holds all `size` slices.  d_b may be null.
+int32_t eb_comm_allgather(eb_comm* c, void* d_a, void* d_b, int64_t bytes_per_rank, void* stream) {
+  EB_REQUIRE(c && d_a && bytes_per_rank >= 0, EB_ERR_ARG, "eb_comm_allgather: bad argument");
+  if (bytes_per_rank == 0 || c->size == 1) return EB_OK;
+  EB_NCCL(api().GroupStart());
+  ncclResult_t r1 = api().AllGather((const char*)d_a + (size_t)c->rank * bytes_per_rank, d_a, (size_t)bytes_per_rank, ncclInt8,
+                                    c->comm, eb::as_stream(stream));
+  ncclResult_t r2 = ncclSuccess;
+  if (d_b && r1 == ncclSuccess)
+    r2 = api().AllGather((const char*)d_b + (size_t)c->rank * bytes_per_rank, d_b, (size_t)bytes_per_rank, ncclInt8, c->comm,
+                         eb::as_stream(stream));
+  ncclResult_t r3 = api().GroupEnd();
+  EB_NCCL(r1);
+  EB_NCCL(r2);
+  EB_NCCL(r3);
   return EB_OK;
 }
 

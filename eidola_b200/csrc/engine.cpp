@@ -56,6 +56,8 @@ struct eb_engine {
   int tp_rank = 0, tp_size = 1;
   eb_comm* comm = nullptr;
   int hq_l = 0, hkv_l = 0, e_l = 0, e0 = 0;
+  int v0 = 0, v1 = 0;      // vocabulary rows [v0, v1) of the LM head live on this rank (whole 128-row scale blocks)
+  float* cand = nullptr;   // argmax candidates of every rank's vocabulary slice: [tp_size][max_tokens][4]
   int kv_band = 0, k_col0 = 0, v_col0 = 0;  // the K and V bands of the local QKV row start on 128-row scale blocks
   float* ar_buf = nullptr;                   // fp32 [max_tokens][hidden] summed across ranks
   int32_t* r_idx_local = nullptr;
@@ -191,8 +193,9 @@ int32_t init_weights(eb_engine* e) {
   }
   EB_TRY(dev_alloc(e, &e->embed, (size_t)c.vocab * H, &e->weight_bytes));
   EB_TRY(eb_synth_normal_bf16(e->embed, (int64_t)c.vocab * H, c.seed, sid(-1, K_EMBED, 0), 0, c.init_std, st));
-  EB_TRY(alloc_fp8(e, &e->lm, 1, c.vocab, H));
-  EB_TRY(eb_synth_weight_fp8(e->lm.codes, e->lm.scales, c.vocab, H, 0, c.vocab, c.seed, sid(-1, K_LMHEAD, 0), c.init_std, st));
+  EB_TRY(alloc_fp8(e, &e->lm, 1, e->v1 - e->v0, H));
+  EB_TRY(eb_synth_weight_fp8(e->lm.codes, e->lm.scales, c.vocab, H, e->v0, e->v1 - e->v0, c.seed, sid(-1, K_LMHEAD, 0), c.init_std,
+                             st));
   EB_TRY(dev_alloc(e, &e->g_final, (size_t)H, &e->weight_bytes));
   EB_TRY(fill_ones(e, e->g_final, H));
   // rotary table
@@ -230,10 +233,15 @@ int32_t init_work(eb_engine* e) {
   EB_TRY(dev_alloc(e, &e->sa, (size_t)(tb * e->kbA), w));
   EB_TRY(dev_alloc(e, &e->sxp, (size_t)(rb * e->kbH), w));
   EB_TRY(dev_alloc(e, &e->sact, (size_t)(rb * e->kbI), w));
-  EB_TRY(dev_alloc(e, &e->r_idx, (size_t)R, w));
+  // routing is computed on a token slice per rank and all-gathered in place: room for tp_size equal chunks
+  const size_t r_cap = (size_t)R + (size_t)e->tp_size * c.top_k;
+  EB_TRY(dev_alloc(e, &e->r_idx, r_cap, w));
   EB_TRY(dev_alloc(e, &e->r_idx_local, (size_t)R, w));
-  if (e->tp_size > 1) EB_TRY(dev_alloc(e, &e->ar_buf, (size_t)T * H, w));
-  EB_TRY(dev_alloc(e, &e->r_wts, (size_t)R, w));
+  if (e->tp_size > 1) {
+    EB_TRY(dev_alloc(e, &e->ar_buf, (size_t)T * H, w));
+    EB_TRY(dev_alloc(e, &e->cand, (size_t)e->tp_size * T * 4, w));
+  }
+  EB_TRY(dev_alloc(e, &e->r_wts, r_cap, w));
   EB_TRY(dev_alloc(e, &e->seg_off, (size_t)E + 1, w));
   EB_TRY(dev_alloc(e, &e->perm_row, (size_t)R, w));
   EB_TRY(dev_alloc(e, &e->row_token, (size_t)R, w));
@@ -327,14 +335,14 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   };
   // Dense GEMM; when `splits` is given the split-K partials are left in gemm_ws for a fused consumer.
   auto dense = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout,
-                   int32_t* splits) -> int32_t {
+                   int32_t* splits, int64_t ldy = 0) -> int32_t {
     eb_gemm_args g = {};
     g.d_x8 = x8;
     g.d_sx = sx;
     g.d_w8 = w.codes;
     g.d_sw = w.scales;
     g.d_y = yout;
-    g.ldy = N;
+    g.ldy = ldy ? ldy : N;
     g.rows = T;
     g.N = N;
     g.K = K;
@@ -442,7 +450,19 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf, 1, nullptr, e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
       n += 2;
     }
-    EB_TRY(eb_moe_route(e->h, L.wr, T, c.n_experts, H, c.top_k, e->r_idx, e->r_wts, nullptr, st));
+    if (!tp) {
+      EB_TRY(eb_moe_route(e->h, L.wr, T, c.n_experts, H, c.top_k, e->r_idx, e->r_wts, nullptr, st));
+    } else {
+      // every rank routes its slice of the (replicated) tokens, then the slices are gathered: the same bits as routing
+      // all tokens everywhere, at 1/tp_size of the work
+      const int chunk = (T + e->tp_size - 1) / e->tp_size;
+      const int t0 = std::min(T, e->tp_rank * chunk), nt = std::min(T, t0 + chunk) - t0;
+      if (nt > 0)
+        EB_TRY(eb_moe_route(e->h + (size_t)t0 * H, L.wr, nt, c.n_experts, H, c.top_k, e->r_idx + (size_t)t0 * c.top_k,
+                            e->r_wts + (size_t)t0 * c.top_k, nullptr, st));
+      EB_TRY(eb_comm_allgather(e->comm, e->r_idx, e->r_wts, (int64_t)chunk * c.top_k * 4, st));
+      n += 1;
+    }
     if (!tp) {
       EB_TRY(eb_moe_permute_tiles(e->r_idx, T, c.top_k, E, e->seg_off, e->perm_row, e->row_token, group_tn, e->group_ws, st));
     } else {
@@ -485,9 +505,20 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   }
   EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
   mark(4);
-  EB_TRY(dense(e->h8, e->sh, e->lm, c.vocab, H, e->logits, nullptr));
-  mark(-1);
-  EB_TRY(eb_argmax(e->logits, T, c.vocab, c.vocab, e->d_next, e->d_margin, st));
+  if (!tp) {
+    EB_TRY(dense(e->h8, e->sh, e->lm, c.vocab, H, e->logits, nullptr));
+    mark(-1);
+    EB_TRY(eb_argmax(e->logits, T, c.vocab, c.vocab, e->d_next, e->d_margin, st));
+  } else {
+    // vocabulary-parallel head: logits of this rank's rows only, one candidate per token and rank, merged everywhere
+    EB_TRY(dense(e->h8, e->sh, e->lm, e->v1 - e->v0, H, e->logits + e->v0, nullptr, c.vocab));
+    mark(-1);
+    const int64_t cap = c.max_tokens;
+    EB_TRY(eb_argmax_partial(e->logits + e->v0, T, e->v1 - e->v0, c.vocab, e->v0, e->cand + (size_t)e->tp_rank * cap * 4, st));
+    EB_TRY(eb_comm_allgather(e->comm, e->cand, nullptr, cap * 4 * (int64_t)sizeof(float), st));
+    EB_TRY(eb_argmax_merge(e->cand, e->tp_size, cap, T, e->d_next, e->d_margin, st));
+    n += 2;
+  }
   n += 3;
   return EB_OK;
 }
@@ -534,6 +565,16 @@ int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_si
   e->hkv_l = c.n_kv_heads / tp_size;
   e->e_l = c.n_experts / tp_size;
   e->e0 = tp_rank * e->e_l;
+  {
+    const int blocks = (c.vocab + 127) / 128, per = (blocks + tp_size - 1) / tp_size;
+    e->v0 = std::min(c.vocab, tp_rank * per * 128);
+    e->v1 = std::min(c.vocab, (tp_rank + 1) * per * 128);
+    if (e->v1 <= e->v0) {
+      delete e;
+      return eb::fail(EB_ERR_UNSUPPORTED, "eb_engine_create_tp: vocabulary %d has fewer 128-row blocks than %d ranks can share",
+                      c.vocab, tp_size);
+    }
+  }
   e->hqd = e->hq_l * c.head_dim;
   if (tp_size == 1) {
     e->kv_band = e->hkv_l * c.head_dim;  // the fused [q | k | v] row as it is

@@ -113,7 +113,8 @@ __global__ void embed_kernel(const uint4* table, int V, int H8, const int32_t* t
 }
 
 // Greedy argmax over bf16 logits, one CTA per token; ties go to the lower id.  Also the top-1 minus top-2 margin.
-__global__ void __launch_bounds__(1024) argmax_kernel(const uint16_t* logits, int64_t V, int64_t ld, int32_t* tok, float* margin) {
+__global__ void __launch_bounds__(1024) argmax_kernel(const uint16_t* logits, int64_t V, int64_t ld, int32_t* tok, float* margin,
+                                                      float* cand, int32_t v_off) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
   const uint16_t* r = logits + (int64_t)blockIdx.x * ld;
@@ -164,9 +165,41 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const uint16_t* logits, in
     __syncthreads();
   }
   if (threadIdx.x == 0) {
-    tok[blockIdx.x] = (int32_t)si[0];
-    if (margin) margin[blockIdx.x] = s1[0] - s2[0];
+    if (cand) {  // a vocabulary slice: leave the candidate for the merge
+      float* c = cand + (int64_t)blockIdx.x * 4;
+      c[0] = s1[0];
+      c[1] = s2[0];
+      c[2] = __int_as_float((int32_t)si[0] + v_off);
+      c[3] = 0.f;
+    } else {
+      tok[blockIdx.x] = (int32_t)si[0];
+      if (margin) margin[blockIdx.x] = s1[0] - s2[0];
+    }
   }
+}
+
+// One thread per row: fold the slices' candidates in ascending id order.
+__global__ void argmax_merge_kernel(const float* cand, int n_parts, int64_t part_stride, int T, int32_t* tok, float* margin) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  float a1 = -INFINITY, a2 = -INFINITY;
+  int32_t ai = 0x7fffffff;
+  for (int r = 0; r < n_parts; ++r) {
+    const float* c = cand + ((int64_t)r * part_stride + t) * 4;
+    const float c1 = c[0], c2 = c[1];
+    const int32_t ci = __float_as_int(c[2]);
+    if (c1 > a1 || (c1 == a1 && ci < ai)) {
+      a2 = fmaxf(a1, c2);
+      a1 = c1;
+      ai = ci;
+    } else {
+      a2 = fmaxf(a2, c1);
+    }
+  }
+  tok[t] = ai;
+  if (margin) margin[t] = a1 - a2;
 }
 
 }  // namespace
@@ -239,7 +272,29 @@ int32_t eb_argmax(const void* d_logits, int32_t T, int64_t V, int64_t ld, int32_
   EB_REQUIRE(d_logits && d_tok, EB_ERR_ARG, "eb_argmax: null pointer");
   EB_REQUIRE(T >= 0 && V >= 1 && ld >= V, EB_ERR_ARG, "eb_argmax: bad size");
   if (T == 0) return EB_OK;
-  EB_CUDA(eb::launch(argmax_kernel, dim3(T), dim3(1024), 0, eb::as_stream(stream), (const uint16_t*)d_logits, V, ld, d_tok, d_margin));
+  EB_CUDA(eb::launch(argmax_kernel, dim3(T), dim3(1024), 0, eb::as_stream(stream), (const uint16_t*)d_logits, V, ld, d_tok, d_margin,
+                     (float*)nullptr, 0));
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_argmax_partial(const void* d_logits, int32_t T, int64_t V, int64_t ld, int32_t v_off, float* d_cand, void* stream) {
+  EB_REQUIRE(d_logits && d_cand, EB_ERR_ARG, "eb_argmax_partial: null pointer");
+  EB_REQUIRE(T >= 0 && V >= 1 && ld >= V && v_off >= 0, EB_ERR_ARG, "eb_argmax_partial: bad size");
+  if (T == 0) return EB_OK;
+  EB_CUDA(eb::launch(argmax_kernel, dim3(T), dim3(1024), 0, eb::as_stream(stream), (const uint16_t*)d_logits, V, ld, (int32_t*)nullptr,
+                     (float*)nullptr, d_cand, v_off));
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_argmax_merge(const float* d_cand, int32_t n_parts, int64_t part_stride, int32_t T, int32_t* d_tok, float* d_margin,
+                        void* stream) {
+  EB_REQUIRE(d_cand && d_tok, EB_ERR_ARG, "eb_argmax_merge: null pointer");
+  EB_REQUIRE(n_parts >= 1 && T >= 0 && part_stride >= T, EB_ERR_ARG, "eb_argmax_merge: bad size");
+  if (T == 0) return EB_OK;
+  EB_CUDA(eb::launch(argmax_merge_kernel, dim3((unsigned)eb::cdiv(T, 128)), dim3(128), 0, eb::as_stream(stream), d_cand, n_parts,
+                     part_stride, T, d_tok, d_margin));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

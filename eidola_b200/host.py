@@ -193,6 +193,10 @@ class Comm:
     def allreduce_f32(self, d_buf, count, stream=None) -> None:
         call("eb_comm_allreduce_f32", self._h, c_vp(d_buf), c_i64(count), c_vp(stream))
 
+    def allgather(self, d_a, bytes_per_rank, d_b=None, stream=None) -> None:
+        """In place: rank r's slice sits at offset r * bytes_per_rank of each buffer."""
+        call("eb_comm_allgather", self._h, c_vp(d_a), c_vp(d_b), c_i64(bytes_per_rank), c_vp(stream))
+
     def close(self):
         if self._h:
             call("eb_comm_destroy", self._h)

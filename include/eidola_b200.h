@@ -339,6 +339,13 @@ int32_t eb_moe_combine_rmsnorm(const void* d_y, const int32_t* d_perm_row, const
 int32_t eb_embed(const void* d_table, int32_t V, int32_t H, const int32_t* d_tokens, int32_t T, void* d_x, void* stream);
 /* Greedy argmax over bf16 logits [T][ld], ties to the lower id; d_margin (top1 - top2) may be NULL. */
 int32_t eb_argmax(const void* d_logits, int32_t T, int64_t V, int64_t ld, int32_t* d_tok, float* d_margin, void* stream);
+/* Vocabulary-parallel argmax.  Partial: over columns [0, V) of d_logits (a rank's slice, whose first column is token id
+ * v_off) write per row a candidate {top1 value, top2 value, top1 id as int bits, 0} to d_cand[T][4].  Merge: n_parts
+ * candidate sets laid out [n_parts][part_stride rows][4], slices in ascending id order -> greedy token (ties to the
+ * lower id) and top1 - top2 margin, identical to eb_argmax over the concatenated logits. */
+int32_t eb_argmax_partial(const void* d_logits, int32_t T, int64_t V, int64_t ld, int32_t v_off, float* d_cand, void* stream);
+int32_t eb_argmax_merge(const float* d_cand, int32_t n_parts, int64_t part_stride, int32_t T, int32_t* d_tok, float* d_margin,
+                        void* stream);
 
 /* ---- engine: the whole decode step ------------------------------------------------------------
  * What an in-process implementation of the reference's engine boundary would drive once per generated token:
@@ -371,6 +378,9 @@ int32_t eb_comm_create(const void* h_id128, int32_t rank, int32_t size, eb_comm*
 int32_t eb_comm_destroy(eb_comm* c);
 int32_t eb_comm_info(const eb_comm* c, int32_t* rank, int32_t* size);
 int32_t eb_comm_allreduce_f32(eb_comm* c, void* d_buf, int64_t count, void* stream);
+/* In-place all-gather of one or two buffers (d_b may be NULL) in one NCCL group: rank r's bytes_per_rank bytes sit at
+ * offset r * bytes_per_rank of each buffer before the call, every rank holds all slices after it. */
+int32_t eb_comm_allgather(eb_comm* c, void* d_a, void* d_b, int64_t bytes_per_rank, void* stream);
 /* 0 = healthy.  A host whose step does not return within its own deadline, or that reads a non-zero value, aborts
  * the communicator and rebuilds it (failure handling stays on the host; kernels never wait on a peer). */
 int32_t eb_comm_async_error(eb_comm* c, int32_t* err);

@@ -117,3 +117,29 @@ def test_combine_rmsnorm_and_permute_tiles(gpu):
           c_vp(d_g.ptr), c_f32(1e-5), c_vp(d_h.ptr), None)
     assert np.array_equal(d_x.to_array(np.uint16, (T, H)), want_x)
     assert_close_bf16(d_h.to_array(np.uint16, (T, H)), orc.rmsnorm(want_x, g, 1e-5), atol=1e-6, rtol=2.0 ** -7, what="fused rmsnorm")
+
+
+def test_argmax_partial_and_merge_equal_whole_row_argmax(gpu):
+    """Vocabulary-parallel argmax: candidates of three unequal slices merge to the same token and top1 - top2 margin
+    as eb_argmax over the whole row, including ties across slices (lower id wins)."""
+    from eidola_b200.capi import DeviceBuffer, c_i32, c_i64, c_vp
+    T, V = 37, 5000
+    logits = orc.synth_normal_bf16(11, 1, 0, T * V, 2.0).reshape(T, V)
+    logits[3, 100] = logits[3, 4000] = 0x4120   # 10.0 twice: a tie between the first and the last slice
+    logits[5, :] = 0x3F80                       # a constant row: token 0, margin 0
+    d_l = _dev(logits)
+    d_tok, d_mg = DeviceBuffer(T * 4), DeviceBuffer(T * 4)
+    _call("eb_argmax", c_vp(d_l.ptr), c_i32(T), c_i64(V), c_i64(V), c_vp(d_tok.ptr), c_vp(d_mg.ptr), None)
+    want_tok, want_mg = d_tok.to_array(np.int32, T), d_mg.to_array(np.float32, T)
+    cuts = [0, 1280, 3968, V]
+    cap = 40
+    d_cand = DeviceBuffer(3 * cap * 4 * 4)
+    for r in range(3):
+        v0, v1 = cuts[r], cuts[r + 1]
+        _call("eb_argmax_partial", c_vp(d_l.ptr + 2 * v0), c_i32(T), c_i64(v1 - v0), c_i64(V), c_i32(v0),
+              c_vp(d_cand.ptr + r * cap * 16), None)
+    d_tok2, d_mg2 = DeviceBuffer(T * 4), DeviceBuffer(T * 4)
+    _call("eb_argmax_merge", c_vp(d_cand.ptr), c_i32(3), c_i64(cap), c_i32(T), c_vp(d_tok2.ptr), c_vp(d_mg2.ptr), None)
+    assert np.array_equal(d_tok2.to_array(np.int32, T), want_tok)
+    assert np.array_equal(d_mg2.to_array(np.float32, T), want_mg)
+    assert want_tok[3] == 100 and want_mg[3] == 0 and want_tok[5] == 0 and want_mg[5] == 0

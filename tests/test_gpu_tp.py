@@ -11,7 +11,7 @@ import pytest
 from oracle import binding as orc
 from oracle import sched as osched
 from tests.decoder_cases import compare_forced_step, free_running_error
-from tests.tp_worker import CONTEXTS, run_steps, tp_config
+from tests.tp_worker import CONTEXTS, run_steps, tp_config, vocab_slice
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
@@ -41,6 +41,15 @@ def _spawn(world, name, tmp_path, force_file=None):
     for r, p in enumerate(procs):
         assert p.returncode == 0, f"rank {r} failed:\n{logs[r][-3000:]}"
     return [np.load(o) for o in outs]
+
+
+def _merged_logits(ranks, key, vocab):
+    """The vocabulary-parallel head leaves each rank its own columns: put the slices side by side."""
+    out = np.zeros_like(ranks[0][key])
+    for r, rk in enumerate(ranks):
+        v0, v1 = vocab_slice(vocab, r, len(ranks))
+        out[:, v0:v1] = rk[key][:, v0:v1]
+    return out
 
 
 def _oracle_steps(name):
@@ -74,10 +83,17 @@ def test_two_rank_engine_matches_oracle_and_single_gpu(gpu, tmp_path, name):
     # (1) teacher-forced against the oracle, layer by layer
     ranks = _spawn(2, name, tmp_path, force_file)
     for s in range(2):
-        got = [{k: r[f"s{s}_{k}"] for k in ("next", "margin", "logits", "route_idx", "hidden")} for r in ranks]
-        assert np.array_equal(got[0]["logits"], got[1]["logits"]) and np.array_equal(got[0]["next"], got[1]["next"])
+        got = [{k: r[f"s{s}_{k}"] for k in ("next", "margin", "route_idx", "hidden")} for r in ranks]
+        assert np.array_equal(got[0]["next"], got[1]["next"]) and np.array_equal(got[0]["margin"], got[1]["margin"])
         assert np.array_equal(got[0]["hidden"], got[1]["hidden"])  # ranks stay in lockstep bit for bit
-        g = dict(got[0], route_idx=list(got[0]["route_idx"]), hidden=list(got[0]["hidden"]))
+        assert np.array_equal(got[0]["route_idx"], got[1]["route_idx"])  # token-sharded routing, gathered
+        logits = _merged_logits(ranks, f"s{s}_logits", cfg.vocab)
+        # the merged argmax of the vocabulary slices is the argmax of the whole row (ties to the lower id)
+        lf = (logits.astype(np.uint32) << 16).view(np.float32)
+        assert np.array_equal(got[0]["next"], lf.argmax(axis=1).astype(np.int32))
+        top2 = np.sort(lf, axis=1)[:, -2:]
+        assert np.array_equal(got[0]["margin"], (top2[:, 1] - top2[:, 0]).astype(np.float32))
+        g = dict(got[0], logits=logits, route_idx=list(got[0]["route_idx"]), hidden=list(got[0]["hidden"]))
         wh, wl = compare_forced_step(g, refs[s], cfg, what=f"{name} tp=2 step {s}")
         print(f"{name} tp=2 step {s}: forced hidden err {wh:.4f} logits err {wl:.4f}")
     assert all(int(r["status"][0]) == 0 for r in ranks)
@@ -87,7 +103,7 @@ def test_two_rank_engine_matches_oracle_and_single_gpu(gpu, tmp_path, name):
     eng.kv_fill_synth()
     _, single = run_steps(eng, name)
     for s in range(2):
-        got = {k: ranks[0][f"s{s}_{k}"] for k in ("logits", "hidden")}
+        got = {"hidden": ranks[0][f"s{s}_hidden"], "logits": _merged_logits(ranks, f"s{s}_logits", cfg.vocab)}
         dl, rel = free_running_error({"logits": got["logits"], "hidden": list(got["hidden"])},
                                      {"logits": single[s]["logits"], "hidden": list(single[s]["hidden"])})
         print(f"{name} tp=2 vs single GPU step {s}: logits err {dl.max():.4f} hidden rel {rel:.4f}")

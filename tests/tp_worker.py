@@ -28,11 +28,19 @@ def tp_config(name):
                        max_q_len=5, seed=3, debug=1)
 
 
+def vocab_slice(vocab, rank, world):
+    """Vocabulary rows of the LM head that live on `rank`: whole 128-row scale blocks, dealt in order."""
+    blocks = (vocab + 127) // 128
+    per = (blocks + world - 1) // world
+    return min(vocab, rank * per * 128), min(vocab, (rank + 1) * per * 128)
+
+
 CONTEXTS = {"tp_small": [7, 33, 128, 250], "tp_mid": [5, 40, 130, 300, 17, 1000, 64, 2, 511, 128, 33, 250]}
 
 
-def run_steps(eng, name, force=None):
-    """Two steps (decode, then ragged verify).  `force`: per step the oracle's hidden states to impose."""
+def run_steps(eng, name, force=None, rank=0, world=1):
+    """Two steps (decode, then ragged verify).  `force`: per step the oracle's hidden states to impose.  Under tensor
+    parallelism a rank holds the logits of its vocabulary slice only: the other columns are saved as zeros."""
     cfg = eng.cfg
     ctx = CONTEXTS[name]
     slots = [eng.admit(L) for L in ctx]
@@ -45,7 +53,12 @@ def run_steps(eng, name, force=None):
             for l in range(cfg.n_layers + 1):
                 eng.force_hidden(l, force[step][l])
         nxt, mg = eng.step(slots, q_lens, toks)
-        out.append({"next": nxt, "margin": mg, "logits": eng.read_logits(),
+        logits = eng.read_logits()
+        if world > 1:
+            v0, v1 = vocab_slice(cfg.vocab, rank, world)
+            logits[:, :v0] = 0
+            logits[:, v1:] = 0
+        out.append({"next": nxt, "margin": mg, "logits": logits,
                     "route_idx": np.stack([eng.read_routing(l) for l in range(cfg.n_layers)]),
                     "hidden": np.stack([eng.read_hidden(l) for l in range(-1, cfg.n_layers)]),
                     "tokens": toks, "q_lens": np.array(q_lens, np.int32)})
@@ -78,7 +91,7 @@ def main():
     if force_file:
         f = np.load(force_file)
         force = [[f[f"s{s}_l{l}"] for l in range(cfg.n_layers + 1)] for s in range(2)]
-    _, out = run_steps(eng, name, force)
+    _, out = run_steps(eng, name, force, rank, world)
     flat = {}
     for s, o in enumerate(out):
         for k, v in o.items():
