@@ -292,10 +292,7 @@ class Spec120bWorkload:
 # ------------------------------------------------------------------------------------------ attention workload
 
 class AttnWorkload:
-    name = "paged sink-attention decode, one layer: 256 ragged seqs, 64q/8kv heads, d64, bf16 KV pages of 16, " \
-           "ctx lognormal(median 2048, sigma 1) in [16,32768], full attention"
-
-    def __init__(self, rank: int, n_seqs=256, window=0):
+    def __init__(self, rank: int, n_seqs=256, window=0, sigma=1.0, q_len=1):
         import eidola_b200 as eb
         from eidola_b200 import capi
         from eidola_b200.capi import DeviceBuffer, c_f32, c_i64, c_u64, c_vp
@@ -304,9 +301,13 @@ class AttnWorkload:
         self.info = eb.device_info(rank_device(rank))
         seed = 1 + rank
         self.n_kv, self.n_q, self.window = 8, 64, window
-        self.ctx = lognormal_lengths(n_seqs, 2048, 1.0, 16, 32768, seed)
+        self.name = ("paged sink-attention %s, one layer: %d ragged seqs, 64q/8kv heads, d64, bf16 KV pages of 16, "
+                     "ctx lognormal(median 2048, sigma %g) in [16,32768], %s"
+                     % ("decode" if q_len == 1 else "verify (q_len %d)" % q_len, n_seqs, sigma,
+                        "%d-token sliding window" % window if window else "full attention"))
+        self.ctx = lognormal_lengths(n_seqs, 2048, sigma, 16, 32768, seed)
         n = n_seqs
-        self.q_lens = np.ones(n, np.int32)
+        self.q_lens = np.full(n, q_len, np.int32)
         pages = int(((self.ctx.astype(np.int64) + PAGE - 1) // PAGE).sum())
         self.num_pages = pages + 8
         max_pages = int((self.ctx.max() + PAGE - 1) // PAGE)
@@ -334,7 +335,7 @@ class AttnWorkload:
         capi.call("eb_copy_d2h", self.h_q, c_vp(self.d_q.ptr), capi.c_sz(self.q_bytes), None)
         capi.call("eb_device_sync")
         self.units_per_step = T
-        visible = np.minimum(self.ctx, window) if window else self.ctx
+        visible = np.minimum(self.ctx, window + q_len - 1) if window else self.ctx
         self.alg_bytes = int(visible.astype(np.int64).sum()) * 2 * self.n_kv * HEAD_DIM * 2 + 2 * self.q_bytes \
             + 4 * int(((visible.astype(np.int64) + PAGE - 1) // PAGE).sum())
         self.launches_per_step = 2 if self.plan["n_parts"] > n else 1
@@ -569,7 +570,7 @@ def run_attn(args) -> dict:
     import eidola_b200 as eb
     from eidola_b200 import capi
     capi.call("eb_device_set", capi.c_i32(rank_device(rank)))
-    wl = AttnWorkload(rank, n_seqs=args.seqs)
+    wl = AttnWorkload(rank, n_seqs=args.seqs, window=args.window, sigma=args.sigma, q_len=args.qlen)
     K, W = args.steps, args.warmup
 
     def barrier():
@@ -883,6 +884,9 @@ def main():
     ap.add_argument("--workload", default="decoder", choices=["decoder", "attn", "spec120b", "gemm"])
     ap.add_argument("--profile", action="store_true", help="spec120b: time attention/GEMM calls with CUDA events in every step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--window", type=int, default=0, help="attn: sliding window in tokens (0 = full attention)")
+    ap.add_argument("--sigma", type=float, default=1.0, help="attn: sigma of the lognormal context lengths")
+    ap.add_argument("--qlen", type=int, default=1, help="attn: query positions per sequence (5 = verify of 4 drafts)")
     ap.add_argument("--m", type=int, nargs="*", default=None, help="gemm: token counts to run instead of the whole sweep")
     ap.add_argument("--seqs", type=int, default=256, help="sequences in the batch (smaller values are for profiler captures)")
     ap.add_argument("--layers", type=int, default=24, help="decoder layers (smaller values are for profiler captures)")
