@@ -125,14 +125,19 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return r;
 }
 
-// MT  : 16-row M tiles = ceil(max_q_len * G / 16)
+// MT  : 16-row M tiles per warp
+// WT  : warp sets; set w handles M tiles [w * MT, (w + 1) * MT) of every page, so ceil(max_q_len * G / 16) = MT * WT.
+//       Verify shapes (40 query rows per KV head) run MT = 1, WT = 3: the same 72 MMAs per page and KV head as one
+//       warp with three tiles, but on 24 warps whose dependent MMA chains overlap, at 80 registers instead of 168.
 // HKV : KV heads held by this rank (8, 4, 2 or 1)
 // G   : query heads per KV head (8 or 4); row r of the M tiles = (query position r / G, head r % G of the group)
-template <int MT, int HKV, int STAGES, int G>
-__global__ void __launch_bounds__(kThreads, (MT == 1) ? 2 : 1)
+template <int MT, int WT, int HKV, int STAGES, int G>
+__global__ void __launch_bounds__((kComputeWarps * WT + 1) * 32, (MT == 1 && WT == 1) ? 2 : 1)
 attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
+  constexpr int kCW = kComputeWarps * WT;        // compute warps of the CTA
+  constexpr int kNT = (kCW + 1) * 32;            // threads of the CTA
   constexpr int PPS = kComputeWarps / HKV;       // pages per stage
   constexpr int kPageRows = 2 * HKV * kPage;     // 128-byte rows per page
   constexpr int kPageBytes = kPageRows * 128;
@@ -159,7 +164,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     n_pages = kMaxItemPages;
   }
 
-  for (int j = tid; j < n_pages; j += kThreads) {
+  for (int j = tid; j < n_pages; j += kNT) {
     int32_t id = p.block_tables[(int64_t)slot * p.bt_stride + item.page_begin + j];
     if (id < 0 || id >= p.num_pages) {
       atomicOr(p.status, EB_DEV_BAD_INDEX);
@@ -172,7 +177,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     n_issued = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&bars[s]), 1);
-      mbar_init(smem_u32(&bars[STAGES + s]), kComputeWarps);
+      mbar_init(smem_u32(&bars[STAGES + s]), kCW);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -181,7 +186,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
 
   const int n_iters = (n_pages + PPS - 1) / PPS;
 
-  if (warp == kComputeWarps) {
+  if (warp == kCW) {
     // ---------------- producer: one thread feeds the stage ring with whole pages
     if (lane == 0) {
       for (int it = 0; it < n_iters; ++it) {
@@ -199,8 +204,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     }
   } else {
     // ---------------- consumers
-    const int hk = warp % HKV;   // KV head of this warp
-    const int sub = warp / HKV;  // page of the stage this warp takes
+    const int set = warp / kComputeWarps;             // warp set = which M tiles
+    const int hk = (warp % kComputeWarps) % HKV;      // KV head of this warp
+    const int sub = (warp % kComputeWarps) / HKV;     // page of the stage this warp takes
+    const int row_base = set * MT * 16;               // first query row of this warp's tiles
     const int tq = lane & 3;
 
     // Q fragments (A operand): rows = (query position, head of the group), kept in registers.
@@ -209,7 +216,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int row = mt * 16 + half * 8 + (lane >> 2);
+        const int row = row_base + mt * 16 + half * 8 + (lane >> 2);
         const int qi = row / G;
         const uint16_t* qrow = p.q + (int64_t)(q0 + qi) * p.q_stride + (int64_t)(hk * G + row % G) * kHeadDim;
 #pragma unroll
@@ -273,7 +280,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
         for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
-            const int pq = L - ql + (mt * 16 + half * 8 + (lane >> 2)) / G;  // absolute position of this row's query
+            const int pq = L - ql + (row_base + mt * 16 + half * 8 + (lane >> 2)) / G;  // absolute position of this row's query
             const int lo = p.window > 0 ? pq - p.window + 1 : 0;
             float v[2][2];
             float mx = kNegBig;
@@ -282,30 +289,34 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
                 const int t = t0 + nt * 8 + tq * 2 + e;
-                float x = sc[mt][nt][half * 2 + e] * p.scale_log2;
+                float x = sc[mt][nt][half * 2 + e];  // raw score; the positive scale is applied after the max
                 if (edge && (t > pq || t < lo)) x = -INFINITY;
                 v[nt][e] = x;
                 mx = fmaxf(mx, x);
               }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m_run[mt][half], mx);
-            const float alpha = fast_exp2(m_run[mt][half] - m_new);
-            m_run[mt][half] = m_new;
+            const float m_new = fmaxf(m_run[mt][half], mx * p.scale_log2);
             float ps = 0.f;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
-                v[nt][e] = fast_exp2(v[nt][e] - m_new);
+                v[nt][e] = fast_exp2(fmaf(v[nt][e], p.scale_log2, -m_new));
                 ps += v[nt][e];
               }
-            l_run[mt][half] = l_run[mt][half] * alpha + ps;
+            // the running maximum of a quad's row rarely moves after the first pages: rescale only then
+            if (m_new != m_run[mt][half]) {
+              const float alpha = fast_exp2(m_run[mt][half] - m_new);
+              m_run[mt][half] = m_new;
+              l_run[mt][half] *= alpha;
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-              o[mt][nt][half * 2 + 0] *= alpha;
-              o[mt][nt][half * 2 + 1] *= alpha;
+              for (int nt = 0; nt < 8; ++nt) {
+                o[mt][nt][half * 2 + 0] *= alpha;
+                o[mt][nt][half * 2 + 1] *= alpha;
+              }
             }
+            l_run[mt][half] += ps;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {  // a0 / a1: tokens 0-7, a2 / a3: tokens 8-15
               const uint32_t hi = pack_bf16(v[nt][0], v[nt][1]);
@@ -340,7 +351,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int row = mt * 16 + half * 8 + (lane >> 2);
+        const int row = row_base + mt * 16 + half * 8 + (lane >> 2);
         const int qi = row / G;
         float l = l_run[mt][half];
         l += __shfl_xor_sync(0xffffffffu, l, 1);
@@ -461,28 +472,28 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int MT, int HKV, int STAGES, int G>
+template <int MT, int WT, int HKV, int STAGES, int G>
 int32_t launch_attn(const CUtensorMap& tm, const AttnParams& p, int n_items, cudaStream_t st) {
   const size_t smem = 1024 + (size_t)STAGES * kStageBytes + 2 * STAGES * sizeof(uint64_t) + kMaxItemPages * sizeof(int32_t);
-  auto kfn = attn_kernel<MT, HKV, STAGES, G>;
+  auto kfn = attn_kernel<MT, WT, HKV, STAGES, G>;
   static bool configured = false;
   if (!configured) {
     EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  EB_CUDA(eb::launch(kfn, dim3(n_items), dim3(kThreads), smem, st, tm, p));
+  EB_CUDA(eb::launch(kfn, dim3(n_items), dim3((kComputeWarps * WT + 1) * 32), smem, st, tm, p));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
 
-template <int MT, int G>
+template <int WT, int G>
 int32_t dispatch_hkv(int n_kv, const CUtensorMap& tm, const AttnParams& p, int n_items, cudaStream_t st) {
-  constexpr int ST = (MT == 1) ? 3 : 6;
+  constexpr int ST = (WT == 1) ? 3 : 6;
   switch (n_kv) {
-    case 8: return launch_attn<MT, 8, ST, G>(tm, p, n_items, st);
-    case 4: return launch_attn<MT, 4, ST, G>(tm, p, n_items, st);
-    case 2: return launch_attn<MT, 2, ST, G>(tm, p, n_items, st);
-    case 1: return launch_attn<MT, 1, ST, G>(tm, p, n_items, st);
+    case 8: return launch_attn<1, WT, 8, ST, G>(tm, p, n_items, st);
+    case 4: return launch_attn<1, WT, 4, ST, G>(tm, p, n_items, st);
+    case 2: return launch_attn<1, WT, 2, ST, G>(tm, p, n_items, st);
+    case 1: return launch_attn<1, WT, 1, ST, G>(tm, p, n_items, st);
   }
   return eb::fail(EB_ERR_UNSUPPORTED, "attention: n_kv %d not in {1,2,4,8}", n_kv);
 }
