@@ -279,14 +279,15 @@ class Spec120bWorkload:
         kv_full = (c.n_layers // 2) * int(ctx.sum()) * 2048 // G
         kv_win = (c.n_layers - c.n_layers // 2) * int(np.minimum(ctx, 128 + 5 + PAGE).sum()) * 2048 // G
         return {"weights": weights, "kv_full": kv_full, "kv_window": kv_win, "total": weights + kv_full + kv_win,
-                "allreduce_bytes_per_layer": 2 * 5 * len(ctx) * 2880 * 4}
+                "reduce_scatter_bytes_per_layer": 2 * 5 * len(ctx) * 2880 * 4, "allgather_bytes_per_layer": 2 * 5 * len(ctx) * 2880 * 2}
 
     def config(self) -> dict:
         return {"workload": self.name, "n_seqs": int(len(self.ctx0)), "n_layers": int(self.cfg.n_layers),
                 "mean_context": float(self.lens.mean()), "device_bytes_per_rank": self.mem,
                 "prefill": "KV pages filled with seeded N(0,1) values (stand-in for prefill)",
-                "parallelism": "tp%d (heads) x ep%d (experts); per layer 2 fp32 all-reduces of [2560, 2880] and one all-gather of the "
-                               "token-sharded routing; vocabulary-parallel LM head with an all-gather of argmax candidates" % (self.world, self.world)}
+                "parallelism": "tp%d (heads) x ep%d (experts); per layer 2 fp32 reduce-scatters of [2560, 2880] over token "
+                               "slices, residual + norm + routing on the slice, 2 all-gathers of the bf16 rows (+ routing); "
+                               "vocabulary-parallel LM head with an all-gather of argmax candidates" % (self.world, self.world)}
 
 
 # ------------------------------------------------------------------------------------------ attention workload

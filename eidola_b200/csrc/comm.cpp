@@ -24,6 +24,7 @@ struct NcclApi {
   ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*GroupStart)() = nullptr;
   ncclResult_t (*GroupEnd)() = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -45,12 +46,13 @@ NcclApi& api() {
     EB_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
     EB_SYM(AllReduce, "ncclAllReduce");
     EB_SYM(AllGather, "ncclAllGather");
+    EB_SYM(ReduceScatter, "ncclReduceScatter");
     EB_SYM(GroupStart, "ncclGroupStart");
     EB_SYM(GroupEnd, "ncclGroupEnd");
     EB_SYM(GetErrorString, "ncclGetErrorString");
 #undef EB_SYM
     a.ok = a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.CommAbort && a.CommGetAsyncError && a.AllReduce &&
-           a.AllGather && a.GroupStart && a.GroupEnd && a.GetErrorString;
+           a.AllGather && a.ReduceScatter && a.GroupStart && a.GroupEnd && a.GetErrorString;
   });
   return a;
 }
@@ -120,22 +122,32 @@ int32_t eb_comm_allreduce_f32(eb_comm* c, void* d_buf, int64_t count, void* stre
   return EB_OK;
 }
 
-// In-place all-gather of up to two buffers in one NCCL group: rank r's `bytes_per_rank` bytes already sit at offset
-// r * bytes_per_rank of each buffer; on return every rank holds all `size` slices.  d_b may be null.
-int32_t eb_comm_allgather(eb_comm* c, void* d_a, void* d_b, int64_t bytes_per_rank, void* stream) {
-  EB_REQUIRE(c && d_a && bytes_per_rank >= 0, EB_ERR_ARG, "eb_comm_allgather: bad argument");
-  if (bytes_per_rank == 0 || c->size == 1) return EB_OK;
+// In-place all-gather of up to three buffers in one NCCL group: rank r's bytes[i] bytes already sit at offset
+// r * bytes[i] of buffer i; on return every rank holds all `size` slices of every buffer.
+int32_t eb_comm_allgather(eb_comm* c, int32_t n_bufs, void* const* d_bufs, const int64_t* bytes_per_rank, void* stream) {
+  EB_REQUIRE(c && d_bufs && bytes_per_rank && n_bufs >= 1 && n_bufs <= 3, EB_ERR_ARG, "eb_comm_allgather: bad argument");
+  for (int i = 0; i < n_bufs; ++i)
+    EB_REQUIRE(d_bufs[i] && bytes_per_rank[i] >= 0, EB_ERR_ARG, "eb_comm_allgather: buffer %d", i);
+  if (c->size == 1) return EB_OK;
   EB_NCCL(api().GroupStart());
-  ncclResult_t r1 = api().AllGather((const char*)d_a + (size_t)c->rank * bytes_per_rank, d_a, (size_t)bytes_per_rank, ncclInt8,
-                                    c->comm, eb::as_stream(stream));
-  ncclResult_t r2 = ncclSuccess;
-  if (d_b && r1 == ncclSuccess)
-    r2 = api().AllGather((const char*)d_b + (size_t)c->rank * bytes_per_rank, d_b, (size_t)bytes_per_rank, ncclInt8, c->comm,
-                         eb::as_stream(stream));
-  ncclResult_t r3 = api().GroupEnd();
-  EB_NCCL(r1);
-  EB_NCCL(r2);
-  EB_NCCL(r3);
+  ncclResult_t r = ncclSuccess;
+  for (int i = 0; i < n_bufs && r == ncclSuccess; ++i)
+    if (bytes_per_rank[i] > 0)
+      r = api().AllGather((const char*)d_bufs[i] + (size_t)c->rank * bytes_per_rank[i], d_bufs[i], (size_t)bytes_per_rank[i],
+                          ncclInt8, c->comm, eb::as_stream(stream));
+  ncclResult_t re = api().GroupEnd();
+  EB_NCCL(r);
+  EB_NCCL(re);
+  return EB_OK;
+}
+
+// In-place reduce-scatter (fp32 sum): every rank contributes size * count_per_rank floats at d_buf; rank r's sum of
+// slice r lands at d_buf + r * count_per_rank (the other slices of d_buf are left undefined).
+int32_t eb_comm_reduce_scatter_f32(eb_comm* c, void* d_buf, int64_t count_per_rank, void* stream) {
+  EB_REQUIRE(c && d_buf && count_per_rank >= 0, EB_ERR_ARG, "eb_comm_reduce_scatter_f32: bad argument");
+  if (count_per_rank == 0 || c->size == 1) return EB_OK;
+  EB_NCCL(api().ReduceScatter(d_buf, (float*)d_buf + (size_t)c->rank * count_per_rank, (size_t)count_per_rank, ncclFloat32, ncclSum,
+                              c->comm, eb::as_stream(stream)));
   return EB_OK;
 }
 

@@ -216,8 +216,10 @@ int32_t init_work(eb_engine* e) {
   const int H = c.hidden, I = c.inter, E = e->e_l, T = c.max_tokens;
   const int64_t R = (int64_t)T * c.top_k;
   int64_t* w = &e->work_bytes;
-  EB_TRY(dev_alloc(e, &e->x, (size_t)T * H, w));
-  EB_TRY(dev_alloc(e, &e->h, (size_t)T * H, w));
+  // under tensor parallelism rows are dealt to ranks in tp_size equal chunks for the in-place collectives: slack rows
+  const size_t Tc = (size_t)T + (size_t)e->tp_size;
+  EB_TRY(dev_alloc(e, &e->x, Tc * H, w));
+  EB_TRY(dev_alloc(e, &e->h, Tc * H, w));
   EB_TRY(dev_alloc(e, &e->qkv, (size_t)T * e->nqkv, w));
   EB_TRY(dev_alloc(e, &e->attn, (size_t)T * e->hqd, w));
   EB_TRY(dev_alloc(e, &e->o, (size_t)T * H, w));
@@ -238,7 +240,7 @@ int32_t init_work(eb_engine* e) {
   EB_TRY(dev_alloc(e, &e->r_idx, r_cap, w));
   EB_TRY(dev_alloc(e, &e->r_idx_local, (size_t)R, w));
   if (e->tp_size > 1) {
-    EB_TRY(dev_alloc(e, &e->ar_buf, (size_t)T * H, w));
+    EB_TRY(dev_alloc(e, &e->ar_buf, Tc * H, w));
     EB_TRY(dev_alloc(e, &e->cand, (size_t)e->tp_size * T * 4, w));
   }
   EB_TRY(dev_alloc(e, &e->r_wts, r_cap, w));
@@ -315,6 +317,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   const eb_config& c = e->c;
   const int H = c.hidden, I = c.inter, E = e->e_l, R = T * c.top_k;  // E: local experts; R: upper bound of local rows
   const bool tp = e->tp_size > 1;
+  // token slice of this rank for the reduce-scatter / all-gather pairs (tp_size equal chunks, the last ones may be short)
+  const int chunk = (T + e->tp_size - 1) / e->tp_size;
+  const int t0 = std::min(T, e->tp_rank * chunk), nt = std::min(T, t0 + chunk) - t0;
   void* st = e->stream;
   const int max_pos = c.max_pages_per_seq * c.page_size;
   int& n = e->launches;
@@ -444,23 +449,25 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       EB_TRY(eb_oproj_residual_rmsnorm(splits > 1 ? (const float*)e->gemm_ws : nullptr, splits, e->o, e->x, L.g_mlp, T, H,
                                        c.rms_eps, e->h, st));
     } else {
-      // C1: this rank's heads contributed a partial [T, H]; sum the partials of all ranks in fp32, then round once
+      // C1: this rank's heads contributed a partial [T, H].  Reduce-scatter the fp32 partials over token slices; the
+      // owner of a slice adds the residual, rounds once and normalises; the normalised rows are gathered below.
       EB_TRY(eb_sum_planes_f32(splits > 1 ? (const float*)e->gemm_ws : nullptr, splits, e->o, (int64_t)T * H, e->ar_buf, st));
-      EB_TRY(eb_comm_allreduce_f32(e->comm, e->ar_buf, (int64_t)T * H, st));
-      EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf, 1, nullptr, e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
+      EB_TRY(eb_comm_reduce_scatter_f32(e->comm, e->ar_buf, (int64_t)chunk * H, st));
+      EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf + (size_t)t0 * H, 1, nullptr, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
+                                       e->h + (size_t)t0 * H, st));
       n += 2;
     }
     if (!tp) {
       EB_TRY(eb_moe_route(e->h, L.wr, T, c.n_experts, H, c.top_k, e->r_idx, e->r_wts, nullptr, st));
     } else {
-      // every rank routes its slice of the (replicated) tokens, then the slices are gathered: the same bits as routing
-      // all tokens everywhere, at 1/tp_size of the work
-      const int chunk = (T + e->tp_size - 1) / e->tp_size;
-      const int t0 = std::min(T, e->tp_rank * chunk), nt = std::min(T, t0 + chunk) - t0;
+      // every rank routes its slice of the tokens, then normalised rows and routing are gathered in one group: the
+      // same bits as doing all tokens everywhere, at 1/tp_size of the work
       if (nt > 0)
         EB_TRY(eb_moe_route(e->h + (size_t)t0 * H, L.wr, nt, c.n_experts, H, c.top_k, e->r_idx + (size_t)t0 * c.top_k,
                             e->r_wts + (size_t)t0 * c.top_k, nullptr, st));
-      EB_TRY(eb_comm_allgather(e->comm, e->r_idx, e->r_wts, (int64_t)chunk * c.top_k * 4, st));
+      void* bufs[3] = {e->h, e->r_idx, e->r_wts};
+      const int64_t sizes[3] = {(int64_t)chunk * H * 2, (int64_t)chunk * c.top_k * 4, (int64_t)chunk * c.top_k * 4};
+      EB_TRY(eb_comm_allgather(e->comm, 3, bufs, sizes, st));
       n += 1;
     }
     if (!tp) {
@@ -487,9 +494,15 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       // C2: partial mix of this rank's experts, summed across ranks (tokens are replicated, so the combine of an
       // expert-parallel layer is an all-reduce and the dispatch needs no exchange)
       EB_TRY(eb_moe_combine_f32(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->ar_buf, st));
-      EB_TRY(eb_comm_allreduce_f32(e->comm, e->ar_buf, (int64_t)T * H, st));
-      EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf, 1, nullptr, e->x, g_next, T, H, c.rms_eps, e->h, st));
-      n += 2;
+      EB_TRY(eb_comm_reduce_scatter_f32(e->comm, e->ar_buf, (int64_t)chunk * H, st));
+      EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf + (size_t)t0 * H, 1, nullptr, e->x + (size_t)t0 * H, g_next, nt, H, c.rms_eps,
+                                       e->h + (size_t)t0 * H, st));
+      // the next consumer (QKV projection of the next layer, or the LM head) needs every token's normalised row; the
+      // residual stream itself stays sliced, except when the debug taps want it whole
+      void* bufs[2] = {e->h, e->x};
+      const int64_t sizes[2] = {(int64_t)chunk * H * 2, (int64_t)chunk * H * 2};
+      EB_TRY(eb_comm_allgather(e->comm, (c.debug & 1) ? 2 : 1, bufs, sizes, st));
+      n += 3;
     }
     n += 9 + (plans[pi].n_parts > n_seqs ? 1 : 0);
     if (c.debug & 1) {
@@ -515,7 +528,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     mark(-1);
     const int64_t cap = c.max_tokens;
     EB_TRY(eb_argmax_partial(e->logits + e->v0, T, e->v1 - e->v0, c.vocab, e->v0, e->cand + (size_t)e->tp_rank * cap * 4, st));
-    EB_TRY(eb_comm_allgather(e->comm, e->cand, nullptr, cap * 4 * (int64_t)sizeof(float), st));
+    void* cb[1] = {e->cand};
+    const int64_t csz[1] = {cap * 4 * (int64_t)sizeof(float)};
+    EB_TRY(eb_comm_allgather(e->comm, 1, cb, csz, st));
     EB_TRY(eb_argmax_merge(e->cand, e->tp_size, cap, T, e->d_next, e->d_margin, st));
     n += 2;
   }

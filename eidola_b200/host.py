@@ -193,9 +193,15 @@ class Comm:
     def allreduce_f32(self, d_buf, count, stream=None) -> None:
         call("eb_comm_allreduce_f32", self._h, c_vp(d_buf), c_i64(count), c_vp(stream))
 
-    def allgather(self, d_a, bytes_per_rank, d_b=None, stream=None) -> None:
-        """In place: rank r's slice sits at offset r * bytes_per_rank of each buffer."""
-        call("eb_comm_allgather", self._h, c_vp(d_a), c_vp(d_b), c_i64(bytes_per_rank), c_vp(stream))
+    def allgather(self, bufs, bytes_per_rank, stream=None) -> None:
+        """In place, 1..3 buffers: rank r's slice of buffer i sits at offset r * bytes_per_rank[i]."""
+        n = len(bufs)
+        ptrs = (C.c_void_p * n)(*[int(b) for b in bufs])
+        sizes = (C.c_int64 * n)(*[int(b) for b in bytes_per_rank])
+        call("eb_comm_allgather", self._h, c_i32(n), ptrs, sizes, c_vp(stream))
+
+    def reduce_scatter_f32(self, d_buf, count_per_rank, stream=None) -> None:
+        call("eb_comm_reduce_scatter_f32", self._h, c_vp(d_buf), c_i64(count_per_rank), c_vp(stream))
 
     def close(self):
         if self._h:

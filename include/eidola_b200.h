@@ -378,9 +378,12 @@ int32_t eb_comm_create(const void* h_id128, int32_t rank, int32_t size, eb_comm*
 int32_t eb_comm_destroy(eb_comm* c);
 int32_t eb_comm_info(const eb_comm* c, int32_t* rank, int32_t* size);
 int32_t eb_comm_allreduce_f32(eb_comm* c, void* d_buf, int64_t count, void* stream);
-/* In-place all-gather of one or two buffers (d_b may be NULL) in one NCCL group: rank r's bytes_per_rank bytes sit at
- * offset r * bytes_per_rank of each buffer before the call, every rank holds all slices after it. */
-int32_t eb_comm_allgather(eb_comm* c, void* d_a, void* d_b, int64_t bytes_per_rank, void* stream);
+/* In-place all-gather of 1..3 buffers in one NCCL group: rank r's bytes_per_rank[i] bytes sit at offset
+ * r * bytes_per_rank[i] of buffer i before the call, every rank holds all slices after it. */
+int32_t eb_comm_allgather(eb_comm* c, int32_t n_bufs, void* const* d_bufs, const int64_t* bytes_per_rank, void* stream);
+/* In-place fp32 reduce-scatter: d_buf holds size * count_per_rank floats; on return rank r's slice
+ * [r * count_per_rank, (r + 1) * count_per_rank) holds the sum over ranks, the other slices are undefined. */
+int32_t eb_comm_reduce_scatter_f32(eb_comm* c, void* d_buf, int64_t count_per_rank, void* stream);
 /* 0 = healthy.  A host whose step does not return within its own deadline, or that reads a non-zero value, aborts
  * the communicator and rebuilds it (failure handling stays on the host; kernels never wait on a peer). */
 int32_t eb_comm_async_error(eb_comm* c, int32_t* err);
