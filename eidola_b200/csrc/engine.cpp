@@ -404,7 +404,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       EB_TRY(eb_rmsnorm(e->x, L.g_attn, T, H, c.rms_eps, e->h, st));
     }
     int32_t splits = 1;
+    mark(7);
     EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
+    mark(-1);
     mark(2);
     EB_TRY(dense(e->h8, e->sh, L.wqkv, e->nqkv, H, e->qkv, &splits));
     mark(-1);
@@ -441,7 +443,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     mark(pi ? 1 : 0);
     EB_TRY(eb_attn_paged_sink(&a, st));
     mark(-1);
+    mark(7);
     EB_TRY(eb_quant_act_block128(e->attn, e->hqd, T, e->hqd, nullptr, 1, e->a8, e->sa, st));
+    mark(-1);
     mark(2);
     EB_TRY(dense(e->a8, e->sa, L.wo, H, e->hqd, e->o, &splits));
     mark(-1);
@@ -452,22 +456,29 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       // C1: this rank's heads contributed a partial [T, H].  Reduce-scatter the fp32 partials over token slices; the
       // owner of a slice adds the residual, rounds once and normalises; the normalised rows are gathered below.
       EB_TRY(eb_sum_planes_f32(splits > 1 ? (const float*)e->gemm_ws : nullptr, splits, e->o, (int64_t)T * H, e->ar_buf, st));
+      mark(5);
       EB_TRY(eb_comm_reduce_scatter_f32(e->comm, e->ar_buf, (int64_t)chunk * H, st));
+      mark(-1);
       EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf + (size_t)t0 * H, 1, nullptr, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
                                        e->h + (size_t)t0 * H, st));
       n += 2;
     }
+    mark(6);
     if (!tp) {
       EB_TRY(eb_moe_route(e->h, L.wr, T, c.n_experts, H, c.top_k, e->r_idx, e->r_wts, nullptr, st));
+      mark(-1);
     } else {
       // every rank routes its slice of the tokens, then normalised rows and routing are gathered in one group: the
       // same bits as doing all tokens everywhere, at 1/tp_size of the work
       if (nt > 0)
         EB_TRY(eb_moe_route(e->h + (size_t)t0 * H, L.wr, nt, c.n_experts, H, c.top_k, e->r_idx + (size_t)t0 * c.top_k,
                             e->r_wts + (size_t)t0 * c.top_k, nullptr, st));
+      mark(-1);
       void* bufs[3] = {e->h, e->r_idx, e->r_wts};
       const int64_t sizes[3] = {(int64_t)chunk * H * 2, (int64_t)chunk * c.top_k * 4, (int64_t)chunk * c.top_k * 4};
+      mark(5);
       EB_TRY(eb_comm_allgather(e->comm, 3, bufs, sizes, st));
+      mark(-1);
       n += 1;
     }
     if (!tp) {
@@ -479,11 +490,15 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
                                         e->group_ws, st));
       n += 1;
     }
+    mark(7);
     EB_TRY(eb_quant_gather_block128(e->h, H, T, e->row_token, R, H, e->seg_off, E, e->xp8, e->sxp, st));
+    mark(-1);
     mark(3);
     EB_TRY(grouped(e->xp8, e->sxp, L.w1, 2 * I, H, e->gu));
     mark(-1);
+    mark(7);
     EB_TRY(eb_quant_silu_mul_block128(e->gu, 2 * I, R, I, e->seg_off, E, e->act8, e->sact, st));
+    mark(-1);
     mark(3);
     EB_TRY(grouped(e->act8, e->sact, L.w2, H, I, e->y));
     mark(-1);
@@ -494,14 +509,18 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       // C2: partial mix of this rank's experts, summed across ranks (tokens are replicated, so the combine of an
       // expert-parallel layer is an all-reduce and the dispatch needs no exchange)
       EB_TRY(eb_moe_combine_f32(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->ar_buf, st));
+      mark(5);
       EB_TRY(eb_comm_reduce_scatter_f32(e->comm, e->ar_buf, (int64_t)chunk * H, st));
+      mark(-1);
       EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf + (size_t)t0 * H, 1, nullptr, e->x + (size_t)t0 * H, g_next, nt, H, c.rms_eps,
                                        e->h + (size_t)t0 * H, st));
       // the next consumer (QKV projection of the next layer, or the LM head) needs every token's normalised row; the
       // residual stream itself stays sliced, except when the debug taps want it whole
       void* bufs[2] = {e->h, e->x};
       const int64_t sizes[2] = {(int64_t)chunk * H * 2, (int64_t)chunk * H * 2};
+      mark(5);
       EB_TRY(eb_comm_allgather(e->comm, (c.debug & 1) ? 2 : 1, bufs, sizes, st));
+      mark(-1);
       n += 3;
     }
     n += 9 + (plans[pi].n_parts > n_seqs ? 1 : 0);
@@ -530,7 +549,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     EB_TRY(eb_argmax_partial(e->logits + e->v0, T, e->v1 - e->v0, c.vocab, e->v0, e->cand + (size_t)e->tp_rank * cap * 4, st));
     void* cb[1] = {e->cand};
     const int64_t csz[1] = {cap * 4 * (int64_t)sizeof(float)};
+    mark(5);
     EB_TRY(eb_comm_allgather(e->comm, 1, cb, csz, st));
+    mark(-1);
     EB_TRY(eb_argmax_merge(e->cand, e->tp_size, cap, T, e->d_next, e->d_margin, st));
     n += 2;
   }
@@ -862,10 +883,10 @@ int32_t eb_engine_last_step_stats(const eb_engine* e, float* device_ms, int32_t*
   return EB_OK;
 }
 
-int32_t eb_engine_last_step_breakdown(const eb_engine* e, float* ms5) {
-  EB_REQUIRE(e && ms5, EB_ERR_ARG, "eb_engine_last_step_breakdown: null");
+int32_t eb_engine_last_step_breakdown(const eb_engine* e, float* ms8) {
+  EB_REQUIRE(e && ms8, EB_ERR_ARG, "eb_engine_last_step_breakdown: null");
   EB_REQUIRE(e->c.debug & 2, EB_ERR_STATE, "eb_engine_last_step_breakdown: engine was not created with debug & 2");
-  for (int i = 0; i < 5; ++i) ms5[i] = e->prof_ms[i];
+  for (int i = 0; i < 8; ++i) ms8[i] = e->prof_ms[i];
   return EB_OK;
 }
 

@@ -18,6 +18,127 @@ constexpr int kMaxTopK = 8;
 
 __device__ __forceinline__ float bf(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
 
+// Top-k selection and softmax weights of one token, run by one warp: lane l holds the logits of experts l + 32 q.
+template <int EPL>
+__device__ __forceinline__ void router_select(float (&lg)[EPL], int lane, int E, int top_k, int64_t t, int32_t* idx, float* wts) {
+  float sel[kMaxTopK];
+  for (int j = 0; j < top_k; ++j) {
+    // local best (lowest index on ties: ascending scan with strict >)
+    float bv = -INFINITY;
+    int bi = 0x7FFFFFFF;
+#pragma unroll
+    for (int q = 0; q < EPL; ++q) {
+      const int e = lane + 32 * q;
+      if (e < E && lg[q] > bv) {
+        bv = lg[q];
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    sel[j] = bv;
+    if (lane == 0) idx[(int64_t)t * top_k + j] = bi;
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int q = 0; q < EPL; ++q)
+        if (q == (bi >> 5)) lg[q] = -INFINITY;  // taken
+    }
+  }
+  if (lane == 0) {
+    float ex[kMaxTopK], den = 0.f;
+    for (int j = 0; j < top_k; ++j) {
+      ex[j] = expf(sel[j] - sel[0]);
+      den += ex[j];
+    }
+    for (int j = 0; j < top_k; ++j) wts[(int64_t)t * top_k + j] = ex[j] / den;
+  }
+}
+
+// Few tokens (decode batches): one CTA per token, the experts dealt to its eight warps, router rows read straight from
+// L2 (every lane's loads are issued before any is used, so a token costs about one memory round trip).  The dot
+// products use exactly the order of router_topk_kernel (lane l owns 8-element groups l, l + 32, ..., ascending k,
+// xor butterfly), so both kernels produce the same bits.
+template <int EPL, int GPL>
+__global__ void __launch_bounds__(256)
+router_direct_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, int top_k, int32_t* idx, float* wts,
+                     float* logits_out) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
+  __shared__ float s_lg[kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int H8 = H >> 3;
+  float xr[GPL][8];
+#pragma unroll
+  for (int j = 0; j < GPL; ++j) {
+    const int g = lane + 32 * j;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (g < H8) v = *reinterpret_cast<const uint4*>(x + (int64_t)t * H + 8 * g);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      xr[j][2 * q] = __uint_as_float(w[q] << 16);
+      xr[j][2 * q + 1] = __uint_as_float(w[q] & 0xFFFF0000u);
+    }
+  }
+  for (int e = warp; e < E; e += 16) {  // two experts per pass: e and e + 8
+    const bool two = e + 8 < E;
+    const uint4* w0 = reinterpret_cast<const uint4*>(wr + (int64_t)e * H);
+    const uint4* w1 = reinterpret_cast<const uint4*>(wr + (int64_t)(two ? e + 8 : e) * H);
+    uint4 u0[GPL], u1[GPL];
+#pragma unroll
+    for (int j = 0; j < GPL; ++j) {
+      const int g = lane + 32 * j;
+      u0[j] = u1[j] = make_uint4(0, 0, 0, 0);
+      if (g < H8) {
+        u0[j] = w0[g];
+        u1[j] = w1[g];
+      }
+    }
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < GPL; ++j) {
+      const int g = lane + 32 * j;
+      if (g < H8) {
+        const uint32_t p0[4] = {u0[j].x, u0[j].y, u0[j].z, u0[j].w}, p1[4] = {u1[j].x, u1[j].y, u1[j].z, u1[j].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          a0 = __fmaf_rn(xr[j][2 * q], __uint_as_float(p0[q] << 16), a0);
+          a0 = __fmaf_rn(xr[j][2 * q + 1], __uint_as_float(p0[q] & 0xFFFF0000u), a0);
+          a1 = __fmaf_rn(xr[j][2 * q], __uint_as_float(p1[q] << 16), a1);
+          a1 = __fmaf_rn(xr[j][2 * q + 1], __uint_as_float(p1[q] & 0xFFFF0000u), a1);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      a0 = __fadd_rn(a0, __shfl_xor_sync(0xffffffffu, a0, o));
+      a1 = __fadd_rn(a1, __shfl_xor_sync(0xffffffffu, a1, o));
+    }
+    if (lane == 0) {
+      s_lg[e] = a0;
+      if (two) s_lg[e + 8] = a1;
+      if (logits_out) {
+        logits_out[(int64_t)t * E + e] = a0;
+        if (two) logits_out[(int64_t)t * E + e + 8] = a1;
+      }
+    }
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float lg[EPL];
+#pragma unroll
+  for (int q = 0; q < EPL; ++q) lg[q] = (lane + 32 * q < E) ? s_lg[lane + 32 * q] : -INFINITY;
+  router_select<EPL>(lg, lane, E, top_k, t, idx, wts);
+}
+
 // One warp per token, eight tokens per CTA.  Lane l keeps its slice of the token row (x[k], k = l mod 32) in
 // registers; the CTA streams the router matrix through shared memory eight expert rows at a time (double
 // buffered: the next chunk's 16-byte loads are in flight while the current chunk is reduced), so every row is
@@ -112,44 +233,7 @@ router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, i
   }
   if (!on) return;
 
-  float sel[kMaxTopK];
-  for (int j = 0; j < top_k; ++j) {
-    // local best (lowest index on ties: ascending scan with strict >)
-    float bv = -INFINITY;
-    int bi = 0x7FFFFFFF;
-#pragma unroll
-    for (int q = 0; q < EPL; ++q) {
-      const int e = lane + 32 * q;
-      if (e < E && lg[q] > bv) {
-        bv = lg[q];
-        bi = e;
-      }
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) {
-        bv = ov;
-        bi = oi;
-      }
-    }
-    sel[j] = bv;
-    if (lane == 0) idx[(int64_t)t * top_k + j] = bi;
-    if ((bi & 31) == lane) {
-#pragma unroll
-      for (int q = 0; q < EPL; ++q)
-        if (q == (bi >> 5)) lg[q] = -INFINITY;  // taken
-    }
-  }
-  if (lane == 0) {
-    float ex[kMaxTopK], den = 0.f;
-    for (int j = 0; j < top_k; ++j) {
-      ex[j] = expf(sel[j] - sel[0]);
-      den += ex[j];
-    }
-    for (int j = 0; j < top_k; ++j) wts[(int64_t)t * top_k + j] = ex[j] / den;
-  }
+  router_select<EPL>(lg, lane, E, top_k, t, idx, wts);
 }
 
 // Stable counting sort of the T*top_k routed slots by expert, one CTA of 1024 threads.
@@ -292,6 +376,10 @@ __global__ void moe_combine_kernel(const uint16_t* y, const int32_t* perm_row, c
 template <int EPL, int HPL>
 int32_t launch_router2(unsigned grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wr, int T, int E, int H,
                     int top_k, int32_t* idx, float* wts, float* logits) {
+  if ((int64_t)T * E <= 16384) {  // decode-sized: T * E router rows through L2 cost less than the staged pipeline's latency
+    EB_CUDA(eb::launch(router_direct_kernel<EPL, HPL>, dim3((unsigned)T), dim3(256), 0, st, x, wr, T, E, H, top_k, idx, wts, logits));
+    return EB_OK;
+  }
   auto kfn = router_topk_kernel<EPL, HPL>;
   static bool configured = false;
   if (!configured) {

@@ -317,9 +317,10 @@ class Engine:
             call("eb_engine_debug_force_hidden", self._h, c_i32(layer), ptr(x), c_i32(x.shape[0]))
 
     def last_step_breakdown(self) -> dict:
-        ms = (c_f32 * 5)()
+        ms = (c_f32 * 8)()
         call("eb_engine_last_step_breakdown", self._h, ms)
-        return dict(zip(("attn_full", "attn_window", "dense_gemm", "expert_gemm", "lm_head"), [float(v) for v in ms]))
+        return dict(zip(("attn_full", "attn_window", "dense_gemm", "expert_gemm", "lm_head", "collectives", "router",
+                         "quantisers"), [float(v) for v in ms]))
 
     def stream(self):
         st = c_vp()

@@ -44,7 +44,7 @@
 extern "C" {
 #endif
 
-#define EB_ABI_VERSION 3
+#define EB_ABI_VERSION 4
 
 /* status codes (negative: host validation) */
 #define EB_OK 0
@@ -423,9 +423,11 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
 int32_t eb_engine_step_wait(eb_engine* e, int32_t* h_next, float* h_margin);
 /* Milliseconds the last step spent on the device (CUDA events around its kernels) and kernels it launched. */
 int32_t eb_engine_last_step_stats(const eb_engine* e, float* device_ms, int32_t* kernel_launches);
-/* debug bit 1: device milliseconds of the last step by category: [0] attention on full layers, [1] attention on
- * windowed layers, [2] QKV and O projections, [3] expert GEMMs, [4] LM head. */
-int32_t eb_engine_last_step_breakdown(const eb_engine* e, float* ms5);
+/* debug bit 1: device milliseconds of the last step by category (8 floats): [0] attention on full layers, [1] attention
+ * on windowed layers, [2] QKV and O projections, [3] expert GEMMs, [4] LM head, [5] collectives (tensor-parallel
+ * engines), [6] router, [7] activation quantisers.  What is left of the step is norms, rotary/append, permutation,
+ * combine, argmax and the gaps between kernels. */
+int32_t eb_engine_last_step_breakdown(const eb_engine* e, float* ms8);
 /* The stream the engine launches on (borrowed), so a caller can record its own events around steps. */
 int32_t eb_engine_stream(eb_engine* e, void** stream);
 /* debug bit 0 only: copy out the last step's logits [T][vocab] bf16 and layer routing indices [T][top_k]. */
