@@ -6,10 +6,11 @@
 // conflicts.
 //
 // attn_kernel: one CTA per work item (a run of logical pages of one sequence, planned on the host by
-// eb_attn_plan).  Eight compute warps and one producer warp.  A pipeline stage holds 256 rows (32 KiB):
-// one page when the rank holds 8 KV heads, 8/n_kv pages otherwise.  Compute warp w owns KV head w % n_kv of
-// page w / n_kv of each stage: S = Q K^T and O += P V on mma.sync m16n8k16 (bf16 in, fp32 accumulate), rows of
-// the M tile = (query position, query head of the GQA group), online softmax in base 2 with quad shuffles.
+// eb_attn_plan).  Eight compute warps per 16 query rows (one set for decode, two or three sets for speculative
+// verification) and one producer warp.  A pipeline stage holds 256 rows (32 KiB): one page when the rank holds 8 KV
+// heads, 8/n_kv pages otherwise.  Compute warp w of a set owns KV head w % n_kv of page w / n_kv of each stage:
+// S = Q K^T and O += P V on mma.sync m16n8k16 (bf16 in, fp32 accumulate), rows of the M tile = (query position,
+// query head of the GQA group), online softmax in base 2 with quad shuffles.
 // P is fed to the second MMA as a bf16 head plus a bf16 remainder (two MMAs), so the result carries about 16
 // bits of the softmax weights.  The kernel is HBM-bound: per 2 KiB of K and 2 KiB of V a warp issues 24 MMAs.
 //
@@ -28,7 +29,6 @@ namespace {
 constexpr int kHeadDim = 64;
 constexpr int kPage = 16;
 constexpr int kComputeWarps = 8;
-constexpr int kThreads = (kComputeWarps + 1) * 32;
 constexpr int kStageBytes = 32768;   // 256 rows of 128 bytes
 constexpr int kMaxItemPages = 512;
 constexpr uint32_t kWaitTries = 1u << 22;
@@ -476,10 +476,12 @@ template <int MT, int WT, int HKV, int STAGES, int G>
 int32_t launch_attn(const CUtensorMap& tm, const AttnParams& p, int n_items, cudaStream_t st) {
   const size_t smem = 1024 + (size_t)STAGES * kStageBytes + 2 * STAGES * sizeof(uint64_t) + kMaxItemPages * sizeof(int32_t);
   auto kfn = attn_kernel<MT, WT, HKV, STAGES, G>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {false};  // the attribute is per device
+  int dev = 0;
+  EB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   EB_CUDA(eb::launch(kfn, dim3(n_items), dim3((kComputeWarps * WT + 1) * 32), smem, st, tm, p));
   EB_LAUNCH_CHECK();

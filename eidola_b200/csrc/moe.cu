@@ -381,10 +381,13 @@ int32_t launch_router2(unsigned grid, size_t smem, cudaStream_t st, const uint16
     return EB_OK;
   }
   auto kfn = router_topk_kernel<EPL, HPL>;
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kRouterChunk * HPL * 256 * (int)sizeof(uint16_t));
-    configured = true;
+  static bool configured[64] = {false};  // the attribute is per device
+  int dev = 0;
+  EB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 2 * kRouterChunk * HPL * 256 * (int)sizeof(uint16_t)));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   EB_CUDA(eb::launch(kfn, dim3(grid), dim3(256), smem, st, x, wr, T, E, H, top_k, idx, wts, logits));
   return EB_OK;
