@@ -410,8 +410,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
 //            maximum that is only raised when a score exceeds it by 2^8 (then O is rescaled in tensor memory), and
 //            writes P back over S as a bf16 head and a bf16 remainder (the same ~16 bits as the mma.sync kernel)
 //   O[128 x 64] += P (tensor memory) x V                                                         4 MMAs (16 keys each)
-// S is double buffered: the elected thread of the warpgroup issues P V of block i and S of block i + 2 together, so the
-// softmax of block i + 1 never waits for a product of block i.
+// S is double buffered: one thread of the warpgroup (lane 0 of a warp that holds no rows, when there is one) issues P V
+// of block i and S of block i + 2 together, so the softmax of block i + 1 never waits for a product of block i.
 // Odd heads place their rows 64 lanes up (their Q operand starts 8 KiB early), which spreads the exponentials of a
 // 40-row verify step over all four scheduler partitions.
 constexpr int kTcKeys = 32;
@@ -600,7 +600,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
     const int r = (tid & 127) - row_off;            // query row of this thread (may be outside [0, q_rows))
     const int first_q = row_off >> 5;
     const bool active = qtr >= first_q && qtr < first_q + n_act;   // warp-uniform
-    const bool elected = active && qtr == first_q && lane == 0;
+    // the MMA issuer of the head: lane 0 of a warp that holds no rows (rows <= 64), else of the first active warp
+    const bool spare_issuer = n_act <= 2;
+    const bool issuer_warp = spare_issuer ? qtr == ((first_q + 2) & 3) : qtr == first_q;
+    const bool elected = issuer_warp && lane == 0;
     const bool row_ok = r >= 0 && r < q_rows;
     const int qi = row_ok ? r / tp.group : 0;
     const int head = (head0 + h) * tp.group + (row_ok ? r - qi * tp.group : 0);
@@ -630,9 +633,32 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
       tc_commit(bar_s + 8 * (blk & 1));
       return true;
     };
+    // every active warp of the head has written its rows of P for block `blk`: O += P V, then the S of the block after
+    // next (or the final commit)
+    auto issue_pv = [&](int blk) -> bool {
+      const int b = blk & 1;
+      if (!mbar_wait(bar_pd, blk & 1, &abort_flag, p.status)) return false;
+      tc_fence_after();
+      const int sidx = blk % NS;
+      const uint64_t dv = tc_desc_sw128(stage0 + sidx * kStage + HPC * kHeadK + h * kHeadK);
+#pragma unroll
+      for (int kk = 0; kk < kTcKeys / 16; ++kk) {  // 16 keys per instruction; head, then remainder
+        const uint32_t a_hi = tS + b * 32 + kk * 8;
+        tc_mma_ts(tO, a_hi, dv + (uint64_t)kk * (2048 >> 4), idesc_o, (blk > 0 || kk > 0) ? 1u : 0u);
+        tc_mma_ts(tO, a_hi + 16, dv + (uint64_t)kk * (2048 >> 4), idesc_o, 1u);
+      }
+      tc_commit(bar_empty + 8 * sidx);  // the stage is free once these have read V (K was read by S)
+      tc_commit(bar_pv + 8 * b);
+      bool good = true;
+      if (blk + 2 < n_blk) good = issue_s(blk + 2);
+      if (blk + 1 == n_blk) tc_commit(bar_o);
+      return good;
+    };
     if (elected) {
       ok = issue_s(0);
       if (ok && n_blk > 1) ok = issue_s(1);
+      if (spare_issuer)  // a warp without rows: it only issues, block after block
+        for (int blk = 0; blk < n_blk && ok; ++blk) ok = issue_pv(blk);
     }
 
     if (active) {
@@ -699,27 +725,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_pd);
-        if (elected) {
-          // every active warp of the head has written its rows of P: O += P V, then the S of the block after next
-          if (!mbar_wait(bar_pd, blk & 1, &abort_flag, p.status)) {
-            ok = false;
-          } else {
-            tc_fence_after();
-            const int sidx = blk % NS;
-            const uint64_t dv = tc_desc_sw128(stage0 + sidx * kStage + HPC * kHeadK + h * kHeadK);
-#pragma unroll
-            for (int kk = 0; kk < kTcKeys / 16; ++kk) {  // 16 keys per instruction; head, then remainder
-              const uint32_t a_hi = tS + b * 32 + kk * 8;
-              tc_mma_ts(tO, a_hi, dv + (uint64_t)kk * (2048 >> 4), idesc_o, (blk > 0 || kk > 0) ? 1u : 0u);
-              tc_mma_ts(tO, a_hi + 16, dv + (uint64_t)kk * (2048 >> 4), idesc_o, 1u);
-            }
-            tc_commit(bar_empty + 8 * sidx);  // the stage is free once these have read V (K was read by S)
-            tc_commit(bar_pv + 8 * b);
-            if (blk + 2 < n_blk) ok = issue_s(blk + 2);
-            if (blk + 1 == n_blk) tc_commit(bar_o);
-          }
-        }
-        if (qtr == first_q) ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;  // the issuer's warp follows its lane 0
+        if (elected && !spare_issuer) ok = issue_pv(blk);
+        if (issuer_warp) ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;  // the issuer's warp follows its lane 0
       }
       // ---------------- epilogue: O of this row
       if (ok && n_blk > 0 && mbar_wait(bar_o, 0, &abort_flag, p.status)) {
@@ -918,7 +925,7 @@ int32_t launch_attn_tc(EncodeTiledFn enc, const void* d_cache, int64_t cache_row
 }
 
 // EIDOLA_B200_ATTN_TC=1 runs verify shapes on the tcgen05 kernel.  It is exact to the same tolerance as the mma.sync
-// kernel but measured slower (901 us against 530 us at q_len 5 on the 256-sequence benchmark: the per-block chain
+// kernel but measured slower (741 us against 530 us at q_len 5 on the 256-sequence benchmark: the per-block chain
 // tensor-memory load -> exponentials -> tensor-memory store -> barrier -> MMA issue is what bounds it, not the tensor
 // pipe, which is 13 % busy), so it is off unless asked for.  Read on every call so that a test can switch it.
 bool attn_tc_enabled() {
