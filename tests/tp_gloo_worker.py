@@ -4,8 +4,12 @@
 
 Each rank computes its shard of every decoder layer with the CPU oracle's operators -- its query heads, its KV heads
 (with the 128-row K/V weight bands a rank shares with its neighbour when it holds a single KV head), its slice of
-the O projection's K dimension, its experts -- and the two per-layer sums go through torch.distributed (gloo).
-Every layer starts from the unsharded oracle's input (teacher forcing); rank 0 saves the outputs.
+the O projection's K dimension, its experts -- and the per-layer exchanges go through torch.distributed (gloo) in
+the engine's form: the two fp32 sums are reduce-scatters over token slices (gloo has no reduce-scatter: an
+all-reduce of which a rank keeps its slice), the slice's owner adds the residual, normalises and routes its tokens,
+and the rows and the routing are all-gathered.  The LM head is split over the vocabulary and the ranks' argmax
+candidates are merged.  Every layer starts from the unsharded oracle's input (teacher forcing); rank 0 saves the
+outputs.
 """
 import os
 import sys
@@ -58,6 +62,18 @@ def main():
     toks = np.random.default_rng(1).integers(0, cfg.vocab, size=T).astype(np.int32)
     ref = model.step(p, toks, bt, want_debug=True)
 
+    chunk = -(-T // world)                                   # token slice of this rank: equal chunks, the last may be short
+    t0, t1 = min(T, rank * chunk), min(T, (rank + 1) * chunk)
+
+    def gather_rows(mine, width, dtype):
+        """All-gather of equal chunks of rows; returns the first T rows."""
+        buf = np.zeros((chunk, width), dtype)
+        buf[: t1 - t0] = mine
+        wire = buf.view(np.uint8)                                  # gloo has no 16-bit integer types: send the bytes
+        parts = [torch.zeros(wire.shape, dtype=torch.uint8) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(wire))
+        return np.concatenate([q.numpy() for q in parts]).view(dtype)[:T]
+
     cos, sin = orc.rope_table(cfg.max_pages_per_seq * cfg.page_size, D, float(cfg.rope_theta))
     ones = np.ones(H, np.float32)
     outs = []
@@ -87,12 +103,22 @@ def main():
         o_part = bf16_to_f32(orc.gemm_fp8_block(a8, sa, np.ascontiguousarray(wo[:, c0:c0 + hqd_l]),
                                                 np.ascontiguousarray(so[:, c0 // 128:(c0 + hqd_l) // 128]))).copy()
         t_o = torch.from_numpy(o_part)
-        dist.all_reduce(t_o)                                   # C1: sum over the ranks' heads
-        orc.residual_add(x, orc.bf16_encode(t_o.numpy()))
-        # ---- expert half, this rank's experts
-        h2 = orc.rmsnorm(x, ones, cfg.rms_eps)
+        dist.all_reduce(t_o)                                   # C1: sum over the ranks' heads; this rank keeps rows [t0, t1)
+        xs = np.ascontiguousarray(x[t0:t1])
+        orc.residual_add(xs, orc.bf16_encode(t_o.numpy()[t0:t1]))
+        # ---- expert half: the slice's owner normalises and routes, rows and routing are gathered
+        h2s = orc.rmsnorm(xs, ones, cfg.rms_eps) if t1 > t0 else np.zeros((0, H), np.uint16)
         wr = orc.synth_normal_bf16(cfg.seed, sid(l, 3), 0, E * H, cfg.init_std).reshape(E, H)
-        idx, wts, _ = orc.router_topk(h2, wr, K)               # replicated: identical on every rank
+        if t1 > t0:
+            idx_s, wts_s, _ = orc.router_topk(h2s, wr, K)
+        else:
+            idx_s, wts_s = np.zeros((0, K), np.int32), np.zeros((0, K), np.float32)
+        h2 = gather_rows(h2s, H, np.uint16)
+        idx = gather_rows(idx_s, K, np.int32)
+        wts = gather_rows(wts_s, K, np.float32)
+        x = gather_rows(xs, H, np.uint16)                      # (the engine keeps the residual sliced; the check wants it whole)
+        idx_all, wts_all, _ = orc.router_topk(h2, wr, K)       # routing a slice gives the bits of routing everything
+        assert np.array_equal(idx, idx_all) and np.array_equal(wts, wts_all)
         mine = (idx >= rank * e_l) & (idx < (rank + 1) * e_l)
         w1 = [orc.synth_weight_fp8(cfg.seed, sid(l, 4, e), 2 * I, H, 0, 2 * I, cfg.init_std) for e in range(E)]
         w2 = [orc.synth_weight_fp8(cfg.seed, sid(l, 5, e), H, I, 0, H, cfg.init_std) for e in range(E)]
@@ -100,12 +126,40 @@ def main():
                                            np.stack([a for a, _ in w1]), np.stack([b for _, b in w1]),
                                            np.stack([a for a, _ in w2]), np.stack([b for _, b in w2]))).copy()
         t_m = torch.from_numpy(part)
-        dist.all_reduce(t_m)                                   # C2: sum over the ranks' experts
-        orc.residual_add(x, orc.bf16_encode(t_m.numpy()))
+        dist.all_reduce(t_m)                                   # C2: sum over the ranks' experts; rows [t0, t1) kept
+        xs = np.ascontiguousarray(x[t0:t1])
+        orc.residual_add(xs, orc.bf16_encode(t_m.numpy()[t0:t1]))
+        x = gather_rows(xs, H, np.uint16)
         outs.append(x)
         gathered = [None] * world
         dist.all_gather_object(gathered, idx.tobytes())
         assert all(g == gathered[0] for g in gathered), "routing differs between ranks"
+    # ---- vocabulary-parallel LM head on the oracle's final hidden state: candidates {top1, top2, id} per rank, merged
+    blocks = (cfg.vocab + 127) // 128
+    per = -(-blocks // world)
+    v0, v1 = min(cfg.vocab, rank * per * 128), min(cfg.vocab, (rank + 1) * per * 128)
+    hf = orc.rmsnorm(ref["hidden"][cfg.n_layers], ones, cfg.rms_eps)
+    hf8, shf = orc.quant_act_block128(hf)
+    wlm, slm = orc.synth_weight_fp8(cfg.seed, sid(-1, 2), cfg.vocab, H, v0, v1 - v0, cfg.init_std)
+    lg = bf16_to_f32(orc.gemm_fp8_block(hf8, shf, wlm, slm))
+    order = np.argsort(-lg, axis=1, kind="stable")           # stable: ties keep the lower id first
+    cand = np.stack([lg[np.arange(T), order[:, 0]], lg[np.arange(T), order[:, 1]], (order[:, 0] + v0).astype(np.float32)], axis=1)
+    parts = [torch.zeros(T, 3) for _ in range(world)]
+    dist.all_gather(parts, torch.from_numpy(cand.astype(np.float32)))
+    best = np.full(T, -np.inf, np.float32)
+    second = np.full(T, -np.inf, np.float32)
+    tok = np.zeros(T, np.int64)
+    for q in parts:                                           # ranks in ascending vocabulary order: strict > keeps the lower id
+        c = q.numpy()
+        win = c[:, 0] > best
+        second = np.where(win, np.maximum(best, c[:, 1]), np.maximum(second, c[:, 0]))
+        tok = np.where(win, c[:, 2].astype(np.int64), tok)
+        best = np.where(win, c[:, 0], best)
+    full = bf16_to_f32(ref["logits"])
+    want_tok = full.argmax(axis=1)
+    top2 = np.sort(full, axis=1)[:, -2:]
+    assert np.array_equal(tok, want_tok), "merged vocabulary-parallel argmax differs from the whole-row argmax"
+    assert np.array_equal(best - second, top2[:, 1] - top2[:, 0])
     if rank == 0:
         np.savez(sys.argv[1], got=np.stack(outs), want=ref["hidden"][1:], route=ref["route_idx"])
     dist.barrier()
