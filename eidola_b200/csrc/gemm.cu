@@ -936,12 +936,14 @@ int32_t launch_gemm_persistent(const CUtensorMap& tw, const CUtensorMap& tx, con
 
 // Dense GEMMs of 512 tokens and more take the 128-token x 256-row kernel unless the caller fixed a tile or a split.
 // EIDOLA_B200_GEMM_BIG=0 keeps them on the decode kernels (for A/B timing).
-bool gemm_big(int rows, int tile_tokens, int splits) {
+bool gemm_big(int rows, int N, int tile_tokens, int splits) {
   static const bool on = [] {
     const char* v = getenv("EIDOLA_B200_GEMM_BIG");
     return !(v && v[0] == '0');
   }();
-  return on && rows >= 512 && tile_tokens == 0 && splits <= 1;
+  // 512 tokens and more; from 256 tokens on when the weight matrix is so tall (an LM head) that the decode kernels'
+  // re-reading of the activations through L2 costs more than half-empty 128-token tiles
+  return on && (rows >= 512 || (rows >= 256 && N >= 65536)) && tile_tokens == 0 && splits <= 1;
 }
 
 int pick_tn(int64_t rows_per_group) {
@@ -1029,7 +1031,7 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
   }
   EB_REQUIRE(nb <= 65535, EB_ERR_UNSUPPORTED, "gemm: %d weight tiles exceed the grid", nb);
 
-  if (!grouped && gemm_big(a->rows, a->tile_tokens, a->splits)) {
+  if (!grouped && gemm_big(a->rows, a->N, a->tile_tokens, a->splits)) {
     CUtensorMap bw, bx;
     int32_t brc = eb::make_tmap_2d_sw128(&bw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, (uint64_t)a->N, (uint64_t)a->K,
                                          (uint64_t)a->K, kBigRows);
