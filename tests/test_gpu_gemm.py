@@ -149,9 +149,10 @@ def test_gemm_workspace_too_small_is_refused_or_degrades(gpu):
                       work=DeviceBuffer(8))
 
 
-@pytest.mark.parametrize("M,N,K", [(1024, 5120, 2880), (600, 2880, 512), (513, 200, 4096)])
+@pytest.mark.parametrize("M,N,K", [(1024, 5120, 2880), (600, 2880, 512), (513, 200, 4096), (300, 65536, 256)])
 def test_gemm_dense_prefill_sized_matches_oracle(gpu, M, N, K):
-    """512 tokens and more run on the 128-token x 256-row kernel: ragged token and weight-row edges included."""
+    """512 tokens and more (256 and more against a very tall weight matrix, the LM-head shape) run on the 128-token x
+    256-row kernel: ragged token and weight-row edges included."""
     import eidola_b200.host as host
     from eidola_b200.capi import DeviceBuffer
     x8, sx, w8, sw = _sweep_inputs(M, N, K, seed=6)
