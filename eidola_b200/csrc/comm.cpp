@@ -151,6 +151,15 @@ int32_t eb_comm_reduce_scatter_f32(eb_comm* c, void* d_buf, int64_t count_per_ra
   return EB_OK;
 }
 
+// The same on bf16 elements (half the bytes on the wire; the sum is rounded to bf16 on the way).
+int32_t eb_comm_reduce_scatter_bf16(eb_comm* c, void* d_buf, int64_t count_per_rank, void* stream) {
+  EB_REQUIRE(c && d_buf && count_per_rank >= 0, EB_ERR_ARG, "eb_comm_reduce_scatter_bf16: bad argument");
+  if (count_per_rank == 0 || c->size == 1) return EB_OK;
+  EB_NCCL(api().ReduceScatter(d_buf, (uint16_t*)d_buf + (size_t)c->rank * count_per_rank, (size_t)count_per_rank, ncclBfloat16,
+                              ncclSum, c->comm, eb::as_stream(stream)));
+  return EB_OK;
+}
+
 // Asynchronous error of the communicator (0 = healthy).  A host that sees a non-zero value, or whose step does not
 // return within its own deadline, calls eb_comm_abort and rebuilds the communicator.
 int32_t eb_comm_async_error(eb_comm* c, int32_t* err) {

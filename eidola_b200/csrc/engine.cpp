@@ -222,7 +222,7 @@ int32_t init_work(eb_engine* e) {
   EB_TRY(dev_alloc(e, &e->h, Tc * H, w));
   EB_TRY(dev_alloc(e, &e->qkv, (size_t)T * e->nqkv, w));
   EB_TRY(dev_alloc(e, &e->attn, (size_t)T * e->hqd, w));
-  EB_TRY(dev_alloc(e, &e->o, (size_t)T * H, w));
+  EB_TRY(dev_alloc(e, &e->o, Tc * H, w));  // also the bf16 operand of the tensor-parallel reduce-scatters
   EB_TRY(dev_alloc(e, &e->gu, (size_t)R * 2 * I, w));
   EB_TRY(dev_alloc(e, &e->y, (size_t)R * H, w));
   EB_TRY(dev_alloc(e, &e->logits, (size_t)T * c.vocab, w));
@@ -453,15 +453,26 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       EB_TRY(eb_oproj_residual_rmsnorm(splits > 1 ? (const float*)e->gemm_ws : nullptr, splits, e->o, e->x, L.g_mlp, T, H,
                                        c.rms_eps, e->h, st));
     } else {
-      // C1: this rank's heads contributed a partial [T, H].  Reduce-scatter the fp32 partials over token slices; the
-      // owner of a slice adds the residual, rounds once and normalises; the normalised rows are gathered below.
-      EB_TRY(eb_sum_planes_f32(splits > 1 ? (const float*)e->gemm_ws : nullptr, splits, e->o, (int64_t)T * H, e->ar_buf, st));
-      mark(5);
-      EB_TRY(eb_comm_reduce_scatter_f32(e->comm, e->ar_buf, (int64_t)chunk * H, st));
-      mark(-1);
-      EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf + (size_t)t0 * H, 1, nullptr, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
-                                       e->h + (size_t)t0 * H, st));
-      n += 2;
+      // C1: this rank's heads contributed a partial [T, H].  Reduce-scatter the partials over token slices; the owner
+      // of a slice adds the residual, rounds once and normalises; the normalised rows are gathered below.  Prefill-
+      // sized steps have the partial in bf16 already (the GEMM's output) and scatter it as such, half the bytes;
+      // decode-sized steps sum their split-K planes in fp32 and scatter fp32.
+      if (splits == 1) {
+        mark(5);
+        EB_TRY(eb_comm_reduce_scatter_bf16(e->comm, e->o, (int64_t)chunk * H, st));
+        mark(-1);
+        EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
+                                         e->h + (size_t)t0 * H, st));
+        n += 1;
+      } else {
+        EB_TRY(eb_sum_planes_f32((const float*)e->gemm_ws, splits, e->o, (int64_t)T * H, e->ar_buf, st));
+        mark(5);
+        EB_TRY(eb_comm_reduce_scatter_f32(e->comm, e->ar_buf, (int64_t)chunk * H, st));
+        mark(-1);
+        EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf + (size_t)t0 * H, 1, nullptr, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
+                                         e->h + (size_t)t0 * H, st));
+        n += 2;
+      }
     }
     mark(6);
     if (!tp) {
@@ -508,11 +519,11 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     } else {
       // C2: partial mix of this rank's experts, summed across ranks (tokens are replicated, so the combine of an
       // expert-parallel layer is an all-reduce and the dispatch needs no exchange)
-      EB_TRY(eb_moe_combine_f32(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->ar_buf, st));
+      EB_TRY(eb_moe_combine_bf16(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->o, st));
       mark(5);
-      EB_TRY(eb_comm_reduce_scatter_f32(e->comm, e->ar_buf, (int64_t)chunk * H, st));
+      EB_TRY(eb_comm_reduce_scatter_bf16(e->comm, e->o, (int64_t)chunk * H, st));
       mark(-1);
-      EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf + (size_t)t0 * H, 1, nullptr, e->x + (size_t)t0 * H, g_next, nt, H, c.rms_eps,
+      EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, g_next, nt, H, c.rms_eps,
                                        e->h + (size_t)t0 * H, st));
       // the next consumer (QKV projection of the next layer, or the LM head) needs every token's normalised row; the
       // residual stream itself stays sliced, except when the debug taps want it whole

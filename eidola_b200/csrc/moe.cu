@@ -509,6 +509,7 @@ __global__ void localize_experts_kernel(const int32_t* idx, int n, int e0, int e
 }
 
 // out[t] = sum over this rank's slots j of w[t][j] * y[perm_row[t][j]]  (fp32, slots in ascending j)
+template <int BF16_OUT>
 __global__ void moe_combine_f32_kernel(const uint16_t* y, const int32_t* perm_row, const float* wts, int T, int top_k, int H,
                                        float* out, int64_t n_rows) {
   eb::pdl_wait();
@@ -530,9 +531,16 @@ __global__ void moe_combine_f32_kernel(const uint16_t* y, const int32_t* perm_ro
       acc[2 * k + 1] = __fmaf_rn(w, __uint_as_float(u[k] & 0xFFFF0000u), acc[2 * k + 1]);
     }
   }
-  float4* o = reinterpret_cast<float4*>(out + (int64_t)t * H + c);
-  o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-  o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  if (BF16_OUT) {
+    uint32_t h[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(h[k]) : "f"(acc[2 * k + 1]), "f"(acc[2 * k]));
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (int64_t)t * H + c) = make_uint4(h[0], h[1], h[2], h[3]);
+  } else {
+    float4* o = reinterpret_cast<float4*>(out + (int64_t)t * H + c);
+    o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
 }
 
 }  // namespace
@@ -559,8 +567,20 @@ int32_t eb_moe_combine_f32(const void* d_y, const int32_t* d_perm_row, const flo
   EB_REQUIRE(T >= 0 && top_k >= 1 && H >= 8 && H % 8 == 0, EB_ERR_ARG, "eb_moe_combine_f32: H %d must be a multiple of 8", H);
   if (T == 0) return EB_OK;
   const int64_t n = (int64_t)T * (H / 8);
-  EB_CUDA(eb::launch(moe_combine_f32_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream),
+  EB_CUDA(eb::launch(moe_combine_f32_kernel<0>, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream),
                      (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, d_out, (int64_t)T * top_k));
+  return EB_OK;
+}
+
+int32_t eb_moe_combine_bf16(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k, int32_t H,
+                            void* d_out, void* stream) {
+  EB_REQUIRE(d_y && d_perm_row && d_wts && d_out, EB_ERR_ARG, "eb_moe_combine_bf16: null pointer");
+  EB_REQUIRE(T >= 0 && top_k >= 1 && H >= 8 && H % 8 == 0, EB_ERR_ARG, "eb_moe_combine_bf16: H %d must be a multiple of 8", H);
+  EB_REQUIRE((uintptr_t)d_out % 16 == 0, EB_ERR_ARG, "eb_moe_combine_bf16: output must be 16-byte aligned");
+  if (T == 0) return EB_OK;
+  const int64_t n = (int64_t)T * (H / 8);
+  EB_CUDA(eb::launch(moe_combine_f32_kernel<1>, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream),
+                     (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, (float*)d_out, (int64_t)T * top_k));
   return EB_OK;
 }
 

@@ -333,6 +333,9 @@ int32_t eb_moe_permute_tiles_local(const int32_t* d_idx_local, int32_t T, int32_
                                    void* stream);
 int32_t eb_moe_combine_f32(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k, int32_t H,
                            float* d_out, void* stream);
+/* The same partial mix rounded once to bf16 (the operand of a bf16 reduce-scatter). */
+int32_t eb_moe_combine_bf16(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k, int32_t H,
+                            void* d_out, void* stream);
 /* x = bf16(x + bf16(sum_j w_j y[perm_row])) as eb_moe_combine, then h = rmsnorm(x) * g for the next consumer. */
 int32_t eb_moe_combine_rmsnorm(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
                                int32_t H, void* d_x, const float* d_g, float eps, void* d_h, void* stream);
@@ -384,6 +387,8 @@ int32_t eb_comm_allgather(eb_comm* c, int32_t n_bufs, void* const* d_bufs, const
 /* In-place fp32 reduce-scatter: d_buf holds size * count_per_rank floats; on return rank r's slice
  * [r * count_per_rank, (r + 1) * count_per_rank) holds the sum over ranks, the other slices are undefined. */
 int32_t eb_comm_reduce_scatter_f32(eb_comm* c, void* d_buf, int64_t count_per_rank, void* stream);
+/* The same on bf16 elements: half the bytes, the sum rounded to bf16 on the way. */
+int32_t eb_comm_reduce_scatter_bf16(eb_comm* c, void* d_buf, int64_t count_per_rank, void* stream);
 /* 0 = healthy.  A host whose step does not return within its own deadline, or that reads a non-zero value, aborts
  * the communicator and rebuilds it (failure handling stays on the host; kernels never wait on a peer). */
 int32_t eb_comm_async_error(eb_comm* c, int32_t* err);
