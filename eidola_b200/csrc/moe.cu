@@ -9,6 +9,8 @@
 // The reference project has no router (inference is delegated, crates/eidola-server/src/backend.rs:421-433).
 #include <cuda_runtime.h>
 
+#include <stdlib.h>
+
 #include "common.h"
 
 namespace {
@@ -61,7 +63,7 @@ __device__ __forceinline__ void router_select(float (&lg)[EPL], int lane, int E,
   }
 }
 
-// Few tokens (decode batches): one CTA per token, the experts dealt to its eight warps, router rows read straight from
+// Few tokens (decode batches, token slices of a tensor-parallel rank): one CTA per token, the experts dealt to its eight warps, router rows read straight from
 // L2 (every lane's loads are issued before any is used, so a token costs about one memory round trip).  The dot
 // products use exactly the order of router_topk_kernel (lane l owns 8-element groups l, l + 32, ..., ascending k,
 // xor butterfly), so both kernels produce the same bits.
@@ -376,7 +378,10 @@ __global__ void moe_combine_kernel(const uint16_t* y, const int32_t* perm_row, c
 template <int EPL, int HPL>
 int32_t launch_router2(unsigned grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wr, int T, int E, int H,
                     int top_k, int32_t* idx, float* wts, float* logits) {
-  if ((int64_t)T * E <= 16384) {  // decode-sized: T * E router rows through L2 cost less than the staged pipeline's latency
+  // Up to 640 tokens the one-token-per-CTA kernel wins: it costs ~1.1 ns per (token, expert) (router rows re-read
+  // through L2), the staged pipeline at least ~5 us per 8 experts however few tokens there are (measured at 32 and 128
+  // experts: 46 against 85 us at 320 x 128, 11 against 21 us at 256 x 32; the staged kernel leads from ~1000 tokens).
+  if (T <= 640) {
     EB_CUDA(eb::launch(router_direct_kernel<EPL, HPL>, dim3((unsigned)T), dim3(256), 0, st, x, wr, T, E, H, top_k, idx, wts, logits));
     return EB_OK;
   }
