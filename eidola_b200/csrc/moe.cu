@@ -63,33 +63,30 @@ __device__ __forceinline__ void router_select(float (&lg)[EPL], int lane, int E,
   }
 }
 
-// Few tokens (decode batches, token slices of a tensor-parallel rank): one CTA per token, the experts dealt to its eight warps, router rows read straight from
-// L2 (every lane's loads are issued before any is used, so a token costs about one memory round trip).  The dot
-// products use exactly the order of router_topk_kernel (lane l owns 8-element groups l, l + 32, ..., ascending k,
-// xor butterfly), so both kernels produce the same bits.
-template <int EPL, int GPL>
+// Few tokens (decode batches, token slices of a tensor-parallel rank): one CTA per TPC tokens (1 or 2), the experts
+// dealt to its eight warps, router rows read straight from L2 (every lane's loads are issued before any is used, so
+// a pass over two experts costs about one memory round trip; with TPC = 2 a row fetched once serves two tokens).
+// The dot products use exactly the order of router_topk_kernel (lane l owns 8-element groups l, l + 32, ...,
+// ascending k, xor butterfly), so all router kernels produce the same bits.
+template <int EPL, int GPL, int TPC>
 __global__ void __launch_bounds__(256)
 router_direct_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, int top_k, int32_t* idx, float* wts,
                      float* logits_out) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
-  __shared__ float s_lg[kMaxExperts];
+  __shared__ float s_lg[TPC][kMaxExperts];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x;
+  const int t0 = blockIdx.x * TPC;
   const int H8 = H >> 3;
-  float xr[GPL][8];
+  uint4 xp[TPC][GPL];  // the tokens' rows as packed bf16 pairs
 #pragma unroll
-  for (int j = 0; j < GPL; ++j) {
-    const int g = lane + 32 * j;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (g < H8) v = *reinterpret_cast<const uint4*>(x + (int64_t)t * H + 8 * g);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  for (int k = 0; k < TPC; ++k)
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      xr[j][2 * q] = __uint_as_float(w[q] << 16);
-      xr[j][2 * q + 1] = __uint_as_float(w[q] & 0xFFFF0000u);
+    for (int j = 0; j < GPL; ++j) {
+      const int g = lane + 32 * j;
+      xp[k][j] = make_uint4(0, 0, 0, 0);
+      if (g < H8 && t0 + k < T) xp[k][j] = *reinterpret_cast<const uint4*>(x + (int64_t)(t0 + k) * H + 8 * g);
     }
-  }
   for (int e = warp; e < E; e += 16) {  // two experts per pass: e and e + 8
     const bool two = e + 8 < E;
     const uint4* w0 = reinterpret_cast<const uint4*>(wr + (int64_t)e * H);
@@ -104,41 +101,51 @@ router_direct_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H,
         u1[j] = w1[g];
       }
     }
-    float a0 = 0.f, a1 = 0.f;
+    float a0[TPC], a1[TPC];
+#pragma unroll
+    for (int k = 0; k < TPC; ++k) a0[k] = a1[k] = 0.f;
 #pragma unroll
     for (int j = 0; j < GPL; ++j) {
       const int g = lane + 32 * j;
       if (g < H8) {
         const uint32_t p0[4] = {u0[j].x, u0[j].y, u0[j].z, u0[j].w}, p1[4] = {u1[j].x, u1[j].y, u1[j].z, u1[j].w};
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          a0 = __fmaf_rn(xr[j][2 * q], __uint_as_float(p0[q] << 16), a0);
-          a0 = __fmaf_rn(xr[j][2 * q + 1], __uint_as_float(p0[q] & 0xFFFF0000u), a0);
-          a1 = __fmaf_rn(xr[j][2 * q], __uint_as_float(p1[q] << 16), a1);
-          a1 = __fmaf_rn(xr[j][2 * q + 1], __uint_as_float(p1[q] & 0xFFFF0000u), a1);
+        for (int k = 0; k < TPC; ++k) {
+          const uint32_t xw[4] = {xp[k][j].x, xp[k][j].y, xp[k][j].z, xp[k][j].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float xl = __uint_as_float(xw[q] << 16), xh = __uint_as_float(xw[q] & 0xFFFF0000u);
+            a0[k] = __fmaf_rn(xl, __uint_as_float(p0[q] << 16), a0[k]);
+            a0[k] = __fmaf_rn(xh, __uint_as_float(p0[q] & 0xFFFF0000u), a0[k]);
+            a1[k] = __fmaf_rn(xl, __uint_as_float(p1[q] << 16), a1[k]);
+            a1[k] = __fmaf_rn(xh, __uint_as_float(p1[q] & 0xFFFF0000u), a1[k]);
+          }
         }
       }
     }
 #pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      a0 = __fadd_rn(a0, __shfl_xor_sync(0xffffffffu, a0, o));
-      a1 = __fadd_rn(a1, __shfl_xor_sync(0xffffffffu, a1, o));
-    }
-    if (lane == 0) {
-      s_lg[e] = a0;
-      if (two) s_lg[e + 8] = a1;
-      if (logits_out) {
-        logits_out[(int64_t)t * E + e] = a0;
-        if (two) logits_out[(int64_t)t * E + e + 8] = a1;
+    for (int k = 0; k < TPC; ++k) {
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        a0[k] = __fadd_rn(a0[k], __shfl_xor_sync(0xffffffffu, a0[k], o));
+        a1[k] = __fadd_rn(a1[k], __shfl_xor_sync(0xffffffffu, a1[k], o));
+      }
+      if (lane == 0 && t0 + k < T) {
+        s_lg[k][e] = a0[k];
+        if (two) s_lg[k][e + 8] = a1[k];
+        if (logits_out) {
+          logits_out[(int64_t)(t0 + k) * E + e] = a0[k];
+          if (two) logits_out[(int64_t)(t0 + k) * E + e + 8] = a1[k];
+        }
       }
     }
   }
   __syncthreads();
-  if (warp != 0) return;
+  if (warp >= TPC || t0 + warp >= T) return;  // warp k finishes token t0 + k
   float lg[EPL];
 #pragma unroll
-  for (int q = 0; q < EPL; ++q) lg[q] = (lane + 32 * q < E) ? s_lg[lane + 32 * q] : -INFINITY;
-  router_select<EPL>(lg, lane, E, top_k, t, idx, wts);
+  for (int q = 0; q < EPL; ++q) lg[q] = (lane + 32 * q < E) ? s_lg[warp][lane + 32 * q] : -INFINITY;
+  router_select<EPL>(lg, lane, E, top_k, t0 + warp, idx, wts);
 }
 
 // One warp per token, eight tokens per CTA.  Lane l keeps its slice of the token row (x[k], k = l mod 32) in
@@ -382,7 +389,11 @@ int32_t launch_router2(unsigned grid, size_t smem, cudaStream_t st, const uint16
   // through L2), the staged pipeline at least ~5 us per 8 experts however few tokens there are (measured at 32 and 128
   // experts: 46 against 85 us at 320 x 128, 11 against 21 us at 256 x 32; the staged kernel leads from ~1000 tokens).
   if (T <= 640) {
-    EB_CUDA(eb::launch(router_direct_kernel<EPL, HPL>, dim3((unsigned)T), dim3(256), 0, st, x, wr, T, E, H, top_k, idx, wts, logits));
+    if (T <= 296)  // one token per CTA while that does not exceed two CTAs per SM
+      EB_CUDA(eb::launch(router_direct_kernel<EPL, HPL, 1>, dim3((unsigned)T), dim3(256), 0, st, x, wr, T, E, H, top_k, idx, wts, logits));
+    else
+      EB_CUDA(eb::launch(router_direct_kernel<EPL, HPL, 2>, dim3((unsigned)((T + 1) / 2)), dim3(256), 0, st, x, wr, T, E, H, top_k, idx,
+                         wts, logits));
     return EB_OK;
   }
   auto kfn = router_topk_kernel<EPL, HPL>;

@@ -18,7 +18,9 @@ def _call(fn, *args):
     capi.call(fn, *args)
 
 
-@pytest.mark.parametrize("T,E,H,k", [(256, 32, 2880, 4), (37, 128, 2880, 4), (4, 8, 512, 2), (5, 256, 512, 8)])
+# 256 / 37 / 4 / 5 tokens: one token per CTA; 601: two tokens per CTA (odd count); 1000: the staged eight-tokens-per-CTA kernel
+@pytest.mark.parametrize("T,E,H,k", [(256, 32, 2880, 4), (37, 128, 2880, 4), (4, 8, 512, 2), (5, 256, 512, 8),
+                                     (601, 128, 2880, 4), (1000, 32, 2880, 4)])
 def test_router_indices_and_logits_bit_exact(gpu, T, E, H, k):
     from eidola_b200.capi import DeviceBuffer, c_i32, c_vp
     x = orc.synth_normal_bf16(5, 1, 0, T * H).reshape(T, H)
