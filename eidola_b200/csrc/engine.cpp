@@ -217,7 +217,7 @@ int32_t init_work(eb_engine* e) {
   const int64_t R = (int64_t)T * c.top_k;
   int64_t* w = &e->work_bytes;
   // under tensor parallelism rows are dealt to ranks in tp_size equal chunks for the in-place collectives: slack rows
-  const size_t Tc = (size_t)T + (size_t)e->tp_size;
+  const size_t Tc = (size_t)T + (e->tp_size > 1 ? (size_t)e->tp_size * 128 : 0);  // slices are whole 128-row scale blocks
   EB_TRY(dev_alloc(e, &e->x, Tc * H, w));
   EB_TRY(dev_alloc(e, &e->h, Tc * H, w));
   EB_TRY(dev_alloc(e, &e->qkv, (size_t)T * e->nqkv, w));
@@ -226,17 +226,17 @@ int32_t init_work(eb_engine* e) {
   EB_TRY(dev_alloc(e, &e->gu, (size_t)R * 2 * I, w));
   EB_TRY(dev_alloc(e, &e->y, (size_t)R * H, w));
   EB_TRY(dev_alloc(e, &e->logits, (size_t)T * c.vocab, w));
-  EB_TRY(dev_alloc(e, &e->h8, (size_t)T * H, w));
+  EB_TRY(dev_alloc(e, &e->h8, Tc * H, w));
   EB_TRY(dev_alloc(e, &e->a8, (size_t)T * e->hqd, w));
   EB_TRY(dev_alloc(e, &e->xp8, (size_t)R * H, w));
   EB_TRY(dev_alloc(e, &e->act8, (size_t)R * I, w));
-  const int64_t tb = eb::cdiv(T, 128), rb = R / 128 + E;
+  const int64_t tb = eb::cdiv((int64_t)Tc, 128), rb = R / 128 + E;
   EB_TRY(dev_alloc(e, &e->sh, (size_t)(tb * e->kbH), w));
   EB_TRY(dev_alloc(e, &e->sa, (size_t)(tb * e->kbA), w));
   EB_TRY(dev_alloc(e, &e->sxp, (size_t)(rb * e->kbH), w));
   EB_TRY(dev_alloc(e, &e->sact, (size_t)(rb * e->kbI), w));
   // routing is computed on a token slice per rank and all-gathered in place: room for tp_size equal chunks
-  const size_t r_cap = (size_t)R + (size_t)e->tp_size * c.top_k;
+  const size_t r_cap = (size_t)R + (e->tp_size > 1 ? (size_t)e->tp_size * 128 * c.top_k : 0);
   EB_TRY(dev_alloc(e, &e->r_idx, r_cap, w));
   EB_TRY(dev_alloc(e, &e->r_idx_local, (size_t)R, w));
   if (e->tp_size > 1) {
@@ -317,8 +317,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   const eb_config& c = e->c;
   const int H = c.hidden, I = c.inter, E = e->e_l, R = T * c.top_k;  // E: local experts; R: upper bound of local rows
   const bool tp = e->tp_size > 1;
-  // token slice of this rank for the reduce-scatter / all-gather pairs (tp_size equal chunks, the last ones may be short)
-  const int chunk = (T + e->tp_size - 1) / e->tp_size;
+  // token slice of this rank for the reduce-scatter / all-gather pairs: tp_size equal chunks of whole 128-row scale
+  // blocks (so that a slice can be quantised by its owner), the last ones may be short or empty
+  const int chunk = ((T + e->tp_size - 1) / e->tp_size + 127) / 128 * 128;
   const int t0 = std::min(T, e->tp_rank * chunk), nt = std::min(T, t0 + chunk) - t0;
   void* st = e->stream;
   const int max_pos = c.max_pages_per_seq * c.page_size;
@@ -392,6 +393,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     return EB_OK;
   };
   // h = rmsnorm(x) of the first layer; later layers get it from the fused combine of the layer before
+  bool h8_ready = false;  // tensor parallel: the e4m3 rows and scales of h were gathered, no rank quantises all of h
   EB_TRY(eb_rmsnorm(e->x, e->layers[0].g_attn, T, H, c.rms_eps, e->h, st));
   n += 1;
   for (int l = 0; l < c.n_layers; ++l) {
@@ -402,11 +404,15 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     if ((c.debug & 1) && e->force_rows[(size_t)l] == T) {
       EB_TRY(impose(l));
       EB_TRY(eb_rmsnorm(e->x, L.g_attn, T, H, c.rms_eps, e->h, st));
+      h8_ready = false;
     }
     int32_t splits = 1;
-    mark(7);
-    EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
-    mark(-1);
+    if (!h8_ready) {
+      mark(7);
+      EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
+      mark(-1);
+    }
+    h8_ready = false;
     mark(2);
     EB_TRY(dense(e->h8, e->sh, L.wqkv, e->nqkv, H, e->qkv, &splits));
     mark(-1);
@@ -525,13 +531,20 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       mark(-1);
       EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, g_next, nt, H, c.rms_eps,
                                        e->h + (size_t)t0 * H, st));
-      // the next consumer (QKV projection of the next layer, or the LM head) needs every token's normalised row; the
-      // residual stream itself stays sliced, except when the debug taps want it whole
-      void* bufs[2] = {e->h, e->x};
-      const int64_t sizes[2] = {(int64_t)chunk * H * 2, (int64_t)chunk * H * 2};
-      mark(5);
-      EB_TRY(eb_comm_allgather(e->comm, (c.debug & 1) ? 2 : 1, bufs, sizes, st));
+      // the next consumer (QKV projection of the next layer, or the LM head) needs every token's normalised row as
+      // e4m3 with block scales: the slice's owner quantises its rows and the codes and scales are gathered (half the
+      // bytes of the bf16 rows, and no rank quantises the whole batch).  The residual stream itself stays sliced,
+      // except when the debug taps want it whole (then the bf16 rows travel too).
+      mark(7);
+      EB_TRY(eb_quant_act_block128(e->h + (size_t)t0 * H, H, nt, H, nullptr, 1, e->h8 + (size_t)t0 * H,
+                                   e->sh + (size_t)(t0 / 128) * e->kbH, st));
       mark(-1);
+      void* bufs[3] = {e->h8, e->sh, e->x};
+      const int64_t sizes[3] = {(int64_t)chunk * H, (int64_t)(chunk / 128) * e->kbH * 4, (int64_t)chunk * H * 2};
+      mark(5);
+      EB_TRY(eb_comm_allgather(e->comm, (c.debug & 1) ? 3 : 2, bufs, sizes, st));
+      mark(-1);
+      h8_ready = true;
       n += 3;
     }
     n += 9 + (plans[pi].n_parts > n_seqs ? 1 : 0);
@@ -545,8 +558,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   if ((c.debug & 1) && e->force_rows[(size_t)c.n_layers] == T) {
     EB_TRY(impose(c.n_layers));
     EB_TRY(eb_rmsnorm(e->x, e->g_final, T, H, c.rms_eps, e->h, st));
+    h8_ready = false;
   }
-  EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
+  if (!h8_ready) EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
   mark(4);
   if (!tp) {
     EB_TRY(dense(e->h8, e->sh, e->lm, c.vocab, H, e->logits, nullptr));
