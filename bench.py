@@ -13,8 +13,11 @@ decoder (default): the gpt-oss-20b-shaped random-init FP8 decoder -- 24 layers (
     back to host memory and are fed to the next step.
 spec120b: the gpt-oss-120b-shaped decoder (36 layers, 128 experts) with tensor-parallel heads and expert-parallel
     experts over 2, 4 or 8 GPUs (torchrun), verifying k=4 draft tokens per sequence on 512 ragged sequences.
-attn: one layer of paged sink-attention decode on 256 ragged sequences with lognormal(median 2048, sigma 1)
-    context lengths clipped to [16, 32768] (seed 1 + rank); the kernel-level benchmark of the attention path.
+attn: one layer of paged sink-attention on 256 ragged sequences with lognormal(median 2048, sigma 1) context lengths
+    clipped to [16, 32768] (seed 1 + rank); the kernel-level benchmark of the attention path.  --sigma, --window 128
+    and --qlen 5 (speculative verify) select the variants.
+gemm: the FP8 block-scaled GEMM sweep X[M,2880] x W[5120,2880]^T, M in {1, 8, 64, 256, 1024, 4096} (--m picks some):
+    GB/s for the small M, TFLOP/s for the large ones.
 
 Inputs are synthetic (seeded, generated on the device).  The per-step working set (weights 20 GB + KV 28 GB for
 the decoder, 1.5 GB of KV for attn) is far larger than the L2, so nothing is flushed between iterations.
