@@ -182,6 +182,7 @@ int32_t eb_attn_plan(const int32_t* ctx_lens, const int32_t* q_lens, int32_t n_s
   };
   std::vector<Range> rg((size_t)n_seqs);
   int64_t total = 0;
+  int32_t max_np = 0;
   for (int32_t i = 0; i < n_seqs; ++i) {
     const int32_t L = ctx_lens[i], ql = q_lens[i];
     EB_REQUIRE(ql >= 1 && L >= ql, EB_ERR_ARG, "eb_attn_plan: sequence %d has q_len %d, context %d", i, ql, L);
@@ -189,11 +190,15 @@ int32_t eb_attn_plan(const int32_t* ctx_lens, const int32_t* q_lens, int32_t n_s
     rg[(size_t)i].pb = t_lo / page_size;
     rg[(size_t)i].pe = (L + page_size - 1) / page_size;
     total += rg[(size_t)i].pe - rg[(size_t)i].pb;
+    max_np = std::max(max_np, rg[(size_t)i].pe - rg[(size_t)i].pb);
   }
   int32_t chunk = chunk_pages;
   if (chunk == 0) {
     const int64_t target = 4ll * sm_count;
     chunk = (int32_t)std::min<int64_t>(512, std::max<int64_t>(8, (total + target - 1) / target));
+    // Short ranges (windowed layers of a large batch): when the unsplit sequences already give every SM an item,
+    // halving each only adds a second wave of CTAs and the merge launch, so leave them whole.
+    if (n_seqs >= sm_count && max_np <= 2 * chunk) chunk = std::max(chunk, std::min(512, max_np));
   }
   EB_REQUIRE(chunk >= 1 && chunk <= 512, EB_ERR_ARG, "eb_attn_plan: chunk_pages %d outside 1..512", chunk);
   int32_t n = 0, parts = 0;

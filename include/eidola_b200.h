@@ -158,7 +158,8 @@ typedef struct eb_attn_item {
 
 /*
  * Split-K plan for one attention launch.  Long contexts are cut into runs of at most `chunk_pages` pages
- * (0 = choose so that about 4 items per SM exist); items are ordered longest first.
+ * (0 = choose so that about 4 items per SM exist, at least 8 pages each; a batch of at least sm_count sequences
+ * whose longest visible range is within two such runs is left unsplit); items are ordered longest first.
  *   items[cap_items], seq_part[n_seqs+1] (partial-slot range of each sequence)
  * window = 0 plans a full layer, otherwise only the pages a `window`-token sliding window can see.
  * parts_per_item = 8 / n_kv_local (warps that share a KV head write separate partials).

@@ -100,6 +100,9 @@ def attn_plan(ctx_lens, q_lens, page_size, window, sm_count, chunk_pages=0, part
     if chunk == 0:
         target = 4 * sm_count
         chunk = min(512, max(8, (total + target - 1) // target))
+        max_np = max((pe - pb for pb, pe in rng), default=0)
+        if len(rng) >= sm_count and max_np <= 2 * chunk:  # short ranges that already fill the SMs stay whole
+            chunk = max(chunk, min(512, max_np))
     items, seq_part, parts = [], [], 0
     for i, (pb, pe) in enumerate(rng):
         np_ = pe - pb

@@ -130,6 +130,20 @@ def test_attn_plan_matches_oracle(window, chunk, ppi):
         assert all(a[1] == b[0] for a, b in zip(runs, runs[1:]))
 
 
+def test_attn_plan_leaves_short_ranges_whole_when_they_fill_the_sms():
+    rng = np.random.default_rng(3)
+    ctx = rng.integers(128, 8192, size=256).astype(np.int32)
+    ql = np.ones(256, np.int32)
+    got = eb.attn_plan(ctx, ql, 16, 128, 148)
+    want = osched.attn_plan(ctx.tolist(), ql.tolist(), 16, 128, 148)
+    assert got["items"].tolist() == [list(x) for x in want["items"]]
+    assert got["n_parts"] == 256 and len(got["items"]) == 256  # one item per sequence: no merge launch
+    full = eb.attn_plan(ctx, ql, 16, 0, 148)  # full layers of the same batch are still split
+    assert len(full["items"]) > 256
+    few = eb.attn_plan(ctx[:40], ql[:40], 16, 128, 148)  # fewer sequences than SMs: split for parallelism
+    assert len(few["items"]) > 40
+
+
 def test_attn_plan_rejects_bad_input():
     with pytest.raises(eb.EbError):
         eb.attn_plan([5], [6], 16, 0, 148)
