@@ -285,14 +285,16 @@ class Spec120bWorkload:
         kv_full = (c.n_layers // 2) * int(ctx.sum()) * 2048 // G
         kv_win = (c.n_layers - c.n_layers // 2) * int(np.minimum(ctx, 128 + 5 + PAGE).sum()) * 2048 // G
         return {"weights": weights, "kv_full": kv_full, "kv_window": kv_win, "total": weights + kv_full + kv_win,
-                "reduce_scatter_bytes_per_layer": 2 * 5 * len(ctx) * 2880 * 4, "allgather_bytes_per_layer": 2 * 5 * len(ctx) * 2880 * 2}
+                "reduce_scatter_bytes_per_layer": 2 * 5 * len(ctx) * 2880 * 2,
+                "allgather_bytes_per_layer": 5 * len(ctx) * (2880 * 2 + 32) + 5 * len(ctx) * 2880 + (5 * len(ctx) // 128) * 23 * 4}
 
     def config(self) -> dict:
         return {"workload": self.name, "n_seqs": int(len(self.ctx0)), "n_layers": int(self.cfg.n_layers),
                 "mean_context": float(self.lens.mean()), "device_bytes_per_rank": self.mem,
                 "prefill": "KV pages filled with seeded N(0,1) values (stand-in for prefill)",
-                "parallelism": "tp%d (heads) x ep%d (experts); per layer 2 fp32 reduce-scatters of [2560, 2880] over token "
-                               "slices, residual + norm + routing on the slice, 2 all-gathers of the bf16 rows (+ routing); "
+                "parallelism": "tp%d (heads) x ep%d (experts); per layer 2 bf16 reduce-scatters of [2560, 2880] over token "
+                               "slices of whole 128-row blocks, residual + norm + routing on the slice, one all-gather of the "
+                               "bf16 rows + routing and one of the e4m3 codes + block scales quantised by the slice's owner; "
                                "vocabulary-parallel LM head with an all-gather of argmax candidates" % (self.world, self.world)}
 
 
