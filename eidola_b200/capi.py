@@ -182,6 +182,20 @@ def device_info(device: int = 0) -> dict:
     return {"sm_count": sm.value, "l2_bytes": l2.value, "hbm_bytes": hbm.value, "cc": (maj.value, mnr.value)}
 
 
+def mem_info() -> tuple[int, int]:
+    """(free, total) bytes of the current device."""
+    f, t = c_i64(0), c_i64(0)
+    call("eb_device_mem_info", C.byref(f), C.byref(t))
+    return int(f.value), int(t.value)
+
+
+def static_status_read() -> int:
+    """Status word built into the library for eb_attn_paged_sink_static calls that passed none; reading clears it."""
+    s = c_i32(0)
+    call("eb_attn_static_status_read", C.byref(s))
+    return int(s.value)
+
+
 def status_read() -> int:
     s = c_i32(0)
     call("eb_status_read", C.byref(s))

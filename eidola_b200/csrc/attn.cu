@@ -24,6 +24,7 @@
 #include <stdlib.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "common.h"
 
@@ -54,6 +55,7 @@ struct AttnParams {
   const int32_t* seq_part;
   float* part_acc;
   float* part_ml;
+  int32_t part_slots;  // partial slots part_acc / part_ml hold; a slot index outside [0, part_slots) is skipped and flagged
   int32_t* status;
 };
 
@@ -350,6 +352,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     const int n_parts_seq = p.seq_part[seq + 1] - p.seq_part[seq];
     const bool direct = (n_parts_seq == 1);
     const int part = item.part + sub;
+    // a plan that disagrees with the scratch the caller sized (stale items, an understated n_parts) is not followed
+    const bool part_ok = direct || (part >= 0 && part < p.part_slots);
+    if (!part_ok && lane == 0) atomicOr(p.status, EB_DEV_BAD_INDEX);
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -359,7 +364,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
         float l = l_run[mt][half];
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
-        if (qi >= ql) continue;
+        if (qi >= ql || !part_ok) continue;
         const int head = hk * G + row % G;
         const float m = m_run[mt][half];
         if (direct) {
@@ -733,6 +738,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
         tc_fence_after();
         const int n_parts_seq = p.seq_part[seq + 1] - p.seq_part[seq];
         const bool direct = (n_parts_seq == 1);
+        // partial slots [item.part, item.part + ppi) must lie inside the scratch; otherwise skip and flag
+        const bool part_ok = direct || (item.part >= 0 && item.part + tp.ppi <= p.part_slots);
+        if (!part_ok && lane == 0) atomicOr(p.status, EB_DEV_BAD_INDEX);
+        const bool store_ok = row_ok && part_ok;
         float inv = 0.f;
         if (direct) {
           const float sk = p.sinks[head] * 1.4426950408889634f;
@@ -744,7 +753,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
         for (int half = 0; half < 2; ++half) {
           uint32_t ov[32];
           tc_ld32(tO + lane_sel + half * 32, ov);
-          if (!row_ok) continue;
+          if (!store_ok) continue;
           if (direct) {
             uint32_t* orow = reinterpret_cast<uint32_t*>(p.out + (int64_t)(q0 + qi) * p.out_stride + (int64_t)head * kHeadDim + half * 32);
 #pragma unroll
@@ -760,7 +769,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
             if (half == 0) *reinterpret_cast<float2*>(p.part_ml + prow * 2) = make_float2(m_used, l_run);
           }
         }
-        if (!direct && row_ok) {
+        if (!direct && store_ok) {
           // the plan reserves tp.ppi partial slots per item; this kernel fills one, the others are declared empty
           for (int e = 1; e < tp.ppi; ++e) {
             const int64_t prow = ((int64_t)(item.part + e) * p.max_q_len + qi) * p.n_q + head;
@@ -799,6 +808,10 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
   const int seq = blockIdx.x;
   const int pb = p.seq_part[seq], pe = p.seq_part[seq + 1];
   if (pe - pb <= 1) return;  // written directly by attn_kernel
+  if (pb < 0 || pe > p.part_slots) {  // partial range outside the scratch: leave the output alone and flag it
+    if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(p.status, EB_DEV_BAD_INDEX);
+    return;
+  }
   const int head = blockIdx.y * 8 + (threadIdx.x >> 5);
   if (head >= p.n_q) return;
   const int lane = threadIdx.x & 31;
@@ -994,31 +1007,37 @@ int32_t eb_attn_workspace(int32_t n_parts, int32_t max_q_len, int32_t n_q, int32
   return EB_OK;
 }
 
-int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
-  EB_REQUIRE(a, EB_ERR_ARG, "eb_attn_paged_sink: null args");
+}  // extern "C"
+
+namespace {
+
+// Validation, tensor map, dispatch and merge shared by eb_attn_paged_sink and eb_attn_paged_sink_static: the two entry
+// points differ only in whose memory holds the split-K partials and the status word.  `who` names the entry point in
+// messages.  part_acc / part_ml hold a->n_parts partial slots.
+int32_t run_attn(const eb_attn_args* a, float* part_acc, float* part_ml, int32_t* status, const char* who, void* stream) {
   EB_REQUIRE(a->d_q && a->d_out && a->d_cache && a->d_block_tables && a->d_seq_slots && a->d_q_off && a->d_ctx_lens &&
                  a->d_sinks && a->d_items && a->d_seq_part,
-             EB_ERR_ARG, "eb_attn_paged_sink: null pointer");
-  EB_REQUIRE(a->head_dim == kHeadDim && a->page_size == kPage, EB_ERR_UNSUPPORTED,
-             "eb_attn_paged_sink: head_dim %d / page_size %d (built for 64 / 16)", a->head_dim, a->page_size);
+             EB_ERR_ARG, "%s: null pointer", who);
+  EB_REQUIRE(a->head_dim == kHeadDim && a->page_size == kPage, EB_ERR_UNSUPPORTED, "%s: head_dim %d / page_size %d (built for 64 / 16)",
+             who, a->head_dim, a->page_size);
   EB_REQUIRE(a->n_kv >= 1 && (a->n_q == a->n_kv * 8 || a->n_q == a->n_kv * 4), EB_ERR_UNSUPPORTED,
-             "eb_attn_paged_sink: %d query heads over %d KV heads (built for groups of 8 or 4)", a->n_q, a->n_kv);
+             "%s: %d query heads over %d KV heads (built for groups of 8 or 4)", who, a->n_q, a->n_kv);
   const int group = a->n_q / a->n_kv;
-  EB_REQUIRE(a->max_q_len >= 1 && a->max_q_len * group <= 48, EB_ERR_UNSUPPORTED,
-             "eb_attn_paged_sink: max_q_len %d exceeds %d", a->max_q_len, 48 / group);
+  EB_REQUIRE(a->max_q_len >= 1 && a->max_q_len * group <= 48, EB_ERR_UNSUPPORTED, "%s: max_q_len %d exceeds %d", who, a->max_q_len,
+             48 / group);
   EB_REQUIRE(a->n_seqs >= 0 && a->n_items >= 0 && a->n_parts >= 0 && a->num_pages >= 1 && a->window >= 0, EB_ERR_ARG,
-             "eb_attn_paged_sink: negative size");
+             "%s: negative size", who);
   EB_REQUIRE(a->q_stride % 2 == 0 && a->out_stride % 2 == 0 && (uintptr_t)a->d_q % 4 == 0 && (uintptr_t)a->d_out % 4 == 0,
-             EB_ERR_ARG, "eb_attn_paged_sink: q/out must be 4-byte aligned with even strides");
-  EB_REQUIRE((uintptr_t)a->d_cache % 16 == 0, EB_ERR_ARG, "eb_attn_paged_sink: cache must be 16-byte aligned");
-  EB_REQUIRE(a->n_parts == 0 || (a->d_part_acc && a->d_part_ml), EB_ERR_ARG, "eb_attn_paged_sink: null workspace");
+             EB_ERR_ARG, "%s: q/out must be 4-byte aligned with even strides", who);
+  EB_REQUIRE((uintptr_t)a->d_cache % 16 == 0, EB_ERR_ARG, "%s: cache must be 16-byte aligned", who);
+  EB_REQUIRE(a->n_parts == 0 || (part_acc && part_ml), EB_ERR_ARG, "%s: null workspace", who);
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "%s: no device status word", who);
   if (a->n_seqs == 0 || a->n_items == 0) return EB_OK;
   const int64_t rows = (int64_t)a->num_pages * 2 * a->n_kv * kPage;
-  EB_REQUIRE(rows < (1ll << 31), EB_ERR_UNSUPPORTED, "eb_attn_paged_sink: cache of %lld rows exceeds a tensor map",
-             (long long)rows);
+  EB_REQUIRE(rows < (1ll << 31), EB_ERR_UNSUPPORTED, "%s: cache of %lld rows exceeds a tensor map", who, (long long)rows);
 
   EncodeTiledFn enc = encode_tiled_fn();
-  EB_REQUIRE(enc, EB_ERR_NODEVICE, "eb_attn_paged_sink: driver entry point cuTensorMapEncodeTiled not found");
+  EB_REQUIRE(enc, EB_ERR_NODEVICE, "%s: driver entry point cuTensorMapEncodeTiled not found", who);
   CUtensorMap tm;
   const cuuint64_t gdim[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows};
   const cuuint64_t gstr[1] = {128};
@@ -1027,7 +1046,7 @@ int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
   CUresult cr = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a->d_cache), gdim, gstr, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  EB_REQUIRE(cr == CUDA_SUCCESS, EB_ERR_ARG, "eb_attn_paged_sink: cuTensorMapEncodeTiled failed (%d)", (int)cr);
+  EB_REQUIRE(cr == CUDA_SUCCESS, EB_ERR_ARG, "%s: cuTensorMapEncodeTiled failed (%d)", who, (int)cr);
 
   AttnParams p;
   p.q = (const uint16_t*)a->d_q;
@@ -1047,10 +1066,10 @@ int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
   p.scale_log2 = a->scale * 1.4426950408889634f;
   p.items = a->d_items;
   p.seq_part = a->d_seq_part;
-  p.part_acc = (float*)a->d_part_acc;
-  p.part_ml = (float*)a->d_part_ml;
-  p.status = eb::status_word();
-  EB_REQUIRE(p.status, EB_ERR_NODEVICE, "eb_attn_paged_sink: no device");
+  p.part_acc = part_acc;  // every partial row that the merge reads is written by this launch first: nothing to clear
+  p.part_ml = part_ml;
+  p.part_slots = a->n_parts;
+  p.status = status;
 
   cudaStream_t st = eb::as_stream(stream);
   const int mt = (a->max_q_len * group + 15) / 16;
@@ -1074,24 +1093,20 @@ int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
   }
   if (rc != EB_OK) return rc;
   if (a->n_parts > a->n_seqs) {  // at least one sequence has more than one partial
-    EB_CUDA(eb::launch(attn_merge_kernel, dim3(dim3((unsigned)a->n_seqs, (unsigned)((a->n_q + 7) / 8))), dim3(256), 0, st, p));
+    EB_CUDA(eb::launch(attn_merge_kernel, dim3((unsigned)a->n_seqs, (unsigned)((a->n_q + 7) / 8)), dim3(256), 0, st, p));
     EB_LAUNCH_CHECK();
   }
   return EB_OK;
 }
 
-}  // extern "C"
-
 // ---------------------------------------------------------------------------------------------
-// Paged sink attention for callers that must not allocate.
+// Scratch of the entry point for callers that must not allocate.
 //
 // Some hosts of this library cannot call cudaMalloc where they need attention: a host that has handed all device
 // memory to its own pool, a plugin that runs inside another runtime's allocator arena, a latency-critical thread
 // that must not take the allocator's lock.  For them the split-K scratch (partial accumulators and their
 // (max, sum) pairs) lives in the two file-scope device arrays below, which every GPU that loads the library holds
 // until the process exits (16.5 MiB together).  The caller still owns every input and output.
-
-namespace {
 
 constexpr int64_t kStaticRows = 65536;  // (partial slot, query position, query head) rows the scratch can hold
 
@@ -1100,7 +1115,8 @@ static __device__ __align__(256) float g_static_part_ml[kStaticRows * 2];       
 static __device__ __align__(256) int32_t g_static_status[64];                       // status word when the caller passes none
 
 struct StaticScratch {
-  bool ready = false;
+  std::once_flag once;
+  cudaError_t err = cudaErrorNotReady;
   float* acc = nullptr;
   float* ml = nullptr;
   int32_t* status = nullptr;
@@ -1108,107 +1124,66 @@ struct StaticScratch {
 StaticScratch g_static_scratch[64];  // per device: in host code the array names above are only host-side stand-ins,
                                      // the device addresses come from cudaGetSymbolAddress with that device current
 
+// Resolves the device addresses of the scratch arrays once per device (thread-safe), with that device current.
+int32_t static_scratch(StaticScratch** out) {
+  int dev = -1;
+  EB_CUDA(cudaGetDevice(&dev));
+  EB_REQUIRE(dev >= 0 && dev < 64, EB_ERR_UNSUPPORTED, "eb_attn_paged_sink_static: device ordinal %d", dev);
+  StaticScratch& sc = g_static_scratch[dev];
+  std::call_once(sc.once, [&sc] {
+    cudaError_t e = cudaGetSymbolAddress((void**)&sc.acc, g_static_part_acc);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress((void**)&sc.ml, g_static_part_ml);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress((void**)&sc.status, g_static_status);
+    sc.err = e;
+  });
+  if (sc.err != cudaSuccess)
+    return eb::fail((int32_t)sc.err, "eb_attn_paged_sink_static: cudaGetSymbolAddress: %s", cudaGetErrorString(sc.err));
+  *out = &sc;
+  return EB_OK;
+}
+
 }  // namespace
+
+namespace eb {
+// The library's built-in status word of the current device when eb_attn_paged_sink_static has resolved it, else nullptr
+// (eb_status_read folds it into what it reports).
+int32_t* static_status_word_if_ready() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  StaticScratch& sc = g_static_scratch[dev];
+  return sc.err == cudaSuccess ? sc.status : nullptr;
+}
+}  // namespace eb
 
 extern "C" {
 
+int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream) {
+  EB_REQUIRE(a, EB_ERR_ARG, "eb_attn_paged_sink: null args");
+  return run_attn(a, (float*)a->d_part_acc, (float*)a->d_part_ml, eb::status_word(), "eb_attn_paged_sink", stream);
+}
+
 int32_t eb_attn_paged_sink_static(const eb_attn_args* a, int32_t* d_status, void* stream) {
   EB_REQUIRE(a, EB_ERR_ARG, "eb_attn_paged_sink_static: null args");
-  EB_REQUIRE(a->d_q && a->d_out && a->d_cache && a->d_block_tables && a->d_seq_slots && a->d_q_off && a->d_ctx_lens &&
-                 a->d_sinks && a->d_items && a->d_seq_part,
-             EB_ERR_ARG, "eb_attn_paged_sink_static: null pointer");
-  EB_REQUIRE(a->head_dim == kHeadDim && a->page_size == kPage, EB_ERR_UNSUPPORTED,
-             "eb_attn_paged_sink_static: head_dim %d / page_size %d (built for 64 / 16)", a->head_dim, a->page_size);
-  EB_REQUIRE(a->n_kv >= 1 && (a->n_q == a->n_kv * 8 || a->n_q == a->n_kv * 4), EB_ERR_UNSUPPORTED,
-             "eb_attn_paged_sink_static: %d query heads over %d KV heads (built for groups of 8 or 4)", a->n_q, a->n_kv);
-  const int group = a->n_q / a->n_kv;
-  EB_REQUIRE(a->max_q_len >= 1 && a->max_q_len * group <= 48, EB_ERR_UNSUPPORTED,
-             "eb_attn_paged_sink_static: max_q_len %d exceeds %d", a->max_q_len, 48 / group);
-  EB_REQUIRE(a->n_seqs >= 0 && a->n_items >= 0 && a->n_parts >= 0 && a->num_pages >= 1 && a->window >= 0, EB_ERR_ARG,
-             "eb_attn_paged_sink_static: negative size");
-  EB_REQUIRE(a->q_stride % 2 == 0 && a->out_stride % 2 == 0 && (uintptr_t)a->d_q % 4 == 0 && (uintptr_t)a->d_out % 4 == 0,
-             EB_ERR_ARG, "eb_attn_paged_sink_static: q/out must be 4-byte aligned with even strides");
-  EB_REQUIRE((uintptr_t)a->d_cache % 16 == 0, EB_ERR_ARG, "eb_attn_paged_sink_static: cache must be 16-byte aligned");
+  EB_REQUIRE(a->n_parts >= 0 && a->max_q_len >= 1 && a->n_q >= 1, EB_ERR_ARG, "eb_attn_paged_sink_static: negative size");
   const int64_t need_rows = (int64_t)a->n_parts * a->max_q_len * a->n_q;
   EB_REQUIRE(need_rows <= kStaticRows, EB_ERR_NOMEM,
              "eb_attn_paged_sink_static: %d partial slots x %d query positions x %d heads = %lld rows exceed the built-in "
              "scratch of %lld rows; plan with a larger chunk_pages or use eb_attn_paged_sink with a caller workspace",
              a->n_parts, a->max_q_len, a->n_q, (long long)need_rows, (long long)kStaticRows);
-  if (a->n_seqs == 0 || a->n_items == 0) return EB_OK;
-  const int64_t rows = (int64_t)a->num_pages * 2 * a->n_kv * kPage;
-  EB_REQUIRE(rows < (1ll << 31), EB_ERR_UNSUPPORTED, "eb_attn_paged_sink_static: cache of %lld rows exceeds a tensor map",
-             (long long)rows);
-
-  // Set-up, once per device, with that device current: resolve the device addresses of the scratch arrays.
-  int dev = -1;
-  EB_CUDA(cudaGetDevice(&dev));
-  EB_REQUIRE(dev >= 0 && dev < 64, EB_ERR_UNSUPPORTED, "eb_attn_paged_sink_static: device ordinal %d", dev);
-  StaticScratch& sc = g_static_scratch[dev];
-  if (!sc.ready) {
-    EB_CUDA(cudaGetSymbolAddress((void**)&sc.acc, g_static_part_acc));
-    EB_CUDA(cudaGetSymbolAddress((void**)&sc.ml, g_static_part_ml));
-    EB_CUDA(cudaGetSymbolAddress((void**)&sc.status, g_static_status));
-    sc.ready = true;
-  }
-
-  EncodeTiledFn enc = encode_tiled_fn();
-  EB_REQUIRE(enc, EB_ERR_NODEVICE, "eb_attn_paged_sink_static: driver entry point cuTensorMapEncodeTiled not found");
-  CUtensorMap tm;
-  const cuuint64_t gdim[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)rows};
-  const cuuint64_t gstr[1] = {128};
-  const cuuint32_t box[2] = {(cuuint32_t)kHeadDim, (cuuint32_t)(2 * a->n_kv * kPage)};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult cr = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a->d_cache), gdim, gstr, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  EB_REQUIRE(cr == CUDA_SUCCESS, EB_ERR_ARG, "eb_attn_paged_sink_static: cuTensorMapEncodeTiled failed (%d)", (int)cr);
-
-  AttnParams p;
-  p.q = (const uint16_t*)a->d_q;
-  p.q_stride = a->q_stride;
-  p.out = (uint16_t*)a->d_out;
-  p.out_stride = a->out_stride;
-  p.block_tables = a->d_block_tables;
-  p.bt_stride = a->bt_stride;
-  p.seq_slots = a->d_seq_slots;
-  p.q_off = a->d_q_off;
-  p.ctx_lens = a->d_ctx_lens;
-  p.sinks = a->d_sinks;
-  p.window = a->window;
-  p.n_q = a->n_q;
-  p.max_q_len = a->max_q_len;
-  p.num_pages = a->num_pages;
-  p.scale_log2 = a->scale * 1.4426950408889634f;
-  p.items = a->d_items;
-  p.seq_part = a->d_seq_part;
-  p.part_acc = sc.acc;  // every partial row that the merge reads is written by this call first: nothing to clear
-  p.part_ml = sc.ml;
-  p.status = d_status ? d_status : sc.status;
-
-  cudaStream_t st = eb::as_stream(stream);
-  const int mt = (a->max_q_len * group + 15) / 16;
-  int32_t rc;
-  if (mt >= 2 && attn_tc_enabled()) {
-    rc = dispatch_attn_tc(enc, a->d_cache, rows, p, a->n_items, a->n_kv, group, st);
-  } else if (group == 8) {
-    if (mt == 1)
-      rc = dispatch_hkv<1, 8>(a->n_kv, tm, p, a->n_items, st);
-    else if (mt == 2)
-      rc = dispatch_hkv<2, 8>(a->n_kv, tm, p, a->n_items, st);
-    else
-      rc = dispatch_hkv<3, 8>(a->n_kv, tm, p, a->n_items, st);
-  } else {
-    if (mt == 1)
-      rc = dispatch_hkv<1, 4>(a->n_kv, tm, p, a->n_items, st);
-    else if (mt == 2)
-      rc = dispatch_hkv<2, 4>(a->n_kv, tm, p, a->n_items, st);
-    else
-      rc = dispatch_hkv<3, 4>(a->n_kv, tm, p, a->n_items, st);
-  }
+  // Set-up, once per device, with that device current: the device addresses of the scratch arrays.
+  StaticScratch* sc = nullptr;
+  int32_t rc = static_scratch(&sc);
   if (rc != EB_OK) return rc;
-  if (a->n_parts > a->n_seqs) {
-    EB_CUDA(eb::launch(attn_merge_kernel, dim3((unsigned)a->n_seqs, (unsigned)((a->n_q + 7) / 8)), dim3(256), 0, st, p));
-  }
+  return run_attn(a, sc->acc, sc->ml, d_status ? d_status : sc->status, "eb_attn_paged_sink_static", stream);
+}
+
+int32_t eb_attn_static_status_read(int32_t* status) {
+  EB_REQUIRE(status, EB_ERR_ARG, "eb_attn_static_status_read: null");
+  StaticScratch* sc = nullptr;
+  int32_t rc = static_scratch(&sc);
+  if (rc != EB_OK) return rc;
+  EB_CUDA(cudaMemcpy(status, sc->status, sizeof(int32_t), cudaMemcpyDeviceToHost));
+  EB_CUDA(cudaMemset(sc->status, 0, sizeof(int32_t)));
   return EB_OK;
 }
 

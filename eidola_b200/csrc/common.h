@@ -15,6 +15,9 @@ int32_t fail(int32_t code, const char* fmt, ...) __attribute__((format(printf, 2
 
 // Device pointer to this device's status word (allocated on first use; nullptr if CUDA is unavailable).
 int32_t* status_word();
+// Status word built into the library for eb_attn_paged_sink_static on the current device; nullptr until that entry
+// point has resolved it.
+int32_t* static_status_word_if_ready();
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 

@@ -111,6 +111,7 @@ struct eb_engine {
   bool in_flight = false;
   int32_t launches = 0;
   float last_ms = 0.f;
+  int64_t h2d_bytes = 0, d2h_bytes = 0;  // bytes the last step copied host -> device (staging block) and back (results)
 };
 
 namespace {
@@ -258,7 +259,9 @@ int32_t init_work(eb_engine* e) {
   EB_TRY(dev_alloc(e, &p8, ws2, w));
   e->group_ws = p8;
   e->group_ws_bytes = ws2;
-  e->cap_items = 4 * e->sm_count + c.max_seqs + 16;
+  // work items of one attention launch: ~4 per SM from the planner, one per sequence at least, and enough for a pool
+  // whose every page is in use at the largest run the kernel accepts (512 pages per item)
+  e->cap_items = 4 * e->sm_count + c.max_seqs + 16 + c.num_pages / 512;
   const int ppi = 8 / e->hkv_l;
   size_t acc_b = 0, ml_b = 0;
   EB_TRY(eb_attn_workspace(e->cap_items * ppi, c.max_q_len, e->hq_l, c.head_dim, &acc_b, &ml_b));
@@ -584,6 +587,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   return EB_OK;
 }
 
+int32_t step_launch_body(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
+                         const int32_t* h_tokens, int T, int max_q);
+
 }  // namespace
 
 extern "C" {
@@ -786,17 +792,42 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
     EB_REQUIRE(h_tokens[t] >= 0 && h_tokens[t] < c.vocab, EB_ERR_ARG, "eb_engine_step: token id %d of row %d outside the vocabulary",
                h_tokens[t], t);
 
-  // grow every sequence; on failure undo the ones already grown so a refused step leaves no trace
-  std::vector<int32_t> old_len((size_t)n_seqs);
+  // grow every sequence; on ANY failure before the step is in flight undo the growth (lengths, pages and the record
+  // of which block-table entries the device holds), so a refused step leaves no trace
+  std::vector<int32_t> old_len((size_t)n_seqs), old_uploaded((size_t)n_seqs);
+  int grown = 0;
+  auto rollback = [&](int32_t rc) -> int32_t {
+    for (int j = 0; j < grown; ++j) {
+      eb_sched_truncate(e->sched, h_slots[j], old_len[(size_t)j]);
+      e->uploaded_pages[(size_t)h_slots[j]] = old_uploaded[(size_t)j];
+    }
+    return rc;
+  };
   for (int i = 0; i < n_seqs; ++i) {
     int32_t rc = eb_sched_seq_len(e->sched, h_slots[i], &old_len[(size_t)i]);
-    if (rc == EB_OK) rc = eb_sched_extend(e->sched, h_slots[i], old_len[(size_t)i] + h_q_lens[i]);
-    if (rc != EB_OK) {
-      for (int j = 0; j < i; ++j) eb_engine_seq_truncate(e, h_slots[j], old_len[(size_t)j]);
-      return rc;
+    if (rc == EB_OK) {
+      old_uploaded[(size_t)i] = e->uploaded_pages[(size_t)h_slots[i]];
+      rc = eb_sched_extend(e->sched, h_slots[i], old_len[(size_t)i] + h_q_lens[i]);
     }
+    if (rc != EB_OK) return rollback(rc);
+    grown = i + 1;
   }
+  const int32_t rc_body = step_launch_body(e, h_slots, h_q_lens, n_seqs, h_tokens, T, max_q);
+  if (rc_body != EB_OK) return rollback(rc_body);
+  e->cur_T = T;
+  e->in_flight = true;
+  return EB_OK;
+}
 
+}  // extern "C"
+
+namespace {
+
+// Everything of a step after the sequences have grown: staging block, copies, kernels.  Any non-zero return leaves
+// nothing in flight; the caller undoes the growth.
+int32_t step_launch_body(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
+                         const int32_t* h_tokens, int T, int max_q) {
+  const eb_config& c = e->c;
   // ---- one staging block
   int32_t* hs = e->h_stage;
   size_t off = 0;
@@ -873,10 +904,14 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
   EB_CUDA(cudaMemcpyAsync(e->h_result, e->d_next, (size_t)T * sizeof(int32_t), cudaMemcpyDeviceToHost, e->stream));
   EB_CUDA(cudaMemcpyAsync(e->h_result + T, e->d_margin, (size_t)T * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
   EB_CUDA(cudaEventRecord(e->ev1, e->stream));
-  e->cur_T = T;
-  e->in_flight = true;
+  e->h2d_bytes = (int64_t)(off * sizeof(int32_t));
+  e->d2h_bytes = (int64_t)T * (int64_t)(sizeof(int32_t) + sizeof(float));
   return EB_OK;
 }
+
+}  // namespace
+
+extern "C" {
 
 int32_t eb_engine_step_wait(eb_engine* e, int32_t* h_next, float* h_margin) {
   EB_REQUIRE(e && h_next, EB_ERR_ARG, "eb_engine_step_wait: null pointer");
@@ -905,6 +940,13 @@ int32_t eb_engine_last_step_stats(const eb_engine* e, float* device_ms, int32_t*
   EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_last_step_stats: null engine");
   if (device_ms) *device_ms = e->last_ms;
   if (kernel_launches) *kernel_launches = e->launches;
+  return EB_OK;
+}
+
+int32_t eb_engine_last_step_copies(const eb_engine* e, int64_t* h2d_bytes, int64_t* d2h_bytes) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_last_step_copies: null engine");
+  if (h2d_bytes) *h2d_bytes = e->h2d_bytes;
+  if (d2h_bytes) *d2h_bytes = e->d2h_bytes;
   return EB_OK;
 }
 

@@ -113,8 +113,10 @@ __global__ void embed_kernel(const uint4* table, int V, int H8, const int32_t* t
 }
 
 // Greedy argmax over bf16 logits, one CTA per token; ties go to the lower id.  Also the top-1 minus top-2 margin.
+// NaN logits are never chosen.  A row without any value above -inf (all NaN or -inf) yields token 0, inside the
+// vocabulary, and raises EB_DEV_BAD_INDEX.
 __global__ void __launch_bounds__(1024) argmax_kernel(const uint16_t* logits, int64_t V, int64_t ld, int32_t* tok, float* margin,
-                                                      float* cand, int32_t v_off) {
+                                                      float* cand, int32_t v_off, int32_t* status) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
   const uint16_t* r = logits + (int64_t)blockIdx.x * ld;
@@ -165,21 +167,25 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const uint16_t* logits, in
     __syncthreads();
   }
   if (threadIdx.x == 0) {
-    if (cand) {  // a vocabulary slice: leave the candidate for the merge
+    const bool none = si[0] >= V;  // no value above -inf in this row (or slice)
+    const int32_t best = none ? 0 : (int32_t)si[0];
+    if (cand) {  // a vocabulary slice: leave the candidate for the merge, which decides whether the whole row is empty
       float* c = cand + (int64_t)blockIdx.x * 4;
       c[0] = s1[0];
       c[1] = s2[0];
-      c[2] = __int_as_float((int32_t)si[0] + v_off);
+      c[2] = __int_as_float(best + v_off);
       c[3] = 0.f;
     } else {
-      tok[blockIdx.x] = (int32_t)si[0];
+      if (none) atomicOr(status, EB_DEV_BAD_INDEX);
+      tok[blockIdx.x] = best;
       if (margin) margin[blockIdx.x] = s1[0] - s2[0];
     }
   }
 }
 
 // One thread per row: fold the slices' candidates in ascending id order.
-__global__ void argmax_merge_kernel(const float* cand, int n_parts, int64_t part_stride, int T, int32_t* tok, float* margin) {
+__global__ void argmax_merge_kernel(const float* cand, int n_parts, int64_t part_stride, int T, int32_t* tok, float* margin,
+                                    int32_t* status) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -197,6 +203,10 @@ __global__ void argmax_merge_kernel(const float* cand, int n_parts, int64_t part
     } else {
       a2 = fmaxf(a2, c1);
     }
+  }
+  if (!(a1 > -INFINITY)) {  // every slice was empty (all NaN or -inf): token 0, flagged, as eb_argmax does
+    atomicOr(status, EB_DEV_BAD_INDEX);
+    ai = 0;
   }
   tok[t] = ai;
   if (margin) margin[t] = a1 - a2;
@@ -272,8 +282,10 @@ int32_t eb_argmax(const void* d_logits, int32_t T, int64_t V, int64_t ld, int32_
   EB_REQUIRE(d_logits && d_tok, EB_ERR_ARG, "eb_argmax: null pointer");
   EB_REQUIRE(T >= 0 && V >= 1 && ld >= V, EB_ERR_ARG, "eb_argmax: bad size");
   if (T == 0) return EB_OK;
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_argmax: no device");
   EB_CUDA(eb::launch(argmax_kernel, dim3(T), dim3(1024), 0, eb::as_stream(stream), (const uint16_t*)d_logits, V, ld, d_tok, d_margin,
-                     (float*)nullptr, 0));
+                     (float*)nullptr, 0, status));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -283,7 +295,7 @@ int32_t eb_argmax_partial(const void* d_logits, int32_t T, int64_t V, int64_t ld
   EB_REQUIRE(T >= 0 && V >= 1 && ld >= V && v_off >= 0, EB_ERR_ARG, "eb_argmax_partial: bad size");
   if (T == 0) return EB_OK;
   EB_CUDA(eb::launch(argmax_kernel, dim3(T), dim3(1024), 0, eb::as_stream(stream), (const uint16_t*)d_logits, V, ld, (int32_t*)nullptr,
-                     (float*)nullptr, d_cand, v_off));
+                     (float*)nullptr, d_cand, v_off, (int32_t*)nullptr));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -293,8 +305,10 @@ int32_t eb_argmax_merge(const float* d_cand, int32_t n_parts, int64_t part_strid
   EB_REQUIRE(d_cand && d_tok, EB_ERR_ARG, "eb_argmax_merge: null pointer");
   EB_REQUIRE(n_parts >= 1 && T >= 0 && part_stride >= T, EB_ERR_ARG, "eb_argmax_merge: bad size");
   if (T == 0) return EB_OK;
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_argmax_merge: no device");
   EB_CUDA(eb::launch(argmax_merge_kernel, dim3((unsigned)eb::cdiv(T, 128)), dim3(128), 0, eb::as_stream(stream), d_cand, n_parts,
-                     part_stride, T, d_tok, d_margin));
+                     part_stride, T, d_tok, d_margin, status));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

@@ -93,6 +93,14 @@ int32_t eb_device_info(int32_t device, int32_t* sm_count, int64_t* l2_bytes, int
   return EB_OK;
 }
 
+int32_t eb_device_mem_info(int64_t* free_bytes, int64_t* total_bytes) {
+  size_t f = 0, t = 0;
+  EB_CUDA(cudaMemGetInfo(&f, &t));
+  if (free_bytes) *free_bytes = (int64_t)f;
+  if (total_bytes) *total_bytes = (int64_t)t;
+  return EB_OK;
+}
+
 int32_t eb_malloc(void** d_ptr, size_t bytes) {
   EB_REQUIRE(d_ptr, EB_ERR_ARG, "eb_malloc: null");
   EB_CUDA(cudaMalloc(d_ptr, bytes ? bytes : 1));
@@ -174,6 +182,13 @@ int32_t eb_status_read(int32_t* status) {
   EB_REQUIRE(p, EB_ERR_NODEVICE, "eb_status_read: no device status word");
   EB_CUDA(cudaMemcpy(status, p, sizeof(int32_t), cudaMemcpyDeviceToHost));
   EB_CUDA(cudaMemset(p, 0, sizeof(int32_t)));
+  // bits raised by eb_attn_paged_sink_static calls that passed no status word of their own
+  if (int32_t* q = eb::static_status_word_if_ready()) {
+    int32_t extra = 0;
+    EB_CUDA(cudaMemcpy(&extra, q, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    EB_CUDA(cudaMemset(q, 0, sizeof(int32_t)));
+    *status |= extra;
+  }
   return EB_OK;
 }
 

@@ -67,6 +67,8 @@ int32_t eb_device_count(int32_t* n);
 int32_t eb_device_set(int32_t device);
 int32_t eb_device_info(int32_t device, int32_t* sm_count, int64_t* l2_bytes, int64_t* hbm_bytes, int32_t* cc_major,
                        int32_t* cc_minor);
+/* Free and total device memory of the current device in bytes (cudaMemGetInfo). */
+int32_t eb_device_mem_info(int64_t* free_bytes, int64_t* total_bytes);
 int32_t eb_malloc(void** d_ptr, size_t bytes);
 int32_t eb_free(void* d_ptr);
 int32_t eb_host_alloc(void** h_ptr, size_t bytes); /* pinned */
@@ -212,16 +214,23 @@ int32_t eb_attn_paged_sink(const eb_attn_args* a, void* stream);
  * workspace; here the split-K scratch is two device arrays built into the library (16 MiB + 512 KiB, held by every
  * GPU that loads the library until the process exits).  d_part_acc / d_part_ml of the arguments are ignored.
  *   limit    : n_parts * max_q_len * n_q <= 65536 rows, else EB_ERR_NOMEM and nothing is launched (plan with a
- *              larger chunk_pages, or use eb_attn_paged_sink);
- *   d_status : caller-owned device int32 that receives EB_DEV_* bits (OR-ed in; NULL = a word inside the library);
+ *              larger chunk_pages, or use eb_attn_paged_sink).  The kernels also check every partial slot the plan
+ *              names against n_parts: a slot outside [0, n_parts) is skipped and EB_DEV_BAD_INDEX is raised, so a
+ *              stale plan cannot write past the built-in arrays;
+ *   d_status : caller-owned device int32 that receives EB_DEV_* bits (OR-ed in).  NULL = a word inside the library,
+ *              read and cleared by eb_attn_static_status_read (which allocates nothing) and also folded into what
+ *              eb_status_read reports (that one allocates its own word on first use);
  *   calls no cudaMalloc, cudaFree or other allocating routine.  The first call on a device resolves the addresses
- *   of the built-in arrays (cudaGetSymbolAddress, once per device, with that device current): make that first call
- *   before any stream capture begins;
+ *   of the built-in arrays (cudaGetSymbolAddress, once per device, with that device current; concurrent first
+ *   calls from several host threads are safe): make that first call before any stream capture begins;
  *   every call on a device shares the same scratch, which keeps the previous call's contents.  Nothing in it has
  *   to start at zero (each partial row is written before it is read), but two calls that overlap on the GPU --
  *   different streams, or the same scratch from two threads -- race on it: serialise them.
  */
 int32_t eb_attn_paged_sink_static(const eb_attn_args* a, int32_t* d_status, void* stream);
+/* EB_DEV_* bits raised by eb_attn_paged_sink_static calls on the current device that passed d_status = NULL; reading
+ * clears them.  Allocates nothing (no counterpart in the reference project either). */
+int32_t eb_attn_static_status_read(int32_t* status);
 /* Workspace sizes for the two partial buffers of eb_attn_args. */
 int32_t eb_attn_workspace(int32_t n_parts, int32_t max_q_len, int32_t n_q, int32_t head_dim, size_t* acc_bytes,
                           size_t* ml_bytes);
@@ -397,10 +406,15 @@ int32_t eb_comm_abort(eb_comm* c);
 
 int32_t eb_engine_create(const eb_config* cfg, eb_engine** out);
 /* Tensor-parallel heads + expert-parallel experts over tp_size ranks (one process per GPU): rank r holds query heads
- * [r*n_q/tp, ...), KV heads [r*n_kv/tp, ...) with their slice of every KV page, and experts [r*E/tp, ...); the
- * router, embeddings and LM head are replicated, and every rank is given the same steps and returns the same
- * tokens.  Two fp32 all-reduces of [tokens, hidden] per layer (after the O projection and after the experts)
- * run on `comm`.  The model is the same tensor for every tp_size (weights are slices of the single-GPU tensors). */
+ * [r*n_q/tp, ...), KV heads [r*n_kv/tp, ...) with their slice of every KV page (page ids are the same on all ranks),
+ * the matching rows of W_qkv and columns of W_o, experts [r*E/tp, ...) and a band of whole 128-row blocks of the
+ * LM head.  Every rank is given the same steps and returns the same tokens.  Per layer the partial [tokens, hidden]
+ * products of the O projection and of the rank's experts are summed over token slices (reduce-scatter: tp_size equal
+ * chunks of whole 128-row scale blocks); the owner of a slice adds the residual, normalises, routes and quantises
+ * its rows, and all-gathers return the normalised rows, the routing and the e4m3 codes with their block scales.
+ * The LM head is vocabulary-parallel: each rank leaves one argmax candidate per token, the candidates are gathered
+ * and merged.  All cross-rank traffic runs on `comm`; no kernel of one rank waits on another rank's kernel outside
+ * it.  The model is the same tensor for every tp_size (weights are slices of the single-GPU tensors). */
 int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_size, eb_comm* comm, eb_engine** out);
 int32_t eb_engine_destroy(eb_engine* e);
 /* Device bytes held by weights, KV pages and workspaces. */
@@ -429,6 +443,9 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
 int32_t eb_engine_step_wait(eb_engine* e, int32_t* h_next, float* h_margin);
 /* Milliseconds the last step spent on the device (CUDA events around its kernels) and kernels it launched. */
 int32_t eb_engine_last_step_stats(const eb_engine* e, float* device_ms, int32_t* kernel_launches);
+/* Bytes the last step copied host -> device (the staging block: tokens, packing arrays, block-table patches, the two
+ * attention plans) and device -> host (greedy tokens and margins). */
+int32_t eb_engine_last_step_copies(const eb_engine* e, int64_t* h2d_bytes, int64_t* d2h_bytes);
 /* debug bit 1: device milliseconds of the last step by category (8 floats): [0] attention on full layers, [1] attention
  * on windowed layers, [2] QKV and O projections, [3] expert GEMMs, [4] LM head, [5] collectives (tensor-parallel
  * engines), [6] router, [7] activation quantisers.  What is left of the step is norms, rotary/append, permutation,

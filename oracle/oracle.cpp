@@ -370,14 +370,15 @@ void orc_moe_forward(const uint16_t* h, int32_t T, int32_t H, int32_t I, int32_t
     }
 }
 
-/* greedy argmax over bf16 logits, ties to the lower id; margin = top1 - top2 (fp32 of the bf16 values). */
+/* greedy argmax over bf16 logits, ties to the lower id; margin = top1 - top2 (fp32 of the bf16 values).
+ * NaN logits are never chosen; a row without any value above -inf yields token 0. */
 void orc_argmax(const uint16_t* logits, int32_t T, int64_t V, int32_t* tok, float* margin) {
 #pragma omp parallel for schedule(static)
   for (int32_t t = 0; t < T; ++t) {
     const uint16_t* r = logits + (int64_t)t * V;
     int64_t b = 0;
-    float bv = bf(r[0]), sv = -INFINITY;
-    for (int64_t v = 1; v < V; ++v) {
+    float bv = -INFINITY, sv = -INFINITY;
+    for (int64_t v = 0; v < V; ++v) {
       const float x = bf(r[v]);
       if (x > bv) {
         sv = bv;

@@ -143,3 +143,34 @@ def test_argmax_partial_and_merge_equal_whole_row_argmax(gpu):
     assert np.array_equal(d_tok2.to_array(np.int32, T), want_tok)
     assert np.array_equal(d_mg2.to_array(np.float32, T), want_mg)
     assert want_tok[3] == 100 and want_mg[3] == 0 and want_tok[5] == 0 and want_mg[5] == 0
+
+
+def test_argmax_of_rows_without_a_finite_maximum_stays_in_the_vocabulary(gpu):
+    """A row of NaN or -inf logits yields token 0 (never an id outside the vocabulary) and raises the status word, in
+    the whole-row kernel and in the vocabulary-parallel pair alike; NaNs among finite values are ignored, as in the
+    oracle."""
+    import eidola_b200 as eb
+    from eidola_b200.capi import DeviceBuffer, c_i32, c_i64, c_vp
+    T, V = 6, 1000
+    logits = orc.synth_normal_bf16(12, 1, 0, T * V, 2.0).reshape(T, V)
+    logits[1, :] = 0x7FC0            # NaN everywhere
+    logits[2, :] = 0xFF80            # -inf everywhere
+    logits[3, 0] = 0x7FC0            # a NaN first, finite values after it
+    logits[4, ::2] = 0x7FC0          # NaNs interleaved
+    want_tok, _ = orc.argmax(logits)
+    assert want_tok[1] == 0 and want_tok[2] == 0 and want_tok[3] != 0
+    d_l = _dev(logits)
+    d_tok, d_mg = DeviceBuffer(T * 4), DeviceBuffer(T * 4)
+    _call("eb_argmax", c_vp(d_l.ptr), c_i32(T), c_i64(V), c_i64(V), c_vp(d_tok.ptr), c_vp(d_mg.ptr), None)
+    assert np.array_equal(d_tok.to_array(np.int32, T), want_tok)
+    assert eb.status_read() & 0x2000
+    cuts = [0, 384, V]
+    d_cand = DeviceBuffer(2 * T * 16)
+    for r in range(2):
+        _call("eb_argmax_partial", c_vp(d_l.ptr + 2 * cuts[r]), c_i32(T), c_i64(cuts[r + 1] - cuts[r]), c_i64(V), c_i32(cuts[r]),
+              c_vp(d_cand.ptr + r * T * 16), None)
+    d_tok2 = DeviceBuffer(T * 4)
+    _call("eb_argmax_merge", c_vp(d_cand.ptr), c_i32(2), c_i64(T), c_i32(T), c_vp(d_tok2.ptr), None, None)
+    assert np.array_equal(d_tok2.to_array(np.int32, T), want_tok)
+    assert eb.status_read() & 0x2000
+    assert eb.status_read() == 0

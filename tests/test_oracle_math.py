@@ -144,3 +144,7 @@ def test_rmsnorm_rope_argmax():
     logits = orc.bf16_encode(np.array([[0.5, 2.0, 2.0, -1.0], [3.0, 1.0, 0.0, 2.5]], np.float32))
     tok, margin = orc.argmax(logits)
     assert tok.tolist() == [1, 0] and margin.tolist() == [0.0, 0.5]
+    # NaN is never chosen; a row with nothing above -inf yields token 0
+    odd = np.array([[0x7FC0, 0x3F80, 0x4000, 0x7FC0], [0x7FC0] * 4, [0xFF80] * 4], np.uint16)
+    tok, _ = orc.argmax(odd)
+    assert tok.tolist() == [2, 0, 0]
