@@ -55,6 +55,7 @@ struct AttnParams {
   const int32_t* seq_part;
   float* part_acc;
   float* part_ml;
+  uint32_t wait_tries;  // polls a bounded wait makes before it gives up (eb_wait_limit_set)
   int32_t part_slots;  // partial slots part_acc / part_ml hold; a slot index outside [0, part_slots) is skipped and flagged
   int32_t* status;
 };
@@ -81,9 +82,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kWaitTries polls, raises the CTA's abort flag and the device status word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
-  for (uint32_t i = 0; i < kWaitTries; ++i) {
+// Bounded wait: gives up after `tries` polls, raises the CTA's abort flag and the device status word.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                          uint32_t tries) {
+  for (uint32_t i = 0; i < tries; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) {
       __nanosleep(64);
@@ -197,7 +199,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
       for (int it = 0; it < n_iters; ++it) {
         const int s = it % STAGES;
         if (it >= STAGES) {
-          if (!mbar_wait(smem_u32(&bars[STAGES + s]), ((it / STAGES) - 1) & 1, &abort_flag, p.status)) break;
+          if (!mbar_wait(smem_u32(&bars[STAGES + s]), ((it / STAGES) - 1) & 1, &abort_flag, p.status, p.wait_tries)) break;
         }
         const int np = min(PPS, n_pages - it * PPS);
         const uint32_t full = smem_u32(&bars[s]);
@@ -254,7 +256,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
 
     for (int it = 0; it < n_iters; ++it) {
       const int s = it % STAGES;
-      if (!mbar_wait(smem_u32(&bars[s]), (it / STAGES) & 1, &abort_flag, p.status)) break;
+      if (!mbar_wait(smem_u32(&bars[s]), (it / STAGES) & 1, &abort_flag, p.status, p.wait_tries)) break;
       const int pl = it * PPS + sub;
       if (pl < n_pages) {
         const uint32_t page_base = stage0 + s * kStageBytes + sub * kPageBytes;
@@ -582,7 +584,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
     if (lane == 0) {
       for (int blk = 0; blk < n_blk; ++blk) {
         const int sidx = blk % NS;
-        if (blk >= NS && !mbar_wait(bar_empty + 8 * sidx, ((blk / NS) - 1) & 1, &abort_flag, p.status)) break;
+        if (blk >= NS && !mbar_wait(bar_empty + 8 * sidx, ((blk / NS) - 1) & 1, &abort_flag, p.status, p.wait_tries)) break;
         const uint32_t full = bar_full + 8 * sidx;
         mbar_arrive_expect_tx(full, (uint32_t)kStage);
         const uint32_t sb = stage0 + sidx * kStage;
@@ -630,7 +632,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
     // read that buffer)
     auto issue_s = [&](int blk) -> bool {
       const int sidx = blk % NS;
-      if (!mbar_wait(bar_full + 8 * sidx, (blk / NS) & 1, &abort_flag, p.status)) return false;
+      if (!mbar_wait(bar_full + 8 * sidx, (blk / NS) & 1, &abort_flag, p.status, p.wait_tries)) return false;
       tc_fence_after();
       const uint64_t dq = tc_desc_sw128(q_addr), dk = tc_desc_sw128(stage0 + sidx * kStage + h * kHeadK);
 #pragma unroll
@@ -642,7 +644,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
     // next (or the final commit)
     auto issue_pv = [&](int blk) -> bool {
       const int b = blk & 1;
-      if (!mbar_wait(bar_pd, blk & 1, &abort_flag, p.status)) return false;
+      if (!mbar_wait(bar_pd, blk & 1, &abort_flag, p.status, p.wait_tries)) return false;
       tc_fence_after();
       const int sidx = blk % NS;
       const uint64_t dv = tc_desc_sw128(stage0 + sidx * kStage + HPC * kHeadK + h * kHeadK);
@@ -669,7 +671,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
     if (active) {
       for (int blk = 0; blk < n_blk && ok; ++blk) {
         const int b = blk & 1;
-        if (!mbar_wait(bar_s + 8 * b, (blk >> 1) & 1, &abort_flag, p.status)) {
+        if (!mbar_wait(bar_s + 8 * b, (blk >> 1) & 1, &abort_flag, p.status, p.wait_tries)) {
           ok = false;
           break;
         }
@@ -699,7 +701,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
           l_run *= alpha;
           if (blk > 0) {
             // O holds earlier blocks: wait for the last product that adds to it, then rescale this row in tensor memory
-            if (!mbar_wait(bar_pv + 8 * ((blk - 1) & 1), ((blk - 1) >> 1) & 1, &abort_flag, p.status)) {
+            if (!mbar_wait(bar_pv + 8 * ((blk - 1) & 1), ((blk - 1) >> 1) & 1, &abort_flag, p.status, p.wait_tries)) {
               ok = false;
               break;
             }
@@ -734,7 +736,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
         if (issuer_warp) ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;  // the issuer's warp follows its lane 0
       }
       // ---------------- epilogue: O of this row
-      if (ok && n_blk > 0 && mbar_wait(bar_o, 0, &abort_flag, p.status)) {
+      if (ok && n_blk > 0 && mbar_wait(bar_o, 0, &abort_flag, p.status, p.wait_tries)) {
         tc_fence_after();
         const int n_parts_seq = p.seq_part[seq + 1] - p.seq_part[seq];
         const bool direct = (n_parts_seq == 1);
@@ -1069,6 +1071,7 @@ int32_t run_attn(const eb_attn_args* a, float* part_acc, float* part_ml, int32_t
   p.part_acc = part_acc;  // every partial row that the merge reads is written by this launch first: nothing to clear
   p.part_ml = part_ml;
   p.part_slots = a->n_parts;
+  p.wait_tries = eb::wait_tries();
   p.status = status;
 
   cudaStream_t st = eb::as_stream(stream);

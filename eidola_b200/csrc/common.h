@@ -19,6 +19,10 @@ int32_t* status_word();
 // point has resolved it.
 int32_t* static_status_word_if_ready();
 
+// Polls a bounded device-side wait (mbarrier, flag) makes before it gives up with EB_DEV_WAIT_TIMEOUT.
+// Default 1 << 22 (seconds); EIDOLA_B200_WAIT_TRIES or eb_wait_limit_set() change it for launches made afterwards.
+uint32_t wait_tries();
+
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }

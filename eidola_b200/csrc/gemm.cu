@@ -45,6 +45,7 @@ struct GemmParams {
   const int32_t* tile_row0;   // grouped: [max_tiles]
   const int32_t* n_tiles;     // grouped: device scalar
   int32_t* status;
+  uint32_t wait_tries;  // polls a bounded wait makes before it gives up (eb_wait_limit_set)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -68,8 +69,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
-  for (uint32_t i = 0; i < kWaitTries; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                          uint32_t tries) {
+  for (uint32_t i = 0; i < tries; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) {
       __nanosleep(64);
@@ -241,7 +243,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     if (lane == 0) {
       for (int i = prefilled; i < nkb; ++i) {
         const int s = i % S;
-        if (i >= S && !mbar_wait(bar_empty + 8 * s, ((i / S) - 1) & 1, &abort_flag, p.status)) break;
+        if (i >= S && !mbar_wait(bar_empty + 8 * s, ((i / S) - 1) & 1, &abort_flag, p.status, p.wait_tries)) break;
         const uint32_t a_dst = stage0 + s * C::kStageBytes, b_dst = a_dst + kTileN * kBlockK;
         mbar_arrive_expect_tx(bar_full + 8 * s, C::kStageBytes);
         tma_load_2d(a_dst, &tm_w, (kb0 + i) * kBlockK, wy, bar_full + 8 * s);
@@ -254,8 +256,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(kTileN >> 4) << 24);
       for (int i = 0; i < nkb; ++i) {
         const int s = i % S, b = i & 1;
-        if (!mbar_wait(bar_full + 8 * s, (i / S) & 1, &abort_flag, p.status)) break;
-        if (i >= 2 && !mbar_wait(bar_tempty + 8 * b, ((i >> 1) - 1) & 1, &abort_flag, p.status)) break;
+        if (!mbar_wait(bar_full + 8 * s, (i / S) & 1, &abort_flag, p.status, p.wait_tries)) break;
+        if (i >= 2 && !mbar_wait(bar_tempty + 8 * b, ((i >> 1) - 1) & 1, &abort_flag, p.status, p.wait_tries)) break;
         tc_fence_after();
         const uint32_t a_addr = stage0 + s * C::kStageBytes, b_addr = a_addr + kTileN * kBlockK;
         const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
@@ -275,7 +277,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     for (int j = 0; j < TN; ++j) acc[j] = 0.f;
     for (int i = 0; i < nkb; ++i) {
       const int b = i & 1;
-      if (!mbar_wait(bar_tfull + 8 * b, (i >> 1) & 1, &abort_flag, p.status)) break;
+      if (!mbar_wait(bar_tfull + 8 * b, (i >> 1) & 1, &abort_flag, p.status, p.wait_tries)) break;
       tc_fence_after();
       const float sc = sprod[i];
 #pragma unroll
@@ -407,7 +409,7 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
         const int wy = t.g * p.N + t.n0;
         for (int i = 0; i < t.nkb; ++i, ++it) {
           const uint32_t s = it % S;
-          if (it >= (uint32_t)S && !mbar_wait(bar_empty + 8 * s, ((it / S) - 1) & 1, &abort_flag, p.status)) {
+          if (it >= (uint32_t)S && !mbar_wait(bar_empty + 8 * s, ((it / S) - 1) & 1, &abort_flag, p.status, p.wait_tries)) {
             ok = false;
             break;
           }
@@ -427,8 +429,8 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
         const TileInfo t = decode_tile(p, w, TT, NB, KB, TN);
         for (int i = 0; i < t.nkb; ++i, ++it) {
           const uint32_t s = it % S, b = it % NBUF;
-          if (!mbar_wait(bar_full + 8 * s, (it / S) & 1, &abort_flag, p.status) ||
-              (it >= (uint32_t)NBUF && !mbar_wait(bar_tempty + 8 * b, ((it / NBUF) - 1) & 1, &abort_flag, p.status))) {
+          if (!mbar_wait(bar_full + 8 * s, (it / S) & 1, &abort_flag, p.status, p.wait_tries) ||
+              (it >= (uint32_t)NBUF && !mbar_wait(bar_tempty + 8 * b, ((it / NBUF) - 1) & 1, &abort_flag, p.status, p.wait_tries))) {
             ok = false;
             break;
           }
@@ -466,7 +468,7 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
       for (int j = 0; j < TN; ++j) acc[j] = 0.f;
       for (int i = 0; i < t.nkb; ++i, ++it) {
         const uint32_t b = it % NBUF;
-        if (!mbar_wait(bar_tfull + 8 * b, (it / NBUF) & 1, &abort_flag, p.status)) {
+        if (!mbar_wait(bar_tfull + 8 * b, (it / NBUF) & 1, &abort_flag, p.status, p.wait_tries)) {
           ok = false;
           break;
         }
@@ -595,7 +597,7 @@ gemm_fp8_big_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int row0 = (w % TT) * kBigTokens, n0 = (w / TT) * kBigRows;
         for (int i = 0; i < KB; ++i, ++it) {
           const uint32_t s = it % S;
-          if (it >= (uint32_t)S && !mbar_wait(bar_empty + 8 * s, ((it / S) - 1) & 1, &abort_flag, p.status)) {
+          if (it >= (uint32_t)S && !mbar_wait(bar_empty + 8 * s, ((it / S) - 1) & 1, &abort_flag, p.status, p.wait_tries)) {
             ok = false;
             break;
           }
@@ -612,8 +614,8 @@ gemm_fp8_big_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
         for (int i = 0; i < KB; ++i, ++it) {
           const uint32_t s = it % S, b = it % NBUF;
-          if (!mbar_wait(bar_full + 8 * s, (it / S) & 1, &abort_flag, p.status) ||
-              (it >= (uint32_t)NBUF && !mbar_wait(bar_tempty + 8 * b, ((it / NBUF) - 1) & 1, &abort_flag, p.status))) {
+          if (!mbar_wait(bar_full + 8 * s, (it / S) & 1, &abort_flag, p.status, p.wait_tries) ||
+              (it >= (uint32_t)NBUF && !mbar_wait(bar_tempty + 8 * b, ((it / NBUF) - 1) & 1, &abort_flag, p.status, p.wait_tries))) {
             ok = false;
             break;
           }
@@ -653,7 +655,7 @@ gemm_fp8_big_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
       for (int i = 0; i < KB; ++i, ++it) {
         const uint32_t b = it % NBUF;
-        if (!mbar_wait(bar_tfull + 8 * b, (it / NBUF) & 1, &abort_flag, p.status)) {
+        if (!mbar_wait(bar_tfull + 8 * b, (it / NBUF) & 1, &abort_flag, p.status, p.wait_tries)) {
           ok = false;
           break;
         }
@@ -975,6 +977,7 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
   p.K = a->K;
   p.n_groups = a->n_groups;
   p.status = status;
+  p.wait_tries = eb::wait_tries();
   p.splits = 1;
 
   const int KB = (a->K + kBlockK - 1) / kBlockK;

@@ -2,6 +2,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 #include <string>
 
@@ -28,6 +29,21 @@ bool pdl_enabled() {
     return !(v && v[0] == '1');
   }();
   return on;
+}
+
+static std::atomic<uint32_t> g_wait_tries{0};
+
+uint32_t wait_tries() {
+  uint32_t v = g_wait_tries.load(std::memory_order_relaxed);
+  if (v == 0) {
+    v = 1u << 22;
+    if (const char* e = getenv("EIDOLA_B200_WAIT_TRIES")) {
+      const long long x = atoll(e);
+      if (x >= 1 && x <= 0x7fffffffll) v = (uint32_t)x;
+    }
+    g_wait_tries.store(v, std::memory_order_relaxed);
+  }
+  return v;
 }
 
 static std::mutex g_status_mu;
@@ -176,6 +192,18 @@ int32_t eb_event_elapsed_ms(void* ev_start, void* ev_stop, float* ms) {
   return EB_OK;
 }
 
+int32_t eb_wait_limit_set(uint32_t tries) {
+  EB_REQUIRE(tries >= 1 && tries <= 0x7fffffffu, EB_ERR_ARG, "eb_wait_limit_set: %u polls outside 1..2^31-1", tries);
+  eb::g_wait_tries.store(tries, std::memory_order_relaxed);
+  return EB_OK;
+}
+
+int32_t eb_wait_limit_get(uint32_t* tries) {
+  EB_REQUIRE(tries, EB_ERR_ARG, "eb_wait_limit_get: null");
+  *tries = eb::wait_tries();
+  return EB_OK;
+}
+
 int32_t eb_status_read(int32_t* status) {
   EB_REQUIRE(status, EB_ERR_ARG, "eb_status_read: null");
   int32_t* p = eb::status_word();
@@ -198,6 +226,36 @@ int32_t eb_status_read(int32_t* status) {
 // kernels
 
 namespace {
+
+// One CTA waits, with the library's bounded-wait discipline, on a shared-memory barrier that nothing will ever
+// complete: the wait runs out after `tries` polls, the status word gets EB_DEV_WAIT_TIMEOUT and the kernel returns.
+__global__ void wait_expires_kernel(uint32_t tries, int32_t* status, uint32_t* polls_out) {
+  __shared__ uint64_t bar;
+  const uint32_t b = (uint32_t)__cvta_generic_to_shared(&bar);
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(b), "r"(1u));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t i = 0;
+    bool done = false;
+    for (; i < tries && !done; ++i) {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(b), "r"(0u)
+          : "memory");
+      done = ok != 0;
+      if (!done && i > 64) __nanosleep(64);
+    }
+    if (!done) atomicOr(status, EB_DEV_WAIT_TIMEOUT);
+    *polls_out = i;
+  }
+}
 
 __global__ void l2_flush_kernel(uint4* p, size_t n16, uint32_t v) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -280,6 +338,23 @@ int32_t launch_synth(void* d_out, int64_t n, uint64_t seed, uint64_t sid, uint64
 }  // namespace
 
 extern "C" {
+
+int32_t eb_selftest_wait_expires(uint32_t tries, uint32_t* h_polls) {
+  EB_REQUIRE(tries >= 1 && tries <= (1u << 20), EB_ERR_ARG, "eb_selftest_wait_expires: %u polls outside 1..2^20", tries);
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_selftest_wait_expires: no device");
+  uint32_t* d_polls = nullptr;
+  EB_CUDA(cudaMalloc(&d_polls, sizeof(uint32_t)));
+  wait_expires_kernel<<<1, 32>>>(tries, status, d_polls);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  uint32_t polls = 0;
+  if (e == cudaSuccess) e = cudaMemcpy(&polls, d_polls, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+  cudaFree(d_polls);
+  if (e != cudaSuccess) return eb::fail((int32_t)e, "eb_selftest_wait_expires: %s", cudaGetErrorString(e));
+  if (h_polls) *h_polls = polls;
+  return EB_OK;
+}
 
 int32_t eb_l2_flush(void* d_scratch, size_t bytes, void* stream) {
   EB_REQUIRE(d_scratch && bytes >= 16, EB_ERR_ARG, "eb_l2_flush: null or too small");

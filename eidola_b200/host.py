@@ -203,10 +203,94 @@ class Comm:
     def reduce_scatter_f32(self, d_buf, count_per_rank, stream=None) -> None:
         call("eb_comm_reduce_scatter_f32", self._h, c_vp(d_buf), c_i64(count_per_rank), c_vp(stream))
 
+    def async_error(self) -> int:
+        """0 while the communicator is healthy (ncclCommGetAsyncError)."""
+        e = c_i32(0)
+        call("eb_comm_async_error", self._h, C.byref(e))
+        return int(e.value)
+
+    def abort(self) -> None:
+        """Tear the communicator down without waiting for its peers (after a lost rank or a missed deadline)."""
+        if self._h:
+            call("eb_comm_abort", self._h)
+
     def close(self):
         if self._h:
             call("eb_comm_destroy", self._h)
             self._h = None
+
+
+class PeerLost(RuntimeError):
+    """A rank of the tensor-parallel group left or stopped answering; the communicator has been aborted."""
+
+    def __init__(self, msg: str, ranks):
+        super().__init__(msg)
+        self.ranks = list(ranks)
+
+
+class StepGuard:
+    """Host-side liveness check of a tensor-parallel group, run BETWEEN steps, before the next launch.
+
+    No kernel of this library waits on another rank outside a collective, and a collective whose peer never joins
+    would block the stream.  So failure detection stays on the host, in the reference's style: its engine supervisor
+    polls a child with a deadline and turns silence into an error (crates/eidola-app-core/src/local_models.rs:
+    2020-2064, 2066-2099), and its tests script the failing peer (tests/chat_harness/mod.rs:100-108).  Every rank
+    announces the step it is about to launch in a key-value store (anything with set(key, value) and get(key), e.g.
+    torch.distributed.TCPStore); a rank that shuts down says so with leave().  wait_peers(step) returns once every
+    peer has announced `step`; if a peer has left, or the deadline passes, it aborts the communicator (so that no
+    collective of the next step can block) and raises PeerLost.  A rank leaves only between steps, with none of its
+    kernels or collectives in flight.
+    """
+
+    def __init__(self, store, rank: int, world: int, comm=None, deadline_s: float = 5.0, poll_s: float = 0.005,
+                 clock=None, sleep=None):
+        import time
+        self.store, self.rank, self.world, self.comm = store, rank, world, comm
+        self.deadline_s, self.poll_s = deadline_s, poll_s
+        self.clock = clock or time.monotonic
+        self.sleep = sleep or time.sleep
+        self.aborted = False
+
+    def _get(self, key: str):
+        try:
+            if hasattr(self.store, "check") and not self.store.check([key]):
+                return None
+            v = self.store.get(key)
+        except (KeyError, RuntimeError):
+            return None
+        return v.decode() if isinstance(v, (bytes, bytearray)) else v
+
+    def announce(self, step: int) -> None:
+        self.store.set(f"eb/step/{self.rank}", str(int(step)))
+
+    def leave(self) -> None:
+        self.store.set(f"eb/left/{self.rank}", "1")
+
+    def _abort(self, msg: str, ranks):
+        if self.comm is not None and not self.aborted:
+            self.comm.abort()
+        self.aborted = True
+        raise PeerLost(msg, ranks)
+
+    def wait_peers(self, step: int) -> None:
+        t0 = self.clock()
+        peers = [r for r in range(self.world) if r != self.rank]
+        while True:
+            behind = []
+            for r in peers:
+                v = self._get(f"eb/step/{r}")
+                if v is None or int(v) < step:
+                    behind.append(r)
+            if not behind:
+                return  # a peer that leaves after announcing this step is caught before the next one
+            left = [r for r in behind if self._get(f"eb/left/{r}") is not None]
+            if left:
+                self._abort(f"rank(s) {left} left the group before step {step}", left)
+            if self.comm is not None and self.comm.async_error() != 0:
+                self._abort(f"communicator reports an asynchronous error before step {step}", behind)
+            if self.clock() - t0 > self.deadline_s:
+                self._abort(f"rank(s) {behind} did not announce step {step} within {self.deadline_s} s", behind)
+            self.sleep(self.poll_s)
 
 
 class Engine:
@@ -315,6 +399,12 @@ class Engine:
         else:
             x = np.ascontiguousarray(x, np.uint16)
             call("eb_engine_debug_force_hidden", self._h, c_i32(layer), ptr(x), c_i32(x.shape[0]))
+
+    def last_step_copies(self) -> tuple[int, int]:
+        """(host -> device, device -> host) bytes the last step copied."""
+        a, b = c_i64(0), c_i64(0)
+        call("eb_engine_last_step_copies", self._h, C.byref(a), C.byref(b))
+        return int(a.value), int(b.value)
 
     def last_step_breakdown(self) -> dict:
         ms = (c_f32 * 8)()

@@ -87,6 +87,16 @@ int32_t eb_event_record(void* ev, void* stream);
 int32_t eb_event_elapsed_ms(void* ev_start, void* ev_stop, float* ms); /* synchronises on ev_stop */
 /* Writes `bytes` of a scratch buffer so that the L2 holds none of the caller's tensors. */
 int32_t eb_l2_flush(void* d_scratch, size_t bytes, void* stream);
+/* Every wait inside a kernel (on a shared-memory barrier fed by TMA or by the tensor core) is a bounded poll: after
+ * `tries` polls the kernel raises EB_DEV_WAIT_TIMEOUT, drains its copies in flight, frees its tensor memory and
+ * returns, so the context stays usable and the host decides what to do (the reference turns a stalled engine into an
+ * error the same way: a 300 s readiness budget, crates/eidola-app-core/src/local_models.rs:2020-2064).  The default
+ * is 2^22 polls (seconds); EIDOLA_B200_WAIT_TRIES or eb_wait_limit_set() set it for launches made afterwards. */
+int32_t eb_wait_limit_set(uint32_t tries);
+int32_t eb_wait_limit_get(uint32_t* tries);
+/* Self-test of that discipline: one CTA polls, at most `tries` (<= 2^20) times, a barrier that nothing completes.  The
+ * kernel returns, EB_DEV_WAIT_TIMEOUT appears in the status word, *h_polls receives the polls made.  Nothing hangs. */
+int32_t eb_selftest_wait_expires(uint32_t tries, uint32_t* h_polls);
 /* Device status word (EB_DEV_* bits) accumulated by kernels since the last read; reading clears it. */
 int32_t eb_status_read(int32_t* status);
 

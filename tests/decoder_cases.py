@@ -89,6 +89,19 @@ def free_running_error(got, ref):
     return np.abs(g - r).max(axis=1), float(np.linalg.norm(hg - hr) / np.linalg.norm(hr))
 
 
+def error_bias(got_u16, ref_u16):
+    """(signed mean, rms) of gpu - oracle over a bf16 tensor.  Quantisation noise is unbiased: its mean is a small
+    fraction of its rms (about 1/sqrt(elements)); a systematic error -- a dropped term, a wrong scale -- is not."""
+    d = bf16_to_f32(got_u16).astype(np.float64) - bf16_to_f32(ref_u16).astype(np.float64)
+    return float(d.mean()), float(np.sqrt((d * d).mean()))
+
+
+def assert_unbiased(got_u16, ref_u16, what, ratio=0.05):
+    mean, rms = error_bias(got_u16, ref_u16)
+    assert abs(mean) <= ratio * rms + 1e-6, f"{what}: signed mean error {mean:.3e} against rms {rms:.3e} (a bias, not noise)"
+    return mean, rms
+
+
 def compare_step(got, ref, cfg, what=""):
     """got: dict(next, margin, logits, route_idx[L], hidden[L+1]) from the engine; ref: the oracle's step dict.
     Returns the set of token rows that diverged through an explained routing tie (excluded from later checks)."""

@@ -15,6 +15,11 @@ S_KV, S_Q, S_SINK = 101, 102, 103
 # |gpu - oracle| <= ATOL + RTOL * |oracle|, RTOL = one bf16 ulp (2^-7 relative spacing is 2^-8..2^-7).
 ATOL = 1e-2
 RTOL = 2.0 ** -7
+# Attention outputs are convex combinations of N(0,1) values: O(1) for a handful of keys, O(0.05) over thousands.
+# The measured worst difference from the oracle is 1e-3..2e-3 (the softmax weights reach the second MMA as a bf16
+# head plus remainder), so the absolute part of the bound is 3e-3: a dropped page or a wrong mask on a long
+# sequence (errors of 1e-2 and more) fails it.
+ATTN_ATOL = 3e-3
 
 
 def bf16_to_f32(h: np.ndarray) -> np.ndarray:

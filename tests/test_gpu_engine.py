@@ -6,7 +6,8 @@ import pytest
 
 from oracle import binding as orc
 from oracle import sched as osched
-from tests.decoder_cases import (TINY_CONTEXTS, compare_forced_step, free_running_error, mid_config, tiny_config)
+from tests.decoder_cases import (TINY_CONTEXTS, assert_unbiased, compare_forced_step, free_running_error, mid_config,
+                                 tiny_config)
 
 pytestmark = pytest.mark.gpu
 GOLD = np.load(Path(__file__).parent / "golden" / "tiny_decode.npz")
@@ -76,6 +77,8 @@ def test_tiny_decode_step_matches_golden_and_oracle(gpu):
     got = _engine_step(eng, slots, [1, 1, 1, 1], toks)
     dl, rel = free_running_error(got, ref)
     assert dl.max() <= FREE_LOGIT_ABS["tiny"] and rel <= FREE_HIDDEN_REL, (dl, rel)
+    assert_unbiased(got["logits"], ref["logits"], "tiny free-running logits")
+    assert_unbiased(got["hidden"][-1], ref["hidden"][-1], "tiny free-running hidden")
     assert np.array_equal(got["route_idx"][0], GOLD["route_idx0"][0])  # layer 0 routing sees identical inputs
     print(f"tiny: forced hidden err {worst_h:.4f} logits err {worst_l:.4f}; free logits err {dl.max():.4f} hidden rel {rel:.4f}")
 
@@ -103,6 +106,36 @@ def test_tiny_greedy_64_steps(gpu):
     assert clear_matched == clear, (clear_matched, clear)
     assert matched >= 0.6 * 256, matched
     print(f"greedy: {matched}/256 tokens equal the golden stream; {clear_matched}/{clear} where the margin is clear")
+
+
+def test_tiny_greedy_64_steps_free_running(gpu):
+    """Greedy decode for 64 steps with the engine's own tokens fed back (nothing imposed).  The golden stream is the
+    oracle's own free run, so a sequence can be compared until its first disagreement; that disagreement must sit
+    where the oracle's top-2 margin is within the free-running logit noise (two logits each off by at most the
+    bound), i.e. the engine never picks a different token at a clear margin."""
+    import eidola_b200 as eb
+    cfg = tiny_config()
+    eng = eb.Engine(cfg)
+    eng.kv_fill_synth()
+    slots = [eng.admit(L) for L in TINY_CONTEXTS]
+    toks = np.array([11, 222, 3333, 4000], np.int32)
+    alive = [True] * 4
+    agreed = [0] * 4
+    for step in range(64):
+        nxt, _ = eng.step(slots, [1, 1, 1, 1], toks)
+        for i in range(4):
+            if not alive[i]:
+                continue
+            if nxt[i] == GOLD["tokens"][step][i]:
+                agreed[i] += 1
+            else:
+                alive[i] = False
+                assert GOLD["margins"][step][i] <= 2 * FREE_LOGIT_ABS["tiny"], (
+                    f"sequence {i} leaves the oracle's stream at step {step} where the oracle's margin is "
+                    f"{GOLD['margins'][step][i]:.3f}")
+        toks = nxt.copy()
+    print(f"free-running greedy: steps in agreement with the oracle's stream per sequence {agreed} (of 64)")
+    assert sum(agreed) >= 64  # the streams share at least a sequence's worth of steps
 
 
 def test_mid_config_ragged_verify_steps(gpu):
@@ -138,7 +171,9 @@ def test_mid_config_ragged_verify_steps(gpu):
     ref, _ = _oracle_step(model, sch, slots, q_lens, toks)
     got = _engine_step(eng, slots, q_lens, toks)
     dl, rel = free_running_error(got, ref)
-    print(f"mid free-running: logits err {dl.max():.4f} hidden rel {rel:.4f}")
+    ml, rl = assert_unbiased(got["logits"], ref["logits"], "mid free-running logits")
+    mh, rh = assert_unbiased(got["hidden"][-1], ref["hidden"][-1], "mid free-running hidden")
+    print(f"mid free-running: logits err max {dl.max():.4f} mean {ml:+.2e} rms {rl:.2e}; hidden rel {rel:.4f} mean {mh:+.2e} rms {rh:.2e}")
     assert dl.max() <= FREE_LOGIT_ABS["mid"] and rel <= FREE_HIDDEN_REL, (dl, rel)
 
 
