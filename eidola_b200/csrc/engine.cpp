@@ -993,6 +993,19 @@ int32_t eb_engine_read_hidden(eb_engine* e, int32_t layer, void* h_x, int64_t by
 }
 
 
+int32_t eb_engine_debug_read_last(eb_engine* e, int32_t which, void* h_out, int64_t bytes) {
+  EB_REQUIRE(e && h_out, EB_ERR_ARG, "eb_engine_debug_read_last: null");
+  EB_REQUIRE(e->c.debug & 1, EB_ERR_STATE, "eb_engine_debug_read_last: engine was not created with debug = 1");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_debug_read_last: a step is in flight");
+  EB_REQUIRE(which == 0 || which == 1, EB_ERR_ARG, "eb_engine_debug_read_last: which %d (0 = q rows, 1 = attention output)", which);
+  const void* src = which == 0 ? (const void*)e->qkv : (const void*)e->attn;
+  const int64_t width = which == 0 ? e->nqkv : e->hqd;
+  EB_REQUIRE(bytes == (int64_t)e->cur_T * width * 2, EB_ERR_ARG, "eb_engine_debug_read_last: expected %lld bytes",
+             (long long)e->cur_T * width * 2);
+  EB_CUDA(cudaMemcpy(h_out, src, (size_t)bytes, cudaMemcpyDeviceToHost));
+  return EB_OK;
+}
+
 int32_t eb_engine_debug_force_hidden(eb_engine* e, int32_t layer, const void* h_x, int32_t rows) {
   EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_debug_force_hidden: null engine");
   EB_REQUIRE(e->c.debug && e->dbg_force, EB_ERR_STATE, "eb_engine_debug_force_hidden: engine was not created with debug = 1");

@@ -19,6 +19,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return r;
 }
 
+// Sum over a 256-thread CTA in a fixed order (an xor butterfly inside each warp, then the warps in ascending order), so
+// that the CPU restatement can add the same numbers in the same order and RMSNorm is reproducible bit for bit.
 __device__ __forceinline__ float block_sum(float v, float* red) {
 #pragma unroll
   for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -30,7 +32,16 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
+// r = 1 / sqrt(ss / H + eps) with every operation rounded once (no contraction, no approximate reciprocal).
+__device__ __forceinline__ float rms_scale(float ss, int H, float eps) {
+  return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)H), eps)));
+}
+__device__ __forceinline__ float rms_apply(float x, float r, float g) { return __fmul_rn(__fmul_rn(x, r), g); }
+
 // One CTA per token row: y = bf16(x * rsqrt(mean(x^2) + eps) * g).  H is a multiple of 8.
+// Summation order of the squares (shared with the fused kernels below and restated by the CPU checker): thread t of
+// 256 owns the 8-column chunks t, t + 256, ... and adds their squares in ascending column order with fused
+// multiply-adds; the 256 partial sums are combined by block_sum.
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* x, const float* g, int H, float eps, uint16_t* y) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
@@ -42,19 +53,22 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t* x, const f
     const uint4 v = *reinterpret_cast<const uint4*>(xr + c);
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int k = 0; k < 4; ++k) ss += bf_lo(w[k]) * bf_lo(w[k]) + bf_hi(w[k]) * bf_hi(w[k]);
+    for (int k = 0; k < 4; ++k) {
+      ss = __fmaf_rn(bf_lo(w[k]), bf_lo(w[k]), ss);
+      ss = __fmaf_rn(bf_hi(w[k]), bf_hi(w[k]), ss);
+    }
   }
   ss = block_sum(ss, red);
-  const float r = 1.0f / sqrtf(ss / (float)H + eps);
+  const float r = rms_scale(ss, H, eps);
   for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
     const uint4 v = *reinterpret_cast<const uint4*>(xr + c);
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
     const float4 g0 = *reinterpret_cast<const float4*>(g + c), g1 = *reinterpret_cast<const float4*>(g + c + 4);
     uint4 o;
-    o.x = pack_bf16(bf_lo(w[0]) * r * g0.x, bf_hi(w[0]) * r * g0.y);
-    o.y = pack_bf16(bf_lo(w[1]) * r * g0.z, bf_hi(w[1]) * r * g0.w);
-    o.z = pack_bf16(bf_lo(w[2]) * r * g1.x, bf_hi(w[2]) * r * g1.y);
-    o.w = pack_bf16(bf_lo(w[3]) * r * g1.z, bf_hi(w[3]) * r * g1.w);
+    o.x = pack_bf16(rms_apply(bf_lo(w[0]), r, g0.x), rms_apply(bf_hi(w[0]), r, g0.y));
+    o.y = pack_bf16(rms_apply(bf_lo(w[1]), r, g0.z), rms_apply(bf_hi(w[1]), r, g0.w));
+    o.z = pack_bf16(rms_apply(bf_lo(w[2]), r, g1.x), rms_apply(bf_hi(w[2]), r, g1.y));
+    o.w = pack_bf16(rms_apply(bf_lo(w[3]), r, g1.z), rms_apply(bf_hi(w[3]), r, g1.w));
     *reinterpret_cast<uint4*>(yr + c) = o;
   }
 }
@@ -483,22 +497,23 @@ row_residual_rmsnorm_kernel(const float* part, int splits, const uint16_t* o_bf1
       xo[k] = pack_bf16(__fadd_rn(bf_lo(xw[k]), v[2 * k]), __fadd_rn(bf_hi(xw[k]), v[2 * k + 1]));
       xv[q][2 * k] = bf_lo(xo[k]);
       xv[q][2 * k + 1] = bf_hi(xo[k]);
-      ss += xv[q][2 * k] * xv[q][2 * k] + xv[q][2 * k + 1] * xv[q][2 * k + 1];
+      ss = __fmaf_rn(xv[q][2 * k], xv[q][2 * k], ss);
+      ss = __fmaf_rn(xv[q][2 * k + 1], xv[q][2 * k + 1], ss);
     }
     *reinterpret_cast<uint4*>(x + e) = make_uint4(xo[0], xo[1], xo[2], xo[3]);
   }
   ss = block_sum(ss, red);
-  const float r = 1.0f / sqrtf(ss / (float)H + eps);
+  const float r = rms_scale(ss, H, eps);
 #pragma unroll
   for (int q = 0; q < 2; ++q) {
     const int ch = threadIdx.x + 256 * q;
     if (ch >= H8) continue;
     const float4 g0 = *reinterpret_cast<const float4*>(g + ch * 8), g1 = *reinterpret_cast<const float4*>(g + ch * 8 + 4);
     uint4 o;
-    o.x = pack_bf16(xv[q][0] * r * g0.x, xv[q][1] * r * g0.y);
-    o.y = pack_bf16(xv[q][2] * r * g0.z, xv[q][3] * r * g0.w);
-    o.z = pack_bf16(xv[q][4] * r * g1.x, xv[q][5] * r * g1.y);
-    o.w = pack_bf16(xv[q][6] * r * g1.z, xv[q][7] * r * g1.w);
+    o.x = pack_bf16(rms_apply(xv[q][0], r, g0.x), rms_apply(xv[q][1], r, g0.y));
+    o.y = pack_bf16(rms_apply(xv[q][2], r, g0.z), rms_apply(xv[q][3], r, g0.w));
+    o.z = pack_bf16(rms_apply(xv[q][4], r, g1.x), rms_apply(xv[q][5], r, g1.y));
+    o.w = pack_bf16(rms_apply(xv[q][6], r, g1.z), rms_apply(xv[q][7], r, g1.w));
     *reinterpret_cast<uint4*>(hout + (int64_t)t * H + ch * 8) = o;
   }
 }

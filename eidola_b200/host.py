@@ -393,6 +393,12 @@ class Engine:
         call("eb_engine_read_hidden", self._h, c_i32(layer), ptr(out), c_i64(out.nbytes))
         return out
 
+    def read_last(self, which: str, width: int) -> np.ndarray:
+        """debug = 1: "qkv" (projection rows, q heads rotated) or "attn" (attention output) of the last layer."""
+        out = np.empty((self._last_T, width), np.uint16)
+        call("eb_engine_debug_read_last", self._h, c_i32({"qkv": 0, "attn": 1}[which]), ptr(out), c_i64(out.nbytes))
+        return out
+
     def force_hidden(self, layer: int, x=None) -> None:
         if x is None:
             call("eb_engine_debug_force_hidden", self._h, c_i32(layer), c_vp(None), c_i32(0))

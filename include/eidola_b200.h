@@ -468,6 +468,10 @@ int32_t eb_engine_read_logits(eb_engine* e, void* h_logits, int64_t bytes);
 int32_t eb_engine_read_routing(eb_engine* e, int32_t layer, int32_t* h_idx, int64_t bytes);
 /* Copy out the residual stream [T][hidden] bf16 as it stood after `layer` (debug = 1; layer = -1: embeddings). */
 int32_t eb_engine_read_hidden(eb_engine* e, int32_t layer, void* h_x, int64_t bytes);
+/* debug bit 0: work buffers of the LAST layer of the last step, so a parity test can tell attention from what follows
+ * it: which = 0 the fused projection rows [T][local q | k | v width] bf16 (the q heads rotated; the k and v columns
+ * are not kept, they went to the cache), which = 1 the attention output [T][local q heads * head_dim] bf16. */
+int32_t eb_engine_debug_read_last(eb_engine* e, int32_t which, void* h_out, int64_t bytes);
 /* Teacher forcing for parity tests (debug = 1): before `layer` runs (layer = n_layers: before the final norm) the
  * residual stream of the next steps with exactly `rows` token rows is replaced by h_x [rows][hidden] bf16.  FP8
  * activation quantisation amplifies a one-ulp difference into percent-level differences a layer later, so a

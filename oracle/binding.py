@@ -265,6 +265,17 @@ class Model:
     def kv_fill_synth(self):
         _void("orc_model_kv_fill_synth", self._h)
 
+    def last(self, which: str) -> np.ndarray:
+        """Intermediate of the last layer the last step ran: "qkv" (rotated q | k | v rows), "attn" (attention output) or
+        "o" (O projection output); a copy, [T][width] bf16 bits."""
+        idx = {"qkv": 0, "attn": 1, "o": 2}[which]
+        p = C.POINTER(C.c_uint16)()
+        _lib.orc_model_last.restype = C.c_int64
+        n = int(_lib.orc_model_last(self._h, C.c_int32(idx), C.byref(p)))
+        c = self.cfg
+        width = {"qkv": (c.n_q_heads + 2 * c.n_kv_heads) * c.head_dim, "attn": c.n_q_heads * c.head_dim, "o": c.hidden}[which]
+        return np.ctypeslib.as_array(p, shape=(n // width, width)).copy()
+
     def embed_table(self) -> np.ndarray:
         """A writable view of the embedding table [vocab][hidden] (uint16 bf16 bits)."""
         _lib.orc_model_embed.restype = C.POINTER(C.c_uint16)

@@ -76,6 +76,8 @@ struct orc_model {
   std::vector<uint16_t> embed;
   W8 lm;
   std::vector<float> g_final, rope_cos, rope_sin;
+  /* intermediates of the last layer of the last step: rotated q | k | v rows, attention output, O projection */
+  std::vector<uint16_t> last_qkv, last_att, last_o;
 };
 
 extern "C" {
@@ -125,6 +127,14 @@ void orc_model_kv_fill_synth(orc_model* m) {
   }
 }
 
+/* Intermediates of the last layer the last step ran (which: 0 = [q | k | v] rows after the rotary embedding,
+ * 1 = attention output, 2 = O projection output); returns the element count. */
+int64_t orc_model_last(orc_model* m, int32_t which, const uint16_t** p) {
+  const std::vector<uint16_t>& v = which == 0 ? m->last_qkv : which == 1 ? m->last_att : m->last_o;
+  *p = v.data();
+  return (int64_t)v.size();
+}
+
 uint16_t* orc_model_cache(orc_model* m, int32_t layer) { return m->layers[(size_t)layer].cache.data(); }
 /* Embedding table [vocab][hidden] bf16 (tests perturb one entry by one ulp to measure the decoder's own sensitivity). */
 uint16_t* orc_model_embed(orc_model* m) { return m->embed.data(); }
@@ -164,6 +174,11 @@ void orc_model_step(orc_model* m, int32_t T, int32_t n_seqs, const int32_t* toke
                         L.sinks.data(), window, c.n_q_heads, c.n_kv_heads, c.head_dim, c.page_size, 0.125f, att.data(), m->hqd);
     orc_quant_act_block128(att.data(), m->hqd, seg, 1, a8.data(), sa.data());
     orc_gemm_fp8_block(a8.data(), sa.data(), L.wo.codes.data(), L.wo.scales.data(), T, H, m->hqd, o.data());
+    if (l + 1 == nl) {
+      m->last_qkv = qkv;
+      m->last_att = att;
+      m->last_o = o;
+    }
     orc_residual_add(x.data(), o.data(), (int64_t)T * H);
     orc_rmsnorm(x.data(), L.g_mlp.data(), T, H, c.rms_eps, h.data());
     orc_router_topk(h.data(), L.wr.data(), T, E, H, K, idx.data(), wts.data(), rl.data());

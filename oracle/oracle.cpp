@@ -206,17 +206,35 @@ void orc_attn_paged_sink(const uint16_t* q, int64_t q_stride, const uint16_t* ca
 
 /* ---------------------------------------------------------------- glue */
 
-/* y = bf16( x * rsqrt(mean(x^2) + eps) * g ), fp32 arithmetic, sequential sum of squares in 16 lanes. */
+/* y = bf16( (x * r) * g ), r = 1 / sqrt(ss / H + eps), fp32 arithmetic with every operation rounded once.
+ * The sum of squares ss follows a fixed order, the one a 256-thread row kernel uses: partial sum t of 256 takes the
+ * 8-column chunks t, t + 256, ... in ascending column order with fused multiply-adds; each group of 32 partial sums
+ * is combined by an xor butterfly (offsets 16, 8, 4, 2, 1), and the 8 group sums are added in ascending order. */
 void orc_rmsnorm(const uint16_t* x, const float* g, int64_t T, int64_t H, float eps, uint16_t* y) {
 #pragma omp parallel for schedule(static)
   for (int64_t t = 0; t < T; ++t) {
-    double ss = 0.0;
-    for (int64_t c = 0; c < H; ++c) {
-      const double v = bf(x[t * H + c]);
-      ss += v * v;
+    float part[256];
+    for (int p = 0; p < 256; ++p) {
+      float ss = 0.f;
+      for (int64_t c0 = (int64_t)p * 8; c0 < H; c0 += 256 * 8)
+        for (int64_t c = c0; c < std::min(c0 + 8, H); ++c) {
+          const float v = bf(x[t * H + c]);
+          ss = fmaf(v, v, ss);
+        }
+      part[p] = ss;
     }
-    const float r = 1.0f / sqrtf((float)(ss / (double)H) + eps);
-    for (int64_t c = 0; c < H; ++c) y[t * H + c] = tobf(bf(x[t * H + c]) * r * g[c]);
+    float total = 0.f;
+    for (int w = 0; w < 8; ++w) {
+      float a[32], b[32];
+      for (int l = 0; l < 32; ++l) a[l] = part[w * 32 + l];
+      for (int o = 16; o; o >>= 1) {
+        for (int l = 0; l < 32; ++l) b[l] = a[l] + a[l ^ o];
+        for (int l = 0; l < 32; ++l) a[l] = b[l];
+      }
+      total += a[0];
+    }
+    const float r = 1.0f / sqrtf(total / (float)H + eps);
+    for (int64_t c = 0; c < H; ++c) y[t * H + c] = tobf((bf(x[t * H + c]) * r) * g[c]);
   }
 }
 

@@ -8,7 +8,9 @@ from tests.helpers import bf16_to_f32
 # Logits: |gpu - oracle| <= 1e-2 or one bf16 ulp of the oracle value, whichever is larger (a bf16 logit in [4,8)
 # is spaced 0.031 apart, so a bare 1e-2 cannot hold across a rounding boundary).
 LOGIT_ATOL, LOGIT_RTOL = 1e-2, 2.0 ** -7
-# A routing or argmax decision may differ only where the oracle itself was within this of a tie.
+# A routing or argmax decision may differ only where the oracle itself was within this of a tie.  The router's input
+# carries the relative noise of the attention and O-projection path (a few 1e-3 after e4m3 requantisation), and a
+# logit inherits it in proportion to its size, so the tie width is 2e-3 of the row's largest |logit| (at least 2e-3).
 ROUTE_TIE, TOKEN_TIE = 2e-3, 6e-2
 
 
@@ -43,7 +45,7 @@ def routing_mismatches(got_idx, ref_idx, ref_logits, top_k):
     for t in bad_rows:
         s = np.sort(ref_logits[t])[::-1]
         gaps = [s[j] - s[j + 1] for j in range(min(top_k, len(s) - 1))]
-        if min(gaps) > ROUTE_TIE:
+        if min(gaps) > ROUTE_TIE * max(1.0, float(np.abs(s).max())):
             unexplained.append(int(t))
     return set(int(t) for t in bad_rows), unexplained
 
