@@ -950,6 +950,13 @@ int32_t eb_engine_last_step_copies(const eb_engine* e, int64_t* h2d_bytes, int64
   return EB_OK;
 }
 
+int32_t eb_engine_profile(eb_engine* e, int32_t on) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_profile: null engine");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_profile: a step is in flight");
+  e->c.debug = on ? (e->c.debug | 2) : (e->c.debug & ~2);
+  return EB_OK;
+}
+
 int32_t eb_engine_last_step_breakdown(const eb_engine* e, float* ms8) {
   EB_REQUIRE(e && ms8, EB_ERR_ARG, "eb_engine_last_step_breakdown: null");
   EB_REQUIRE(e->c.debug & 2, EB_ERR_STATE, "eb_engine_last_step_breakdown: engine was not created with debug & 2");

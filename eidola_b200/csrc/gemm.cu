@@ -710,6 +710,61 @@ gemm_fp8_big_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Issue-rate microbenchmark of the FP8 tensor path: the denominator for "fraction of FP8 peak".  Every CTA (one per
+// SM) fills two operand stages in shared memory with pseudo-random e4m3 codes once, then one thread issues `blocks`
+// groups of four tcgen05.mma.kind::f8f6f4 (M = 128, N = 256, K = 32 each) back to back, alternating between the two
+// stages and two accumulators in tensor memory.  Nothing is loaded from global memory and nothing is read back, so the
+// time is the tensor pipe's alone: 2 * 128 * 256 * 128 flop per group per SM.
+constexpr int kPeakStageBytes = (128 + 256) * kBlockK;
+constexpr size_t kPeakSmem = 1024 + 2 * kPeakStageBytes + 64;
+
+__global__ void __launch_bounds__(128, 1) fp8_mma_peak_kernel(int blocks, int32_t* status, uint32_t wait_tries) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t stage0 = (raw + 1023u) & ~1023u;
+  uint8_t* stages = smem_raw + (stage0 - raw);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(stages + 2 * kPeakStageBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  // operands: hashed bytes with the exponent field kept below all-ones (no NaN codes), so the data toggles as real
+  // activations and weights would
+  for (int i = tid; i < 2 * kPeakStageBytes / 4; i += blockDim.x) {
+    uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
+    h ^= h >> 15;
+    h *= 2246822519u;
+    h ^= h >> 13;
+    reinterpret_cast<uint32_t*>(stages)[i] = h & 0xBFBFBFBFu;
+  }
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes visible to the tensor core
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (tid == 0) {
+    constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    for (int i = 0; i < blocks; ++i) {
+      const uint32_t a_addr = stage0 + (i & 1) * kPeakStageBytes, b_addr = a_addr + 128 * kBlockK;
+      const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(b_addr);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) tc_mma_f8(tmem_base + (i & 1) * 256, da + 2 * k, db + 2 * k, idesc, (i > 1 || k > 0) ? 1u : 0u);
+    }
+    tc_commit(smem_u32(bar));
+    mbar_wait(smem_u32(bar), 0, &abort_flag, status, wait_tries);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
 // Sum split-K partials in split order and round to bf16.
 __global__ void gemm_splitk_reduce_kernel(const float* part, uint16_t* y, int64_t ldy, int rows, int N, int splits) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
@@ -1142,6 +1197,42 @@ int32_t eb_gemm_group_tiles(const int32_t* d_seg_off, int32_t n_groups, int32_t 
   EB_CUDA(eb::launch(gemm_tiles_kernel, dim3(1), dim3(256), 0, eb::as_stream(stream), d_seg_off, n_groups, tile_tokens, token_tiles, w, tile_group,
                                                           tile_group + token_tiles, n_tiles, status));
   EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_fp8_mma_peak(int32_t blocks, int32_t reps, float* best_ms, double* tflops) {
+  EB_REQUIRE(blocks >= 1 && blocks <= (1 << 16) && reps >= 1 && reps <= 64, EB_ERR_ARG, "eb_fp8_mma_peak: blocks %d / reps %d",
+             blocks, reps);
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_fp8_mma_peak: no device");
+  static bool configured[64] = {false};
+  int dev = 0;
+  EB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    EB_CUDA(cudaFuncSetAttribute(fp8_mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPeakSmem));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int sms = sm_count_now();
+  cudaEvent_t e0, e1;
+  EB_CUDA(cudaEventCreate(&e0));
+  EB_CUDA(cudaEventCreate(&e1));
+  float best = 0.f;
+  cudaError_t err = cudaSuccess;
+  for (int r = 0; r <= reps && err == cudaSuccess; ++r) {  // repetition 0 is a warm-up
+    cudaEventRecord(e0, nullptr);
+    fp8_mma_peak_kernel<<<sms, 128, kPeakSmem>>>(blocks, status, eb::wait_tries());
+    cudaEventRecord(e1, nullptr);
+    err = cudaGetLastError();
+    if (err == cudaSuccess) err = cudaEventSynchronize(e1);
+    float ms = 0.f;
+    if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, e0, e1);
+    if (r >= 1 && (best == 0.f || ms < best)) best = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (err != cudaSuccess) return eb::fail((int32_t)err, "eb_fp8_mma_peak: %s", cudaGetErrorString(err));
+  if (best_ms) *best_ms = best;
+  if (tflops) *tflops = best > 0.f ? 2.0 * 128 * 256 * 128 * (double)blocks * sms / (best * 1e-3) / 1e12 : 0.0;
   return EB_OK;
 }
 

@@ -412,6 +412,9 @@ class Engine:
         call("eb_engine_last_step_copies", self._h, C.byref(a), C.byref(b))
         return int(a.value), int(b.value)
 
+    def profile(self, on: bool) -> None:
+        call("eb_engine_profile", self._h, c_i32(1 if on else 0))
+
     def last_step_breakdown(self) -> dict:
         ms = (c_f32 * 8)()
         call("eb_engine_last_step_breakdown", self._h, ms)

@@ -290,6 +290,11 @@ int32_t eb_gemm_workspace(int32_t rows, int32_t N, int32_t n_groups, size_t* byt
 /* Dense GEMM that leaves split-K partials for a fused consumer: when it chose splits_used > 1 the fp32 partials
  * [splits_used][rows][N] are in d_work and d_y is untouched; when splits_used == 1 d_y holds the bf16 result. */
 int32_t eb_gemm_fp8_block_partial(const eb_gemm_args* a, int32_t* splits_used, void* stream);
+/* Measured ceiling of the FP8 tensor path on the current device: one CTA per SM issues `blocks` groups of four
+ * tcgen05.mma.kind::f8f6f4 (128 x 256 x 32) back to back on operands resident in shared memory, no loads, no
+ * epilogue; best of `reps` timed launches after a warm-up.  tflops = 2 * 128 * 256 * 128 * blocks * SMs / time: the
+ * denominator "fraction of FP8 peak" is reported against (sample the SM clock beside it: the figure scales with it). */
+int32_t eb_fp8_mma_peak(int32_t blocks, int32_t reps, float* best_ms, double* tflops);
 /* Token-tile table of a grouped GEMM, built once and shared by GEMMs over the same segments (tiles_ready = 1). */
 int32_t eb_gemm_group_tiles(const int32_t* d_seg_off, int32_t n_groups, int32_t rows, int32_t tile_tokens, void* d_work,
                             void* stream);
@@ -456,6 +461,9 @@ int32_t eb_engine_last_step_stats(const eb_engine* e, float* device_ms, int32_t*
 /* Bytes the last step copied host -> device (the staging block: tokens, packing arrays, block-table patches, the two
  * attention plans) and device -> host (greedy tokens and margins). */
 int32_t eb_engine_last_step_copies(const eb_engine* e, int64_t* h2d_bytes, int64_t* d2h_bytes);
+/* Switch the per-call timing of debug bit 1 on or off between steps (the events add a millisecond or two to a step, so
+ * a benchmark times its steps with it off and takes the breakdown from a few extra steps with it on). */
+int32_t eb_engine_profile(eb_engine* e, int32_t on);
 /* debug bit 1: device milliseconds of the last step by category (8 floats): [0] attention on full layers, [1] attention
  * on windowed layers, [2] QKV and O projections, [3] expert GEMMs, [4] LM head, [5] collectives (tensor-parallel
  * engines), [6] router, [7] activation quantisers.  What is left of the step is norms, rotary/append, permutation,

@@ -46,6 +46,12 @@ def set_threads(n: int) -> int:
     return int(_lib.orc_set_threads(C.c_int(n)))
 
 
+def set_threads_pinned(n: int) -> int:
+    """Use n OpenMP threads and pin each worker (not the calling thread) to one allowed CPU; returns the number in effect."""
+    _lib.orc_set_threads_pinned.restype = C.c_int
+    return int(_lib.orc_set_threads_pinned(C.c_int(n)))
+
+
 # ---- formats / synthetic tensors
 
 def synth_normal_f32(seed, stream, idx0, n, scale=1.0) -> np.ndarray:
@@ -242,6 +248,33 @@ def argmax(logits):
 
 
 # ---- whole decoder
+
+class Config(C.Structure):
+    """eb_config as include/eidola_b200.h declares it, mirrored here so that the CPU checker (and a benchmark arm that
+    runs nothing but the checker) needs no part of the CUDA library's binding."""
+    _fields_ = [
+        ("n_layers", c_i32), ("hidden", c_i32), ("n_q_heads", c_i32), ("n_kv_heads", c_i32), ("head_dim", c_i32),
+        ("window", c_i32),
+        ("n_experts", c_i32), ("top_k", c_i32), ("inter", c_i32), ("vocab", c_i32),
+        ("page_size", c_i32), ("num_pages", c_i32), ("max_seqs", c_i32), ("max_pages_per_seq", c_i32),
+        ("max_tokens", c_i32), ("max_q_len", c_i32),
+        ("rope_theta", c_f32), ("rms_eps", c_f32), ("init_std", c_f32),
+        ("seed", c_u64),
+        ("debug", c_i32),
+        ("window_ring", c_i32),
+    ]
+
+
+def make_config(**kw) -> Config:
+    """The benchmark family's defaults (head_dim 64, page 16, window 128, top-4, std 0.02), as the engine's binding has them."""
+    d = dict(head_dim=64, window=128, top_k=4, page_size=16, max_q_len=1, rope_theta=150000.0, rms_eps=1e-5,
+             init_std=0.02, seed=0, debug=0, window_ring=0)
+    d.update(kw)
+    c = Config()
+    for k, v in d.items():
+        setattr(c, k, v)
+    return c
+
 
 class Model:
     """orc_model_*: the CPU decoder.  `cfg` is the ctypes eb_config the engine is created with."""

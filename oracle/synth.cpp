@@ -13,6 +13,8 @@
 #include <stddef.h>
 
 #include <omp.h>
+#include <pthread.h>
+#include <sched.h>
 
 #include "../include/eb_synth.h"
 
@@ -22,6 +24,33 @@ extern "C" {
 int orc_set_threads(int n) {
   if (n > 0) omp_set_num_threads(n);
   return omp_get_max_threads();
+}
+
+/* The same, and every worker thread but the calling one is pinned to one of the CPUs the process may run on (worker t
+ * to the t-th allowed CPU, round robin), so that repeated timings see the same placement.  The calling thread keeps
+ * its affinity: the host program's own scheduling is left alone.  Returns the number of threads. */
+int orc_set_threads_pinned(int n) {
+  cpu_set_t allowed;
+  CPU_ZERO(&allowed);
+  int cpus[1024], n_cpu = 0;
+  if (sched_getaffinity(0, sizeof(allowed), &allowed) == 0)
+    for (int c = 0; c < CPU_SETSIZE && n_cpu < 1024; ++c)
+      if (CPU_ISSET(c, &allowed)) cpus[n_cpu++] = c;
+  if (n > 0) omp_set_num_threads(n);
+  const int nt = omp_get_max_threads();
+  if (n_cpu > 0) {
+#pragma omp parallel num_threads(nt)
+    {
+      const int t = omp_get_thread_num();
+      if (t > 0) {
+        cpu_set_t one;
+        CPU_ZERO(&one);
+        CPU_SET(cpus[t % n_cpu], &one);
+        pthread_setaffinity_np(pthread_self(), sizeof(one), &one);
+      }
+    }
+  }
+  return nt;
 }
 
 /* out[i] = scale * N(0,1)(seed, stream, idx0 + i) */

@@ -37,3 +37,15 @@ def test_validation_happens_before_any_launch():
                       C.c_void_p(16), C.c_void_p(16), C.c_int64(512), C.c_void_p(16), C.c_int32(4), C.c_void_p(16),
                       C.c_void_p(16), C.c_int32(1), C.c_void_p())
     assert rc == -2 and "head_dim" in capi.last_error()
+
+
+def test_oracle_config_mirror_matches_the_engine_binding():
+    """The CPU checker declares eb_config on its own (so that it never imports the CUDA binding): same layout."""
+    import ctypes as C
+
+    from eidola_b200 import capi
+    from oracle import binding as orc
+    assert [(n, t) for n, t in capi.Config._fields_] == [(n, t) for n, t in orc.Config._fields_]
+    assert C.sizeof(capi.Config) == C.sizeof(orc.Config)
+    a, b = capi.make_config(n_layers=3, vocab=17), orc.make_config(n_layers=3, vocab=17)
+    assert bytes(a) == bytes(b)
