@@ -430,8 +430,9 @@ def make_comm(eb, rank, world, dist):
         return None
     # NCCL's own record of the communicator ("... rank r nranks N ...") goes to the log, so that a reader of the run
     # can check that N ranks really joined
-    os.environ.setdefault("NCCL_DEBUG", "INFO")
-    os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+    if os.environ.get("NCCL_DEBUG", "").upper() not in ("INFO", "TRACE"):
+        os.environ["NCCL_DEBUG"] = "INFO"
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
     uid = [eb.Comm.unique_id() if rank == 0 else None]
     dist.broadcast_object_list(uid, src=0)
     return eb.Comm(uid[0], rank, world)
@@ -477,12 +478,17 @@ def tp_parity_block(eb, rank, world, dist, comm):
     dl = np.abs(f(logits_tp[:, :v1]) - f(logits_1[:, :v1]))
     dh = f(hid_tp) - f(hid_1)
     clear = mg_1 > 0.2
+    same_route = np.ones(n, bool)
+    for l in range(layers):
+        same_route &= ~(route_tp[l] != route_1[l]).any(axis=1)
     return {"what": "first decode step of a 2-layer slice, %d sequences: tp%d x ep%d engine vs the single-GPU engine" % (n, world, world),
             "greedy_tokens_equal": int((nxt == ref).sum()), "of": n,
             "tokens_equal_where_margin_above_0.2": "%d/%d" % (int((nxt[clear] == ref[clear]).sum()), int(clear.sum())),
             "max_margin_of_a_differing_token": float(mg_1[nxt != ref].max()) if (nxt != ref).any() else 0.0,
             "routing_rows_differing_per_layer": [int((route_tp[l] != route_1[l]).any(axis=1).sum()) for l in range(layers)],
-            "max_abs_logit_diff_rank0_band": float(dl.max()), "mean_signed_logit_diff": float((f(logits_tp[:, :v1]) - f(logits_1[:, :v1])).mean()),
+            "max_abs_logit_diff_rank0_band": float(dl.max()),
+            "max_abs_logit_diff_rows_with_equal_routing": float(dl[same_route].max()) if same_route.any() else None,
+            "rms_logit_diff": float(np.sqrt((dl * dl).mean())), "mean_signed_logit_diff": float((f(logits_tp[:, :v1]) - f(logits_1[:, :v1])).mean()),
             "hidden_rel_l2": float(np.linalg.norm(dh) / np.linalg.norm(f(hid_1))),
             "margin_max_abs_diff": float(np.abs(mg_tp - mg_1).max())}
 
