@@ -50,7 +50,7 @@ class GemmArgs(C.Structure):
         ("d_x8", c_vp), ("d_sx", c_vp), ("d_w8", c_vp), ("d_sw", c_vp), ("d_y", c_vp), ("ldy", c_i64),
         ("rows", c_i32), ("N", c_i32), ("K", c_i32), ("n_groups", c_i32),
         ("d_seg_off", c_vp), ("d_work", c_vp), ("tile_tokens", c_i32), ("splits", c_i32), ("tiles_ready", c_i32),
-        ("work_bytes", c_sz),
+        ("work_bytes", c_sz), ("w_tiled", c_i32),
     ]
 
 

@@ -76,6 +76,7 @@ struct eb_engine {
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   std::vector<void*> allocs;
+  uint8_t* w_scratch = nullptr;  // row-major staging while the weights are generated
   int64_t weight_bytes = 0, kv_bytes = 0, work_bytes = 0;
 
   // step workspaces
@@ -140,8 +141,11 @@ int32_t dev_alloc(eb_engine* e, T** p, size_t count, int64_t* tally) {
   return EB_OK;
 }
 
+// Weights live in HBM as 16 KiB tiles (eb_weight_tile_fp8): a GEMM stage is then one contiguous read.
 int32_t alloc_fp8(eb_engine* e, Fp8Weight* w, int64_t groups, int64_t rows, int64_t cols) {
-  EB_TRY(dev_alloc(e, &w->codes, (size_t)(groups * rows * cols), &e->weight_bytes));
+  size_t tiled = 0;
+  EB_TRY(eb_weight_tiled_bytes((int32_t)groups, (int32_t)rows, (int32_t)cols, &tiled));
+  EB_TRY(dev_alloc(e, &w->codes, tiled, &e->weight_bytes));
   EB_TRY(dev_alloc(e, &w->scales, (size_t)(groups * eb::cdiv(rows, 128) * eb::cdiv(cols, 128)), &e->weight_bytes));
   return EB_OK;
 }
@@ -153,11 +157,33 @@ int32_t fill_ones(eb_engine* e, float* d, int n) {
   return EB_OK;
 }
 
+// Generate rows [src_row0, +nrows) of a seeded [rows_total x cols] weight (row-major, into the scratch buffer) and store
+// them as tiles at weight-row block dst_row0 / 128 of `w` (group `group` of a tensor whose groups have rows_per_group
+// rows).  Bands start on 128-row boundaries, so their tiles are whole and consecutive.
+int32_t synth_band_tiled(eb_engine* e, Fp8Weight* w, int64_t group, int64_t rows_per_group, int64_t dst_row0, float* scales_dst,
+                         int64_t rows_total, int64_t cols, int64_t src_row0, int64_t nrows, uint64_t stream_id) {
+  const eb_config& c = e->c;
+  const int64_t KB = eb::cdiv(cols, 128), NB = eb::cdiv(rows_per_group, 128);
+  const int64_t band = 65536;  // rows generated per pass: bounds the scratch buffer (an LM head has 200k rows)
+  for (int64_t r = 0; r < nrows; r += band) {
+    const int64_t n = std::min(band, nrows - r);
+    EB_TRY(eb_synth_weight_fp8(e->w_scratch, scales_dst + ((r) / 128) * KB, rows_total, cols, src_row0 + r, n, c.seed, stream_id,
+                               c.init_std, e->stream));
+    uint8_t* dst = w->codes + ((group * NB + (dst_row0 + r) / 128) * KB) * (int64_t)(128 * 128);
+    EB_TRY(eb_weight_tile_fp8(e->w_scratch, 1, (int32_t)n, (int32_t)cols, dst, e->stream));
+  }
+  return EB_OK;
+}
+
 int32_t init_weights(eb_engine* e) {
   const eb_config& c = e->c;
   const int H = c.hidden, I = c.inter, E = e->e_l;  // E: experts held by this rank
   void* st = e->stream;
   const int hqd_g = c.n_q_heads * c.head_dim, hkd_g = c.n_kv_heads * c.head_dim, nqkv_g = hqd_g + 2 * hkd_g;
+  {  // row-major staging for one band of one weight tensor; released when the weights are in place
+    const int64_t widest = std::max<int64_t>(std::max(H, I), e->hqd);
+    EB_CUDA(cudaMalloc((void**)&e->w_scratch, (size_t)(65536 * widest)));
+  }
   const int kv_row0 = (e->tp_rank * e->hkv_l * c.head_dim) / 128 * 128;  // start of this rank's K (and V) band
   for (int l = 0; l < c.n_layers; ++l) {
     Layer& L = e->layers[(size_t)l];
@@ -174,18 +200,17 @@ int32_t init_weights(eb_engine* e) {
     const int64_t band_src[3] = {(int64_t)e->tp_rank * e->hqd, hqd_g + kv_row0, hqd_g + hkd_g + kv_row0};
     int64_t dst_row = 0;
     for (int b = 0; b < 3; ++b) {
-      EB_TRY(eb_synth_weight_fp8(L.wqkv.codes + dst_row * H, L.wqkv.scales + (dst_row / 128) * e->kbH, nqkv_g, H, band_src[b],
-                                 band_rows[b], c.seed, sid(l, K_WQKV, 0), c.init_std, st));
+      EB_TRY(synth_band_tiled(e, &L.wqkv, 0, e->nqkv, dst_row, L.wqkv.scales + (dst_row / 128) * e->kbH, nqkv_g, H, band_src[b],
+                              band_rows[b], sid(l, K_WQKV, 0)));
       dst_row += band_rows[b];
     }
-    EB_TRY(eb_synth_weight_fp8_slice(L.wo.codes, L.wo.scales, H, hqd_g, 0, H, (int64_t)e->tp_rank * e->hqd, e->hqd, c.seed,
+    EB_TRY(eb_synth_weight_fp8_slice(e->w_scratch, L.wo.scales, H, hqd_g, 0, H, (int64_t)e->tp_rank * e->hqd, e->hqd, c.seed,
                                      sid(l, K_WO, 0), c.init_std, st));
+    EB_TRY(eb_weight_tile_fp8(e->w_scratch, 1, H, e->hqd, L.wo.codes, st));
     const int64_t s1 = eb::cdiv(2 * I, 128) * e->kbH, s2 = eb::cdiv(H, 128) * e->kbI;
     for (int x = 0; x < E; ++x) {
-      EB_TRY(eb_synth_weight_fp8(L.w1.codes + (int64_t)x * 2 * I * H, L.w1.scales + x * s1, 2 * I, H, 0, 2 * I, c.seed,
-                                 sid(l, K_W1, e->e0 + x), c.init_std, st));
-      EB_TRY(eb_synth_weight_fp8(L.w2.codes + (int64_t)x * H * I, L.w2.scales + x * s2, H, I, 0, H, c.seed,
-                                 sid(l, K_W2, e->e0 + x), c.init_std, st));
+      EB_TRY(synth_band_tiled(e, &L.w1, x, 2 * I, 0, L.w1.scales + x * s1, 2 * I, H, 0, 2 * I, sid(l, K_W1, e->e0 + x)));
+      EB_TRY(synth_band_tiled(e, &L.w2, x, H, 0, L.w2.scales + x * s2, H, I, 0, H, sid(l, K_W2, e->e0 + x)));
     }
     EB_TRY(eb_synth_normal_bf16(L.wr, (int64_t)c.n_experts * H, c.seed, sid(l, K_ROUTER, 0), 0, c.init_std, st));
     EB_TRY(eb_synth_normal_f32(L.sinks, c.n_q_heads, c.seed, sid(l, K_SINK, 0), 0, 1.0f, st));
@@ -195,8 +220,7 @@ int32_t init_weights(eb_engine* e) {
   EB_TRY(dev_alloc(e, &e->embed, (size_t)c.vocab * H, &e->weight_bytes));
   EB_TRY(eb_synth_normal_bf16(e->embed, (int64_t)c.vocab * H, c.seed, sid(-1, K_EMBED, 0), 0, c.init_std, st));
   EB_TRY(alloc_fp8(e, &e->lm, 1, e->v1 - e->v0, H));
-  EB_TRY(eb_synth_weight_fp8(e->lm.codes, e->lm.scales, c.vocab, H, e->v0, e->v1 - e->v0, c.seed, sid(-1, K_LMHEAD, 0), c.init_std,
-                             st));
+  EB_TRY(synth_band_tiled(e, &e->lm, 0, e->v1 - e->v0, 0, e->lm.scales, c.vocab, H, e->v0, e->v1 - e->v0, sid(-1, K_LMHEAD, 0)));
   EB_TRY(dev_alloc(e, &e->g_final, (size_t)H, &e->weight_bytes));
   EB_TRY(fill_ones(e, e->g_final, H));
   // rotary table
@@ -209,6 +233,8 @@ int32_t init_weights(eb_engine* e) {
   EB_CUDA(cudaMemcpyAsync(e->rope_cos, hc.data(), n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
   EB_CUDA(cudaMemcpyAsync(e->rope_sin, hs.data(), n * sizeof(float), cudaMemcpyHostToDevice, e->stream));
   EB_CUDA(cudaStreamSynchronize(e->stream));
+  cudaFree(e->w_scratch);
+  e->w_scratch = nullptr;
   return EB_OK;
 }
 
@@ -356,6 +382,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     g.N = N;
     g.K = K;
     g.n_groups = 1;
+    g.w_tiled = 1;
     g.d_work = (T <= 512 && N <= std::max(e->nqkv, H)) ? e->gemm_ws : nullptr;
     g.work_bytes = g.d_work ? e->gemm_ws_bytes : 0;
     n += 1;
@@ -380,6 +407,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     g.work_bytes = e->group_ws_bytes;
     g.tile_tokens = group_tn;
     g.tiles_ready = 1;
+    g.w_tiled = 1;
     n += 1;
     return eb_gemm_fp8_grouped(&g, st);
   };
@@ -699,6 +727,7 @@ int32_t eb_engine_destroy(eb_engine* e) {
   if (!e) return EB_OK;
   if (e->stream) cudaStreamSynchronize(e->stream);
   for (void* p : e->allocs) cudaFree(p);
+  if (e->w_scratch) cudaFree(e->w_scratch);
   for (cudaEvent_t ev : e->prof_ev) cudaEventDestroy(ev);
   if (e->h_stage) cudaFreeHost(e->h_stage);
   if (e->h_result) cudaFreeHost(e->h_result);

@@ -46,6 +46,7 @@ struct GemmParams {
   const int32_t* n_tiles;     // grouped: device scalar
   int32_t* status;
   uint32_t wait_tries;  // polls a bounded wait makes before it gives up (eb_wait_limit_set)
+  int32_t w_tiled;      // weights are stored as contiguous 16 KiB tiles (eb_weight_tile_fp8), not row-major
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -87,6 +88,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+
+// One pipeline stage of weights: 128 weight rows x one 128-byte K block of group g, weight-row block nb, K block kb.
+// Row-major weights [groups][N][K]: a box of 128 rows, 2880 bytes apart in HBM.  Tiled weights
+// [groups][ceil(N/128)][ceil(K/128)][128 rows][128 bytes] (eb_weight_tile_fp8): the same box is 16 KiB of consecutive
+// bytes, which HBM serves at its streaming rate instead of 128 separate 128-byte bursts.
+__device__ __forceinline__ void load_w_tile(uint32_t dst, const CUtensorMap* map, const GemmParams& p, int g, int nb, int kb,
+                                            uint32_t bar) {
+  if (p.w_tiled) {
+    const int NBw = (p.N + kTileN - 1) / kTileN, KBw = (p.K + kBlockK - 1) / kBlockK;
+    tma_load_2d(dst, map, 0, ((g * NBw + nb) * KBw + kb) * kTileN, bar);
+  } else {
+    tma_load_2d(dst, map, kb * kBlockK, g * p.N + nb * kTileN, bar);
+  }
 }
 
 // ---- tcgen05 wrappers
@@ -191,7 +206,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       prefilled = min(S, nkb);
       for (int i = 0; i < prefilled; ++i) {
         mbar_arrive_expect_tx(bar_full + 8 * i, C::kStageBytes);
-        tma_load_2d(stage0 + i * C::kStageBytes, &tm_w, (kb0 + i) * kBlockK, n0, bar_full + 8 * i);
+        load_w_tile(stage0 + i * C::kStageBytes, &tm_w, p, 0, nb, kb0 + i, bar_full + 8 * i);
       }
     }
   }
@@ -215,7 +230,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     row_end = p.rows;
     xblk = row0 / 128;
   }
-  const int wy = g * p.N + n0;
   if (tid == 0) {
     // Fill the pipeline before the rest of the CTA has finished setting up (scale products, the set-up barrier):
     // the first stages are in flight one barrier round trip earlier.
@@ -223,7 +237,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
       prefilled = min(S, nkb);
       for (int i = 0; i < prefilled; ++i) {
         mbar_arrive_expect_tx(bar_full + 8 * i, C::kStageBytes);
-        tma_load_2d(stage0 + i * C::kStageBytes, &tm_w, (kb0 + i) * kBlockK, wy, bar_full + 8 * i);
+        load_w_tile(stage0 + i * C::kStageBytes, &tm_w, p, g, nb, kb0 + i, bar_full + 8 * i);
       }
     }
     for (int i = 0; i < prefilled; ++i)
@@ -246,7 +260,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         if (i >= S && !mbar_wait(bar_empty + 8 * s, ((i / S) - 1) & 1, &abort_flag, p.status, p.wait_tries)) break;
         const uint32_t a_dst = stage0 + s * C::kStageBytes, b_dst = a_dst + kTileN * kBlockK;
         mbar_arrive_expect_tx(bar_full + 8 * s, C::kStageBytes);
-        tma_load_2d(a_dst, &tm_w, (kb0 + i) * kBlockK, wy, bar_full + 8 * s);
+        load_w_tile(a_dst, &tm_w, p, g, nb, kb0 + i, bar_full + 8 * s);
         tma_load_2d(b_dst, &tm_x, (kb0 + i) * kBlockK, row0, bar_full + 8 * s);
       }
     }
@@ -406,7 +420,6 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
       bool ok = true;
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
         const TileInfo t = decode_tile(p, w, TT, NB, KB, TN);
-        const int wy = t.g * p.N + t.n0;
         for (int i = 0; i < t.nkb; ++i, ++it) {
           const uint32_t s = it % S;
           if (it >= (uint32_t)S && !mbar_wait(bar_empty + 8 * s, ((it / S) - 1) & 1, &abort_flag, p.status, p.wait_tries)) {
@@ -415,7 +428,7 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
           }
           const uint32_t a_dst = stage0 + s * C::kStageBytes, b_dst = a_dst + kTileN * kBlockK;
           mbar_arrive_expect_tx(bar_full + 8 * s, C::kStageBytes);
-          tma_load_2d(a_dst, &tm_w, (t.kb0 + i) * kBlockK, wy, bar_full + 8 * s);
+          load_w_tile(a_dst, &tm_w, p, t.g, t.nb, t.kb0 + i, bar_full + 8 * s);
           tma_load_2d(b_dst, &tm_x, (t.kb0 + i) * kBlockK, t.row0, bar_full + 8 * s);
         }
       }
@@ -604,7 +617,12 @@ gemm_fp8_big_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const uint32_t a_dst = stage0 + s * kBigStageBytes, b_dst = a_dst + kBigTokens * kBlockK;
           mbar_arrive_expect_tx(bar_full + 8 * s, kBigStageBytes);
           tma_load_2d(a_dst, &tm_x, i * kBlockK, row0, bar_full + 8 * s);
-          tma_load_2d(b_dst, &tm_w, i * kBlockK, n0, bar_full + 8 * s);
+          if (p.w_tiled) {  // 256 weight rows = two 16 KiB tiles (a block beyond the last one is filled with zeros)
+            load_w_tile(b_dst, &tm_w, p, 0, n0 / kTileN, i, bar_full + 8 * s);
+            load_w_tile(b_dst + kTileN * kBlockK, &tm_w, p, 0, n0 / kTileN + 1, i, bar_full + 8 * s);
+          } else {
+            tma_load_2d(b_dst, &tm_w, i * kBlockK, n0, bar_full + 8 * s);
+          }
         }
       }
     } else if (warp == 1 && lane == 0) {
@@ -763,6 +781,25 @@ __global__ void __launch_bounds__(128, 1) fp8_mma_peak_kernel(int blocks, int32_
   __syncthreads();
   tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// Row-major e4m3 weights [groups][N][K] -> tiles [groups][ceil(N/128)][ceil(K/128)][128][128], zero padded.
+// One CTA per tile, 256 threads x four 16-byte chunks.
+__global__ void __launch_bounds__(256) weight_tile_kernel(const uint8_t* src, uint8_t* dst, int N, int K) {
+  const int KBw = (K + kBlockK - 1) / kBlockK, NBw = (N + kTileN - 1) / kTileN;
+  const int64_t tile = blockIdx.x;
+  const int kb = (int)(tile % KBw), nb = (int)((tile / KBw) % NBw);
+  const int64_t g = tile / ((int64_t)KBw * NBw);
+  uint4* out = reinterpret_cast<uint4*>(dst + tile * (kTileN * kBlockK));
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int ch = threadIdx.x + 256 * q;  // chunk of the tile: row ch / 8, bytes [16 * (ch % 8), +16)
+    const int r = ch >> 3, c = (ch & 7) * 16;
+    const int n = nb * kTileN + r, k = kb * kBlockK + c;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (n < N && k < K) v = *reinterpret_cast<const uint4*>(src + (g * N + n) * (int64_t)K + k);  // K is a multiple of 16
+    out[ch] = v;
+  }
 }
 
 // Sum split-K partials in split order and round to bf16.
@@ -1034,6 +1071,10 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
   p.status = status;
   p.wait_tries = eb::wait_tries();
   p.splits = 1;
+  p.w_tiled = a->w_tiled ? 1 : 0;
+  // tiled weights: rows of the tensor map are the 128-byte rows of all tiles, one after the other
+  const uint64_t tiled_rows = (uint64_t)a->n_groups * ((a->N + kTileN - 1) / kTileN) * ((a->K + kBlockK - 1) / kBlockK) * kTileN;
+  EB_REQUIRE(!a->w_tiled || tiled_rows < (1ull << 31), EB_ERR_UNSUPPORTED, "gemm: tiled weights exceed a tensor map");
 
   const int KB = (a->K + kBlockK - 1) / kBlockK;
   const int nb = (a->N + kTileN - 1) / kTileN;
@@ -1091,8 +1132,9 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
 
   if (!grouped && gemm_big(a->rows, a->N, a->tile_tokens, a->splits)) {
     CUtensorMap bw, bx;
-    int32_t brc = eb::make_tmap_2d_sw128(&bw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, (uint64_t)a->N, (uint64_t)a->K,
-                                         (uint64_t)a->K, kBigRows);
+    int32_t brc = a->w_tiled ? eb::make_tmap_2d_sw128(&bw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, tiled_rows, kBlockK, kBlockK, kTileN)
+                             : eb::make_tmap_2d_sw128(&bw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, (uint64_t)a->N, (uint64_t)a->K,
+                                                      (uint64_t)a->K, kBigRows);
     if (brc != EB_OK) return brc;
     brc = eb::make_tmap_2d_sw128(&bx, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_x8, (uint64_t)a->rows, (uint64_t)a->K, (uint64_t)a->K,
                                  kBigTokens);
@@ -1113,8 +1155,9 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
   }
 
   CUtensorMap tw, tx;
-  int32_t rc = eb::make_tmap_2d_sw128(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, (uint64_t)a->n_groups * a->N,
-                                      (uint64_t)a->K, (uint64_t)a->K, kTileN);
+  int32_t rc = a->w_tiled ? eb::make_tmap_2d_sw128(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, tiled_rows, kBlockK, kBlockK, kTileN)
+                          : eb::make_tmap_2d_sw128(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_w8, (uint64_t)a->n_groups * a->N,
+                                                   (uint64_t)a->K, (uint64_t)a->K, kTileN);
   if (rc != EB_OK) return rc;
   rc = eb::make_tmap_2d_sw128(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->d_x8, (uint64_t)a->rows, (uint64_t)a->K,
                               (uint64_t)a->K, (uint32_t)tn);
@@ -1233,6 +1276,23 @@ int32_t eb_fp8_mma_peak(int32_t blocks, int32_t reps, float* best_ms, double* tf
   if (err != cudaSuccess) return eb::fail((int32_t)err, "eb_fp8_mma_peak: %s", cudaGetErrorString(err));
   if (best_ms) *best_ms = best;
   if (tflops) *tflops = best > 0.f ? 2.0 * 128 * 256 * 128 * (double)blocks * sms / (best * 1e-3) / 1e12 : 0.0;
+  return EB_OK;
+}
+
+int32_t eb_weight_tiled_bytes(int32_t n_groups, int32_t N, int32_t K, size_t* bytes) {
+  EB_REQUIRE(bytes && n_groups >= 1 && N >= 1 && K >= 16, EB_ERR_ARG, "eb_weight_tiled_bytes: bad argument");
+  *bytes = (size_t)n_groups * ((N + kTileN - 1) / kTileN) * ((K + kBlockK - 1) / kBlockK) * (kTileN * kBlockK);
+  return EB_OK;
+}
+
+int32_t eb_weight_tile_fp8(const void* d_w8, int32_t n_groups, int32_t N, int32_t K, void* d_tiled, void* stream) {
+  EB_REQUIRE(d_w8 && d_tiled, EB_ERR_ARG, "eb_weight_tile_fp8: null pointer");
+  EB_REQUIRE(n_groups >= 1 && N >= 1 && K >= 16 && K % 16 == 0, EB_ERR_ARG, "eb_weight_tile_fp8: bad size (K a multiple of 16)");
+  EB_REQUIRE(((uintptr_t)d_w8 % 16 == 0) && ((uintptr_t)d_tiled % 16 == 0), EB_ERR_ARG, "eb_weight_tile_fp8: 16-byte alignment");
+  const int64_t tiles = (int64_t)n_groups * ((N + kTileN - 1) / kTileN) * ((K + kBlockK - 1) / kBlockK);
+  EB_REQUIRE(tiles < (1ll << 31), EB_ERR_UNSUPPORTED, "eb_weight_tile_fp8: too many tiles");
+  weight_tile_kernel<<<(unsigned)tiles, 256, 0, eb::as_stream(stream)>>>((const uint8_t*)d_w8, (uint8_t*)d_tiled, N, K);
+  EB_LAUNCH_CHECK();
   return EB_OK;
 }
 

@@ -162,7 +162,7 @@ def gemm_workspace(rows, N, n_groups) -> int:
 
 
 def gemm_fp8(d_x8, d_sx, d_w8, d_sw, d_y, rows, N, K, *, ldy=None, n_groups=1, d_seg_off=None, work=None,
-             tile_tokens=0, splits=0, stream=None) -> None:
+             tile_tokens=0, splits=0, stream=None, w_tiled=False) -> None:
     """eb_gemm_fp8_block (n_groups == 1, no segments) or eb_gemm_fp8_grouped.  `work` is the DeviceBuffer lent as
     workspace (its size travels with the call, the library refuses what would not fit)."""
     d_work, work_bytes = (work.ptr, work.nbytes) if work is not None else (None, 0)
@@ -172,7 +172,17 @@ def gemm_fp8(d_x8, d_sx, d_w8, d_sw, d_y, rows, N, K, *, ldy=None, n_groups=1, d
     a.rows, a.N, a.K, a.n_groups = rows, N, K, n_groups
     a.d_seg_off, a.d_work, a.tile_tokens, a.splits = d_seg_off, d_work, tile_tokens, splits
     a.work_bytes = work_bytes
+    a.w_tiled = 1 if w_tiled else 0
     call("eb_gemm_fp8_grouped" if d_seg_off is not None else "eb_gemm_fp8_block", C.byref(a), c_vp(stream))
+
+
+def weight_tile_fp8(d_w8, n_groups, N, K, stream=None) -> DeviceBuffer:
+    """eb_weight_tile_fp8: a new device buffer holding the 16 KiB-tile layout of row-major e4m3 weights."""
+    b = c_sz(0)
+    call("eb_weight_tiled_bytes", c_i32(n_groups), c_i32(N), c_i32(K), C.byref(b))
+    out = DeviceBuffer(int(b.value))
+    call("eb_weight_tile_fp8", c_vp(d_w8), c_i32(n_groups), c_i32(N), c_i32(K), c_vp(out.ptr), c_vp(stream))
+    return out
 
 
 class Comm:

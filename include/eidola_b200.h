@@ -44,7 +44,7 @@
 extern "C" {
 #endif
 
-#define EB_ABI_VERSION 4
+#define EB_ABI_VERSION 5
 
 /* status codes (negative: host validation) */
 #define EB_OK 0
@@ -277,8 +277,17 @@ typedef struct eb_gemm_args {
   int32_t tiles_ready;        /* grouped: 1 = d_work already holds eb_gemm_group_tiles() output for these segments */
   size_t work_bytes;          /* bytes the caller owns at d_work; a call that would need more is refused (explicit
                                  splits, grouped) or falls back to fewer K splits (splits = 0) */
+  int32_t w_tiled;            /* 0: d_w8 is row-major [n_groups][N][K]; 1: d_w8 holds the 16 KiB tiles eb_weight_tile_fp8
+                                 writes (same results bit for bit; HBM serves a tile as one contiguous read) */
 } eb_gemm_args;
 
+/* Weight layout for streaming.  A GEMM stage is 128 weight rows x 128 bytes of K; in a row-major matrix those are 128
+ * separate 128-byte reads 1 K apart.  eb_weight_tile_fp8 rewrites [n_groups][N][K] e4m3 codes as
+ * [n_groups][ceil(N/128)][ceil(K/128)][128 rows][128 bytes] (zero padded), so a stage is 16 KiB of consecutive bytes;
+ * pass the result with w_tiled = 1.  Done once per weight tensor, e.g. when a checkpoint is loaded.  The block scales
+ * keep their layout.  eb_weight_tiled_bytes gives the size of the tiled buffer. */
+int32_t eb_weight_tiled_bytes(int32_t n_groups, int32_t N, int32_t K, size_t* bytes);
+int32_t eb_weight_tile_fp8(const void* d_w8, int32_t n_groups, int32_t N, int32_t K, void* d_tiled, void* stream);
 /* K4.  Y = X * W^T, e4m3 x e4m3 -> fp32 with per-128x128 block scales, bf16 out (tcgen05 tensor cores).
  * The weights (d_w8, d_sw) must be complete when the call is made: the kernel may fetch them before the work queued
  * ahead of it on the stream has finished (activations and scales of X are read only after it has). */

@@ -15,7 +15,7 @@ def test_header_symbols_are_exported():
 def test_version_and_error_text():
     v = C.c_int32(0)
     capi.call("eb_version", C.byref(v))
-    assert v.value == 4
+    assert v.value == 5
     rc = capi.call_rc("eb_sched_create", C.c_int32(0), C.c_int32(16), C.c_int32(1), C.c_int32(1), C.c_uint64(0),
                       C.byref(C.c_void_p()))
     assert rc == -1

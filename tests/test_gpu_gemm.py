@@ -185,3 +185,60 @@ def test_gemm_prefill_sized_power_of_two_scales_exact(gpu):
     d_y = DeviceBuffer(M * N * 2)
     host.gemm_fp8(d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, d_y.ptr, M, N, K)
     assert np.array_equal(d_y.to_array(np.uint16, (M, N)), want)
+
+
+def test_weight_tiling_layout_bit_exact(gpu):
+    """eb_weight_tile_fp8 against a numpy restatement: [groups][N][K] -> [groups][ceil(N/128)][ceil(K/128)][128][128],
+    zero padded, ragged N and K."""
+    import eidola_b200.host as host
+    G, N, K = 3, 200, 2880
+    w = np.random.default_rng(7).integers(0, 256, size=(G, N, K)).astype(np.uint8)
+    NB, KB = (N + 127) // 128, (K + 127) // 128
+    pad = np.zeros((G, NB * 128, KB * 128), np.uint8)
+    pad[:, :N, :K] = w
+    want = pad.reshape(G, NB, 128, KB, 128).transpose(0, 1, 3, 2, 4)
+    d_w = _dev(w)
+    tiled = host.weight_tile_fp8(d_w.ptr, G, N, K)
+    assert tiled.nbytes == want.size
+    assert np.array_equal(tiled.to_array(np.uint8, want.shape), want)
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 5120, 2880), (256, 2880, 4096), (300, 65536, 256), (1024, 2880, 2880), (513, 200, 4096)])
+def test_gemm_dense_tiled_weights_equal_row_major(gpu, M, N, K):
+    """The same GEMM on weights stored as 16 KiB tiles: every kernel (decode tiles, split K, persistent, the 128-token x
+    256-row kernel, ragged N) must give the row-major result bit for bit -- only the addresses of the loads differ."""
+    import eidola_b200.host as host
+    from eidola_b200.capi import DeviceBuffer
+    x8, sx, w8, sw = _sweep_inputs(M, N, K, seed=8)
+    d = [_dev(a) for a in (x8, sx, w8, sw)]
+    tiled = host.weight_tile_fp8(d[2].ptr, 1, N, K)
+    d_work = DeviceBuffer(host.gemm_workspace(M, N, 1))
+    for splits, tn in ((0, 0), (1, 0), (1, 16)) if M <= 512 else ((0, 0),):
+        ya, yb = DeviceBuffer(M * N * 2), DeviceBuffer(M * N * 2)
+        host.gemm_fp8(d[0].ptr, d[1].ptr, d[2].ptr, d[3].ptr, ya.ptr, M, N, K, work=d_work, splits=splits, tile_tokens=tn)
+        host.gemm_fp8(d[0].ptr, d[1].ptr, tiled.ptr, d[3].ptr, yb.ptr, M, N, K, work=d_work, splits=splits, tile_tokens=tn,
+                      w_tiled=True)
+        assert np.array_equal(ya.to_array(np.uint16, (M, N)), yb.to_array(np.uint16, (M, N))), (splits, tn)
+
+
+@pytest.mark.parametrize("tn", [0, 64])
+def test_gemm_grouped_tiled_weights_equal_row_major(gpu, tn):
+    import eidola_b200.host as host
+    from eidola_b200.capi import DeviceBuffer
+    G, N, K = 6, 2880, 2880  # N = 22.5 blocks: every group's last weight tile is half padding
+    seg = np.array([0, 5, 5, 140, 141, 400, 437], np.int32)
+    R = int(seg[-1])
+    x = orc.synth_normal_bf16(5, 1, 0, R * K).reshape(R, K)
+    x8, sx = orc.quant_act_block128(x, seg)
+    w = [orc.synth_weight_fp8(5, 10 + g, N, K, 0, N, 0.02) for g in range(G)]
+    w8, sw = np.stack([a for a, _ in w]), np.stack([b for _, b in w])
+    d_x8, d_sx, d_seg, d_w8, d_sw = _dev(x8), _dev(sx), _dev(seg), _dev(w8), _dev(sw)
+    tiled = host.weight_tile_fp8(d_w8.ptr, G, N, K)
+    d_work = DeviceBuffer(host.gemm_workspace(R, N, G))
+    ya, yb = DeviceBuffer(R * N * 2), DeviceBuffer(R * N * 2)
+    host.gemm_fp8(d_x8.ptr, d_sx.ptr, d_w8.ptr, d_sw.ptr, ya.ptr, R, N, K, n_groups=G, d_seg_off=d_seg.ptr, work=d_work, tile_tokens=tn)
+    host.gemm_fp8(d_x8.ptr, d_sx.ptr, tiled.ptr, d_sw.ptr, yb.ptr, R, N, K, n_groups=G, d_seg_off=d_seg.ptr, work=d_work, tile_tokens=tn,
+                  w_tiled=True)
+    got = yb.to_array(np.uint16, (R, N))
+    assert np.array_equal(ya.to_array(np.uint16, (R, N)), got)
+    assert_close_bf16(got, orc.gemm_fp8_grouped(x8, sx, seg, w8, sw), atol=1e-3, rtol=G_RTOL, what=f"grouped tiled tn={tn}")
