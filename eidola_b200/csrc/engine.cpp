@@ -12,6 +12,7 @@
 //
 // What would sit above this in the reference: the loopback HTTP client of a local engine
 // (crates/eidola-app-core/src/lib.rs:7155-7163) or a `ChatBackend` (crates/eidola-server/src/backend.rs:87-108).
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -60,6 +61,11 @@ struct eb_engine {
   float* cand = nullptr;   // argmax candidates of every rank's vocabulary slice: [tp_size][max_tokens][4]
   int kv_band = 0, k_col0 = 0, v_col0 = 0;  // the K and V bands of the local QKV row start on 128-row scale blocks
   float* ar_buf = nullptr;                   // fp32 [max_tokens][hidden] summed across ranks
+  // peer-memory collectives (tensor parallel): the buffers that cross ranks live in one symmetric arena
+  eb_symm* symm = nullptr;
+  uint8_t* arena = nullptr;                  // this rank's arena
+  size_t arena_used = 0;
+  uint8_t* planes = nullptr;                 // [tp_size][chunk rows][hidden] fp32 or bf16: the ranks' partial rows of my slice
   int32_t* r_idx_local = nullptr;
   float* sinks_all = nullptr;
   int nqkv = 0, hqd = 0, kbH = 0, kbI = 0, kbA = 0;
@@ -245,32 +251,64 @@ int32_t init_work(eb_engine* e) {
   int64_t* w = &e->work_bytes;
   // under tensor parallelism rows are dealt to ranks in tp_size equal chunks for the in-place collectives: slack rows
   const size_t Tc = (size_t)T + (e->tp_size > 1 ? (size_t)e->tp_size * 128 : 0);  // slices are whole 128-row scale blocks
-  EB_TRY(dev_alloc(e, &e->x, Tc * H, w));
-  EB_TRY(dev_alloc(e, &e->h, Tc * H, w));
+  const int64_t tb0 = eb::cdiv((int64_t)Tc, 128);
+  const size_t r_cap0 = (size_t)R + (e->tp_size > 1 ? (size_t)e->tp_size * 128 * c.top_k : 0);
+  const bool want_symm = e->tp_size > 1 && !(getenv("EIDOLA_B200_TP_NCCL") && getenv("EIDOLA_B200_TP_NCCL")[0] == '1');
+  if (want_symm) {
+    // everything another rank writes into, or that is pushed from, sits in the arena
+    auto a256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    const size_t sz_rows2 = a256(Tc * H * 2), sz_rows1 = a256(Tc * H), sz_rows4 = a256(Tc * H * 4);
+    const size_t sz_sh = a256((size_t)(tb0 * e->kbH) * 4), sz_r = a256(r_cap0 * 4), sz_cand = a256((size_t)e->tp_size * T * 4 * 4);
+    const size_t total = 3 * sz_rows2 + sz_rows1 + 2 * sz_rows4 + sz_sh + 2 * sz_r + sz_cand;
+    EB_TRY(eb_symm_create(e->comm, total, &e->symm));
+    void* base = nullptr;
+    EB_TRY(eb_symm_ptr(e->symm, e->tp_rank, &base, nullptr));
+    e->arena = (uint8_t*)base;
+    size_t o = 0;
+    auto carve = [&](size_t bytes) {
+      uint8_t* p = e->arena + o;
+      o += bytes;
+      return p;
+    };
+    e->x = (uint16_t*)carve(sz_rows2);
+    e->h = (uint16_t*)carve(sz_rows2);
+    e->o = (uint16_t*)carve(sz_rows2);
+    e->h8 = carve(sz_rows1);
+    e->ar_buf = (float*)carve(sz_rows4);
+    e->planes = carve(sz_rows4);
+    e->sh = (float*)carve(sz_sh);
+    e->r_idx = (int32_t*)carve(sz_r);
+    e->r_wts = (float*)carve(sz_r);
+    e->cand = (float*)carve(sz_cand);
+    e->arena_used = o;
+    *w += (int64_t)total;
+  }
+  if (!e->x) EB_TRY(dev_alloc(e, &e->x, Tc * H, w));
+  if (!e->h) EB_TRY(dev_alloc(e, &e->h, Tc * H, w));
   EB_TRY(dev_alloc(e, &e->qkv, (size_t)T * e->nqkv, w));
   EB_TRY(dev_alloc(e, &e->attn, (size_t)T * e->hqd, w));
-  EB_TRY(dev_alloc(e, &e->o, Tc * H, w));  // also the bf16 operand of the tensor-parallel reduce-scatters
+  if (!e->o) EB_TRY(dev_alloc(e, &e->o, Tc * H, w));  // also the bf16 operand of the tensor-parallel reduce-scatters
   EB_TRY(dev_alloc(e, &e->gu, (size_t)R * 2 * I, w));
   EB_TRY(dev_alloc(e, &e->y, (size_t)R * H, w));
   EB_TRY(dev_alloc(e, &e->logits, (size_t)T * c.vocab, w));
-  EB_TRY(dev_alloc(e, &e->h8, Tc * H, w));
+  if (!e->h8) EB_TRY(dev_alloc(e, &e->h8, Tc * H, w));
   EB_TRY(dev_alloc(e, &e->a8, (size_t)T * e->hqd, w));
   EB_TRY(dev_alloc(e, &e->xp8, (size_t)R * H, w));
   EB_TRY(dev_alloc(e, &e->act8, (size_t)R * I, w));
   const int64_t tb = eb::cdiv((int64_t)Tc, 128), rb = R / 128 + E;
-  EB_TRY(dev_alloc(e, &e->sh, (size_t)(tb * e->kbH), w));
+  if (!e->sh) EB_TRY(dev_alloc(e, &e->sh, (size_t)(tb * e->kbH), w));
   EB_TRY(dev_alloc(e, &e->sa, (size_t)(tb * e->kbA), w));
   EB_TRY(dev_alloc(e, &e->sxp, (size_t)(rb * e->kbH), w));
   EB_TRY(dev_alloc(e, &e->sact, (size_t)(rb * e->kbI), w));
   // routing is computed on a token slice per rank and all-gathered in place: room for tp_size equal chunks
   const size_t r_cap = (size_t)R + (e->tp_size > 1 ? (size_t)e->tp_size * 128 * c.top_k : 0);
-  EB_TRY(dev_alloc(e, &e->r_idx, r_cap, w));
+  if (!e->r_idx) EB_TRY(dev_alloc(e, &e->r_idx, r_cap, w));
   EB_TRY(dev_alloc(e, &e->r_idx_local, (size_t)R, w));
-  if (e->tp_size > 1) {
+  if (e->tp_size > 1 && !e->symm) {
     EB_TRY(dev_alloc(e, &e->ar_buf, Tc * H, w));
     EB_TRY(dev_alloc(e, &e->cand, (size_t)e->tp_size * T * 4, w));
   }
-  EB_TRY(dev_alloc(e, &e->r_wts, r_cap, w));
+  if (!e->r_wts) EB_TRY(dev_alloc(e, &e->r_wts, r_cap, w));
   EB_TRY(dev_alloc(e, &e->seg_off, (size_t)E + 1, w));
   EB_TRY(dev_alloc(e, &e->perm_row, (size_t)R, w));
   EB_TRY(dev_alloc(e, &e->row_token, (size_t)R, w));
@@ -354,6 +392,35 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   const int max_pos = c.max_pages_per_seq * c.page_size;
   int& n = e->launches;
   n = 0;
+  // ---- collectives over the symmetric arena (peer stores + flags) when the engine has one, NCCL otherwise
+  const bool symm = e->symm != nullptr;
+  bool first_exchange = true;
+  auto aoff = [&](const void* p) { return (int64_t)((const uint8_t*)p - e->arena); };
+  // in-place all-gather of buffers whose per-rank slices are per_rank[i] bytes apart; this rank's slice holds valid[i] bytes
+  auto gather = [&](int nb, void* const* bufs, const int64_t* per_rank, const int64_t* valid) -> int32_t {
+    if (!symm) return eb_comm_allgather(e->comm, nb, bufs, per_rank, st);
+    int64_t so[4], zero[4] = {0, 0, 0, 0}, by[4];
+    for (int i = 0; i < nb; ++i) {
+      so[i] = aoff(bufs[i]) + (int64_t)e->tp_rank * per_rank[i];
+      by[i] = std::min(per_rank[i], (valid[i] + 15) / 16 * 16);
+      if (per_rank[i] % 16) by[i] = std::min(per_rank[i], (valid[i] + 3) / 4 * 4);
+    }
+    int32_t seq = 0;
+    EB_TRY(eb_symm_push(e->symm, nb, so, zero, so, zero, by, nullptr, 0, &seq, st));
+    n += 1;
+    return eb_symm_wait(e->symm, seq, 1, st);
+  };
+  // the ranks' slices of a [T][H] partial (esz bytes per element, in the arena) to their owners, side by side as planes
+  auto scatter_planes = [&](const void* src, int esz) -> int32_t {
+    const int64_t so = aoff(src), step = (int64_t)chunk * H * esz, dof = aoff(e->planes), valid = (int64_t)T * H * esz;
+    int32_t seq = 0;
+    EB_TRY(eb_symm_push(e->symm, 1, &so, &step, &dof, &step, &step, &valid, 1, &seq, st));
+    n += 1;
+    // the first exchange of a step also absorbs the skew between the ranks' host loops
+    const int patience = first_exchange ? 32 : 1;
+    first_exchange = false;
+    return eb_symm_wait(e->symm, seq, patience, st);
+  };
 
   const bool prof = (c.debug & 2) != 0;
   size_t prof_used = 0;
@@ -496,18 +563,32 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       // decode-sized steps sum their split-K planes in fp32 and scatter fp32.
       if (splits == 1) {
         mark(5);
-        EB_TRY(eb_comm_reduce_scatter_bf16(e->comm, e->o, (int64_t)chunk * H, st));
+        if (symm)
+          EB_TRY(scatter_planes(e->o, 2));
+        else
+          EB_TRY(eb_comm_reduce_scatter_bf16(e->comm, e->o, (int64_t)chunk * H, st));
         mark(-1);
-        EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
-                                         e->h + (size_t)t0 * H, st));
+        if (symm)  // the ranks' bf16 planes of my slice, added in rank order in fp32, rounded once
+          EB_TRY(eb_planes_residual_rmsnorm(e->planes, 1, e->tp_size, (int64_t)chunk * H, e->x + (size_t)t0 * H, L.g_mlp, nt, H,
+                                            c.rms_eps, e->h + (size_t)t0 * H, st));
+        else
+          EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
+                                           e->h + (size_t)t0 * H, st));
         n += 1;
       } else {
         EB_TRY(eb_sum_planes_f32((const float*)e->gemm_ws, splits, e->o, (int64_t)T * H, e->ar_buf, st));
         mark(5);
-        EB_TRY(eb_comm_reduce_scatter_f32(e->comm, e->ar_buf, (int64_t)chunk * H, st));
+        if (symm)
+          EB_TRY(scatter_planes(e->ar_buf, 4));
+        else
+          EB_TRY(eb_comm_reduce_scatter_f32(e->comm, e->ar_buf, (int64_t)chunk * H, st));
         mark(-1);
-        EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf + (size_t)t0 * H, 1, nullptr, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
-                                         e->h + (size_t)t0 * H, st));
+        if (symm)
+          EB_TRY(eb_planes_residual_rmsnorm(e->planes, 0, e->tp_size, (int64_t)chunk * H, e->x + (size_t)t0 * H, L.g_mlp, nt, H,
+                                            c.rms_eps, e->h + (size_t)t0 * H, st));
+        else
+          EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf + (size_t)t0 * H, 1, nullptr, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
+                                           e->h + (size_t)t0 * H, st));
         n += 2;
       }
     }
@@ -524,8 +605,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       mark(-1);
       void* bufs[3] = {e->h, e->r_idx, e->r_wts};
       const int64_t sizes[3] = {(int64_t)chunk * H * 2, (int64_t)chunk * c.top_k * 4, (int64_t)chunk * c.top_k * 4};
+      const int64_t valid[3] = {(int64_t)nt * H * 2, (int64_t)nt * c.top_k * 4, (int64_t)nt * c.top_k * 4};
       mark(5);
-      EB_TRY(eb_comm_allgather(e->comm, 3, bufs, sizes, st));
+      EB_TRY(gather(3, bufs, sizes, valid));
       mark(-1);
       n += 1;
     }
@@ -558,10 +640,17 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       // expert-parallel layer is an all-reduce and the dispatch needs no exchange)
       EB_TRY(eb_moe_combine_bf16(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->o, st));
       mark(5);
-      EB_TRY(eb_comm_reduce_scatter_bf16(e->comm, e->o, (int64_t)chunk * H, st));
+      if (symm)
+        EB_TRY(scatter_planes(e->o, 2));
+      else
+        EB_TRY(eb_comm_reduce_scatter_bf16(e->comm, e->o, (int64_t)chunk * H, st));
       mark(-1);
-      EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, g_next, nt, H, c.rms_eps,
-                                       e->h + (size_t)t0 * H, st));
+      if (symm)
+        EB_TRY(eb_planes_residual_rmsnorm(e->planes, 1, e->tp_size, (int64_t)chunk * H, e->x + (size_t)t0 * H, g_next, nt, H,
+                                          c.rms_eps, e->h + (size_t)t0 * H, st));
+      else
+        EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, g_next, nt, H, c.rms_eps,
+                                         e->h + (size_t)t0 * H, st));
       // the next consumer (QKV projection of the next layer, or the LM head) needs every token's normalised row as
       // e4m3 with block scales: the slice's owner quantises its rows and the codes and scales are gathered (half the
       // bytes of the bf16 rows, and no rank quantises the whole batch).  The residual stream itself stays sliced,
@@ -572,8 +661,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       mark(-1);
       void* bufs[3] = {e->h8, e->sh, e->x};
       const int64_t sizes[3] = {(int64_t)chunk * H, (int64_t)(chunk / 128) * e->kbH * 4, (int64_t)chunk * H * 2};
+      const int64_t valid[3] = {(int64_t)nt * H, (int64_t)((nt + 127) / 128) * e->kbH * 4, (int64_t)nt * H * 2};
       mark(5);
-      EB_TRY(eb_comm_allgather(e->comm, (c.debug & 1) ? 3 : 2, bufs, sizes, st));
+      EB_TRY(gather((c.debug & 1) ? 3 : 2, bufs, sizes, valid));
       mark(-1);
       h8_ready = true;
       n += 3;
@@ -605,8 +695,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     EB_TRY(eb_argmax_partial(e->logits + e->v0, T, e->v1 - e->v0, c.vocab, e->v0, e->cand + (size_t)e->tp_rank * cap * 4, st));
     void* cb[1] = {e->cand};
     const int64_t csz[1] = {cap * 4 * (int64_t)sizeof(float)};
+    const int64_t cvalid[1] = {(int64_t)T * 4 * (int64_t)sizeof(float)};
     mark(5);
-    EB_TRY(eb_comm_allgather(e->comm, 1, cb, csz, st));
+    EB_TRY(gather(1, cb, csz, cvalid));
     mark(-1);
     EB_TRY(eb_argmax_merge(e->cand, e->tp_size, cap, T, e->d_next, e->d_margin, st));
     n += 2;
@@ -728,6 +819,7 @@ int32_t eb_engine_destroy(eb_engine* e) {
   if (e->stream) cudaStreamSynchronize(e->stream);
   for (void* p : e->allocs) cudaFree(p);
   if (e->w_scratch) cudaFree(e->w_scratch);
+  if (e->symm) eb_symm_destroy(e->symm);
   for (cudaEvent_t ev : e->prof_ev) cudaEventDestroy(ev);
   if (e->h_stage) cudaFreeHost(e->h_stage);
   if (e->h_result) cudaFreeHost(e->h_result);

@@ -47,6 +47,7 @@ struct GemmParams {
   int32_t* status;
   uint32_t wait_tries;  // polls a bounded wait makes before it gives up (eb_wait_limit_set)
   int32_t w_tiled;      // weights are stored as contiguous 16 KiB tiles (eb_weight_tile_fp8), not row-major
+  const uint8_t* w8;    // the weights' address (for L2 prefetches of tiles; the pipeline itself loads through the tensor map)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -406,6 +407,18 @@ gemm_fp8_persistent_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+  if (tid == 32 * 2 && p.w_tiled) {
+    // While the predecessor drains: pull the first K blocks of this CTA's first weight tile into L2.  The weights do
+    // not depend on the predecessor; which tile comes first does (grouped: the tile table), so it is guessed -- one
+    // token tile per group, the common case in a decode batch -- and a wrong guess costs a little bandwidth, nothing else.
+    const int TTg = p.seg_off ? p.n_groups : (p.rows + TN - 1) / TN;
+    const int w0 = blockIdx.x, nb0 = w0 / TTg, g0 = p.seg_off ? w0 % TTg : 0;
+    if (nb0 < NB) {
+      const uint8_t* src = p.w8 + ((int64_t)(g0 * NB + nb0) * KB) * (kTileN * kBlockK);
+      const uint32_t bytes = (uint32_t)min(KB, 8) * (kTileN * kBlockK);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -1072,6 +1085,7 @@ int32_t run_gemm(const eb_gemm_args* a, bool grouped, cudaStream_t st, int32_t* 
   p.wait_tries = eb::wait_tries();
   p.splits = 1;
   p.w_tiled = a->w_tiled ? 1 : 0;
+  p.w8 = (const uint8_t*)a->d_w8;
   // tiled weights: rows of the tensor map are the 128-byte rows of all tiles, one after the other
   const uint64_t tiled_rows = (uint64_t)a->n_groups * ((a->N + kTileN - 1) / kTileN) * ((a->K + kBlockK - 1) / kBlockK) * kTileN;
   EB_REQUIRE(!a->w_tiled || tiled_rows < (1ull << 31), EB_ERR_UNSUPPORTED, "gemm: tiled weights exceed a tensor map");

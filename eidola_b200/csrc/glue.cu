@@ -436,7 +436,7 @@ template <int MODE>
 __global__ void __launch_bounds__(256)
 row_residual_rmsnorm_kernel(const float* part, int splits, const uint16_t* o_bf16, const uint16_t* y, const int32_t* perm_row,
                             const float* wts, int top_k, int64_t n_rows, uint16_t* x, const float* g, int T, int H, float eps,
-                            uint16_t* hout) {
+                            uint16_t* hout, int64_t plane_stride, int planes_bf16) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
   __shared__ float red[8];
@@ -451,10 +451,24 @@ row_residual_rmsnorm_kernel(const float* part, int splits, const uint16_t* o_bf1
     const int64_t e = (int64_t)t * H + ch * 8;
     float v[8];
     if (MODE == 0) {
-      if (part) {
+      if (planes_bf16) {  // `splits` bf16 planes (one per rank), added in plane order in fp32 and rounded once
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[k] = 0.f;
-        const int64_t plane = (int64_t)T * H;
+        for (int s = 0; s < splits; ++s) {
+          const uint4 pv = *reinterpret_cast<const uint4*>(o_bf16 + s * plane_stride + e);
+          const uint32_t w[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            v[2 * k] += bf_lo(w[k]);
+            v[2 * k + 1] += bf_hi(w[k]);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = round_bf16(v[k]);
+      } else if (part) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = 0.f;
+        const int64_t plane = plane_stride ? plane_stride : (int64_t)T * H;
         for (int s = 0; s < splits; ++s) {
           const float4* pp = reinterpret_cast<const float4*>(part + s * plane + e);
           const float4 p0 = pp[0], p1 = pp[1];
@@ -557,7 +571,23 @@ int32_t eb_oproj_residual_rmsnorm(const float* d_part, int32_t splits, const voi
   if (splits > 1 && !d_part) return eb::fail(EB_ERR_ARG, "eb_oproj_residual_rmsnorm: partials missing");
   EB_CUDA(eb::launch(row_residual_rmsnorm_kernel<0>, dim3(T), dim3(256), 0, eb::as_stream(stream), d_part, splits, (const uint16_t*)d_o_bf16, nullptr,
                                                                        nullptr, nullptr, 0, 0, (uint16_t*)d_x, d_g, T, H, eps,
-                                                                       (uint16_t*)d_h));
+                                                                       (uint16_t*)d_h, (int64_t)0, 0));
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_planes_residual_rmsnorm(const void* d_planes, int32_t planes_are_bf16, int32_t n_planes, int64_t plane_stride, void* d_x,
+                                   const float* d_g, int32_t T, int32_t H, float eps, void* d_h, void* stream) {
+  EB_REQUIRE(d_planes && d_x && d_g && d_h, EB_ERR_ARG, "eb_planes_residual_rmsnorm: null pointer");
+  EB_REQUIRE(n_planes >= 1 && n_planes <= 64 && plane_stride >= (int64_t)T * H && plane_stride % 8 == 0, EB_ERR_ARG,
+             "eb_planes_residual_rmsnorm: %d planes, stride %lld", n_planes, (long long)plane_stride);
+  EB_REQUIRE(T >= 0 && H >= 8 && H % 8 == 0 && H <= 4096, EB_ERR_UNSUPPORTED, "eb_planes_residual_rmsnorm: H %d (multiple of 8, <= 4096)", H);
+  if (T == 0) return EB_OK;
+  EB_CUDA(eb::launch(row_residual_rmsnorm_kernel<0>, dim3(T), dim3(256), 0, eb::as_stream(stream),
+                     planes_are_bf16 ? (const float*)nullptr : (const float*)d_planes, n_planes,
+                     planes_are_bf16 ? (const uint16_t*)d_planes : (const uint16_t*)nullptr, (const uint16_t*)nullptr, (const int32_t*)nullptr,
+                     (const float*)nullptr, 0, (int64_t)0, (uint16_t*)d_x, d_g, T, H, eps, (uint16_t*)d_h, plane_stride,
+                     planes_are_bf16 ? 1 : 0));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -569,7 +599,7 @@ int32_t eb_moe_combine_rmsnorm(const void* d_y, const int32_t* d_perm_row, const
   if (T == 0) return EB_OK;
   EB_CUDA(eb::launch(row_residual_rmsnorm_kernel<1>, dim3(T), dim3(256), 0, eb::as_stream(stream), nullptr, 1, nullptr, (const uint16_t*)d_y, d_perm_row,
                                                                        d_wts, top_k, (int64_t)T * top_k, (uint16_t*)d_x, d_g, T,
-                                                                       H, eps, (uint16_t*)d_h));
+                                                                       H, eps, (uint16_t*)d_h, (int64_t)0, 0));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

@@ -348,6 +348,11 @@ int32_t eb_qkv_rope_append(const float* d_part, int32_t splits, void* d_qkv, int
                            const int32_t* d_block_tables, int32_t bt_stride, const int32_t* d_tok_slot, void* stream);
 int32_t eb_oproj_residual_rmsnorm(const float* d_part, int32_t splits, const void* d_o_bf16, void* d_x, const float* d_g,
                                   int32_t T, int32_t H, float eps, void* d_h, void* stream);
+/* x = bf16(x + bf16(sum over n_planes planes)); h = rmsnorm(x) * g.  The planes ([n_planes][plane_stride elements], the
+ * first T*H of each used) are the partial products of the ranks of a tensor-parallel group, fp32 or bf16; they are added
+ * in plane order in fp32 and the sum is rounded once. */
+int32_t eb_planes_residual_rmsnorm(const void* d_planes, int32_t planes_are_bf16, int32_t n_planes, int64_t plane_stride, void* d_x,
+                                   const float* d_g, int32_t T, int32_t H, float eps, void* d_h, void* stream);
 /* The same with explicit row geometry: a row of d_qkv has row_elems elements, the K heads start at k_col0 and the V
  * heads at v_col0 (a tensor-parallel rank whose K/V heads share a 128-row scale block with a neighbour computes the
  * whole block and uses its part). */
@@ -427,6 +432,30 @@ int32_t eb_comm_reduce_scatter_bf16(eb_comm* c, void* d_buf, int64_t count_per_r
  * the communicator and rebuilds it (failure handling stays on the host; kernels never wait on a peer). */
 int32_t eb_comm_async_error(eb_comm* c, int32_t* err);
 int32_t eb_comm_abort(eb_comm* c);
+
+/* ---- symmetric peer memory (NVLink / NVSwitch stores) ------------------------------------------------------------
+ * Every rank of a communicator allocates an arena of `bytes` and maps its peers' arenas (CUDA IPC; the handles travel
+ * once through the communicator).  eb_symm_push copies rows from the local arena straight into the peers' arenas with
+ * plain stores and then raises this rank's flag on every peer; eb_symm_wait polls, with the library's bounded-wait
+ * discipline, the flags the peers raise here.  An all-gather or the data movement of a reduce-scatter is one push and
+ * one wait (two small kernels) instead of a library collective; sums are left to the consumer kernel, which adds the
+ * ranks' planes in a fixed order.  Nothing ever loads from a peer.  A rank that stops pushing makes its peers' waits
+ * run out: EB_DEV_WAIT_TIMEOUT appears in the status word and the step's results must be discarded. */
+typedef struct eb_symm eb_symm;
+int32_t eb_symm_create(eb_comm* c, size_t bytes, eb_symm** out);
+int32_t eb_symm_destroy(eb_symm* s);
+/* Base address, in this process, of rank `rank`'s arena (the own rank's is ordinary device memory). */
+int32_t eb_symm_ptr(const eb_symm* s, int32_t rank, void** ptr, size_t* bytes);
+/* Segment i copies, for every destination rank p, min(bytes[i], src_valid[i] - p * src_step[i]) bytes from local offset
+ * src_off[i] + p * src_step[i] to offset dst_off[i] + my_rank * dst_step[i] of rank p's arena (all multiples of 4;
+ * src_valid NULL = everything; self_copy: also to the own arena).  At most 4 segments.  *seq identifies the collective. */
+int32_t eb_symm_push(eb_symm* s, int32_t n_segs, const int64_t* src_off, const int64_t* src_step, const int64_t* dst_off,
+                     const int64_t* dst_step, const int64_t* bytes, const int64_t* src_valid, int32_t self_copy, int32_t* seq,
+                     void* stream);
+/* Returns (in stream order) once every peer's push `seq` has arrived here, or the bounded wait has run out.  `patience`
+ * (1..64) multiplies the wait limit: the first collective of a step also absorbs the skew between the ranks' host
+ * loops, the later ones only the skew between their kernels. */
+int32_t eb_symm_wait(eb_symm* s, int32_t seq, int32_t patience, void* stream);
 
 int32_t eb_engine_create(const eb_config* cfg, eb_engine** out);
 /* Tensor-parallel heads + expert-parallel experts over tp_size ranks (one process per GPU): rank r holds query heads
