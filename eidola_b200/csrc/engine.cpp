@@ -66,6 +66,9 @@ struct eb_engine {
   uint8_t* arena = nullptr;                  // this rank's arena
   size_t arena_used = 0;
   uint8_t* planes = nullptr;                 // [tp_size][chunk rows][hidden] fp32 or bf16: the ranks' partial rows of my slice
+  // expert parallelism as dispatch / return of rows (the all-to-all pair) instead of gather-everything + reduce-scatter
+  bool a2a = false;
+  uint16_t* xp16 = nullptr;                  // [tokens * top_k][hidden] bf16: rows dispatched to this rank's experts (global row numbering)
   int32_t* r_idx_local = nullptr;
   float* sinks_all = nullptr;
   int nqkv = 0, hqd = 0, kbH = 0, kbI = 0, kbA = 0;
@@ -259,7 +262,12 @@ int32_t init_work(eb_engine* e) {
     auto a256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
     const size_t sz_rows2 = a256(Tc * H * 2), sz_rows1 = a256(Tc * H), sz_rows4 = a256(Tc * H * 4);
     const size_t sz_sh = a256((size_t)(tb0 * e->kbH) * 4), sz_r = a256(r_cap0 * 4), sz_cand = a256((size_t)e->tp_size * T * 4 * 4);
-    const size_t total = 3 * sz_rows2 + sz_rows1 + 2 * sz_rows4 + sz_sh + 2 * sz_r + sz_cand;
+    {
+      const char* v = getenv("EIDOLA_B200_EP_A2A");
+      e->a2a = v ? v[0] == '1' : e->tp_size >= 4;  // measured: the row exchange moves fewer bytes from four ranks on
+    }
+    const size_t sz_routed = e->a2a ? a256((size_t)R * H * 2) : 0;
+    const size_t total = 3 * sz_rows2 + sz_rows1 + 2 * sz_rows4 + sz_sh + 2 * sz_r + sz_cand + 2 * sz_routed;
     EB_TRY(eb_symm_create(e->comm, total, &e->symm));
     void* base = nullptr;
     EB_TRY(eb_symm_ptr(e->symm, e->tp_rank, &base, nullptr));
@@ -280,6 +288,10 @@ int32_t init_work(eb_engine* e) {
     e->r_idx = (int32_t*)carve(sz_r);
     e->r_wts = (float*)carve(sz_r);
     e->cand = (float*)carve(sz_cand);
+    if (e->a2a) {
+      e->xp16 = (uint16_t*)carve(sz_routed);
+      e->y = (uint16_t*)carve(sz_routed);
+    }
     e->arena_used = o;
     *w += (int64_t)total;
   }
@@ -289,7 +301,7 @@ int32_t init_work(eb_engine* e) {
   EB_TRY(dev_alloc(e, &e->attn, (size_t)T * e->hqd, w));
   if (!e->o) EB_TRY(dev_alloc(e, &e->o, Tc * H, w));  // also the bf16 operand of the tensor-parallel reduce-scatters
   EB_TRY(dev_alloc(e, &e->gu, (size_t)R * 2 * I, w));
-  EB_TRY(dev_alloc(e, &e->y, (size_t)R * H, w));
+  if (!e->y) EB_TRY(dev_alloc(e, &e->y, (size_t)R * H, w));
   EB_TRY(dev_alloc(e, &e->logits, (size_t)T * c.vocab, w));
   if (!e->h8) EB_TRY(dev_alloc(e, &e->h8, Tc * H, w));
   EB_TRY(dev_alloc(e, &e->a8, (size_t)T * e->hqd, w));
@@ -309,7 +321,7 @@ int32_t init_work(eb_engine* e) {
     EB_TRY(dev_alloc(e, &e->cand, (size_t)e->tp_size * T * 4, w));
   }
   if (!e->r_wts) EB_TRY(dev_alloc(e, &e->r_wts, r_cap, w));
-  EB_TRY(dev_alloc(e, &e->seg_off, (size_t)E + 1, w));
+  EB_TRY(dev_alloc(e, &e->seg_off, (size_t)c.n_experts + 1, w));  // all experts' segments under row dispatch, the local ones otherwise
   EB_TRY(dev_alloc(e, &e->perm_row, (size_t)R, w));
   EB_TRY(dev_alloc(e, &e->row_token, (size_t)R, w));
   size_t ws = 0, ws2 = 0;
@@ -457,6 +469,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   };
   const int avg2 = std::min(128, 2 * ((R / e->tp_size + E - 1) / E));
   const int group_tn = avg2 <= 16 ? 16 : avg2 <= 32 ? 32 : avg2 <= 64 ? 64 : 128;
+  // under row dispatch the segment table covers all experts (global row numbering) and this rank works on its own part
+  const bool a2a = tp && e->a2a;
+  const int32_t* seg = a2a ? e->seg_off + e->e0 : e->seg_off;
   auto grouped = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout) -> int32_t {
     eb_gemm_args g = {};
     g.d_x8 = x8;
@@ -469,7 +484,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     g.N = N;
     g.K = K;
     g.n_groups = E;
-    g.d_seg_off = e->seg_off;
+    g.d_seg_off = seg;
     g.d_work = e->group_ws;
     g.work_bytes = e->group_ws_bytes;
     g.tile_tokens = group_tn;
@@ -603,31 +618,51 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
         EB_TRY(eb_moe_route(e->h + (size_t)t0 * H, L.wr, nt, c.n_experts, H, c.top_k, e->r_idx + (size_t)t0 * c.top_k,
                             e->r_wts + (size_t)t0 * c.top_k, nullptr, st));
       mark(-1);
-      void* bufs[3] = {e->h, e->r_idx, e->r_wts};
-      const int64_t sizes[3] = {(int64_t)chunk * H * 2, (int64_t)chunk * c.top_k * 4, (int64_t)chunk * c.top_k * 4};
-      const int64_t valid[3] = {(int64_t)nt * H * 2, (int64_t)nt * c.top_k * 4, (int64_t)nt * c.top_k * 4};
+      // row dispatch needs only the routing everywhere; the normalised rows travel to their experts' ranks below
+      void* bufs[3] = {e->r_idx, e->r_wts, e->h};
+      const int64_t sizes[3] = {(int64_t)chunk * c.top_k * 4, (int64_t)chunk * c.top_k * 4, (int64_t)chunk * H * 2};
+      const int64_t valid[3] = {(int64_t)nt * c.top_k * 4, (int64_t)nt * c.top_k * 4, (int64_t)nt * H * 2};
       mark(5);
-      EB_TRY(gather(3, bufs, sizes, valid));
+      EB_TRY(gather(a2a ? 2 : 3, bufs, sizes, valid));
       mark(-1);
       n += 1;
     }
     if (!tp) {
       EB_TRY(eb_moe_permute_tiles(e->r_idx, T, c.top_k, E, e->seg_off, e->perm_row, e->row_token, group_tn, e->group_ws, st));
+      mark(7);
+      EB_TRY(eb_quant_gather_block128(e->h, H, T, e->row_token, R, H, e->seg_off, E, e->xp8, e->sxp, st));
+      mark(-1);
+    } else if (a2a) {
+      // C2 as a row exchange: every rank sorts ALL routed slots by expert (the routing is the same everywhere), so a
+      // slot's row number is known to sender and receiver alike; the owner of a token stores its normalised row into
+      // the arena of each of its experts' ranks at that row, and the outputs come back the same way
+      EB_TRY(eb_moe_permute(e->r_idx, T, c.top_k, c.n_experts, e->seg_off, e->perm_row, e->row_token, st));
+      EB_TRY(eb_gemm_group_tiles(seg, E, R, group_tn, e->group_ws, st));
+      int32_t seq = 0;
+      mark(5);
+      EB_TRY(eb_symm_dispatch_rows(e->symm, aoff(e->h), aoff(e->xp16), H * 2, e->r_idx, e->perm_row, t0, nt, c.top_k, E, c.n_experts, R,
+                                   &seq, st));
+      EB_TRY(eb_symm_wait(e->symm, seq, 1, st));
+      mark(-1);
+      mark(7);
+      EB_TRY(eb_quant_act_block128(e->xp16, H, R, H, seg, E, e->xp8, e->sxp, st));
+      mark(-1);
+      n += 3;
     } else {
       // routing is replicated; keep the slots of this rank's experts only
       EB_TRY(eb_moe_localize(e->r_idx, T * c.top_k, e->e0, E, e->r_idx_local, st));
       EB_TRY(eb_moe_permute_tiles_local(e->r_idx_local, T, c.top_k, E, e->seg_off, e->perm_row, e->row_token, group_tn,
                                         e->group_ws, st));
       n += 1;
+      mark(7);
+      EB_TRY(eb_quant_gather_block128(e->h, H, T, e->row_token, R, H, e->seg_off, E, e->xp8, e->sxp, st));
+      mark(-1);
     }
-    mark(7);
-    EB_TRY(eb_quant_gather_block128(e->h, H, T, e->row_token, R, H, e->seg_off, E, e->xp8, e->sxp, st));
-    mark(-1);
     mark(3);
     EB_TRY(grouped(e->xp8, e->sxp, L.w1, 2 * I, H, e->gu));
     mark(-1);
     mark(7);
-    EB_TRY(eb_quant_silu_mul_block128(e->gu, 2 * I, R, I, e->seg_off, E, e->act8, e->sact, st));
+    EB_TRY(eb_quant_silu_mul_block128(e->gu, 2 * I, R, I, seg, E, e->act8, e->sact, st));
     mark(-1);
     mark(3);
     EB_TRY(grouped(e->act8, e->sact, L.w2, H, I, e->y));
@@ -636,21 +671,32 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     if (!tp) {
       EB_TRY(eb_moe_combine_rmsnorm(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->x, g_next, c.rms_eps, e->h, st));
     } else {
-      // C2: partial mix of this rank's experts, summed across ranks (tokens are replicated, so the combine of an
-      // expert-parallel layer is an all-reduce and the dispatch needs no exchange)
-      EB_TRY(eb_moe_combine_bf16(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->o, st));
-      mark(5);
-      if (symm)
-        EB_TRY(scatter_planes(e->o, 2));
-      else
-        EB_TRY(eb_comm_reduce_scatter_bf16(e->comm, e->o, (int64_t)chunk * H, st));
-      mark(-1);
-      if (symm)
-        EB_TRY(eb_planes_residual_rmsnorm(e->planes, 1, e->tp_size, (int64_t)chunk * H, e->x + (size_t)t0 * H, g_next, nt, H,
-                                          c.rms_eps, e->h + (size_t)t0 * H, st));
-      else
-        EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, g_next, nt, H, c.rms_eps,
-                                         e->h + (size_t)t0 * H, st));
+      if (a2a) {
+        // the expert outputs return to their tokens' owners, who mix the four rows of a token exactly as one GPU would
+        int32_t seq = 0;
+        mark(5);
+        EB_TRY(eb_symm_return_rows(e->symm, aoff(e->y), aoff(e->y), H * 2, e->row_token, e->seg_off, e->e0, E, chunk, R, &seq, st));
+        EB_TRY(eb_symm_wait(e->symm, seq, 1, st));
+        mark(-1);
+        EB_TRY(eb_moe_combine_rmsnorm_ex(e->y, e->perm_row + (size_t)t0 * c.top_k, e->r_wts + (size_t)t0 * c.top_k, nt, c.top_k, H, R,
+                                         e->x + (size_t)t0 * H, g_next, c.rms_eps, e->h + (size_t)t0 * H, st));
+      } else {
+        // C2 without an exchange of rows: every rank holds every token, mixes its own experts' outputs into a partial
+        // [T, H] and the partials are summed over token slices
+        EB_TRY(eb_moe_combine_bf16(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->o, st));
+        mark(5);
+        if (symm)
+          EB_TRY(scatter_planes(e->o, 2));
+        else
+          EB_TRY(eb_comm_reduce_scatter_bf16(e->comm, e->o, (int64_t)chunk * H, st));
+        mark(-1);
+        if (symm)
+          EB_TRY(eb_planes_residual_rmsnorm(e->planes, 1, e->tp_size, (int64_t)chunk * H, e->x + (size_t)t0 * H, g_next, nt, H,
+                                            c.rms_eps, e->h + (size_t)t0 * H, st));
+        else
+          EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, g_next, nt, H, c.rms_eps,
+                                           e->h + (size_t)t0 * H, st));
+      }
       // the next consumer (QKV projection of the next layer, or the LM head) needs every token's normalised row as
       // e4m3 with block scales: the slice's owner quantises its rows and the codes and scales are gathered (half the
       // bytes of the bf16 rows, and no rank quantises the whole batch).  The residual stream itself stays sliced,

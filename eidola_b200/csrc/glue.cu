@@ -594,11 +594,16 @@ int32_t eb_planes_residual_rmsnorm(const void* d_planes, int32_t planes_are_bf16
 
 int32_t eb_moe_combine_rmsnorm(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
                                int32_t H, void* d_x, const float* d_g, float eps, void* d_h, void* stream) {
-  EB_REQUIRE(d_y && d_perm_row && d_wts && d_x && d_g && d_h, EB_ERR_ARG, "eb_moe_combine_rmsnorm: null pointer");
+  return eb_moe_combine_rmsnorm_ex(d_y, d_perm_row, d_wts, T, top_k, H, (int64_t)T * top_k, d_x, d_g, eps, d_h, stream);
+}
+
+int32_t eb_moe_combine_rmsnorm_ex(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
+                                  int32_t H, int64_t n_rows, void* d_x, const float* d_g, float eps, void* d_h, void* stream) {
+  EB_REQUIRE(d_y && d_perm_row && d_wts && d_x && d_g && d_h && n_rows >= 0, EB_ERR_ARG, "eb_moe_combine_rmsnorm: null pointer");
   EB_REQUIRE(T >= 0 && top_k >= 1 && H >= 8 && H % 8 == 0 && H <= 4096, EB_ERR_UNSUPPORTED, "eb_moe_combine_rmsnorm: H %d (multiple of 8, <= 4096)", H);
   if (T == 0) return EB_OK;
   EB_CUDA(eb::launch(row_residual_rmsnorm_kernel<1>, dim3(T), dim3(256), 0, eb::as_stream(stream), nullptr, 1, nullptr, (const uint16_t*)d_y, d_perm_row,
-                                                                       d_wts, top_k, (int64_t)T * top_k, (uint16_t*)d_x, d_g, T,
+                                                                       d_wts, top_k, n_rows, (uint16_t*)d_x, d_g, T,
                                                                        H, eps, (uint16_t*)d_h, (int64_t)0, 0));
   EB_LAUNCH_CHECK();
   return EB_OK;

@@ -94,6 +94,82 @@ __global__ void __launch_bounds__(256) symm_push_kernel(const PushArgs a) {
   }
 }
 
+// Expert-parallel dispatch and return: whole rows to (rank, row) destinations computed from the routing, which every rank
+// holds.  Row numbering is global (position in the expert-major order over all experts), so a row has the same offset
+// in every rank's arena and neither direction needs a count exchange.
+//   mode 0 (dispatch): row r of the grid is slot j = r % top_k of token t = t0 + r / top_k of this rank's token slice;
+//                      it goes to the rank that holds expert idx[t][j], at row perm[t][j].
+//   mode 1 (return)  : row i = seg[lo_e] + r of this rank's experts' range goes back to the owner of its token
+//                      (rank row_token[i] / chunk), at the same row i.
+struct RowsArgs {
+  uint8_t* arena[kMaxRanks];
+  int32_t* flags[kMaxRanks];
+  int32_t* counter;
+  int64_t src_off, dst_off;
+  int32_t row_bytes, rank, size, seq, mode;
+  const int32_t* idx;
+  const int32_t* perm;
+  int32_t t0, nt, top_k, e_l, n_experts;
+  const int32_t* row_token;
+  const int32_t* seg;
+  int32_t lo_e, hi_e, chunk, n_rows;
+  int32_t* status;
+};
+
+__global__ void __launch_bounds__(128) symm_rows_kernel(const RowsArgs a) {
+  eb::pdl_wait();
+  eb::pdl_trigger();
+  const int r = blockIdx.x;
+  int p = -1;
+  int64_t srow = 0, drow = 0;
+  if (a.mode == 0) {
+    const int t = a.t0 + r / a.top_k, j = r % a.top_k;
+    if (r < a.nt * a.top_k) {
+      const int e = a.idx[(int64_t)t * a.top_k + j];
+      const int d = a.perm[(int64_t)t * a.top_k + j];
+      if (e < 0 || e >= a.n_experts || d < 0 || d >= a.n_rows) {
+        if (threadIdx.x == 0) atomicOr(a.status, EB_DEV_BAD_INDEX);
+      } else {
+        p = e / a.e_l;
+        srow = t;
+        drow = d;
+      }
+    }
+  } else {
+    const int i = a.seg[a.lo_e] + r;
+    if (i < a.seg[a.hi_e] && i >= 0 && i < a.n_rows) {
+      const int t = a.row_token[i];
+      if (t < 0) {
+        if (threadIdx.x == 0) atomicOr(a.status, EB_DEV_BAD_INDEX);
+      } else {
+        p = min(t / a.chunk, a.size - 1);
+        srow = drow = i;
+      }
+    }
+  }
+  if (p >= 0) {
+    const uint4* src = reinterpret_cast<const uint4*>(a.arena[a.rank] + a.src_off + srow * a.row_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(a.arena[p] + a.dst_off + drow * a.row_bytes);
+    if (src != dst)
+      for (int c = threadIdx.x; c < (a.row_bytes >> 4); c += blockDim.x) dst[c] = src[c];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(a.counter, 1);
+    if (prev == (int)gridDim.x - 1) {
+      *a.counter = 0;
+      __threadfence_system();
+      const int slot = a.seq % kFlagSlots;
+      for (int q = 0; q < a.size; ++q) {
+        if (q == a.rank) continue;
+        int32_t* f = a.flags[q] + slot * kMaxRanks + a.rank;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f), "r"(a.seq) : "memory");
+      }
+    }
+  }
+}
+
 // One warp: lane p polls the word rank p writes.  Bounded; raises the status word when it gives up.
 __global__ void symm_wait_kernel(const int32_t* flags, int rank, int size, int seq, uint32_t tries, int32_t* status) {
   eb::pdl_wait();
@@ -262,6 +338,65 @@ int32_t eb_symm_push(eb_symm* s, int32_t n_segs, const int64_t* src_off, const i
   EB_CUDA(eb::launch(symm_push_kernel, dim3(grid), dim3(256), 0, eb::as_stream(stream), a));
   EB_LAUNCH_CHECK();
   return EB_OK;
+}
+
+static int32_t rows_common(eb_symm* s, RowsArgs& a, int64_t src_off, int64_t dst_off, int32_t row_bytes, int32_t n_rows, int64_t grid,
+                           int32_t* seq, void* stream) {
+  EB_REQUIRE(row_bytes >= 16 && row_bytes % 16 == 0 && src_off >= 0 && dst_off >= 0 && src_off % 16 == 0 && dst_off % 16 == 0 &&
+                 n_rows >= 0 && dst_off + (int64_t)n_rows * row_bytes <= (int64_t)s->bytes,
+             EB_ERR_ARG, "eb_symm rows: %d rows of %d bytes at %lld leave the arena", n_rows, row_bytes, (long long)dst_off);
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_symm rows: no device");
+  a.src_off = src_off;
+  a.dst_off = dst_off;
+  a.row_bytes = row_bytes;
+  a.rank = s->rank;
+  a.size = s->size;
+  a.seq = ++s->seq;
+  a.n_rows = n_rows;
+  a.status = status;
+  for (int p = 0; p < s->size; ++p) {
+    a.arena[p] = s->arena[p];
+    a.flags[p] = reinterpret_cast<int32_t*>(s->arena[p] + s->bytes);
+  }
+  a.counter = reinterpret_cast<int32_t*>(s->arena[s->rank] + s->bytes) + kFlagSlots * kMaxRanks;
+  *seq = a.seq;
+  EB_CUDA(eb::launch(symm_rows_kernel, dim3((unsigned)std::max<int64_t>(1, grid)), dim3(128), 0, eb::as_stream(stream), a));
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_symm_dispatch_rows(eb_symm* s, int64_t src_off, int64_t dst_off, int32_t row_bytes, const int32_t* d_idx,
+                              const int32_t* d_perm, int32_t t0, int32_t nt, int32_t top_k, int32_t experts_per_rank,
+                              int32_t n_experts, int32_t n_rows, int32_t* seq, void* stream) {
+  EB_REQUIRE(s && d_idx && d_perm && seq && t0 >= 0 && nt >= 0 && top_k >= 1 && experts_per_rank >= 1 &&
+                 n_experts == experts_per_rank * s->size,
+             EB_ERR_ARG, "eb_symm_dispatch_rows: bad argument");
+  RowsArgs a = {};
+  a.mode = 0;
+  a.idx = d_idx;
+  a.perm = d_perm;
+  a.t0 = t0;
+  a.nt = nt;
+  a.top_k = top_k;
+  a.e_l = experts_per_rank;
+  a.n_experts = n_experts;
+  return rows_common(s, a, src_off, dst_off, row_bytes, n_rows, (int64_t)nt * top_k, seq, stream);
+}
+
+int32_t eb_symm_return_rows(eb_symm* s, int64_t src_off, int64_t dst_off, int32_t row_bytes, const int32_t* d_row_token,
+                            const int32_t* d_seg_off, int32_t first_expert, int32_t experts_per_rank, int32_t chunk_tokens,
+                            int32_t n_rows, int32_t* seq, void* stream) {
+  EB_REQUIRE(s && d_row_token && d_seg_off && seq && first_expert >= 0 && experts_per_rank >= 1 && chunk_tokens >= 1, EB_ERR_ARG,
+             "eb_symm_return_rows: bad argument");
+  RowsArgs a = {};
+  a.mode = 1;
+  a.row_token = d_row_token;
+  a.seg = d_seg_off;
+  a.lo_e = first_expert;
+  a.hi_e = first_expert + experts_per_rank;
+  a.chunk = chunk_tokens;
+  return rows_common(s, a, src_off, dst_off, row_bytes, n_rows, n_rows, seq, stream);
 }
 
 int32_t eb_symm_wait(eb_symm* s, int32_t seq, int32_t patience, void* stream) {

@@ -378,6 +378,10 @@ int32_t eb_moe_combine_bf16(const void* d_y, const int32_t* d_perm_row, const fl
 /* x = bf16(x + bf16(sum_j w_j y[perm_row])) as eb_moe_combine, then h = rmsnorm(x) * g for the next consumer. */
 int32_t eb_moe_combine_rmsnorm(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
                                int32_t H, void* d_x, const float* d_g, float eps, void* d_h, void* stream);
+/* The same with the bound of d_perm_row's values given explicitly (rows of d_y): the tokens may be a slice of a batch
+ * whose rows are numbered over the whole batch. */
+int32_t eb_moe_combine_rmsnorm_ex(const void* d_y, const int32_t* d_perm_row, const float* d_wts, int32_t T, int32_t top_k,
+                                  int32_t H, int64_t n_rows, void* d_x, const float* d_g, float eps, void* d_h, void* stream);
 int32_t eb_embed(const void* d_table, int32_t V, int32_t H, const int32_t* d_tokens, int32_t T, void* d_x, void* stream);
 /* Greedy argmax over bf16 logits [T][ld], ties to the lower id; d_margin (top1 - top2) may be NULL. */
 int32_t eb_argmax(const void* d_logits, int32_t T, int64_t V, int64_t ld, int32_t* d_tok, float* d_margin, void* stream);
@@ -452,6 +456,22 @@ int32_t eb_symm_ptr(const eb_symm* s, int32_t rank, void** ptr, size_t* bytes);
 int32_t eb_symm_push(eb_symm* s, int32_t n_segs, const int64_t* src_off, const int64_t* src_step, const int64_t* dst_off,
                      const int64_t* dst_step, const int64_t* bytes, const int64_t* src_valid, int32_t self_copy, int32_t* seq,
                      void* stream);
+/* C2, expert-parallel dispatch and return (the all-to-all pair) as row stores.  Rows are numbered globally -- position in
+ * the expert-major order over ALL experts, which every rank computes from the gathered routing (eb_moe_permute) -- so a
+ * row sits at the same offset in every arena and no counts are exchanged.
+ * dispatch: for each token t in [t0, t0 + nt) of this rank's slice and each slot j, the row src_off + t * row_bytes goes
+ *           to the rank that holds expert d_idx[t][j] (experts_per_rank consecutive experts per rank), at row d_perm[t][j]
+ *           of dst_off.
+ * return  : every row i of this rank's experts' range [d_seg_off[first_expert], d_seg_off[first_expert + experts_per_rank])
+ *           goes from src_off + i * row_bytes to the same row of dst_off on the rank that owns token d_row_token[i]
+ *           (tokens are dealt to ranks in chunks of chunk_tokens).
+ * Both raise the flags like eb_symm_push; eb_symm_wait(seq) on the receiving side. */
+int32_t eb_symm_dispatch_rows(eb_symm* s, int64_t src_off, int64_t dst_off, int32_t row_bytes, const int32_t* d_idx,
+                              const int32_t* d_perm, int32_t t0, int32_t nt, int32_t top_k, int32_t experts_per_rank,
+                              int32_t n_experts, int32_t n_rows, int32_t* seq, void* stream);
+int32_t eb_symm_return_rows(eb_symm* s, int64_t src_off, int64_t dst_off, int32_t row_bytes, const int32_t* d_row_token,
+                            const int32_t* d_seg_off, int32_t first_expert, int32_t experts_per_rank, int32_t chunk_tokens,
+                            int32_t n_rows, int32_t* seq, void* stream);
 /* Returns (in stream order) once every peer's push `seq` has arrived here, or the bounded wait has run out.  `patience`
  * (1..64) multiplies the wait limit: the first collective of a step also absorbs the skew between the ranks' host
  * loops, the later ones only the skew between their kernels. */

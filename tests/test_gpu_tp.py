@@ -1,5 +1,7 @@
-"""GPU (needs two devices): tensor-parallel heads + expert-parallel experts over NCCL against the single-GPU engine
-and the CPU oracle.  One process per GPU, started here as children; skipped on a box with one GPU."""
+"""GPU (needs two or more devices): tensor-parallel heads + expert-parallel experts against the single-GPU engine and
+the CPU oracle, for 2, 4 and 8 ranks, with the exchanges over peer memory (default) or NCCL, and the expert exchange
+as partial sums or as dispatch / return of rows.  One process per GPU, started here as children; a case that needs
+more GPUs than the box has is skipped."""
 import os
 import subprocess
 import sys
@@ -17,11 +19,11 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _spawn(world, name, tmp_path, force_file=None):
+def _spawn(world, name, tmp_path, force_file=None, extra_env=None):
     import uuid
     id_file = str(tmp_path / f"nccl_id_{uuid.uuid4().hex}")
     procs, outs = [], []
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
     for r in range(world):
         out = str(tmp_path / f"rank{r}.npz")
         outs.append(out)
@@ -72,21 +74,33 @@ def _oracle_steps(name):
     return cfg, refs
 
 
-@pytest.mark.parametrize("name", ["tp_small", "tp_mid"])
-def test_two_rank_engine_matches_oracle_and_single_gpu(gpu, tmp_path, name):
+MODES = {
+    "peer": {},                                                        # peer-memory exchanges, the default expert form for the rank count
+    "peer_rows": {"EIDOLA_B200_EP_A2A": "1"},                          # experts by dispatch / return of rows
+    "peer_sums": {"EIDOLA_B200_EP_A2A": "0"},                          # experts by partial sums over token slices
+    "nccl": {"EIDOLA_B200_TP_NCCL": "1"},                              # NCCL reduce-scatter / all-gather
+}
+
+
+@pytest.mark.parametrize("name,world,mode", [("tp_small", 2, "peer_sums"), ("tp_small", 2, "peer_rows"), ("tp_mid", 2, "peer"),
+                                             ("tp_mid", 2, "nccl"), ("tp_mid", 2, "peer_rows"), ("tp_mid", 4, "peer"),
+                                             ("tp_mid", 4, "peer_sums"), ("tp_mid", 8, "peer"), ("tp_mid", 8, "nccl")])
+def test_tp_engine_matches_oracle_and_single_gpu(gpu, tmp_path, name, world, mode):
     import eidola_b200 as eb
-    if eb.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if eb.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = MODES[mode]
     cfg, refs = _oracle_steps(name)
     force_file = str(tmp_path / "force.npz")
     np.savez(force_file, **{f"s{s}_l{l}": refs[s]["hidden"][l] for s in range(2) for l in range(cfg.n_layers + 1)})
     # (1) teacher-forced against the oracle, layer by layer
-    ranks = _spawn(2, name, tmp_path, force_file)
+    ranks = _spawn(world, name, tmp_path, force_file, env)
     for s in range(2):
         got = [{k: r[f"s{s}_{k}"] for k in ("next", "margin", "route_idx", "hidden")} for r in ranks]
-        assert np.array_equal(got[0]["next"], got[1]["next"]) and np.array_equal(got[0]["margin"], got[1]["margin"])
-        assert np.array_equal(got[0]["hidden"], got[1]["hidden"])  # ranks stay in lockstep bit for bit
-        assert np.array_equal(got[0]["route_idx"], got[1]["route_idx"])  # token-sharded routing, gathered
+        for other in got[1:]:
+            assert np.array_equal(got[0]["next"], other["next"]) and np.array_equal(got[0]["margin"], other["margin"])
+            assert np.array_equal(got[0]["hidden"], other["hidden"])  # ranks stay in lockstep bit for bit
+            assert np.array_equal(got[0]["route_idx"], other["route_idx"])  # token-sharded routing, gathered
         logits = _merged_logits(ranks, f"s{s}_logits", cfg.vocab)
         # the merged argmax of the vocabulary slices is the argmax of the whole row (ties to the lower id)
         lf = (logits.astype(np.uint32) << 16).view(np.float32)
@@ -94,11 +108,12 @@ def test_two_rank_engine_matches_oracle_and_single_gpu(gpu, tmp_path, name):
         top2 = np.sort(lf, axis=1)[:, -2:]
         assert np.array_equal(got[0]["margin"], (top2[:, 1] - top2[:, 0]).astype(np.float32))
         g = dict(got[0], logits=logits, route_idx=list(got[0]["route_idx"]), hidden=list(got[0]["hidden"]))
-        wh, wl = compare_forced_step(g, refs[s], cfg, what=f"{name} tp=2 step {s}")
-        print(f"{name} tp=2 step {s}: forced hidden err {wh:.4f} logits err {wl:.4f}")
+        wh, wl = compare_forced_step(g, refs[s], cfg, what=f"{name} tp={world} {mode} step {s}")
+        print(f"{name} tp={world} {mode} step {s}: forced hidden err {wh:.4f} logits err {wl:.4f}")
     assert all(int(r["status"][0]) == 0 for r in ranks)
+    assert all(int(r["comm_async_error"][0]) == 0 for r in ranks)  # the communicator stayed healthy throughout
     # (2) free-running against the single-GPU engine on the same steps
-    ranks = _spawn(2, name, tmp_path)
+    ranks = _spawn(world, name, tmp_path, None, env)
     eng = eb.Engine(cfg)
     eng.kv_fill_synth()
     _, single = run_steps(eng, name)
@@ -106,5 +121,5 @@ def test_two_rank_engine_matches_oracle_and_single_gpu(gpu, tmp_path, name):
         got = {"hidden": ranks[0][f"s{s}_hidden"], "logits": _merged_logits(ranks, f"s{s}_logits", cfg.vocab)}
         dl, rel = free_running_error({"logits": got["logits"], "hidden": list(got["hidden"])},
                                      {"logits": single[s]["logits"], "hidden": list(single[s]["hidden"])})
-        print(f"{name} tp=2 vs single GPU step {s}: logits err {dl.max():.4f} hidden rel {rel:.4f}")
+        print(f"{name} tp={world} {mode} vs single GPU step {s}: logits err {dl.max():.4f} hidden rel {rel:.4f}")
         assert rel <= 0.15

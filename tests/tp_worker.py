@@ -97,6 +97,7 @@ def main():
         for k, v in o.items():
             flat[f"s{s}_{k}"] = v
     flat["status"] = np.array([eb.status_read()], np.int32)
+    flat["comm_async_error"] = np.array([comm.async_error()], np.int32)
     np.savez(out_file, **flat)
     eng.close()
     comm.close()
