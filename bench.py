@@ -125,12 +125,12 @@ class ClockSampler:
 
 # ------------------------------------------------------------------------------------------ decoder workload
 
-def decoder_config(make_config, n_layers=24, n_seqs=256, max_ctx=8192, steps=0, n_experts=32, debug=0, seed=4):
+def decoder_config(make_config, n_layers=24, n_seqs=256, max_ctx=8192, steps=0, n_experts=32, debug=0, seed=4, max_q_len=1):
     """eb_config of the 20b-shaped decoder; `make_config` is the binding's (engine arm) or the CPU checker's (CPU arm)."""
     pages_per_seq = (max_ctx + steps + PAGE) // PAGE + 1
     return make_config(n_layers=n_layers, hidden=2880, n_q_heads=64, n_kv_heads=8, window=128, n_experts=n_experts,
                        top_k=4, inter=2880, vocab=201088, num_pages=1, max_seqs=n_seqs,
-                       max_pages_per_seq=pages_per_seq, max_tokens=n_seqs, max_q_len=1, seed=seed, debug=debug)
+                       max_pages_per_seq=pages_per_seq, max_tokens=n_seqs * max_q_len, max_q_len=max_q_len, seed=seed, debug=debug)
 
 
 DECODER_NAME = ("gpt-oss-20b-shaped random-init FP8 decoder: 24 layers (even 128-window, odd full), hidden 2880, 64q/8kv "
@@ -143,7 +143,7 @@ class DecoderWorkload:
     name = DECODER_NAME
 
     def __init__(self, total_steps: int, n_seqs=256, n_layers=24, profile=False, rank=0, world=1, comm=None, debug=0,
-                 max_ctx=8192, min_ctx=128):
+                 max_ctx=8192, min_ctx=128, prefill="synthetic"):
         import eidola_b200 as eb
         from eidola_b200.capi import make_config
         self.eb, self.rank, self.world = eb, rank, world
@@ -151,14 +151,28 @@ class DecoderWorkload:
         rng = np.random.default_rng(seed)
         self.ctx0 = rng.integers(min_ctx, max_ctx + 1, size=n_seqs).astype(np.int32)
         cfg = decoder_config(make_config, n_layers=n_layers, n_seqs=n_seqs, max_ctx=max_ctx, steps=total_steps,
-                             debug=(2 if profile else 0) | debug, seed=seed)
+                             debug=(2 if profile else 0) | debug, seed=seed, max_q_len=6 if prefill == "real" else 1)
         cfg.num_pages = int(((self.ctx0.astype(np.int64) + total_steps + PAGE) // PAGE + 1).sum()) + 64
         self.cfg = cfg
         self.eng = eb.Engine(cfg, rank, world, comm)
-        self.eng.kv_fill_synth()
-        self.slots = np.array([self.eng.admit(int(L)) for L in self.ctx0], np.int32)
+        self.prefill_stats = None
+        if prefill == "real":
+            # the engine computes the cache itself: every prompt runs through all layers in chunks of 6 tokens
+            self.slots = np.array([self.eng.admit(0) for _ in self.ctx0], np.int32)
+            prompts = [rng.integers(0, cfg.vocab, size=int(L)).astype(np.int32) for L in self.ctx0]
+            t0 = time.perf_counter()
+            first, _, steps, ms = self.eng.prefill(self.slots, prompts)
+            wall = time.perf_counter() - t0
+            n_tok = int(self.ctx0.astype(np.int64).sum())
+            self.prefill_stats = {"prompt_tokens": n_tok, "steps": steps, "device_ms": ms, "wall_ms": wall * 1e3,
+                                  "prompt_tokens_per_s": n_tok / (ms * 1e-3), "chunk": 6,
+                                  "prompts": "U[%d,%d] tokens per sequence" % (min_ctx, max_ctx)}
+            self.tokens = first.astype(np.int32)
+        else:
+            self.eng.kv_fill_synth()
+            self.slots = np.array([self.eng.admit(int(L)) for L in self.ctx0], np.int32)
+            self.tokens = rng.integers(0, cfg.vocab, size=n_seqs).astype(np.int32)
         self.q_lens = np.ones(n_seqs, np.int32)
-        self.tokens = rng.integers(0, cfg.vocab, size=n_seqs).astype(np.int32)
         self.steps_done = 0
         self.units_per_step = n_seqs
         self.mem = self.eng.memory()
@@ -198,7 +212,8 @@ class DecoderWorkload:
         return {"workload": self.name, "n_seqs": int(len(self.ctx0)), "n_layers": int(self.cfg.n_layers),
                 "mean_context": float(self.ctx_now().mean()),
                 "device_bytes_per_rank": self.mem,
-                "prefill": "KV pages filled with seeded N(0,1) values (stand-in for prefill)",
+                "prefill": ("real: eb_engine_prefill ran every prompt through all layers in chunks of 6 tokens" if self.prefill_stats
+                            else "KV pages filled with seeded N(0,1) values (stand-in for prefill)"),
                 "l2": "per-step working set ~%.0f GB per GPU >> L2, no flush" % (self.step_alg_bytes()["total"] / 1e9)}
 
 
@@ -501,7 +516,10 @@ def run_decoder(args) -> dict:
     K, W = args.steps, args.warmup
     n_prof = 3
     comm = make_comm(eb, rank, world, dist)
-    wl = DecoderWorkload(total_steps=K + W + n_prof + 8, n_seqs=args.seqs, n_layers=args.layers, rank=rank, world=world, comm=comm)
+    kw = {}
+    if args.prefill == "real":  # a stated subset of the prompt lengths: one eighth of the range, so the run stays in seconds
+        kw = dict(prefill="real", min_ctx=16, max_ctx=1024)
+    wl = DecoderWorkload(total_steps=K + W + n_prof + 8, n_seqs=args.seqs, n_layers=args.layers, rank=rank, world=world, comm=comm, **kw)
     stream = wl.eng.stream()
 
     def barrier():
@@ -576,6 +594,7 @@ def run_decoder(args) -> dict:
                     "bytes_are": "what eb_engine_step staged and copied in the middle timed step (eb_engine_last_step_copies)"},
             "gpu_launches": launches,
             "serving": serving_metrics(stamps, units),
+            "prefill": wl.prefill_stats,
             "step_bytes_per_rank": ctx_mid,
             "step_hbm_bound": {"bytes_per_rank": ctx_mid["total"], "floor_ms": ctx_mid["total"] / (peak * 1e6),
                                "frac_of_floor": (ctx_mid["total"] / (peak * 1e6)) / (dev_ms / K), "peak_gbs": peak, "peak_kind": peak_kind},
@@ -1101,6 +1120,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decoder", choices=["decoder", "attn", "spec120b", "gemm", "peak"])
+    ap.add_argument("--prefill", default="synthetic", choices=["synthetic", "real"],
+                    help="decoder: 'real' computes the KV cache with eb_engine_prefill on prompts of U[16,1024] tokens (one eighth of "
+                         "the benchmark's range) instead of filling the pages with seeded values")
     ap.add_argument("--no-sub", action="store_true", help="decoder, 1 GPU: skip the attn / gemm_sweep / fp8_peak sub-records")
     ap.add_argument("--no-spec", action="store_true", help="decoder, N > 1 GPUs: skip the 120b-shaped verify sub-record")
     ap.add_argument("--spec-steps", type=int, default=6, help="decoder, N > 1 GPUs: timed steps of the 120b-shaped verify sub-record")

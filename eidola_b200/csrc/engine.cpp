@@ -121,6 +121,7 @@ struct eb_engine {
   bool in_flight = false;
   int32_t launches = 0;
   float last_ms = 0.f;
+  int64_t tick = 0;                      // steps launched so far: the clock of least-recently-used admission
   int64_t h2d_bytes = 0, d2h_bytes = 0;  // bytes the last step copied host -> device (staging block) and back (results)
 };
 
@@ -903,6 +904,21 @@ int32_t eb_engine_seq_admit(eb_engine* e, int32_t context_len, int32_t* slot) {
   return EB_OK;
 }
 
+int32_t eb_engine_seq_admit_evicting(eb_engine* e, int32_t context_len, int32_t* slot, int32_t* h_evicted, int32_t cap,
+                                     int32_t* n_evicted) {
+  EB_REQUIRE(e && slot && n_evicted, EB_ERR_ARG, "eb_engine_seq_admit_evicting: null");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_seq_admit_evicting: a step is in flight");
+  EB_TRY(eb_sched_admit_evicting(e->sched, context_len, e->tick, slot, h_evicted, cap, n_evicted));
+  for (int32_t i = 0; i < *n_evicted; ++i) e->uploaded_pages[(size_t)h_evicted[i]] = 0;
+  e->uploaded_pages[(size_t)*slot] = 0;
+  return EB_OK;
+}
+
+int32_t eb_engine_seq_pin(eb_engine* e, int32_t slot, int32_t pinned) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_seq_pin: null");
+  return eb_sched_set_flags(e->sched, slot, pinned ? 1 : 0, -1);
+}
+
 int32_t eb_engine_seq_release(eb_engine* e, int32_t slot) {
   EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_seq_release: null");
   EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_seq_release: a step is in flight");
@@ -981,6 +997,8 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
   }
   const int32_t rc_body = step_launch_body(e, h_slots, h_q_lens, n_seqs, h_tokens, T, max_q);
   if (rc_body != EB_OK) return rollback(rc_body);
+  ++e->tick;
+  for (int i = 0; i < n_seqs; ++i) eb_sched_touch(e->sched, h_slots[i], e->tick);
   e->cur_T = T;
   e->in_flight = true;
   return EB_OK;
@@ -1101,6 +1119,63 @@ int32_t eb_engine_step(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_
                        const int32_t* h_tokens, int32_t* h_next, float* h_margin) {
   EB_TRY(eb_engine_step_launch(e, h_slots, h_q_lens, n_seqs, h_tokens));
   return eb_engine_step_wait(e, h_next, h_margin);
+}
+
+int32_t eb_engine_prefill(eb_engine* e, const int32_t* h_slots, const int32_t* h_n_tokens, int32_t n_seqs, const int32_t* h_tokens,
+                          int32_t* h_next, float* h_margin, int32_t* steps_run, float* device_ms) {
+  EB_REQUIRE(e && h_slots && h_n_tokens && h_tokens && h_next, EB_ERR_ARG, "eb_engine_prefill: null pointer");
+  const eb_config& c = e->c;
+  EB_REQUIRE(n_seqs >= 1 && n_seqs <= c.max_seqs, EB_ERR_ARG, "eb_engine_prefill: n_seqs %d outside 1..%d", n_seqs, c.max_seqs);
+  std::vector<int64_t> off((size_t)n_seqs + 1, 0);
+  for (int i = 0; i < n_seqs; ++i) {
+    EB_REQUIRE(h_n_tokens[i] >= 1, EB_ERR_ARG, "eb_engine_prefill: sequence %d has %d prompt tokens", i, h_n_tokens[i]);
+    off[(size_t)i + 1] = off[(size_t)i] + h_n_tokens[i];
+  }
+  std::vector<int32_t> done((size_t)n_seqs, 0), b_slots, b_q, b_tok, b_seq;
+  std::vector<int32_t> next((size_t)c.max_tokens);
+  std::vector<float> margin((size_t)c.max_tokens);
+  int32_t steps = 0;
+  float ms = 0.f;
+  int64_t left = off[(size_t)n_seqs];
+  int start = 0;  // rotate the first sequence considered, so that a batch too wide for max_tokens starves nobody
+  while (left > 0) {
+    b_slots.clear();
+    b_q.clear();
+    b_tok.clear();
+    b_seq.clear();
+    int32_t rows = 0;
+    for (int k = 0; k < n_seqs; ++k) {
+      const int i = (start + k) % n_seqs;
+      const int32_t rem = h_n_tokens[i] - done[(size_t)i];
+      if (rem <= 0) continue;
+      const int32_t q = std::min(rem, c.max_q_len);
+      if (rows + q > c.max_tokens) continue;
+      b_slots.push_back(h_slots[i]);
+      b_q.push_back(q);
+      b_seq.push_back(i);
+      for (int32_t j = 0; j < q; ++j) b_tok.push_back(h_tokens[off[(size_t)i] + done[(size_t)i] + j]);
+      rows += q;
+    }
+    EB_REQUIRE(rows > 0, EB_ERR_STATE, "eb_engine_prefill: no sequence fits a step of %d token rows", c.max_tokens);
+    EB_TRY(eb_engine_step(e, b_slots.data(), b_q.data(), (int32_t)b_slots.size(), b_tok.data(), next.data(), margin.data()));
+    ms += e->last_ms;
+    ++steps;
+    int32_t row = 0;
+    for (size_t k = 0; k < b_seq.size(); ++k) {
+      const int i = b_seq[k];
+      row += b_q[k];
+      done[(size_t)i] += b_q[k];
+      left -= b_q[k];
+      if (done[(size_t)i] == h_n_tokens[i]) {  // the row of the prompt's last token predicts the first generated token
+        h_next[i] = next[(size_t)row - 1];
+        if (h_margin) h_margin[i] = margin[(size_t)row - 1];
+      }
+    }
+    start = (start + 1) % n_seqs;
+  }
+  if (steps_run) *steps_run = steps;
+  if (device_ms) *device_ms = ms;
+  return EB_OK;
 }
 
 int32_t eb_engine_last_step_stats(const eb_engine* e, float* device_ms, int32_t* kernel_launches) {

@@ -17,6 +17,10 @@ struct eb_sched {
   std::vector<int32_t> free_list;  // allocation pops from the back
   std::vector<int32_t> tables;     // [max_seqs][max_pages]
   std::vector<int32_t> len;        // tokens held, -1 = slot free
+  // admission with eviction (the reference's engine pool, one level down): when a sequence was last used, whether
+  // its owner pinned it, whether a step that includes it is in flight
+  std::vector<int64_t> last_used;
+  std::vector<uint8_t> pinned, in_flight;
 };
 
 namespace {
@@ -48,6 +52,9 @@ int32_t eb_sched_create(int32_t num_pages, int32_t page_size, int32_t max_seqs, 
   }
   s->tables.assign((size_t)max_seqs * max_pages_per_seq, -1);
   s->len.assign((size_t)max_seqs, -1);
+  s->last_used.assign((size_t)max_seqs, 0);
+  s->pinned.assign((size_t)max_seqs, 0);
+  s->in_flight.assign((size_t)max_seqs, 0);
   *out = s;
   return EB_OK;
 }
@@ -77,6 +84,8 @@ int32_t eb_sched_admit(eb_sched* s, int32_t context_len, int32_t* slot) {
     s->free_list.pop_back();
   }
   s->len[(size_t)found] = context_len;
+  s->pinned[(size_t)found] = s->in_flight[(size_t)found] = 0;
+  s->last_used[(size_t)found] = 0;
   *slot = found;
   return EB_OK;
 }
@@ -122,6 +131,78 @@ int32_t eb_sched_release(eb_sched* s, int32_t slot) {
   if (rc != EB_OK) return rc;
   s->len[(size_t)slot] = -1;
   return EB_OK;
+}
+
+int32_t eb_sched_touch(eb_sched* s, int32_t slot, int64_t now) {
+  EB_REQUIRE(s, EB_ERR_ARG, "eb_sched_touch: null");
+  EB_REQUIRE(live(s, slot), EB_ERR_STATE, "eb_sched_touch: slot %d is not live", slot);
+  s->last_used[(size_t)slot] = now;
+  return EB_OK;
+}
+
+int32_t eb_sched_set_flags(eb_sched* s, int32_t slot, int32_t pinned, int32_t in_flight) {
+  EB_REQUIRE(s, EB_ERR_ARG, "eb_sched_set_flags: null");
+  EB_REQUIRE(live(s, slot), EB_ERR_STATE, "eb_sched_set_flags: slot %d is not live", slot);
+  if (pinned >= 0) s->pinned[(size_t)slot] = pinned ? 1 : 0;
+  if (in_flight >= 0) s->in_flight[(size_t)slot] = in_flight ? 1 : 0;
+  return EB_OK;
+}
+
+// The reference's plan_evictions (crates/eidola-app-core/src/local_models.rs:653-701) with pages for bytes and sequences
+// for engines: nothing to do when the request fits; otherwise least recently used first, but only sequences that are
+// neither pinned nor part of a step in flight, and only as many as needed; when even that cannot make room, refuse and
+// change nothing (message: what is holding the pages).
+int32_t eb_sched_plan_evictions(const eb_sched* s, int32_t context_len, int32_t* evict_slots, int32_t cap, int32_t* n_evict) {
+  EB_REQUIRE(s && n_evict && (evict_slots || cap == 0) && cap >= 0, EB_ERR_ARG, "eb_sched_plan_evictions: bad argument");
+  EB_REQUIRE(context_len >= 0, EB_ERR_ARG, "eb_sched_plan_evictions: negative length %d", context_len);
+  *n_evict = 0;
+  const int32_t required = pages_for(s, context_len);
+  EB_REQUIRE(required <= s->max_pages && required <= s->num_pages, EB_ERR_NOMEM,
+             "eb_sched_plan_evictions: the sequence needs %d pages but the budget is %d (a sequence may hold %d)", required,
+             s->num_pages, s->max_pages);
+  int64_t free_pages = (int64_t)s->free_list.size();
+  bool slot_free = false;
+  for (int32_t i = 0; i < s->max_seqs; ++i) slot_free |= s->len[(size_t)i] < 0;
+  if (free_pages >= required && slot_free) return EB_OK;
+  std::vector<int32_t> cand;
+  int64_t held = 0;
+  for (int32_t i = 0; i < s->max_seqs; ++i) {
+    if (s->len[(size_t)i] < 0) continue;
+    if (s->pinned[(size_t)i] || s->in_flight[(size_t)i])
+      held += pages_for(s, s->len[(size_t)i]);
+    else
+      cand.push_back(i);
+  }
+  std::stable_sort(cand.begin(), cand.end(), [&](int32_t a, int32_t b) { return s->last_used[(size_t)a] < s->last_used[(size_t)b]; });
+  int32_t n = 0;
+  for (int32_t slot : cand) {
+    if (free_pages >= required && (slot_free || n > 0)) break;
+    free_pages += pages_for(s, s->len[(size_t)slot]);
+    if (n < cap) evict_slots[n] = slot;
+    ++n;
+  }
+  if (!(free_pages >= required && (slot_free || n > 0)))
+    return eb::fail(EB_ERR_NOMEM, "eb_sched_plan_evictions: the sequence needs %d pages, but %lld pages are held by pinned or in-use "
+                    "sequences", required, (long long)held);
+  EB_REQUIRE(n <= cap, EB_ERR_ARG, "eb_sched_plan_evictions: %d evictions needed, room for %d", n, cap);
+  *n_evict = n;
+  return EB_OK;
+}
+
+// Plan and reserve in one call (the reference does both inside one critical section, local_models.rs:441-485): the
+// victims are released and the new sequence admitted, or nothing changes.
+int32_t eb_sched_admit_evicting(eb_sched* s, int32_t context_len, int64_t now, int32_t* slot, int32_t* evict_slots, int32_t cap,
+                                int32_t* n_evict) {
+  EB_REQUIRE(s && slot && n_evict, EB_ERR_ARG, "eb_sched_admit_evicting: null");
+  int32_t rc = eb_sched_plan_evictions(s, context_len, evict_slots, cap, n_evict);
+  if (rc != EB_OK) return rc;
+  for (int32_t i = 0; i < *n_evict; ++i) {
+    rc = eb_sched_release(s, evict_slots[i]);
+    if (rc != EB_OK) return rc;
+  }
+  rc = eb_sched_admit(s, context_len, slot);
+  if (rc == EB_OK) s->last_used[(size_t)*slot] = now;
+  return rc;
 }
 
 int32_t eb_sched_free_pages(const eb_sched* s, int32_t* n) {

@@ -373,6 +373,19 @@ class Engine:
         self._last_T = T
         return nxt, mg
 
+    def prefill(self, slots, prompts):
+        """eb_engine_prefill: `prompts` is a list of token-id arrays.  Returns (first generated token per sequence, its
+        margin, steps run, summed device milliseconds)."""
+        slots = _i32(slots)
+        lens = _i32([len(p) for p in prompts])
+        flat = _i32(np.concatenate([np.asarray(p, I32) for p in prompts]))
+        nxt, mg = np.empty(len(slots), I32), np.empty(len(slots), np.float32)
+        steps, ms = c_i32(0), c_f32(0)
+        call("eb_engine_prefill", self._h, ptr(slots), ptr(lens), c_i32(len(slots)), ptr(flat), ptr(nxt), ptr(mg), C.byref(steps),
+             C.byref(ms))
+        self._last_T = 0
+        return nxt, mg, int(steps.value), float(ms.value)
+
     def step_launch(self, slots, q_lens, tokens) -> None:
         slots, q_lens, tokens = _i32(slots), _i32(q_lens), _i32(tokens)
         self._last_T = int(q_lens.sum())

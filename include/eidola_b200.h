@@ -142,6 +142,18 @@ int32_t eb_sched_extend(eb_sched* s, int32_t slot, int32_t new_len);
 /* Roll a sequence back to `new_len` tokens (rejected draft tokens); whole pages past the end are returned. */
 int32_t eb_sched_truncate(eb_sched* s, int32_t slot, int32_t new_len);
 int32_t eb_sched_release(eb_sched* s, int32_t slot);
+/* Admission with eviction: the reference's memory-pool planner (`plan_evictions`, crates/eidola-app-core/src/
+ * local_models.rs:653-701: least recently used first, never a pinned engine nor one serving a turn, refuse without
+ * unloading anything when that cannot make room) and its plan-and-reserve critical section (`reserve_engine`,
+ * local_models.rs:441-485), with 16-token pages for bytes and sequences for engines.
+ * eb_sched_touch records a use (`now` is any monotonic tick of the caller); eb_sched_set_flags sets pinned / in_flight
+ * (-1 = leave as is); eb_sched_plan_evictions only plans (victims in LRU order; nothing changes);
+ * eb_sched_admit_evicting releases the victims and admits, or returns EB_ERR_NOMEM having changed nothing. */
+int32_t eb_sched_touch(eb_sched* s, int32_t slot, int64_t now);
+int32_t eb_sched_set_flags(eb_sched* s, int32_t slot, int32_t pinned, int32_t in_flight);
+int32_t eb_sched_plan_evictions(const eb_sched* s, int32_t context_len, int32_t* evict_slots, int32_t cap, int32_t* n_evict);
+int32_t eb_sched_admit_evicting(eb_sched* s, int32_t context_len, int64_t now, int32_t* slot, int32_t* evict_slots, int32_t cap,
+                                int32_t* n_evict);
 int32_t eb_sched_free_pages(const eb_sched* s, int32_t* n);
 int32_t eb_sched_seq_len(const eb_sched* s, int32_t slot, int32_t* len);
 /* Block table of all slots: [max_seqs][max_pages_per_seq] int32, unused entries -1.  The pointer stays valid
@@ -497,6 +509,12 @@ int32_t eb_engine_memory(const eb_engine* e, int64_t* weight_bytes, int64_t* kv_
 int32_t eb_engine_kv_fill_synth(eb_engine* e);
 /* Scheduler of this engine (continuous batching): admit / release between steps. */
 int32_t eb_engine_seq_admit(eb_engine* e, int32_t context_len, int32_t* slot);
+/* The same through eb_sched_admit_evicting: idle sequences are released, least recently stepped first, to make room
+ * (h_evicted receives their slots; their owners must re-admit and prefill them if they come back).  A sequence is
+ * "used" whenever a step includes it. */
+int32_t eb_engine_seq_admit_evicting(eb_engine* e, int32_t context_len, int32_t* slot, int32_t* h_evicted, int32_t cap,
+                                     int32_t* n_evicted);
+int32_t eb_engine_seq_pin(eb_engine* e, int32_t slot, int32_t pinned);
 int32_t eb_engine_seq_release(eb_engine* e, int32_t slot);
 int32_t eb_engine_seq_truncate(eb_engine* e, int32_t slot, int32_t new_len);
 /* Roll n sequences back in one call (after a verify step: new length = old length + accepted drafts + 1). */
@@ -510,6 +528,17 @@ int32_t eb_engine_sched(eb_engine* e, eb_sched** sched); /* borrowed; lives as l
  */
 int32_t eb_engine_step(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
                        const int32_t* h_tokens, int32_t* h_next, float* h_margin);
+/*
+ * Prefill: run the prompts of n_seqs admitted sequences (h_n_tokens[i] tokens each, flat in h_tokens in sequence order)
+ * through every layer, so that their K and V are in the paged cache, in chunks of up to max_q_len tokens per sequence
+ * and max_tokens rows per step -- the same kernels, pages and block tables as decode and draft verification (a chunk
+ * is causal among its own tokens and sees everything before it).  h_next[i] / h_margin[i] receive the greedy token and
+ * top-2 margin after the LAST prompt token of sequence i: the first generated token.  What the reference's client
+ * sends as `messages` and its engine turns into a prompt (crates/eidola-app-core/src/lib.rs:10812-10825) ends up here
+ * as token ids.  steps_run / device_ms (may be NULL): steps taken and their summed device time.
+ */
+int32_t eb_engine_prefill(eb_engine* e, const int32_t* h_slots, const int32_t* h_n_tokens, int32_t n_seqs, const int32_t* h_tokens,
+                          int32_t* h_next, float* h_margin, int32_t* steps_run, float* device_ms);
 /* The same split in two so a caller can overlap host work: launch, then wait for the results. */
 int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
                               const int32_t* h_tokens);

@@ -26,6 +26,26 @@ def eb_hash(seed: int, stream: int, idx: int) -> int:
     return z
 
 
+def plan_evictions(required, budget, entries):
+    """The reference's pure eviction planner (crates/eidola-app-core/src/local_models.rs:653-701), restated: `entries` is a
+    list of (key, footprint, last_used, pinned, in_flight) in registry order.  Returns the keys to evict, least recently
+    used first and only as many as needed, [] when the request already fits, or a string starting with "budget" /
+    "held" when it cannot fit (nothing is evicted then)."""
+    if required > budget:
+        return "budget"
+    free = max(0, budget - sum(e[1] for e in entries))
+    if free >= required:
+        return []
+    cand = sorted((e for e in entries if not e[3] and not e[4]), key=lambda e: e[2])
+    out = []
+    for e in cand:
+        if free >= required:
+            break
+        free += e[1]
+        out.append(e[0])
+    return out if free >= required else "held"
+
+
 class Sched:
     def __init__(self, num_pages, page_size, max_seqs, max_pages, seed):
         self.page_size, self.max_seqs, self.max_pages = page_size, max_seqs, max_pages

@@ -1,0 +1,94 @@
+"""GPU: chunked prefill through the decode / verify kernels -- the cache the engine fills itself must be the cache the
+oracle fills, and chunking must not matter."""
+import numpy as np
+import pytest
+
+from oracle import binding as orc
+from oracle import sched as osched
+from tests.decoder_cases import tiny_config
+from tests.helpers import bf16_to_f32
+
+pytestmark = pytest.mark.gpu
+
+PROMPTS = [7, 33, 12, 50]
+
+
+def _prompts(cfg, seed=3):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, cfg.vocab, size=n).astype(np.int32) for n in PROMPTS]
+
+
+def _oracle_prefill(cfg, prompts, chunk):
+    """The oracle fed the same chunks: returns (first generated tokens, margins, the model and scheduler afterwards)."""
+    model = orc.Model(cfg)
+    sch = osched.Sched(cfg.num_pages, cfg.page_size, cfg.max_seqs, cfg.max_pages_per_seq, cfg.seed)
+    slots = [sch.admit(0) for _ in prompts]
+    done = [0] * len(prompts)
+    first, margin = [None] * len(prompts), [None] * len(prompts)
+    while any(d < len(p) for d, p in zip(done, prompts)):
+        b = [i for i in range(len(prompts)) if done[i] < len(prompts[i])]
+        q = [min(chunk, len(prompts[i]) - done[i]) for i in b]
+        toks = np.concatenate([prompts[i][done[i]:done[i] + qq] for i, qq in zip(b, q)])
+        for i, qq in zip(b, q):
+            sch.extend(slots[i], sch.len[slots[i]] + qq)
+        p = sch.pack([slots[i] for i in b], q)
+        p.update(slots=[slots[i] for i in b], n_tokens=int(sum(q)))
+        r = model.step(p, toks, np.array(sch.tables, np.int32))
+        row = 0
+        for i, qq in zip(b, q):
+            row += qq
+            done[i] += qq
+            if done[i] == len(prompts[i]):
+                first[i], margin[i] = int(r["next"][row - 1]), float(r["margin"][row - 1])
+    return first, margin, model, sch, slots
+
+
+def test_prefill_fills_the_cache_the_oracle_fills(gpu):
+    import eidola_b200 as eb
+    cfg = tiny_config()
+    prompts = _prompts(cfg)
+    want_first, want_margin, model, sch, oslots = _oracle_prefill(cfg, prompts, cfg.max_q_len)
+    eng = eb.Engine(cfg)
+    slots = [eng.admit(0) for _ in prompts]
+    first, margin, steps, ms = eng.prefill(slots, prompts)
+    assert steps == -(-max(PROMPTS) // cfg.max_q_len) and ms > 0
+    assert [eng.seq_len(s) for s in slots] == PROMPTS
+    assert np.array_equal(eng.block_tables(), np.array(sch.tables, np.int32))  # the same pages in the same order
+    for i in range(len(prompts)):
+        if want_margin[i] > 0.05:
+            assert first[i] == want_first[i], (i, first[i], want_first[i], want_margin[i])
+    # one more decode step on both: the logits depend on every K and V the prefill wrote
+    toks = np.array(want_first, np.int32)
+    nxt, _ = eng.step(slots, [1] * 4, toks)
+    for s in oslots:
+        sch.extend(s, sch.len[s] + 1)
+    p = sch.pack(oslots, [1] * 4)
+    p.update(slots=oslots, n_tokens=4)
+    ref = model.step(p, toks, np.array(sch.tables, np.int32))
+    err = np.abs(bf16_to_f32(eng.read_logits()) - bf16_to_f32(ref["logits"])).max()
+    print(f"prefill: {steps} steps; decode step after it: max |logit diff| vs oracle {err:.4f}")
+    assert err <= 0.1
+
+
+def test_prefill_chunking_does_not_matter(gpu):
+    """Chunks of five tokens and token-by-token decode steps leave the same context behind: the next step's logits agree
+    (different kernels shapes computed them, so to rounding, not bit for bit)."""
+    import eidola_b200 as eb
+    cfg = tiny_config()
+    prompts = _prompts(cfg, seed=4)
+    a = eb.Engine(cfg)
+    sa = [a.admit(0) for _ in prompts]
+    first_a, _, _, _ = a.prefill(sa, prompts)
+    b = eb.Engine(cfg)
+    sb = [b.admit(0) for _ in prompts]
+    for t in range(max(PROMPTS)):
+        live = [i for i in range(4) if t < PROMPTS[i]]
+        b.step([sb[i] for i in live], [1] * len(live), [int(prompts[i][t]) for i in live])
+    toks = np.array(first_a, np.int32)
+    a.step(sa, [1] * 4, toks)
+    b.step(sb, [1] * 4, toks)
+    err = np.abs(bf16_to_f32(a.read_logits()) - bf16_to_f32(b.read_logits())).max()
+    print(f"chunked vs token-by-token prefill: max |logit diff| {err:.4f}")
+    assert err <= 0.1
+    with pytest.raises(eb.EbError):
+        a.prefill(sa[:1], [np.zeros(0, np.int32)])
