@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "common.h"
+#include "loader.h"
 
 namespace {
 
@@ -883,6 +884,134 @@ int32_t eb_engine_memory(const eb_engine* e, int64_t* weight_bytes, int64_t* kv_
   if (weight_bytes) *weight_bytes = e->weight_bytes;
   if (kv_bytes) *kv_bytes = e->kv_bytes;
   if (work_bytes) *work_bytes = e->work_bytes;
+  return EB_OK;
+}
+
+namespace {
+
+struct LoadCtx {
+  eb::GgufFile gg;
+  std::vector<float> host;   // one band of rows as fp32
+  float* d_f32 = nullptr;    // the same on the device
+  uint8_t* d_codes = nullptr;  // its e4m3 codes, row-major, before tiling
+  int64_t band_rows = 8192, max_cols = 0;
+  ~LoadCtx() {
+    if (d_f32) cudaFree(d_f32);
+    if (d_codes) cudaFree(d_codes);
+  }
+};
+
+// Tensor `name` must exist with `cols` columns and rows_total * groups rows (GGUF extents are innermost first).
+int32_t find_tensor(LoadCtx& L, const std::string& name, int64_t groups, int64_t rows_total, int64_t cols, const eb::GgufTensor** out) {
+  const eb::GgufTensor* t = L.gg.find(name);
+  EB_REQUIRE(t, EB_ERR_ARG, "eb_engine_load_gguf: tensor %s is missing", name.c_str());
+  EB_REQUIRE(t->ne[0] == cols && t->elements() == groups * rows_total * cols, EB_ERR_ARG,
+             "eb_engine_load_gguf: tensor %s has %lld elements in rows of %lld, the configuration needs %lld x %lld x %lld", name.c_str(),
+             (long long)t->elements(), (long long)t->ne[0], (long long)groups, (long long)rows_total, (long long)cols);
+  *out = t;
+  return EB_OK;
+}
+
+// rows [src_row0, +nrows) of group `src_group` of tensor t, fp32 on the device (d_f32, row pitch = cols_total)
+int32_t stage_rows(eb_engine* e, LoadCtx& L, const eb::GgufTensor& t, int64_t rows_total, int64_t cols_total, int64_t src_group,
+                   int64_t src_row0, int64_t nrows) {
+  EB_TRY(L.gg.read_f32(t, (src_group * rows_total + src_row0) * cols_total, nrows * cols_total, L.host.data()));
+  EB_CUDA(cudaMemcpyAsync(L.d_f32, L.host.data(), (size_t)(nrows * cols_total) * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+  EB_CUDA(cudaStreamSynchronize(e->stream));  // the host band is reused by the next read
+  return EB_OK;
+}
+
+// A linear layer's rows [src_row0, +nrows) x columns [col0, +ncols) -> e4m3 + block scales -> tiles at weight-row block
+// dst_row0 / 128 of group dst_group of w (whose groups have rows_per_group rows).  Bands start on 128-row boundaries.
+int32_t load_linear(eb_engine* e, LoadCtx& L, const eb::GgufTensor& t, int64_t rows_total, int64_t cols_total, int64_t src_group,
+                    int64_t src_row0, int64_t nrows, int64_t col0, int64_t ncols, Fp8Weight* w, int64_t dst_group,
+                    int64_t rows_per_group, int64_t dst_row0, float* scales_dst) {
+  const int64_t KB = eb::cdiv(ncols, 128), NB = eb::cdiv(rows_per_group, 128);
+  for (int64_t r = 0; r < nrows; r += L.band_rows) {
+    const int64_t n = std::min(L.band_rows, nrows - r);
+    EB_TRY(stage_rows(e, L, t, rows_total, cols_total, src_group, src_row0 + r, n));
+    EB_TRY(eb_quant_weight_f32(L.d_f32 + col0, cols_total, n, ncols, L.d_codes, scales_dst + (r / 128) * KB, e->stream));
+    uint8_t* dst = w->codes + ((dst_group * NB + (dst_row0 + r) / 128) * KB) * (int64_t)(128 * 128);
+    EB_TRY(eb_weight_tile_fp8(L.d_codes, 1, (int32_t)n, (int32_t)ncols, dst, e->stream));
+  }
+  return EB_OK;
+}
+
+// A small tensor kept as it is: fp32 (to_bf16 = false) or bf16.
+int32_t load_plain(eb_engine* e, LoadCtx& L, const eb::GgufTensor& t, int64_t rows, int64_t cols, void* d_dst, bool to_bf16) {
+  for (int64_t r = 0; r < rows; r += L.band_rows) {
+    const int64_t n = std::min(L.band_rows, rows - r);
+    EB_TRY(stage_rows(e, L, t, rows, cols, 0, r, n));
+    if (to_bf16)
+      EB_TRY(eb_f32_to_bf16(L.d_f32, (uint16_t*)d_dst + r * cols, n * cols, e->stream));
+    else
+      EB_CUDA(cudaMemcpyAsync((float*)d_dst + r * cols, L.d_f32, (size_t)(n * cols) * sizeof(float), cudaMemcpyDeviceToDevice, e->stream));
+  }
+  return EB_OK;
+}
+
+}  // namespace
+
+int32_t eb_engine_load_gguf(eb_engine* e, const char* path) {
+  EB_REQUIRE(e && path, EB_ERR_ARG, "eb_engine_load_gguf: null");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_load_gguf: a step is in flight");
+  const eb_config& c = e->c;
+  const int64_t H = c.hidden, I = c.inter, E = e->e_l, D = c.head_dim;
+  const int64_t hqd_g = (int64_t)c.n_q_heads * D, hkd_g = (int64_t)c.n_kv_heads * D, nqkv_g = hqd_g + 2 * hkd_g;
+  LoadCtx L;
+  EB_TRY(L.gg.open(path));
+  L.max_cols = std::max(std::max(H, I), hqd_g);
+  L.host.resize((size_t)(L.band_rows * L.max_cols));
+  EB_CUDA(cudaMalloc((void**)&L.d_f32, (size_t)(L.band_rows * L.max_cols) * sizeof(float)));
+  EB_CUDA(cudaMalloc((void**)&L.d_codes, (size_t)(L.band_rows * L.max_cols)));
+  const eb::GgufTensor* t = nullptr;
+  const int64_t kv_row0 = ((int64_t)e->tp_rank * e->hkv_l * D) / 128 * 128;
+  char name[128];
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer& Ly = e->layers[(size_t)l];
+    snprintf(name, sizeof(name), "blk.%d.attn_qkv.weight", l);
+    EB_TRY(find_tensor(L, name, 1, nqkv_g, H, &t));
+    const int64_t band_rows[3] = {e->hqd, e->kv_band, e->kv_band};
+    const int64_t band_src[3] = {(int64_t)e->tp_rank * e->hqd, hqd_g + kv_row0, hqd_g + hkd_g + kv_row0};
+    int64_t dst_row = 0;
+    for (int b = 0; b < 3; ++b) {
+      EB_TRY(load_linear(e, L, *t, nqkv_g, H, 0, band_src[b], band_rows[b], 0, H, &Ly.wqkv, 0, e->nqkv, dst_row,
+                         Ly.wqkv.scales + (dst_row / 128) * e->kbH));
+      dst_row += band_rows[b];
+    }
+    snprintf(name, sizeof(name), "blk.%d.attn_output.weight", l);
+    EB_TRY(find_tensor(L, name, 1, H, hqd_g, &t));
+    EB_TRY(load_linear(e, L, *t, H, hqd_g, 0, 0, H, (int64_t)e->tp_rank * e->hqd, e->hqd, &Ly.wo, 0, H, 0, Ly.wo.scales));
+    snprintf(name, sizeof(name), "blk.%d.ffn_gate_up_exps.weight", l);
+    EB_TRY(find_tensor(L, name, c.n_experts, 2 * I, H, &t));
+    const eb::GgufTensor* td = nullptr;
+    snprintf(name, sizeof(name), "blk.%d.ffn_down_exps.weight", l);
+    EB_TRY(find_tensor(L, name, c.n_experts, H, I, &td));
+    const int64_t s1 = eb::cdiv(2 * I, 128) * e->kbH, s2 = eb::cdiv(H, 128) * e->kbI;
+    for (int64_t x = 0; x < E; ++x) {
+      EB_TRY(load_linear(e, L, *t, 2 * I, H, e->e0 + x, 0, 2 * I, 0, H, &Ly.w1, x, 2 * I, 0, Ly.w1.scales + x * s1));
+      EB_TRY(load_linear(e, L, *td, H, I, e->e0 + x, 0, H, 0, I, &Ly.w2, x, H, 0, Ly.w2.scales + x * s2));
+    }
+    snprintf(name, sizeof(name), "blk.%d.ffn_gate_inp.weight", l);
+    EB_TRY(find_tensor(L, name, 1, c.n_experts, H, &t));
+    EB_TRY(load_plain(e, L, *t, c.n_experts, H, Ly.wr, true));
+    snprintf(name, sizeof(name), "blk.%d.attn_sinks.weight", l);
+    EB_TRY(find_tensor(L, name, 1, 1, c.n_q_heads, &t));
+    EB_TRY(load_plain(e, L, *t, 1, c.n_q_heads, Ly.sinks, false));
+    snprintf(name, sizeof(name), "blk.%d.attn_norm.weight", l);
+    EB_TRY(find_tensor(L, name, 1, 1, H, &t));
+    EB_TRY(load_plain(e, L, *t, 1, H, Ly.g_attn, false));
+    snprintf(name, sizeof(name), "blk.%d.ffn_norm.weight", l);
+    EB_TRY(find_tensor(L, name, 1, 1, H, &t));
+    EB_TRY(load_plain(e, L, *t, 1, H, Ly.g_mlp, false));
+  }
+  EB_TRY(find_tensor(L, "token_embd.weight", 1, c.vocab, H, &t));
+  EB_TRY(load_plain(e, L, *t, c.vocab, H, e->embed, true));
+  EB_TRY(find_tensor(L, "output.weight", 1, c.vocab, H, &t));
+  EB_TRY(load_linear(e, L, *t, c.vocab, H, 0, e->v0, e->v1 - e->v0, 0, H, &e->lm, 0, e->v1 - e->v0, 0, e->lm.scales));
+  EB_TRY(find_tensor(L, "output_norm.weight", 1, 1, H, &t));
+  EB_TRY(load_plain(e, L, *t, 1, H, e->g_final, false));
+  EB_CUDA(cudaStreamSynchronize(e->stream));
   return EB_OK;
 }
 

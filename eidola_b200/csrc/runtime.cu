@@ -309,6 +309,38 @@ __global__ void synth_weight_fp8_kernel(uint8_t* codes, float* scales, int64_t c
   }
 }
 
+// The same quantiser on values read from memory: fp32 weights [nrows][ld] (cols used) -> e4m3 codes [nrows][cols] and one
+// scale per 128x128 block.  One CTA per block, the arithmetic of synth_weight_fp8_kernel operation for operation.
+__global__ void quant_weight_f32_kernel(const float* w, int64_t ld, int64_t nrows, int64_t cols, uint8_t* codes, float* scales) {
+  const int64_t cb = (cols + 127) / 128;
+  const int64_t br = blockIdx.x / cb, bc = blockIdx.x % cb;
+  const int64_t r_lo = br * 128, c_lo = bc * 128;
+  const int r_n = (int)min((int64_t)128, nrows - r_lo), c_n = (int)min((int64_t)128, cols - c_lo);
+  __shared__ float red[8];
+  float amax = 0.f;
+  for (int e = threadIdx.x; e < r_n * c_n; e += blockDim.x) {
+    const int r = e / c_n, c = e % c_n;
+    amax = fmaxf(amax, fabsf(w[(r_lo + r) * ld + c_lo + c]));
+  }
+  for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+  for (int x = 1; x < (int)(blockDim.x >> 5); ++x) amax = fmaxf(amax, red[x]);
+  const float s = amax > 0.f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+  if (threadIdx.x == 0) scales[br * cb + bc] = s;
+  for (int e = threadIdx.x; e < r_n * c_n; e += blockDim.x) {
+    const int r = e / c_n, c = e % c_n;
+    codes[(r_lo + r) * cols + c_lo + c] = eb_f32_to_e4m3(__fdiv_rn(w[(r_lo + r) * ld + c_lo + c], s));
+  }
+}
+
+__global__ void f32_to_bf16_kernel(const float* in, uint16_t* out, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) out[i] = eb_f32_to_bf16(in[i]);
+}
+
 // Local KV heads [head0, head0 + n_local) of a cache whose global layout is [pages][2][n_total][page][dim]:
 // element i of the local cache takes the value of its global index, so every rank fills the same global tensor.
 __global__ void synth_kv_heads_kernel(uint16_t* out, int64_t n, int n_total, int head0, int n_local, int head_elems,
@@ -408,6 +440,24 @@ int32_t eb_synth_weight_fp8_slice(void* d_codes, void* d_scales, int64_t rows_to
   EB_REQUIRE(blocks < (1ll << 31), EB_ERR_ARG, "eb_synth_weight_fp8_slice: too many blocks");
   synth_weight_fp8_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>((uint8_t*)d_codes, (float*)d_scales, ncols,
                                                                            row0, nrows, seed, sid, std, cols_total, col0);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_quant_weight_f32(const float* d_w, int64_t ld, int64_t nrows, int64_t cols, void* d_codes, void* d_scales, void* stream) {
+  EB_REQUIRE(d_w && d_codes && d_scales && nrows > 0 && cols > 0 && ld >= cols, EB_ERR_ARG, "eb_quant_weight_f32: bad argument");
+  const int64_t blocks = eb::cdiv(nrows, 128) * eb::cdiv(cols, 128);
+  EB_REQUIRE(blocks < (1ll << 31), EB_ERR_ARG, "eb_quant_weight_f32: too many blocks");
+  quant_weight_f32_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(d_w, ld, nrows, cols, (uint8_t*)d_codes, (float*)d_scales);
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
+int32_t eb_f32_to_bf16(const float* d_in, void* d_out, int64_t n, void* stream) {
+  EB_REQUIRE(d_in && d_out && n >= 0, EB_ERR_ARG, "eb_f32_to_bf16: bad argument");
+  if (n == 0) return EB_OK;
+  const int64_t blocks = std::min<int64_t>(eb::cdiv(n, 256), 148 * 32);
+  f32_to_bf16_kernel<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(d_in, (uint16_t*)d_out, n);
   EB_LAUNCH_CHECK();
   return EB_OK;
 }

@@ -332,6 +332,9 @@ class Engine:
         call("eb_engine_memory", self._h, C.byref(w), C.byref(k), C.byref(x))
         return {"weights": w.value, "kv": k.value, "work": x.value}
 
+    def load_gguf(self, path: str) -> None:
+        call("eb_engine_load_gguf", self._h, C.c_char_p(str(path).encode()))
+
     def kv_fill_synth(self) -> None:
         call("eb_engine_kv_fill_synth", self._h)
 

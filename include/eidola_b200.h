@@ -120,6 +120,10 @@ int32_t eb_synth_weight_fp8(void* d_codes, void* d_scales, int64_t rows_total, i
 int32_t eb_synth_weight_fp8_slice(void* d_codes, void* d_scales, int64_t rows_total, int64_t cols_total, int64_t row0,
                                   int64_t nrows, int64_t col0, int64_t ncols, uint64_t seed, uint64_t stream_id,
                                   float std, void* stream);
+/* Checkpoint weights: fp32 [nrows][ld] (the first `cols` of each row) -> e4m3 codes [nrows][cols] + one fp32 scale per
+ * 128x128 block (scale = block amax / 448, codes = rne(w / scale) saturating), the quantiser the seeded weights use. */
+int32_t eb_quant_weight_f32(const float* d_w, int64_t ld, int64_t nrows, int64_t cols, void* d_codes, void* d_scales, void* stream);
+int32_t eb_f32_to_bf16(const float* d_in, void* d_out, int64_t n, void* stream);
 /* KV heads [head0, head0+n_kv_local) of a cache filled with N(0,1) values indexed by their position in the global
  * layout [pages][2][n_kv_total][page_size][head_dim], so every rank holds its slice of one global tensor. */
 int32_t eb_synth_kv_heads_bf16(void* d_cache, int64_t num_pages, int32_t n_kv_total, int32_t head0, int32_t n_kv_local,
@@ -504,6 +508,22 @@ int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_si
 int32_t eb_engine_destroy(eb_engine* e);
 /* Device bytes held by weights, KV pages and workspaces. */
 int32_t eb_engine_memory(const eb_engine* e, int64_t* weight_bytes, int64_t* kv_bytes, int64_t* work_bytes);
+/*
+ * Replace the seeded weights by a checkpoint in GGUF, the container the reference's client downloads and keeps on disk
+ * (crates/eidola-app-core/src/local_models.rs:29-34, 1310-1385).  Tensors (F32, F16 or BF16; rows of `cols` elements):
+ *   token_embd.weight [vocab][hidden]            output.weight [vocab][hidden]            output_norm.weight [hidden]
+ *   blk.L.attn_norm.weight [hidden]              blk.L.ffn_norm.weight [hidden]           blk.L.attn_sinks.weight [n_q_heads]
+ *   blk.L.attn_qkv.weight [(n_q + 2 n_kv) * head_dim][hidden]   (q heads, then k heads, then v heads)
+ *   blk.L.attn_output.weight [hidden][n_q * head_dim]
+ *   blk.L.ffn_gate_inp.weight [experts][hidden]                 (router)
+ *   blk.L.ffn_gate_up_exps.weight [experts][2 * inter][hidden]  (gate rows, then up rows)
+ *   blk.L.ffn_down_exps.weight [experts][hidden][inter]
+ * The linear layers are quantised on the device to e4m3 with 128x128 block scales (eb_quant_weight_f32) and stored as
+ * tiles; embeddings and router become bf16; norms and sinks stay fp32.  A tensor-parallel rank reads only its own rows,
+ * columns and experts.  Quantised GGUF types are refused.  Returns EB_ERR_ARG naming the tensor when one is missing or
+ * has the wrong shape; the engine's weights are then partly replaced and it must be reloaded or destroyed.
+ */
+int32_t eb_engine_load_gguf(eb_engine* e, const char* path);
 /* Stand-in for prefill: fill every KV page of every layer with seeded N(0,1) values (element i of layer l is
  * eb_normal(seed, 20000 + l, i)), so a sequence admitted with a context length has keys and values to attend to. */
 int32_t eb_engine_kv_fill_synth(eb_engine* e);
