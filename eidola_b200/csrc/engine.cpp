@@ -1273,12 +1273,16 @@ int32_t eb_engine_prefill(eb_engine* e, const int32_t* h_slots, const int32_t* h
     b_tok.clear();
     b_seq.clear();
     int32_t rows = 0;
+    bool skipped = false;
     for (int k = 0; k < n_seqs; ++k) {
       const int i = (start + k) % n_seqs;
       const int32_t rem = h_n_tokens[i] - done[(size_t)i];
       if (rem <= 0) continue;
       const int32_t q = std::min(rem, c.max_q_len);
-      if (rows + q > c.max_tokens) continue;
+      if (rows + q > c.max_tokens) {
+        skipped = true;
+        continue;
+      }
       b_slots.push_back(h_slots[i]);
       b_q.push_back(q);
       b_seq.push_back(i);
@@ -1300,7 +1304,7 @@ int32_t eb_engine_prefill(eb_engine* e, const int32_t* h_slots, const int32_t* h
         if (h_margin) h_margin[i] = margin[(size_t)row - 1];
       }
     }
-    start = (start + 1) % n_seqs;
+    if (skipped) start = (start + 1) % n_seqs;  // only a batch too wide for one step changes the order of the sequences
   }
   if (steps_run) *steps_run = steps;
   if (device_ms) *device_ms = ms;
