@@ -343,6 +343,17 @@ class Engine:
         call("eb_engine_seq_admit", self._h, c_i32(context_len), C.byref(slot))
         return int(slot.value)
 
+    def admit_evicting(self, context_len: int):
+        """eb_engine_seq_admit_evicting: (slot, slots evicted to make room)."""
+        cap = int(self.cfg.max_seqs)
+        slot, n = c_i32(-1), c_i32(0)
+        ev = (C.c_int32 * cap)()
+        call("eb_engine_seq_admit_evicting", self._h, c_i32(context_len), C.byref(slot), ev, c_i32(cap), C.byref(n))
+        return int(slot.value), [int(ev[i]) for i in range(n.value)]
+
+    def pin(self, slot: int, pinned: bool = True) -> None:
+        call("eb_engine_seq_pin", self._h, c_i32(slot), c_i32(1 if pinned else 0))
+
     def release(self, slot: int) -> None:
         call("eb_engine_seq_release", self._h, c_i32(slot))
 

@@ -1,0 +1,325 @@
+"""An engine process that honours the `llama-server` contract of the reference's client.
+
+The reference's client starts its local engine as a child process
+
+    <engine> -m <model.gguf> --host 127.0.0.1 --port P --alias <model id> -c 8192 -ngl 999 --jinja --no-webui
+
+(crates/eidola-app-core/src/local_models.rs:1612-1626), waits for `GET /health` to answer 200 within 300 s
+(local_models.rs:2020-2064), then posts `{model, messages, max_completion_tokens, [stream, stream_options]}` to
+`/v1/chat/completions` (crates/eidola-common/src/lib.rs:116-139) and reads either one JSON body or server-sent events
+whose `data:` lines carry `choices[0].delta.content`, a final `usage` object and `[DONE]`
+(crates/eidola-app-core/src/lib.rs:7232-7340).  This module is that process for libeidola_b200:
+
+    python -m eidola_b200.server -m model.gguf --host 127.0.0.1 --port 8080 --alias gpt-oss-20b -c 8192 -ngl 999 --jinja --no-webui
+
+One engine thread owns the engine handle (one thread per handle, as the reference's supervisor owns its child,
+local_models.rs:1633-1638) and runs continuous batching: requests that arrive are admitted (idle sequences are evicted,
+least recently used first, when the page pool is full), their prompts are prefilled together, and every iteration
+decodes one token for every live sequence.  HTTP threads only enqueue requests and drain per-request token queues.
+
+What this is NOT: the reference contains no tokenizer, chat template or sampler (they live inside the third-party
+engine), and neither does this library.  The tokenizer here is the identity on UTF-8 bytes (ids 0..255) with a plain
+`<|role|>` template, and decoding is greedy; a checkpoint with its own vocabulary needs its tokenizer in front.  With
+the random-init weights the replies are noise -- the process contract, the batching and the timings are what is real.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import queue
+import sys
+import threading
+import time
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+import numpy as np
+
+
+class ByteTokenizer:
+    """Token id = UTF-8 byte.  Ids at or above 256 (a model with a larger vocabulary produces them) print as '?'."""
+    eos = 0
+
+    @staticmethod
+    def encode(text: str) -> list[int]:
+        return list(text.encode("utf-8"))
+
+    @staticmethod
+    def template(messages) -> list[int]:
+        out: list[int] = []
+        for m in messages:
+            content = m.get("content") or ""
+            if isinstance(content, list):  # OpenAI content parts: keep the text parts
+                content = "".join(p.get("text", "") for p in content if isinstance(p, dict))
+            out += ByteTokenizer.encode("<|%s|>\n%s\n" % (m.get("role", "user"), content))
+        out += ByteTokenizer.encode("<|assistant|>\n")
+        return [b if b != 0 else 32 for b in out] or [32]
+
+    @staticmethod
+    def decode(ids) -> str:
+        return bytes((i if 0 < i < 256 else 63) for i in ids).decode("utf-8", errors="replace")
+
+
+class Request:
+    def __init__(self, prompt_ids, max_tokens):
+        self.prompt_ids, self.max_tokens = prompt_ids, max_tokens
+        self.out: "queue.Queue[tuple[str, object]]" = queue.Queue()  # ("token", id) ... ("done", usage) | ("error", message)
+        self.slot = None
+        self.generated = 0
+        self.t_arrive = time.perf_counter()
+
+
+class EngineLoop(threading.Thread):
+    """The thread that owns the engine.  `engine` needs admit_evicting(context_len) -> (slot, evicted), prefill(slots,
+    prompts) -> (first_tokens, ...), step(slots, q_lens, tokens) -> (next, margins), release(slot), and max_seqs /
+    context_tokens attributes: eidola_b200.host.Engine behind a thin adapter, or a scripted fake in the CPU tests."""
+
+    def __init__(self, engine, context_tokens: int):
+        super().__init__(daemon=True)
+        self.engine, self.context_tokens = engine, context_tokens
+        self.inbox: "queue.Queue[Request]" = queue.Queue()
+        self.live: dict[int, Request] = {}
+        self.last: dict[int, int] = {}
+        self.ready = threading.Event()
+        self.stop = threading.Event()
+        self.stats = {"steps": 0, "prefill_tokens": 0, "generated": 0, "evicted": 0}
+
+    def submit(self, req: Request) -> None:
+        self.inbox.put(req)
+
+    def _admit_new(self) -> None:
+        fresh = []
+        while len(self.live) + len(fresh) < self.engine.max_seqs:
+            try:
+                req = self.inbox.get(block=not self.live and not fresh, timeout=0.05)
+            except queue.Empty:
+                break
+            if len(req.prompt_ids) + req.max_tokens > self.context_tokens:
+                req.out.put(("error", "the request needs %d tokens of context, the engine was started with -c %d"
+                             % (len(req.prompt_ids) + req.max_tokens, self.context_tokens)))
+                continue
+            try:
+                slot, evicted = self.engine.admit_evicting(0)
+            except Exception as e:  # pool exhausted by live sequences: refuse, nothing changed
+                req.out.put(("error", "no room for another sequence: %s" % e))
+                continue
+            self.stats["evicted"] += len(evicted)
+            req.slot = slot
+            fresh.append(req)
+        if fresh:
+            first = self.engine.prefill([r.slot for r in fresh], [np.asarray(r.prompt_ids, np.int32) for r in fresh])[0]
+            for r, tok in zip(fresh, first):
+                self.stats["prefill_tokens"] += len(r.prompt_ids)
+                self.live[r.slot] = r
+                self._deliver(r, int(tok))
+
+    def _deliver(self, r: Request, tok: int) -> None:
+        r.generated += 1
+        self.stats["generated"] += 1
+        done = r.generated >= r.max_tokens or tok == ByteTokenizer.eos
+        if not (tok == ByteTokenizer.eos):
+            r.out.put(("token", tok))
+        if done:
+            r.out.put(("done", {"prompt_tokens": len(r.prompt_ids), "completion_tokens": r.generated,
+                                "total_tokens": len(r.prompt_ids) + r.generated}))
+            self.engine.release(r.slot)
+            self.live.pop(r.slot, None)
+            self.last.pop(r.slot, None)
+        else:
+            self.last[r.slot] = tok
+
+    def run(self) -> None:
+        self.ready.set()
+        while not self.stop.is_set():
+            try:
+                self._admit_new()
+                if not self.live:
+                    continue
+                slots = sorted(self.live)
+                nxt, _ = self.engine.step(slots, [1] * len(slots), [self.last[s] for s in slots])
+                self.stats["steps"] += 1
+                for s, tok in zip(slots, nxt):
+                    self._deliver(self.live[s], int(tok))
+            except Exception as e:  # an engine error ends every request in flight with a message, not a hang
+                for r in list(self.live.values()):
+                    r.out.put(("error", "engine: %s" % e))
+                self.live.clear()
+                self.last.clear()
+
+
+class EngineAdapter:
+    """eidola_b200.host.Engine with the three calls the loop needs."""
+
+    def __init__(self, eng, cfg):
+        self.eng, self.max_seqs = eng, cfg.max_seqs
+
+    def admit_evicting(self, context_len):
+        slot, evicted = self.eng.admit_evicting(context_len)
+        self.eng.pin(slot, True)  # a sequence that is being served is never a victim
+        return slot, evicted
+
+    def prefill(self, slots, prompts):
+        return self.eng.prefill(slots, prompts)
+
+    def step(self, slots, q_lens, tokens):
+        return self.eng.step(slots, q_lens, tokens)
+
+    def release(self, slot):
+        self.eng.release(slot)
+
+
+def make_handler(loop: EngineLoop, alias: str):
+    class Handler(BaseHTTPRequestHandler):
+        protocol_version = "HTTP/1.1"
+
+        def log_message(self, fmt, *args):  # stderr stays for failures: the client keeps its last 30 lines
+            pass
+
+        def _json(self, code, obj):
+            body = json.dumps(obj).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def do_GET(self):
+            if self.path.split("?")[0] == "/health":
+                if loop.ready.is_set():
+                    self._json(200, {"status": "ok"})
+                else:
+                    self._json(503, {"error": {"message": "loading model", "type": "unavailable_error", "code": 503}})
+            elif self.path.split("?")[0] == "/v1/models":
+                self._json(200, {"object": "list", "data": [{"id": alias, "object": "model", "owned_by": "eidola_b200"}]})
+            else:
+                self._json(404, {"error": {"message": "not found", "type": "not_found_error", "code": 404}})
+
+        def do_POST(self):
+            if self.path.split("?")[0] != "/v1/chat/completions":
+                return self._json(404, {"error": {"message": "not found", "type": "not_found_error", "code": 404}})
+            try:
+                n = int(self.headers.get("Content-Length", "0"))
+                body = json.loads(self.rfile.read(n) or b"{}")
+                messages = body["messages"]
+                assert isinstance(messages, list) and messages
+            except Exception:
+                return self._json(400, {"error": {"message": "body must be JSON with a non-empty `messages` array",
+                                                  "type": "invalid_request_error", "code": 400}})
+            if not loop.ready.is_set():
+                return self._json(503, {"error": {"message": "loading model", "type": "unavailable_error", "code": 503}})
+            max_tokens = int(body.get("max_completion_tokens") or body.get("max_tokens") or 256)
+            stream = bool(body.get("stream"))
+            include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
+            req = Request(ByteTokenizer.template(messages), max(1, max_tokens))
+            loop.submit(req)
+            rid, created = "chatcmpl-%x" % id(req), int(time.time())
+            base = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": body.get("model") or alias}
+            if not stream:
+                toks, usage = [], None
+                while True:
+                    kind, val = req.out.get()
+                    if kind == "token":
+                        toks.append(val)
+                    elif kind == "done":
+                        usage = val
+                        break
+                    else:
+                        return self._json(500, {"error": {"message": str(val), "type": "server_error", "code": 500}})
+                return self._json(200, {"id": rid, "object": "chat.completion", "created": created, "model": base["model"],
+                                        "choices": [{"index": 0, "finish_reason": "stop" if usage["completion_tokens"] < req.max_tokens else "length",
+                                                     "message": {"role": "assistant", "content": ByteTokenizer.decode(toks)}}],
+                                        "usage": usage})
+            self.send_response(200)
+            self.send_header("Content-Type", "text/event-stream")
+            self.send_header("Cache-Control", "no-cache")
+            self.send_header("Connection", "close")
+            self.end_headers()
+
+            def event(obj):
+                self.wfile.write(b"data: " + (obj if isinstance(obj, bytes) else json.dumps(obj).encode()) + b"\n\n")
+                self.wfile.flush()
+
+            try:
+                event(dict(base, choices=[{"index": 0, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]))
+                while True:
+                    kind, val = req.out.get()
+                    if kind == "token":
+                        event(dict(base, choices=[{"index": 0, "delta": {"content": ByteTokenizer.decode([val])}, "finish_reason": None}]))
+                    elif kind == "done":
+                        event(dict(base, choices=[{"index": 0, "delta": {}, "finish_reason": "stop" if val["completion_tokens"] < req.max_tokens else "length"}]))
+                        if include_usage:
+                            event(dict(base, choices=[], usage=val))
+                        event(b"[DONE]")
+                        break
+                    else:
+                        event({"error": {"message": str(val), "type": "server_error", "code": 500}})
+                        break
+            except (BrokenPipeError, ConnectionResetError):
+                pass  # the client went away; the sequence finishes and is released by the loop
+            self.close_connection = True
+
+    return Handler
+
+
+def serve(loop: EngineLoop, host: str, port: int, alias: str) -> ThreadingHTTPServer:
+    httpd = ThreadingHTTPServer((host, port), make_handler(loop, alias))
+    httpd.daemon_threads = True
+    return httpd
+
+
+def build_engine(args):
+    import eidola_b200 as eb
+    from eidola_b200.capi import make_config
+    eb.capi.call("eb_device_set", eb.capi.c_i32(args.device))
+    ctx = args.ctx
+    pages_per_seq = ctx // 16 + 2
+    shapes = {
+        "tiny": dict(n_layers=2, hidden=512, n_q_heads=8, n_kv_heads=2, n_experts=8, inter=512, vocab=4096),
+        "20b": dict(n_layers=24, hidden=2880, n_q_heads=64, n_kv_heads=8, n_experts=32, inter=2880, vocab=201088),
+    }[args.shape]
+    cfg = make_config(window=128, top_k=4, num_pages=args.seqs * pages_per_seq, max_seqs=args.seqs, max_pages_per_seq=pages_per_seq,
+                      max_tokens=args.seqs * 6, max_q_len=6, seed=args.seed, **shapes)
+    eng = eb.Engine(cfg)
+    if args.model and args.model.endswith(".gguf") and not args.random_init:
+        eng.load_gguf(args.model)
+    return EngineAdapter(eng, cfg)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("-m", "--model", default="")
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8080)
+    ap.add_argument("--alias", default="eidola-b200")
+    ap.add_argument("-c", "--ctx", type=int, default=8192)
+    ap.add_argument("-ngl", "--n-gpu-layers", type=int, default=999)  # everything runs on the GPU; accepted for the contract
+    ap.add_argument("--jinja", action="store_true")                   # the template is fixed; accepted for the contract
+    ap.add_argument("--no-webui", action="store_true")
+    ap.add_argument("--shape", default="20b", choices=["tiny", "20b"], help="decoder shape when the weights are random-init")
+    ap.add_argument("--random-init", action="store_true", help="ignore -m and use the seeded weights")
+    ap.add_argument("--seqs", type=int, default=64, help="concurrent sequences")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--device", type=int, default=0)
+    args = ap.parse_args(argv)
+    holder = {}
+    loop = EngineLoop(None, args.ctx)
+    httpd = serve(loop, args.host, args.port, args.alias)   # the socket answers 503 on /health while the model loads
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    try:
+        loop.engine = build_engine(args)
+    except Exception as e:  # the client shows the last lines of stderr when its engine exits
+        print("eidola_b200.server: cannot start the engine: %s" % e, file=sys.stderr, flush=True)
+        return 1
+    loop.start()
+    holder["loop"] = loop
+    try:
+        while loop.is_alive():
+            time.sleep(0.2)
+    except KeyboardInterrupt:
+        pass
+    loop.stop.set()
+    httpd.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,75 @@
+"""GPU: the engine process started the way the reference's client starts its engine -- the `llama-server` argv of
+crates/eidola-app-core/src/local_models.rs:1612-1626, stdin/stdout closed, stderr piped -- polled on /health like
+local_models.rs:2020-2064 and spoken to over /v1/chat/completions.  Weights: a GGUF checkpoint of the tiny decoder."""
+import json
+import os
+import socket
+import subprocess
+import sys
+import time
+import urllib.request
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from tests.decoder_cases import tiny_config
+from tests.gguf_writer import write_gguf
+from tests.test_gpu_loader import _seeded_tensors
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_engine_process_honours_the_llama_server_contract(gpu, tmp_path):
+    cfg = tiny_config()
+    model = tmp_path / "tiny.gguf"
+    write_gguf(model, _seeded_tensors(cfg))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    argv = [sys.executable, "-m", "eidola_b200.server", "-m", str(model), "--host", "127.0.0.1", "--port", str(port), "--alias",
+            "tiny@local", "-c", "256", "-ngl", "999", "--jinja", "--no-webui", "--shape", "tiny", "--seqs", "4"]
+    child = subprocess.Popen(argv, cwd=str(ROOT), stdin=subprocess.DEVNULL, stdout=subprocess.DEVNULL, stderr=subprocess.PIPE,
+                             env=dict(os.environ, PYTHONPATH=str(ROOT)))
+    url = "http://127.0.0.1:%d" % port
+    try:
+        deadline = time.time() + 120          # the client allows 300 s and polls every 250 ms
+        ready = False
+        while time.time() < deadline and child.poll() is None:
+            try:
+                ready = urllib.request.urlopen(url + "/health", timeout=2).status == 200
+            except Exception:
+                ready = False
+            if ready:
+                break
+            time.sleep(0.25)
+        assert ready, "engine never became healthy: " + (child.stderr.read().decode()[-2000:] if child.poll() is not None else "still loading")
+        body = {"model": "tiny@local", "messages": [{"role": "user", "content": "Hello"}], "max_completion_tokens": 12,
+                "stream": True, "stream_options": {"include_usage": True}}
+        req = urllib.request.Request(url + "/v1/chat/completions", data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+        t0 = time.perf_counter()
+        raw = urllib.request.urlopen(req, timeout=60).read().decode()
+        dt = time.perf_counter() - t0
+        chunks, usage, done = 0, None, False
+        for event in raw.split("\n\n"):
+            for line in event.splitlines():
+                if line.startswith("data:"):
+                    p = line[5:].lstrip()
+                    if p == "[DONE]":
+                        done = True
+                    else:
+                        j = json.loads(p)
+                        usage = j.get("usage") or usage
+                        chunks += bool(j.get("choices") and "content" in j["choices"][0]["delta"] and j["choices"][0]["delta"]["content"] != "")
+        assert done and usage and usage["completion_tokens"] >= 1 and usage["prompt_tokens"] > 10
+        # greedy decoding of fixed weights: the same request gives the same reply
+        blocking = dict(body, stream=False)
+        blocking.pop("stream_options")
+        a = json.load(urllib.request.urlopen(urllib.request.Request(url + "/v1/chat/completions", data=json.dumps(blocking).encode()), timeout=60))
+        b = json.load(urllib.request.urlopen(urllib.request.Request(url + "/v1/chat/completions", data=json.dumps(blocking).encode()), timeout=60))
+        assert a["choices"][0]["message"]["content"] == b["choices"][0]["message"]["content"] and a["usage"] == b["usage"]
+        print(f"engine process: healthy, streamed {chunks} content chunks and usage {usage} in {dt * 1e3:.1f} ms")
+    finally:
+        child.kill()                            # the client ends its engine with SIGKILL (kill_on_drop)
+        child.wait(timeout=30)

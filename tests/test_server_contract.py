@@ -1,0 +1,128 @@
+"""CPU: the engine process's HTTP contract against a scripted engine, read the way the reference's client reads it.
+
+The reference tests its engine boundary with a scripted peer on the other side of HTTP
+(crates/eidola-app-core/tests/chat_harness/mod.rs); here the roles are swapped: the server under test is ours, the
+engine behind it is scripted (next token = last token + 1), and the test plays the client: `/health` must answer 200,
+a blocking completion must carry `choices[0].message.content` and `usage`, a streamed one must arrive as `data:` events
+with `choices[0].delta.content`, a `usage` event when `stream_options.include_usage` is set, and `[DONE]`
+(crates/eidola-app-core/src/lib.rs:7232-7340)."""
+import json
+import threading
+import urllib.request
+
+import numpy as np
+
+from eidola_b200.server import ByteTokenizer, EngineLoop, serve
+
+
+class ScriptedEngine:
+    """Counts up from the last prompt byte; records what the loop asked of it."""
+    max_seqs = 4
+
+    def __init__(self):
+        self.free = list(range(self.max_seqs))
+        self.calls = []
+
+    def admit_evicting(self, context_len):
+        return self.free.pop(0), []
+
+    def prefill(self, slots, prompts):
+        self.calls.append(("prefill", list(slots), [len(p) for p in prompts]))
+        return (np.array([(int(p[-1]) + 1) % 256 or 1 for p in prompts], np.int32),)
+
+    def step(self, slots, q_lens, tokens):
+        import time
+        time.sleep(0.003)  # a decode step takes milliseconds: requests that arrive meanwhile join the next one
+        self.calls.append(("step", list(slots)))
+        return np.array([(t + 1) % 256 or 1 for t in tokens], np.int32), None
+
+    def release(self, slot):
+        self.free.append(slot)
+
+
+def _start():
+    eng = ScriptedEngine()
+    loop = EngineLoop(eng, context_tokens=512)
+    httpd = serve(loop, "127.0.0.1", 0, "test-model")
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    return eng, loop, httpd, "http://127.0.0.1:%d" % httpd.server_address[1]
+
+
+def _post(url, body):
+    req = urllib.request.Request(url + "/v1/chat/completions", data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+    return urllib.request.urlopen(req, timeout=30)
+
+
+def test_health_then_blocking_and_streamed_completions():
+    eng, loop, httpd, url = _start()
+    try:
+        try:
+            urllib.request.urlopen(url + "/health", timeout=5)
+            assert False, "healthy before the engine loop is up"
+        except urllib.error.HTTPError as e:
+            assert e.code == 503                                  # the socket answers while the model loads
+        loop.start()
+        assert loop.ready.wait(5)
+        assert json.load(urllib.request.urlopen(url + "/health", timeout=5)) == {"status": "ok"}
+        body = {"model": "test-model", "messages": [{"role": "user", "content": "hi"}], "max_completion_tokens": 5}
+        out = json.load(_post(url, body))
+        prompt = ByteTokenizer.template(body["messages"])
+        want = bytes((prompt[-1] + 1 + i) % 256 for i in range(5)).decode("utf-8", errors="replace")
+        assert out["choices"][0]["message"]["content"] == want and out["choices"][0]["finish_reason"] == "length"
+        assert out["usage"] == {"prompt_tokens": len(prompt), "completion_tokens": 5, "total_tokens": len(prompt) + 5}
+        # streamed, parsed as the client does: data: lines, usage, choices[0].delta.content, [DONE]
+        resp = _post(url, dict(body, stream=True, stream_options={"include_usage": True}))
+        assert resp.headers["Content-Type"] == "text/event-stream"
+        text, usage, finished = "", None, False
+        for event in resp.read().decode().split("\n\n"):
+            for line in event.splitlines():
+                if not line.startswith("data:"):
+                    continue
+                payload = line[5:].lstrip()
+                if payload == "[DONE]":
+                    finished = True
+                    continue
+                j = json.loads(payload)
+                usage = j.get("usage") or usage
+                if j.get("choices"):
+                    text += j["choices"][0]["delta"].get("content") or ""
+        assert finished and text == want and usage["completion_tokens"] == 5 and usage["prompt_tokens"] == len(prompt)
+        assert eng.free and sorted(eng.free) == [0, 1, 2, 3]      # every sequence was released
+    finally:
+        loop.stop.set()
+        httpd.shutdown()
+
+
+def test_requests_that_overlap_share_decode_steps_and_bad_requests_are_refused():
+    eng, loop, httpd, url = _start()
+    loop.start()
+    try:
+        results = {}
+
+        def client(i):
+            body = {"model": "m", "messages": [{"role": "user", "content": "q%d" % i}], "max_completion_tokens": 40}
+            results[i] = json.load(_post(url, body))
+
+        ts = [threading.Thread(target=client, args=(i,)) for i in range(3)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join(30)
+        assert all(results[i]["usage"]["completion_tokens"] == 40 for i in range(3))
+        steps = [c for c in eng.calls if c[0] == "step"]
+        assert any(len(c[1]) > 1 for c in steps)                   # continuous batching: several sequences in one step
+        assert len(steps) < 3 * 40
+        for bad in (b"not json", json.dumps({"model": "m"}).encode(), json.dumps({"messages": []}).encode()):
+            try:
+                urllib.request.urlopen(urllib.request.Request(url + "/v1/chat/completions", data=bad), timeout=5)
+                assert False
+            except urllib.error.HTTPError as e:
+                assert e.code == 400 and "error" in json.load(e)
+        try:  # more context than the engine was started with: refused with a message, like the reference's -c cap
+            _post(url, {"messages": [{"role": "user", "content": "x" * 600}], "max_completion_tokens": 10})
+            assert False
+        except urllib.error.HTTPError as e:
+            assert e.code == 500 and "context" in json.load(e)["error"]["message"]
+    finally:
+        loop.stop.set()
+        httpd.shutdown()
