@@ -332,10 +332,12 @@ class Spec120bWorkload:
         return {"workload": self.name, "n_seqs": int(len(self.ctx0)), "n_layers": int(self.cfg.n_layers),
                 "mean_context": float(self.lens.mean()), "device_bytes_per_rank": self.mem,
                 "prefill": "KV pages filled with seeded N(0,1) values (stand-in for prefill)",
-                "parallelism": "tp%d (heads) x ep%d (experts); per layer 2 bf16 reduce-scatters of [2560, 2880] over token "
-                               "slices of whole 128-row blocks, residual + norm + routing on the slice, one all-gather of the "
-                               "bf16 rows + routing and one of the e4m3 codes + block scales quantised by the slice's owner; "
-                               "vocabulary-parallel LM head with an all-gather of argmax candidates" % (self.world, self.world)}
+                "parallelism": "tp%d (heads) x ep%d (experts); rows dealt to ranks in slices of whole 128-row blocks: partial "
+                               "[2560, 2880] products go to the slice owners as planes (summed in rank order), residual + norm + "
+                               "routing on the slice; experts by dispatch / return of rows from 4 ranks on, by partial sums at 2; "
+                               "e4m3 codes + block scales gathered for the next layer; vocabulary-parallel LM head with a gather "
+                               "of argmax candidates; transport: %s" % (self.world, self.world,
+                               "NCCL" if os.environ.get("EIDOLA_B200_TP_NCCL") == "1" else "peer-memory stores over NVLink")}
 
 
 # ------------------------------------------------------------------------------------------ attention workload
@@ -577,9 +579,11 @@ def run_decoder(args) -> dict:
     peak, peak_kind = measured_peaks()
     out = {}
     if rank == 0:
+        transport = "NCCL reduce-scatter / all-gather" if os.environ.get("EIDOLA_B200_TP_NCCL") == "1" else \
+            "peer-memory stores over NVLink with flag waits (whole-batch planes for steps of <= 512 rows: two exchanges per layer)"
         parallelism = ("tp %d x ep %d: one engine over %d GPUs (query/KV heads and the O projection tensor-parallel, experts "
-                       "expert-parallel, LM head vocabulary-parallel); NCCL reduce-scatter + all-gather pairs on the two shard "
-                       "boundaries of every layer" % (world, world, world)) if world > 1 else "single GPU"
+                       "expert-parallel, LM head vocabulary-parallel); exchanges on the two shard boundaries of every layer by %s"
+                       % (world, world, world, transport)) if world > 1 else "single GPU"
         out = {
             "metric": METRIC,
             "value": units * K / (dev_ms * 1e-3), "unit": "tokens/s",

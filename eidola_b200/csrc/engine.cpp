@@ -24,6 +24,11 @@
 
 namespace {
 
+// Tensor parallel, steps of at most this many token rows: every rank sends its WHOLE partial [T, H] to every peer and
+// sums all rows itself, so residual, norm, routing and quantisation run replicated and a layer needs two exchanges
+// instead of four.  Larger steps deal the rows to the ranks in slices (fewer bytes, more exchanges).
+constexpr int kWholeBatchTokens = 512;
+
 inline uint64_t sid(int layer, int kind, int expert) {
   return ((uint64_t)(layer + 1) << 20) | ((uint64_t)kind << 12) | (uint64_t)expert;
 }
@@ -68,7 +73,8 @@ struct eb_engine {
   size_t arena_used = 0;
   uint8_t* planes = nullptr;                 // [tp_size][chunk rows][hidden] fp32 or bf16: the ranks' partial rows of my slice
   // expert parallelism as dispatch / return of rows (the all-to-all pair) instead of gather-everything + reduce-scatter
-  bool a2a = false;
+  bool slices_forced = false;
+  bool a2a = false, a2a_forced = false;  // forced: EIDOLA_B200_EP_A2A=1 (tests): row dispatch whatever the step's size
   uint16_t* xp16 = nullptr;                  // [tokens * top_k][hidden] bf16: rows dispatched to this rank's experts (global row numbering)
   int32_t* r_idx_local = nullptr;
   float* sinks_all = nullptr;
@@ -263,13 +269,18 @@ int32_t init_work(eb_engine* e) {
     // everything another rank writes into, or that is pushed from, sits in the arena
     auto a256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
     const size_t sz_rows2 = a256(Tc * H * 2), sz_rows1 = a256(Tc * H), sz_rows4 = a256(Tc * H * 4);
+    // small steps exchange whole [T, H] partials (one plane per rank, every rank sums all rows): room for tp_size planes
+    const size_t sz_planes = std::max(sz_rows4, a256((size_t)e->tp_size * std::min(T, kWholeBatchTokens) * H * 4));
     const size_t sz_sh = a256((size_t)(tb0 * e->kbH) * 4), sz_r = a256(r_cap0 * 4), sz_cand = a256((size_t)e->tp_size * T * 4 * 4);
     {
       const char* v = getenv("EIDOLA_B200_EP_A2A");
-      e->a2a = v ? v[0] == '1' : e->tp_size >= 4;  // measured: the row exchange moves fewer bytes from four ranks on
+      e->a2a = v ? v[0] == '1' : e->tp_size >= 4;  // the row exchange moves fewer bytes from four ranks on (large steps)
+      e->a2a_forced = v && v[0] == '1';
+      const char* w = getenv("EIDOLA_B200_TP_WHOLE");  // =0 (tests, A/B timing): token slices even for small steps
+      e->slices_forced = w && w[0] == '0';
     }
     const size_t sz_routed = e->a2a ? a256((size_t)R * H * 2) : 0;
-    const size_t total = 3 * sz_rows2 + sz_rows1 + 2 * sz_rows4 + sz_sh + 2 * sz_r + sz_cand + 2 * sz_routed;
+    const size_t total = 3 * sz_rows2 + sz_rows1 + sz_rows4 + sz_planes + sz_sh + 2 * sz_r + sz_cand + 2 * sz_routed;
     EB_TRY(eb_symm_create(e->comm, total, &e->symm));
     void* base = nullptr;
     EB_TRY(eb_symm_ptr(e->symm, e->tp_rank, &base, nullptr));
@@ -285,7 +296,7 @@ int32_t init_work(eb_engine* e) {
     e->o = (uint16_t*)carve(sz_rows2);
     e->h8 = carve(sz_rows1);
     e->ar_buf = (float*)carve(sz_rows4);
-    e->planes = carve(sz_rows4);
+    e->planes = carve(sz_planes);
     e->sh = (float*)carve(sz_sh);
     e->r_idx = (int32_t*)carve(sz_r);
     e->r_wts = (float*)carve(sz_r);
@@ -424,6 +435,16 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     n += 1;
     return eb_symm_wait(e->symm, seq, 1, st);
   };
+  // the WHOLE [T][H] partial to every rank (this rank's copy included), side by side as planes of T rows
+  auto share_planes = [&](const void* src, int esz) -> int32_t {
+    const int64_t so = aoff(src), zero = 0, dof = aoff(e->planes), step = (int64_t)T * H * esz;
+    int32_t seq = 0;
+    EB_TRY(eb_symm_push(e->symm, 1, &so, &zero, &dof, &step, &step, nullptr, 1, &seq, st));
+    n += 1;
+    const int patience = first_exchange ? 32 : 1;
+    first_exchange = false;
+    return eb_symm_wait(e->symm, seq, patience, st);
+  };
   // the ranks' slices of a [T][H] partial (esz bytes per element, in the arena) to their owners, side by side as planes
   auto scatter_planes = [&](const void* src, int esz) -> int32_t {
     const int64_t so = aoff(src), step = (int64_t)chunk * H * esz, dof = aoff(e->planes), valid = (int64_t)T * H * esz;
@@ -472,7 +493,10 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   const int avg2 = std::min(128, 2 * ((R / e->tp_size + E - 1) / E));
   const int group_tn = avg2 <= 16 ? 16 : avg2 <= 32 ? 32 : avg2 <= 64 ? 64 : 128;
   // under row dispatch the segment table covers all experts (global row numbering) and this rank works on its own part
-  const bool a2a = tp && e->a2a;
+  // small steps: whole-batch planes (see kWholeBatchTokens); large steps: token slices, with the experts by row
+  // dispatch from four ranks on
+  const bool whole = tp && e->symm != nullptr && T <= kWholeBatchTokens && !e->a2a_forced && !e->slices_forced;
+  const bool a2a = tp && e->a2a && !whole && (e->a2a_forced || T >= 1024);
   const int32_t* seg = a2a ? e->seg_off + e->e0 : e->seg_off;
   auto grouped = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout) -> int32_t {
     eb_gemm_args g = {};
@@ -578,7 +602,17 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       // of a slice adds the residual, rounds once and normalises; the normalised rows are gathered below.  Prefill-
       // sized steps have the partial in bf16 already (the GEMM's output) and scatter it as such, half the bytes;
       // decode-sized steps sum their split-K planes in fp32 and scatter fp32.
-      if (splits == 1) {
+      if (whole) {
+        // every rank gets every rank's partial and adds them itself, in rank order: residual, norm and routing then run
+        // on all rows everywhere with identical bits, and nothing has to be gathered
+        const int esz = splits == 1 ? 2 : 4;
+        if (splits > 1) EB_TRY(eb_sum_planes_f32((const float*)e->gemm_ws, splits, e->o, (int64_t)T * H, e->ar_buf, st));
+        mark(5);
+        EB_TRY(share_planes(splits == 1 ? (const void*)e->o : (const void*)e->ar_buf, esz));
+        mark(-1);
+        EB_TRY(eb_planes_residual_rmsnorm(e->planes, esz == 2, e->tp_size, (int64_t)T * H, e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
+        n += 2;
+      } else if (splits == 1) {
         mark(5);
         if (symm)
           EB_TRY(scatter_planes(e->o, 2));
@@ -610,7 +644,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       }
     }
     mark(6);
-    if (!tp) {
+    if (!tp || whole) {
       EB_TRY(eb_moe_route(e->h, L.wr, T, c.n_experts, H, c.top_k, e->r_idx, e->r_wts, nullptr, st));
       mark(-1);
     } else {
@@ -686,6 +720,14 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
         // C2 without an exchange of rows: every rank holds every token, mixes its own experts' outputs into a partial
         // [T, H] and the partials are summed over token slices
         EB_TRY(eb_moe_combine_bf16(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->o, st));
+        if (whole) {
+          mark(5);
+          EB_TRY(share_planes(e->o, 2));
+          mark(-1);
+          EB_TRY(eb_planes_residual_rmsnorm(e->planes, 1, e->tp_size, (int64_t)T * H, e->x, g_next, T, H, c.rms_eps, e->h, st));
+          n += 2;
+          goto layer_done;  // every rank holds every normalised row: the next consumer quantises them itself
+        }
         mark(5);
         if (symm)
           EB_TRY(scatter_planes(e->o, 2));
@@ -716,6 +758,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       h8_ready = true;
       n += 3;
     }
+  layer_done:
     n += 9 + (plans[pi].n_parts > n_seqs ? 1 : 0);
     if (c.debug & 1) {
       EB_CUDA(cudaMemcpyAsync(e->dbg_route + (size_t)l * c.max_tokens * c.top_k, e->r_idx, (size_t)R * sizeof(int32_t),

@@ -75,14 +75,15 @@ def _oracle_steps(name):
 
 
 MODES = {
-    "peer": {},                                                        # peer-memory exchanges, the default expert form for the rank count
+    "peer": {},                                                        # peer memory; small steps exchange whole-batch planes
+    "peer_slices": {"EIDOLA_B200_TP_WHOLE": "0"},                      # peer memory, rows dealt to ranks in slices (what large steps do)
     "peer_rows": {"EIDOLA_B200_EP_A2A": "1"},                          # experts by dispatch / return of rows
-    "peer_sums": {"EIDOLA_B200_EP_A2A": "0"},                          # experts by partial sums over token slices
+    "peer_sums": {"EIDOLA_B200_EP_A2A": "0", "EIDOLA_B200_TP_WHOLE": "0"},  # slices, experts by partial sums
     "nccl": {"EIDOLA_B200_TP_NCCL": "1"},                              # NCCL reduce-scatter / all-gather
 }
 
 
-@pytest.mark.parametrize("name,world,mode", [("tp_small", 2, "peer_sums"), ("tp_small", 2, "peer_rows"), ("tp_mid", 2, "peer"),
+@pytest.mark.parametrize("name,world,mode", [("tp_small", 2, "peer_sums"), ("tp_small", 2, "peer_rows"), ("tp_small", 2, "peer"), ("tp_mid", 2, "peer"), ("tp_mid", 2, "peer_slices"),
                                              ("tp_mid", 2, "nccl"), ("tp_mid", 2, "peer_rows"), ("tp_mid", 4, "peer"),
                                              ("tp_mid", 4, "peer_sums"), ("tp_mid", 8, "peer"), ("tp_mid", 8, "nccl")])
 def test_tp_engine_matches_oracle_and_single_gpu(gpu, tmp_path, name, world, mode):
