@@ -450,6 +450,7 @@ def make_comm(eb, rank, world, dist):
     if os.environ.get("NCCL_DEBUG", "").upper() not in ("INFO", "TRACE"):
         os.environ["NCCL_DEBUG"] = "INFO"
         os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # stdout carries the one JSON line and nothing else
     uid = [eb.Comm.unique_id() if rank == 0 else None]
     dist.broadcast_object_list(uid, src=0)
     return eb.Comm(uid[0], rank, world)
