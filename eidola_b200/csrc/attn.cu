@@ -803,6 +803,414 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, con
   if (warp == HPC * 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kCols) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Verify shapes on tcgen05 with 64-row tiles.  One CTA = one work item x one KV head, two CTAs per SM; a block is 128
+// keys (8 pages), fetched per page as one 2 KiB TMA copy of the head's K rows and one of its V rows.
+//   S[64 x 128] = Q K^T                  4 MMAs (M = 64: row r of the tile lives in tensor-memory lane 32 (r / 16) + r % 16)
+//   softmax                              warps w and w + 4 own rows 16 w .. 16 w + 15 (keys 0..63 and 64..127) and read them
+//                                        with the 16x256b shape: a thread holds, per group of 8 keys, two adjacent keys of
+//                                        row lane / 4 and of row lane / 4 + 8, so all 32 lanes work whenever the warp has 16
+//                                        rows; the two warps exchange their halves' maxima through shared memory.  The reference
+//                                        maximum of a row is shared by the four lanes of its quad and only raised when a
+//                                        score exceeds it by 2^8 (then the row of O is rescaled in tensor memory); a thread
+//                                        keeps the sum of its own weights and the row sums are formed once, at the end.
+//   O[64 x 64] += P V                    16 MMAs: P overwrites S in place as a bf16 head (columns 0..63) and a bf16
+//                                        remainder (columns 64..127), packed two keys per column with the 16x128b store
+//                                        shape, which lands exactly where the A operand of the product is read; V is the
+//                                        MN-major B operand.  (A 72-column product that also accumulated the row sums
+//                                        against a tile of ones was measured at the cost of 128 columns, 65 clocks per MMA
+//                                        instead of 32.)
+// The chain S -> softmax -> P V of one CTA is serial (P lives where S was); the second CTA of the SM fills its gaps.
+constexpr int kV64Keys = 128;
+constexpr int kV64Pages = kV64Keys / kPage;
+constexpr int kV64Stage = 2 * kV64Keys * 128;  // K rows then V rows of one head
+constexpr int kV64Stages = 3;
+constexpr int kV64Threads = 320;               // 8 softmax warps, producer warp, MMA warp
+
+#define EB_O16(a, o) EB_O8(a, o), EB_O8(a, o + 8)
+#define EB_I16(a, o) EB_I8(a, o), EB_I8(a, o + 8)
+// 16 lanes x 128 columns: registers 4 j .. 4 j + 3 = (row lane/4, columns 8 j + 2 (lane%4) + {0, 1}), (row lane/4 + 8, same)
+__device__ __forceinline__ void tc_ld_16x256b_x16(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,"
+      "%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+      : EB_O16(r, 0), EB_O16(r, 16), EB_O16(r, 32), EB_O16(r, 48)
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : EB_O16(r, 0), EB_O16(r, 16)
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_ld_16x256b_x1(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_st_16x256b_x8(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x8.b32 [%32], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
+      ::EB_I16(r, 0), EB_I16(r, 16), "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st_16x256b_x1(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%4], {%0,%1,%2,%3};" ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(taddr)
+               : "memory");
+}
+// 16 lanes x 16 columns: registers 2 j, 2 j + 1 = (row lane/4, column 4 j + lane%4), (row lane/4 + 8, same column)
+__device__ __forceinline__ void tc_st_16x128b_x4(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};" ::EB_I8(r, 0), "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ void tc_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : EB_O16(r, 0)
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_st_16x256b_x4(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x4.b32 [%16], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15};"
+      ::EB_I16(r, 0), "r"(taddr)
+      : "memory");
+}
+
+struct V64Params {
+  int32_t n_kv;  // KV heads held by this rank
+  int32_t ppi;   // partial slots the plan reserves per item (8 / n_kv)
+};
+
+template <int G>  // query heads per KV head
+__global__ void __launch_bounds__(kV64Threads, 2)
+attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, const V64Params vp) {
+  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
+  eb::pdl_trigger();
+  constexpr int NS = kV64Stages;
+  constexpr uint32_t kCols = 256;  // S / P: 0..127, O: 128..191
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+  const uint32_t q_addr = base;                                // 64 rows x 128 B
+  const uint32_t stage0 = base + 8192;                         // NS stages
+  uint8_t* after = sm + 8192 + NS * kV64Stage;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after);         // full[NS], empty[NS], s_ready, p_ready, o_ready
+  int32_t* page_ids = reinterpret_cast<int32_t*>(after + (2 * NS + 3) * sizeof(uint64_t) + 8);
+  __shared__ int abort_flag;
+  __shared__ int n_issued;
+  __shared__ uint32_t tmem_slot;
+  __shared__ float s_mx[2][64];  // half-row maxima of the two warps that share a row set
+  __shared__ float s_l[2][64];   // and, at the end, their shares of the row sums
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const eb_attn_item item = p.items[blockIdx.x];
+  const int kvh = blockIdx.y;
+  const int seq = item.seq;
+  const int slot = p.seq_slots[seq];
+  const int L = p.ctx_lens[seq];
+  const int q0 = p.q_off[seq];
+  const int ql = p.q_off[seq + 1] - q0;
+  int n_pages = item.page_end - item.page_begin;
+  if (n_pages > kMaxItemPages) {
+    if (tid == 0) atomicOr(p.status, EB_DEV_BAD_INDEX);
+    n_pages = kMaxItemPages;
+  }
+  for (int j = tid; j < n_pages; j += kV64Threads) {
+    int32_t id = p.block_tables[(int64_t)slot * p.bt_stride + item.page_begin + j];
+    if (id < 0 || id >= p.num_pages) {
+      atomicOr(p.status, EB_DEV_BAD_INDEX);
+      id = 0;
+    }
+    page_ids[j] = id;
+  }
+  const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[NS]);
+  const uint32_t bar_s = smem_u32(&bars[2 * NS]), bar_p = bar_s + 8, bar_o = bar_s + 16;
+  const int q_rows = ql * G;                 // real query rows
+  const int n_act = (q_rows + 15) / 16;      // row sets (16 rows, two softmax warps each) that hold real rows
+  if (tid == 0) {
+    abort_flag = 0;
+    n_issued = 0;
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, 1);
+    }
+    mbar_init(bar_s, 1);
+    mbar_init(bar_p, (uint32_t)(2 * n_act));
+    mbar_init(bar_o, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 8) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp < 8) {
+    // the Q tile with the 128-byte swizzle a TMA copy would apply; rows past the real ones are zero
+    for (int i = tid; i < 64 * 8; i += 256) {
+      const int r = i >> 3, c = i & 7;
+      const int qi = r / G, g = r - qi * G;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (qi < ql) {
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.q + (int64_t)(q0 + qi) * p.q_stride +
+                                                                (int64_t)(kvh * G + g) * kHeadDim + c * 8);
+        v = make_uint4(src[0], src[1], src[2], src[3]);
+      }
+      *reinterpret_cast<uint4*>(sm + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tS = tmem, tO = tmem + 128;
+  const int n_blk = (n_pages + kV64Pages - 1) / kV64Pages;
+  const int page_rows = 2 * vp.n_kv * kPage;
+
+  if (warp == 8) {
+    // ---------------- producer
+    if (lane == 0) {
+      for (int blk = 0; blk < n_blk; ++blk) {
+        const int sidx = blk % NS;
+        if (blk >= NS && !mbar_wait(bar_empty + 8 * sidx, ((blk / NS) - 1) & 1, &abort_flag, p.status, p.wait_tries)) break;
+        const uint32_t full = bar_full + 8 * sidx;
+        mbar_arrive_expect_tx(full, (uint32_t)kV64Stage);
+        const uint32_t sb = stage0 + sidx * kV64Stage;
+        for (int j = 0; j < kV64Pages; ++j) {
+          const int pl = min(blk * kV64Pages + j, n_pages - 1);  // a block's missing pages repeat the last one (masked below)
+          const int row = page_ids[pl] * page_rows;
+          tma_load_2d(sb + j * 2048, &tmap, 0, row + kvh * kPage, full);
+          tma_load_2d(sb + kV64Keys * 128 + j * 2048, &tmap, 0, row + (vp.n_kv + kvh) * kPage, full);
+        }
+        n_issued = blk + 1;
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kV64Keys >> 3) << 17) | ((uint32_t)(64 >> 4) << 24);
+      constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(64 >> 4) << 24);
+      const uint64_t dq = tc_desc_sw128(q_addr);
+      bool ok = true;
+      for (int blk = 0; blk < n_blk && ok; ++blk) {
+        const int sidx = blk % NS;
+        if (!mbar_wait(bar_full + 8 * sidx, (blk / NS) & 1, &abort_flag, p.status, p.wait_tries)) break;
+        tc_fence_after();
+        const uint32_t kb = stage0 + sidx * kV64Stage, vb = kb + kV64Keys * 128;
+        const uint64_t dk = tc_desc_sw128(kb);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tc_mma_ss(tS, dq + 2 * k, dk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+        tc_commit(bar_s);
+        if (!mbar_wait(bar_p, blk & 1, &abort_flag, p.status, p.wait_tries)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < kV64Keys / 16; ++kk) {  // 16 keys per instruction; head, then remainder
+          const uint64_t dv = tc_desc_sw128(vb + kk * 2048);
+          tc_mma_ts(tO, tS + kk * 8, dv, idesc_o, (blk > 0 || kk > 0) ? 1u : 0u);
+          tc_mma_ts(tO, tS + 64 + kk * 8, dv, idesc_o, 1u);
+        }
+        tc_commit(bar_empty + 8 * sidx);
+        if (blk + 1 == n_blk) tc_commit(bar_o);
+      }
+    }
+  } else if ((warp & 3) < n_act) {
+    // ---------------- softmax of rows 16 w .. 16 w + 15, keys 64 kh .. 64 kh + 63 of every block
+    const int w = warp & 3, kh = warp >> 2;
+    const int quad = lane >> 2, qc = lane & 3;
+    const int r_lo = 16 * w + quad, r_hi = r_lo + 8;
+    const bool hi_on = 16 * w + 8 < q_rows;  // warp-uniform: the upper eight rows hold real rows
+    const bool ok_lo = r_lo < q_rows, ok_hi = r_hi < q_rows;
+    const int qi_lo = ok_lo ? r_lo / G : 0, qi_hi = ok_hi ? r_hi / G : 0;
+    const int pq_lo = L - ql + qi_lo, pq_hi = L - ql + qi_hi;  // absolute positions of the rows' queries
+    const int lw_lo = p.window > 0 ? pq_lo - p.window + 1 : 0, lw_hi = p.window > 0 ? pq_hi - p.window + 1 : 0;
+    const int t_end = item.page_end * kPage;
+    const uint32_t t_lane = (uint32_t)(32 * w) << 16;
+    float m_lo = kNegBig, m_hi = kNegBig;
+    float l_lo = 0.f, l_hi = 0.f;  // this thread's share of the rows' sums (its keys of every block)
+    bool ok = true;
+    for (int blk = 0; blk < n_blk; ++blk) {
+      if (!mbar_wait(bar_s, blk & 1, &abort_flag, p.status, p.wait_tries)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t sv[32];
+      tc_ld_16x256b_x8(tS + t_lane + kh * 64, sv);
+      const int t0 = (item.page_begin + blk * kV64Pages) * kPage;
+      // only blocks at the ends of the visible range need the causal / window / end-of-item mask (CTA-uniform test)
+      const bool edge = (t0 + kV64Keys - 1 > L - ql) || (p.window > 0 && t0 < L - p.window) || (t0 + kV64Keys > t_end);
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+      if (edge) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int t = t0 + kh * 64 + 8 * j + 2 * qc + e;
+            if (t > pq_lo || t < lw_lo || t >= t_end) sv[4 * j + e] = __float_as_uint(-INFINITY);
+            if (t > pq_hi || t < lw_hi || t >= t_end) sv[4 * j + 2 + e] = __float_as_uint(-INFINITY);
+          }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        mx_lo = fmaxf(mx_lo, fmaxf(__uint_as_float(sv[4 * j]), __uint_as_float(sv[4 * j + 1])));
+        if (hi_on) mx_hi = fmaxf(mx_hi, fmaxf(__uint_as_float(sv[4 * j + 2]), __uint_as_float(sv[4 * j + 3])));
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      // the other warp of the row set holds the other 64 keys: exchange the maxima so that both take the same decision
+      // (the next write of these slots follows this block's P V, which waits for both warps' arrival below)
+      if (qc == 0) {
+        s_mx[kh][r_lo] = mx_lo;
+        s_mx[kh][r_hi] = mx_hi;
+      }
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + w) : "memory");
+      mx_lo = fmaxf(mx_lo, s_mx[kh ^ 1][r_lo]);
+      mx_hi = fmaxf(mx_hi, s_mx[kh ^ 1][r_hi]);
+      const float mb_lo = mx_lo * p.scale_log2, mb_hi = mx_hi * p.scale_log2;
+      // raise a row's reference maximum only when a score exceeds it by 2^8 (always on the first finite one)
+      const bool raise_lo = mb_lo > m_lo + 8.0f, raise_hi = mb_hi > m_hi + 8.0f;
+      if (__any_sync(0xffffffffu, raise_lo || raise_hi)) {
+        const float n_lo = raise_lo ? mb_lo : m_lo, n_hi = raise_hi ? mb_hi : m_hi;
+        const float a_lo = fast_exp2(m_lo - n_lo), a_hi = fast_exp2(m_hi - n_hi);
+        m_lo = n_lo;
+        m_hi = n_hi;
+        l_lo *= a_lo;
+        l_hi *= a_hi;
+        if (blk > 0) {
+          // O holds earlier blocks (their products are complete: S of this block was issued after them).  Each warp
+          // rescales its half of the columns.
+          uint32_t ov[16];
+          tc_ld_16x256b_x4(tO + t_lane + kh * 32, ov);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            ov[4 * j] = __float_as_uint(__uint_as_float(ov[4 * j]) * a_lo);
+            ov[4 * j + 1] = __float_as_uint(__uint_as_float(ov[4 * j + 1]) * a_lo);
+            ov[4 * j + 2] = __float_as_uint(__uint_as_float(ov[4 * j + 2]) * a_hi);
+            ov[4 * j + 3] = __float_as_uint(__uint_as_float(ov[4 * j + 3]) * a_hi);
+          }
+          tc_st_16x256b_x4(tO + t_lane + kh * 32, ov);
+        }
+      }
+      // P = 2^(s * scale - m), written over S: bf16 head in columns 0..63, bf16 remainder in columns 64..127
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        uint32_t ph[8], pl[8];
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const int j = 4 * jj + j4;
+          const float a0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j]), p.scale_log2, -m_lo));
+          const float a1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j + 1]), p.scale_log2, -m_lo));
+          l_lo += a0 + a1;
+          const uint32_t h0 = pack_bf16(a0, a1);
+          ph[2 * j4] = h0;
+          pl[2 * j4] = pack_bf16(a0 - __uint_as_float(h0 << 16), a1 - __uint_as_float(h0 & 0xFFFF0000u));
+          if (hi_on) {
+            const float b0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j + 2]), p.scale_log2, -m_hi));
+            const float b1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j + 3]), p.scale_log2, -m_hi));
+            l_hi += b0 + b1;
+            const uint32_t h1 = pack_bf16(b0, b1);
+            ph[2 * j4 + 1] = h1;
+            pl[2 * j4 + 1] = pack_bf16(b0 - __uint_as_float(h1 << 16), b1 - __uint_as_float(h1 & 0xFFFF0000u));
+          } else {
+            ph[2 * j4 + 1] = 0u;
+            pl[2 * j4 + 1] = 0u;
+          }
+        }
+        tc_st_16x128b_x4(tS + t_lane + kh * 32 + jj * 16, ph);
+        tc_st_16x128b_x4(tS + 64 + t_lane + kh * 32 + jj * 16, pl);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
+    }
+    // ---------------- epilogue: this warp's 32 columns of the rows of O; the row sums are added over the quad and the
+    // two warps of the row set (both warps pass the barrier: a failed wait above has raised the abort flag for all)
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if (qc == 0) {
+      s_l[kh][r_lo] = l_lo;
+      s_l[kh][r_hi] = l_hi;
+    }
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + w) : "memory");
+    l_lo = s_l[0][r_lo] + s_l[1][r_lo];
+    l_hi = s_l[0][r_hi] + s_l[1][r_hi];
+    if (ok && n_blk > 0 && mbar_wait(bar_o, 0, &abort_flag, p.status, p.wait_tries)) {
+      tc_fence_after();
+      const int n_parts_seq = p.seq_part[seq + 1] - p.seq_part[seq];
+      const bool direct = (n_parts_seq == 1);
+      // partial slots [item.part, item.part + ppi) must lie inside the scratch; otherwise skip and flag
+      const bool part_ok = direct || (item.part >= 0 && item.part + vp.ppi <= p.part_slots);
+      if (!part_ok && lane == 0 && kh == 0) atomicOr(p.status, EB_DEV_BAD_INDEX);
+      uint32_t ov[16];
+      tc_ld_16x256b_x4(tO + t_lane + kh * 32, ov);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const bool row_ok = half ? ok_hi : ok_lo;
+        if (!(row_ok && part_ok)) continue;
+        const int r = half ? r_hi : r_lo, qi = half ? qi_hi : qi_lo;
+        const int head = kvh * G + (r - qi * G);
+        const float m_row = half ? m_hi : m_lo, l_row = half ? l_hi : l_lo;
+        if (direct) {
+          const float sk = p.sinks[head] * 1.4426950408889634f;
+          const float mf = fmaxf(m_row, sk);
+          const float wgt = exp2f(m_row - mf);
+          const float inv = wgt / (l_row * wgt + exp2f(sk - mf));
+          uint32_t* orow = reinterpret_cast<uint32_t*>(p.out + (int64_t)(q0 + qi) * p.out_stride + (int64_t)head * kHeadDim) + kh * 16;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            orow[4 * j + qc] = pack_bf16(__uint_as_float(ov[4 * j + 2 * half]) * inv, __uint_as_float(ov[4 * j + 2 * half + 1]) * inv);
+        } else {
+          const int64_t prow = ((int64_t)item.part * p.max_q_len + qi) * p.n_q + head;
+          float2* arow = reinterpret_cast<float2*>(p.part_acc + prow * kHeadDim) + kh * 16;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            arow[4 * j + qc] = make_float2(__uint_as_float(ov[4 * j + 2 * half]), __uint_as_float(ov[4 * j + 2 * half + 1]));
+          if (qc == 0 && kh == 0) *reinterpret_cast<float2*>(p.part_ml + prow * 2) = make_float2(m_row, l_row);
+          // the plan reserves vp.ppi partial slots per item; this kernel fills one, the others are declared empty
+          for (int e = 1; e < vp.ppi; ++e) {
+            const int64_t pe = ((int64_t)(item.part + e) * p.max_q_len + qi) * p.n_q + head;
+            if (qc == 0 && kh == 0) *reinterpret_cast<float2*>(p.part_ml + pe * 2) = make_float2(kNegBig, 0.f);
+            float4* zrow = reinterpret_cast<float4*>(p.part_acc + pe * kHeadDim) + kh * 8;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) zrow[4 * j + qc] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (abort_flag && tid == 0) {
+    // A wait gave up.  Before the CTA releases its shared memory, wait (bounded) for the copies still in flight.
+    const int issued = n_issued;
+    for (int blk = max(0, issued - NS); blk < issued; ++blk) {
+      const uint32_t bar = bar_full + 8 * (blk % NS);
+      for (uint32_t i = 0; i < kWaitTries; ++i) {
+        if (mbar_try_wait(bar, (blk / NS) & 1)) break;
+        __nanosleep(64);
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kCols) : "memory");
+}
+
 // Combine the split-K partials of one (sequence, KV group): warp = query head, lane = two dims.
 __global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
@@ -939,6 +1347,37 @@ int32_t launch_attn_tc(EncodeTiledFn enc, const void* d_cache, int64_t cache_row
   return EB_OK;
 }
 
+// Verify shapes on tcgen05 with 64-row tiles: grid = (items, KV heads), two CTAs per SM.
+template <int G>
+int32_t launch_attn_v64(EncodeTiledFn enc, const void* d_cache, int64_t cache_rows, const AttnParams& p, int n_items, int n_kv,
+                        cudaStream_t st) {
+  CUtensorMap tm;  // the cache as rows of 128 bytes; a copy is the 16 rows (tokens) of one head's K or V in one page
+  const cuuint64_t gdim[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)cache_rows};
+  const cuuint64_t gstr[1] = {128};
+  const cuuint32_t box[2] = {(cuuint32_t)kHeadDim, (cuuint32_t)kPage};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult cr = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(d_cache), gdim, gstr, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  EB_REQUIRE(cr == CUDA_SUCCESS, EB_ERR_ARG, "attention: cuTensorMapEncodeTiled failed (%d)", (int)cr);
+  V64Params vp;
+  vp.n_kv = n_kv;
+  vp.ppi = 8 / n_kv;
+  const size_t smem = 1024 + 8192 + (size_t)kV64Stages * kV64Stage + (2 * kV64Stages + 3) * sizeof(uint64_t) + 8 +
+                      kMaxItemPages * sizeof(int32_t);
+  auto kfn = attn_v64_kernel<G>;
+  static bool configured[64] = {false};  // the attribute is per device
+  int dev = 0;
+  EB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  EB_CUDA(eb::launch(kfn, dim3((unsigned)n_items, (unsigned)n_kv), dim3(kV64Threads), smem, st, tm, p, vp));
+  EB_LAUNCH_CHECK();
+  return EB_OK;
+}
+
 // EIDOLA_B200_ATTN_TC=1 runs verify shapes on the tcgen05 kernel.  It is exact to the same tolerance as the mma.sync
 // kernel but measured slower (741 us against 530 us at q_len 5 on the 256-sequence benchmark: the per-block chain
 // tensor-memory load -> exponentials -> tensor-memory store -> barrier -> MMA issue is what bounds it, not the tensor
@@ -946,6 +1385,10 @@ int32_t launch_attn_tc(EncodeTiledFn enc, const void* d_cache, int64_t cache_row
 bool attn_tc_enabled() {
   const char* v = getenv("EIDOLA_B200_ATTN_TC");
   return v && v[0] == '1';
+}
+bool attn_v64_enabled() {
+  const char* v = getenv("EIDOLA_B200_ATTN_TC");
+  return v && v[0] == '2';
 }
 
 int32_t dispatch_attn_tc(EncodeTiledFn enc, const void* d_cache, int64_t cache_rows, const AttnParams& p, int n_items, int n_kv,
@@ -1077,7 +1520,10 @@ int32_t run_attn(const eb_attn_args* a, float* part_acc, float* part_ml, int32_t
   cudaStream_t st = eb::as_stream(stream);
   const int mt = (a->max_q_len * group + 15) / 16;
   int32_t rc;
-  if (mt >= 2 && attn_tc_enabled()) {
+  if (mt >= 2 && attn_v64_enabled()) {
+    rc = group == 8 ? launch_attn_v64<8>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st)
+                    : launch_attn_v64<4>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st);
+  } else if (mt >= 2 && attn_tc_enabled()) {
     rc = dispatch_attn_tc(enc, a->d_cache, rows, p, a->n_items, a->n_kv, group, st);
   } else if (group == 8) {
     if (mt == 1)

@@ -81,19 +81,21 @@ def test_attention_small_matches_oracle(gpu, n_kv, window, q_mode):
     assert plan["n_items"] > len(ctx) or window  # chunk 3 really split something
 
 
+@pytest.mark.parametrize("kernel", ["1", "2"])
 @pytest.mark.parametrize("n_kv", [8, 4, 1])
 @pytest.mark.parametrize("window", [0, 128])
-def test_attention_verify_on_tcgen05_matches_oracle(gpu, n_kv, window, monkeypatch):
-    """The opt-in tcgen05 kernel for verify shapes (S and O in tensor memory, P fed from tensor memory): same oracle, same
-    tolerance, ragged query lengths, split contexts, window, fewer KV heads per rank."""
-    monkeypatch.setenv("EIDOLA_B200_ATTN_TC", "1")
+def test_attention_verify_on_tcgen05_matches_oracle(gpu, n_kv, window, kernel, monkeypatch):
+    """The tcgen05 kernels for verify shapes (S and O in tensor memory, P fed from tensor memory; "1": 128-row tiles, a
+    thread per row; "2": 64-row tiles, 128-key blocks): same oracle, same tolerance, ragged query lengths, split contexts,
+    window, fewer KV heads per rank."""
+    monkeypatch.setenv("EIDOLA_B200_ATTN_TC", kernel)
     ctx = np.array(CTX_SMALL, np.int32)
     for ql in (np.minimum(ctx, 5), np.minimum(ctx, np.array([1, 2, 3, 4, 5, 1, 6, 2, 1, 3], np.int32))):
         case = AttnCase(ctx, ql, n_kv, seed=2, sm_count=gpu["sm_count"])
         want = case.oracle(window)
         for chunk in (0, 3):
             got, _ = case.run(window, chunk)
-            assert_close_bf16(got, want, atol=ATTN_ATOL, what=f"tcgen05 n_kv={n_kv} window={window} chunk={chunk}")
+            assert_close_bf16(got, want, atol=ATTN_ATOL, what=f"tcgen05[{kernel}] n_kv={n_kv} window={window} chunk={chunk}")
 
 
 @pytest.mark.parametrize("n_kv", [2, 8])
