@@ -888,7 +888,7 @@ struct V64Params {
   int32_t ppi;   // partial slots the plan reserves per item (8 / n_kv)
 };
 
-template <int G>  // query heads per KV head
+template <int G, bool LO>  // query heads per KV head; LO: P carries a bf16 remainder besides its bf16 head
 __global__ void __launch_bounds__(kV64Threads, 2)
 attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, const V64Params vp) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
@@ -1016,7 +1016,7 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
         for (int kk = 0; kk < kV64Keys / 16; ++kk) {  // 16 keys per instruction; head, then remainder
           const uint64_t dv = tc_desc_sw128(vb + kk * 2048);
           tc_mma_ts(tO, tS + kk * 8, dv, idesc_o, (blk > 0 || kk > 0) ? 1u : 0u);
-          tc_mma_ts(tO, tS + 64 + kk * 8, dv, idesc_o, 1u);
+          if (LO) tc_mma_ts(tO, tS + 64 + kk * 8, dv, idesc_o, 1u);
         }
         tc_commit(bar_empty + 8 * sidx);
         if (blk + 1 == n_blk) tc_commit(bar_o);
@@ -1059,10 +1059,17 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
             if (t > pq_hi || t < lw_hi || t >= t_end) sv[4 * j + 2 + e] = __float_as_uint(-INFINITY);
           }
       }
+      {
+        float ta[4], tb[4];  // independent partial maxima, then a tree
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        mx_lo = fmaxf(mx_lo, fmaxf(__uint_as_float(sv[4 * j]), __uint_as_float(sv[4 * j + 1])));
-        if (hi_on) mx_hi = fmaxf(mx_hi, fmaxf(__uint_as_float(sv[4 * j + 2]), __uint_as_float(sv[4 * j + 3])));
+        for (int j = 0; j < 4; ++j) {
+          ta[j] = fmaxf(fmaxf(__uint_as_float(sv[8 * j]), __uint_as_float(sv[8 * j + 1])),
+                        fmaxf(__uint_as_float(sv[8 * j + 4]), __uint_as_float(sv[8 * j + 5])));
+          tb[j] = fmaxf(fmaxf(__uint_as_float(sv[8 * j + 2]), __uint_as_float(sv[8 * j + 3])),
+                        fmaxf(__uint_as_float(sv[8 * j + 6]), __uint_as_float(sv[8 * j + 7])));
+        }
+        mx_lo = fmaxf(fmaxf(ta[0], ta[1]), fmaxf(ta[2], ta[3]));
+        if (hi_on) mx_hi = fmaxf(fmaxf(tb[0], tb[1]), fmaxf(tb[2], tb[3]));
       }
       mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
       mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
@@ -1102,33 +1109,72 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
           tc_st_16x256b_x4(tO + t_lane + kh * 32, ov);
         }
       }
-      // P = 2^(s * scale - m), written over S: bf16 head in columns 0..63, bf16 remainder in columns 64..127
+      // P = 2^(s * scale - m), written over S: bf16 head in columns 0..63, bf16 remainder in columns 64..127.  The steps
+      // are written as separate passes over the thread's 32 values so that independent instructions follow each other
+      // (one warp per scheduler has nothing else to hide an exponential's latency behind).
+      float ev[32];
 #pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        uint32_t ph[8], pl[8];
+      for (int j = 0; j < 8; ++j) {
+        ev[4 * j] = fmaf(__uint_as_float(sv[4 * j]), p.scale_log2, -m_lo);
+        ev[4 * j + 1] = fmaf(__uint_as_float(sv[4 * j + 1]), p.scale_log2, -m_lo);
+        ev[4 * j + 2] = fmaf(__uint_as_float(sv[4 * j + 2]), p.scale_log2, -m_hi);
+        ev[4 * j + 3] = fmaf(__uint_as_float(sv[4 * j + 3]), p.scale_log2, -m_hi);
+      }
 #pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const int j = 4 * jj + j4;
-          const float a0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j]), p.scale_log2, -m_lo));
-          const float a1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j + 1]), p.scale_log2, -m_lo));
-          l_lo += a0 + a1;
-          const uint32_t h0 = pack_bf16(a0, a1);
-          ph[2 * j4] = h0;
-          pl[2 * j4] = pack_bf16(a0 - __uint_as_float(h0 << 16), a1 - __uint_as_float(h0 & 0xFFFF0000u));
+      for (int j = 0; j < 8; ++j) {
+        ev[4 * j] = fast_exp2(ev[4 * j]);
+        ev[4 * j + 1] = fast_exp2(ev[4 * j + 1]);
+        if (hi_on) {
+          ev[4 * j + 2] = fast_exp2(ev[4 * j + 2]);
+          ev[4 * j + 3] = fast_exp2(ev[4 * j + 3]);
+        }
+      }
+      uint32_t ph[16], pl[16];  // registers 2 j, 2 j + 1: rows lane/4 and lane/4 + 8 of key group j
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        ph[2 * j] = pack_bf16(ev[4 * j], ev[4 * j + 1]);
+        ph[2 * j + 1] = hi_on ? pack_bf16(ev[4 * j + 2], ev[4 * j + 3]) : 0u;
+      }
+      if (LO) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          pl[2 * j] = pack_bf16(ev[4 * j] - __uint_as_float(ph[2 * j] << 16), ev[4 * j + 1] - __uint_as_float(ph[2 * j] & 0xFFFF0000u));
+          pl[2 * j + 1] = hi_on ? pack_bf16(ev[4 * j + 2] - __uint_as_float(ph[2 * j + 1] << 16),
+                                            ev[4 * j + 3] - __uint_as_float(ph[2 * j + 1] & 0xFFFF0000u))
+                                : 0u;
+        }
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;  // four independent chains
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          s0 += ev[4 * j] + ev[4 * j + 1];
+          s1 += ev[4 * j + 4] + ev[4 * j + 5];
           if (hi_on) {
-            const float b0 = fast_exp2(fmaf(__uint_as_float(sv[4 * j + 2]), p.scale_log2, -m_hi));
-            const float b1 = fast_exp2(fmaf(__uint_as_float(sv[4 * j + 3]), p.scale_log2, -m_hi));
-            l_hi += b0 + b1;
-            const uint32_t h1 = pack_bf16(b0, b1);
-            ph[2 * j4 + 1] = h1;
-            pl[2 * j4 + 1] = pack_bf16(b0 - __uint_as_float(h1 << 16), b1 - __uint_as_float(h1 & 0xFFFF0000u));
-          } else {
-            ph[2 * j4 + 1] = 0u;
-            pl[2 * j4 + 1] = 0u;
+            s2 += ev[4 * j + 2] + ev[4 * j + 3];
+            s3 += ev[4 * j + 6] + ev[4 * j + 7];
           }
         }
-        tc_st_16x128b_x4(tS + t_lane + kh * 32 + jj * 16, ph);
-        tc_st_16x128b_x4(tS + 64 + t_lane + kh * 32 + jj * 16, pl);
+        l_lo += s0 + s1;
+        l_hi += s2 + s3;
+      } else {  // the row sum is that of the rounded weights, the ones that enter O
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          l_lo += __uint_as_float(ph[2 * j] << 16) + __uint_as_float(ph[2 * j] & 0xFFFF0000u);
+          l_hi += __uint_as_float(ph[2 * j + 1] << 16) + __uint_as_float(ph[2 * j + 1] & 0xFFFF0000u);
+        }
+      }
+      {
+        uint32_t t8[8];
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) t8[i] = ph[8 * jj + i];
+          tc_st_16x128b_x4(tS + t_lane + kh * 32 + jj * 16, t8);
+          if (LO) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t8[i] = pl[8 * jj + i];
+            tc_st_16x128b_x4(tS + 64 + t_lane + kh * 32 + jj * 16, t8);
+          }
+        }
       }
       tc_wait_st();
       tc_fence_before();
@@ -1348,7 +1394,7 @@ int32_t launch_attn_tc(EncodeTiledFn enc, const void* d_cache, int64_t cache_row
 }
 
 // Verify shapes on tcgen05 with 64-row tiles: grid = (items, KV heads), two CTAs per SM.
-template <int G>
+template <int G, bool LO>
 int32_t launch_attn_v64(EncodeTiledFn enc, const void* d_cache, int64_t cache_rows, const AttnParams& p, int n_items, int n_kv,
                         cudaStream_t st) {
   CUtensorMap tm;  // the cache as rows of 128 bytes; a copy is the 16 rows (tokens) of one head's K or V in one page
@@ -1365,7 +1411,7 @@ int32_t launch_attn_v64(EncodeTiledFn enc, const void* d_cache, int64_t cache_ro
   vp.ppi = 8 / n_kv;
   const size_t smem = 1024 + 8192 + (size_t)kV64Stages * kV64Stage + (2 * kV64Stages + 3) * sizeof(uint64_t) + 8 +
                       kMaxItemPages * sizeof(int32_t);
-  auto kfn = attn_v64_kernel<G>;
+  auto kfn = attn_v64_kernel<G, LO>;
   static bool configured[64] = {false};  // the attribute is per device
   int dev = 0;
   EB_CUDA(cudaGetDevice(&dev));
@@ -1521,8 +1567,13 @@ int32_t run_attn(const eb_attn_args* a, float* part_acc, float* part_ml, int32_t
   const int mt = (a->max_q_len * group + 15) / 16;
   int32_t rc;
   if (mt >= 2 && attn_v64_enabled()) {
-    rc = group == 8 ? launch_attn_v64<8>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st)
-                    : launch_attn_v64<4>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st);
+    const char* lo = getenv("EB_V64_LO");
+    if (lo && lo[0] == '0')
+      rc = group == 8 ? launch_attn_v64<8, false>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st)
+                      : launch_attn_v64<4, false>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st);
+    else
+      rc = group == 8 ? launch_attn_v64<8, true>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st)
+                      : launch_attn_v64<4, true>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st);
   } else if (mt >= 2 && attn_tc_enabled()) {
     rc = dispatch_attn_tc(enc, a->d_cache, rows, p, a->n_items, a->n_kv, group, st);
   } else if (group == 8) {
