@@ -829,46 +829,12 @@ constexpr int kV64Threads = 320;               // 8 softmax warps, producer warp
 
 #define EB_O16(a, o) EB_O8(a, o), EB_O8(a, o + 8)
 #define EB_I16(a, o) EB_I8(a, o), EB_I8(a, o + 8)
-// 16 lanes x 128 columns: registers 4 j .. 4 j + 3 = (row lane/4, columns 8 j + 2 (lane%4) + {0, 1}), (row lane/4 + 8, same)
-__device__ __forceinline__ void tc_ld_16x256b_x16(uint32_t taddr, uint32_t (&r)[64]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
-      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,"
-      "%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
-      : EB_O16(r, 0), EB_O16(r, 16), EB_O16(r, 32), EB_O16(r, 48)
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
-      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : EB_O16(r, 0), EB_O16(r, 16)
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc_ld_16x256b_x1(uint32_t taddr, uint32_t (&r)[4]) {
-  asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc_st_16x256b_x8(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.16x256b.x8.b32 [%32], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
-      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
-      ::EB_I16(r, 0), EB_I16(r, 16), "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tc_st_16x256b_x1(uint32_t taddr, const uint32_t (&r)[4]) {
-  asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%4], {%0,%1,%2,%3};" ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(taddr)
-               : "memory");
-}
 // 16 lanes x 16 columns: registers 2 j, 2 j + 1 = (row lane/4, column 4 j + lane%4), (row lane/4 + 8, same column)
 __device__ __forceinline__ void tc_st_16x128b_x4(uint32_t taddr, const uint32_t (&r)[8]) {
   asm volatile("tcgen05.st.sync.aligned.16x128b.x4.b32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};" ::EB_I8(r, 0), "r"(taddr) : "memory");
 }
 
+// 16 lanes x 32 columns: registers 4 j .. 4 j + 3 = (row lane/4, columns 8 j + 2 (lane%4) + {0, 1}), (row lane/4 + 8, same)
 __device__ __forceinline__ void tc_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -894,7 +860,7 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
   constexpr int NS = kV64Stages;
-  constexpr uint32_t kCols = 256;  // S / P: 0..127, O: 128..191
+  constexpr uint32_t kCols = 256;  // S / P of even sub-blocks: 0..63, of odd sub-blocks: 64..127, O: 128..191
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -903,8 +869,8 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
   const uint32_t q_addr = base;                                // 64 rows x 128 B
   const uint32_t stage0 = base + 8192;                         // NS stages
   uint8_t* after = sm + 8192 + NS * kV64Stage;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(after);         // full[NS], empty[NS], s_ready, p_ready, o_ready
-  int32_t* page_ids = reinterpret_cast<int32_t*>(after + (2 * NS + 3) * sizeof(uint64_t) + 8);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after);         // full[NS], empty[NS], s_ready[2], p_ready[2], pv_done[2], o_ready
+  int32_t* page_ids = reinterpret_cast<int32_t*>(after + (2 * NS + 7) * sizeof(uint64_t) + 8);
   __shared__ int abort_flag;
   __shared__ int n_issued;
   __shared__ uint32_t tmem_slot;
@@ -933,7 +899,7 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
     page_ids[j] = id;
   }
   const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[NS]);
-  const uint32_t bar_s = smem_u32(&bars[2 * NS]), bar_p = bar_s + 8, bar_o = bar_s + 16;
+  const uint32_t bar_s = smem_u32(&bars[2 * NS]), bar_p = bar_s + 16, bar_pv = bar_s + 32, bar_o = bar_s + 48;  // [2] each
   const int q_rows = ql * G;                 // real query rows
   const int n_act = (q_rows + 15) / 16;      // row sets (16 rows, two softmax warps each) that hold real rows
   if (tid == 0) {
@@ -943,8 +909,11 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
       mbar_init(bar_full + 8 * i, 1);
       mbar_init(bar_empty + 8 * i, 1);
     }
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, (uint32_t)(2 * n_act));
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_s + 8 * i, 1);
+      mbar_init(bar_p + 8 * i, (uint32_t)(2 * n_act));
+      mbar_init(bar_pv + 8 * i, 1);
+    }
     mbar_init(bar_o, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -972,8 +941,9 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 128;
-  const int n_blk = (n_pages + kV64Pages - 1) / kV64Pages;
+  const uint32_t tO = tmem + 128;
+  const int n_blk = (n_pages + kV64Pages - 1) / kV64Pages;   // stages of 128 keys
+  const int n_sub = (n_pages + kV64Pages / 2 - 1) / (kV64Pages / 2);  // sub-blocks of 64 keys
   const int page_rows = 2 * vp.n_kv * kPage;
 
   if (warp == 8) {
@@ -995,35 +965,46 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
       }
     }
   } else if (warp == 9) {
-    // ---------------- MMA issuer
+    // ---------------- MMA issuer: S of sub-block i + 2 follows P V of sub-block i into the same 64 columns, so the
+    // products of one sub-block run while the softmax warps work on the next
     if (lane == 0) {
-      constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kV64Keys >> 3) << 17) | ((uint32_t)(64 >> 4) << 24);
+      constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(64 >> 4) << 24);
       constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(64 >> 4) << 24);
       const uint64_t dq = tc_desc_sw128(q_addr);
-      bool ok = true;
-      for (int blk = 0; blk < n_blk && ok; ++blk) {
-        const int sidx = blk % NS;
-        if (!mbar_wait(bar_full + 8 * sidx, (blk / NS) & 1, &abort_flag, p.status, p.wait_tries)) break;
-        tc_fence_after();
-        const uint32_t kb = stage0 + sidx * kV64Stage, vb = kb + kV64Keys * 128;
-        const uint64_t dk = tc_desc_sw128(kb);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) tc_mma_ss(tS, dq + 2 * k, dk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
-        tc_commit(bar_s);
-        if (!mbar_wait(bar_p, blk & 1, &abort_flag, p.status, p.wait_tries)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < kV64Keys / 16; ++kk) {  // 16 keys per instruction; head, then remainder
-          const uint64_t dv = tc_desc_sw128(vb + kk * 2048);
-          tc_mma_ts(tO, tS + kk * 8, dv, idesc_o, (blk > 0 || kk > 0) ? 1u : 0u);
-          if (LO) tc_mma_ts(tO, tS + 64 + kk * 8, dv, idesc_o, 1u);
+      auto issue_s = [&](int i) -> bool {
+        const int blk = i >> 1, sidx = blk % NS;
+        if ((i & 1) == 0) {
+          if (!mbar_wait(bar_full + 8 * sidx, (blk / NS) & 1, &abort_flag, p.status, p.wait_tries)) return false;
+          tc_fence_after();
         }
-        tc_commit(bar_empty + 8 * sidx);
-        if (blk + 1 == n_blk) tc_commit(bar_o);
+        const uint64_t dk = tc_desc_sw128(stage0 + sidx * kV64Stage + (i & 1) * 8192);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tc_mma_ss(tmem + (i & 1) * 64, dq + 2 * k, dk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+        tc_commit(bar_s + 8 * (i & 1));
+        return true;
+      };
+      bool ok = issue_s(0);
+      if (ok && n_sub > 1) ok = issue_s(1);
+      for (int i = 0; i < n_sub && ok; ++i) {
+        const int b = i & 1, blk = i >> 1, sidx = blk % NS;
+        if (!mbar_wait(bar_p + 8 * b, (i >> 1) & 1, &abort_flag, p.status, p.wait_tries)) break;
+        tc_fence_after();
+        const uint32_t vb = stage0 + sidx * kV64Stage + kV64Keys * 128 + b * 8192;
+        const uint32_t tP = tmem + b * 64;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {  // 16 keys per instruction; head, then remainder
+          const uint64_t dv = tc_desc_sw128(vb + kk * 2048);
+          tc_mma_ts(tO, tP + kk * 8, dv, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+          if (LO) tc_mma_ts(tO, tP + 32 + kk * 8, dv, idesc_o, 1u);
+        }
+        tc_commit(bar_pv + 8 * b);
+        if (b == 1 || i + 1 == n_sub) tc_commit(bar_empty + 8 * sidx);  // the stage's last sub-block has read its V rows
+        if (i + 1 == n_sub) tc_commit(bar_o);
+        if (i + 2 < n_sub) ok = issue_s(i + 2);
       }
     }
   } else if ((warp & 3) < n_act) {
-    // ---------------- softmax of rows 16 w .. 16 w + 15, keys 64 kh .. 64 kh + 63 of every block
+    // ---------------- softmax of rows 16 w .. 16 w + 15, keys 32 kh .. 32 kh + 31 of every sub-block
     const int w = warp & 3, kh = warp >> 2;
     const int quad = lane >> 2, qc = lane & 3;
     const int r_lo = 16 * w + quad, r_hi = r_lo + 8;
@@ -1035,48 +1016,51 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
     const int t_end = item.page_end * kPage;
     const uint32_t t_lane = (uint32_t)(32 * w) << 16;
     float m_lo = kNegBig, m_hi = kNegBig;
-    float l_lo = 0.f, l_hi = 0.f;  // this thread's share of the rows' sums (its keys of every block)
+    float l_lo = 0.f, l_hi = 0.f;  // this thread's share of the rows' sums (its keys of every sub-block)
     bool ok = true;
-    for (int blk = 0; blk < n_blk; ++blk) {
-      if (!mbar_wait(bar_s, blk & 1, &abort_flag, p.status, p.wait_tries)) {
+    for (int i = 0; i < n_sub; ++i) {
+      const int b = i & 1;
+      const uint32_t tS = tmem + b * 64;
+      if (!mbar_wait(bar_s + 8 * b, (i >> 1) & 1, &abort_flag, p.status, p.wait_tries)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      uint32_t sv[32];
-      tc_ld_16x256b_x8(tS + t_lane + kh * 64, sv);
-      const int t0 = (item.page_begin + blk * kV64Pages) * kPage;
-      // only blocks at the ends of the visible range need the causal / window / end-of-item mask (CTA-uniform test)
-      const bool edge = (t0 + kV64Keys - 1 > L - ql) || (p.window > 0 && t0 < L - p.window) || (t0 + kV64Keys > t_end);
-      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+      uint32_t sv[16];
+      tc_ld_16x256b_x4(tS + t_lane + kh * 32, sv);
+      const int t0 = (item.page_begin + i * (kV64Pages / 2)) * kPage;
+      // only sub-blocks at the ends of the visible range need the causal / window / end-of-item mask (CTA-uniform test)
+      const bool edge = (t0 + 63 > L - ql) || (p.window > 0 && t0 < L - p.window) || (t0 + 64 > t_end);
       if (edge) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int t = t0 + kh * 64 + 8 * j + 2 * qc + e;
+            const int t = t0 + kh * 32 + 8 * j + 2 * qc + e;
             if (t > pq_lo || t < lw_lo || t >= t_end) sv[4 * j + e] = __float_as_uint(-INFINITY);
             if (t > pq_hi || t < lw_hi || t >= t_end) sv[4 * j + 2 + e] = __float_as_uint(-INFINITY);
           }
       }
+      float mx_lo, mx_hi = -INFINITY;
       {
-        float ta[4], tb[4];  // independent partial maxima, then a tree
+        float ta[2], tb[2];  // independent partial maxima, then a tree
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 2; ++j) {
           ta[j] = fmaxf(fmaxf(__uint_as_float(sv[8 * j]), __uint_as_float(sv[8 * j + 1])),
                         fmaxf(__uint_as_float(sv[8 * j + 4]), __uint_as_float(sv[8 * j + 5])));
           tb[j] = fmaxf(fmaxf(__uint_as_float(sv[8 * j + 2]), __uint_as_float(sv[8 * j + 3])),
                         fmaxf(__uint_as_float(sv[8 * j + 6]), __uint_as_float(sv[8 * j + 7])));
         }
-        mx_lo = fmaxf(fmaxf(ta[0], ta[1]), fmaxf(ta[2], ta[3]));
-        if (hi_on) mx_hi = fmaxf(fmaxf(tb[0], tb[1]), fmaxf(tb[2], tb[3]));
+        mx_lo = fmaxf(ta[0], ta[1]);
+        if (hi_on) mx_hi = fmaxf(tb[0], tb[1]);
       }
       mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-      // the other warp of the row set holds the other 64 keys: exchange the maxima so that both take the same decision
-      // (the next write of these slots follows this block's P V, which waits for both warps' arrival below)
+      // The other warp of the row set holds the other 32 keys: exchange the maxima so that both take the same decision.
+      // The barrier also orders this warp's stores of P behind the partner's loads of S (P overwrites both warps' columns),
+      // and the next write of these slots follows the partner's read: it comes two arrivals of both warps later.
       if (qc == 0) {
         s_mx[kh][r_lo] = mx_lo;
         s_mx[kh][r_hi] = mx_hi;
@@ -1094,9 +1078,14 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
         m_hi = n_hi;
         l_lo *= a_lo;
         l_hi *= a_hi;
-        if (blk > 0) {
-          // O holds earlier blocks (their products are complete: S of this block was issued after them).  Each warp
-          // rescales its half of the columns.
+        if (i > 0) {
+          // O holds earlier sub-blocks; the product of the last one may still run: wait for it, then each warp rescales
+          // its half of the columns
+          if (!mbar_wait(bar_pv + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, &abort_flag, p.status, p.wait_tries)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
           uint32_t ov[16];
           tc_ld_16x256b_x4(tO + t_lane + kh * 32, ov);
 #pragma unroll
@@ -1109,19 +1098,19 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
           tc_st_16x256b_x4(tO + t_lane + kh * 32, ov);
         }
       }
-      // P = 2^(s * scale - m), written over S: bf16 head in columns 0..63, bf16 remainder in columns 64..127.  The steps
-      // are written as separate passes over the thread's 32 values so that independent instructions follow each other
-      // (one warp per scheduler has nothing else to hide an exponential's latency behind).
-      float ev[32];
+      // P = 2^(s * scale - m), written over S: bf16 head in columns 0..31 of the buffer, bf16 remainder in columns
+      // 32..63.  The steps are written as separate passes over the thread's 16 values so that independent instructions
+      // follow each other (a warp has little else to hide an exponential's latency behind).
+      float ev[16];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 4; ++j) {
         ev[4 * j] = fmaf(__uint_as_float(sv[4 * j]), p.scale_log2, -m_lo);
         ev[4 * j + 1] = fmaf(__uint_as_float(sv[4 * j + 1]), p.scale_log2, -m_lo);
         ev[4 * j + 2] = fmaf(__uint_as_float(sv[4 * j + 2]), p.scale_log2, -m_hi);
         ev[4 * j + 3] = fmaf(__uint_as_float(sv[4 * j + 3]), p.scale_log2, -m_hi);
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 4; ++j) {
         ev[4 * j] = fast_exp2(ev[4 * j]);
         ev[4 * j + 1] = fast_exp2(ev[4 * j + 1]);
         if (hi_on) {
@@ -1129,63 +1118,41 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
           ev[4 * j + 3] = fast_exp2(ev[4 * j + 3]);
         }
       }
-      uint32_t ph[16], pl[16];  // registers 2 j, 2 j + 1: rows lane/4 and lane/4 + 8 of key group j
+      uint32_t ph[8], pl[8];  // registers 2 j, 2 j + 1: rows lane/4 and lane/4 + 8 of key group j
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 4; ++j) {
         ph[2 * j] = pack_bf16(ev[4 * j], ev[4 * j + 1]);
         ph[2 * j + 1] = hi_on ? pack_bf16(ev[4 * j + 2], ev[4 * j + 3]) : 0u;
       }
       if (LO) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
           pl[2 * j] = pack_bf16(ev[4 * j] - __uint_as_float(ph[2 * j] << 16), ev[4 * j + 1] - __uint_as_float(ph[2 * j] & 0xFFFF0000u));
           pl[2 * j + 1] = hi_on ? pack_bf16(ev[4 * j + 2] - __uint_as_float(ph[2 * j + 1] << 16),
                                             ev[4 * j + 3] - __uint_as_float(ph[2 * j + 1] & 0xFFFF0000u))
                                 : 0u;
         }
-        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;  // four independent chains
-#pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          s0 += ev[4 * j] + ev[4 * j + 1];
-          s1 += ev[4 * j + 4] + ev[4 * j + 5];
-          if (hi_on) {
-            s2 += ev[4 * j + 2] + ev[4 * j + 3];
-            s3 += ev[4 * j + 6] + ev[4 * j + 7];
-          }
-        }
-        l_lo += s0 + s1;
-        l_hi += s2 + s3;
+        l_lo += (ev[0] + ev[1]) + (ev[4] + ev[5]) + ((ev[8] + ev[9]) + (ev[12] + ev[13]));
+        if (hi_on) l_hi += (ev[2] + ev[3]) + (ev[6] + ev[7]) + ((ev[10] + ev[11]) + (ev[14] + ev[15]));
       } else {  // the row sum is that of the rounded weights, the ones that enter O
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 4; ++j) {
           l_lo += __uint_as_float(ph[2 * j] << 16) + __uint_as_float(ph[2 * j] & 0xFFFF0000u);
           l_hi += __uint_as_float(ph[2 * j + 1] << 16) + __uint_as_float(ph[2 * j + 1] & 0xFFFF0000u);
         }
       }
-      {
-        uint32_t t8[8];
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) t8[i] = ph[8 * jj + i];
-          tc_st_16x128b_x4(tS + t_lane + kh * 32 + jj * 16, t8);
-          if (LO) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) t8[i] = pl[8 * jj + i];
-            tc_st_16x128b_x4(tS + 64 + t_lane + kh * 32 + jj * 16, t8);
-          }
-        }
-      }
+      tc_st_16x128b_x4(tS + t_lane + kh * 16, ph);
+      if (LO) tc_st_16x128b_x4(tS + 32 + t_lane + kh * 16, pl);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p);
+      if (lane == 0) mbar_arrive(bar_p + 8 * b);
     }
     // ---------------- epilogue: this warp's 32 columns of the rows of O; the row sums are added over the quad and the
     // two warps of the row set (both warps pass the barrier: a failed wait above has raised the abort flag for all)
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
     if (qc == 0) {
       s_l[kh][r_lo] = l_lo;
@@ -1194,7 +1161,7 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
     asm volatile("bar.sync %0, 64;" ::"r"(1 + w) : "memory");
     l_lo = s_l[0][r_lo] + s_l[1][r_lo];
     l_hi = s_l[0][r_hi] + s_l[1][r_hi];
-    if (ok && n_blk > 0 && mbar_wait(bar_o, 0, &abort_flag, p.status, p.wait_tries)) {
+    if (ok && n_sub > 0 && mbar_wait(bar_o, 0, &abort_flag, p.status, p.wait_tries)) {
       tc_fence_after();
       const int n_parts_seq = p.seq_part[seq + 1] - p.seq_part[seq];
       const bool direct = (n_parts_seq == 1);
@@ -1409,7 +1376,7 @@ int32_t launch_attn_v64(EncodeTiledFn enc, const void* d_cache, int64_t cache_ro
   V64Params vp;
   vp.n_kv = n_kv;
   vp.ppi = 8 / n_kv;
-  const size_t smem = 1024 + 8192 + (size_t)kV64Stages * kV64Stage + (2 * kV64Stages + 3) * sizeof(uint64_t) + 8 +
+  const size_t smem = 1024 + 8192 + (size_t)kV64Stages * kV64Stage + (2 * kV64Stages + 7) * sizeof(uint64_t) + 8 +
                       kMaxItemPages * sizeof(int32_t);
   auto kfn = attn_v64_kernel<G, LO>;
   static bool configured[64] = {false};  // the attribute is per device
