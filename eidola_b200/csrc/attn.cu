@@ -969,7 +969,9 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
     // products of one sub-block run while the softmax warps work on the next
     if (lane == 0) {
       constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(64 >> 4) << 24);
-      constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) | ((uint32_t)(64 >> 4) << 24);
+      // P V as a 128-row product: lanes 32 w .. 32 w + 15 of P hold the heads, lanes 32 w + 16 .. 32 w + 31 the remainders
+      constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) |
+                                   ((uint32_t)((LO ? 128 : 64) >> 4) << 24);
       const uint64_t dq = tc_desc_sw128(q_addr);
       auto issue_s = [&](int i) -> bool {
         const int blk = i >> 1, sidx = blk % NS;
@@ -992,11 +994,8 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
         const uint32_t vb = stage0 + sidx * kV64Stage + kV64Keys * 128 + b * 8192;
         const uint32_t tP = tmem + b * 64;
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {  // 16 keys per instruction; head, then remainder
-          const uint64_t dv = tc_desc_sw128(vb + kk * 2048);
-          tc_mma_ts(tO, tP + kk * 8, dv, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
-          if (LO) tc_mma_ts(tO, tP + 32 + kk * 8, dv, idesc_o, 1u);
-        }
+        for (int kk = 0; kk < 4; ++kk)  // 16 keys per instruction
+          tc_mma_ts(tO, tP + kk * 8, tc_desc_sw128(vb + kk * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
         tc_commit(bar_pv + 8 * b);
         if (b == 1 || i + 1 == n_sub) tc_commit(bar_empty + 8 * sidx);  // the stage's last sub-block has read its V rows
         if (i + 1 == n_sub) tc_commit(bar_o);
@@ -1086,20 +1085,25 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
             break;
           }
           tc_fence_after();
-          uint32_t ov[16];
-          tc_ld_16x256b_x4(tO + t_lane + kh * 32, ov);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            ov[4 * j] = __float_as_uint(__uint_as_float(ov[4 * j]) * a_lo);
-            ov[4 * j + 1] = __float_as_uint(__uint_as_float(ov[4 * j + 1]) * a_lo);
-            ov[4 * j + 2] = __float_as_uint(__uint_as_float(ov[4 * j + 2]) * a_hi);
-            ov[4 * j + 3] = __float_as_uint(__uint_as_float(ov[4 * j + 3]) * a_hi);
+          for (int part = 0; part < (LO ? 2 : 1); ++part) {  // the heads' product, then the remainders'
+            const uint32_t ta = tO + t_lane + ((uint32_t)(16 * part) << 16) + kh * 32;
+            uint32_t ov[16];
+            tc_ld_16x256b_x4(ta, ov);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              ov[4 * j] = __float_as_uint(__uint_as_float(ov[4 * j]) * a_lo);
+              ov[4 * j + 1] = __float_as_uint(__uint_as_float(ov[4 * j + 1]) * a_lo);
+              ov[4 * j + 2] = __float_as_uint(__uint_as_float(ov[4 * j + 2]) * a_hi);
+              ov[4 * j + 3] = __float_as_uint(__uint_as_float(ov[4 * j + 3]) * a_hi);
+            }
+            tc_st_16x256b_x4(ta, ov);
           }
-          tc_st_16x256b_x4(tO + t_lane + kh * 32, ov);
+          tc_wait_st();
         }
       }
-      // P = 2^(s * scale - m), written over S: bf16 head in columns 0..31 of the buffer, bf16 remainder in columns
-      // 32..63.  The steps are written as separate passes over the thread's 16 values so that independent instructions
+      // P = 2^(s * scale - m), written over S, two keys per column (columns 0..31 of the buffer): the bf16 heads in the
+      // rows' own lanes, the bf16 remainders 16 lanes up, which the 64-row product S never touches.  The steps are written as separate passes over the thread's 16 values so that independent instructions
       // follow each other (a warp has little else to hide an exponential's latency behind).
       float ev[16];
 #pragma unroll
@@ -1142,7 +1146,7 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
         }
       }
       tc_st_16x128b_x4(tS + t_lane + kh * 16, ph);
-      if (LO) tc_st_16x128b_x4(tS + 32 + t_lane + kh * 16, pl);
+      if (LO) tc_st_16x128b_x4(tS + t_lane + (16u << 16) + kh * 16, pl);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -1170,6 +1174,12 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
       if (!part_ok && lane == 0 && kh == 0) atomicOr(p.status, EB_DEV_BAD_INDEX);
       uint32_t ov[16];
       tc_ld_16x256b_x4(tO + t_lane + kh * 32, ov);
+      if (LO) {  // O = P_head V + P_remainder V
+        uint32_t o2[16];
+        tc_ld_16x256b_x4(tO + t_lane + (16u << 16) + kh * 32, o2);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) + __uint_as_float(o2[j]));
+      }
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const bool row_ok = half ? ok_hi : ok_lo;
