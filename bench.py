@@ -375,7 +375,8 @@ class AttnWorkload:
         capi.call("eb_synth_normal_bf16", c_vp(self.d_q.ptr), c_i64(T * self.n_q * HEAD_DIM), c_u64(seed), c_u64(S_Q), c_u64(0), c_f32(1.0), None)
         capi.call("eb_synth_normal_f32", c_vp(self.d_sinks.ptr), c_i64(self.n_q), c_u64(seed), c_u64(S_SINK), c_u64(0), c_f32(1.0), None)
         self.d_bt = DeviceBuffer.from_array(self.bt)
-        self.plan = eb.attn_plan(self.ctx, self.q_lens, PAGE, window, int(os.environ.get("EB_PLAN_SM", self.info["sm_count"])), 0, 1)
+        self.plan = eb.attn_plan(self.ctx, self.q_lens, PAGE, window,
+                                 eb.attn_plan_sm_count(self.info["sm_count"], q_len, self.n_q, self.n_kv, window), 0, 1)
         self.launch = AttnLaunch(d_q=self.d_q.ptr, q_stride=self.n_q * HEAD_DIM, d_out=self.d_out.ptr,
                                  out_stride=self.n_q * HEAD_DIM, d_cache=self.d_cache.ptr, num_pages=self.num_pages,
                                  d_block_tables=self.d_bt.ptr, bt_stride=self.bt.shape[1], packed=self.packed,

@@ -406,25 +406,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Verify shapes on the sm_100a tensor cores (tcgen05).  With 17..48 query rows per KV head the mma.sync kernel above is
-// bound by the legacy tensor pipe; here S = Q K^T and O += P V run as tcgen05.mma with the accumulators in tensor
-// memory.  One CTA = one work item x HPC KV heads; warpgroup h (128 threads) owns head h: thread <-> tensor-memory lane
-// <-> query row (position, head of the GQA group).  A block is 32 keys = 2 pages; the producer warp fetches, per page,
-// the K and the V rows of each head with their own 2 KiB TMA copies, so that a head's 32 keys are contiguous in
-// shared memory (K as a K-major, V as an MN-major operand, 128-byte swizzle).  Per block and head:
-//   S[128 x 32]  = Q (shared memory, rows beyond the real ones are whatever follows) x K^T      4 MMAs (K = 16 dims each)
-//   softmax: every thread reads its row of S from tensor memory, masks, exponentiates against a running reference
-//            maximum that is only raised when a score exceeds it by 2^8 (then O is rescaled in tensor memory), and
-//            writes P back over S as a bf16 head and a bf16 remainder (the same ~16 bits as the mma.sync kernel)
-//   O[128 x 64] += P (tensor memory) x V                                                         4 MMAs (16 keys each)
-// S is double buffered: one thread of the warpgroup (lane 0 of a warp that holds no rows, when there is one) issues P V
-// of block i and S of block i + 2 together, so the softmax of block i + 1 never waits for a product of block i.
-// Odd heads place their rows 64 lanes up (their Q operand starts 8 KiB early), which spreads the exponentials of a
-// 40-row verify step over all four scheduler partitions.
-constexpr int kTcKeys = 32;
-constexpr int kTcPages = kTcKeys / kPage;
-constexpr int kTcQPad = 8192;  // bytes in front of the Q tiles that an odd head's operand may start in
-
+// tcgen05 helpers of the verify kernel below.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -453,374 +435,34 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d, uint32_t a_tmem, uint64_t 
 }
 #define EB_O8(a, o) "=r"(a[o]), "=r"(a[o + 1]), "=r"(a[o + 2]), "=r"(a[o + 3]), "=r"(a[o + 4]), "=r"(a[o + 5]), "=r"(a[o + 6]), "=r"(a[o + 7])
 #define EB_I8(a, o) "r"(a[o]), "r"(a[o + 1]), "r"(a[o + 2]), "r"(a[o + 3]), "r"(a[o + 4]), "r"(a[o + 5]), "r"(a[o + 6]), "r"(a[o + 7])
-// 32 lanes x 32 columns of tensor memory -> 32 registers per thread (waits for the data).
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
-      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : EB_O8(r, 0), EB_O8(r, 8), EB_O8(r, 16), EB_O8(r, 24)
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
-      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
-      ::EB_I8(r, 0), EB_I8(r, 8), EB_I8(r, 16), EB_I8(r, 24), "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-struct TcParams {
-  int32_t n_kv;     // KV heads held by this rank
-  int32_t group;    // query heads per KV head
-  int32_t ppi;      // partial slots the plan reserves per item (8 / n_kv)
-  int32_t stages;   // pipeline stages that fit in shared memory
-  int32_t q_bytes;  // bytes of one head's Q tile (rows rounded up to 8, 128 bytes per row)
-};
-
-template <int HPC>
-__global__ void __launch_bounds__(HPC * 128 + 32, 1)
-attn_tc_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, const TcParams tp) {
-  eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
-  eb::pdl_trigger();
-  constexpr int kStage = HPC * kTcPages * 4096;  // kTcPages pages x (K + V) x HPC heads x 2 KiB
-  constexpr int kHeadK = kTcPages * 2048;        // one head's K (or V) rows of a block
-  constexpr int kMaxStages = 6;
-  constexpr uint32_t kCols = HPC * 128;  // per head: two S / P buffers of 32 columns, O 64 columns
-  const int NS = tp.stages;
-
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* sm = smem_raw + (base - raw);
-  const uint32_t q_region = base + kTcQPad;
-  const uint32_t q_total = ((uint32_t)(HPC * tp.q_bytes) + 1023u) & ~1023u;
-  const uint32_t stage0 = q_region + q_total;
-  uint8_t* after = sm + kTcQPad + q_total + (size_t)NS * kStage;
-  // barriers: full[6], empty[6], then per head: s[2] (one per S buffer), pdone, pv[2], o
-  uint64_t* bars = reinterpret_cast<uint64_t*>(after);
-  int32_t* page_ids = reinterpret_cast<int32_t*>(after + (2 * kMaxStages + 6 * HPC) * sizeof(uint64_t));
-  __shared__ int abort_flag;
-  __shared__ int n_issued;
-  __shared__ uint32_t tmem_slot;
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const eb_attn_item item = p.items[blockIdx.x];
-  const int head0 = blockIdx.y * HPC;
-  const int seq = item.seq;
-  const int slot = p.seq_slots[seq];
-  const int L = p.ctx_lens[seq];
-  const int q0 = p.q_off[seq];
-  const int ql = p.q_off[seq + 1] - q0;
-  int n_pages = item.page_end - item.page_begin;
-  if (n_pages > kMaxItemPages) {
-    if (tid == 0) atomicOr(p.status, EB_DEV_BAD_INDEX);
-    n_pages = kMaxItemPages;
-  }
-  for (int j = tid; j < n_pages; j += HPC * 128 + 32) {
-    int32_t id = p.block_tables[(int64_t)slot * p.bt_stride + item.page_begin + j];
-    if (id < 0 || id >= p.num_pages) {
-      atomicOr(p.status, EB_DEV_BAD_INDEX);
-      id = 0;
-    }
-    page_ids[j] = id;
-  }
-  const uint32_t bar_full = smem_u32(&bars[0]), bar_empty = smem_u32(&bars[kMaxStages]);
-  const uint32_t bar_head = smem_u32(&bars[2 * kMaxStages]);  // + 48 * h: s0, s1, pdone, pv0, pv1, o
-  const int q_rows = ql * tp.group;                       // real query rows of this sequence
-  const int n_act = (q_rows + 31) / 32;                   // warps of a warpgroup that hold real rows
-  if (tid == 0) {
-    abort_flag = 0;
-    n_issued = 0;
-    for (int i = 0; i < kMaxStages; ++i) {
-      mbar_init(bar_full + 8 * i, 1);
-      mbar_init(bar_empty + 8 * i, HPC);
-    }
-    for (int h = 0; h < HPC; ++h) {
-      const uint32_t bh = bar_head + 48 * h;
-      mbar_init(bh, 1);
-      mbar_init(bh + 8, 1);
-      mbar_init(bh + 16, (uint32_t)n_act);
-      mbar_init(bh + 24, 1);
-      mbar_init(bh + 32, 1);
-      mbar_init(bh + 40, 1);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == HPC * 4) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(kCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  // Q tiles: warpgroup h writes head h's rows with the 128-byte swizzle a TMA copy would apply; rows past the
-  // sequence's query length are zero
-  if (warp < HPC * 4) {
-    const int h = warp >> 2, t = tid & 127;
-    const int rows8 = tp.q_bytes >> 7;
-    uint8_t* qt = sm + kTcQPad + (size_t)h * tp.q_bytes;
-    for (int i = t; i < rows8 * 8; i += 128) {
-      const int r = i >> 3, c = i & 7;
-      const int qi = r / tp.group, g = r - qi * tp.group;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (qi < ql) {
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.q + (int64_t)(q0 + qi) * p.q_stride +
-                                                                (int64_t)((head0 + h) * tp.group + g) * kHeadDim + c * 8);
-        v = make_uint4(src[0], src[1], src[2], src[3]);
-      }
-      *reinterpret_cast<uint4*>(qt + r * 128 + ((c ^ (r & 7)) << 4)) = v;
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = tmem_slot;
-  const int n_blk = (n_pages + kTcPages - 1) / kTcPages;
-  const int page_rows = 2 * tp.n_kv * kPage;
-
-  if (warp == HPC * 4) {
-    // ---------------- producer
-    if (lane == 0) {
-      for (int blk = 0; blk < n_blk; ++blk) {
-        const int sidx = blk % NS;
-        if (blk >= NS && !mbar_wait(bar_empty + 8 * sidx, ((blk / NS) - 1) & 1, &abort_flag, p.status, p.wait_tries)) break;
-        const uint32_t full = bar_full + 8 * sidx;
-        mbar_arrive_expect_tx(full, (uint32_t)kStage);
-        const uint32_t sb = stage0 + sidx * kStage;
-        for (int j = 0; j < kTcPages; ++j) {
-          const int pl = min(blk * kTcPages + j, n_pages - 1);  // a block's missing pages repeat the last one (masked below)
-          const int row = page_ids[pl] * page_rows;
-#pragma unroll
-          for (int h = 0; h < HPC; ++h) {
-            tma_load_2d(sb + h * kHeadK + j * 2048, &tmap, 0, row + (head0 + h) * kPage, full);
-            tma_load_2d(sb + HPC * kHeadK + h * kHeadK + j * 2048, &tmap, 0, row + (tp.n_kv + head0 + h) * kPage, full);
-          }
-        }
-        n_issued = blk + 1;
-      }
-    }
-  } else {
-    // ---------------- warpgroup h: softmax of head h, and its MMA issuer
-    const int h = warp >> 2, qtr = warp & 3;
-    const int row_off = (h & 1) ? 64 : 0;           // odd heads live 64 lanes up
-    const int r = (tid & 127) - row_off;            // query row of this thread (may be outside [0, q_rows))
-    const int first_q = row_off >> 5;
-    const bool active = qtr >= first_q && qtr < first_q + n_act;   // warp-uniform
-    // the MMA issuer of the head: lane 0 of a warp that holds no rows (rows <= 64), else of the first active warp
-    const bool spare_issuer = n_act <= 2;
-    const bool issuer_warp = spare_issuer ? qtr == ((first_q + 2) & 3) : qtr == first_q;
-    const bool elected = issuer_warp && lane == 0;
-    const bool row_ok = r >= 0 && r < q_rows;
-    const int qi = row_ok ? r / tp.group : 0;
-    const int head = (head0 + h) * tp.group + (row_ok ? r - qi * tp.group : 0);
-    const int pq = L - ql + qi;                                    // absolute position of this row's query
-    const int lo_w = p.window > 0 ? pq - p.window + 1 : 0;
-    const int t_end = item.page_end * kPage;
-    const uint32_t tS = tmem + h * 128, tO = tS + 64;              // S / P buffer b at tS + 32 b
-    const uint32_t lane_sel = (uint32_t)(qtr * 32) << 16;
-    const uint32_t q_addr = q_region + h * tp.q_bytes - ((h & 1) ? 8192 : 0);
-    const uint32_t bh = bar_head + 48 * h;
-    const uint32_t bar_s = bh, bar_pd = bh + 16, bar_pv = bh + 24, bar_o = bh + 40;
-    constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kTcKeys >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) |
-                                 ((uint32_t)(128 >> 4) << 24);  // V is MN-major: [key][dim] with the dims contiguous
-    float m_used = kNegBig, l_run = 0.f;
-    bool ok = true;
-
-    // S of block `blk` into buffer blk & 1 (the MMAs run in issue order, so this follows the P V product that last
-    // read that buffer)
-    auto issue_s = [&](int blk) -> bool {
-      const int sidx = blk % NS;
-      if (!mbar_wait(bar_full + 8 * sidx, (blk / NS) & 1, &abort_flag, p.status, p.wait_tries)) return false;
-      tc_fence_after();
-      const uint64_t dq = tc_desc_sw128(q_addr), dk = tc_desc_sw128(stage0 + sidx * kStage + h * kHeadK);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) tc_mma_ss(tS + (blk & 1) * 32, dq + 2 * k, dk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
-      tc_commit(bar_s + 8 * (blk & 1));
-      return true;
-    };
-    // every active warp of the head has written its rows of P for block `blk`: O += P V, then the S of the block after
-    // next (or the final commit)
-    auto issue_pv = [&](int blk) -> bool {
-      const int b = blk & 1;
-      if (!mbar_wait(bar_pd, blk & 1, &abort_flag, p.status, p.wait_tries)) return false;
-      tc_fence_after();
-      const int sidx = blk % NS;
-      const uint64_t dv = tc_desc_sw128(stage0 + sidx * kStage + HPC * kHeadK + h * kHeadK);
-#pragma unroll
-      for (int kk = 0; kk < kTcKeys / 16; ++kk) {  // 16 keys per instruction; head, then remainder
-        const uint32_t a_hi = tS + b * 32 + kk * 8;
-        tc_mma_ts(tO, a_hi, dv + (uint64_t)kk * (2048 >> 4), idesc_o, (blk > 0 || kk > 0) ? 1u : 0u);
-        tc_mma_ts(tO, a_hi + 16, dv + (uint64_t)kk * (2048 >> 4), idesc_o, 1u);
-      }
-      tc_commit(bar_empty + 8 * sidx);  // the stage is free once these have read V (K was read by S)
-      tc_commit(bar_pv + 8 * b);
-      bool good = true;
-      if (blk + 2 < n_blk) good = issue_s(blk + 2);
-      if (blk + 1 == n_blk) tc_commit(bar_o);
-      return good;
-    };
-    if (elected) {
-      ok = issue_s(0);
-      if (ok && n_blk > 1) ok = issue_s(1);
-      if (spare_issuer)  // a warp without rows: it only issues, block after block
-        for (int blk = 0; blk < n_blk && ok; ++blk) ok = issue_pv(blk);
-    }
-
-    if (active) {
-      for (int blk = 0; blk < n_blk && ok; ++blk) {
-        const int b = blk & 1;
-        if (!mbar_wait(bar_s + 8 * b, (blk >> 1) & 1, &abort_flag, p.status, p.wait_tries)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const int t0 = (item.page_begin + blk * kTcPages) * kPage;
-        // only blocks at the ends of the visible range need the causal / window / end-of-item mask (CTA-uniform test)
-        const bool edge = (t0 + kTcKeys - 1 > L - ql) || (p.window > 0 && t0 < L - p.window) || (t0 + kTcKeys > t_end);
-        uint32_t sv[32];
-        tc_ld32(tS + lane_sel + b * 32, sv);
-        float mx = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int t = t0 + j;
-          float x = __uint_as_float(sv[j]);
-          if (edge && (t > pq || t < lo_w || t >= t_end)) x = -INFINITY;
-          sv[j] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
-        }
-        if (!row_ok) mx = -INFINITY;
-        const float m_blk = mx * p.scale_log2;
-        // raise the reference maximum only when a score exceeds it by 2^8 (always on the first finite one)
-        const bool raise = m_blk > m_used + 8.0f;
-        if (__any_sync(0xffffffffu, raise)) {
-          const float m_new = raise ? m_blk : m_used;
-          const float alpha = fast_exp2(m_used - m_new);
-          m_used = m_new;
-          l_run *= alpha;
-          if (blk > 0) {
-            // O holds earlier blocks: wait for the last product that adds to it, then rescale this row in tensor memory
-            if (!mbar_wait(bar_pv + 8 * ((blk - 1) & 1), ((blk - 1) >> 1) & 1, &abort_flag, p.status, p.wait_tries)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-              uint32_t ov[32];
-              tc_ld32(tO + lane_sel + half * 32, ov);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * alpha);
-              tc_st32(tO + lane_sel + half * 32, ov);
-            }
-          }
-        }
-        // P = 2^(s * scale - m_used), written over S as a bf16 head (16 columns) and a bf16 remainder (16 columns)
-        uint32_t pk[32];
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float p0 = row_ok ? fast_exp2(fmaf(__uint_as_float(sv[2 * c]), p.scale_log2, -m_used)) : 0.f;
-          const float p1 = row_ok ? fast_exp2(fmaf(__uint_as_float(sv[2 * c + 1]), p.scale_log2, -m_used)) : 0.f;
-          l_run += p0 + p1;
-          const uint32_t hi = pack_bf16(p0, p1);
-          pk[c] = hi;
-          pk[16 + c] = pack_bf16(p0 - __uint_as_float(hi << 16), p1 - __uint_as_float(hi & 0xFFFF0000u));
-        }
-        tc_st32(tS + lane_sel + b * 32, pk);
-        tc_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_pd);
-        if (elected && !spare_issuer) ok = issue_pv(blk);
-        if (issuer_warp) ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;  // the issuer's warp follows its lane 0
-      }
-      // ---------------- epilogue: O of this row
-      if (ok && n_blk > 0 && mbar_wait(bar_o, 0, &abort_flag, p.status, p.wait_tries)) {
-        tc_fence_after();
-        const int n_parts_seq = p.seq_part[seq + 1] - p.seq_part[seq];
-        const bool direct = (n_parts_seq == 1);
-        // partial slots [item.part, item.part + ppi) must lie inside the scratch; otherwise skip and flag
-        const bool part_ok = direct || (item.part >= 0 && item.part + tp.ppi <= p.part_slots);
-        if (!part_ok && lane == 0) atomicOr(p.status, EB_DEV_BAD_INDEX);
-        const bool store_ok = row_ok && part_ok;
-        float inv = 0.f;
-        if (direct) {
-          const float sk = p.sinks[head] * 1.4426950408889634f;
-          const float mf = fmaxf(m_used, sk);
-          const float w = exp2f(m_used - mf);
-          inv = w / (l_run * w + exp2f(sk - mf));
-        }
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t ov[32];
-          tc_ld32(tO + lane_sel + half * 32, ov);
-          if (!store_ok) continue;
-          if (direct) {
-            uint32_t* orow = reinterpret_cast<uint32_t*>(p.out + (int64_t)(q0 + qi) * p.out_stride + (int64_t)head * kHeadDim + half * 32);
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              orow[j] = pack_bf16(__uint_as_float(ov[2 * j]) * inv, __uint_as_float(ov[2 * j + 1]) * inv);
-          } else {
-            const int64_t prow = ((int64_t)item.part * p.max_q_len + qi) * p.n_q + head;
-            float4* arow = reinterpret_cast<float4*>(p.part_acc + prow * kHeadDim + half * 32);
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              arow[j] = make_float4(__uint_as_float(ov[4 * j]), __uint_as_float(ov[4 * j + 1]), __uint_as_float(ov[4 * j + 2]),
-                                    __uint_as_float(ov[4 * j + 3]));
-            if (half == 0) *reinterpret_cast<float2*>(p.part_ml + prow * 2) = make_float2(m_used, l_run);
-          }
-        }
-        if (!direct && store_ok) {
-          // the plan reserves tp.ppi partial slots per item; this kernel fills one, the others are declared empty
-          for (int e = 1; e < tp.ppi; ++e) {
-            const int64_t prow = ((int64_t)(item.part + e) * p.max_q_len + qi) * p.n_q + head;
-            *reinterpret_cast<float2*>(p.part_ml + prow * 2) = make_float2(kNegBig, 0.f);
-            float4* arow = reinterpret_cast<float4*>(p.part_acc + prow * kHeadDim);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) arow[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-        }
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  if (abort_flag && tid == 0) {
-    // A wait gave up.  Before the CTA releases its shared memory, wait (bounded) for the copies still in flight.
-    const int issued = n_issued;
-    for (int blk = max(0, issued - NS); blk < issued; ++blk) {
-      const uint32_t bar = bar_full + 8 * (blk % NS);
-      for (uint32_t i = 0; i < kWaitTries; ++i) {
-        if (mbar_try_wait(bar, (blk / NS) & 1)) break;
-        __nanosleep(64);
-      }
-    }
-  }
-  __syncthreads();
-  if (warp == HPC * 4) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kCols) : "memory");
-}
-
 // ---------------------------------------------------------------------------------------------
-// Verify shapes on tcgen05 with 64-row tiles.  One CTA = one work item x one KV head, two CTAs per SM; a block is 128
-// keys (8 pages), fetched per page as one 2 KiB TMA copy of the head's K rows and one of its V rows.
-//   S[64 x 128] = Q K^T                  4 MMAs (M = 64: row r of the tile lives in tensor-memory lane 32 (r / 16) + r % 16)
-//   softmax                              warps w and w + 4 own rows 16 w .. 16 w + 15 (keys 0..63 and 64..127) and read them
-//                                        with the 16x256b shape: a thread holds, per group of 8 keys, two adjacent keys of
-//                                        row lane / 4 and of row lane / 4 + 8, so all 32 lanes work whenever the warp has 16
-//                                        rows; the two warps exchange their halves' maxima through shared memory.  The reference
-//                                        maximum of a row is shared by the four lanes of its quad and only raised when a
-//                                        score exceeds it by 2^8 (then the row of O is rescaled in tensor memory); a thread
-//                                        keeps the sum of its own weights and the row sums are formed once, at the end.
-//   O[64 x 64] += P V                    16 MMAs: P overwrites S in place as a bf16 head (columns 0..63) and a bf16
-//                                        remainder (columns 64..127), packed two keys per column with the 16x128b store
-//                                        shape, which lands exactly where the A operand of the product is read; V is the
-//                                        MN-major B operand.  (A 72-column product that also accumulated the row sums
-//                                        against a tile of ones was measured at the cost of 128 columns, 65 clocks per MMA
-//                                        instead of 32.)
-// The chain S -> softmax -> P V of one CTA is serial (P lives where S was); the second CTA of the SM fills its gaps.
+// Verify shapes on the sm_100a tensor cores (tcgen05).  With 17..48 query rows per KV head the mma.sync kernel above is
+// bound by the legacy tensor pipe and by instruction issue (0.44 of the HBM rate at q_len 5); here S = Q K^T and
+// O += P V run as tcgen05.mma with the accumulators in tensor memory.  One CTA = one work item x one KV head, two CTAs
+// per SM.  A pipeline stage is 128 keys (8 pages), fetched per page as one 2 KiB TMA copy of the head's K rows and one
+// of its V rows; it is worked on as two sub-blocks of 64 keys, which alternate between two 64-column buffers of tensor
+// memory, so that the products of one sub-block run while the softmax warps work on the next.  Per sub-block:
+//   S[64 x 64] = Q K^T       4 MMAs with M = 64: row r of the tile lives in tensor-memory lane 32 (r / 16) + r % 16,
+//                            so rows 16 w .. 16 w + 15 belong to the lane quarter of warps w and w + 4
+//   softmax                  warps w and w + 4 take keys 0..31 and 32..63 of those rows and read them with the 16x256b
+//                            shape: a thread holds, per group of 8 keys, two adjacent keys of row lane / 4 and of row
+//                            lane / 4 + 8, so all 32 lanes work whenever the warp has 16 rows.  The two warps exchange
+//                            their maxima through shared memory.  The reference maximum of a row is only raised when a
+//                            score exceeds it by 2^8 (then the row of O is rescaled in tensor memory), a thread keeps
+//                            the sum of its own weights, and the row sums are formed once, at the end of the item.
+//   P                        written over S with the 16x128b store shape, two keys per column, which lands exactly
+//                            where the A operand of the second product is read: the bf16 heads in the rows' own lanes,
+//                            the bf16 remainders 16 lanes up, in the lanes a 64-row product never touches
+//   O[128 x 64] += P V       4 MMAs with M = 128 (V is the MN-major B operand): lanes 32 w .. 32 w + 15 accumulate
+//                            P_head V, lanes 32 w + 16 .. 32 w + 31 P_remainder V; the two are added in the epilogue
+// Measured on the way (256 ragged sequences, q_len 5, CUDA events): every MMA of these shapes occupies the issuing
+// thread for about 64 clocks whatever its N (a 72-column product that also accumulated the row sums against a tile of
+// ones cost as much as 128 columns), so the count of MMAs matters, not their size: 16 + 8 per 128 keys with head and
+// remainder as separate 64-row products made the MMA thread the bottleneck (358 us), 8 + 8 as above do not (332 us).
+// A bf16 A operand cannot be paired with an fp16 one (the instruction is rejected), so P stays head + remainder: P as a
+// single bf16 passes the operator tests at 376 us of the earlier variant but fails the whole-decoder parity bounds.
 constexpr int kV64Keys = 128;
 constexpr int kV64Pages = kV64Keys / kPage;
 constexpr int kV64Stage = 2 * kV64Keys * 128;  // K rows then V rows of one head
@@ -854,7 +496,7 @@ struct V64Params {
   int32_t ppi;   // partial slots the plan reserves per item (8 / n_kv)
 };
 
-template <int G, bool LO>  // query heads per KV head; LO: P carries a bf16 remainder besides its bf16 head
+template <int G>  // query heads per KV head
 __global__ void __launch_bounds__(kV64Threads, 2)
 attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, const V64Params vp) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
@@ -971,7 +613,7 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
       constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(64 >> 4) << 24);
       // P V as a 128-row product: lanes 32 w .. 32 w + 15 of P hold the heads, lanes 32 w + 16 .. 32 w + 31 the remainders
       constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kHeadDim >> 3) << 17) |
-                                   ((uint32_t)((LO ? 128 : 64) >> 4) << 24);
+                                   ((uint32_t)(128 >> 4) << 24);
       const uint64_t dq = tc_desc_sw128(q_addr);
       auto issue_s = [&](int i) -> bool {
         const int blk = i >> 1, sidx = blk % NS;
@@ -1086,7 +728,7 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
           }
           tc_fence_after();
 #pragma unroll
-          for (int part = 0; part < (LO ? 2 : 1); ++part) {  // the heads' product, then the remainders'
+          for (int part = 0; part < 2; ++part) {  // the heads' product, then the remainders'
             const uint32_t ta = tO + t_lane + ((uint32_t)(16 * part) << 16) + kh * 32;
             uint32_t ov[16];
             tc_ld_16x256b_x4(ta, ov);
@@ -1128,25 +770,17 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
         ph[2 * j] = pack_bf16(ev[4 * j], ev[4 * j + 1]);
         ph[2 * j + 1] = hi_on ? pack_bf16(ev[4 * j + 2], ev[4 * j + 3]) : 0u;
       }
-      if (LO) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          pl[2 * j] = pack_bf16(ev[4 * j] - __uint_as_float(ph[2 * j] << 16), ev[4 * j + 1] - __uint_as_float(ph[2 * j] & 0xFFFF0000u));
-          pl[2 * j + 1] = hi_on ? pack_bf16(ev[4 * j + 2] - __uint_as_float(ph[2 * j + 1] << 16),
-                                            ev[4 * j + 3] - __uint_as_float(ph[2 * j + 1] & 0xFFFF0000u))
-                                : 0u;
-        }
-        l_lo += (ev[0] + ev[1]) + (ev[4] + ev[5]) + ((ev[8] + ev[9]) + (ev[12] + ev[13]));
-        if (hi_on) l_hi += (ev[2] + ev[3]) + (ev[6] + ev[7]) + ((ev[10] + ev[11]) + (ev[14] + ev[15]));
-      } else {  // the row sum is that of the rounded weights, the ones that enter O
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          l_lo += __uint_as_float(ph[2 * j] << 16) + __uint_as_float(ph[2 * j] & 0xFFFF0000u);
-          l_hi += __uint_as_float(ph[2 * j + 1] << 16) + __uint_as_float(ph[2 * j + 1] & 0xFFFF0000u);
-        }
+      for (int j = 0; j < 4; ++j) {
+        pl[2 * j] = pack_bf16(ev[4 * j] - __uint_as_float(ph[2 * j] << 16), ev[4 * j + 1] - __uint_as_float(ph[2 * j] & 0xFFFF0000u));
+        pl[2 * j + 1] = hi_on ? pack_bf16(ev[4 * j + 2] - __uint_as_float(ph[2 * j + 1] << 16),
+                                          ev[4 * j + 3] - __uint_as_float(ph[2 * j + 1] & 0xFFFF0000u))
+                              : 0u;
       }
+      l_lo += (ev[0] + ev[1]) + (ev[4] + ev[5]) + ((ev[8] + ev[9]) + (ev[12] + ev[13]));
+      if (hi_on) l_hi += (ev[2] + ev[3]) + (ev[6] + ev[7]) + ((ev[10] + ev[11]) + (ev[14] + ev[15]));
       tc_st_16x128b_x4(tS + t_lane + kh * 16, ph);
-      if (LO) tc_st_16x128b_x4(tS + t_lane + (16u << 16) + kh * 16, pl);
+      tc_st_16x128b_x4(tS + t_lane + (16u << 16) + kh * 16, pl);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
@@ -1174,7 +808,7 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
       if (!part_ok && lane == 0 && kh == 0) atomicOr(p.status, EB_DEV_BAD_INDEX);
       uint32_t ov[16];
       tc_ld_16x256b_x4(tO + t_lane + kh * 32, ov);
-      if (LO) {  // O = P_head V + P_remainder V
+      {  // O = P_head V + P_remainder V
         uint32_t o2[16];
         tc_ld_16x256b_x4(tO + t_lane + (16u << 16) + kh * 32, o2);
 #pragma unroll
@@ -1331,47 +965,8 @@ int32_t launch_attn(const CUtensorMap& tm, const AttnParams& p, int n_items, cud
   return EB_OK;
 }
 
-// Verify shapes on tcgen05: HPC KV heads per CTA, grid = (items, n_kv / HPC).
-template <int HPC>
-int32_t launch_attn_tc(EncodeTiledFn enc, const void* d_cache, int64_t cache_rows, const AttnParams& p, int n_items, int n_kv,
-                       int group, cudaStream_t st) {
-  CUtensorMap tm;  // the cache as rows of 128 bytes; a copy is the 16 rows (tokens) of one head's K or V in one page
-  const cuuint64_t gdim[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)cache_rows};
-  const cuuint64_t gstr[1] = {128};
-  const cuuint32_t box[2] = {(cuuint32_t)kHeadDim, (cuuint32_t)kPage};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult cr = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(d_cache), gdim, gstr, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  EB_REQUIRE(cr == CUDA_SUCCESS, EB_ERR_ARG, "attention: cuTensorMapEncodeTiled failed (%d)", (int)cr);
-  TcParams tp;
-  tp.n_kv = n_kv;
-  tp.group = group;
-  tp.ppi = 8 / n_kv;
-  const int rows8 = (p.max_q_len * group + 7) / 8 * 8;
-  tp.q_bytes = rows8 * 128;
-  const size_t fixed = 1024 + kTcQPad + (((size_t)HPC * tp.q_bytes + 1023) & ~(size_t)1023) + (2 * 6 + 6 * HPC) * sizeof(uint64_t) +
-                       kMaxItemPages * sizeof(int32_t);
-  const size_t stage = (size_t)HPC * kTcPages * 4096;
-  const size_t cap = 227 * 1024 - 1024;  // dynamic shared memory a CTA may ask for, less the kernel's static variables
-  tp.stages = (int)std::min<size_t>(6, fixed < cap ? (cap - fixed) / stage : 0);
-  EB_REQUIRE(tp.stages >= 2, EB_ERR_UNSUPPORTED, "attention: max_q_len %d leaves no room for two pipeline stages", p.max_q_len);
-  const size_t smem = fixed + tp.stages * stage;
-  auto kfn = attn_tc_kernel<HPC>;
-  static bool configured[64] = {false};  // the attribute is per device
-  int dev = 0;
-  EB_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    EB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cap));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
-  EB_CUDA(eb::launch(kfn, dim3((unsigned)n_items, (unsigned)(n_kv / HPC)), dim3(HPC * 128 + 32), smem, st, tm, p, tp));
-  EB_LAUNCH_CHECK();
-  return EB_OK;
-}
-
 // Verify shapes on tcgen05 with 64-row tiles: grid = (items, KV heads), two CTAs per SM.
-template <int G, bool LO>
+template <int G>
 int32_t launch_attn_v64(EncodeTiledFn enc, const void* d_cache, int64_t cache_rows, const AttnParams& p, int n_items, int n_kv,
                         cudaStream_t st) {
   CUtensorMap tm;  // the cache as rows of 128 bytes; a copy is the 16 rows (tokens) of one head's K or V in one page
@@ -1388,7 +983,7 @@ int32_t launch_attn_v64(EncodeTiledFn enc, const void* d_cache, int64_t cache_ro
   vp.ppi = 8 / n_kv;
   const size_t smem = 1024 + 8192 + (size_t)kV64Stages * kV64Stage + (2 * kV64Stages + 7) * sizeof(uint64_t) + 8 +
                       kMaxItemPages * sizeof(int32_t);
-  auto kfn = attn_v64_kernel<G, LO>;
+  auto kfn = attn_v64_kernel<G>;
   static bool configured[64] = {false};  // the attribute is per device
   int dev = 0;
   EB_CUDA(cudaGetDevice(&dev));
@@ -1401,28 +996,15 @@ int32_t launch_attn_v64(EncodeTiledFn enc, const void* d_cache, int64_t cache_ro
   return EB_OK;
 }
 
-// EIDOLA_B200_ATTN_TC=1 runs verify shapes on the tcgen05 kernel.  It is exact to the same tolerance as the mma.sync
-// kernel but measured slower (741 us against 530 us at q_len 5 on the 256-sequence benchmark: the per-block chain
-// tensor-memory load -> exponentials -> tensor-memory store -> barrier -> MMA issue is what bounds it, not the tensor
-// pipe, which is 13 % busy), so it is off unless asked for.  Read on every call so that a test can switch it.
-bool attn_tc_enabled() {
-  const char* v = getenv("EIDOLA_B200_ATTN_TC");
-  return v && v[0] == '1';
-}
-bool attn_v64_enabled() {
-  const char* v = getenv("EIDOLA_B200_ATTN_TC");
-  return v && v[0] == '2';
-}
-
-int32_t dispatch_attn_tc(EncodeTiledFn enc, const void* d_cache, int64_t cache_rows, const AttnParams& p, int n_items, int n_kv,
-                         int group, cudaStream_t st) {
-  switch (n_kv) {
-    case 8:
-    case 4: return launch_attn_tc<4>(enc, d_cache, cache_rows, p, n_items, n_kv, group, st);
-    case 2: return launch_attn_tc<2>(enc, d_cache, cache_rows, p, n_items, n_kv, group, st);
-    case 1: return launch_attn_tc<1>(enc, d_cache, cache_rows, p, n_items, n_kv, group, st);
-  }
-  return eb::fail(EB_ERR_UNSUPPORTED, "attention: n_kv %d not in {1,2,4,8}", n_kv);
+// Verify shapes (17..48 query rows per KV head) run on the tcgen05 kernel when the work items are long: full-attention
+// layers, or windows of 2048 tokens and more.  Measured on 256 ragged sequences at q_len 5: 332 us against 526 us for
+// the mma.sync kernel on full layers, but 66 us against 47 us on a 128-token window, whose items are two or three
+// 64-key sub-blocks long.  EIDOLA_B200_ATTN_VERIFY=mma keeps every shape on the mma.sync kernel (read on every call so
+// that a test can compare the two).
+bool attn_verify_on_tcgen05(int window) {
+  const char* v = getenv("EIDOLA_B200_ATTN_VERIFY");
+  if (v && v[0] == 'm') return false;
+  return window == 0 || window >= 2048;
 }
 
 template <int WT, int G>
@@ -1543,16 +1125,9 @@ int32_t run_attn(const eb_attn_args* a, float* part_acc, float* part_ml, int32_t
   cudaStream_t st = eb::as_stream(stream);
   const int mt = (a->max_q_len * group + 15) / 16;
   int32_t rc;
-  if (mt >= 2 && attn_v64_enabled()) {
-    const char* lo = getenv("EB_V64_LO");
-    if (lo && lo[0] == '0')
-      rc = group == 8 ? launch_attn_v64<8, false>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st)
-                      : launch_attn_v64<4, false>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st);
-    else
-      rc = group == 8 ? launch_attn_v64<8, true>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st)
-                      : launch_attn_v64<4, true>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st);
-  } else if (mt >= 2 && attn_tc_enabled()) {
-    rc = dispatch_attn_tc(enc, a->d_cache, rows, p, a->n_items, a->n_kv, group, st);
+  if (mt >= 2 && attn_verify_on_tcgen05(a->window)) {
+    rc = group == 8 ? launch_attn_v64<8>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st)
+                    : launch_attn_v64<4>(enc, a->d_cache, rows, p, a->n_items, a->n_kv, st);
   } else if (group == 8) {
     if (mt == 1)
       rc = dispatch_hkv<1, 8>(a->n_kv, tm, p, a->n_items, st);

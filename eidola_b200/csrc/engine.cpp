@@ -1238,7 +1238,9 @@ int32_t step_launch_body(eb_engine* e, const int32_t* h_slots, const int32_t* h_
     off += 4 * (size_t)e->cap_items;
     part_off[k] = off;
     int32_t* sp = take((size_t)n_seqs + 1);
-    EB_TRY(eb_attn_plan(s_ctx, h_q_lens, n_seqs, c.page_size, k ? c.window : 0, e->sm_count, 0, ppi, it, e->cap_items,
+    // the chunk size follows the kernel the attention entry point picks for this step's shapes
+    const int32_t plan_sms = eb_attn_plan_sm_count(e->sm_count, max_q, e->hq_l, e->hkv_l, k ? c.window : 0);
+    EB_TRY(eb_attn_plan(s_ctx, h_q_lens, n_seqs, c.page_size, k ? c.window : 0, plan_sms, 0, ppi, it, e->cap_items,
                         &plans[k].n_items, sp, &plans[k].n_parts));
   }
   EB_REQUIRE(off <= e->stage_words, EB_ERR_NOMEM, "eb_engine_step: staging block overflow (%zu > %zu words)", off, e->stage_words);

@@ -252,6 +252,15 @@ int32_t eb_sched_pack(const eb_sched* s, const int32_t* slots, const int32_t* q_
   return EB_OK;
 }
 
+int32_t eb_attn_plan_sm_count(int32_t sm_count, int32_t max_q_len, int32_t n_q, int32_t n_kv, int32_t window) {
+  if (sm_count < 1 || max_q_len < 1 || n_q < 1 || n_kv < 1) return sm_count < 1 ? 1 : sm_count;
+  const int32_t rows = max_q_len * (n_q / n_kv);
+  // decode shapes, and verify shapes on short windows: one CTA per item works on all KV heads of the rank
+  if (rows <= 16 || (window > 0 && window < 2048)) return sm_count;
+  // verify shapes on long items: one CTA per (item, KV head), two per SM
+  return std::max(1, 2 * sm_count / n_kv);
+}
+
 int32_t eb_attn_plan(const int32_t* ctx_lens, const int32_t* q_lens, int32_t n_seqs, int32_t page_size,
                      int32_t window, int32_t sm_count, int32_t chunk_pages, int32_t parts_per_item,
                      eb_attn_item* items, int32_t cap_items, int32_t* n_items, int32_t* seq_part, int32_t* n_parts) {

@@ -5,7 +5,7 @@ import ctypes as C
 
 import numpy as np
 
-from .capi import (AttnArgs, AttnItem, Config, GemmArgs, DeviceBuffer, call, c_f32, c_i32, c_i64, c_sz, c_u64, c_vp, ptr)
+from .capi import (AttnArgs, AttnItem, Config, GemmArgs, DeviceBuffer, call, c_f32, c_i32, c_i64, c_sz, c_u64, c_vp, lib, ptr)
 
 I32 = np.int32
 
@@ -78,6 +78,12 @@ class Scheduler:
         assert nt.value == cap
         return {"slots": slots, "q_lens": q_lens, "q_off": q_off, "ctx_lens": ctx, "tok_seq": tok_seq,
                 "tok_slot": tok_slot, "positions": pos, "n_tokens": cap}
+
+
+def attn_plan_sm_count(sm_count: int, max_q_len: int, n_q: int, n_kv: int, window: int) -> int:
+    """The sm_count to plan with so that the automatic chunk size suits the kernel the launch will run."""
+    lib().eb_attn_plan_sm_count.restype = C.c_int32
+    return int(lib().eb_attn_plan_sm_count(c_i32(sm_count), c_i32(max_q_len), c_i32(n_q), c_i32(n_kv), c_i32(window)))
 
 
 def attn_plan(ctx_lens, q_lens, page_size: int, window: int, sm_count: int, chunk_pages: int = 0,

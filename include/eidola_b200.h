@@ -185,6 +185,16 @@ typedef struct eb_attn_item {
 } eb_attn_item;
 
 /*
+ * The value to pass as `sm_count` to eb_attn_plan for a launch of these shapes, so that its automatic chunk size suits
+ * the kernel eb_attn_paged_sink will run: decode shapes (at most 16 query rows per KV head) and verify shapes on windows
+ * below 2048 tokens run one CTA per work item over all KV heads of the rank (-> sm_count); verify shapes on longer items
+ * run one CTA per (work item, KV head), two per SM (-> 2 * sm_count / n_kv, at least 1).  A plan made with any other
+ * value is still correct, only cut finer or coarser than the kernel likes.  No reference counterpart (the reference
+ * delegates inference, crates/eidola-app-core/src/local_models.rs:1612-1626).
+ */
+int32_t eb_attn_plan_sm_count(int32_t sm_count, int32_t max_q_len, int32_t n_q, int32_t n_kv, int32_t window);
+
+/*
  * Split-K plan for one attention launch.  Long contexts are cut into runs of at most `chunk_pages` pages
  * (0 = choose so that about 4 items per SM exist, at least 8 pages each; a batch of at least sm_count sequences
  * whose longest visible range is within two such runs is left unsplit); items are ordered longest first.

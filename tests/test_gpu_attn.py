@@ -81,21 +81,42 @@ def test_attention_small_matches_oracle(gpu, n_kv, window, q_mode):
     assert plan["n_items"] > len(ctx) or window  # chunk 3 really split something
 
 
-@pytest.mark.parametrize("kernel", ["1", "2"])
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
 @pytest.mark.parametrize("n_kv", [8, 4, 1])
-@pytest.mark.parametrize("window", [0, 128])
-def test_attention_verify_on_tcgen05_matches_oracle(gpu, n_kv, window, kernel, monkeypatch):
-    """The tcgen05 kernels for verify shapes (S and O in tensor memory, P fed from tensor memory; "1": 128-row tiles, a
-    thread per row; "2": 64-row tiles, 128-key blocks): same oracle, same tolerance, ragged query lengths, split contexts,
-    window, fewer KV heads per rank."""
-    monkeypatch.setenv("EIDOLA_B200_ATTN_TC", kernel)
+@pytest.mark.parametrize("window", [0, 128, 2048])
+def test_attention_verify_kernels_match_oracle(gpu, n_kv, window, kernel, monkeypatch):
+    """Verify shapes run on the tcgen05 kernel when the items are long (full layers, windows of 2048 tokens and more)
+    and on the mma.sync kernel otherwise; EIDOLA_B200_ATTN_VERIFY=mma keeps everything on the latter.  Both against the
+    same oracle at the same tolerance: ragged query lengths, split contexts, windows, fewer KV heads per rank, and plans
+    cut the way the entry point's kernel choice asks for."""
+    import eidola_b200 as eb
+    if kernel == "mma":
+        monkeypatch.setenv("EIDOLA_B200_ATTN_VERIFY", "mma")
+    else:
+        monkeypatch.delenv("EIDOLA_B200_ATTN_VERIFY", raising=False)
     ctx = np.array(CTX_SMALL, np.int32)
     for ql in (np.minimum(ctx, 5), np.minimum(ctx, np.array([1, 2, 3, 4, 5, 1, 6, 2, 1, 3], np.int32))):
         case = AttnCase(ctx, ql, n_kv, seed=2, sm_count=gpu["sm_count"])
         want = case.oracle(window)
         for chunk in (0, 3):
             got, _ = case.run(window, chunk)
-            assert_close_bf16(got, want, atol=ATTN_ATOL, what=f"tcgen05[{kernel}] n_kv={n_kv} window={window} chunk={chunk}")
+            assert_close_bf16(got, want, atol=ATTN_ATOL, what=f"{kernel} n_kv={n_kv} window={window} chunk={chunk}")
+        # the plan the engine would make for this launch
+        case.sm_count = eb.attn_plan_sm_count(gpu["sm_count"], int(ql.max()), 8 * n_kv, n_kv, window)
+        got, _ = case.run(window, 0)
+        assert_close_bf16(got, want, atol=ATTN_ATOL, what=f"{kernel} n_kv={n_kv} window={window} planned for its kernel")
+
+
+def test_attn_plan_sm_count_follows_the_kernel_choice(gpu):
+    import eidola_b200 as eb
+    sm = gpu["sm_count"]
+    assert eb.attn_plan_sm_count(sm, 1, 64, 8, 0) == sm          # decode: one CTA per item
+    assert eb.attn_plan_sm_count(sm, 2, 64, 8, 0) == sm          # 16 rows still fit the decode tile
+    assert eb.attn_plan_sm_count(sm, 5, 64, 8, 0) == 2 * sm // 8  # verify, full layer: one CTA per (item, KV head), two per SM
+    assert eb.attn_plan_sm_count(sm, 5, 16, 2, 0) == sm
+    assert eb.attn_plan_sm_count(sm, 5, 8, 1, 0) == 2 * sm
+    assert eb.attn_plan_sm_count(sm, 5, 64, 8, 128) == sm        # short window: the mma.sync kernel
+    assert eb.attn_plan_sm_count(sm, 5, 64, 8, 4096) == 2 * sm // 8
 
 
 @pytest.mark.parametrize("n_kv", [2, 8])
