@@ -507,13 +507,24 @@ int32_t eb_engine_create(const eb_config* cfg, eb_engine** out);
 /* Tensor-parallel heads + expert-parallel experts over tp_size ranks (one process per GPU): rank r holds query heads
  * [r*n_q/tp, ...), KV heads [r*n_kv/tp, ...) with their slice of every KV page (page ids are the same on all ranks),
  * the matching rows of W_qkv and columns of W_o, experts [r*E/tp, ...) and a band of whole 128-row blocks of the
- * LM head.  Every rank is given the same steps and returns the same tokens.  Per layer the partial [tokens, hidden]
- * products of the O projection and of the rank's experts are summed over token slices (reduce-scatter: tp_size equal
- * chunks of whole 128-row scale blocks); the owner of a slice adds the residual, normalises, routes and quantises
- * its rows, and all-gathers return the normalised rows, the routing and the e4m3 codes with their block scales.
- * The LM head is vocabulary-parallel: each rank leaves one argmax candidate per token, the candidates are gathered
- * and merged.  All cross-rank traffic runs on `comm`; no kernel of one rank waits on another rank's kernel outside
- * it.  The model is the same tensor for every tp_size (weights are slices of the single-GPU tensors). */
+ * LM head.  Every rank is given the same steps and returns the same tokens; the model is the same tensor for every
+ * tp_size (weights are slices of the single-GPU tensors).  The LM head is vocabulary-parallel: each rank leaves one
+ * argmax candidate per token, the candidates are gathered and merged.
+ *
+ * Per layer the partial [tokens, hidden] products of the O projection and of the rank's experts have to be summed over
+ * the ranks.  Three forms, chosen per step from its token count (every form gives the same bits):
+ *   up to 512 tokens   every rank receives every rank's whole partial and adds them itself in rank order, so residual,
+ *                      norm and routing run on all rows everywhere and nothing is gathered (two exchanges per layer);
+ *   larger steps       the partials are summed over token slices (tp_size equal chunks of whole 128-row scale blocks);
+ *                      the owner of a slice adds the residual, normalises, routes and quantises its rows, and gathers
+ *                      return the normalised rows, the routing and the e4m3 codes with their block scales;
+ *   from 1024 tokens   on four ranks and more the expert step instead sends each token's normalised row to the ranks of
+ *                      its experts and the expert outputs back to the token's owner (dispatch / return of rows).
+ * The exchanges are this library's own kernels over a symmetric peer-memory arena (eb_symm_*: plain stores into the
+ * peers' memory, a flag per sender, a consumer kernel that waits for the flags with a bounded number of polls and
+ * raises EB_DEV_WAIT_TIMEOUT instead of hanging); `comm` carries the set-up (exchange of the memory handles) and, with
+ * EIDOLA_B200_TP_NCCL=1, the exchanges themselves as NCCL reduce-scatter / all-gather calls.  EIDOLA_B200_TP_WHOLE=0 and
+ * EIDOLA_B200_EP_A2A=0|1 force one of the forms (A/B runs and tests). */
 int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_size, eb_comm* comm, eb_engine** out);
 int32_t eb_engine_destroy(eb_engine* e);
 /* Device bytes held by weights, KV pages and workspaces. */
