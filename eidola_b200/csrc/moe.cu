@@ -63,9 +63,11 @@ __device__ __forceinline__ void router_select(float (&lg)[EPL], int lane, int E,
   }
 }
 
-// Few tokens (decode batches, token slices of a tensor-parallel rank): one CTA per TPC tokens (1 or 2), the experts
-// dealt to its eight warps, router rows read straight from L2 (every lane's loads are issued before any is used, so
-// a pass over two experts costs about one memory round trip; with TPC = 2 a row fetched once serves two tokens).
+// Up to a few thousand tokens: one CTA per TPC tokens (1, 2, 4 or 8), the experts dealt to its eight warps, router rows
+// read straight from L2 (every lane's loads are issued before any is used, so a pass over two experts costs about one
+// memory round trip, and a row fetched once serves all the CTA's tokens: the router matrix crosses the L2 -> SM path
+// T / TPC times, which is what bounds the kernel once T is in the hundreds).  With more than one token per CTA the
+// token rows live in shared memory instead of registers.
 // The dot products use exactly the order of router_topk_kernel (lane l owns 8-element groups l, l + 32, ...,
 // ascending k, xor butterfly), so all router kernels produce the same bits.
 template <int EPL, int GPL, int TPC>
@@ -75,18 +77,30 @@ router_direct_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H,
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
   __shared__ float s_lg[TPC][kMaxExperts];
+  extern __shared__ __align__(16) uint16_t xs[];  // TPC > 1: the CTA's token rows, [TPC][H]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = blockIdx.x * TPC;
   const int H8 = H >> 3;
-  uint4 xp[TPC][GPL];  // the tokens' rows as packed bf16 pairs
-#pragma unroll
-  for (int k = 0; k < TPC; ++k)
-#pragma unroll
-    for (int j = 0; j < GPL; ++j) {
-      const int g = lane + 32 * j;
-      xp[k][j] = make_uint4(0, 0, 0, 0);
-      if (g < H8 && t0 + k < T) xp[k][j] = *reinterpret_cast<const uint4*>(x + (int64_t)(t0 + k) * H + 8 * g);
+  constexpr bool XS = TPC > 1;  // several tokens per CTA keep their rows in shared memory, not in registers
+  uint4 xp[XS ? 1 : TPC][GPL];  // the tokens' rows as packed bf16 pairs
+  if (XS) {
+    for (int i = threadIdx.x; i < TPC * H8; i += 256) {
+      const int k = i / H8, g = i - k * H8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (t0 + k < T) v = *reinterpret_cast<const uint4*>(x + (int64_t)(t0 + k) * H + 8 * g);
+      *reinterpret_cast<uint4*>(xs + (size_t)k * H + 8 * g) = v;
     }
+    __syncthreads();
+  } else {
+#pragma unroll
+    for (int k = 0; k < (XS ? 1 : TPC); ++k)
+#pragma unroll
+      for (int j = 0; j < GPL; ++j) {
+        const int g = lane + 32 * j;
+        xp[k][j] = make_uint4(0, 0, 0, 0);
+        if (g < H8 && t0 + k < T) xp[k][j] = *reinterpret_cast<const uint4*>(x + (int64_t)(t0 + k) * H + 8 * g);
+      }
+  }
   for (int e = warp; e < E; e += 16) {  // two experts per pass: e and e + 8
     const bool two = e + 8 < E;
     const uint4* w0 = reinterpret_cast<const uint4*>(wr + (int64_t)e * H);
@@ -111,7 +125,8 @@ router_direct_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H,
         const uint32_t p0[4] = {u0[j].x, u0[j].y, u0[j].z, u0[j].w}, p1[4] = {u1[j].x, u1[j].y, u1[j].z, u1[j].w};
 #pragma unroll
         for (int k = 0; k < TPC; ++k) {
-          const uint32_t xw[4] = {xp[k][j].x, xp[k][j].y, xp[k][j].z, xp[k][j].w};
+          const uint4 xv = XS ? *reinterpret_cast<const uint4*>(xs + (size_t)k * H + 8 * g) : xp[XS ? 0 : k][j];
+          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const float xl = __uint_as_float(xw[q] << 16), xh = __uint_as_float(xw[q] & 0xFFFF0000u);
@@ -385,15 +400,27 @@ __global__ void moe_combine_kernel(const uint16_t* y, const int32_t* perm_row, c
 template <int EPL, int HPL>
 int32_t launch_router2(unsigned grid, size_t smem, cudaStream_t st, const uint16_t* x, const uint16_t* wr, int T, int E, int H,
                     int top_k, int32_t* idx, float* wts, float* logits) {
-  // Up to 640 tokens the one-token-per-CTA kernel wins: it costs ~1.1 ns per (token, expert) (router rows re-read
-  // through L2), the staged pipeline at least ~5 us per 8 experts however few tokens there are (measured at 32 and 128
-  // experts: 46 against 85 us at 320 x 128, 11 against 21 us at 256 x 32; the staged kernel leads from ~1000 tokens).
-  if (T <= 640) {
-    if (T <= 296)  // one token per CTA while that does not exceed two CTAs per SM
+  // The one-CTA-per-few-tokens kernel up to 4096 tokens; tokens per CTA: the fewest of 1, 2, 4, 8 that give at most one
+  // CTA per SM (the kernel's registers allow one CTA per SM), 8 beyond that.  (The staged pipeline below costs at least
+  // ~5 us per 8 experts however few tokens there are: 85 us at 320 tokens x 128 experts, 21 us at 256 x 32.)
+  if (T <= 4096) {
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const size_t xs_bytes = (size_t)H * sizeof(uint16_t);
+    if (T <= sms) {
       EB_CUDA(eb::launch(router_direct_kernel<EPL, HPL, 1>, dim3((unsigned)T), dim3(256), 0, st, x, wr, T, E, H, top_k, idx, wts, logits));
-    else
-      EB_CUDA(eb::launch(router_direct_kernel<EPL, HPL, 2>, dim3((unsigned)((T + 1) / 2)), dim3(256), 0, st, x, wr, T, E, H, top_k, idx,
-                         wts, logits));
+    } else if (T <= 2 * sms) {
+      EB_CUDA(eb::launch(router_direct_kernel<EPL, HPL, 2>, dim3((unsigned)((T + 1) / 2)), dim3(256), 2 * xs_bytes, st, x, wr, T, E, H,
+                         top_k, idx, wts, logits));
+    } else if (T <= 4 * sms) {
+      auto k4 = router_direct_kernel<EPL, HPL, 4>;
+      EB_CUDA(cudaFuncSetAttribute(k4, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(4 * xs_bytes)));
+      EB_CUDA(eb::launch(k4, dim3((unsigned)((T + 3) / 4)), dim3(256), 4 * xs_bytes, st, x, wr, T, E, H, top_k, idx, wts, logits));
+    } else {
+      auto k8 = router_direct_kernel<EPL, HPL, 8>;
+      EB_CUDA(cudaFuncSetAttribute(k8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(8 * xs_bytes)));
+      EB_CUDA(eb::launch(k8, dim3((unsigned)((T + 7) / 8)), dim3(256), 8 * xs_bytes, st, x, wr, T, E, H, top_k, idx, wts, logits));
+    }
     return EB_OK;
   }
   auto kfn = router_topk_kernel<EPL, HPL>;
