@@ -638,7 +638,7 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // 16 keys per instruction
           tc_mma_ts(tO, tP + kk * 8, tc_desc_sw128(vb + kk * 2048), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(bar_pv + 8 * b);
+        if (i + 2 >= n_sub) tc_commit(bar_pv + 8 * b);  // otherwise S of sub-block i + 2, issued below, signals this product too
         if (b == 1 || i + 1 == n_sub) tc_commit(bar_empty + 8 * sidx);  // the stage's last sub-block has read its V rows
         if (i + 1 == n_sub) tc_commit(bar_o);
         if (i + 2 < n_sub) ok = issue_s(i + 2);
@@ -722,7 +722,11 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
         if (i > 0) {
           // O holds earlier sub-blocks; the product of the last one may still run: wait for it, then each warp rescales
           // its half of the columns
-          if (!mbar_wait(bar_pv + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, &abort_flag, p.status, p.wait_tries)) {
+          // (S of sub-block i + 1 was issued after that product, so its arrival covers it; the last two products of an
+          // item, which no S follows, arrive on a barrier of their own)
+          const bool done = (i + 1 < n_sub) ? mbar_wait(bar_s + 8 * ((i + 1) & 1), ((i + 1) >> 1) & 1, &abort_flag, p.status, p.wait_tries)
+                                            : mbar_wait(bar_pv + 8 * ((i - 1) & 1), 0, &abort_flag, p.status, p.wait_tries);
+          if (!done) {
             ok = false;
             break;
           }
