@@ -436,14 +436,14 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     return eb_symm_wait(e->symm, seq, 1, st);
   };
   // the WHOLE [T][H] partial to every rank (this rank's copy included), side by side as planes of T rows
-  auto share_planes = [&](const void* src, int esz) -> int32_t {
+  // (the consumer, eb_planes_residual_rmsnorm_after, waits for the peers' flags itself: no wait launch)
+  auto share_planes = [&](const void* src, int esz, int32_t* seq, int32_t* patience) -> int32_t {
     const int64_t so = aoff(src), zero = 0, dof = aoff(e->planes), step = (int64_t)T * H * esz;
-    int32_t seq = 0;
-    EB_TRY(eb_symm_push(e->symm, 1, &so, &zero, &dof, &step, &step, nullptr, 1, &seq, st));
+    EB_TRY(eb_symm_push(e->symm, 1, &so, &zero, &dof, &step, &step, nullptr, 1, seq, st));
     n += 1;
-    const int patience = first_exchange ? 32 : 1;
+    *patience = first_exchange ? 32 : 1;  // the first exchange of a step also absorbs the skew between the ranks' host loops
     first_exchange = false;
-    return eb_symm_wait(e->symm, seq, patience, st);
+    return EB_OK;
   };
   // the ranks' slices of a [T][H] partial (esz bytes per element, in the arena) to their owners, side by side as planes
   auto scatter_planes = [&](const void* src, int esz) -> int32_t {
@@ -606,11 +606,19 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
         // every rank gets every rank's partial and adds them itself, in rank order: residual, norm and routing then run
         // on all rows everywhere with identical bits, and nothing has to be gathered
         const int esz = splits == 1 ? 2 : 4;
-        if (splits > 1) EB_TRY(eb_sum_planes_f32((const float*)e->gemm_ws, splits, e->o, (int64_t)T * H, e->ar_buf, st));
+        int32_t seq = 0, patience = 1;
         mark(5);
-        EB_TRY(share_planes(splits == 1 ? (const void*)e->o : (const void*)e->ar_buf, esz));
+        if (splits > 1) {  // the sum of the split-K planes goes straight into every rank's plane
+          EB_TRY(eb_sum_planes_f32_to_peers(e->symm, aoff(e->planes), (int64_t)T * H * 4, (const float*)e->gemm_ws, splits, (int64_t)T * H,
+                                            &seq, st));
+          patience = first_exchange ? 32 : 1;
+          first_exchange = false;
+        } else {
+          EB_TRY(share_planes(e->o, esz, &seq, &patience));
+        }
+        EB_TRY(eb_planes_residual_rmsnorm_after(e->symm, seq, patience, e->planes, esz == 2, e->tp_size, (int64_t)T * H, e->x, L.g_mlp, T,
+                                                H, c.rms_eps, e->h, st));
         mark(-1);
-        EB_TRY(eb_planes_residual_rmsnorm(e->planes, esz == 2, e->tp_size, (int64_t)T * H, e->x, L.g_mlp, T, H, c.rms_eps, e->h, st));
         n += 2;
       } else if (splits == 1) {
         mark(5);
@@ -719,15 +727,20 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       } else {
         // C2 without an exchange of rows: every rank holds every token, mixes its own experts' outputs into a partial
         // [T, H] and the partials are summed over token slices
-        EB_TRY(eb_moe_combine_bf16(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->o, st));
         if (whole) {
+          // this rank's experts' mix of every token goes straight into every rank's plane
+          int32_t seq = 0, patience = first_exchange ? 32 : 1;
+          first_exchange = false;
           mark(5);
-          EB_TRY(share_planes(e->o, 2));
+          EB_TRY(eb_moe_combine_bf16_to_peers(e->symm, aoff(e->planes), (int64_t)T * H * 2, e->y, e->perm_row, e->r_wts, T, c.top_k, H, &seq,
+                                              st));
+          EB_TRY(eb_planes_residual_rmsnorm_after(e->symm, seq, patience, e->planes, 1, e->tp_size, (int64_t)T * H, e->x, g_next, T, H,
+                                                  c.rms_eps, e->h, st));
           mark(-1);
-          EB_TRY(eb_planes_residual_rmsnorm(e->planes, 1, e->tp_size, (int64_t)T * H, e->x, g_next, T, H, c.rms_eps, e->h, st));
           n += 2;
           goto layer_done;  // every rank holds every normalised row: the next consumer quantises them itself
         }
+        EB_TRY(eb_moe_combine_bf16(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->o, st));
         mark(5);
         if (symm)
           EB_TRY(scatter_planes(e->o, 2));

@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <math.h>
 
+#include <algorithm>
+
 #include "common.h"
 
 namespace {
@@ -436,9 +438,10 @@ template <int MODE>
 __global__ void __launch_bounds__(256)
 row_residual_rmsnorm_kernel(const float* part, int splits, const uint16_t* o_bf16, const uint16_t* y, const int32_t* perm_row,
                             const float* wts, int top_k, int64_t n_rows, uint16_t* x, const float* g, int T, int H, float eps,
-                            uint16_t* hout, int64_t plane_stride, int planes_bf16) {
+                            uint16_t* hout, int64_t plane_stride, int planes_bf16, const eb::PeerWait pw) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
+  eb::peer_wait_cta(pw);  // planes pushed by the peers: wait for their flags here instead of behind a wait launch
   __shared__ float red[8];
   const int t = blockIdx.x;
   const int H8 = H >> 3;
@@ -571,13 +574,25 @@ int32_t eb_oproj_residual_rmsnorm(const float* d_part, int32_t splits, const voi
   if (splits > 1 && !d_part) return eb::fail(EB_ERR_ARG, "eb_oproj_residual_rmsnorm: partials missing");
   EB_CUDA(eb::launch(row_residual_rmsnorm_kernel<0>, dim3(T), dim3(256), 0, eb::as_stream(stream), d_part, splits, (const uint16_t*)d_o_bf16, nullptr,
                                                                        nullptr, nullptr, 0, 0, (uint16_t*)d_x, d_g, T, H, eps,
-                                                                       (uint16_t*)d_h, (int64_t)0, 0));
+                                                                       (uint16_t*)d_h, (int64_t)0, 0, eb::PeerWait{}));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
 
 int32_t eb_planes_residual_rmsnorm(const void* d_planes, int32_t planes_are_bf16, int32_t n_planes, int64_t plane_stride, void* d_x,
                                    const float* d_g, int32_t T, int32_t H, float eps, void* d_h, void* stream) {
+  return eb_planes_residual_rmsnorm_after(nullptr, 0, 1, d_planes, planes_are_bf16, n_planes, plane_stride, d_x, d_g, T, H, eps, d_h,
+                                          stream);
+}
+
+int32_t eb_planes_residual_rmsnorm_after(eb_symm* s, int32_t seq, int32_t patience, const void* d_planes, int32_t planes_are_bf16,
+                                         int32_t n_planes, int64_t plane_stride, void* d_x, const float* d_g, int32_t T, int32_t H,
+                                         float eps, void* d_h, void* stream) {
+  eb::PeerWait pw = {};
+  if (s) {
+    const int32_t rc = eb::symm_peer_wait(s, seq, patience, &pw);
+    if (rc != EB_OK) return rc;
+  }
   EB_REQUIRE(d_planes && d_x && d_g && d_h, EB_ERR_ARG, "eb_planes_residual_rmsnorm: null pointer");
   EB_REQUIRE(n_planes >= 1 && n_planes <= 64 && plane_stride >= (int64_t)T * H && plane_stride % 8 == 0, EB_ERR_ARG,
              "eb_planes_residual_rmsnorm: %d planes, stride %lld", n_planes, (long long)plane_stride);
@@ -587,7 +602,7 @@ int32_t eb_planes_residual_rmsnorm(const void* d_planes, int32_t planes_are_bf16
                      planes_are_bf16 ? (const float*)nullptr : (const float*)d_planes, n_planes,
                      planes_are_bf16 ? (const uint16_t*)d_planes : (const uint16_t*)nullptr, (const uint16_t*)nullptr, (const int32_t*)nullptr,
                      (const float*)nullptr, 0, (int64_t)0, (uint16_t*)d_x, d_g, T, H, eps, (uint16_t*)d_h, plane_stride,
-                     planes_are_bf16 ? 1 : 0));
+                     planes_are_bf16 ? 1 : 0, pw));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -604,7 +619,7 @@ int32_t eb_moe_combine_rmsnorm_ex(const void* d_y, const int32_t* d_perm_row, co
   if (T == 0) return EB_OK;
   EB_CUDA(eb::launch(row_residual_rmsnorm_kernel<1>, dim3(T), dim3(256), 0, eb::as_stream(stream), nullptr, 1, nullptr, (const uint16_t*)d_y, d_perm_row,
                                                                        d_wts, top_k, n_rows, (uint16_t*)d_x, d_g, T,
-                                                                       H, eps, (uint16_t*)d_h, (int64_t)0, 0));
+                                                                       H, eps, (uint16_t*)d_h, (int64_t)0, 0, eb::PeerWait{}));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -616,20 +631,28 @@ int32_t eb_moe_combine_rmsnorm_ex(const void* d_y, const int32_t* d_perm_row, co
 
 namespace {
 
-__global__ void sum_planes_kernel(const float4* part, int splits, int64_t n4, float4* out) {
+// out == nullptr: the sum goes straight into every rank's plane of a whole-batch exchange (pp), and the launch raises the
+// collective's flags itself.
+__global__ void sum_planes_kernel(const float4* part, int splits, int64_t n4, float4* out, const eb::PeerPlanes pp) {
   eb::pdl_wait();
   eb::pdl_trigger();
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n4) return;
-  float4 a = part[i];
-  for (int s = 1; s < splits; ++s) {
-    const float4 b = part[(int64_t)s * n4 + i];
-    a.x += b.x;
-    a.y += b.y;
-    a.z += b.z;
-    a.w += b.w;
+  if (i < n4) {
+    float4 a = part[i];
+    for (int s = 1; s < splits; ++s) {
+      const float4 b = part[(int64_t)s * n4 + i];
+      a.x += b.x;
+      a.y += b.y;
+      a.z += b.z;
+      a.w += b.w;
+    }
+    if (out) {
+      out[i] = a;
+    } else {
+      for (int p = 0; p < pp.size; ++p) reinterpret_cast<float4*>(pp.dst[p])[i] = a;
+    }
   }
-  out[i] = a;
+  if (!out) eb::peer_arrive_cta(pp);
 }
 
 __global__ void bf16_to_f32_kernel(const uint16_t* in, int64_t n, float* out) {
@@ -676,10 +699,24 @@ int32_t eb_sum_planes_f32(const float* d_part, int32_t splits, const void* d_bf1
   if (n == 0) return EB_OK;
   if (d_part)
     EB_CUDA(eb::launch(sum_planes_kernel, dim3((unsigned)eb::cdiv(n / 4, 256)), dim3(256), 0, eb::as_stream(stream),
-                       (const float4*)d_part, splits, n / 4, (float4*)d_out));
+                       (const float4*)d_part, splits, n / 4, (float4*)d_out, eb::PeerPlanes{}));
   else
     EB_CUDA(eb::launch(bf16_to_f32_kernel, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream),
                        (const uint16_t*)d_bf16, n, d_out));
+  return EB_OK;
+}
+
+
+int32_t eb_sum_planes_f32_to_peers(eb_symm* s, int64_t dst_off, int64_t plane_step, const float* d_part, int32_t splits, int64_t n,
+                                   int32_t* seq, void* stream) {
+  EB_REQUIRE(s && d_part && seq && splits >= 1 && n >= 0 && n % 4 == 0 && ((uintptr_t)d_part % 16 == 0), EB_ERR_ARG,
+             "eb_sum_planes_f32_to_peers: bad argument");
+  eb::PeerPlanes pp;
+  const int32_t rc = eb::symm_peer_planes(s, dst_off, plane_step, n * (int64_t)sizeof(float), &pp, seq);
+  if (rc != EB_OK) return rc;
+  const unsigned grid = (unsigned)std::max<int64_t>(1, eb::cdiv(n / 4, 256));
+  EB_CUDA(eb::launch(sum_planes_kernel, dim3(grid), dim3(256), 0, eb::as_stream(stream), (const float4*)d_part, splits, n / 4,
+                     (float4*)nullptr, pp));
   return EB_OK;
 }
 

@@ -552,38 +552,47 @@ __global__ void localize_experts_kernel(const int32_t* idx, int n, int e0, int e
 }
 
 // out[t] = sum over this rank's slots j of w[t][j] * y[perm_row[t][j]]  (fp32, slots in ascending j)
+// out == nullptr (bf16 only): the mix goes straight into every rank's plane of a whole-batch exchange (pp), and the launch
+// raises the collective's flags itself.
 template <int BF16_OUT>
 __global__ void moe_combine_f32_kernel(const uint16_t* y, const int32_t* perm_row, const float* wts, int T, int top_k, int H,
-                                       float* out, int64_t n_rows) {
+                                       float* out, int64_t n_rows, const eb::PeerPlanes pp) {
   eb::pdl_wait();
   eb::pdl_trigger();
   const int h8 = H >> 3;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)T * h8) return;
-  const int t = (int)(idx / h8), c = (int)(idx % h8) * 8;
-  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (int j = 0; j < top_k; ++j) {
-    const int r = perm_row[(int64_t)t * top_k + j];
-    if (r < 0 || r >= n_rows) continue;
-    const float w = wts[(int64_t)t * top_k + j];
-    const uint4 v = *reinterpret_cast<const uint4*>(y + (int64_t)r * H + c);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+  if (idx < (int64_t)T * h8) {
+    const int t = (int)(idx / h8), c = (int)(idx % h8) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int j = 0; j < top_k; ++j) {
+      const int r = perm_row[(int64_t)t * top_k + j];
+      if (r < 0 || r >= n_rows) continue;
+      const float w = wts[(int64_t)t * top_k + j];
+      const uint4 v = *reinterpret_cast<const uint4*>(y + (int64_t)r * H + c);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      acc[2 * k] = __fmaf_rn(w, __uint_as_float(u[k] << 16), acc[2 * k]);
-      acc[2 * k + 1] = __fmaf_rn(w, __uint_as_float(u[k] & 0xFFFF0000u), acc[2 * k + 1]);
+      for (int k = 0; k < 4; ++k) {
+        acc[2 * k] = __fmaf_rn(w, __uint_as_float(u[k] << 16), acc[2 * k]);
+        acc[2 * k + 1] = __fmaf_rn(w, __uint_as_float(u[k] & 0xFFFF0000u), acc[2 * k + 1]);
+      }
+    }
+    if (BF16_OUT) {
+      uint32_t h[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(h[k]) : "f"(acc[2 * k + 1]), "f"(acc[2 * k]));
+      const uint4 hv = make_uint4(h[0], h[1], h[2], h[3]);
+      if (out) {
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (int64_t)t * H + c) = hv;
+      } else {
+        for (int p = 0; p < pp.size; ++p) *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(pp.dst[p]) + (int64_t)t * H + c) = hv;
+      }
+    } else {
+      float4* o = reinterpret_cast<float4*>(out + (int64_t)t * H + c);
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
   }
-  if (BF16_OUT) {
-    uint32_t h[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(h[k]) : "f"(acc[2 * k + 1]), "f"(acc[2 * k]));
-    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + (int64_t)t * H + c) = make_uint4(h[0], h[1], h[2], h[3]);
-  } else {
-    float4* o = reinterpret_cast<float4*>(out + (int64_t)t * H + c);
-    o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-  }
+  if (BF16_OUT && !out) eb::peer_arrive_cta(pp);  // reached by every thread of the CTA
 }
 
 }  // namespace
@@ -611,7 +620,7 @@ int32_t eb_moe_combine_f32(const void* d_y, const int32_t* d_perm_row, const flo
   if (T == 0) return EB_OK;
   const int64_t n = (int64_t)T * (H / 8);
   EB_CUDA(eb::launch(moe_combine_f32_kernel<0>, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream),
-                     (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, d_out, (int64_t)T * top_k));
+                     (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, d_out, (int64_t)T * top_k, eb::PeerPlanes{}));
   return EB_OK;
 }
 
@@ -623,7 +632,20 @@ int32_t eb_moe_combine_bf16(const void* d_y, const int32_t* d_perm_row, const fl
   if (T == 0) return EB_OK;
   const int64_t n = (int64_t)T * (H / 8);
   EB_CUDA(eb::launch(moe_combine_f32_kernel<1>, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream),
-                     (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, (float*)d_out, (int64_t)T * top_k));
+                     (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, (float*)d_out, (int64_t)T * top_k, eb::PeerPlanes{}));
+  return EB_OK;
+}
+
+int32_t eb_moe_combine_bf16_to_peers(eb_symm* s, int64_t dst_off, int64_t plane_step, const void* d_y, const int32_t* d_perm_row,
+                                     const float* d_wts, int32_t T, int32_t top_k, int32_t H, int32_t* seq, void* stream) {
+  EB_REQUIRE(s && d_y && d_perm_row && d_wts && seq, EB_ERR_ARG, "eb_moe_combine_bf16_to_peers: null pointer");
+  EB_REQUIRE(T >= 1 && top_k >= 1 && H >= 8 && H % 8 == 0, EB_ERR_ARG, "eb_moe_combine_bf16_to_peers: T %d, H %d (a multiple of 8)", T, H);
+  eb::PeerPlanes pp;
+  const int32_t rc = eb::symm_peer_planes(s, dst_off, plane_step, (int64_t)T * H * 2, &pp, seq);
+  if (rc != EB_OK) return rc;
+  const int64_t n = (int64_t)T * (H / 8);
+  EB_CUDA(eb::launch(moe_combine_f32_kernel<1>, dim3((unsigned)eb::cdiv(n, 256)), dim3(256), 0, eb::as_stream(stream),
+                     (const uint16_t*)d_y, d_perm_row, d_wts, T, top_k, H, (float*)nullptr, (int64_t)T * top_k, pp));
   return EB_OK;
 }
 

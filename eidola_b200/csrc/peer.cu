@@ -30,8 +30,8 @@
 
 namespace {
 
-constexpr int kMaxRanks = 8;
-constexpr int kFlagSlots = 8;       // collectives in flight never span more than two sequence numbers
+constexpr int kMaxRanks = eb::kPeerMaxRanks;
+constexpr int kFlagSlots = eb::kPeerFlagSlots;  // collectives in flight never span more than two sequence numbers
 constexpr int kMaxSegs = 4;
 constexpr size_t kFlagBytes = 4096;  // flags + the push kernel's completion counter, at the end of the arena
 
@@ -198,6 +198,38 @@ struct eb_symm {
   int32_t waited = 0;
   int sms = 148;
 };
+
+namespace eb {
+int32_t symm_peer_wait(eb_symm* s, int32_t seq, int32_t patience, PeerWait* out) {
+  EB_REQUIRE(s && out && patience >= 1 && patience <= 64, EB_ERR_ARG, "peer wait: bad argument (patience 1..64)");
+  *out = PeerWait{nullptr, s->rank, s->size, seq, 0, nullptr};
+  if (s->size == 1) return EB_OK;
+  out->status = eb::status_word();
+  EB_REQUIRE(out->status, EB_ERR_NODEVICE, "peer wait: no device");
+  out->flags = reinterpret_cast<const int32_t*>(s->arena[s->rank] + s->bytes);
+  out->tries = (uint32_t)std::min<uint64_t>((uint64_t)eb::wait_tries() * (uint64_t)patience, 0x7fffffffull);
+  s->waited = seq;
+  return EB_OK;
+}
+int32_t symm_peer_planes(eb_symm* s, int64_t dst_off, int64_t plane_step, int64_t plane_bytes, PeerPlanes* out, int32_t* seq) {
+  EB_REQUIRE(s && out && seq, EB_ERR_ARG, "peer planes: null argument");
+  EB_REQUIRE(dst_off >= 0 && dst_off % 16 == 0 && plane_step >= plane_bytes && plane_step % 16 == 0 && plane_bytes >= 0 &&
+                 dst_off + (int64_t)(s->size - 1) * plane_step + plane_bytes <= (int64_t)s->bytes,
+             EB_ERR_ARG, "peer planes: %d planes of %lld bytes at %lld leave the arena of %zu bytes", s->size, (long long)plane_bytes,
+             (long long)dst_off, s->bytes);
+  *out = PeerPlanes{};
+  out->rank = s->rank;
+  out->size = s->size;
+  out->seq = ++s->seq;
+  *seq = out->seq;
+  for (int p = 0; p < s->size; ++p) {
+    out->dst[p] = s->arena[p] + dst_off + (int64_t)s->rank * plane_step;
+    out->flags[p] = reinterpret_cast<int32_t*>(s->arena[p] + s->bytes);
+  }
+  out->counter = reinterpret_cast<int32_t*>(s->arena[s->rank] + s->bytes) + kFlagSlots * kMaxRanks;
+  return EB_OK;
+}
+}  // namespace eb
 
 extern "C" {
 

@@ -502,6 +502,20 @@ int32_t eb_symm_return_rows(eb_symm* s, int64_t src_off, int64_t dst_off, int32_
  * (1..64) multiplies the wait limit: the first collective of a step also absorbs the skew between the ranks' host
  * loops, the later ones only the skew between their kernels. */
 int32_t eb_symm_wait(eb_symm* s, int32_t seq, int32_t patience, void* stream);
+/* Producers of a whole-batch exchange that store their result straight into every rank's arena (this rank's plane at
+ * dst_off + rank * plane_step, its own arena included) and raise the collective's flags themselves, so no eb_symm_push
+ * launch follows them: the sum of `splits` fp32 planes of n elements (the arithmetic of eb_sum_planes_f32), and the
+ * bf16 mix of this rank's experts' rows (the arithmetic of eb_moe_combine_bf16).  `seq` receives the collective's
+ * sequence number for eb_symm_wait / eb_planes_residual_rmsnorm_after. */
+int32_t eb_sum_planes_f32_to_peers(eb_symm* s, int64_t dst_off, int64_t plane_step, const float* d_part, int32_t splits, int64_t n,
+                                   int32_t* seq, void* stream);
+int32_t eb_moe_combine_bf16_to_peers(eb_symm* s, int64_t dst_off, int64_t plane_step, const void* d_y, const int32_t* d_perm_row,
+                                     const float* d_wts, int32_t T, int32_t top_k, int32_t H, int32_t* seq, void* stream);
+/* eb_planes_residual_rmsnorm on planes that the ranks of `s` pushed as collective `seq`: every CTA waits, bounded, for its
+ * peers' flags itself, so no eb_symm_wait launch is needed between the push and this call.  s == NULL: no wait. */
+int32_t eb_planes_residual_rmsnorm_after(eb_symm* s, int32_t seq, int32_t patience, const void* d_planes, int32_t planes_are_bf16,
+                                         int32_t n_planes, int64_t plane_stride, void* d_x, const float* d_g, int32_t T, int32_t H,
+                                         float eps, void* d_h, void* stream);
 
 int32_t eb_engine_create(const eb_config* cfg, eb_engine** out);
 /* Tensor-parallel heads + expert-parallel experts over tp_size ranks (one process per GPU): rank r holds query heads
