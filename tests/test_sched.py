@@ -144,6 +144,27 @@ def test_attn_plan_leaves_short_ranges_whole_when_they_fill_the_sms():
     assert len(few["items"]) > 40
 
 
+def test_attn_plan_sm_count_follows_the_kernel_choice():
+    """The planner's granularity hint: one CTA per item for decode shapes and short windows, one CTA per (item, KV head),
+    two per SM, for verify shapes on long items; and a plan made with the hint has about 4 x 2 x SMs / n_kv items."""
+    sm = 148
+    assert eb.attn_plan_sm_count(sm, 1, 64, 8, 0) == sm
+    assert eb.attn_plan_sm_count(sm, 2, 64, 8, 0) == sm            # 16 rows still fit the decode tile
+    assert eb.attn_plan_sm_count(sm, 5, 64, 8, 0) == 2 * sm // 8
+    assert eb.attn_plan_sm_count(sm, 5, 16, 2, 0) == sm
+    assert eb.attn_plan_sm_count(sm, 5, 8, 1, 0) == 2 * sm
+    assert eb.attn_plan_sm_count(sm, 5, 64, 8, 128) == sm          # short window: the one-CTA-per-item kernel
+    assert eb.attn_plan_sm_count(sm, 5, 64, 8, 4096) == 2 * sm // 8
+    assert eb.attn_plan_sm_count(2, 6, 64, 8, 0) == 1              # never below one
+    rng = np.random.default_rng(5)
+    ctx = rng.integers(2048, 8192, size=256).astype(np.int32)
+    ql = np.full(256, 5, np.int32)
+    coarse = eb.attn_plan(ctx, ql, 16, 0, eb.attn_plan_sm_count(sm, 5, 64, 8, 0))
+    fine = eb.attn_plan(ctx, ql, 16, 0, sm)
+    assert len(coarse["items"]) < len(fine["items"])
+    assert 256 <= len(coarse["items"]) <= 2 * 256                 # 4 x 37 = 148 wanted, one item per sequence at least
+
+
 def test_attn_plan_rejects_bad_input():
     with pytest.raises(eb.EbError):
         eb.attn_plan([5], [6], 16, 0, 148)
