@@ -78,13 +78,15 @@ def test_static_scratch_status_without_a_caller_word(gpu):
         assert capi.static_status_read() == 0 and eb.status_read() == 0
 
 
-def test_static_scratch_refuses_a_partial_slot_outside_the_plan(gpu):
+@pytest.mark.parametrize("q_len", [1, 5])
+def test_static_scratch_refuses_a_partial_slot_outside_the_plan(gpu, q_len):
     """A plan whose items name a partial slot >= n_parts (a stale plan) is skipped and flagged, not followed past the
-    built-in arrays: the rows of the other sequences are still right, and the flagged sequence's output is untouched."""
+    built-in arrays: the rows of the other sequences are still right, and the flagged sequence's output is untouched.
+    q_len 1 runs the decode kernel, q_len 5 the tcgen05 verify kernel."""
     from eidola_b200 import capi
     from eidola_b200.capi import DeviceBuffer
     from eidola_b200.host import attn_paged_sink_static
-    case = AttnCase([2000, 900], [1, 1], 8, seed=15, sm_count=gpu["sm_count"])
+    case = AttnCase([2000, 900], [q_len, q_len], 8, seed=15, sm_count=gpu["sm_count"])
     launch, plan = case.launch(0, 16)
     case.d_out.zero()
     launch.run()
@@ -101,4 +103,4 @@ def test_static_scratch_refuses_a_partial_slot_outside_the_plan(gpu):
     capi.call("eb_device_sync")
     assert d_status.to_array(np.int32, 1)[0] & 0x2000
     got = case.d_out.to_array(np.uint16, (case.T, case.n_q * 64))
-    assert np.array_equal(got[1], want[1])  # the sequence whose plan was intact
+    assert np.array_equal(got[q_len:], want[q_len:])  # the sequence whose plan was intact
