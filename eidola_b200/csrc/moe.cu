@@ -260,104 +260,117 @@ router_topk_kernel(const uint16_t* x, const uint16_t* wr, int T, int E, int H, i
   router_select<EPL>(lg, lane, E, top_k, t, idx, wts);
 }
 
-// Stable counting sort of the T*top_k routed slots by expert, one CTA of 1024 threads.
+// Stable counting sort of the T*top_k routed slots by expert, one CTA per expert (512 threads):
 //   seg_off[E+1]  : expert segment bounds in the permuted row space
 //   perm_row[i]   : permuted row of slot i = t*top_k + j   (order: expert, then slot index)
 //   row_token[r]  : token whose activations permuted row r carries
-__global__ void __launch_bounds__(1024)
+// Every CTA counts all slots per expert (shared-memory histogram, then a prefix sum over the experts, so it knows where
+// every segment starts without talking to the others) and then places the slots of ITS expert in slot order (ballot +
+// prefix over the CTA, 512 slots per round).  CTA 0 also writes the segment bounds and the tile table.  The result is
+// the one a sequential stable sort gives, whatever the number of CTAs.
+constexpr int kPermThreads = 512;
+
+__global__ void __launch_bounds__(kPermThreads)
 moe_permute_kernel(const int32_t* idx, int n_slots, int top_k, int E, int32_t* seg_off, int32_t* perm_row,
                    int32_t* row_token, int tn, int max_tiles, int32_t* tile_ws, int32_t* status, int skip_foreign) {
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
   eb::pdl_trigger();
-  __shared__ int32_t base[kMaxExperts + 1];   // running start of each expert's unplaced slots
-  __shared__ int32_t wcnt[32][kMaxExperts];   // per-warp counts of the current tile
+  __shared__ int32_t base[kMaxExperts + 1];  // counts, then exclusive prefix sums: start of each expert's segment
+  __shared__ int32_t t_off[kMaxExperts + 1];
+  __shared__ int32_t wsum[kPermThreads / 32];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  for (int e = tid; e <= E; e += 1024) base[e] = 0;
+  const int me = blockIdx.x;
+  for (int e = tid; e <= E; e += kPermThreads) base[e] = 0;
   __syncthreads();
-  for (int i = tid; i < n_slots; i += 1024) {
+  // a slot whose expert is out of range: another rank's under expert parallelism (skipped, perm_row = -1), else a bad
+  // index (flagged, counted as expert 0)
+  auto expert_of = [&](int i) -> int {
     int e = idx[i];
-    if (e < 0 || e >= E) {
-      if (skip_foreign) continue;  // expert parallel: the slot belongs to another rank's expert
-      atomicOr(status, EB_DEV_BAD_INDEX);
-      e = 0;
+    if (e < 0 || e >= E) e = skip_foreign ? -1 : 0;
+    return e;
+  };
+  for (int i = tid; i < n_slots; i += kPermThreads) {
+    const int raw = idx[i];
+    if (raw < 0 || raw >= E) {
+      if (skip_foreign) continue;
+      if (me == 0) atomicOr(status, EB_DEV_BAD_INDEX);
     }
-    atomicAdd(&base[e + 1], 1);
+    atomicAdd(&base[expert_of(i) + 1], 1);
   }
   __syncthreads();
-  if (tid == 0) {
-    for (int e = 0; e < E; ++e) base[e + 1] += base[e];
-  }
-  __syncthreads();
-  for (int e = tid; e <= E; e += 1024) seg_off[e] = base[e];
-  if (tile_ws) {
-    // token-tile table of the grouped GEMMs over these segments (layout of eb_gemm_group_tiles):
-    // blk_off[E+1], n_tiles, tile_group[max_tiles], tile_row0[max_tiles]
-    __shared__ int32_t t_off[kMaxExperts + 1];
-    int32_t* blk_off = tile_ws;
-    int32_t* n_tiles = tile_ws + (E + 1);
-    int32_t* tile_group = n_tiles + 1;
-    int32_t* tile_row0 = tile_group + max_tiles;
-    if (tid == 0) {
-      int tt = 0, bb = 0;
-      for (int e = 0; e < E; ++e) {
-        const int len = base[e + 1] - base[e];
-        t_off[e] = tt;
-        blk_off[e] = bb;
-        tt += (len + tn - 1) / tn;
-        bb += (len + 127) / 128;
+  if (warp == 0) {  // inclusive prefix over base[1..E], 32 experts per step
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      int v = e < E ? base[e + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
       }
-      t_off[E] = tt;
-      blk_off[E] = bb;
-      if (tt > max_tiles) {
-        atomicOr(status, EB_DEV_BAD_INDEX);
-        tt = max_tiles;
-      }
-      *n_tiles = tt;
+      if (e < E) base[e + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
     }
-    __syncthreads();
-    for (int e = tid; e < E; e += 1024)
-      for (int t = t_off[e]; t < t_off[e + 1] && t < max_tiles; ++t) {
-        tile_group[t] = e;
-        tile_row0[t] = base[e] + (t - t_off[e]) * tn;
-      }
   }
   __syncthreads();
-
-  for (int i0 = 0; i0 < n_slots; i0 += 1024) {
-    for (int k = tid; k < 32 * E; k += 1024) wcnt[k / E][k % E] = 0;
-    __syncthreads();
+  if (me == 0) {
+    for (int e = tid; e <= E; e += kPermThreads) seg_off[e] = base[e];
+    if (tile_ws) {
+      // token-tile table of the grouped GEMMs over these segments (layout of eb_gemm_group_tiles):
+      // blk_off[E+1], n_tiles, tile_group[max_tiles], tile_row0[max_tiles]
+      int32_t* blk_off = tile_ws;
+      int32_t* n_tiles = tile_ws + (E + 1);
+      int32_t* tile_group = n_tiles + 1;
+      int32_t* tile_row0 = tile_group + max_tiles;
+      if (tid == 0) {
+        int tt = 0, bb = 0;
+        for (int e = 0; e < E; ++e) {
+          const int len = base[e + 1] - base[e];
+          t_off[e] = tt;
+          blk_off[e] = bb;
+          tt += (len + tn - 1) / tn;
+          bb += (len + 127) / 128;
+        }
+        t_off[E] = tt;
+        blk_off[E] = bb;
+        if (tt > max_tiles) {
+          atomicOr(status, EB_DEV_BAD_INDEX);
+          tt = max_tiles;
+        }
+        *n_tiles = tt;
+      }
+      __syncthreads();
+      for (int e = tid; e < E; e += kPermThreads)
+        for (int t = t_off[e]; t < t_off[e + 1] && t < max_tiles; ++t) {
+          tile_group[t] = e;
+          tile_row0[t] = base[e] + (t - t_off[e]) * tn;
+        }
+    }
+  }
+  // the slots of expert `me`, in slot order
+  int placed = base[me];
+  for (int i0 = 0; i0 < n_slots; i0 += kPermThreads) {
     const int i = i0 + tid;
-    const bool on0 = i < n_slots;
-    int e = on0 ? idx[i] : -1;
-    bool on = on0;
-    if (on && (e < 0 || e >= E)) {
-      if (skip_foreign) {
-        on = false;
-        e = -1;
-        perm_row[i] = -1;
-      } else {
-        e = 0;
-      }
-    }
-    const unsigned peers = __match_any_sync(0xffffffffu, e);
-    const int rank = __popc(peers & ((1u << lane) - 1u));
-    if (on && rank == 0) wcnt[warp][e] = __popc(peers);
+    const int e = i < n_slots ? expert_of(i) : -2;
+    const bool mine = e == me;
+    const unsigned votes = __ballot_sync(0xffffffffu, mine);
+    if (lane == 0) wsum[warp] = __popc(votes);
     __syncthreads();
-    if (tid < E) {  // exclusive prefix over the 32 warps, continuing from the expert's running base
-      int run = base[tid];
-      for (int w = 0; w < 32; ++w) {
-        const int c = wcnt[w][tid];
-        wcnt[w][tid] = run;
-        run += c;
-      }
-      base[tid] = run;
+    int before = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kPermThreads / 32; ++w) {
+      const int c = wsum[w];
+      if (w < warp) before += c;
+      total += c;
     }
-    __syncthreads();
-    if (on) {
-      const int r = wcnt[warp][e] + rank;
+    if (mine) {
+      const int r = placed + before + __popc(votes & ((1u << lane) - 1u));
       perm_row[i] = r;
       row_token[r] = i / top_k;
+    } else if (me == 0 && e == -1) {
+      perm_row[i] = -1;  // another rank's expert
     }
+    placed += total;
     __syncthreads();
   }
 }
@@ -487,8 +500,8 @@ int32_t eb_moe_permute(const int32_t* d_idx, int32_t T, int32_t top_k, int32_t E
              kMaxExperts);
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_moe_permute: no device");
-  EB_CUDA(eb::launch(moe_permute_kernel, dim3(1), dim3(1024), 0, eb::as_stream(stream), d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
-                                                             d_row_token, 0, 0, nullptr, status, 0));
+  EB_CUDA(eb::launch(moe_permute_kernel, dim3((unsigned)E), dim3(kPermThreads), 0, eb::as_stream(stream), d_idx, T * top_k, top_k, E,
+                     d_seg_off, d_perm_row, d_row_token, 0, 0, nullptr, status, 0));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -514,8 +527,8 @@ static int32_t permute_tiles(const int32_t* d_idx, int32_t T, int32_t top_k, int
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_moe_permute_tiles: no device");
   const int max_tiles = (T * top_k) / tile_tokens + E;
-  EB_CUDA(eb::launch(moe_permute_kernel, dim3(1), dim3(1024), 0, eb::as_stream(stream), d_idx, T * top_k, top_k, E, d_seg_off, d_perm_row,
-                                                             d_row_token, tile_tokens, max_tiles, (int32_t*)d_group_work, status, skip_foreign));
+  EB_CUDA(eb::launch(moe_permute_kernel, dim3((unsigned)E), dim3(kPermThreads), 0, eb::as_stream(stream), d_idx, T * top_k, top_k, E,
+                     d_seg_off, d_perm_row, d_row_token, tile_tokens, max_tiles, (int32_t*)d_group_work, status, skip_foreign));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
