@@ -446,7 +446,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     return EB_OK;
   };
   // the ranks' slices of a [T][H] partial (esz bytes per element, in the arena) to their owners, side by side as planes
-  auto scatter_planes = [&](const void* src, int esz) -> int32_t {
+  // and the owner's residual + norm over the planes of its slice; its CTAs wait for the peers' flags themselves (a rank
+  // whose slice is empty still waits, with a launch of its own: every rank meets every exchange)
+  auto scatter_planes_norm = [&](const void* src, int esz, const float* gain) -> int32_t {
     const int64_t so = aoff(src), step = (int64_t)chunk * H * esz, dof = aoff(e->planes), valid = (int64_t)T * H * esz;
     int32_t seq = 0;
     EB_TRY(eb_symm_push(e->symm, 1, &so, &step, &dof, &step, &step, &valid, 1, &seq, st));
@@ -454,7 +456,9 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     // the first exchange of a step also absorbs the skew between the ranks' host loops
     const int patience = first_exchange ? 32 : 1;
     first_exchange = false;
-    return eb_symm_wait(e->symm, seq, patience, st);
+    if (nt == 0) return eb_symm_wait(e->symm, seq, patience, st);
+    return eb_planes_residual_rmsnorm_after(e->symm, seq, patience, e->planes, esz == 2, e->tp_size, (int64_t)chunk * H,
+                                            e->x + (size_t)t0 * H, gain, nt, H, c.rms_eps, e->h + (size_t)t0 * H, st);
   };
 
   const bool prof = (c.debug & 2) != 0;
@@ -622,32 +626,28 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
         n += 2;
       } else if (splits == 1) {
         mark(5);
-        if (symm)
-          EB_TRY(scatter_planes(e->o, 2));
-        else
+        if (symm) {  // the ranks' bf16 planes of my slice, added in rank order in fp32, rounded once
+          EB_TRY(scatter_planes_norm(e->o, 2, L.g_mlp));
+          mark(-1);
+        } else {
           EB_TRY(eb_comm_reduce_scatter_bf16(e->comm, e->o, (int64_t)chunk * H, st));
-        mark(-1);
-        if (symm)  // the ranks' bf16 planes of my slice, added in rank order in fp32, rounded once
-          EB_TRY(eb_planes_residual_rmsnorm(e->planes, 1, e->tp_size, (int64_t)chunk * H, e->x + (size_t)t0 * H, L.g_mlp, nt, H,
-                                            c.rms_eps, e->h + (size_t)t0 * H, st));
-        else
+          mark(-1);
           EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
                                            e->h + (size_t)t0 * H, st));
+        }
         n += 1;
       } else {
         EB_TRY(eb_sum_planes_f32((const float*)e->gemm_ws, splits, e->o, (int64_t)T * H, e->ar_buf, st));
         mark(5);
-        if (symm)
-          EB_TRY(scatter_planes(e->ar_buf, 4));
-        else
+        if (symm) {
+          EB_TRY(scatter_planes_norm(e->ar_buf, 4, L.g_mlp));
+          mark(-1);
+        } else {
           EB_TRY(eb_comm_reduce_scatter_f32(e->comm, e->ar_buf, (int64_t)chunk * H, st));
-        mark(-1);
-        if (symm)
-          EB_TRY(eb_planes_residual_rmsnorm(e->planes, 0, e->tp_size, (int64_t)chunk * H, e->x + (size_t)t0 * H, L.g_mlp, nt, H,
-                                            c.rms_eps, e->h + (size_t)t0 * H, st));
-        else
+          mark(-1);
           EB_TRY(eb_oproj_residual_rmsnorm(e->ar_buf + (size_t)t0 * H, 1, nullptr, e->x + (size_t)t0 * H, L.g_mlp, nt, H, c.rms_eps,
                                            e->h + (size_t)t0 * H, st));
+        }
         n += 2;
       }
     }
@@ -742,17 +742,15 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
         }
         EB_TRY(eb_moe_combine_bf16(e->y, e->perm_row, e->r_wts, T, c.top_k, H, e->o, st));
         mark(5);
-        if (symm)
-          EB_TRY(scatter_planes(e->o, 2));
-        else
+        if (symm) {
+          EB_TRY(scatter_planes_norm(e->o, 2, g_next));
+          mark(-1);
+        } else {
           EB_TRY(eb_comm_reduce_scatter_bf16(e->comm, e->o, (int64_t)chunk * H, st));
-        mark(-1);
-        if (symm)
-          EB_TRY(eb_planes_residual_rmsnorm(e->planes, 1, e->tp_size, (int64_t)chunk * H, e->x + (size_t)t0 * H, g_next, nt, H,
-                                            c.rms_eps, e->h + (size_t)t0 * H, st));
-        else
+          mark(-1);
           EB_TRY(eb_oproj_residual_rmsnorm(nullptr, 1, e->o + (size_t)t0 * H, e->x + (size_t)t0 * H, g_next, nt, H, c.rms_eps,
                                            e->h + (size_t)t0 * H, st));
+        }
       }
       // the next consumer (QKV projection of the next layer, or the LM head) needs every token's normalised row as
       // e4m3 with block scales: the slice's owner quantises its rows and the codes and scales are gathered (half the
