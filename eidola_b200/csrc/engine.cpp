@@ -476,7 +476,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   };
   // Dense GEMM; when `splits` is given the split-K partials are left in gemm_ws for a fused consumer.
   auto dense = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout,
-                   int32_t* splits, int64_t ldy = 0) -> int32_t {
+                   int32_t* splits, int64_t ldy = 0, int want_splits = 0) -> int32_t {
     eb_gemm_args g = {};
     g.d_x8 = x8;
     g.d_sx = sx;
@@ -489,6 +489,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     g.K = K;
     g.n_groups = 1;
     g.w_tiled = 1;
+    g.splits = want_splits;
     g.d_work = (T <= 512 && N <= std::max(e->nqkv, H)) ? e->gemm_ws : nullptr;
     g.work_bytes = g.d_work ? e->gemm_ws_bytes : 0;
     n += 1;
@@ -596,7 +597,14 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     EB_TRY(eb_quant_act_block128(e->attn, e->hqd, T, e->hqd, nullptr, 1, e->a8, e->sa, st));
     mark(-1);
     mark(2);
-    EB_TRY(dense(e->a8, e->sa, L.wo, H, e->hqd, e->o, &splits));
+    {
+      // Whole-batch exchanges add the ranks' partials in fp32: the projection must then leave fp32 (split-K) planes, not a
+      // bf16 result rounded per rank.  The GEMM splits K by itself only while the tiles do not fill the GPU and every
+      // split keeps four K blocks; otherwise (8 ranks: K = 512; steps above 256 tokens) two splits are asked for.
+      const int kb_o = (e->hqd + 127) / 128;
+      const int o_splits = (whole && !(kb_o >= 8 && T <= 256) && kb_o >= 2) ? 2 : 0;
+      EB_TRY(dense(e->a8, e->sa, L.wo, H, e->hqd, e->o, &splits, 0, o_splits));
+    }
     mark(-1);
     if (!tp) {
       EB_TRY(eb_oproj_residual_rmsnorm(splits > 1 ? (const float*)e->gemm_ws : nullptr, splits, e->o, e->x, L.g_mlp, T, H,
