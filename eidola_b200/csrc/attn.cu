@@ -841,13 +841,11 @@ attn_v64_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p, co
           for (int j = 0; j < 4; ++j)
             arow[4 * j + qc] = make_float2(__uint_as_float(ov[4 * j + 2 * half]), __uint_as_float(ov[4 * j + 2 * half + 1]));
           if (qc == 0 && kh == 0) *reinterpret_cast<float2*>(p.part_ml + prow * 2) = make_float2(m_row, l_row);
-          // the plan reserves vp.ppi partial slots per item; this kernel fills one, the others are declared empty
+          // the plan reserves vp.ppi partial slots per item; this kernel fills one, the others are declared empty (a sum of
+          // zero: the merge skips such a slot without reading its accumulator, which is left as it was)
           for (int e = 1; e < vp.ppi; ++e) {
             const int64_t pe = ((int64_t)(item.part + e) * p.max_q_len + qi) * p.n_q + head;
             if (qc == 0 && kh == 0) *reinterpret_cast<float2*>(p.part_ml + pe * 2) = make_float2(kNegBig, 0.f);
-            float4* zrow = reinterpret_cast<float4*>(p.part_acc + pe * kHeadDim) + kh * 8;
-#pragma unroll
-            for (int j = 0; j < 2; ++j) zrow[4 * j + qc] = make_float4(0.f, 0.f, 0.f, 0.f);
           }
         }
       }
@@ -898,14 +896,23 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(const AttnParams p) {
     for (int o = 16; o; o >>= 1) mf = fmaxf(mf, __shfl_xor_sync(0xffffffffu, mf, o));
     float den = exp2f(sk - mf);
     float ax = 0.f, ay = 0.f;
-    for (int j = pb; j < pe; ++j) {
-      const int64_t row = ((int64_t)j * p.max_q_len + qi) * p.n_q + head;
-      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + row * 2);
-      const float w = exp2f(ml.x - mf);
-      den += w * ml.y;
-      const float2 a = *reinterpret_cast<const float2*>(p.part_acc + row * kHeadDim + lane * 2);
-      ax += w * a.x;
-      ay += w * a.y;
+    // partials in ascending order, 32 at a time: lane k holds (m, l) of partial base + k; the ones with an empty sum (no
+    // visible key, or a slot its kernel did not use) are passed over without touching their accumulators
+    for (int base = pb; base < pe; base += 32) {
+      const int jl = base + lane;
+      float2 ml = make_float2(kNegBig, 0.f);
+      if (jl < pe) ml = *reinterpret_cast<const float2*>(p.part_ml + (((int64_t)jl * p.max_q_len + qi) * p.n_q + head) * 2);
+      unsigned live = __ballot_sync(0xffffffffu, ml.y != 0.f);
+      while (live) {
+        const int k = __ffs(live) - 1;
+        live &= live - 1;
+        const float w = exp2f(__shfl_sync(0xffffffffu, ml.x, k) - mf);
+        den += w * __shfl_sync(0xffffffffu, ml.y, k);
+        const int64_t row = ((int64_t)(base + k) * p.max_q_len + qi) * p.n_q + head;
+        const float2 a = *reinterpret_cast<const float2*>(p.part_acc + row * kHeadDim + lane * 2);
+        ax += w * a.x;
+        ay += w * a.y;
+      }
     }
     const float inv = 1.0f / den;
     uint16_t* orow = p.out + (int64_t)(q0 + qi) * p.out_stride + (int64_t)head * kHeadDim;
