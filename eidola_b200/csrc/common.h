@@ -66,14 +66,14 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 bool pdl_enabled();
 // Called by every thread of a CTA after its last store into the peers' arenas: the stores are fenced, and the CTA of
-// the grid (x dimension) that arrives last writes the collective's sequence number into this rank's flag word on every
+// the grid that arrives last writes the collective's sequence number into this rank's flag word on every
 // peer (the protocol of the push kernels).
 __device__ __forceinline__ void peer_arrive_cta(const PeerPlanes& a) {
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
     const int prev = atomicAdd(a.counter, 1);
-    if (prev == (int)gridDim.x - 1) {
+    if (prev == (int)(gridDim.x * gridDim.y * gridDim.z) - 1) {
       *a.counter = 0;  // every other CTA has arrived: the counter is free for the next collective
       __threadfence_system();
       for (int p = 0; p < a.size; ++p) {

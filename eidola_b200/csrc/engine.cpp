@@ -74,6 +74,15 @@ struct eb_engine {
   uint8_t* planes = nullptr;                 // [tp_size][chunk rows][hidden] fp32 or bf16: the ranks' partial rows of my slice
   // expert parallelism as dispatch / return of rows (the all-to-all pair) instead of gather-everything + reduce-scatter
   bool slices_forced = false;
+  // Tensor-parallel O projection on the GATHERED attention output: every rank keeps the full W_o, quantises its heads'
+  // columns straight into the other ranks' copies of the operand, and multiplies full-K rows itself (all rows of a small
+  // step, its token slice of a large one).  One byte per (token, head column) crosses the links instead of a partial
+  // [T, H] per rank, and the sum over K is the single-GPU one.  Default from four ranks on (EIDOLA_B200_TP_OGATHER=1 / 0 forces it on / off);
+  // otherwise, and with NCCL transport, the ranks keep their column band of W_o and exchange partial results.
+  bool o_gather = false;
+  int o_cols = 0;           // columns of the W_o this rank holds: all head columns (o_gather) or its own heads'
+  uint8_t* a8g = nullptr;   // [Tc][n_q_heads * head_dim] e4m3 gathered operand (arena)
+  float* sag = nullptr;     // its block scales
   bool a2a = false, a2a_forced = false;  // forced: EIDOLA_B200_EP_A2A=1 (tests): row dispatch whatever the step's size
   uint16_t* xp16 = nullptr;                  // [tokens * top_k][hidden] bf16: rows dispatched to this rank's experts (global row numbering)
   int32_t* r_idx_local = nullptr;
@@ -198,14 +207,14 @@ int32_t init_weights(eb_engine* e) {
   void* st = e->stream;
   const int hqd_g = c.n_q_heads * c.head_dim, hkd_g = c.n_kv_heads * c.head_dim, nqkv_g = hqd_g + 2 * hkd_g;
   {  // row-major staging for one band of one weight tensor; released when the weights are in place
-    const int64_t widest = std::max<int64_t>(std::max(H, I), e->hqd);
+    const int64_t widest = std::max<int64_t>(std::max(H, I), e->o_cols);
     EB_CUDA(cudaMalloc((void**)&e->w_scratch, (size_t)(65536 * widest)));
   }
   const int kv_row0 = (e->tp_rank * e->hkv_l * c.head_dim) / 128 * 128;  // start of this rank's K (and V) band
   for (int l = 0; l < c.n_layers; ++l) {
     Layer& L = e->layers[(size_t)l];
     EB_TRY(alloc_fp8(e, &L.wqkv, 1, e->nqkv, H));
-    EB_TRY(alloc_fp8(e, &L.wo, 1, H, e->hqd));
+    EB_TRY(alloc_fp8(e, &L.wo, 1, H, e->o_cols));
     EB_TRY(alloc_fp8(e, &L.w1, E, 2 * I, H));
     EB_TRY(alloc_fp8(e, &L.w2, E, H, I));
     EB_TRY(dev_alloc(e, &L.wr, (size_t)c.n_experts * H, &e->weight_bytes));
@@ -221,9 +230,9 @@ int32_t init_weights(eb_engine* e) {
                               band_rows[b], sid(l, K_WQKV, 0)));
       dst_row += band_rows[b];
     }
-    EB_TRY(eb_synth_weight_fp8_slice(e->w_scratch, L.wo.scales, H, hqd_g, 0, H, (int64_t)e->tp_rank * e->hqd, e->hqd, c.seed,
-                                     sid(l, K_WO, 0), c.init_std, st));
-    EB_TRY(eb_weight_tile_fp8(e->w_scratch, 1, H, e->hqd, L.wo.codes, st));
+    EB_TRY(eb_synth_weight_fp8_slice(e->w_scratch, L.wo.scales, H, hqd_g, 0, H, e->o_gather ? 0 : (int64_t)e->tp_rank * e->hqd,
+                                     e->o_cols, c.seed, sid(l, K_WO, 0), c.init_std, st));
+    EB_TRY(eb_weight_tile_fp8(e->w_scratch, 1, H, e->o_cols, L.wo.codes, st));
     const int64_t s1 = eb::cdiv(2 * I, 128) * e->kbH, s2 = eb::cdiv(H, 128) * e->kbI;
     for (int x = 0; x < E; ++x) {
       EB_TRY(synth_band_tiled(e, &L.w1, x, 2 * I, 0, L.w1.scales + x * s1, 2 * I, H, 0, 2 * I, sid(l, K_W1, e->e0 + x)));
@@ -280,7 +289,8 @@ int32_t init_work(eb_engine* e) {
       e->slices_forced = w && w[0] == '0';
     }
     const size_t sz_routed = e->a2a ? a256((size_t)R * H * 2) : 0;
-    const size_t total = 3 * sz_rows2 + sz_rows1 + sz_rows4 + sz_planes + sz_sh + 2 * sz_r + sz_cand + 2 * sz_routed;
+    const size_t sz_a8g = e->o_gather ? a256(Tc * (size_t)e->o_cols) : 0, sz_sag = e->o_gather ? a256((size_t)tb0 * (e->o_cols / 128) * 4) : 0;
+    const size_t total = 3 * sz_rows2 + sz_rows1 + sz_rows4 + sz_planes + sz_sh + 2 * sz_r + sz_cand + 2 * sz_routed + sz_a8g + sz_sag;
     EB_TRY(eb_symm_create(e->comm, total, &e->symm));
     void* base = nullptr;
     EB_TRY(eb_symm_ptr(e->symm, e->tp_rank, &base, nullptr));
@@ -304,6 +314,10 @@ int32_t init_work(eb_engine* e) {
     if (e->a2a) {
       e->xp16 = (uint16_t*)carve(sz_routed);
       e->y = (uint16_t*)carve(sz_routed);
+    }
+    if (e->o_gather) {
+      e->a8g = carve(sz_a8g);
+      e->sag = (float*)carve(sz_sag);
     }
     e->arena_used = o;
     *w += (int64_t)total;
@@ -476,7 +490,8 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   };
   // Dense GEMM; when `splits` is given the split-K partials are left in gemm_ws for a fused consumer.
   auto dense = [&](const uint8_t* x8, const float* sx, const Fp8Weight& w, int N, int K, uint16_t* yout,
-                   int32_t* splits, int64_t ldy = 0, int want_splits = 0) -> int32_t {
+                   int32_t* splits, int64_t ldy = 0, int want_splits = 0, int rows = -1) -> int32_t {
+    if (rows < 0) rows = T;
     eb_gemm_args g = {};
     g.d_x8 = x8;
     g.d_sx = sx;
@@ -484,13 +499,13 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     g.d_sw = w.scales;
     g.d_y = yout;
     g.ldy = ldy ? ldy : N;
-    g.rows = T;
+    g.rows = rows;
     g.N = N;
     g.K = K;
     g.n_groups = 1;
     g.w_tiled = 1;
     g.splits = want_splits;
-    g.d_work = (T <= 512 && N <= std::max(e->nqkv, H)) ? e->gemm_ws : nullptr;
+    g.d_work = (rows <= 512 && N <= std::max(e->nqkv, H)) ? e->gemm_ws : nullptr;
     g.work_bytes = g.d_work ? e->gemm_ws_bytes : 0;
     n += 1;
     return splits ? eb_gemm_fp8_block_partial(&g, splits, st) : eb_gemm_fp8_block(&g, st);
@@ -593,16 +608,39 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     mark(pi ? 1 : 0);
     EB_TRY(eb_attn_paged_sink(&a, st));
     mark(-1);
+    if (tp && e->o_gather && symm) {
+      // C1 on the gathered operand: my heads' columns go, quantised, into every rank's operand (small steps) or into the
+      // operand of the rank that owns the rows (large steps); then full-K rows of the projection, the residual and the
+      // norm exactly as on one GPU.
+      int32_t seq = 0;
+      mark(5);
+      EB_TRY(eb_quant_act_block128_to_peers(e->symm, e->attn, e->hqd, T, e->hqd, aoff(e->a8g), e->o_cols, aoff(e->sag), e->o_cols / 128,
+                                            whole ? 0 : chunk, &seq, st));
+      EB_TRY(eb_symm_wait(e->symm, seq, first_exchange ? 32 : 1, st));
+      first_exchange = false;
+      mark(-1);
+      const int r0 = whole ? 0 : t0, nr = whole ? T : nt;
+      if (nr > 0) {
+        mark(2);
+        EB_TRY(dense(e->a8g + (size_t)r0 * e->o_cols, e->sag + (size_t)(r0 / 128) * (e->o_cols / 128), L.wo, H, e->o_cols,
+                     e->o + (size_t)r0 * H, &splits, 0, 0, nr));
+        mark(-1);
+        EB_TRY(eb_oproj_residual_rmsnorm(splits > 1 ? (const float*)e->gemm_ws : nullptr, splits, e->o + (size_t)r0 * H,
+                                         e->x + (size_t)r0 * H, L.g_mlp, nr, H, c.rms_eps, e->h + (size_t)r0 * H, st));
+      }
+      n += 3;
+    } else {
     mark(7);
     EB_TRY(eb_quant_act_block128(e->attn, e->hqd, T, e->hqd, nullptr, 1, e->a8, e->sa, st));
     mark(-1);
     mark(2);
     {
-      // Whole-batch exchanges add the ranks' partials in fp32: the projection must then leave fp32 (split-K) planes, not a
-      // bf16 result rounded per rank.  The GEMM splits K by itself only while the tiles do not fill the GPU and every
-      // split keeps four K blocks; otherwise (8 ranks: K = 512; steps above 256 tokens) two splits are asked for.
+      // Decode-sized tensor-parallel steps add the ranks' partials in fp32 (whatever the transport): the projection must
+      // then leave fp32 (split-K) planes, not a bf16 result rounded per rank.  The GEMM splits K by itself only while the
+      // tiles do not fill the GPU and every split keeps four K blocks; otherwise (8 ranks: K = 512; steps above 256
+      // tokens) two splits are asked for.
       const int kb_o = (e->hqd + 127) / 128;
-      const int o_splits = (whole && !(kb_o >= 8 && T <= 256) && kb_o >= 2) ? 2 : 0;
+      const int o_splits = (tp && T <= kWholeBatchTokens && !(kb_o >= 8 && T <= 256) && kb_o >= 2) ? 2 : 0;
       EB_TRY(dense(e->a8, e->sa, L.wo, H, e->hqd, e->o, &splits, 0, o_splits));
     }
     mark(-1);
@@ -658,6 +696,7 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
         }
         n += 2;
       }
+    }
     }
     mark(6);
     if (!tp || whole) {
@@ -886,6 +925,13 @@ int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_si
   e->kbH = (int)eb::cdiv(c.hidden, 128);
   e->kbI = (int)eb::cdiv(c.inter, 128);
   e->kbA = (int)eb::cdiv(e->hqd, 128);
+  {
+    const char* nccl = getenv("EIDOLA_B200_TP_NCCL");
+    const char* og = getenv("EIDOLA_B200_TP_OGATHER");
+    // measured: 2 % slower than the partial planes on 2 ranks (bytes do not matter there), 2 % faster on 4
+    e->o_gather = tp_size > 1 && !(nccl && nccl[0] == '1') && (og ? og[0] == '1' : tp_size >= 4);
+    e->o_cols = e->o_gather ? c.n_q_heads * c.head_dim : e->hqd;
+  }
   e->layers.resize((size_t)c.n_layers);
   e->uploaded_pages.assign((size_t)c.max_seqs, 0);
   int32_t rc = EB_OK;
@@ -1043,7 +1089,8 @@ int32_t eb_engine_load_gguf(eb_engine* e, const char* path) {
     }
     snprintf(name, sizeof(name), "blk.%d.attn_output.weight", l);
     EB_TRY(find_tensor(L, name, 1, H, hqd_g, &t));
-    EB_TRY(load_linear(e, L, *t, H, hqd_g, 0, 0, H, (int64_t)e->tp_rank * e->hqd, e->hqd, &Ly.wo, 0, H, 0, Ly.wo.scales));
+    EB_TRY(load_linear(e, L, *t, H, hqd_g, 0, 0, H, e->o_gather ? 0 : (int64_t)e->tp_rank * e->hqd, e->o_cols, &Ly.wo, 0, H, 0,
+                       Ly.wo.scales));
     snprintf(name, sizeof(name), "blk.%d.ffn_gate_up_exps.weight", l);
     EB_TRY(find_tensor(L, name, c.n_experts, 2 * I, H, &t));
     const eb::GgufTensor* td = nullptr;

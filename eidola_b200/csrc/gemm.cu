@@ -879,6 +879,17 @@ __device__ __forceinline__ float exact_div(float x, float s, float r, bool plain
   return q == 0.f ? q : c;  // a zero keeps its sign (the correction term would turn -0 into +0)
 }
 
+// Destinations of a quantiser launch whose result is one column band of an operand that every rank of a tensor-parallel
+// group assembles (size == 0: a plain launch into `codes` / `scales`): rank p receives the codes at codes[p] (row pitch
+// ldc) and the scales at scales[p] (lds scales per row block); the launch raises the collective's flags itself.
+struct QuantPeers {
+  uint8_t* codes[eb::kPeerMaxRanks];
+  float* scales[eb::kPeerMaxRanks];
+  int64_t ldc;
+  int32_t lds, size, chunk;  // chunk > 0: rows [p * chunk, +chunk) go to rank p only (its token slice); 0: all rows to all
+  eb::PeerPlanes arrive;
+};
+
 // Activation quantiser: one CTA per (128-row block, 128-column block) of a bf16 matrix.
 // NT threads; thread t holds 2048 / NT rows x one 16-byte chunk; block amax -> scale -> e4m3.  Grids with fewer CTAs
 // than SMs run 1024 threads (32 warps hide each other's load and arithmetic latency), large grids 512.
@@ -887,7 +898,7 @@ __device__ __forceinline__ float exact_div(float x, float s, float r, bool plain
 template <int MODE, int NT>
 __global__ void __launch_bounds__(NT, NT == 1024 ? 1 : 2)
 quant_act_kernel(const uint16_t* x, int64_t ldx, int rows, int cols, const int32_t* seg_off, int n_groups,
-                 const int32_t* row_map, int src_rows, uint8_t* codes, float* scales, int32_t* status) {
+                 const int32_t* row_map, int src_rows, uint8_t* codes, float* scales, int32_t* status, const QuantPeers qp) {
   constexpr int RPT = 2048 / NT;   // rows per thread
   constexpr int RSTEP = NT / 16;   // rows between a thread's consecutive chunks
   eb::pdl_wait();  // programmatic dependent launch: the predecessor in the stream has completed
@@ -931,6 +942,7 @@ quant_act_kernel(const uint16_t* x, int64_t ldx, int rows, int cols, const int32
     r1 = min(r0 + 128, rows);
     if (r0 >= rows) return;
   }
+  const int p_lo = qp.chunk > 0 ? r0 / qp.chunk : 0, p_hi = qp.chunk > 0 ? p_lo + 1 : qp.size;  // receivers of this row block
   const int c0 = cb * 128;
   const int chunk = threadIdx.x & 15, rsub = threadIdx.x >> 4;
   const int col = c0 + chunk * 8;
@@ -982,7 +994,13 @@ quant_act_kernel(const uint16_t* x, int64_t ldx, int rows, int cols, const int32
 #pragma unroll
   for (int w = 1; w < NT / 32; ++w) amax = fmaxf(amax, red[w]);
   const float s = amax > 0.f ? __fdiv_rn(amax, 448.0f) : 1.0f;
-  if (threadIdx.x == 0) scales[(int64_t)blk * n_cb + cb] = s;
+  if (threadIdx.x == 0) {
+    if (qp.size == 0) {
+      scales[(int64_t)blk * n_cb + cb] = s;
+    } else {
+      for (int pr = p_lo; pr < p_hi; ++pr) qp.scales[pr][(int64_t)blk * qp.lds + cb] = s;
+    }
+  }
   const float rs = __frcp_rn(s);
   const bool plain = exact_div_plain(s);
 #pragma unroll
@@ -1002,8 +1020,13 @@ quant_act_kernel(const uint16_t* x, int64_t ldx, int rows, int cols, const int32
       asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi16) : "f"(a3), "f"(a2));
       o[k] = (uint32_t)lo16 | ((uint32_t)hi16 << 16);
     }
-    *reinterpret_cast<uint2*>(codes + (int64_t)r * cols + col) = make_uint2(o[0], o[1]);
+    if (qp.size == 0) {
+      *reinterpret_cast<uint2*>(codes + (int64_t)r * cols + col) = make_uint2(o[0], o[1]);
+    } else {
+      for (int pr = p_lo; pr < p_hi; ++pr) *reinterpret_cast<uint2*>(qp.codes[pr] + (int64_t)r * qp.ldc + col) = make_uint2(o[0], o[1]);
+    }
   }
+  if (qp.size) eb::peer_arrive_cta(qp.arrive);  // (such a launch has no segments: every CTA has a block and gets here)
 }
 
 template <int TN>
@@ -1356,13 +1379,13 @@ static int32_t run_quant(int mode, const void* d_x, int64_t ldx, int32_t rows, i
   float* ss = (float*)d_scales;
   cudaStream_t st = eb::as_stream(stream);
   if (mode == 0 && few)
-    EB_CUDA(eb::launch(quant_act_kernel<0, 1024>, dim3(grid), dim3(1024), 0, st, xs, ldx, rows, cols, d_seg_off, n_groups, d_row_map, src_rows, cs, ss, status));
+    EB_CUDA(eb::launch(quant_act_kernel<0, 1024>, dim3(grid), dim3(1024), 0, st, xs, ldx, rows, cols, d_seg_off, n_groups, d_row_map, src_rows, cs, ss, status, QuantPeers{}));
   else if (mode == 0)
-    EB_CUDA(eb::launch(quant_act_kernel<0, 512>, dim3(grid), dim3(512), 0, st, xs, ldx, rows, cols, d_seg_off, n_groups, d_row_map, src_rows, cs, ss, status));
+    EB_CUDA(eb::launch(quant_act_kernel<0, 512>, dim3(grid), dim3(512), 0, st, xs, ldx, rows, cols, d_seg_off, n_groups, d_row_map, src_rows, cs, ss, status, QuantPeers{}));
   else if (few)
-    EB_CUDA(eb::launch(quant_act_kernel<1, 1024>, dim3(grid), dim3(1024), 0, st, xs, ldx, rows, cols, d_seg_off, n_groups, (const int32_t*)nullptr, rows, cs, ss, status));
+    EB_CUDA(eb::launch(quant_act_kernel<1, 1024>, dim3(grid), dim3(1024), 0, st, xs, ldx, rows, cols, d_seg_off, n_groups, (const int32_t*)nullptr, rows, cs, ss, status, QuantPeers{}));
   else
-    EB_CUDA(eb::launch(quant_act_kernel<1, 512>, dim3(grid), dim3(512), 0, st, xs, ldx, rows, cols, d_seg_off, n_groups, (const int32_t*)nullptr, rows, cs, ss, status));
+    EB_CUDA(eb::launch(quant_act_kernel<1, 512>, dim3(grid), dim3(512), 0, st, xs, ldx, rows, cols, d_seg_off, n_groups, (const int32_t*)nullptr, rows, cs, ss, status, QuantPeers{}));
   EB_LAUNCH_CHECK();
   return EB_OK;
 }
@@ -1370,6 +1393,44 @@ static int32_t run_quant(int mode, const void* d_x, int64_t ldx, int32_t rows, i
 int32_t eb_quant_act_block128(const void* d_x, int64_t ldx, int32_t rows, int32_t cols, const int32_t* d_seg_off,
                               int32_t n_groups, void* d_codes, void* d_scales, void* stream) {
   return run_quant(0, d_x, ldx, rows, cols, d_seg_off, n_groups, nullptr, rows, d_codes, d_scales, stream);
+}
+
+int32_t eb_quant_act_block128_to_peers(eb_symm* s, const void* d_x, int64_t ldx, int32_t rows, int32_t cols, int64_t codes_off,
+                                       int64_t ld_codes, int64_t scales_off, int32_t ld_scales, int32_t slice_rows, int32_t* seq,
+                                       void* stream) {
+  EB_REQUIRE(s && d_x && seq, EB_ERR_ARG, "eb_quant_act_block128_to_peers: null pointer");
+  EB_REQUIRE(rows >= 1 && cols >= 128 && cols % 128 == 0 && ldx >= cols && ldx % 8 == 0 && ((uintptr_t)d_x % 16 == 0), EB_ERR_ARG,
+             "eb_quant_act_block128_to_peers: rows %d, cols %d (a multiple of 128), ldx %lld", rows, cols, (long long)ldx);
+  EB_REQUIRE(slice_rows >= 0 && slice_rows % 128 == 0, EB_ERR_ARG, "eb_quant_act_block128_to_peers: slices of %d rows (whole 128-row blocks)", slice_rows);
+  eb::PeerPlanes pp;
+  int32_t rc = eb::symm_peer_planes(s, 0, 0, 0, &pp, seq);  // dst[p] = base of rank p's arena
+  if (rc != EB_OK) return rc;
+  void* base = nullptr;
+  size_t arena_bytes = 0;
+  rc = eb_symm_ptr(s, pp.rank, &base, &arena_bytes);
+  if (rc != EB_OK) return rc;
+  const int64_t n_rb = (rows + 127) / 128, band = (int64_t)pp.size * cols;
+  EB_REQUIRE(codes_off >= 0 && codes_off % 8 == 0 && ld_codes >= band && ld_codes % 8 == 0 && scales_off >= 0 && scales_off % 4 == 0 &&
+                 ld_scales >= band / 128 && codes_off + (int64_t)(rows - 1) * ld_codes + band <= (int64_t)arena_bytes &&
+                 scales_off + ((n_rb - 1) * ld_scales + band / 128) * 4 <= (int64_t)arena_bytes,
+             EB_ERR_ARG, "eb_quant_act_block128_to_peers: the gathered operand leaves the arena of %zu bytes", arena_bytes);
+  int32_t* status = eb::status_word();
+  EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_quant_act_block128_to_peers: no device");
+  QuantPeers qp = {};
+  qp.size = pp.size;
+  qp.ldc = ld_codes;
+  qp.lds = ld_scales;
+  qp.chunk = slice_rows;
+  qp.arrive = pp;
+  for (int p = 0; p < pp.size; ++p) {
+    qp.codes[p] = pp.dst[p] + codes_off + (int64_t)pp.rank * cols;
+    qp.scales[p] = reinterpret_cast<float*>(pp.dst[p] + scales_off) + (int64_t)pp.rank * (cols / 128);
+  }
+  const dim3 grid((unsigned)(cols / 128), (unsigned)n_rb);
+  EB_CUDA(eb::launch(quant_act_kernel<0, 1024>, dim3(grid), dim3(1024), 0, eb::as_stream(stream), (const uint16_t*)d_x, ldx, rows, cols,
+                     (const int32_t*)nullptr, 1, (const int32_t*)nullptr, rows, (uint8_t*)nullptr, (float*)nullptr, status, qp));
+  EB_LAUNCH_CHECK();
+  return EB_OK;
 }
 
 int32_t eb_quant_gather_block128(const void* d_x, int64_t ldx, int32_t src_rows, const int32_t* d_row_map, int32_t rows,

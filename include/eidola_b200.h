@@ -511,6 +511,15 @@ int32_t eb_sum_planes_f32_to_peers(eb_symm* s, int64_t dst_off, int64_t plane_st
                                    int32_t* seq, void* stream);
 int32_t eb_moe_combine_bf16_to_peers(eb_symm* s, int64_t dst_off, int64_t plane_step, const void* d_y, const int32_t* d_perm_row,
                                      const float* d_wts, int32_t T, int32_t top_k, int32_t H, int32_t* seq, void* stream);
+/* Quantises this rank's column band of an operand that every rank assembles (the attention output before a replicated O
+ * projection): x [rows][cols] bf16 -> e4m3 codes and 128x128 block scales, stored straight into EVERY rank's arena, the
+ * codes at codes_off + rank * cols with row pitch ld_codes, the scales at scales_off + rank * cols / 128 (floats) with
+ * ld_scales scales per row block; the launch raises the collective's flags itself (seq for eb_symm_wait).  With
+ * slice_rows > 0 (a multiple of 128) rows [p * slice_rows, +slice_rows) go to rank p alone, the owner of that token slice;
+ * with 0 all rows go to all ranks.  The codes and scales are those of eb_quant_act_block128 on the same band. */
+int32_t eb_quant_act_block128_to_peers(eb_symm* s, const void* d_x, int64_t ldx, int32_t rows, int32_t cols, int64_t codes_off,
+                                       int64_t ld_codes, int64_t scales_off, int32_t ld_scales, int32_t slice_rows, int32_t* seq,
+                                       void* stream);
 /* eb_planes_residual_rmsnorm on planes that the ranks of `s` pushed as collective `seq`: every CTA waits, bounded, for its
  * peers' flags itself, so no eb_symm_wait launch is needed between the push and this call.  s == NULL: no wait. */
 int32_t eb_planes_residual_rmsnorm_after(eb_symm* s, int32_t seq, int32_t patience, const void* d_planes, int32_t planes_are_bf16,
@@ -538,7 +547,13 @@ int32_t eb_engine_create(const eb_config* cfg, eb_engine** out);
  * peers' memory, a flag per sender, a consumer kernel that waits for the flags with a bounded number of polls and
  * raises EB_DEV_WAIT_TIMEOUT instead of hanging); `comm` carries the set-up (exchange of the memory handles) and, with
  * EIDOLA_B200_TP_NCCL=1, the exchanges themselves as NCCL reduce-scatter / all-gather calls.  EIDOLA_B200_TP_WHOLE=0 and
- * EIDOLA_B200_EP_A2A=0|1 force one of the forms (A/B runs and tests). */
+ * EIDOLA_B200_EP_A2A=0|1 force one of the forms (A/B runs and tests).
+ *
+ * From four ranks on (peer-memory transport; EIDOLA_B200_TP_OGATHER=1|0 forces it on or off) the O projection has no
+ * partial products at all: every rank keeps the whole W_o, quantises its heads' columns of the attention output straight
+ * into the other ranks' copies of the operand (eb_quant_act_block128_to_peers: all rows to all ranks for steps of up to
+ * 512 tokens, a token slice to its owner otherwise) and multiplies full-K rows itself.  One byte per (token, head column)
+ * crosses the links instead of a [tokens, hidden] partial per rank, and the projection's bits are the single-GPU ones. */
 int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_size, eb_comm* comm, eb_engine** out);
 int32_t eb_engine_destroy(eb_engine* e);
 /* Device bytes held by weights, KV pages and workspaces. */

@@ -80,11 +80,17 @@ MODES = {
     "peer_rows": {"EIDOLA_B200_EP_A2A": "1"},                          # experts by dispatch / return of rows
     "peer_sums": {"EIDOLA_B200_EP_A2A": "0", "EIDOLA_B200_TP_WHOLE": "0"},  # slices, experts by partial sums
     "nccl": {"EIDOLA_B200_TP_NCCL": "1"},                              # NCCL reduce-scatter / all-gather
+    # O projection: from four ranks on the engine multiplies the GATHERED attention output by a replicated W_o, below that
+    # W_o stays split by columns and the ranks' partial results are exchanged; these force one or the other
+    "peer_gather": {"EIDOLA_B200_TP_OGATHER": "1"},
+    "peer_gather_slices": {"EIDOLA_B200_TP_OGATHER": "1", "EIDOLA_B200_TP_WHOLE": "0"},
+    "peer_partials": {"EIDOLA_B200_TP_OGATHER": "0"},
 }
 
 
 @pytest.mark.parametrize("name,world,mode", [("tp_small", 2, "peer_sums"), ("tp_small", 2, "peer_rows"), ("tp_small", 2, "peer"), ("tp_mid", 2, "peer"), ("tp_mid", 2, "peer_slices"),
-                                             ("tp_mid", 2, "nccl"), ("tp_mid", 2, "peer_rows"), ("tp_mid", 4, "peer"),
+                                             ("tp_mid", 2, "nccl"), ("tp_mid", 2, "peer_rows"), ("tp_mid", 2, "peer_gather"),
+                                             ("tp_mid", 2, "peer_gather_slices"), ("tp_mid", 4, "peer"), ("tp_mid", 4, "peer_partials"),
                                              ("tp_mid", 4, "peer_sums"), ("tp_mid", 8, "peer"), ("tp_mid", 8, "nccl")])
 def test_tp_engine_matches_oracle_and_single_gpu(gpu, tmp_path, name, world, mode):
     import eidola_b200 as eb
