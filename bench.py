@@ -125,13 +125,17 @@ class ClockSampler:
 
 # ------------------------------------------------------------------------------------------ decoder workload
 
-def decoder_config(make_config, n_layers=24, n_seqs=256, max_ctx=8192, steps=0, n_experts=32, debug=0, seed=4, max_q_len=1):
+def decoder_config(make_config, n_layers=24, n_seqs=256, max_ctx=8192, steps=0, n_experts=32, debug=0, seed=4, max_q_len=1,
+                   max_tokens=0):
     """eb_config of the 20b-shaped decoder; `make_config` is the binding's (engine arm) or the CPU checker's (CPU arm)."""
     pages_per_seq = (max_ctx + steps + PAGE) // PAGE + 1
     return make_config(n_layers=n_layers, hidden=2880, n_q_heads=64, n_kv_heads=8, window=128, n_experts=n_experts,
                        top_k=4, inter=2880, vocab=201088, num_pages=1, max_seqs=n_seqs,
-                       max_pages_per_seq=pages_per_seq, max_tokens=n_seqs * max_q_len, max_q_len=max_q_len, seed=seed, debug=debug)
+                       max_pages_per_seq=pages_per_seq, max_tokens=max(max_tokens, n_seqs * max_q_len), max_q_len=max_q_len, seed=seed,
+                       debug=debug)
 
+
+PREFILL_STEP_ROWS = 4096  # token rows of a prefill step (--prefill real): whole prompts, several sequences per step
 
 DECODER_NAME = ("gpt-oss-20b-shaped random-init FP8 decoder: 24 layers (even 128-window, odd full), hidden 2880, 64q/8kv "
                 "heads d64, 32 experts top-4 inter 2880, vocab 201088; 256 ragged seqs, prompts U[128,8192], greedy decode")
@@ -151,13 +155,14 @@ class DecoderWorkload:
         rng = np.random.default_rng(seed)
         self.ctx0 = rng.integers(min_ctx, max_ctx + 1, size=n_seqs).astype(np.int32)
         cfg = decoder_config(make_config, n_layers=n_layers, n_seqs=n_seqs, max_ctx=max_ctx, steps=total_steps,
-                             debug=(2 if profile else 0) | debug, seed=seed, max_q_len=6 if prefill == "real" else 1)
+                             debug=(2 if profile else 0) | debug, seed=seed, max_q_len=6 if prefill == "real" else 1,
+                             max_tokens=PREFILL_STEP_ROWS if prefill == "real" else 0)
         cfg.num_pages = int(((self.ctx0.astype(np.int64) + total_steps + PAGE) // PAGE + 1).sum()) + 64
         self.cfg = cfg
         self.eng = eb.Engine(cfg, rank, world, comm)
         self.prefill_stats = None
         if prefill == "real":
-            # the engine computes the cache itself: every prompt runs through all layers in chunks of 6 tokens
+            # the engine computes the cache itself: the prompts run through all layers, PREFILL_STEP_ROWS token rows per step
             self.slots = np.array([self.eng.admit(0) for _ in self.ctx0], np.int32)
             prompts = [rng.integers(0, cfg.vocab, size=int(L)).astype(np.int32) for L in self.ctx0]
             t0 = time.perf_counter()
@@ -165,7 +170,8 @@ class DecoderWorkload:
             wall = time.perf_counter() - t0
             n_tok = int(self.ctx0.astype(np.int64).sum())
             self.prefill_stats = {"prompt_tokens": n_tok, "steps": steps, "device_ms": ms, "wall_ms": wall * 1e3,
-                                  "prompt_tokens_per_s": n_tok / (ms * 1e-3), "chunk": 6,
+                                  "prompt_tokens_per_s": n_tok / (ms * 1e-3), "chunk": self.eng.chunk_tokens(),
+                                  "rows_per_step": PREFILL_STEP_ROWS,
                                   "prompts": "U[%d,%d] tokens per sequence" % (min_ctx, max_ctx)}
             self.tokens = first.astype(np.int32)
         else:
@@ -212,7 +218,7 @@ class DecoderWorkload:
         return {"workload": self.name, "n_seqs": int(len(self.ctx0)), "n_layers": int(self.cfg.n_layers),
                 "mean_context": float(self.ctx_now().mean()),
                 "device_bytes_per_rank": self.mem,
-                "prefill": ("real: eb_engine_prefill ran every prompt through all layers in chunks of 6 tokens" if self.prefill_stats
+                "prefill": ("real: eb_engine_prefill ran every prompt through all layers, %d token rows per step" % PREFILL_STEP_ROWS if self.prefill_stats
                             else "KV pages filled with seeded N(0,1) values (stand-in for prefill)"),
                 "l2": "per-step working set ~%.0f GB per GPU >> L2, no flush" % (self.step_alg_bytes()["total"] / 1e9)}
 

@@ -120,6 +120,8 @@ struct eb_engine {
   size_t stage_words = 0;
   int32_t* h_result = nullptr;  // pinned: next[T] then margin[T]
   int32_t cap_items = 0;
+  int32_t chunk_cap = 0;  // most new tokens one sequence may bring to a step (a prefill chunk); see eb_engine_chunk_tokens
+  int32_t cap_ent = 0;    // most attention entries of a step: a sequence's new tokens in runs of at most max_q_len
   // debug
   int32_t* dbg_route = nullptr;
   uint16_t* dbg_hidden = nullptr;
@@ -364,7 +366,8 @@ int32_t init_work(eb_engine* e) {
   e->group_ws_bytes = ws2;
   // work items of one attention launch: ~4 per SM from the planner, one per sequence at least, and enough for a pool
   // whose every page is in use at the largest run the kernel accepts (512 pages per item)
-  e->cap_items = 4 * e->sm_count + c.max_seqs + 16 + c.num_pages / 512;
+  e->cap_ent = c.max_seqs + c.max_tokens / c.max_q_len;
+  e->cap_items = 4 * e->sm_count + e->cap_ent + 16 + c.num_pages / 512;
   const int ppi = 8 / e->hkv_l;
   size_t acc_b = 0, ml_b = 0;
   EB_TRY(eb_attn_workspace(e->cap_items * ppi, c.max_q_len, e->hq_l, c.head_dim, &acc_b, &ml_b));
@@ -374,10 +377,11 @@ int32_t init_work(eb_engine* e) {
   EB_TRY(dev_alloc(e, &e->d_margin, (size_t)T, w));
   EB_TRY(dev_alloc(e, &e->d_bt, (size_t)c.max_seqs * c.max_pages_per_seq, w));
   EB_CUDA(cudaMemsetAsync(e->d_bt, 0xFF, (size_t)c.max_seqs * c.max_pages_per_seq * sizeof(int32_t), e->stream));
-  // staging: tokens, tok_slot, positions [T each]; slots, ctx_lens [S]; q_off [S+1]; patches 3*P (P <= all pages of
-  // newly admitted sequences: bounded by max_seqs*max_pages); two plans (items 4 words each + seq_part)
-  const size_t S = (size_t)c.max_seqs;
-  e->stage_words = 3 * (size_t)T + 3 * S + 1 + 3 * S * (size_t)c.max_pages_per_seq + 2 * (4 * (size_t)e->cap_items + S + 1) + 64;
+  // staging: tokens, tok_slot, positions [T each]; slots, ctx_lens [N], q_off [N+1] of the N attention entries; patches
+  // 3*P (P <= all pages of newly admitted sequences: bounded by max_seqs*max_pages); two plans (items 4 words each +
+  // seq_part)
+  const size_t S = (size_t)c.max_seqs, N = (size_t)e->cap_ent;
+  e->stage_words = 3 * (size_t)T + 3 * N + 1 + 3 * S * (size_t)c.max_pages_per_seq + 2 * (4 * (size_t)e->cap_items + N + 1) + 64;
   EB_CUDA(cudaMallocHost((void**)&e->h_stage, e->stage_words * sizeof(int32_t)));
   EB_TRY(dev_alloc(e, &e->d_stage, e->stage_words, w));
   EB_CUDA(cudaMallocHost((void**)&e->h_result, 2 * (size_t)T * sizeof(int32_t)));
@@ -925,6 +929,8 @@ int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_si
   e->kbH = (int)eb::cdiv(c.hidden, 128);
   e->kbI = (int)eb::cdiv(c.inter, 128);
   e->kbA = (int)eb::cdiv(e->hqd, 128);
+  // a ring of window pages has to hold a whole chunk besides the window: chunks stay short when rings are asked for
+  e->chunk_cap = std::max(c.max_q_len, (c.window_ring && c.window > 0) ? std::min(c.max_tokens, 256) : c.max_tokens);
   {
     const char* nccl = getenv("EIDOLA_B200_TP_NCCL");
     const char* og = getenv("EIDOLA_B200_TP_OGATHER");
@@ -943,7 +949,7 @@ int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_si
     }
     if ((rc = eb_sched_create(c.num_pages, c.page_size, c.max_seqs, c.max_pages_per_seq, c.seed, &e->sched)) != EB_OK) break;
     if ((rc = init_weights(e)) != EB_OK) break;
-    e->ring = (c.window_ring && c.window > 0) ? (c.window + c.max_q_len + c.page_size - 1) / c.page_size + 1 : 0;
+    e->ring = (c.window_ring && c.window > 0) ? (c.window + e->chunk_cap + c.page_size - 1) / c.page_size + 1 : 0;
     for (int l = 0; l < c.n_layers && rc == EB_OK; ++l) {
       const size_t cache_elems = (size_t)layer_pages(e, l) * 2 * e->hkv_l * c.page_size * c.head_dim;
       rc = dev_alloc(e, &e->layers[(size_t)l].cache, cache_elems, &e->kv_bytes);
@@ -1200,12 +1206,12 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
   int64_t T64 = 0;
   int max_q = 1;
   for (int i = 0; i < n_seqs; ++i) {
-    EB_REQUIRE(h_q_lens[i] >= 1 && h_q_lens[i] <= c.max_q_len, EB_ERR_ARG, "eb_engine_step: q_len %d of sequence %d outside 1..%d",
-               h_q_lens[i], i, c.max_q_len);
+    EB_REQUIRE(h_q_lens[i] >= 1 && h_q_lens[i] <= e->chunk_cap, EB_ERR_ARG, "eb_engine_step: q_len %d of sequence %d outside 1..%d",
+               h_q_lens[i], i, e->chunk_cap);
     for (int j = 0; j < i; ++j)
       EB_REQUIRE(h_slots[j] != h_slots[i], EB_ERR_ARG, "eb_engine_step: slot %d appears twice", h_slots[i]);
     T64 += h_q_lens[i];
-    max_q = std::max(max_q, h_q_lens[i]);
+    max_q = std::max(max_q, std::min(h_q_lens[i], c.max_q_len));  // longer runs are cut into attention entries of max_q_len
   }
   EB_REQUIRE(T64 <= c.max_tokens, EB_ERR_ARG, "eb_engine_step: %lld token rows exceed max_tokens %d", (long long)T64, c.max_tokens);
   const int T = (int)T64;
@@ -1262,14 +1268,32 @@ int32_t step_launch_body(eb_engine* e, const int32_t* h_slots, const int32_t* h_
   int32_t* s_tokens = take((size_t)T);
   int32_t* s_tok_slot = take((size_t)T);
   int32_t* s_pos = take((size_t)T);
-  int32_t* s_slots = take((size_t)n_seqs);
-  int32_t* s_ctx = take((size_t)n_seqs);
-  int32_t* s_qoff = take((size_t)n_seqs + 1);
   memcpy(s_tokens, h_tokens, (size_t)T * sizeof(int32_t));
-  memcpy(s_slots, h_slots, (size_t)n_seqs * sizeof(int32_t));
-  std::vector<int32_t> tok_seq((size_t)T);
+  std::vector<int32_t> tok_seq((size_t)T), seq_ctx((size_t)n_seqs), seq_qoff((size_t)n_seqs + 1);
   int32_t nt = 0;
-  EB_TRY(eb_sched_pack(e->sched, h_slots, h_q_lens, n_seqs, s_qoff, s_ctx, tok_seq.data(), s_tok_slot, s_pos, &nt));
+  EB_TRY(eb_sched_pack(e->sched, h_slots, h_q_lens, n_seqs, seq_qoff.data(), seq_ctx.data(), tok_seq.data(), s_tok_slot, s_pos, &nt));
+  // Attention entries: a sequence's new tokens in runs of at most max_q_len.  Decode and verify steps have one entry per
+  // sequence; a prefill chunk has several on the same block-table row, entry j seeing the context up to its own last
+  // token (every K and V of the step is in the cache before any attention kernel of a layer runs).
+  int n_ent = 0;
+  for (int i = 0; i < n_seqs; ++i) n_ent += (h_q_lens[i] + c.max_q_len - 1) / c.max_q_len;
+  EB_REQUIRE(n_ent <= e->cap_ent, EB_ERR_NOMEM, "eb_engine_step: %d attention entries exceed the %d planned for", n_ent, e->cap_ent);
+  int32_t* s_slots = take((size_t)n_ent);
+  int32_t* s_ctx = take((size_t)n_ent);
+  int32_t* s_qoff = take((size_t)n_ent + 1);
+  std::vector<int32_t> ent_q((size_t)n_ent);
+  {
+    int k = 0;
+    for (int i = 0; i < n_seqs; ++i)
+      for (int b = 0; b < h_q_lens[i]; b += c.max_q_len, ++k) {
+        const int len = std::min(c.max_q_len, h_q_lens[i] - b);
+        s_slots[k] = h_slots[i];
+        s_qoff[k] = seq_qoff[(size_t)i] + b;
+        s_ctx[k] = seq_ctx[(size_t)i] - h_q_lens[i] + b + len;
+        ent_q[(size_t)k] = len;
+      }
+    s_qoff[n_ent] = T;
+  }
   // block-table patches
   const int32_t* tables = nullptr;
   int32_t stride = 0;
@@ -1278,7 +1302,7 @@ int32_t step_launch_body(eb_engine* e, const int32_t* h_slots, const int32_t* h_
   int n_patch = 0;
   for (int i = 0; i < n_seqs; ++i) {
     const int slot = h_slots[i];
-    const int pages = (s_ctx[i] + c.page_size - 1) / c.page_size;
+    const int pages = (seq_ctx[(size_t)i] + c.page_size - 1) / c.page_size;
     for (int p = e->uploaded_pages[(size_t)slot]; p < pages; ++p) {
       s_patch[3 * n_patch] = slot;
       s_patch[3 * n_patch + 1] = p;
@@ -1303,10 +1327,10 @@ int32_t step_launch_body(eb_engine* e, const int32_t* h_slots, const int32_t* h_
     eb_attn_item* it = reinterpret_cast<eb_attn_item*>(hs + off);
     off += 4 * (size_t)e->cap_items;
     part_off[k] = off;
-    int32_t* sp = take((size_t)n_seqs + 1);
+    int32_t* sp = take((size_t)n_ent + 1);
     // the chunk size follows the kernel the attention entry point picks for this step's shapes
     const int32_t plan_sms = eb_attn_plan_sm_count(e->sm_count, max_q, e->hq_l, e->hkv_l, k ? c.window : 0);
-    EB_TRY(eb_attn_plan(s_ctx, h_q_lens, n_seqs, c.page_size, k ? c.window : 0, plan_sms, 0, ppi, it, e->cap_items,
+    EB_TRY(eb_attn_plan(s_ctx, ent_q.data(), n_ent, c.page_size, k ? c.window : 0, plan_sms, 0, ppi, it, e->cap_items,
                         &plans[k].n_items, sp, &plans[k].n_parts));
   }
   EB_REQUIRE(off <= e->stage_words, EB_ERR_NOMEM, "eb_engine_step: staging block overflow (%zu > %zu words)", off, e->stage_words);
@@ -1322,7 +1346,7 @@ int32_t step_launch_body(eb_engine* e, const int32_t* h_slots, const int32_t* h_
   const eb_attn_item* d_items[2] = {reinterpret_cast<const eb_attn_item*>(ds + items_off[0]),
                                     reinterpret_cast<const eb_attn_item*>(ds + items_off[1])};
   const int32_t* d_seq_part[2] = {ds + part_off[0], ds + part_off[1]};
-  int32_t rc = run_layers(e, T, n_seqs, ds + (s_tokens - hs), ds + (s_tok_slot - hs), ds + (s_pos - hs), ds + (s_slots - hs),
+  int32_t rc = run_layers(e, T, n_ent, ds + (s_tokens - hs), ds + (s_tok_slot - hs), ds + (s_pos - hs), ds + (s_slots - hs),
                           ds + (s_qoff - hs), ds + (s_ctx - hs), d_items, d_seq_part, plans, max_q);
   if (rc != EB_OK) return rc;
   e->launches += (n_patch > 0 ? 1 : 0);
@@ -1389,8 +1413,8 @@ int32_t eb_engine_prefill(eb_engine* e, const int32_t* h_slots, const int32_t* h
       const int i = (start + k) % n_seqs;
       const int32_t rem = h_n_tokens[i] - done[(size_t)i];
       if (rem <= 0) continue;
-      const int32_t q = std::min(rem, c.max_q_len);
-      if (rows + q > c.max_tokens) {
+      const int32_t q = std::min(std::min(rem, e->chunk_cap), c.max_tokens - rows);  // what is left of the step, if short
+      if (q < rem && q < std::min(rem, c.max_q_len)) {  // less room than one attention entry: the next step
         skipped = true;
         continue;
       }
@@ -1419,6 +1443,12 @@ int32_t eb_engine_prefill(eb_engine* e, const int32_t* h_slots, const int32_t* h
   }
   if (steps_run) *steps_run = steps;
   if (device_ms) *device_ms = ms;
+  return EB_OK;
+}
+
+int32_t eb_engine_chunk_tokens(const eb_engine* e, int32_t* tokens) {
+  EB_REQUIRE(e && tokens, EB_ERR_ARG, "eb_engine_chunk_tokens: null");
+  *tokens = e->chunk_cap;
   return EB_OK;
 }
 

@@ -406,6 +406,12 @@ class Engine:
         self._last_T = 0
         return nxt, mg, int(steps.value), float(ms.value)
 
+    def chunk_tokens(self) -> int:
+        """Most new tokens one sequence may bring to a step (eb_engine_chunk_tokens)."""
+        n = c_i32(0)
+        call("eb_engine_chunk_tokens", self._h, C.byref(n))
+        return int(n.value)
+
     def step_launch(self, slots, q_lens, tokens) -> None:
         slots, q_lens, tokens = _i32(slots), _i32(q_lens), _i32(tokens)
         self._last_T = int(q_lens.sum())

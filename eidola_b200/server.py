@@ -277,7 +277,7 @@ def build_engine(args):
         "20b": dict(n_layers=24, hidden=2880, n_q_heads=64, n_kv_heads=8, n_experts=32, inter=2880, vocab=201088),
     }[args.shape]
     cfg = make_config(window=128, top_k=4, num_pages=args.seqs * pages_per_seq, max_seqs=args.seqs, max_pages_per_seq=pages_per_seq,
-                      max_tokens=args.seqs * 6, max_q_len=6, seed=args.seed, **shapes)
+                      max_tokens=max(args.seqs * 6, min(ctx, 2048)), max_q_len=6, seed=args.seed, **shapes)
     eng = eb.Engine(cfg)
     if args.model and args.model.endswith(".gguf") and not args.random_init:
         eng.load_gguf(args.model)

@@ -431,13 +431,15 @@ typedef struct eb_config {
   int32_t n_experts, top_k, inter, vocab;
   int32_t page_size, num_pages, max_seqs, max_pages_per_seq;
   int32_t max_tokens;   /* token rows per step (sum of q_len) */
-  int32_t max_q_len;    /* new tokens per sequence per step: 1 = decode, k+1 = verify k drafts */
+  int32_t max_q_len;    /* new tokens per sequence per decode / verify step: 1 = decode, k+1 = verify k drafts; also the
+                           run of tokens one attention work entry covers (prefill chunks are cut into such runs) */
   float rope_theta, rms_eps, init_std;
   uint64_t seed;        /* weights are a pure function of (shape, seed) */
   int32_t debug;        /* bit 0: keep per-layer routing indices / hidden states readable and allow teacher forcing;
                            bit 1: time attention, GEMM and LM-head calls of each step with CUDA events */
-  int32_t window_ring;  /* 1: sliding-window layers keep only a ring of ceil((window + max_q_len)/page_size) + 1 pages
-                           per sequence (logical page p lives in ring page p mod ring) instead of the whole context */
+  int32_t window_ring;  /* 1: sliding-window layers keep only a ring of ceil((window + chunk)/page_size) + 1 pages per
+                           sequence (logical page p lives in ring page p mod ring) instead of the whole context; chunk =
+                           eb_engine_chunk_tokens, which a ring holds down to min(max_tokens, 256) */
 } eb_config;
 
 typedef struct eb_engine eb_engine;
@@ -595,20 +597,27 @@ int32_t eb_engine_sched(eb_engine* e, eb_sched** sched); /* borrowed; lives as l
  * One step for n_seqs sequences: sequence i appends q_lens[i] tokens (h_tokens, flat, in sequence order), every
  * layer runs, and h_next[row] receives the greedy token after each of the T = sum(q_lens) rows (h_margin: top-1
  * minus top-2 logit, may be NULL).  Host buffers; the call returns after the results have arrived.
+ * q_lens[i] may be anything from 1 to eb_engine_chunk_tokens (T <= max_tokens): runs longer than max_q_len (prefill
+ * chunks) are cut into attention work entries of max_q_len tokens on the same block-table row, each causal among its own
+ * tokens and seeing everything before it, so a whole prompt can go through in one step.
  */
 int32_t eb_engine_step(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
                        const int32_t* h_tokens, int32_t* h_next, float* h_margin);
 /*
  * Prefill: run the prompts of n_seqs admitted sequences (h_n_tokens[i] tokens each, flat in h_tokens in sequence order)
- * through every layer, so that their K and V are in the paged cache, in chunks of up to max_q_len tokens per sequence
- * and max_tokens rows per step -- the same kernels, pages and block tables as decode and draft verification (a chunk
- * is causal among its own tokens and sees everything before it).  h_next[i] / h_margin[i] receive the greedy token and
+ * through every layer, so that their K and V are in the paged cache, in chunks of up to eb_engine_chunk_tokens tokens
+ * per sequence and max_tokens rows per step (sequences in order, each taking what it still needs or what is left of
+ * the step) -- the same kernels, pages and block tables as decode and draft verification (a chunk is causal among its
+ * own tokens and sees everything before it).  h_next[i] / h_margin[i] receive the greedy token and
  * top-2 margin after the LAST prompt token of sequence i: the first generated token.  What the reference's client
  * sends as `messages` and its engine turns into a prompt (crates/eidola-app-core/src/lib.rs:10812-10825) ends up here
  * as token ids.  steps_run / device_ms (may be NULL): steps taken and their summed device time.
  */
 int32_t eb_engine_prefill(eb_engine* e, const int32_t* h_slots, const int32_t* h_n_tokens, int32_t n_seqs, const int32_t* h_tokens,
                           int32_t* h_next, float* h_margin, int32_t* steps_run, float* device_ms);
+/* Most new tokens one sequence may bring to a step: max_tokens, or min(max_tokens, 256) with window_ring (never less than
+ * max_q_len). */
+int32_t eb_engine_chunk_tokens(const eb_engine* e, int32_t* tokens);
 /* The same split in two so a caller can overlap host work: launch, then wait for the results. */
 int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
                               const int32_t* h_tokens);
