@@ -17,6 +17,7 @@
 
 #include <algorithm>
 #include <new>
+#include <utility>
 #include <vector>
 
 #include "common.h"
@@ -120,6 +121,10 @@ struct eb_engine {
   size_t stage_words = 0;
   int32_t* h_result = nullptr;  // pinned: next[T] then margin[T]
   int32_t cap_items = 0;
+  // prefill: the LM head runs only over the 128-row blocks that hold these rows (the last prompt token of a sequence that
+  // finishes in the step); the other rows of the step's results are then undefined
+  bool head_rows_on = false;
+  std::vector<int32_t> head_rows;
   int32_t chunk_cap = 0;  // most new tokens one sequence may bring to a step (a prefill chunk); see eb_engine_chunk_tokens
   int32_t cap_ent = 0;    // most attention entries of a step: a sequence's new tokens in runs of at most max_q_len
   // debug
@@ -835,24 +840,49 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
     h8_ready = false;
   }
   if (!h8_ready) EB_TRY(eb_quant_act_block128(e->h, H, T, H, nullptr, 1, e->h8, e->sh, st));
+  // rows the head runs over: all of them, or (prefill) the 128-row scale blocks that hold a wanted row, as ranges
+  std::vector<std::pair<int, int>> ranges;  // (first row, rows)
+  if (!e->head_rows_on) {
+    ranges.emplace_back(0, T);
+  } else {
+    std::vector<int32_t> rows = e->head_rows;
+    std::sort(rows.begin(), rows.end());
+    for (int32_t r : rows) {
+      if (r < 0 || r >= T) continue;
+      const int b0 = r / 128 * 128, b1 = std::min(T, b0 + 128);
+      if (!ranges.empty() && ranges.back().first + ranges.back().second >= b0)
+        ranges.back().second = std::max(ranges.back().second, b1 - ranges.back().first);
+      else
+        ranges.emplace_back(b0, b1 - b0);
+    }
+  }
   mark(4);
   if (!tp) {
-    EB_TRY(dense(e->h8, e->sh, e->lm, c.vocab, H, e->logits, nullptr));
+    for (const auto& rg : ranges) {
+      EB_TRY(dense(e->h8 + (size_t)rg.first * H, e->sh + (size_t)(rg.first / 128) * e->kbH, e->lm, c.vocab, H,
+                   e->logits + (size_t)rg.first * c.vocab, nullptr, 0, 0, rg.second));
+      EB_TRY(eb_argmax(e->logits + (size_t)rg.first * c.vocab, rg.second, c.vocab, c.vocab, e->d_next + rg.first, e->d_margin + rg.first, st));
+    }
     mark(-1);
-    EB_TRY(eb_argmax(e->logits, T, c.vocab, c.vocab, e->d_next, e->d_margin, st));
   } else {
     // vocabulary-parallel head: logits of this rank's rows only, one candidate per token and rank, merged everywhere
-    EB_TRY(dense(e->h8, e->sh, e->lm, e->v1 - e->v0, H, e->logits + e->v0, nullptr, c.vocab));
-    mark(-1);
     const int64_t cap = c.max_tokens;
-    EB_TRY(eb_argmax_partial(e->logits + e->v0, T, e->v1 - e->v0, c.vocab, e->v0, e->cand + (size_t)e->tp_rank * cap * 4, st));
-    void* cb[1] = {e->cand};
-    const int64_t csz[1] = {cap * 4 * (int64_t)sizeof(float)};
-    const int64_t cvalid[1] = {(int64_t)T * 4 * (int64_t)sizeof(float)};
-    mark(5);
-    EB_TRY(gather(1, cb, csz, cvalid));
+    for (const auto& rg : ranges) {
+      EB_TRY(dense(e->h8 + (size_t)rg.first * H, e->sh + (size_t)(rg.first / 128) * e->kbH, e->lm, e->v1 - e->v0, H,
+                   e->logits + (size_t)rg.first * c.vocab + e->v0, nullptr, c.vocab, 0, rg.second));
+      EB_TRY(eb_argmax_partial(e->logits + (size_t)rg.first * c.vocab + e->v0, rg.second, e->v1 - e->v0, c.vocab, e->v0,
+                               e->cand + ((size_t)e->tp_rank * cap + rg.first) * 4, st));
+    }
     mark(-1);
-    EB_TRY(eb_argmax_merge(e->cand, e->tp_size, cap, T, e->d_next, e->d_margin, st));
+    if (!ranges.empty()) {  // every rank has the same ranges: all of them meet the exchange or none does
+      void* cb[1] = {e->cand};
+      const int64_t csz[1] = {cap * 4 * (int64_t)sizeof(float)};
+      const int64_t cvalid[1] = {(int64_t)T * 4 * (int64_t)sizeof(float)};
+      mark(5);
+      EB_TRY(gather(1, cb, csz, cvalid));
+      mark(-1);
+      EB_TRY(eb_argmax_merge(e->cand, e->tp_size, cap, T, e->d_next, e->d_margin, st));
+    }
     n += 2;
   }
   n += 3;
@@ -1425,7 +1455,19 @@ int32_t eb_engine_prefill(eb_engine* e, const int32_t* h_slots, const int32_t* h
       rows += q;
     }
     EB_REQUIRE(rows > 0, EB_ERR_STATE, "eb_engine_prefill: no sequence fits a step of %d token rows", c.max_tokens);
-    EB_TRY(eb_engine_step(e, b_slots.data(), b_q.data(), (int32_t)b_slots.size(), b_tok.data(), next.data(), margin.data()));
+    // only the row after a prompt's last token is read below: the LM head skips the 128-row blocks that hold none
+    e->head_rows.clear();
+    {
+      int32_t row = 0;
+      for (size_t k = 0; k < b_seq.size(); ++k) {
+        row += b_q[k];
+        if (done[(size_t)b_seq[k]] + b_q[k] == h_n_tokens[b_seq[k]]) e->head_rows.push_back(row - 1);
+      }
+    }
+    e->head_rows_on = true;
+    const int32_t rc_step = eb_engine_step(e, b_slots.data(), b_q.data(), (int32_t)b_slots.size(), b_tok.data(), next.data(), margin.data());
+    e->head_rows_on = false;
+    if (rc_step != EB_OK) return rc_step;
     ms += e->last_ms;
     ++steps;
     int32_t row = 0;

@@ -13,7 +13,7 @@ import pytest
 from oracle import binding as orc
 from oracle import sched as osched
 from tests.decoder_cases import compare_forced_step, free_running_error
-from tests.tp_worker import CONTEXTS, run_steps, tp_config, vocab_slice
+from tests.tp_worker import CONTEXTS, run_prefill, run_steps, tp_config, vocab_slice
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
@@ -130,3 +130,32 @@ def test_tp_engine_matches_oracle_and_single_gpu(gpu, tmp_path, name, world, mod
                                      {"logits": single[s]["logits"], "hidden": list(single[s]["hidden"])})
         print(f"{name} tp={world} {mode} vs single GPU step {s}: logits err {dl.max():.4f} hidden rel {rel:.4f}")
         assert rel <= 0.15
+
+
+@pytest.mark.parametrize("world,mode", [(2, "peer"), (2, "peer_gather"), (4, "peer")])
+def test_tp_prefill_matches_single_gpu(gpu, tmp_path, world, mode):
+    """Whole prompts in steps of 256 rows (attention entries of max_q_len tokens, the LM head only on the row blocks that
+    end a prompt) on `world` ranks: the ranks agree bit for bit, and the first tokens and the next decode step's logits are
+    those of the single-GPU engine to rounding."""
+    import eidola_b200 as eb
+    if eb.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ranks = _spawn(world, "tp_mid+prefill", tmp_path, None, MODES[mode])
+    cfg = tp_config("tp_mid")
+    cfg.max_tokens = 256
+    eng = eb.Engine(cfg)
+    single = run_prefill(eng)
+    assert all(int(r["status"][0]) == 0 for r in ranks)
+    for r in ranks[1:]:
+        assert np.array_equal(r["first"], ranks[0]["first"]) and np.array_equal(r["next"], ranks[0]["next"])
+    assert int(ranks[0]["steps"][0]) == int(single["steps"][0]) == 2  # 502 prompt tokens, 256 rows per step
+    clear = single["first_margin"] > 0.3
+    assert np.array_equal(ranks[0]["first"][clear], single["first"][clear])
+    logits = _merged_logits(ranks, "logits", cfg.vocab)
+    lf = (logits.astype(np.uint32) << 16).view(np.float32)
+    sf = (single["logits"].astype(np.uint32) << 16).view(np.float32)
+    rel = float(np.linalg.norm(lf - sf) / np.linalg.norm(sf))
+    print(f"tp={world} {mode} prefill: first tokens {ranks[0]['first'].tolist()} vs {single['first'].tolist()} "
+          f"(margins {np.round(single['first_margin'], 3).tolist()}), "
+          f"decode-step logits rel L2 vs single GPU {rel:.4f}")
+    assert rel <= 0.15

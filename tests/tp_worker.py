@@ -65,6 +65,25 @@ def run_steps(eng, name, force=None, rank=0, world=1):
     return slots, out
 
 
+PREFILL_PROMPTS = [7, 133, 12, 50, 300]
+
+
+def run_prefill(eng, rank=0, world=1):
+    """Whole prompts through eb_engine_prefill (steps of max_tokens rows), then one decode step on seeded tokens."""
+    cfg = eng.cfg
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(0, cfg.vocab, size=n).astype(np.int32) for n in PREFILL_PROMPTS]
+    slots = [eng.admit(0) for _ in prompts]
+    first, margin, steps, _ = eng.prefill(slots, prompts)
+    nxt, mg = eng.step(slots, [1] * len(slots), rng.integers(0, cfg.vocab, size=len(slots)).astype(np.int32))  # the same everywhere
+    logits = eng.read_logits()
+    if world > 1:
+        v0, v1 = vocab_slice(cfg.vocab, rank, world)
+        logits[:, :v0] = 0
+        logits[:, v1:] = 0
+    return {"first": first, "first_margin": margin, "steps": np.array([steps], np.int32), "next": nxt, "margin": mg, "logits": logits}
+
+
 def main():
     rank, world, id_file, out_file, name = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4], sys.argv[5]
     force_file = sys.argv[6] if len(sys.argv) > 6 else None
@@ -84,6 +103,16 @@ def main():
             time.sleep(0.05)
         uid = Path(id_file).read_bytes()
     comm = eb.Comm(uid, rank, world)
+    if name.endswith("+prefill"):
+        cfg = tp_config(name[:-len("+prefill")])
+        cfg.max_tokens = 256
+        eng = eb.Engine(cfg, rank, world, comm)
+        flat = run_prefill(eng, rank, world)
+        flat["status"] = np.array([eb.status_read()], np.int32)
+        np.savez(out_file, **flat)
+        eng.close()
+        comm.close()
+        return
     cfg = tp_config(name)
     eng = eb.Engine(cfg, rank, world, comm)
     eng.kv_fill_synth()
