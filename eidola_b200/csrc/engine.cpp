@@ -125,6 +125,11 @@ struct eb_engine {
   // finishes in the step); the other rows of the step's results are then undefined
   bool head_rows_on = false;
   std::vector<int32_t> head_rows;
+  // per slot: log2(e) / temperature (0: greedy), top_p in units of 2^-24, seed of the counter-based random numbers
+  std::vector<float> samp_scale;
+  std::vector<uint32_t> samp_q24;
+  std::vector<uint64_t> samp_seed;
+  const int32_t* d_samp = nullptr;  // this step's per-row {scale, top_p, rand32} [3][T] in the staging block, or null
   int32_t chunk_cap = 0;  // most new tokens one sequence may bring to a step (a prefill chunk); see eb_engine_chunk_tokens
   int32_t cap_ent = 0;    // most attention entries of a step: a sequence's new tokens in runs of at most max_q_len
   // debug
@@ -382,11 +387,11 @@ int32_t init_work(eb_engine* e) {
   EB_TRY(dev_alloc(e, &e->d_margin, (size_t)T, w));
   EB_TRY(dev_alloc(e, &e->d_bt, (size_t)c.max_seqs * c.max_pages_per_seq, w));
   EB_CUDA(cudaMemsetAsync(e->d_bt, 0xFF, (size_t)c.max_seqs * c.max_pages_per_seq * sizeof(int32_t), e->stream));
-  // staging: tokens, tok_slot, positions [T each]; slots, ctx_lens [N], q_off [N+1] of the N attention entries; patches
+  // staging: tokens, tok_slot, positions, and the sampler's scale, top_p, random number [T each]; slots, ctx_lens [N], q_off [N+1] of the N attention entries; patches
   // 3*P (P <= all pages of newly admitted sequences: bounded by max_seqs*max_pages); two plans (items 4 words each +
   // seq_part)
   const size_t S = (size_t)c.max_seqs, N = (size_t)e->cap_ent;
-  e->stage_words = 3 * (size_t)T + 3 * N + 1 + 3 * S * (size_t)c.max_pages_per_seq + 2 * (4 * (size_t)e->cap_items + N + 1) + 64;
+  e->stage_words = 6 * (size_t)T + 3 * N + 1 + 3 * S * (size_t)c.max_pages_per_seq + 2 * (4 * (size_t)e->cap_items + N + 1) + 64;
   EB_CUDA(cudaMallocHost((void**)&e->h_stage, e->stage_words * sizeof(int32_t)));
   EB_TRY(dev_alloc(e, &e->d_stage, e->stage_words, w));
   EB_CUDA(cudaMallocHost((void**)&e->h_result, 2 * (size_t)T * sizeof(int32_t)));
@@ -862,6 +867,11 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
       EB_TRY(dense(e->h8 + (size_t)rg.first * H, e->sh + (size_t)(rg.first / 128) * e->kbH, e->lm, c.vocab, H,
                    e->logits + (size_t)rg.first * c.vocab, nullptr, 0, 0, rg.second));
       EB_TRY(eb_argmax(e->logits + (size_t)rg.first * c.vocab, rg.second, c.vocab, c.vocab, e->d_next + rg.first, e->d_margin + rg.first, st));
+      if (e->d_samp)  // rows of sequences with a temperature: the drawn token replaces the greedy one
+        EB_TRY(eb_sample_top_p(e->logits + (size_t)rg.first * c.vocab, rg.second, c.vocab, c.vocab,
+                               reinterpret_cast<const float*>(e->d_samp) + rg.first,
+                               reinterpret_cast<const uint32_t*>(e->d_samp) + T + rg.first,
+                               reinterpret_cast<const uint32_t*>(e->d_samp) + 2 * (size_t)T + rg.first, e->d_next + rg.first, st));
     }
     mark(-1);
   } else {
@@ -970,6 +980,9 @@ int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_si
   }
   e->layers.resize((size_t)c.n_layers);
   e->uploaded_pages.assign((size_t)c.max_seqs, 0);
+  e->samp_scale.assign((size_t)c.max_seqs, 0.f);
+  e->samp_q24.assign((size_t)c.max_seqs, 1u << 24);
+  e->samp_seed.assign((size_t)c.max_seqs, 0);
   int32_t rc = EB_OK;
   do {
     if (cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking) != cudaSuccess ||
@@ -1175,6 +1188,7 @@ int32_t eb_engine_seq_admit(eb_engine* e, int32_t context_len, int32_t* slot) {
   EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_seq_admit: a step is in flight");
   EB_TRY(eb_sched_admit(e->sched, context_len, slot));
   e->uploaded_pages[(size_t)*slot] = 0;
+  e->samp_scale[(size_t)*slot] = 0.f;  // a new sequence decodes greedily until eb_engine_seq_sampling says otherwise
   return EB_OK;
 }
 
@@ -1185,12 +1199,30 @@ int32_t eb_engine_seq_admit_evicting(eb_engine* e, int32_t context_len, int32_t*
   EB_TRY(eb_sched_admit_evicting(e->sched, context_len, e->tick, slot, h_evicted, cap, n_evicted));
   for (int32_t i = 0; i < *n_evicted; ++i) e->uploaded_pages[(size_t)h_evicted[i]] = 0;
   e->uploaded_pages[(size_t)*slot] = 0;
+  e->samp_scale[(size_t)*slot] = 0.f;
   return EB_OK;
 }
 
 int32_t eb_engine_seq_pin(eb_engine* e, int32_t slot, int32_t pinned) {
   EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_seq_pin: null");
   return eb_sched_set_flags(e->sched, slot, pinned ? 1 : 0, -1);
+}
+
+int32_t eb_engine_seq_sampling(eb_engine* e, int32_t slot, float temperature, float top_p, uint64_t seed) {
+  EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_seq_sampling: null");
+  EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_seq_sampling: a step is in flight");
+  EB_REQUIRE(e->tp_size == 1 || !(temperature > 0.f), EB_ERR_UNSUPPORTED,
+             "eb_engine_seq_sampling: the sampler needs whole logit rows; under tensor parallelism the LM head is split over the vocabulary");
+  int32_t len = 0;
+  EB_TRY(eb_sched_seq_len(e->sched, slot, &len));  // refuses a slot that is not live
+  EB_REQUIRE(!(temperature > 0.f) || (temperature >= 1e-3f && temperature <= 100.f), EB_ERR_ARG,
+             "eb_engine_seq_sampling: temperature %g outside [0.001, 100]", (double)temperature);
+  EB_REQUIRE(top_p == top_p, EB_ERR_ARG, "eb_engine_seq_sampling: top_p is NaN");
+  e->samp_scale[(size_t)slot] = temperature > 0.f ? 1.4426950408889634f / temperature : 0.f;
+  const float p = top_p < 0.f ? 0.f : top_p > 1.f ? 1.f : top_p;
+  e->samp_q24[(size_t)slot] = (uint32_t)((double)p * 16777216.0);
+  e->samp_seed[(size_t)slot] = seed;
+  return EB_OK;
 }
 
 int32_t eb_engine_seq_release(eb_engine* e, int32_t slot) {
@@ -1298,10 +1330,24 @@ int32_t step_launch_body(eb_engine* e, const int32_t* h_slots, const int32_t* h_
   int32_t* s_tokens = take((size_t)T);
   int32_t* s_tok_slot = take((size_t)T);
   int32_t* s_pos = take((size_t)T);
+  bool sampling = false;
+  for (int i = 0; i < n_seqs; ++i) sampling = sampling || e->samp_scale[(size_t)h_slots[i]] > 0.f;
+  int32_t* s_samp = sampling ? take(3 * (size_t)T) : nullptr;
   memcpy(s_tokens, h_tokens, (size_t)T * sizeof(int32_t));
   std::vector<int32_t> tok_seq((size_t)T), seq_ctx((size_t)n_seqs), seq_qoff((size_t)n_seqs + 1);
   int32_t nt = 0;
   EB_TRY(eb_sched_pack(e->sched, h_slots, h_q_lens, n_seqs, seq_qoff.data(), seq_ctx.data(), tok_seq.data(), s_tok_slot, s_pos, &nt));
+  // the sampler's per-row arguments, when a sequence of the step is not greedy: the random number of a row is a function
+  // of the sequence's seed and the absolute position of the token drawn, whatever else shares the step
+  if (sampling) {
+    for (int t = 0; t < T; ++t) {
+      const size_t slot = (size_t)s_tok_slot[t];
+      memcpy(&s_samp[t], &e->samp_scale[slot], sizeof(float));
+      s_samp[(size_t)T + t] = (int32_t)e->samp_q24[slot];
+      s_samp[2 * (size_t)T + t] = (int32_t)eb_sample_rand32(e->samp_seed[slot], (uint64_t)s_pos[t] + 1);
+    }
+  }
+  e->d_samp = sampling ? e->d_stage + (s_samp - hs) : nullptr;
   // Attention entries: a sequence's new tokens in runs of at most max_q_len.  Decode and verify steps have one entry per
   // sequence; a prefill chunk has several on the same block-table row, entry j seeing the context up to its own last
   // token (every K and V of the step is in the cache before any attention kernel of a layer runs).

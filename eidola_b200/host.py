@@ -406,6 +406,11 @@ class Engine:
         self._last_T = 0
         return nxt, mg, int(steps.value), float(ms.value)
 
+    def sampling(self, slot: int, temperature: float, top_p: float = 1.0, seed: int = 0) -> None:
+        """eb_engine_seq_sampling: temperature > 0 draws this sequence's tokens (nucleus top_p, counter-based random
+        numbers from `seed`); temperature <= 0 returns it to greedy decoding."""
+        call("eb_engine_seq_sampling", self._h, c_i32(slot), c_f32(temperature), c_f32(top_p), C.c_uint64(seed))
+
     def chunk_tokens(self) -> int:
         """Most new tokens one sequence may bring to a step (eb_engine_chunk_tokens)."""
         n = c_i32(0)

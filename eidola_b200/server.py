@@ -18,8 +18,9 @@ least recently used first, when the page pool is full), their prompts are prefil
 decodes one token for every live sequence.  HTTP threads only enqueue requests and drain per-request token queues.
 
 What this is NOT: the reference contains no tokenizer, chat template or sampler (they live inside the third-party
-engine), and neither does this library.  The tokenizer here is the identity on UTF-8 bytes (ids 0..255) with a plain
-`<|role|>` template, and decoding is greedy; a checkpoint with its own vocabulary needs its tokenizer in front.  With
+engine); this library has the sampler and no real tokenizer.  The tokenizer here is the identity on UTF-8 bytes (ids 0..255) with a plain
+`<|role|>` template; a checkpoint with its own vocabulary needs its tokenizer in front.  Decoding is greedy unless
+the request carries `temperature` > 0 (then `top_p` and `seed` apply: eb_engine_seq_sampling, drawn on the device).  With
 the random-init weights the replies are noise -- the process contract, the batching and the timings are what is real.
 """
 from __future__ import annotations
@@ -60,8 +61,9 @@ class ByteTokenizer:
 
 
 class Request:
-    def __init__(self, prompt_ids, max_tokens):
+    def __init__(self, prompt_ids, max_tokens, temperature=0.0, top_p=1.0, seed=0):
         self.prompt_ids, self.max_tokens = prompt_ids, max_tokens
+        self.temperature, self.top_p, self.seed = temperature, top_p, seed  # temperature 0: greedy
         self.out: "queue.Queue[tuple[str, object]]" = queue.Queue()  # ("token", id) ... ("done", usage) | ("error", message)
         self.slot = None
         self.generated = 0
@@ -103,6 +105,8 @@ class EngineLoop(threading.Thread):
                 req.out.put(("error", "no room for another sequence: %s" % e))
                 continue
             self.stats["evicted"] += len(evicted)
+            if req.temperature > 0:  # from the first generated token on (the prefill step draws it)
+                self.engine.sampling(slot, req.temperature, req.top_p, req.seed)
             req.slot = slot
             fresh.append(req)
         if fresh:
@@ -163,6 +167,9 @@ class EngineAdapter:
     def step(self, slots, q_lens, tokens):
         return self.eng.step(slots, q_lens, tokens)
 
+    def sampling(self, slot, temperature, top_p, seed):
+        self.eng.sampling(slot, temperature, top_p, seed)
+
     def release(self, slot):
         self.eng.release(slot)
 
@@ -209,7 +216,17 @@ def make_handler(loop: EngineLoop, alias: str):
             max_tokens = int(body.get("max_completion_tokens") or body.get("max_tokens") or 256)
             stream = bool(body.get("stream"))
             include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
-            req = Request(ByteTokenizer.template(messages), max(1, max_tokens))
+            # `temperature` (0..2) and `top_p` as the reference server's request type has them
+            # (crates/eidola-server/src/types.rs:24-30); absent or 0: greedy.  `seed` makes a sampled reply repeatable.
+            try:
+                temperature = float(body.get("temperature") or 0.0)
+                top_p = float(body["top_p"]) if body.get("top_p") is not None else 1.0
+                seed = int(body["seed"]) & (2**64 - 1) if body.get("seed") is not None else int(time.time_ns()) & (2**64 - 1)
+                assert 0.0 <= temperature <= 2.0 and 0.0 <= top_p <= 1.0
+            except Exception:
+                return self._json(400, {"error": {"message": "`temperature` must lie in [0, 2], `top_p` in [0, 1], `seed` be an integer",
+                                                  "type": "invalid_request_error", "code": 400}})
+            req = Request(ByteTokenizer.template(messages), max(1, max_tokens), temperature, top_p, seed)
             loop.submit(req)
             rid, created = "chatcmpl-%x" % id(req), int(time.time())
             base = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": body.get("model") or alias}

@@ -419,6 +419,20 @@ int32_t eb_argmax_partial(const void* d_logits, int32_t T, int64_t V, int64_t ld
 int32_t eb_argmax_merge(const float* d_cand, int32_t n_parts, int64_t part_stride, int32_t T, int32_t* d_tok, float* d_margin,
                         void* stream);
 
+/* Temperature / nucleus (top-p) sampling over bf16 logits [T][ld], one token per row, for rows whose d_scale is > 0
+ * (the others are left alone: a greedy row keeps what eb_argmax wrote to d_tok).  The reference server's request type
+ * carries `temperature` and `top_p` (crates/eidola-server/src/types.rs:24-30) and forwards them to a remote engine; this
+ * is what an engine behind that boundary does with them.  Per row: d_scale = log2(e) / temperature as fp32;
+ * d_top_p_q24 = top_p in units of 2^-24 (>= 2^24: the whole vocabulary); d_rand32 = one uniform 32-bit number
+ * (eb_sample_rand32(seed, position) gives a counter-based one).  The token is a pure function of those and the logits:
+ * weights W_v = trunc(2^31 * 2^((x_v - max) * scale)) from separately rounded fp32 operations, the nucleus = every
+ * token whose logit is at least the largest threshold with tail mass >= max(1, sum(W) * top_p), and the token = the
+ * first one, in id order, whose running nucleus mass exceeds (mass * rand32) >> 32 -- integer arithmetic throughout, so
+ * the CPU checker reproduces it bit for bit.  Rows without a finite maximum are left alone. */
+int32_t eb_sample_top_p(const void* d_logits, int32_t T, int64_t V, int64_t ld, const float* d_scale, const uint32_t* d_top_p_q24,
+                        const uint32_t* d_rand32, int32_t* d_tok, void* stream);
+uint32_t eb_sample_rand32(uint64_t seed, uint64_t counter); /* host: splitmix64 of (seed, counter), upper half */
+
 /* ---- engine: the whole decode step ------------------------------------------------------------
  * What an in-process implementation of the reference's engine boundary would drive once per generated token:
  * the reference client posts to `llama-server` and reads tokens back as SSE chunks
@@ -618,6 +632,13 @@ int32_t eb_engine_prefill(eb_engine* e, const int32_t* h_slots, const int32_t* h
 /* Most new tokens one sequence may bring to a step: max_tokens, or min(max_tokens, 256) with window_ring (never less than
  * max_q_len). */
 int32_t eb_engine_chunk_tokens(const eb_engine* e, int32_t* tokens);
+/* Sampling for one live sequence, from its next step on: temperature > 0 draws every new token of the sequence with
+ * eb_sample_top_p (scale = log2(e) / temperature in fp32, top_p clamped to [0, 1], rand32 = eb_sample_rand32(seed,
+ * absolute position of the token drawn), so a sequence's tokens do not depend on what shares its steps); temperature
+ * <= 0 is greedy, the state of every newly admitted sequence.  h_margin stays the top-1 minus top-2 logit.  The request
+ * fields this serves: crates/eidola-server/src/types.rs:24-30.  Single-GPU engines only: EB_ERR_UNSUPPORTED under tensor
+ * parallelism, whose LM head is split over the vocabulary. */
+int32_t eb_engine_seq_sampling(eb_engine* e, int32_t slot, float temperature, float top_p, uint64_t seed);
 /* The same split in two so a caller can overlap host work: launch, then wait for the results. */
 int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_t* h_q_lens, int32_t n_seqs,
                               const int32_t* h_tokens);

@@ -26,6 +26,14 @@ def bf16_to_f32(h: np.ndarray) -> np.ndarray:
     return (np.ascontiguousarray(h, np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    """Round to nearest even; infinities and NaN keep their class."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    nan = np.isnan(np.asarray(x, np.float32))
+    return np.where(nan, np.uint16(0x7FC0), r).astype(np.uint16)
+
+
 def assert_close_bf16(got_u16, want_u16, atol=ATOL, rtol=RTOL, what=""):
     g, w = bf16_to_f32(got_u16).astype(np.float64), bf16_to_f32(want_u16).astype(np.float64)
     assert np.isfinite(g).all(), f"{what}: non-finite output"

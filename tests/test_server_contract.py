@@ -36,6 +36,9 @@ class ScriptedEngine:
         self.calls.append(("step", list(slots)))
         return np.array([(t + 1) % 256 or 1 for t in tokens], np.int32), None
 
+    def sampling(self, slot, temperature, top_p, seed):
+        self.calls.append(("sampling", slot, temperature, top_p, seed))
+
     def release(self, slot):
         self.free.append(slot)
 
@@ -118,6 +121,19 @@ def test_requests_that_overlap_share_decode_steps_and_bad_requests_are_refused()
                 assert False
             except urllib.error.HTTPError as e:
                 assert e.code == 400 and "error" in json.load(e)
+        # sampling fields reach the engine before the sequence's first step; greedy requests never touch them
+        assert not any(c[0] == "sampling" for c in eng.calls)
+        json.load(_post(url, {"messages": [{"role": "user", "content": "s"}], "max_completion_tokens": 3, "temperature": 0.7,
+                              "top_p": 0.9, "seed": 5}))
+        samp = [c for c in eng.calls if c[0] == "sampling"]
+        assert len(samp) == 1 and samp[0][2:] == (0.7, 0.9, 5)
+        assert eng.calls.index(samp[0]) < max(i for i, c in enumerate(eng.calls) if c[0] == "prefill")
+        for bad_field in ({"temperature": 2.5}, {"temperature": -1}, {"top_p": 1.5}, {"temperature": "hot"}):
+            try:
+                _post(url, dict({"messages": [{"role": "user", "content": "s"}]}, **bad_field))
+                assert False
+            except urllib.error.HTTPError as e:
+                assert e.code == 400
         try:  # more context than the engine was started with: refused with a message, like the reference's -c cap
             _post(url, {"messages": [{"role": "user", "content": "x" * 600}], "max_completion_tokens": 10})
             assert False
