@@ -243,7 +243,8 @@ def make_handler(loop: EngineLoop, alias: str):
                         return self._json(500, {"error": {"message": str(val), "type": "server_error", "code": 500}})
                 return self._json(200, {"id": rid, "object": "chat.completion", "created": created, "model": base["model"],
                                         "choices": [{"index": 0, "finish_reason": "stop" if usage["completion_tokens"] < req.max_tokens else "length",
-                                                     "message": {"role": "assistant", "content": ByteTokenizer.decode(toks)}}],
+                                                     "message": {"role": "assistant", "content": ByteTokenizer.decode(toks)},
+                                                     **({"token_ids": toks} if body.get("return_token_ids") else {})}],
                                         "usage": usage})
             self.send_response(200)
             self.send_header("Content-Type", "text/event-stream")
