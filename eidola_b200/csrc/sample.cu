@@ -11,15 +11,16 @@
 //              Horner in separately rounded fp32 multiplies and adds (no fused multiply-add: numpy has none);
 //              t < -32 and NaN logits weigh nothing.  W_v is the softmax numerator to 2e-7 relative, cut off where a
 //              token is 2^-31 times less likely than the likeliest.
-//   nucleus    bf16 logits have 65536 possible values: key(x) orders them.  Z = sum W; target = max(1, Z * top_p_q24 >>
-//              24); thr = the largest key whose tail mass sum{W_v : key_v >= thr} reaches target (found by two 256-bin
-//              histograms of integer mass: high byte of the key, then low byte inside the chosen bin; each warp fills
-//              a histogram of its own with warp-aggregated adds); the nucleus is
-//              every token with key >= thr (ties at the threshold all belong), mass M.
+//   nucleus    bf16 logits have 65536 possible values: key(x) orders them, and all logits with one key weigh the same.
+//              Z = sum W; target = max(1, Z * top_p_q24 >> 24); thr = the largest key whose tail mass
+//              sum{W_v : key_v >= thr} reaches target; the nucleus is every token with key >= thr (ties at the
+//              threshold all belong), mass M.  The kernel COUNTS the row's logits per key in shared memory (the lower
+//              and the upper half of the key space in turn, 32768 counters each) and multiplies count by weight once
+//              per key that occurs; a scan over 32-key groups from the top finds thr.
 //   draw       r = (M * rand32) >> 32; the token is the first v, in index order, whose running nucleus mass exceeds r.
 //
-// One CTA of 1024 threads per row; four passes over the row (max, high histogram, low histogram, draw), which stays in
-// L2 between them.  Rows whose scale is <= 0 are left alone (greedy rows keep the argmax token).
+// One CTA of 1024 threads per row; four passes over the row (max, the two counting passes, draw; a fifth when the
+// threshold lies among the negative logits), which stays in L2 between them.  Rows whose scale is <= 0 are left alone (greedy rows keep the argmax token).
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -85,24 +86,29 @@ __device__ __forceinline__ void for_row(const uint16_t* r, int64_t V, bool vec, 
   }
 }
 
-// hist[bin] += w for every lane with w != 0, the whole warp together: the lanes that share a bin add their weights up with
-// two warp reductions (16-bit halves: 32 of them cannot overflow) and one lane does the 64-bit add on the warp's own
-// histogram, so that no atomic and no other warp is involved.  A few distinct bins per call is the common case.
-__device__ __forceinline__ void warp_hist_add(unsigned long long* hist, uint32_t bin, uint32_t w, int lane) {
-  // a lane alone in its bin adds by itself (distinct bins are distinct addresses); the others go through the loop
-  const unsigned peers = __match_any_sync(0xffffffffu, w != 0u ? bin : 0xFFFFFFFFu);
-  const bool alone = peers == (1u << lane);
-  if (w != 0u && alone) hist[bin] += w;
-  unsigned active = __ballot_sync(0xffffffffu, w != 0u && !alone);
-  while (active) {
-    const int leader = __ffs(active) - 1;
-    const uint32_t b0 = __shfl_sync(0xffffffffu, bin, leader);
-    const bool mine = w != 0u && bin == b0;
-    const uint32_t lo = __reduce_add_sync(0xffffffffu, mine ? (w & 0xFFFFu) : 0u);
-    const uint32_t hi = __reduce_add_sync(0xffffffffu, mine ? (w >> 16) : 0u);
-    if (lane == leader) hist[b0] += ((unsigned long long)hi << 16) + lo;
-    active &= ~__ballot_sync(0xffffffffu, mine);
+__device__ __forceinline__ uint32_t bits_of_key(uint32_t key) {  // inverse of key_of
+  return (key & 0x8000u) ? (key & 0x7FFFu) : (~key & 0xFFFFu);
+}
+
+// One half of the key space (the 32768 keys with key >> 15 == half): count the row's logits per key with shared-memory
+// adds of 1, then let thread t turn the counts of its 32 keys [32 t, 32 t + 32) into integer mass, count x W(key): a
+// weight is computed once per KEY that occurs, not once per logit.  Returns the thread's mass.
+__device__ __forceinline__ unsigned long long count_half(const uint16_t* r, int64_t V, bool vec, uint32_t half, uint32_t* cnt, float mx,
+                                                         float sc) {
+  for (int i = threadIdx.x; i < 32768; i += kThreads) cnt[i] = 0u;
+  __syncthreads();
+  for_row(r, V, vec, [&](int64_t, uint32_t b, bool live) {
+    const uint32_t k = key_of(b);
+    if (live && !is_nan_bf16(b) && (k >> 15) == half) atomicAdd(&cnt[k & 0x7FFFu], 1u);
+  });
+  __syncthreads();
+  unsigned long long mass = 0;
+#pragma unroll 4
+  for (int i = 0; i < 32; ++i) {
+    const uint32_t kk = threadIdx.x * 32 + i, c = cnt[kk];
+    if (c) mass += (unsigned long long)c * weight_of(__uint_as_float(bits_of_key((half << 15) | kk) << 16), mx, sc);
   }
+  return mass;
 }
 
 __global__ void __launch_bounds__(kThreads) sample_top_p_kernel(const uint16_t* logits, int64_t V, int64_t ld, const float* scale,
@@ -117,13 +123,12 @@ __global__ void __launch_bounds__(kThreads) sample_top_p_kernel(const uint16_t* 
   const bool vec = (((uintptr_t)r) & 15) == 0;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  extern __shared__ unsigned long long s_whist[];  // [32 warps][256 bins]
-  unsigned long long* my_hist = s_whist + warp * 256;
+  extern __shared__ uint32_t s_cnt[];  // [32768] logits per key of the half being counted
   __shared__ float s_max[32];
-  __shared__ unsigned long long s_hist[256];
-  __shared__ unsigned long long s_part[kThreads];
+  __shared__ unsigned long long s_gm[2 * kThreads];  // mass of 32-key groups, from the largest keys down; then the runs of the draw
   __shared__ unsigned long long s_above, s_target, s_r;
-  __shared__ uint32_t s_hi, s_thr;
+  __shared__ uint32_t s_thr;
+  __shared__ int s_group;
   __shared__ float s_mx;
 
   // ---- pass 1: the row maximum (NaN never wins)
@@ -134,7 +139,6 @@ __global__ void __launch_bounds__(kThreads) sample_top_p_kernel(const uint16_t* 
 #pragma unroll
   for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   if (lane == 0) s_max[warp] = mx;
-  for (int i = lane; i < 256; i += 32) my_hist[i] = 0ull;
   __syncthreads();
   if (warp == 0) {
     float m = s_max[lane];
@@ -146,65 +150,63 @@ __global__ void __launch_bounds__(kThreads) sample_top_p_kernel(const uint16_t* 
   mx = s_mx;
   if (!(mx > -INFINITY) || mx == INFINITY) return;  // nothing to weigh (all -inf / NaN) or an infinite logit: the argmax token stays
 
-  // the warps' histograms, added up in warp order into s_hist (and cleared for the next pass)
-  auto fold = [&]() {
-    __syncthreads();
-    if (tid < 256) {
-      unsigned long long sum = 0;
-      for (int w = 0; w < 32; ++w) {
-        sum += s_whist[w * 256 + tid];
-        s_whist[w * 256 + tid] = 0ull;
-      }
-      s_hist[tid] = sum;
+  // ---- passes 2 and 3: integer mass per group of 32 keys; the lower half of the key space (negative logits) first,
+  // so that the counts left in shared memory are those of the upper half, where the threshold usually lies.
+  // Group g (0 = the largest keys) is thread 1023 - g of the upper half, then thread 2047 - g of the lower half.
+  s_gm[2 * kThreads - 1 - tid] = count_half(r, V, vec, 0u, s_cnt, mx, sc);
+  __syncthreads();
+  s_gm[kThreads - 1 - tid] = count_half(r, V, vec, 1u, s_cnt, mx, sc);
+  __syncthreads();
+  // the total, the target, and the group in which the tail mass reaches it (warp 0: 64 groups per lane)
+  if (warp == 0) {
+    unsigned long long run = 0;
+    for (int i = 0; i < 64; ++i) run += s_gm[lane * 64 + i];
+    unsigned long long incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
     }
-    __syncthreads();
-  };
-
-  // ---- pass 2: integer mass by the high byte of the key
-  for_row(r, V, vec, [&](int64_t, uint32_t b, bool live) {
-    const uint32_t w = (live && !is_nan_bf16(b)) ? weight_of(__uint_as_float(b << 16), mx, sc) : 0u;
-    warp_hist_add(my_hist, key_of(b) >> 8, w, lane);
-  });
-  fold();
-  if (tid == 0) {
-    unsigned long long Z = 0;
-    for (int i = 0; i < 256; ++i) Z += s_hist[i];
+    const unsigned long long Z = __shfl_sync(0xffffffffu, incl, 31);
     const uint32_t q = top_p_q24[row];
     unsigned long long target = q >= (1u << 24) ? Z : __umul64hi(Z, (unsigned long long)q << 40);
     if (target < 1ull) target = 1ull;
-    unsigned long long above = 0;
-    int hb = 255;
-    for (; hb > 0; --hb) {
-      if (above + s_hist[hb] >= target) break;
-      above += s_hist[hb];
+    const unsigned long long before = incl - run;
+    if (before < target && incl >= target) {  // exactly one lane (Z >= target >= 1)
+      unsigned long long cum = before;
+      int g = lane * 64;
+      for (; g < lane * 64 + 63; ++g) {
+        if (cum + s_gm[g] >= target) break;
+        cum += s_gm[g];
+      }
+      s_group = g;
+      s_above = cum;  // mass of the groups above the chosen one
+      s_target = target;
     }
-    s_hi = (uint32_t)hb;
-    s_above = above;  // mass of the bins above the chosen one
-    s_target = target;
   }
   __syncthreads();
-  const uint32_t hb = s_hi;
-
-  // ---- pass 3: inside that bin, mass by the low byte
-  for_row(r, V, vec, [&](int64_t, uint32_t b, bool live) {
-    const uint32_t k = key_of(b);
-    const uint32_t w = (live && !is_nan_bf16(b) && (k >> 8) == hb) ? weight_of(__uint_as_float(b << 16), mx, sc) : 0u;
-    warp_hist_add(my_hist, k & 255u, w, lane);
-  });
-  fold();
+  const int group = s_group;
+  if (group >= kThreads) {  // the threshold lies among the negative logits: their counts again
+    (void)count_half(r, V, vec, 0u, s_cnt, mx, sc);
+    __syncthreads();
+  }
   if (tid == 0) {
+    const uint32_t half = group < kThreads ? 1u : 0u;
+    const uint32_t t_owner = (uint32_t)(group < kThreads ? kThreads - 1 - group : 2 * kThreads - 1 - group);
     unsigned long long cum = s_above;
-    int lb = 255;
-    for (; lb > 0; --lb) {
-      if (cum + s_hist[lb] >= s_target) break;
-      cum += s_hist[lb];
+    int i = 31;
+    for (; i >= 0; --i) {
+      const uint32_t kk = t_owner * 32 + (uint32_t)i, c = s_cnt[kk];
+      if (c) cum += (unsigned long long)c * weight_of(__uint_as_float(bits_of_key((half << 15) | kk) << 16), mx, sc);
+      if (cum >= s_target) break;
     }
-    cum += s_hist[lb];  // the nucleus' mass M: every key >= thr
-    s_thr = (hb << 8) | (uint32_t)lb;
+    if (i < 0) i = 0;  // (cannot happen: the group's mass reaches the target)
+    s_thr = (half << 15) | (t_owner * 32 + (uint32_t)i);  // the nucleus: every key >= thr, mass cum
     s_r = __umul64hi(cum, (unsigned long long)rand32[row] << 32);  // (M * rand32) >> 32 < M
   }
   __syncthreads();
   const uint32_t thr = s_thr;
+  unsigned long long* s_part = s_gm;
 
   // ---- pass 4: the draw, in index order.  Thread t owns the contiguous run [t * per, (t + 1) * per).
   const int64_t per = ((V + kThreads - 1) / kThreads + 7) / 8 * 8;
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(kThreads) sample_top_p_kernel(const uint16_t* 
   }
 }
 
-constexpr size_t kSampleSmem = 32 * 256 * sizeof(unsigned long long);
+constexpr size_t kSampleSmem = 32768 * sizeof(uint32_t);
 
 }  // namespace
 
