@@ -148,3 +148,22 @@ def test_rmsnorm_rope_argmax():
     odd = np.array([[0x7FC0, 0x3F80, 0x4000, 0x7FC0], [0x7FC0] * 4, [0xFF80] * 4], np.uint16)
     tok, _ = orc.argmax(odd)
     assert tok.tolist() == [2, 0, 0]
+
+
+def test_column_bands_quantise_to_the_bands_of_the_whole_matrix():
+    """What lets tensor-parallel ranks assemble the O projection's operand from their own heads: scale blocks are 128
+    columns wide, so quantising a band of whole blocks alone gives the codes and scales the whole matrix has there, and
+    the full-K product on the assembled operand is the single-GPU product bit for bit."""
+    rng = np.random.default_rng(21)
+    T, K, N, ranks = 200, 1024, 256, 4
+    x = orc.bf16_encode(rng.normal(0, 1.5, size=(T, K)).astype(np.float32))
+    codes, scales = orc.quant_act_block128(x)
+    band = K // ranks
+    parts = [orc.quant_act_block128(np.ascontiguousarray(x[:, r * band:(r + 1) * band])) for r in range(ranks)]
+    assert np.array_equal(np.concatenate([p[0] for p in parts], axis=1), codes)
+    assert np.array_equal(np.concatenate([p[1] for p in parts], axis=1), scales)
+    # a token slice (rows 128..199, whole row blocks) of the assembled operand times the whole weight = those rows of Y
+    w8, sw = orc.synth_weight_fp8(5, 9, N, K, 0, N, 0.05)
+    y = orc.gemm_fp8_block(codes, scales, w8, sw)
+    y_slice = orc.gemm_fp8_block(np.ascontiguousarray(codes[128:]), np.ascontiguousarray(scales[1:]), w8, sw)
+    assert np.array_equal(y_slice, y[128:])
