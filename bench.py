@@ -5,7 +5,7 @@
 
 Prints ONE JSON line.  With one GPU the default workload also carries the other two parts of the metric as
 sub-records (`attn`: the paged sink-attention benchmark; `gemm_sweep`: the FP8 GEMM sweep against the measured FP8
-issue-rate ceiling `fp8_peak`).  Under torchrun with N > 1 ranks the SAME 256 sequences are decoded by ONE engine
+issue-rate ceiling `fp8_peak`; `sampler`: top-p sampling beside argmax on 256 rows of the vocabulary).  Under torchrun with N > 1 ranks the SAME 256 sequences are decoded by ONE engine
 spread over the N GPUs -- query/KV heads tensor-parallel, experts expert-parallel, LM head vocabulary-parallel, over
 NCCL -- so the figure scales strongly; the line then also carries `spec120b` (the 120b-shaped speculative-verify
 step on the same ranks) and `parity` (a two-layer slice of the N-rank engine against the single-GPU engine).
@@ -636,6 +636,7 @@ def run_decoder(args) -> dict:
         out["fp8_peak"] = peak_subrecord(eb, capi)
         out["attn"] = attn_subrecord(eb, capi, rank)
         out["gemm_sweep"] = gemm_subrecord(eb, capi, rank, out["fp8_peak"])
+        out["sampler"] = sampler_subrecord(eb, capi)
     if world == 1 and not args.no_cpu:
         cpu = decoder_cpu_sample()
         out["cpu_baseline"] = {"value": cpu["value"], "unit": "tokens/s", "cores": cpu["threads"], "kind": "port",
@@ -874,6 +875,35 @@ def attn_subrecord(eb, capi, rank, n_seqs=256, reps=10) -> dict:
     out["note"] = ("CUDA events around each of %d calls (attention kernel + merge); the window variant moves 71 MB and is latency "
                    "bound, its fraction is reported, not claimed as a roofline" % reps)
     return out
+
+
+def sampler_subrecord(eb, capi) -> dict:
+    """eb_sample_top_p beside eb_argmax on 256 rows of the benchmark's vocabulary: the cost of drawing every token of the
+    batch at temperature 1, top_p 0.9, on the flattest rows there are (N(0,2) logits: every token weighs something)."""
+    from eidola_b200.capi import DeviceBuffer, c_f32, c_i32, c_i64, c_u64, c_vp
+    T, V = 256, 201088
+    logits = DeviceBuffer(T * V * 2)
+    capi.call("eb_synth_normal_bf16", c_vp(logits.ptr), c_i64(T * V), c_u64(1), c_u64(3), c_u64(0), c_f32(2.0), None)
+    sc = DeviceBuffer.from_array(np.full(T, 1.4426950408889634, np.float32))
+    q = DeviceBuffer.from_array(np.full(T, int(0.9 * 2 ** 24), np.uint32))
+    r = DeviceBuffer.from_array((np.arange(T, dtype=np.uint64) * 2654435761 % 2 ** 32).astype(np.uint32))
+    tok, mg = DeviceBuffer(T * 4), DeviceBuffer(T * 4)
+
+    def timed(fn, n=20):
+        for _ in range(3):
+            fn()
+        t = eb.Timer()
+        capi.call("eb_device_sync")
+        t.start()
+        for _ in range(n):
+            fn()
+        return t.stop() / n * 1e3
+
+    am = timed(lambda: capi.call("eb_argmax", c_vp(logits.ptr), c_i32(T), c_i64(V), c_i64(V), c_vp(tok.ptr), c_vp(mg.ptr), None))
+    sm = timed(lambda: capi.call("eb_sample_top_p", c_vp(logits.ptr), c_i32(T), c_i64(V), c_i64(V), c_vp(sc.ptr), c_vp(q.ptr),
+                                 c_vp(r.ptr), c_vp(tok.ptr), None))
+    return {"rows": T, "vocab": V, "argmax_us": am, "sample_top_p_us": sm, "temperature": 1.0, "top_p": 0.9,
+            "note": "20 back-to-back launches each; synthetic N(0,2) logits, the sampler's worst case"}
 
 
 def gemm_subrecord(eb, capi, rank, fp8_peak) -> dict:
