@@ -6,7 +6,9 @@
 //   "GGUF" | u32 version | u64 tensor_count | u64 kv_count | kv_count x (string key, u32 type, value)
 //   | tensor_count x (string name, u32 n_dims, n_dims x u64 extent (innermost first), u32 ggml type, u64 offset)
 //   | padding to `general.alignment` (default 32) | tensor data
-// Tensor types read here: F32 (0), F16 (1), BF16 (30); quantised GGUF types are refused by name.  Host code only;
+// Tensor types read here: F32 (0), F16 (1), BF16 (30) and three block formats of 32 elements along a row: Q4_0 (2),
+// Q8_0 (8), MXFP4 (39), decoded to fp32 as their published definitions say (block_bytes / decode_block below); the other
+// quantised GGUF types are refused by number.  Host code only;
 // everything numeric happens in the engine.
 #include "loader.h"
 
@@ -152,13 +154,65 @@ const GgufTensor* GgufFile::find(const std::string& name) const {
   return it == tensors_.end() ? nullptr : &it->second;
 }
 
+namespace {
+
+// Block formats: 32 consecutive elements of a row share one scale.
+//   Q8_0  (34 bytes): fp16 d, int8 q[32]                      x[i] = d * q[i]
+//   Q4_0  (18 bytes): fp16 d, 16 bytes of two 4-bit codes     x[i] = d * ((b[i] & 15) - 8), x[i + 16] = d * ((b[i] >> 4) - 8)
+//   MXFP4 (17 bytes): e8m0 scale byte e, 16 bytes of two e2m1 codes (the OCP microscaling element: sign, 2 exponent
+//                     bits, 1 mantissa bit: 0, 0.5, 1, 1.5, 2, 3, 4, 6), low nibbles the first 16 elements, high nibbles
+//                     the last 16 as in Q4_0                   x = 2^(e - 127) * e2m1(code); e = 255 is NaN
+int block_bytes(uint32_t type) { return type == 8 ? 34 : type == 2 ? 18 : type == 39 ? 17 : 0; }
+
+void decode_block(uint32_t type, const uint8_t* b, float* x) {
+  if (type == 8) {
+    uint16_t h;
+    memcpy(&h, b, 2);
+    const float d = half_to_float(h);
+    for (int i = 0; i < 32; ++i) x[i] = d * (float)(int8_t)b[2 + i];
+  } else if (type == 2) {
+    uint16_t h;
+    memcpy(&h, b, 2);
+    const float d = half_to_float(h);
+    for (int i = 0; i < 16; ++i) {
+      x[i] = d * (float)((int)(b[2 + i] & 15) - 8);
+      x[i + 16] = d * (float)((int)(b[2 + i] >> 4) - 8);
+    }
+  } else {
+    static const float kE2M1[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+    const float d = b[0] == 255 ? NAN : ldexpf(1.0f, (int)b[0] - 127);
+    for (int i = 0; i < 16; ++i) {
+      const uint8_t lo = b[1 + i] & 15, hi = b[1 + i] >> 4;
+      x[i] = d * ((lo & 8) ? -kE2M1[lo & 7] : kE2M1[lo & 7]);
+      x[i + 16] = d * ((hi & 8) ? -kE2M1[hi & 7] : kE2M1[hi & 7]);
+    }
+  }
+}
+
+}  // namespace
+
 int32_t GgufFile::read_f32(const GgufTensor& t, int64_t elem0, int64_t n, float* out) {
+  if (elem0 < 0 || n < 0 || elem0 + n > t.elements()) return fail(EB_ERR_ARG, "gguf: elements [%lld, +%lld) outside the tensor", (long long)elem0, (long long)n);
+  if (const int bb = block_bytes(t.type)) {
+    if (t.ne[0] % 32) return fail(EB_ERR_UNSUPPORTED, "gguf: block-quantised rows of %lld elements (not a multiple of 32)", (long long)t.ne[0]);
+    const int64_t b0 = elem0 / 32, b1 = (elem0 + n + 31) / 32;
+    raw_.resize((size_t)((b1 - b0) * bb));
+    if (fseeko(f_, (off_t)(data_start_ + t.offset + (uint64_t)b0 * bb), SEEK_SET) != 0) return fail(EB_ERR_ARG, "gguf: seek failed");
+    if (fread(raw_.data(), 1, raw_.size(), f_) != raw_.size()) return fail(EB_ERR_ARG, "gguf: tensor data is truncated");
+    float x[32];
+    for (int64_t b = b0; b < b1; ++b) {
+      decode_block(t.type, raw_.data() + (size_t)((b - b0) * bb), x);
+      const int64_t lo = std::max<int64_t>(elem0, b * 32), hi = std::min<int64_t>(elem0 + n, b * 32 + 32);
+      for (int64_t e = lo; e < hi; ++e) out[e - elem0] = x[e - b * 32];
+    }
+    return EB_OK;
+  }
   int esz;
   switch (t.type) {
     case 0: esz = 4; break;
     case 1: case 30: esz = 2; break;
     default:
-      return fail(EB_ERR_UNSUPPORTED, "gguf: tensor type %u is not F32, F16 or BF16 (quantised GGUF types are not read)", t.type);
+      return fail(EB_ERR_UNSUPPORTED, "gguf: tensor type %u is not F32, F16, BF16, Q4_0, Q8_0 or MXFP4 (the other quantised GGUF types are not read)", t.type);
   }
   if (fseeko(f_, (off_t)(data_start_ + t.offset + (uint64_t)elem0 * esz), SEEK_SET) != 0) return fail(EB_ERR_ARG, "gguf: seek failed");
   if (t.type == 0) {
@@ -179,3 +233,18 @@ int32_t GgufFile::read_f32(const GgufTensor& t, int64_t elem0, int64_t n, float*
 }
 
 }  // namespace eb
+
+extern "C" int32_t eb_gguf_read_f32(const char* path, const char* tensor, int64_t elem0, int64_t n, float* h_out, int32_t* ggml_type,
+                                    int64_t* n_elements) {
+  EB_REQUIRE(path && tensor, EB_ERR_ARG, "eb_gguf_read_f32: null");
+  eb::GgufFile g;
+  const int32_t rc = g.open(path);
+  if (rc != EB_OK) return rc;
+  const eb::GgufTensor* t = g.find(tensor);
+  EB_REQUIRE(t, EB_ERR_ARG, "eb_gguf_read_f32: no tensor %s in %s", tensor, path);
+  if (ggml_type) *ggml_type = (int32_t)t->type;
+  if (n_elements) *n_elements = t->elements();
+  if (n == 0) return EB_OK;
+  EB_REQUIRE(h_out, EB_ERR_ARG, "eb_gguf_read_f32: null output");
+  return g.read_f32(*t, elem0, n, h_out);
+}

@@ -586,10 +586,16 @@ int32_t eb_engine_memory(const eb_engine* e, int64_t* weight_bytes, int64_t* kv_
  *   blk.L.ffn_down_exps.weight [experts][hidden][inter]
  * The linear layers are quantised on the device to e4m3 with 128x128 block scales (eb_quant_weight_f32) and stored as
  * tiles; embeddings and router become bf16; norms and sinks stay fp32.  A tensor-parallel rank reads only its own rows,
- * columns and experts.  Quantised GGUF types are refused.  Returns EB_ERR_ARG naming the tensor when one is missing or
- * has the wrong shape; the engine's weights are then partly replaced and it must be reloaded or destroyed.
+ * columns and experts.  Tensor types read: F32, F16, BF16, and the block formats Q4_0, Q8_0 and MXFP4 (32 elements of a
+ * row per scale; decoded to fp32 on the host, then quantised like the others); the other quantised GGUF types are
+ * refused.  Returns EB_ERR_ARG naming the tensor when one is missing or has the wrong shape; the engine's weights are
+ * then partly replaced and it must be reloaded or destroyed.
  */
 int32_t eb_engine_load_gguf(eb_engine* e, const char* path);
+/* Host only (no device): n elements from element elem0 of tensor `tensor` of a GGUF file as fp32, through the reader the
+ * loader uses; ggml_type / n_elements (may be NULL) receive the tensor's stored type and size; n == 0 only asks for those. */
+int32_t eb_gguf_read_f32(const char* path, const char* tensor, int64_t elem0, int64_t n, float* h_out, int32_t* ggml_type,
+                         int64_t* n_elements);
 /* Stand-in for prefill: fill every KV page of every layer with seeded N(0,1) values (element i of layer l is
  * eb_normal(seed, 20000 + l, i)), so a sequence admitted with a context length has keys and values to attend to. */
 int32_t eb_engine_kv_fill_synth(eb_engine* e);

@@ -9,7 +9,7 @@ import pytest
 
 from oracle import binding as orc
 from tests.decoder_cases import TINY_CONTEXTS, tiny_config
-from tests.gguf_writer import write_gguf
+from tests.gguf_writer import Blocked, write_gguf
 
 pytestmark = pytest.mark.gpu
 
@@ -89,4 +89,31 @@ def test_gguf_checkpoint_reproduces_the_seeded_engine(gpu, tmp_path):
     assert "blk.1.ffn_down_exps.weight" in str(err.value)
     with pytest.raises(eb.EbError):
         eb.Engine(tiny_config(hidden=1024)).load_gguf(path)
+    assert eb.status_read() == 0
+
+
+def test_block_quantised_checkpoint_loads_as_its_dequantised_values(gpu, tmp_path):
+    """Checkpoints as they are distributed keep their linear layers in block formats (8-bit attention and head, 4-bit
+    microscaling experts): loading such a file must be loading the fp32 values its blocks stand for."""
+    import eidola_b200 as eb
+    cfg = tiny_config()
+    tensors = _seeded_tensors(cfg)
+    blocked, plain = dict(tensors), dict(tensors)
+    kinds = {"attn_qkv.weight": "q8_0", "attn_output.weight": "q4_0", "ffn_gate_up_exps.weight": "mxfp4", "ffn_down_exps.weight": "mxfp4"}
+    for l in range(cfg.n_layers):
+        for suffix, kind in kinds.items():
+            b = Blocked(kind, tensors[f"blk.{l}.{suffix}"])
+            blocked[f"blk.{l}.{suffix}"], plain[f"blk.{l}.{suffix}"] = b, b.values
+    b = Blocked("q8_0", tensors["output.weight"])
+    blocked["output.weight"], plain["output.weight"] = b, b.values
+    write_gguf(tmp_path / "blocked.gguf", blocked)
+    write_gguf(tmp_path / "plain.gguf", plain)
+    out = []
+    for name in ("blocked.gguf", "plain.gguf"):
+        eng = eb.Engine(tiny_config())
+        eng.load_gguf(tmp_path / name)
+        out.append(_step(eng, cfg))
+    assert np.array_equal(out[0][1], out[1][1]) and np.array_equal(out[0][0], out[1][0])
+    _, unquantised = _step(eb.Engine(cfg), cfg)
+    assert not np.array_equal(out[0][1], unquantised)  # (the 4-bit experts are a different model, as they should be)
     assert eb.status_read() == 0
