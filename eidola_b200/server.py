@@ -17,15 +17,16 @@ local_models.rs:1633-1638) and runs continuous batching: requests that arrive ar
 least recently used first, when the page pool is full), their prompts are prefilled together, and every iteration
 decodes one token for every live sequence.  HTTP threads only enqueue requests and drain per-request token queues.
 
-What this is NOT: the reference contains no tokenizer, chat template or sampler (they live inside the third-party
-engine); this library has the sampler and no real tokenizer.  The tokenizer here is the identity on UTF-8 bytes (ids 0..255) with a plain
-`<|role|>` template; a checkpoint with its own vocabulary needs its tokenizer in front.  Decoding is greedy unless
+The reference contains no tokenizer, chat template or sampler (they live inside the third-party engine).  Here: a GGUF
+file that carries a byte-level BPE vocabulary (tokenizer.ggml.*) and a chat template is served with them
+(eidola_b200/tokenizer.py); a file without gets the identity on UTF-8 bytes (ids 0..255) with a plain `<|role|>` template.  Decoding is greedy unless
 the request carries `temperature` > 0 (then `top_p` and `seed` apply: eb_engine_seq_sampling, drawn on the device).  With
 the random-init weights the replies are noise -- the process contract, the batching and the timings are what is real.
 """
 from __future__ import annotations
 
 import argparse
+import codecs
 import json
 import queue
 import sys
@@ -56,6 +57,10 @@ class ByteTokenizer:
         return [b if b != 0 else 32 for b in out] or [32]
 
     @staticmethod
+    def token_bytes(i: int) -> bytes:
+        return bytes([i if 0 < i < 256 else 63])
+
+    @staticmethod
     def decode(ids) -> str:
         return bytes((i if 0 < i < 256 else 63) for i in ids).decode("utf-8", errors="replace")
 
@@ -75,9 +80,10 @@ class EngineLoop(threading.Thread):
     prompts) -> (first_tokens, ...), step(slots, q_lens, tokens) -> (next, margins), release(slot), and max_seqs /
     context_tokens attributes: eidola_b200.host.Engine behind a thin adapter, or a scripted fake in the CPU tests."""
 
-    def __init__(self, engine, context_tokens: int):
+    def __init__(self, engine, context_tokens: int, tokenizer=ByteTokenizer):
         super().__init__(daemon=True)
         self.engine, self.context_tokens = engine, context_tokens
+        self.tokenizer = tokenizer  # template(messages) -> ids, token_bytes(id), decode(ids), eos
         self.inbox: "queue.Queue[Request]" = queue.Queue()
         self.live: dict[int, Request] = {}
         self.last: dict[int, int] = {}
@@ -119,8 +125,8 @@ class EngineLoop(threading.Thread):
     def _deliver(self, r: Request, tok: int) -> None:
         r.generated += 1
         self.stats["generated"] += 1
-        done = r.generated >= r.max_tokens or tok == ByteTokenizer.eos
-        if not (tok == ByteTokenizer.eos):
+        done = r.generated >= r.max_tokens or tok == self.tokenizer.eos
+        if not (tok == self.tokenizer.eos):
             r.out.put(("token", tok))
         if done:
             r.out.put(("done", {"prompt_tokens": len(r.prompt_ids), "completion_tokens": r.generated,
@@ -226,7 +232,11 @@ def make_handler(loop: EngineLoop, alias: str):
             except Exception:
                 return self._json(400, {"error": {"message": "`temperature` must lie in [0, 2], `top_p` in [0, 1], `seed` be an integer",
                                                   "type": "invalid_request_error", "code": 400}})
-            req = Request(ByteTokenizer.template(messages), max(1, max_tokens), temperature, top_p, seed)
+            try:
+                prompt_ids = loop.tokenizer.template(messages)
+            except Exception as e:  # a chat template may refuse a conversation (roles out of order, ...)
+                return self._json(400, {"error": {"message": "chat template: %s" % e, "type": "invalid_request_error", "code": 400}})
+            req = Request(prompt_ids, max(1, max_tokens), temperature, top_p, seed)
             loop.submit(req)
             rid, created = "chatcmpl-%x" % id(req), int(time.time())
             base = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": body.get("model") or alias}
@@ -243,7 +253,7 @@ def make_handler(loop: EngineLoop, alias: str):
                         return self._json(500, {"error": {"message": str(val), "type": "server_error", "code": 500}})
                 return self._json(200, {"id": rid, "object": "chat.completion", "created": created, "model": base["model"],
                                         "choices": [{"index": 0, "finish_reason": "stop" if usage["completion_tokens"] < req.max_tokens else "length",
-                                                     "message": {"role": "assistant", "content": ByteTokenizer.decode(toks)},
+                                                     "message": {"role": "assistant", "content": loop.tokenizer.decode(toks)},
                                                      **({"token_ids": toks} if body.get("return_token_ids") else {})}],
                                         "usage": usage})
             self.send_response(200)
@@ -256,13 +266,20 @@ def make_handler(loop: EngineLoop, alias: str):
                 self.wfile.write(b"data: " + (obj if isinstance(obj, bytes) else json.dumps(obj).encode()) + b"\n\n")
                 self.wfile.flush()
 
+            # a token may end inside a UTF-8 sequence: text leaves when its bytes are complete
+            utf8 = codecs.getincrementaldecoder("utf-8")(errors="replace")
             try:
                 event(dict(base, choices=[{"index": 0, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]))
                 while True:
                     kind, val = req.out.get()
                     if kind == "token":
-                        event(dict(base, choices=[{"index": 0, "delta": {"content": ByteTokenizer.decode([val])}, "finish_reason": None}]))
+                        text = utf8.decode(loop.tokenizer.token_bytes(val))
+                        if text:
+                            event(dict(base, choices=[{"index": 0, "delta": {"content": text}, "finish_reason": None}]))
                     elif kind == "done":
+                        tail = utf8.decode(b"", final=True)
+                        if tail:
+                            event(dict(base, choices=[{"index": 0, "delta": {"content": tail}, "finish_reason": None}]))
                         event(dict(base, choices=[{"index": 0, "delta": {}, "finish_reason": "stop" if val["completion_tokens"] < req.max_tokens else "length"}]))
                         if include_usage:
                             event(dict(base, choices=[], usage=val))
@@ -310,7 +327,7 @@ def main(argv=None) -> int:
     ap.add_argument("--alias", default="eidola-b200")
     ap.add_argument("-c", "--ctx", type=int, default=8192)
     ap.add_argument("-ngl", "--n-gpu-layers", type=int, default=999)  # everything runs on the GPU; accepted for the contract
-    ap.add_argument("--jinja", action="store_true")                   # the template is fixed; accepted for the contract
+    ap.add_argument("--jinja", action="store_true")                   # the file's chat template is always used when it has one
     ap.add_argument("--no-webui", action="store_true")
     ap.add_argument("--shape", default="20b", choices=["tiny", "20b"], help="decoder shape when the weights are random-init")
     ap.add_argument("--random-init", action="store_true", help="ignore -m and use the seeded weights")
@@ -324,6 +341,11 @@ def main(argv=None) -> int:
     threading.Thread(target=httpd.serve_forever, daemon=True).start()
     try:
         loop.engine = build_engine(args)
+        if args.model and args.model.endswith(".gguf") and not args.random_init:
+            from .tokenizer import BpeTokenizer
+            tok = BpeTokenizer.from_gguf(args.model)  # the file's vocabulary, merges and chat template, when it has them
+            if tok is not None:
+                loop.tokenizer = tok
     except Exception as e:  # the client shows the last lines of stderr when its engine exits
         print("eidola_b200.server: cannot start the engine: %s" % e, file=sys.stderr, flush=True)
         return 1

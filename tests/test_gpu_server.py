@@ -21,10 +21,19 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def test_engine_process_honours_the_llama_server_contract(gpu, tmp_path):
+@pytest.mark.parametrize("with_tokenizer", [False, True], ids=["byte_tokens", "file_tokenizer"])
+def test_engine_process_honours_the_llama_server_contract(gpu, tmp_path, with_tokenizer):
     cfg = tiny_config()
     model = tmp_path / "tiny.gguf"
-    write_gguf(model, _seeded_tensors(cfg))
+    metadata = None
+    if with_tokenizer:  # the file's own vocabulary, merges and chat template (tests/test_tokenizer.py trains them)
+        from tests.test_tokenizer import TEMPLATE, _train
+        tokens, merges, types = _train()
+        metadata = {"tokenizer.ggml.model": "gpt2", "tokenizer.ggml.pre": "gpt2", "tokenizer.ggml.tokens": tokens,
+                    "tokenizer.ggml.merges": merges, "tokenizer.ggml.token_type": types,
+                    "tokenizer.ggml.bos_token_id": np.uint32(tokens.index("<|start|>")),
+                    "tokenizer.ggml.eos_token_id": np.uint32(tokens.index("<|eot|>")), "tokenizer.chat_template": TEMPLATE}
+    write_gguf(model, _seeded_tensors(cfg), metadata)
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]

@@ -142,3 +142,51 @@ def test_requests_that_overlap_share_decode_steps_and_bad_requests_are_refused()
     finally:
         loop.stop.set()
         httpd.shutdown()
+
+
+def test_a_file_tokenizer_serves_templates_and_streams_whole_characters():
+    """With the vocabulary and chat template of a model file the prompt is the template's rendering, and streamed text
+    leaves only when the bytes of a character are complete (tokens may end inside a UTF-8 sequence)."""
+    from tests.test_tokenizer import _tok
+    tok = _tok()
+    reply = tok.encode("é東 ok")
+
+    class Replaying(ScriptedEngine):
+        def prefill(self, slots, prompts):
+            self.calls.append(("prefill", list(slots), [list(map(int, p)) for p in prompts]))
+            self.pos = {s: 1 for s in slots}
+            return (np.array([reply[0]] * len(slots), np.int32),)
+
+        def step(self, slots, q_lens, tokens):
+            out = []
+            for s in slots:
+                out.append(reply[self.pos[s]] if self.pos[s] < len(reply) else tok.eos)
+                self.pos[s] += 1
+            return np.array(out, np.int32), None
+
+    eng = Replaying()
+    loop = EngineLoop(eng, context_tokens=512, tokenizer=tok)
+    httpd = serve(loop, "127.0.0.1", 0, "test-model")
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    url = "http://127.0.0.1:%d" % httpd.server_address[1]
+    loop.start()
+    try:
+        msgs = [{"role": "user", "content": "hello fox"}]
+        out = json.load(_post(url, {"messages": msgs, "max_completion_tokens": 64}))
+        assert out["choices"][0]["message"]["content"] == "é東 ok" and out["choices"][0]["finish_reason"] == "stop"
+        sent = [c for c in eng.calls if c[0] == "prefill"][0][2][0]
+        assert sent == tok.template(msgs)
+        assert tok.decode(sent, skip_control=False).endswith("<|start|>user<|message|>hello fox<|end|><|start|>assistant<|message|>")
+        resp = _post(url, {"messages": msgs, "max_completion_tokens": 64, "stream": True})
+        pieces = []
+        for event in resp.read().decode().split("\n\n"):
+            for line in event.splitlines():
+                if line.startswith("data:") and line[5:].strip() != "[DONE]":
+                    j = json.loads(line[5:])
+                    if j.get("choices") and j["choices"][0]["delta"].get("content"):
+                        pieces.append(j["choices"][0]["delta"]["content"])
+        assert "".join(pieces) == "é東 ok" and "�" not in "".join(pieces)
+        assert len(pieces) < len(reply)  # the bytes of é and 東 arrived over several tokens and left as whole characters
+    finally:
+        loop.stop.set()
+        httpd.shutdown()
