@@ -66,10 +66,15 @@ class ByteTokenizer:
 
 
 class Request:
-    def __init__(self, prompt_ids, max_tokens, temperature=0.0, top_p=1.0, seed=0):
+    def __init__(self, prompt_ids, max_tokens, temperature=0.0, top_p=1.0, seed=0, stop=()):
         self.prompt_ids, self.max_tokens = prompt_ids, max_tokens
         self.temperature, self.top_p, self.seed = temperature, top_p, seed  # temperature 0: greedy
-        self.out: "queue.Queue[tuple[str, object]]" = queue.Queue()  # ("token", id) ... ("done", usage) | ("error", message)
+        self.stop = [s.encode("utf-8") for s in stop if s]  # generation ends before the first of these appears in the text
+        self.text = bytearray()   # bytes generated so far
+        self.sent = 0             # how many of them have left as ("bytes", ...) events
+        self.finish = "length"
+        # ("token", id) and ("bytes", text bytes) ... ("done", usage) | ("error", message)
+        self.out: "queue.Queue[tuple[str, object]]" = queue.Queue()
         self.slot = None
         self.generated = 0
         self.t_arrive = time.perf_counter()
@@ -125,12 +130,32 @@ class EngineLoop(threading.Thread):
     def _deliver(self, r: Request, tok: int) -> None:
         r.generated += 1
         self.stats["generated"] += 1
-        done = r.generated >= r.max_tokens or tok == self.tokenizer.eos
-        if not (tok == self.tokenizer.eos):
+        eos = tok == self.tokenizer.eos
+        done = r.generated >= r.max_tokens or eos
+        if eos:
+            r.finish = "stop"
+        else:
             r.out.put(("token", tok))
+            r.text += self.tokenizer.token_bytes(tok)
+        # stop sequences: the text ends before the first occurrence; bytes that could still turn out to be the start of
+        # one are held back until the next token decides
+        upto = len(r.text)
+        if r.stop:
+            hits = [p for p in (r.text.find(s, max(0, r.sent - len(s) + 1)) for s in r.stop) if p >= 0]
+            if hits:
+                upto, done, r.finish = min(hits), True, "stop"
+            elif not done:
+                for s in r.stop:
+                    for k in range(min(len(s) - 1, len(r.text) - r.sent), 0, -1):
+                        if r.text.endswith(s[:k]):
+                            upto = min(upto, len(r.text) - k)
+                            break
+        if upto > r.sent:
+            r.out.put(("bytes", bytes(r.text[r.sent:upto])))
+            r.sent = upto
         if done:
             r.out.put(("done", {"prompt_tokens": len(r.prompt_ids), "completion_tokens": r.generated,
-                                "total_tokens": len(r.prompt_ids) + r.generated}))
+                                "total_tokens": len(r.prompt_ids) + r.generated, "finish_reason": r.finish}))
             self.engine.release(r.slot)
             self.live.pop(r.slot, None)
             self.last.pop(r.slot, None)
@@ -232,28 +257,40 @@ def make_handler(loop: EngineLoop, alias: str):
             except Exception:
                 return self._json(400, {"error": {"message": "`temperature` must lie in [0, 2], `top_p` in [0, 1], `seed` be an integer",
                                                   "type": "invalid_request_error", "code": 400}})
+            stop = body.get("stop")  # a string or up to 4 of them (crates/eidola-server/src/types.rs: `stop`)
+            stop = [stop] if isinstance(stop, str) else (stop or [])
+            if not (isinstance(stop, list) and len(stop) <= 4 and all(isinstance(x, str) for x in stop)):
+                return self._json(400, {"error": {"message": "`stop` must be a string or up to 4 strings", "type": "invalid_request_error",
+                                                  "code": 400}})
             try:
-                prompt_ids = loop.tokenizer.template(messages)
+                # `tools` / `tool_choice` are for the model's chat template to spell out; nothing here executes a tool
+                if body.get("tools") and getattr(loop.tokenizer, "chat_template", None):
+                    prompt_ids = loop.tokenizer.template(messages, tools=body["tools"], tool_choice=body.get("tool_choice"))
+                else:
+                    prompt_ids = loop.tokenizer.template(messages)
             except Exception as e:  # a chat template may refuse a conversation (roles out of order, ...)
                 return self._json(400, {"error": {"message": "chat template: %s" % e, "type": "invalid_request_error", "code": 400}})
-            req = Request(prompt_ids, max(1, max_tokens), temperature, top_p, seed)
+            req = Request(prompt_ids, max(1, max_tokens), temperature, top_p, seed, stop)
             loop.submit(req)
             rid, created = "chatcmpl-%x" % id(req), int(time.time())
             base = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": body.get("model") or alias}
             if not stream:
-                toks, usage = [], None
+                toks, text, usage = [], bytearray(), None
                 while True:
                     kind, val = req.out.get()
                     if kind == "token":
                         toks.append(val)
+                    elif kind == "bytes":
+                        text += val
                     elif kind == "done":
-                        usage = val
+                        usage = dict(val)
                         break
                     else:
                         return self._json(500, {"error": {"message": str(val), "type": "server_error", "code": 500}})
+                finish = usage.pop("finish_reason")
                 return self._json(200, {"id": rid, "object": "chat.completion", "created": created, "model": base["model"],
-                                        "choices": [{"index": 0, "finish_reason": "stop" if usage["completion_tokens"] < req.max_tokens else "length",
-                                                     "message": {"role": "assistant", "content": loop.tokenizer.decode(toks)},
+                                        "choices": [{"index": 0, "finish_reason": finish,
+                                                     "message": {"role": "assistant", "content": text.decode("utf-8", errors="replace")},
                                                      **({"token_ids": toks} if body.get("return_token_ids") else {})}],
                                         "usage": usage})
             self.send_response(200)
@@ -273,16 +310,19 @@ def make_handler(loop: EngineLoop, alias: str):
                 while True:
                     kind, val = req.out.get()
                     if kind == "token":
-                        text = utf8.decode(loop.tokenizer.token_bytes(val))
+                        continue
+                    if kind == "bytes":
+                        text = utf8.decode(val)
                         if text:
                             event(dict(base, choices=[{"index": 0, "delta": {"content": text}, "finish_reason": None}]))
                     elif kind == "done":
                         tail = utf8.decode(b"", final=True)
                         if tail:
                             event(dict(base, choices=[{"index": 0, "delta": {"content": tail}, "finish_reason": None}]))
-                        event(dict(base, choices=[{"index": 0, "delta": {}, "finish_reason": "stop" if val["completion_tokens"] < req.max_tokens else "length"}]))
+                        usage = dict(val)
+                        event(dict(base, choices=[{"index": 0, "delta": {}, "finish_reason": usage.pop("finish_reason")}]))
                         if include_usage:
-                            event(dict(base, choices=[], usage=val))
+                            event(dict(base, choices=[], usage=usage))
                         event(b"[DONE]")
                         break
                     else:

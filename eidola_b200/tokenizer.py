@@ -180,21 +180,23 @@ class BpeTokenizer:
     def decode(self, ids, skip_control: bool = True) -> str:
         return b"".join(self.token_bytes(i, skip_control) for i in ids).decode("utf-8", errors="replace")
 
-    def template(self, messages) -> list[int]:
-        """`messages` -> prompt ids: the file's chat template when it has one, a plain role header otherwise."""
+    def template(self, messages, tools=None, tool_choice=None) -> list[int]:
+        """`messages` -> prompt ids: the file's chat template when it has one (it also sees `tools` and `tool_choice`, as
+        the request carries them), a plain role header otherwise."""
         norm = []
         for m in messages:
             content = m.get("content") or ""
             if isinstance(content, list):  # OpenAI content parts: keep the text parts
                 content = "".join(p.get("text", "") for p in content if isinstance(p, dict))
-            norm.append({"role": m.get("role", "user"), "content": content})
+            norm.append(dict(m, role=m.get("role", "user"), content=content))  # (tool_calls, name, ... stay for the template)
         if self.chat_template:
             import jinja2
             env = jinja2.Environment(trim_blocks=True, lstrip_blocks=True, undefined=jinja2.ChainableUndefined)
             env.globals["raise_exception"] = _raise
             tok = lambda i: self.tokens[i] if i is not None and 0 <= i < len(self.tokens) else ""  # noqa: E731
-            text = env.from_string(self.chat_template).render(messages=norm, add_generation_prompt=True,
-                                                              bos_token=tok(self.bos_id), eos_token=tok(self.eos_id))
+            text = env.from_string(self.chat_template).render(messages=norm, add_generation_prompt=True, tools=tools,
+                                                              tool_choice=tool_choice, bos_token=tok(self.bos_id),
+                                                              eos_token=tok(self.eos_id))
         else:
             text = "".join("<|%s|>\n%s\n" % (m["role"], m["content"]) for m in norm) + "<|assistant|>\n"
         ids = self.encode(text)

@@ -190,3 +190,87 @@ def test_a_file_tokenizer_serves_templates_and_streams_whole_characters():
     finally:
         loop.stop.set()
         httpd.shutdown()
+
+
+def _replaying_server(tok, reply_text):
+    reply = tok.encode(reply_text)
+
+    class Replaying(ScriptedEngine):
+        def prefill(self, slots, prompts):
+            self.calls.append(("prefill", list(slots), [list(map(int, p)) for p in prompts]))
+            self.pos = {s: 1 for s in slots}
+            return (np.array([reply[0]] * len(slots), np.int32),)
+
+        def step(self, slots, q_lens, tokens):
+            out = []
+            for s in slots:
+                out.append(reply[self.pos[s]] if self.pos[s] < len(reply) else tok.eos)
+                self.pos[s] += 1
+            return np.array(out, np.int32), None
+
+    eng = Replaying()
+    loop = EngineLoop(eng, context_tokens=512, tokenizer=tok)
+    httpd = serve(loop, "127.0.0.1", 0, "test-model")
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    loop.start()
+    return eng, loop, httpd, "http://127.0.0.1:%d" % httpd.server_address[1]
+
+
+def _stream_text(resp):
+    pieces, finish = [], None
+    for event in resp.read().decode().split("\n\n"):
+        for line in event.splitlines():
+            if line.startswith("data:") and line[5:].strip() != "[DONE]":
+                j = json.loads(line[5:])
+                if j.get("choices"):
+                    finish = j["choices"][0].get("finish_reason") or finish
+                    if j["choices"][0]["delta"].get("content"):
+                        pieces.append(j["choices"][0]["delta"]["content"])
+    return pieces, finish
+
+
+def test_stop_sequences_end_the_text_before_their_first_occurrence():
+    """`stop` of the reference server's request type (crates/eidola-server/src/types.rs): up to four strings; the reply
+    ends before the first of them, nothing of it leaks into a stream, and the sequence is released."""
+    from tests.test_tokenizer import _tok
+    tok = _tok()
+    eng, loop, httpd, url = _replaying_server(tok, "hello world, the fox END and more")
+    try:
+        msgs = [{"role": "user", "content": "hi"}]
+        out = json.load(_post(url, {"messages": msgs, "max_completion_tokens": 64, "stop": ["END", " wor"]}))
+        assert out["choices"][0]["message"]["content"] == "hello" and out["choices"][0]["finish_reason"] == "stop"
+        assert out["usage"]["completion_tokens"] < len(tok.encode("hello world, the fox END and more"))
+        out = json.load(_post(url, {"messages": msgs, "max_completion_tokens": 64, "stop": "END"}))
+        assert out["choices"][0]["message"]["content"] == "hello world, the fox "
+        pieces, finish = _stream_text(_post(url, {"messages": msgs, "max_completion_tokens": 64, "stop": ["END"], "stream": True}))
+        assert "".join(pieces) == "hello world, the fox " and finish == "stop" and not any("E" in p for p in pieces)
+        # a stop sequence that never comes: the whole reply, ended by the end-of-sequence token
+        out = json.load(_post(url, {"messages": msgs, "max_completion_tokens": 64, "stop": ["ENDE", "xyz"]}))
+        assert out["choices"][0]["message"]["content"] == "hello world, the fox END and more" and out["choices"][0]["finish_reason"] == "stop"
+        out = json.load(_post(url, {"messages": msgs, "max_completion_tokens": 3}))
+        assert out["choices"][0]["finish_reason"] == "length" and out["usage"]["completion_tokens"] == 3
+        for bad in ({"stop": ["a", "b", "c", "d", "e"]}, {"stop": 5}, {"stop": [1]}):
+            try:
+                _post(url, dict({"messages": msgs}, **bad))
+                assert False
+            except urllib.error.HTTPError as e:
+                assert e.code == 400
+        assert sorted(eng.free) == [0, 1, 2, 3]
+    finally:
+        loop.stop.set()
+        httpd.shutdown()
+
+
+def test_tools_reach_the_chat_template():
+    from tests.test_tokenizer import TEMPLATE, _tok
+    tok = _tok()
+    tok.chat_template = "{% if tools %}tools {{ tools | length }} {{ tools[0]['function']['name'] }} {% endif %}" + TEMPLATE
+    eng, loop, httpd, url = _replaying_server(tok, "ok")
+    try:
+        tools = [{"type": "function", "function": {"name": "lookup", "parameters": {"type": "object"}}}]
+        json.load(_post(url, {"messages": [{"role": "user", "content": "hi"}], "max_completion_tokens": 4, "tools": tools, "tool_choice": "auto"}))
+        sent = [c for c in eng.calls if c[0] == "prefill"][-1][2][0]
+        assert tok.decode(sent, skip_control=False).startswith("tools 1 lookup ")
+    finally:
+        loop.stop.set()
+        httpd.shutdown()
