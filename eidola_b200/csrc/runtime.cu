@@ -272,7 +272,7 @@ __global__ void synth_kernel(void* out, int64_t n, uint64_t seed, uint64_t sid, 
       ((float*)out)[i] = eb_uniform(seed, sid, idx0 + (uint64_t)i, a, b);
     } else {
       const float v = __fmul_rn(eb_normal(seed, sid, idx0 + (uint64_t)i), a);
-      if (KIND == 0) ((uint16_t*)out)[i] = eb_f32_to_bf16(v);
+      if (KIND == 0) ((uint16_t*)out)[i] = eb_bf16_from_f32(v);
       if (KIND == 1) ((float*)out)[i] = v;
       if (KIND == 2) ((uint8_t*)out)[i] = eb_f32_to_e4m3(v);
     }
@@ -338,7 +338,7 @@ __global__ void quant_weight_f32_kernel(const float* w, int64_t ld, int64_t nrow
 __global__ void f32_to_bf16_kernel(const float* in, uint16_t* out, int64_t n) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (; i < n; i += stride) out[i] = eb_f32_to_bf16(in[i]);
+  for (; i < n; i += stride) out[i] = eb_bf16_from_f32(in[i]);
 }
 
 // Local KV heads [head0, head0 + n_local) of a cache whose global layout is [pages][2][n_total][page][dim]:
@@ -352,7 +352,7 @@ __global__ void synth_kv_heads_kernel(uint16_t* out, int64_t n, int n_total, int
     const int64_t h = (i / head_elems) % n_local;
     const int64_t pk = i / ((int64_t)head_elems * n_local);  // page * 2 + (K or V)
     const uint64_t g = (uint64_t)((pk * n_total + head0 + h) * head_elems + e);
-    out[i] = eb_f32_to_bf16(eb_normal(seed, sid, g));
+    out[i] = eb_bf16_from_f32(eb_normal(seed, sid, g));
   }
 }
 

@@ -151,7 +151,7 @@ EB_HD float eb_uniform(uint64_t seed, uint64_t stream, uint64_t idx, float lo, f
 /* ---- number formats ---------------------------------------------------- */
 
 /* fp32 -> bf16 bits, round to nearest even; NaN stays NaN. */
-EB_HD uint16_t eb_f32_to_bf16(float f) {
+EB_HD uint16_t eb_bf16_from_f32(float f) {
   uint32_t u = eb_f2u(f);
   if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x0040u);
   u += 0x7FFFu + ((u >> 16) & 1u);

@@ -36,7 +36,7 @@
 namespace {
 
 inline float bf(uint16_t h) { return eb_bf16_to_f32(h); }
-inline uint16_t tobf(float f) { return eb_f32_to_bf16(f); }
+inline uint16_t tobf(float f) { return eb_bf16_from_f32(f); }
 
 struct E4Table {
   float v[256];

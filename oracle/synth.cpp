@@ -61,7 +61,7 @@ void orc_synth_normal_f32(uint64_t seed, uint64_t stream, uint64_t idx0, int64_t
 
 void orc_synth_normal_bf16(uint64_t seed, uint64_t stream, uint64_t idx0, int64_t n, float scale, uint16_t* out) {
 #pragma omp parallel for schedule(static)
-  for (int64_t i = 0; i < n; ++i) out[i] = eb_f32_to_bf16(eb_normal(seed, stream, idx0 + (uint64_t)i) * scale);
+  for (int64_t i = 0; i < n; ++i) out[i] = eb_bf16_from_f32(eb_normal(seed, stream, idx0 + (uint64_t)i) * scale);
 }
 
 void orc_synth_uniform_f32(uint64_t seed, uint64_t stream, uint64_t idx0, int64_t n, float lo, float hi, float* out) {
@@ -82,7 +82,7 @@ void orc_e4m3_decode(const uint8_t* q, float* x, int64_t n) {
   for (int64_t i = 0; i < n; ++i) x[i] = eb_e4m3_to_f32(q[i]);
 }
 void orc_bf16_encode(const float* x, uint16_t* h, int64_t n) {
-  for (int64_t i = 0; i < n; ++i) h[i] = eb_f32_to_bf16(x[i]);
+  for (int64_t i = 0; i < n; ++i) h[i] = eb_bf16_from_f32(x[i]);
 }
 void orc_bf16_decode(const uint16_t* h, float* x, int64_t n) {
   for (int64_t i = 0; i < n; ++i) x[i] = eb_bf16_to_f32(h[i]);

@@ -49,3 +49,22 @@ def test_oracle_config_mirror_matches_the_engine_binding():
     assert C.sizeof(capi.Config) == C.sizeof(orc.Config)
     a, b = capi.make_config(n_layers=3, vocab=17), orc.make_config(n_layers=3, vocab=17)
     assert bytes(a) == bytes(b)
+
+
+def test_a_plain_c_host_compiles_links_and_runs(tmp_path):
+    """The headers are C (not only C++): a C11 host built with -pedantic links against the library and drives the
+    entry points that need no device."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    gcc = shutil.which("gcc")
+    assert gcc, "gcc is part of the image"
+    lib = root / "eidola_b200" / "lib"
+    exe = tmp_path / "c_host"
+    subprocess.run([gcc, "-std=c11", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", str(root / "include"),
+                    str(root / "tests" / "c_host" / "host.c"), "-L", str(lib), "-leidola_b200", "-Wl,-rpath," + str(lib), "-lm", "-o", str(exe)],
+                   check=True, capture_output=True, text=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
+    assert "c host ok" in r.stdout and "0x3f80" in r.stdout
