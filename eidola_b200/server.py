@@ -73,6 +73,7 @@ class Request:
         self.text = bytearray()   # bytes generated so far
         self.sent = 0             # how many of them have left as ("bytes", ...) events
         self.finish = "length"
+        self.cancelled = False    # set by the HTTP thread when the client has gone away: the loop ends the sequence
         # ("token", id) and ("bytes", text bytes) ... ("done", usage) | ("error", message)
         self.out: "queue.Queue[tuple[str, object]]" = queue.Queue()
         self.slot = None
@@ -131,7 +132,7 @@ class EngineLoop(threading.Thread):
         r.generated += 1
         self.stats["generated"] += 1
         eos = tok == self.tokenizer.eos
-        done = r.generated >= r.max_tokens or eos
+        done = r.generated >= r.max_tokens or eos or r.cancelled
         if eos:
             r.finish = "stop"
         else:
@@ -177,6 +178,10 @@ class EngineLoop(threading.Thread):
             except Exception as e:  # an engine error ends every request in flight with a message, not a hang
                 for r in list(self.live.values()):
                     r.out.put(("error", "engine: %s" % e))
+                    try:
+                        self.engine.release(r.slot)  # the pages go back even when the step failed
+                    except Exception:
+                        pass
                 self.live.clear()
                 self.last.clear()
 
@@ -329,7 +334,7 @@ def make_handler(loop: EngineLoop, alias: str):
                         event({"error": {"message": str(val), "type": "server_error", "code": 500}})
                         break
             except (BrokenPipeError, ConnectionResetError):
-                pass  # the client went away; the sequence finishes and is released by the loop
+                req.cancelled = True  # the client went away: the loop ends the sequence at its next token and releases it
             self.close_connection = True
 
     return Handler

@@ -8,6 +8,7 @@ with `choices[0].delta.content`, a `usage` event when `stream_options.include_us
 (crates/eidola-app-core/src/lib.rs:7232-7340)."""
 import json
 import threading
+import time
 import urllib.request
 
 import numpy as np
@@ -271,6 +272,43 @@ def test_tools_reach_the_chat_template():
         json.load(_post(url, {"messages": [{"role": "user", "content": "hi"}], "max_completion_tokens": 4, "tools": tools, "tool_choice": "auto"}))
         sent = [c for c in eng.calls if c[0] == "prefill"][-1][2][0]
         assert tok.decode(sent, skip_control=False).startswith("tools 1 lookup ")
+    finally:
+        loop.stop.set()
+        httpd.shutdown()
+
+
+def test_a_client_that_goes_away_frees_its_sequence_and_an_engine_error_frees_them_all():
+    import socket
+    eng, loop, httpd, url = _start()
+    loop.start()
+    try:
+        # a streaming client that hangs up after the first bytes: the sequence ends long before max_completion_tokens
+        host, port = httpd.server_address
+        body = json.dumps({"messages": [{"role": "user", "content": "x"}], "max_completion_tokens": 400, "stream": True}).encode()
+        with socket.create_connection((host, port)) as sk:
+            sk.sendall(b"POST /v1/chat/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\nContent-Length: %d\r\n\r\n" % len(body) + body)
+            sk.recv(256)
+            sk.setsockopt(socket.SOL_SOCKET, socket.SO_LINGER, __import__("struct").pack("ii", 1, 0))  # close with a reset
+        deadline = time.time() + 10
+        while time.time() < deadline and len(eng.free) < 4:
+            time.sleep(0.02)
+        assert sorted(eng.free) == [0, 1, 2, 3]
+        assert len([c for c in eng.calls if c[0] == "step"]) < 380  # (400 tokens were asked for)
+        # an engine that fails a step: every request in flight gets the message, every slot goes back
+        real_step = eng.step
+
+        def failing(slots, q_lens, tokens):
+            raise RuntimeError("device lost")
+        eng.step = failing
+        try:
+            _post(url, {"messages": [{"role": "user", "content": "y"}], "max_completion_tokens": 8})
+            assert False
+        except urllib.error.HTTPError as e:
+            assert e.code == 500 and "device lost" in json.load(e)["error"]["message"]
+        eng.step = real_step
+        assert sorted(eng.free) == [0, 1, 2, 3]
+        out = json.load(_post(url, {"messages": [{"role": "user", "content": "z"}], "max_completion_tokens": 4}))
+        assert out["usage"]["completion_tokens"] == 4  # the loop lives on
     finally:
         loop.stop.set()
         httpd.shutdown()
