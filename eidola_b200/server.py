@@ -74,6 +74,8 @@ class Request:
         self.sent = 0             # how many of them have left as ("bytes", ...) events
         self.finish = "length"
         self.cancelled = False    # set by the HTTP thread when the client has gone away: the loop ends the sequence
+        self.history = []         # the tokens whose K and V are in the sequence's pages
+        self.cached_tokens = 0    # how many of the prompt's tokens were found in an idle sequence's pages
         # ("token", id) and ("bytes", text bytes) ... ("done", usage) | ("error", message)
         self.out: "queue.Queue[tuple[str, object]]" = queue.Queue()
         self.slot = None
@@ -95,7 +97,12 @@ class EngineLoop(threading.Thread):
         self.last: dict[int, int] = {}
         self.ready = threading.Event()
         self.stop = threading.Event()
-        self.stats = {"steps": 0, "prefill_tokens": 0, "generated": 0, "evicted": 0}
+        self.stats = {"steps": 0, "prefill_tokens": 0, "generated": 0, "evicted": 0, "prefix_hits": 0, "prefix_tokens": 0}
+        # Finished sequences stay in the page pool, unpinned, with the tokens their pages hold: a chat client sends the
+        # whole conversation again with every turn, and the next turn then prefills only what is new.  The engine evicts
+        # them, least recently used first, when it needs their pages (eb_engine_seq_admit_evicting).
+        self.idle: dict[int, list[int]] = {}
+        self.min_prefix = 16      # shorter common prefixes are not worth a sequence of their own
 
     def submit(self, req: Request) -> None:
         self.inbox.put(req)
@@ -111,22 +118,58 @@ class EngineLoop(threading.Thread):
                 req.out.put(("error", "the request needs %d tokens of context, the engine was started with -c %d"
                              % (len(req.prompt_ids) + req.max_tokens, self.context_tokens)))
                 continue
-            try:
-                slot, evicted = self.engine.admit_evicting(0)
-            except Exception as e:  # pool exhausted by live sequences: refuse, nothing changed
-                req.out.put(("error", "no room for another sequence: %s" % e))
-                continue
-            self.stats["evicted"] += len(evicted)
-            if req.temperature > 0:  # from the first generated token on (the prefill step draws it)
-                self.engine.sampling(slot, req.temperature, req.top_p, req.seed)
+            slot = self._reuse_idle(req)
+            if slot is None:
+                try:
+                    slot, evicted = self.engine.admit_evicting(0)
+                except Exception as e:  # pool exhausted by live sequences: refuse, nothing changed
+                    req.out.put(("error", "no room for another sequence: %s" % e))
+                    continue
+                self.stats["evicted"] += len(evicted)
+                for s in evicted:
+                    self.idle.pop(s, None)
+                if req.temperature > 0:  # from the first generated token on (the prefill step draws it)
+                    self.engine.sampling(slot, req.temperature, req.top_p, req.seed)
             req.slot = slot
             fresh.append(req)
         if fresh:
-            first = self.engine.prefill([r.slot for r in fresh], [np.asarray(r.prompt_ids, np.int32) for r in fresh])[0]
+            first = self.engine.prefill([r.slot for r in fresh],
+                                        [np.asarray(r.prompt_ids[r.cached_tokens:], np.int32) for r in fresh])[0]
             for r, tok in zip(fresh, first):
-                self.stats["prefill_tokens"] += len(r.prompt_ids)
+                self.stats["prefill_tokens"] += len(r.prompt_ids) - r.cached_tokens
+                r.history = list(r.prompt_ids)
                 self.live[r.slot] = r
                 self._deliver(r, int(tok))
+
+    def _reuse_idle(self, req: Request):
+        """The idle sequence whose pages hold the longest prefix of the request's prompt, cut back to that prefix and
+        pinned again; None when no idle sequence shares min_prefix tokens (or the engine cannot cut sequences)."""
+        if not self.idle or not hasattr(self.engine, "truncate"):
+            return None
+        best, best_len = None, 0
+        for slot, held in self.idle.items():
+            n, lim = 0, min(len(held), len(req.prompt_ids) - 1)  # at least one token is left to run: its logits are needed
+            while n < lim and held[n] == req.prompt_ids[n]:
+                n += 1
+            if n > best_len:
+                best, best_len = slot, n
+        if best is None or best_len < self.min_prefix:
+            return None
+        del self.idle[best]
+        try:
+            self.engine.truncate(best, best_len)
+            self.engine.pin(best, True)
+            self.engine.sampling(best, req.temperature if req.temperature > 0 else 0.0, req.top_p, req.seed)
+        except Exception:  # (for instance a page ring that no longer holds the window before the cut): start afresh
+            try:
+                self.engine.release(best)
+            except Exception:
+                pass
+            return None
+        req.cached_tokens = best_len
+        self.stats["prefix_hits"] += 1
+        self.stats["prefix_tokens"] += best_len
+        return best
 
     def _deliver(self, r: Request, tok: int) -> None:
         r.generated += 1
@@ -155,9 +198,16 @@ class EngineLoop(threading.Thread):
             r.out.put(("bytes", bytes(r.text[r.sent:upto])))
             r.sent = upto
         if done:
-            r.out.put(("done", {"prompt_tokens": len(r.prompt_ids), "completion_tokens": r.generated,
-                                "total_tokens": len(r.prompt_ids) + r.generated, "finish_reason": r.finish}))
-            self.engine.release(r.slot)
+            usage = {"prompt_tokens": len(r.prompt_ids), "completion_tokens": r.generated,
+                     "total_tokens": len(r.prompt_ids) + r.generated, "finish_reason": r.finish}
+            if r.cached_tokens:
+                usage["prompt_tokens_details"] = {"cached_tokens": r.cached_tokens}
+            r.out.put(("done", usage))
+            if hasattr(self.engine, "truncate") and len(r.history) >= self.min_prefix:
+                self.engine.pin(r.slot, False)  # stays in the pool for the conversation's next turn, evictable
+                self.idle[r.slot] = r.history
+            else:
+                self.engine.release(r.slot)
             self.live.pop(r.slot, None)
             self.last.pop(r.slot, None)
         else:
@@ -172,6 +222,8 @@ class EngineLoop(threading.Thread):
                     continue
                 slots = sorted(self.live)
                 nxt, _ = self.engine.step(slots, [1] * len(slots), [self.last[s] for s in slots])
+                for s in slots:
+                    self.live[s].history.append(self.last[s])  # its K and V are in the pages now
                 self.stats["steps"] += 1
                 for s, tok in zip(slots, nxt):
                     self._deliver(self.live[s], int(tok))
@@ -205,6 +257,12 @@ class EngineAdapter:
 
     def sampling(self, slot, temperature, top_p, seed):
         self.eng.sampling(slot, temperature, top_p, seed)
+
+    def truncate(self, slot, new_len):
+        self.eng.truncate(slot, new_len)
+
+    def pin(self, slot, pinned):
+        self.eng.pin(slot, pinned)
 
     def release(self, slot):
         self.eng.release(slot)

@@ -89,7 +89,14 @@ def test_engine_process_honours_the_llama_server_contract(gpu, tmp_path, with_to
         s3 = ask({"temperature": 1.5, "top_p": 0.95, "seed": 12})
         assert s1 == s2 and len(s1) >= 1
         assert s1 != g or s3 != g, (g, s1, s3)  # 4096-way draws at temperature 1.5: both equal to greedy would be no sampling
-        print(f"engine process: healthy, streamed {chunks} content chunks and usage {usage} in {dt * 1e3:.1f} ms")
+        # the next turn of the conversation finds the first turn's pages: only the new tokens are prefilled
+        turn2 = dict(blocking, messages=body["messages"] + [{"role": "assistant", "content": a["choices"][0]["message"]["content"]},
+                                                            {"role": "user", "content": "And then?"}])
+        t2 = json.load(urllib.request.urlopen(urllib.request.Request(url + "/v1/chat/completions", data=json.dumps(turn2).encode()), timeout=60))
+        assert t2["usage"]["prompt_tokens_details"]["cached_tokens"] >= 16 and t2["usage"]["completion_tokens"] >= 1
+        assert t2["usage"]["prompt_tokens"] > a["usage"]["prompt_tokens"]
+        print(f"engine process: healthy, streamed {chunks} content chunks and usage {usage} in {dt * 1e3:.1f} ms; "
+              f"second turn: {t2['usage']['prompt_tokens_details']['cached_tokens']} of {t2['usage']['prompt_tokens']} prompt tokens from the cache")
     finally:
         child.kill()                            # the client ends its engine with SIGKILL (kill_on_drop)
         child.wait(timeout=30)

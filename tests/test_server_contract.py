@@ -312,3 +312,82 @@ def test_a_client_that_goes_away_frees_its_sequence_and_an_engine_error_frees_th
     finally:
         loop.stop.set()
         httpd.shutdown()
+
+
+def test_the_next_turn_of_a_conversation_prefills_only_what_is_new():
+    """A chat client sends the whole conversation with every turn: the pages of the finished turn stay in the pool and the
+    next request that starts with the same tokens is cut back to the common prefix and prefills the rest."""
+    class Caching(ScriptedEngine):
+        def __init__(self):
+            super().__init__()
+            self.len = {}
+
+        def admit_evicting(self, context_len):
+            if not self.free:  # evict the least recently admitted idle sequence
+                victim = next(s for s in self.len if not self.pinned.get(s))
+                self.len.pop(victim)
+                self.free.append(victim)
+                self.calls.append(("evict", victim))
+                slot = self.free.pop(0)
+                self.len[slot], self.pinned[slot] = 0, True
+                return slot, [victim]
+            slot = self.free.pop(0)
+            self.len[slot] = 0
+            self.pinned = getattr(self, "pinned", {})
+            self.pinned[slot] = True
+            return slot, []
+
+        def prefill(self, slots, prompts):
+            for s, p in zip(slots, prompts):
+                self.len[s] += len(p)
+            return super().prefill(slots, prompts)
+
+        def step(self, slots, q_lens, tokens):
+            for s in slots:
+                self.len[s] += 1
+            return super().step(slots, q_lens, tokens)
+
+        def truncate(self, slot, new_len):
+            assert 0 < new_len <= self.len[slot]
+            self.calls.append(("truncate", slot, new_len))
+            self.len[slot] = new_len
+
+        def pin(self, slot, pinned):
+            self.pinned[slot] = pinned
+
+        def release(self, slot):
+            self.len.pop(slot, None)
+            super().release(slot)
+
+    eng = Caching()
+    eng.pinned = {}
+    loop = EngineLoop(eng, context_tokens=2048)
+    httpd = serve(loop, "127.0.0.1", 0, "test-model")
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    url = "http://127.0.0.1:%d" % httpd.server_address[1]
+    loop.start()
+    try:
+        turn1 = [{"role": "user", "content": "tell me about foxes, briefly please"}]
+        a = json.load(_post(url, {"messages": turn1, "max_completion_tokens": 6}))
+        assert "prompt_tokens_details" not in a["usage"]
+        p1 = ByteTokenizer.template(turn1)
+        turn2 = turn1 + [{"role": "assistant", "content": a["choices"][0]["message"]["content"]}, {"role": "user", "content": "and dogs?"}]
+        b = json.load(_post(url, {"messages": turn2, "max_completion_tokens": 6}))
+        p2 = ByteTokenizer.template(turn2)
+        cached = b["usage"]["prompt_tokens_details"]["cached_tokens"]
+        # the pages hold the first prompt and the five reply tokens that were fed back (the sixth never ran); the second
+        # prompt repeats all of it
+        assert p2[:len(p1)] == p1
+        assert cached == len(p1) + 5 and b["usage"]["prompt_tokens"] == len(p2)
+        pre = [c for c in eng.calls if c[0] == "prefill"]
+        assert pre[0][2] == [len(p1)] and pre[1][2] == [len(p2) - cached]  # only the new tokens ran
+        assert ("truncate", pre[1][1][0], cached) in eng.calls and pre[1][1] == pre[0][1]  # the same slot, cut back
+        assert loop.stats["prefix_hits"] == 1 and loop.stats["prefix_tokens"] == cached
+        # an unrelated conversation gets a sequence of its own; idle ones are evicted when the slots run out
+        for i in range(5):
+            json.load(_post(url, {"messages": [{"role": "user", "content": "%d: something else entirely, long enough" % i}], "max_completion_tokens": 2}))
+        assert any(c[0] == "evict" for c in eng.calls)
+        assert all(s in eng.len for s in loop.idle) and len(loop.idle) <= eng.max_seqs
+    finally:
+        loop.stop.set()
+        httpd.shutdown()
