@@ -126,6 +126,7 @@ struct eb_engine {
   bool head_rows_on = false;
   std::vector<int32_t> head_rows;
   // per slot: log2(e) / temperature (0: greedy), top_p in units of 2^-24, seed of the counter-based random numbers
+  std::vector<int32_t> high_len;  // per slot: the largest length the sequence has had (what its page rings were written up to)
   std::vector<float> samp_scale;
   std::vector<uint32_t> samp_q24;
   std::vector<uint64_t> samp_seed;
@@ -980,6 +981,7 @@ int32_t eb_engine_create_tp(const eb_config* cfg, int32_t tp_rank, int32_t tp_si
   }
   e->layers.resize((size_t)c.n_layers);
   e->uploaded_pages.assign((size_t)c.max_seqs, 0);
+  e->high_len.assign((size_t)c.max_seqs, 0);
   e->samp_scale.assign((size_t)c.max_seqs, 0.f);
   e->samp_q24.assign((size_t)c.max_seqs, 1u << 24);
   e->samp_seed.assign((size_t)c.max_seqs, 0);
@@ -1188,6 +1190,7 @@ int32_t eb_engine_seq_admit(eb_engine* e, int32_t context_len, int32_t* slot) {
   EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_seq_admit: a step is in flight");
   EB_TRY(eb_sched_admit(e->sched, context_len, slot));
   e->uploaded_pages[(size_t)*slot] = 0;
+  e->high_len[(size_t)*slot] = context_len;
   e->samp_scale[(size_t)*slot] = 0.f;  // a new sequence decodes greedily until eb_engine_seq_sampling says otherwise
   return EB_OK;
 }
@@ -1199,6 +1202,7 @@ int32_t eb_engine_seq_admit_evicting(eb_engine* e, int32_t context_len, int32_t*
   EB_TRY(eb_sched_admit_evicting(e->sched, context_len, e->tick, slot, h_evicted, cap, n_evicted));
   for (int32_t i = 0; i < *n_evicted; ++i) e->uploaded_pages[(size_t)h_evicted[i]] = 0;
   e->uploaded_pages[(size_t)*slot] = 0;
+  e->high_len[(size_t)*slot] = context_len;
   e->samp_scale[(size_t)*slot] = 0.f;
   return EB_OK;
 }
@@ -1236,6 +1240,15 @@ int32_t eb_engine_seq_release(eb_engine* e, int32_t slot) {
 int32_t eb_engine_seq_truncate(eb_engine* e, int32_t slot, int32_t new_len) {
   EB_REQUIRE(e, EB_ERR_ARG, "eb_engine_seq_truncate: null");
   EB_REQUIRE(!e->in_flight, EB_ERR_STATE, "eb_engine_seq_truncate: a step is in flight");
+  if (e->ring && slot >= 0 && slot < e->c.max_seqs && new_len >= 0) {
+    // Sliding-window layers keep a ring of pages: logical page p shares its ring page with p + ring.  The window before
+    // the cut is still there only while no page written later has taken the place of its first page.
+    const int32_t P = e->c.page_size, high = e->high_len[(size_t)slot];
+    const int32_t first_needed = std::max(0, new_len - e->c.window - 1) / P, last_written = std::max(0, high - 1) / P;
+    EB_REQUIRE(first_needed + e->ring > last_written, EB_ERR_UNSUPPORTED,
+               "eb_engine_seq_truncate: the page rings of slot %d were written up to token %d and no longer hold the window before %d",
+               slot, high, new_len);
+  }
   EB_TRY(eb_sched_truncate(e->sched, slot, new_len));
   const int32_t pages = (new_len + e->c.page_size - 1) / e->c.page_size;
   e->uploaded_pages[(size_t)slot] = std::min(e->uploaded_pages[(size_t)slot], pages);
@@ -1301,6 +1314,8 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
     if (rc != EB_OK) return rollback(rc);
     grown = i + 1;
   }
+  for (int i = 0; i < n_seqs; ++i)  // (kept when the step is refused below: only ever too cautious)
+    e->high_len[(size_t)h_slots[i]] = std::max(e->high_len[(size_t)h_slots[i]], old_len[(size_t)i] + h_q_lens[i]);
   const int32_t rc_body = step_launch_body(e, h_slots, h_q_lens, n_seqs, h_tokens, T, max_q);
   if (rc_body != EB_OK) return rollback(rc_body);
   ++e->tick;

@@ -608,6 +608,9 @@ int32_t eb_engine_seq_admit_evicting(eb_engine* e, int32_t context_len, int32_t*
                                      int32_t* n_evicted);
 int32_t eb_engine_seq_pin(eb_engine* e, int32_t slot, int32_t pinned);
 int32_t eb_engine_seq_release(eb_engine* e, int32_t slot);
+/* Cut a sequence back to new_len tokens (rejected drafts; the common prefix of a conversation's next turn).  With
+ * window_ring a cut deeper than the rings still cover (about eb_engine_chunk_tokens tokens below the longest the
+ * sequence has been) is refused with EB_ERR_UNSUPPORTED and changes nothing. */
 int32_t eb_engine_seq_truncate(eb_engine* e, int32_t slot, int32_t new_len);
 /* Roll n sequences back in one call (after a verify step: new length = old length + accepted drafts + 1). */
 int32_t eb_engine_seq_truncate_many(eb_engine* e, const int32_t* h_slots, const int32_t* h_new_lens, int32_t n);

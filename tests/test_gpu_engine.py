@@ -224,3 +224,30 @@ def test_window_ring_is_bit_identical_to_full_pages(gpu):
         toks = outs[0][0]
     mem_full, mem_ring = engines[0][0].memory()["kv"], engines[1][0].memory()["kv"]
     assert mem_ring < mem_full
+
+
+def test_page_rings_refuse_a_cut_they_no_longer_cover(gpu):
+    """Sliding-window layers with page rings hold the window plus one chunk: rolling back a few rejected drafts is fine, a
+    cut far below the longest the sequence has been is refused (the ring pages there have been overwritten) and changes
+    nothing; without rings any cut is fine."""
+    import eidola_b200 as eb
+    for ring in (1, 0):
+        cfg = tiny_config(window_ring=ring, num_pages=96, max_pages_per_seq=40, max_tokens=20)
+        eng = eb.Engine(cfg)
+        eng.kv_fill_synth()
+        slot = eng.admit(40)
+        rng = np.random.default_rng(1)
+        for _ in range(30):  # 150 more tokens: far more than window + chunk
+            eng.step([slot], [5], rng.integers(0, cfg.vocab, size=5).astype(np.int32))
+        assert eng.seq_len(slot) == 190
+        eng.truncate(slot, 187)  # rejected drafts
+        assert eng.seq_len(slot) == 187
+        if ring:
+            with pytest.raises(eb.EbError) as err:
+                eng.truncate(slot, 20)
+            assert "ring" in str(err.value) and eng.seq_len(slot) == 187
+        else:
+            eng.truncate(slot, 20)
+            assert eng.seq_len(slot) == 20
+        eng.step([slot], [1], np.array([3], np.int32))
+        assert int(eb.status_read()) == 0
