@@ -75,6 +75,8 @@ class Request:
         self.finish = "length"
         self.cancelled = False    # set by the HTTP thread when the client has gone away: the loop ends the sequence
         self.history = []         # the tokens whose K and V are in the sequence's pages
+        self.ngram = {}           # (a, b) -> index of the token that followed the last occurrence of "a b" (draft lookup)
+        self.indexed = 0          # history tokens the index covers
         self.cached_tokens = 0    # how many of the prompt's tokens were found in an idle sequence's pages
         # ("token", id) and ("bytes", text bytes) ... ("done", usage) | ("error", message)
         self.out: "queue.Queue[tuple[str, object]]" = queue.Queue()
@@ -103,6 +105,10 @@ class EngineLoop(threading.Thread):
         # them, least recently used first, when it needs their pages (eb_engine_seq_admit_evicting).
         self.idle: dict[int, list[int]] = {}
         self.min_prefix = 16      # shorter common prefixes are not worth a sequence of their own
+        # Draft tokens without a draft model: when the last two tokens occurred before in the sequence, the tokens that
+        # followed them then are proposed now and verified in the same step (q_len = 1 + drafts: the verify kernels); the
+        # accepted ones cost no step of their own.  Greedy sequences only; 0 = off.
+        self.spec = 0
 
     def submit(self, req: Request) -> None:
         self.inbox.put(req)
@@ -138,6 +144,7 @@ class EngineLoop(threading.Thread):
             for r, tok in zip(fresh, first):
                 self.stats["prefill_tokens"] += len(r.prompt_ids) - r.cached_tokens
                 r.history = list(r.prompt_ids)
+                r.engine_len = len(r.history)
                 self.live[r.slot] = r
                 self._deliver(r, int(tok))
 
@@ -203,6 +210,7 @@ class EngineLoop(threading.Thread):
             if r.cached_tokens:
                 usage["prompt_tokens_details"] = {"cached_tokens": r.cached_tokens}
             r.out.put(("done", usage))
+            self._settle(r)
             if hasattr(self.engine, "truncate") and len(r.history) >= self.min_prefix:
                 self.engine.pin(r.slot, False)  # stays in the pool for the conversation's next turn, evictable
                 self.idle[r.slot] = r.history
@@ -213,6 +221,26 @@ class EngineLoop(threading.Thread):
         else:
             self.last[r.slot] = tok
 
+    def _settle(self, r: Request) -> None:
+        """Cut the engine's sequence back to the tokens that count (rejected drafts ran through the layers too)."""
+        if getattr(r, "engine_len", 0) > len(r.history):
+            self.engine.truncate(r.slot, len(r.history))
+        r.engine_len = len(r.history)
+
+    def _drafts(self, r: Request, last: int) -> list[int]:
+        """Up to self.spec tokens that followed the previous occurrence of (second to last token, last token)."""
+        if self.spec <= 0 or r.temperature > 0 or not r.history or not hasattr(self.engine, "truncate"):
+            return []
+        h = r.history
+        for i in range(max(r.indexed, 2), len(h)):  # index "h[i-2] h[i-1]" -> i as the history grows
+            r.ngram[(h[i - 2], h[i - 1])] = i
+        r.indexed = len(h)
+        at = r.ngram.get((h[-1], last))
+        if at is None:
+            return []
+        room = min(self.spec, r.max_tokens - r.generated - 1, self.context_tokens - len(h) - 2)
+        return [int(t) for t in h[at:at + max(0, room)]]
+
     def run(self) -> None:
         self.ready.set()
         while not self.stop.is_set():
@@ -221,12 +249,24 @@ class EngineLoop(threading.Thread):
                 if not self.live:
                     continue
                 slots = sorted(self.live)
-                nxt, _ = self.engine.step(slots, [1] * len(slots), [self.last[s] for s in slots])
-                for s in slots:
-                    self.live[s].history.append(self.last[s])  # its K and V are in the pages now
+                fed = {s: [self.last[s]] + self._drafts(self.live[s], self.last[s]) for s in slots}
+                nxt, _ = self.engine.step(slots, [len(fed[s]) for s in slots], [t for s in slots for t in fed[s]])
                 self.stats["steps"] += 1
-                for s, tok in zip(slots, nxt):
-                    self._deliver(self.live[s], int(tok))
+                row = 0
+                for s in slots:
+                    r, x = self.live[s], fed[s]
+                    y = [int(t) for t in nxt[row:row + len(x)]]
+                    row += len(x)
+                    r.engine_len = len(r.history) + len(x)
+                    # y[i] follows x[i]; draft x[i + 1] stands if it is what the model says after x[i]
+                    for i in range(len(x)):
+                        r.history.append(x[i])  # its K and V are in the pages and it counts
+                        self._deliver(r, y[i])
+                        if s not in self.live or i + 1 == len(x) or x[i + 1] != y[i]:
+                            break
+                        self.stats["drafts_accepted"] = self.stats.get("drafts_accepted", 0) + 1
+                    if s in self.live:
+                        self._settle(r)
             except Exception as e:  # an engine error ends every request in flight with a message, not a hang
                 for r in list(self.live.values()):
                     r.out.put(("error", "engine: %s" % e))
@@ -436,10 +476,13 @@ def main(argv=None) -> int:
     ap.add_argument("--random-init", action="store_true", help="ignore -m and use the seeded weights")
     ap.add_argument("--seqs", type=int, default=64, help="concurrent sequences")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--spec-lookup", type=int, default=0,
+                    help="draft up to this many tokens per step from the sequence's own earlier text and verify them in the step (0 = off)")
     ap.add_argument("--device", type=int, default=0)
     args = ap.parse_args(argv)
     holder = {}
     loop = EngineLoop(None, args.ctx)
+    loop.spec = max(0, min(args.spec_lookup, 5))  # the engine is created with max_q_len 6: one token and five drafts
     httpd = serve(loop, args.host, args.port, args.alias)   # the socket answers 503 on /health while the model loads
     threading.Thread(target=httpd.serve_forever, daemon=True).start()
     try:

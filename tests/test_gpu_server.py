@@ -21,8 +21,9 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-@pytest.mark.parametrize("with_tokenizer", [False, True], ids=["byte_tokens", "file_tokenizer"])
-def test_engine_process_honours_the_llama_server_contract(gpu, tmp_path, with_tokenizer):
+@pytest.mark.parametrize("with_tokenizer,extra_argv", [(False, []), (True, []), (False, ["--spec-lookup", "4"])],
+                         ids=["byte_tokens", "file_tokenizer", "lookup_drafts"])
+def test_engine_process_honours_the_llama_server_contract(gpu, tmp_path, with_tokenizer, extra_argv):
     cfg = tiny_config()
     model = tmp_path / "tiny.gguf"
     metadata = None
@@ -38,7 +39,7 @@ def test_engine_process_honours_the_llama_server_contract(gpu, tmp_path, with_to
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     argv = [sys.executable, "-m", "eidola_b200.server", "-m", str(model), "--host", "127.0.0.1", "--port", str(port), "--alias",
-            "tiny@local", "-c", "256", "-ngl", "999", "--jinja", "--no-webui", "--shape", "tiny", "--seqs", "4"]
+            "tiny@local", "-c", "256", "-ngl", "999", "--jinja", "--no-webui", "--shape", "tiny", "--seqs", "4"] + extra_argv
     child = subprocess.Popen(argv, cwd=str(ROOT), stdin=subprocess.DEVNULL, stdout=subprocess.DEVNULL, stderr=subprocess.PIPE,
                              env=dict(os.environ, PYTHONPATH=str(ROOT)))
     url = "http://127.0.0.1:%d" % port

@@ -391,3 +391,67 @@ def test_the_next_turn_of_a_conversation_prefills_only_what_is_new():
     finally:
         loop.stop.set()
         httpd.shutdown()
+
+
+def test_drafts_from_the_sequence_itself_are_verified_in_the_step_and_change_nothing_but_the_step_count():
+    """Lookup drafts: when the last two tokens occurred before, the tokens that followed are fed along and verified in the
+    same step.  The reply is the one plain decoding gives; it only takes fewer steps when the text repeats."""
+    class Cyclic(ScriptedEngine):
+        """The next token of t is t % 7 + 65: the text runs in a cycle of seven letters."""
+        def __init__(self):
+            super().__init__()
+            self.len, self.max_len = {}, {}
+
+        def admit_evicting(self, context_len):
+            slot, ev = super().admit_evicting(context_len)
+            self.len[slot] = 0
+            return slot, ev
+
+        def prefill(self, slots, prompts):
+            for s, p in zip(slots, prompts):
+                self.len[s] += len(p)
+            self.calls.append(("prefill", list(slots), [len(p) for p in prompts]))
+            return (np.array([int(p[-1]) % 7 + 65 for p in prompts], np.int32),)
+
+        def step(self, slots, q_lens, tokens):
+            self.calls.append(("step", list(slots), list(q_lens)))
+            for s, q in zip(slots, q_lens):
+                self.len[s] += q
+            return np.array([int(t) % 7 + 65 for t in tokens], np.int32), None
+
+        def truncate(self, slot, new_len):
+            assert new_len <= self.len[slot]
+            self.calls.append(("truncate", slot, new_len))
+            self.len[slot] = new_len
+
+        def pin(self, slot, pinned):
+            pass
+
+    replies, steps = [], []
+    for spec in (0, 4):
+        eng = Cyclic()
+        loop = EngineLoop(eng, context_tokens=512)
+        loop.spec = spec
+        httpd = serve(loop, "127.0.0.1", 0, "test-model")
+        threading.Thread(target=httpd.serve_forever, daemon=True).start()
+        loop.start()
+        try:
+            url = "http://127.0.0.1:%d" % httpd.server_address[1]
+            out = json.load(_post(url, {"messages": [{"role": "user", "content": "go"}], "max_completion_tokens": 40, "return_token_ids": True}))
+            replies.append(out["choices"][0]["token_ids"])
+            steps.append(len([c for c in eng.calls if c[0] == "step"]))
+            assert out["usage"]["completion_tokens"] == 40 and out["choices"][0]["finish_reason"] == "length"
+            if spec:
+                qs = [c[2][0] for c in eng.calls if c[0] == "step"]
+                assert max(qs) == 5 and loop.stats["drafts_accepted"] >= 20
+                # the engine's sequence ends where the text ends: prompt + 39 tokens that ran (the 40th never did)
+                prompt_len = [c for c in eng.calls if c[0] == "prefill"][0][2][0]
+                assert eng.len[0] == prompt_len + 39
+            # a sampled request is never drafted for
+            json.load(_post(url, {"messages": [{"role": "user", "content": "go"}], "max_completion_tokens": 30, "temperature": 0.5}))
+            assert all(c[2] == [1] for c in eng.calls[-25:] if c[0] == "step")
+        finally:
+            loop.stop.set()
+            httpd.shutdown()
+    assert replies[0] == replies[1] and len(replies[0]) == 40
+    assert steps[1] < steps[0] // 2, steps
