@@ -454,8 +454,12 @@ def build_engine(args):
         "tiny": dict(n_layers=2, hidden=512, n_q_heads=8, n_kv_heads=2, n_experts=8, inter=512, vocab=4096),
         "20b": dict(n_layers=24, hidden=2880, n_q_heads=64, n_kv_heads=8, n_experts=32, inter=2880, vocab=201088),
     }[args.shape]
-    cfg = make_config(window=128, top_k=4, num_pages=args.seqs * pages_per_seq, max_seqs=args.seqs, max_pages_per_seq=pages_per_seq,
-                      max_tokens=max(args.seqs * 6, min(ctx, 2048)), max_q_len=6, seed=args.seed, **shapes)
+    dims = dict(window=128, top_k=4, **shapes)
+    if args.model and args.model.endswith(".gguf") and not args.random_init:
+        from .tokenizer import shape_from_gguf
+        dims.update(shape_from_gguf(args.model))  # the file's own dimensions, where its metadata states them
+    cfg = make_config(num_pages=args.seqs * pages_per_seq, max_seqs=args.seqs, max_pages_per_seq=pages_per_seq,
+                      max_tokens=max(args.seqs * 6, min(ctx, 2048)), max_q_len=6, seed=args.seed, **dims)
     eng = eb.Engine(cfg)
     if args.model and args.model.endswith(".gguf") and not args.random_init:
         eng.load_gguf(args.model)

@@ -21,8 +21,9 @@ from functools import lru_cache
 _SCALAR = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
 
 
-def read_gguf_metadata(path, keys_prefix: tuple[str, ...] = ("tokenizer.", "general.")) -> dict:
-    """The metadata entries of a GGUF file whose keys start with one of `keys_prefix` (arrays as Python lists)."""
+def read_gguf_metadata(path, keys_prefix: tuple[str, ...] = ("tokenizer.", "general."), tensor_shapes: dict | None = None) -> dict:
+    """The metadata entries of a GGUF file whose keys start with one of `keys_prefix` (arrays as Python lists).  When
+    `tensor_shapes` is a dict it receives name -> extents (outermost first) of every tensor of the file."""
     out = {}
     with open(path, "rb") as f:
         if f.read(4) != b"GGUF":
@@ -30,7 +31,7 @@ def read_gguf_metadata(path, keys_prefix: tuple[str, ...] = ("tokenizer.", "gene
         version, = struct.unpack("<I", f.read(4))
         if version not in (2, 3):
             raise ValueError("GGUF version %d (2 and 3 are read)" % version)
-        _n_tensors, n_kv = struct.unpack("<QQ", f.read(16))
+        n_tensors, n_kv = struct.unpack("<QQ", f.read(16))
 
         def string():
             n, = struct.unpack("<Q", f.read(8))
@@ -57,6 +58,13 @@ def read_gguf_metadata(path, keys_prefix: tuple[str, ...] = ("tokenizer.", "gene
             v = value(t, keep)
             if keep:
                 out[key] = v
+        if tensor_shapes is not None:
+            for _ in range(n_tensors):
+                name = string()
+                nd, = struct.unpack("<I", f.read(4))
+                ne = struct.unpack("<%dQ" % nd, f.read(8 * nd))
+                f.read(12)  # type, offset
+                tensor_shapes[name] = tuple(reversed(ne))
     return out
 
 
@@ -205,3 +213,33 @@ class BpeTokenizer:
 
 def _raise(msg):
     raise ValueError(msg)
+
+
+def shape_from_gguf(path) -> dict:
+    """The decoder's dimensions as a GGUF file's `<architecture>.*` metadata states them, under the names of eb_config
+    (only the keys the file has).  Keys read: block_count, embedding_length, attention.head_count, .head_count_kv,
+    .key_length (head dimension), .sliding_window, expert_count, expert_used_count, expert_feed_forward_length (else
+    feed_forward_length), rope.freq_base, attention.layer_norm_rms_epsilon; the vocabulary size is the number of rows of
+    token_embd.weight."""
+    general = read_gguf_metadata(path, ("general.",))
+    arch = general.get("general.architecture")
+    if not arch:
+        return {}
+    shapes: dict = {}
+    md = read_gguf_metadata(path, (arch + ".",), shapes)
+    names = {"block_count": "n_layers", "embedding_length": "hidden", "attention.head_count": "n_q_heads",
+             "attention.head_count_kv": "n_kv_heads", "attention.key_length": "head_dim", "attention.sliding_window": "window",
+             "expert_count": "n_experts", "expert_used_count": "top_k", "rope.freq_base": "rope_theta",
+             "attention.layer_norm_rms_epsilon": "rms_eps"}
+    out = {}
+    for key, name in names.items():
+        v = md.get("%s.%s" % (arch, key))
+        if v is not None and not isinstance(v, list):
+            out[name] = float(v) if name in ("rope_theta", "rms_eps") else int(v)
+    inter = md.get(arch + ".expert_feed_forward_length", md.get(arch + ".feed_forward_length"))
+    if inter is not None and not isinstance(inter, list):
+        out["inter"] = int(inter)
+    if out and "token_embd.weight" in shapes:
+        out["vocab"] = int(shapes["token_embd.weight"][0])
+    return out
+

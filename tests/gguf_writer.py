@@ -81,6 +81,8 @@ def write_gguf(path, tensors: dict, metadata: dict | None = None) -> None:
             head += struct.pack("<I", 8) + _string(v)
         elif isinstance(v, np.uint32):
             head += struct.pack("<II", 4, int(v))
+        elif isinstance(v, (float, np.float32)):
+            head += struct.pack("<If", 6, float(v))
         elif isinstance(v, list) and all(isinstance(x, str) for x in v):     # array of strings
             head += struct.pack("<IIQ", 9, 8, len(v)) + b"".join(_string(x) for x in v)
         elif isinstance(v, list):                                            # array of int32

@@ -111,3 +111,24 @@ def test_the_200k_scheme_splits_digits_in_threes_and_keeps_case_runs():
     p = regex.compile(_PATTERNS["gpt-4o"])
     assert p.findall("abc 1234567 XyZ don't") == ["abc", " ", "123", "456", "7", " Xy", "Z", " don't"]
     assert "".join(p.findall(CORPUS)) == CORPUS  # the pattern covers every character
+
+
+def test_engine_dimensions_come_from_the_files_architecture_metadata(tmp_path):
+    from eidola_b200.tokenizer import shape_from_gguf
+    tokens, merges, types = _train()
+    md = {"general.architecture": "gpt-oss", "gpt-oss.block_count": np.uint32(24), "gpt-oss.embedding_length": np.uint32(2880),
+          "gpt-oss.attention.head_count": np.uint32(64), "gpt-oss.attention.head_count_kv": np.uint32(8),
+          "gpt-oss.attention.key_length": np.uint32(64), "gpt-oss.attention.sliding_window": np.uint32(128),
+          "gpt-oss.expert_count": np.uint32(32), "gpt-oss.expert_used_count": np.uint32(4),
+          "gpt-oss.expert_feed_forward_length": np.uint32(2880), "gpt-oss.feed_forward_length": np.uint32(9999),
+          "gpt-oss.rope.freq_base": 150000.0, "gpt-oss.attention.layer_norm_rms_epsilon": 1e-5,
+          "tokenizer.ggml.model": "gpt2", "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.merges": merges, "tokenizer.ggml.token_type": types}
+    path = tmp_path / "arch.gguf"
+    write_gguf(path, {"x": np.zeros((2, 32), np.float32), "token_embd.weight": np.zeros((500, 32), np.float32)}, md)
+    got = shape_from_gguf(path)
+    assert got == {"n_layers": 24, "hidden": 2880, "n_q_heads": 64, "n_kv_heads": 8, "head_dim": 64, "window": 128, "n_experts": 32,
+                   "top_k": 4, "inter": 2880, "rope_theta": 150000.0, "rms_eps": got["rms_eps"], "vocab": 500}
+    assert abs(got["rms_eps"] - 1e-5) < 1e-9
+    # a file that states nothing keeps the caller's defaults
+    write_gguf(tmp_path / "bare.gguf", {"x": np.zeros((2, 32), np.float32)})
+    assert shape_from_gguf(tmp_path / "bare.gguf") == {}
