@@ -85,6 +85,36 @@ class Request:
         self.t_arrive = time.perf_counter()
 
 
+def make_request(tokenizer, body: dict) -> Request:
+    """A request body (the fields of the reference server's ChatCompletionRequest, crates/eidola-server/src/types.rs:10-66,
+    plus `seed` and `max_tokens`) -> Request; ValueError with the message for a 400 otherwise."""
+    messages = body.get("messages")
+    if not (isinstance(messages, list) and messages):
+        raise ValueError("body must be JSON with a non-empty `messages` array")
+    max_tokens = int(body.get("max_completion_tokens") or body.get("max_tokens") or 256)
+    # `temperature` (0..2) and `top_p`: absent or 0 is greedy.  `seed` makes a sampled reply repeatable.
+    try:
+        temperature = float(body.get("temperature") or 0.0)
+        top_p = float(body["top_p"]) if body.get("top_p") is not None else 1.0
+        seed = int(body["seed"]) & (2**64 - 1) if body.get("seed") is not None else int(time.time_ns()) & (2**64 - 1)
+        assert 0.0 <= temperature <= 2.0 and 0.0 <= top_p <= 1.0
+    except Exception:
+        raise ValueError("`temperature` must lie in [0, 2], `top_p` in [0, 1], `seed` be an integer") from None
+    stop = body.get("stop")  # a string or up to 4 of them
+    stop = [stop] if isinstance(stop, str) else (stop or [])
+    if not (isinstance(stop, list) and len(stop) <= 4 and all(isinstance(x, str) for x in stop)):
+        raise ValueError("`stop` must be a string or up to 4 strings")
+    try:
+        # `tools` / `tool_choice` are for the model's chat template to spell out; nothing here executes a tool
+        if body.get("tools") and getattr(tokenizer, "chat_template", None):
+            prompt_ids = tokenizer.template(messages, tools=body["tools"], tool_choice=body.get("tool_choice"))
+        else:
+            prompt_ids = tokenizer.template(messages)
+    except Exception as e:  # a chat template may refuse a conversation (roles out of order, ...)
+        raise ValueError("chat template: %s" % e) from None
+    return Request(prompt_ids, max(1, max_tokens), temperature, top_p, seed, stop)
+
+
 class EngineLoop(threading.Thread):
     """The thread that owns the engine.  `engine` needs admit_evicting(context_len) -> (slot, evicted), prefill(slots,
     prompts) -> (first_tokens, ...), step(slots, q_lens, tokens) -> (next, margins), release(slot), and max_seqs /
@@ -139,8 +169,17 @@ class EngineLoop(threading.Thread):
             req.slot = slot
             fresh.append(req)
         if fresh:
-            first = self.engine.prefill([r.slot for r in fresh],
-                                        [np.asarray(r.prompt_ids[r.cached_tokens:], np.int32) for r in fresh])[0]
+            try:
+                first = self.engine.prefill([r.slot for r in fresh],
+                                            [np.asarray(r.prompt_ids[r.cached_tokens:], np.int32) for r in fresh])[0]
+            except Exception as e:  # the requests that were being admitted hear of it too, and their slots go back
+                for r in fresh:
+                    r.out.put(("error", "engine: %s" % e))
+                    try:
+                        self.engine.release(r.slot)
+                    except Exception:
+                        pass
+                raise
             for r, tok in zip(fresh, first):
                 self.stats["prefill_tokens"] += len(r.prompt_ids) - r.cached_tokens
                 r.history = list(r.prompt_ids)
@@ -340,40 +379,18 @@ def make_handler(loop: EngineLoop, alias: str):
             try:
                 n = int(self.headers.get("Content-Length", "0"))
                 body = json.loads(self.rfile.read(n) or b"{}")
-                messages = body["messages"]
-                assert isinstance(messages, list) and messages
+                assert isinstance(body, dict) and isinstance(body.get("messages"), list) and body["messages"]
             except Exception:
                 return self._json(400, {"error": {"message": "body must be JSON with a non-empty `messages` array",
                                                   "type": "invalid_request_error", "code": 400}})
             if not loop.ready.is_set():
                 return self._json(503, {"error": {"message": "loading model", "type": "unavailable_error", "code": 503}})
-            max_tokens = int(body.get("max_completion_tokens") or body.get("max_tokens") or 256)
             stream = bool(body.get("stream"))
             include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
-            # `temperature` (0..2) and `top_p` as the reference server's request type has them
-            # (crates/eidola-server/src/types.rs:24-30); absent or 0: greedy.  `seed` makes a sampled reply repeatable.
             try:
-                temperature = float(body.get("temperature") or 0.0)
-                top_p = float(body["top_p"]) if body.get("top_p") is not None else 1.0
-                seed = int(body["seed"]) & (2**64 - 1) if body.get("seed") is not None else int(time.time_ns()) & (2**64 - 1)
-                assert 0.0 <= temperature <= 2.0 and 0.0 <= top_p <= 1.0
-            except Exception:
-                return self._json(400, {"error": {"message": "`temperature` must lie in [0, 2], `top_p` in [0, 1], `seed` be an integer",
-                                                  "type": "invalid_request_error", "code": 400}})
-            stop = body.get("stop")  # a string or up to 4 of them (crates/eidola-server/src/types.rs: `stop`)
-            stop = [stop] if isinstance(stop, str) else (stop or [])
-            if not (isinstance(stop, list) and len(stop) <= 4 and all(isinstance(x, str) for x in stop)):
-                return self._json(400, {"error": {"message": "`stop` must be a string or up to 4 strings", "type": "invalid_request_error",
-                                                  "code": 400}})
-            try:
-                # `tools` / `tool_choice` are for the model's chat template to spell out; nothing here executes a tool
-                if body.get("tools") and getattr(loop.tokenizer, "chat_template", None):
-                    prompt_ids = loop.tokenizer.template(messages, tools=body["tools"], tool_choice=body.get("tool_choice"))
-                else:
-                    prompt_ids = loop.tokenizer.template(messages)
-            except Exception as e:  # a chat template may refuse a conversation (roles out of order, ...)
-                return self._json(400, {"error": {"message": "chat template: %s" % e, "type": "invalid_request_error", "code": 400}})
-            req = Request(prompt_ids, max(1, max_tokens), temperature, top_p, seed, stop)
+                req = make_request(loop.tokenizer, body)
+            except ValueError as e:
+                return self._json(400, {"error": {"message": str(e), "type": "invalid_request_error", "code": 400}})
             loop.submit(req)
             rid, created = "chatcmpl-%x" % id(req), int(time.time())
             base = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": body.get("model") or alias}
