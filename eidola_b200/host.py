@@ -411,6 +411,13 @@ class Engine:
         numbers from `seed`); temperature <= 0 returns it to greedy decoding."""
         call("eb_engine_seq_sampling", self._h, c_i32(slot), c_f32(temperature), c_f32(top_p), C.c_uint64(seed))
 
+    def free_pages(self) -> int:
+        """Pages of the pool that no sequence holds."""
+        sp, n = c_vp(), c_i32(0)
+        call("eb_engine_sched", self._h, C.byref(sp))
+        call("eb_sched_free_pages", sp, C.byref(n))
+        return int(n.value)
+
     def chunk_tokens(self) -> int:
         """Most new tokens one sequence may bring to a step (eb_engine_chunk_tokens)."""
         n = c_i32(0)

@@ -169,6 +169,7 @@ class EngineLoop(threading.Thread):
             req.slot = slot
             fresh.append(req)
         if fresh:
+            self._make_room(sum((len(r.prompt_ids) - r.cached_tokens) // 16 + 2 for r in fresh))
             try:
                 first = self.engine.prefill([r.slot for r in fresh],
                                             [np.asarray(r.prompt_ids[r.cached_tokens:], np.int32) for r in fresh])[0]
@@ -260,6 +261,17 @@ class EngineLoop(threading.Thread):
         else:
             self.last[r.slot] = tok
 
+    def _make_room(self, pages: int) -> None:
+        """Idle sequences give their pages back, longest idle first, until `pages` are free: a live sequence that grows
+        never fails for pages that a finished conversation is only keeping in case it returns."""
+        if not self.idle or not hasattr(self.engine, "free_pages"):
+            return
+        while self.idle and self.engine.free_pages() < pages:
+            slot = next(iter(self.idle))  # dicts keep insertion order: the one that has been idle longest
+            del self.idle[slot]
+            self.engine.release(slot)
+            self.stats["evicted"] += 1
+
     def _settle(self, r: Request) -> None:
         """Cut the engine's sequence back to the tokens that count (rejected drafts ran through the layers too)."""
         if getattr(r, "engine_len", 0) > len(r.history):
@@ -289,6 +301,7 @@ class EngineLoop(threading.Thread):
                     continue
                 slots = sorted(self.live)
                 fed = {s: [self.last[s]] + self._drafts(self.live[s], self.last[s]) for s in slots}
+                self._make_room(sum(len(x) for x in fed.values()) // 16 + len(slots))
                 nxt, _ = self.engine.step(slots, [len(fed[s]) for s in slots], [t for s in slots for t in fed[s]])
                 self.stats["steps"] += 1
                 row = 0
@@ -342,6 +355,9 @@ class EngineAdapter:
 
     def pin(self, slot, pinned):
         self.eng.pin(slot, pinned)
+
+    def free_pages(self):
+        return self.eng.free_pages()
 
     def release(self, slot):
         self.eng.release(slot)

@@ -455,3 +455,66 @@ def test_drafts_from_the_sequence_itself_are_verified_in_the_step_and_change_not
             httpd.shutdown()
     assert replies[0] == replies[1] and len(replies[0]) == 40
     assert steps[1] < steps[0] // 2, steps
+
+
+def test_idle_conversations_give_their_pages_back_when_live_ones_need_them():
+    class Pool(ScriptedEngine):
+        """16 tokens per page, 16 pages: a finished conversation's pages stay held until somebody releases it."""
+        pages = 16
+
+        def __init__(self):
+            super().__init__()
+            self.len = {}
+
+        def admit_evicting(self, context_len):
+            slot, ev = super().admit_evicting(context_len)
+            self.len[slot] = 0
+            return slot, ev
+
+        def _grow(self, slot, n):
+            need = -(-(self.len[slot] + n) // 16) - -(-self.len[slot] // 16)
+            if need > self.free_pages():
+                raise RuntimeError("out of pages")
+            self.len[slot] += n
+
+        def free_pages(self):
+            return self.pages - sum(-(-n // 16) for n in self.len.values())
+
+        def prefill(self, slots, prompts):
+            for s, p in zip(slots, prompts):
+                self._grow(s, len(p))
+            return super().prefill(slots, prompts)
+
+        def step(self, slots, q_lens, tokens):
+            for s, q in zip(slots, q_lens):
+                self._grow(s, q)
+            return super().step(slots, q_lens, tokens)
+
+        def truncate(self, slot, new_len):
+            self.len[slot] = new_len
+
+        def pin(self, slot, pinned):
+            pass
+
+        def release(self, slot):
+            self.len.pop(slot, None)
+            super().release(slot)
+
+    eng = Pool()
+    loop = EngineLoop(eng, context_tokens=512)
+    httpd = serve(loop, "127.0.0.1", 0, "test-model")
+    threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    url = "http://127.0.0.1:%d" % httpd.server_address[1]
+    loop.start()
+    try:
+        # three conversations of 4 pages each stay idle (4 pages free); a fourth that needs 6 must still run to its end
+        for i in range(3):
+            out = json.load(_post(url, {"messages": [{"role": "user", "content": chr(65 + i) * 26}], "max_completion_tokens": 8}))  # no common prefix
+            assert out["usage"]["completion_tokens"] == 8
+        assert len(loop.idle) == 3 and eng.free_pages() == 4
+        out = json.load(_post(url, {"messages": [{"role": "user", "content": "x" * 30}], "max_completion_tokens": 40}))
+        assert out["usage"]["completion_tokens"] == 40 and out["choices"][0]["finish_reason"] == "length"
+        assert len(loop.idle) < 4 and loop.stats["evicted"] >= 1
+    finally:
+        loop.stop.set()
+        httpd.shutdown()
