@@ -69,6 +69,7 @@ class EidolaB200Backend:
     """`ChatBackend` for an EngineLoop that is already running (the loop owns the engine handle)."""
 
     provider = "eidola_b200"
+    abandon_after = 30.0  # seconds a full channel may stay untouched before its receiver counts as dropped
 
     def __init__(self, loop: EngineLoop, model: str):
         self.loop, self.model = loop, model
@@ -106,6 +107,16 @@ class EidolaB200Backend:
         out: queue.Queue = queue.Queue(maxsize=32)
         base = {"id": rid, "object": "chat.completion.chunk", "created": int(time.time()), "model": self.model}
 
+        def put(ev) -> bool:
+            """False when the consumer has not taken an event for `abandon_after` seconds: the receiver is taken for
+            dropped (the reference's sender sees a closed channel then), the sequence is ended and the reader leaves."""
+            try:
+                out.put(ev, timeout=self.abandon_after)
+                return True
+            except queue.Full:
+                req.cancelled = True
+                return False
+
         def reader():
             utf8 = codecs.getincrementaldecoder("utf-8")(errors="replace")
             while True:
@@ -113,26 +124,23 @@ class EidolaB200Backend:
                 now = time.monotonic()  # the stamp of the moment the engine produced it
                 if kind == "bytes":
                     text = utf8.decode(val)
-                    if text:
-                        out.put(BackendStreamEvent("chunk", now, dict(base, choices=[{"index": 0, "delta": {"content": text}, "finish_reason": None}])))
+                    if text and not put(BackendStreamEvent("chunk", now, dict(base, choices=[{"index": 0, "delta": {"content": text}, "finish_reason": None}]))):
+                        return
                 elif kind == "done":
                     usage = dict(val)
                     finish = usage.pop("finish_reason")
                     tail = utf8.decode(b"", final=True)
                     if tail:
-                        out.put(BackendStreamEvent("chunk", now, dict(base, choices=[{"index": 0, "delta": {"content": tail}, "finish_reason": None}])))
-                    out.put(BackendStreamEvent("chunk", now, dict(base, choices=[{"index": 0, "delta": {}, "finish_reason": finish}])))
-                    out.put(BackendStreamEvent("done", now, meta=BackendMeta(self.provider, rid, self.model, None, usage), finish_reason=finish))
+                        put(BackendStreamEvent("chunk", now, dict(base, choices=[{"index": 0, "delta": {"content": tail}, "finish_reason": None}])))
+                    put(BackendStreamEvent("chunk", now, dict(base, choices=[{"index": 0, "delta": {}, "finish_reason": finish}])))
+                    put(BackendStreamEvent("done", now, meta=BackendMeta(self.provider, rid, self.model, None, usage), finish_reason=finish))
                     return
                 elif kind == "error":
-                    out.put(ServerError("BackendError", str(val)))  # no Done: a stream without usage is a failed stream
+                    put(ServerError("BackendError", str(val)))  # no Done: a stream without usage is a failed stream
                     return
 
         threading.Thread(target=reader, daemon=True).start()
         return out
-
-    def cancel(self, receiver_request) -> None:  # pragma: no cover - convenience for hosts that drop a receiver
-        receiver_request.cancelled = True
 
     # ---- shared
     def _submit(self, request: dict):

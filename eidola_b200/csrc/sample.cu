@@ -24,6 +24,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/eidola_b200.h"
 #include "common.h"
 
@@ -295,12 +297,16 @@ int32_t eb_sample_top_p(const void* d_logits, int32_t T, int64_t V, int64_t ld, 
   if (T == 0) return EB_OK;
   int32_t* status = eb::status_word();
   EB_REQUIRE(status, EB_ERR_NODEVICE, "eb_sample_top_p: no device");
-  static bool attr_set[64] = {};
+  static std::mutex attr_mu;
+  static bool attr_set[64] = {};  // the attribute is per device
   int dev = 0;
   EB_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    EB_CUDA(cudaFuncSetAttribute(sample_top_p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSampleSmem));
-    attr_set[dev] = true;
+  {
+    std::lock_guard<std::mutex> lk(attr_mu);
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+      EB_CUDA(cudaFuncSetAttribute(sample_top_p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSampleSmem));
+      if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
   }
   EB_CUDA(eb::launch(sample_top_p_kernel, dim3((unsigned)T), dim3(kThreads), kSampleSmem, eb::as_stream(stream), (const uint16_t*)d_logits, V, ld,
                      d_scale, d_top_p_q24, d_rand32, d_tok, status));

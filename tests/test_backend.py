@@ -108,3 +108,18 @@ def test_a_backend_that_drops_the_request_before_any_response():
             call()
         assert err.value.kind == "BackendUnavailable"
     assert dead.inbox.qsize() == 0
+
+
+def test_a_receiver_that_is_dropped_ends_the_sequence():
+    eng, loop, be = _backend()
+    be.abandon_after = 0.2
+    try:
+        rx = be.send_stream(dict(REQ, max_completion_tokens=400, stream=True))  # far more events than the channel holds
+        import time
+        deadline = time.time() + 10
+        while time.time() < deadline and len(eng.free) < 4:
+            time.sleep(0.05)                                       # nobody reads rx
+        assert sorted(eng.free) == [0, 1, 2, 3] and rx.full()
+        assert len([c for c in eng.calls if c[0] == "step"]) < 300
+    finally:
+        loop.stop.set()
