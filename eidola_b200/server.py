@@ -516,7 +516,9 @@ def main(argv=None) -> int:
     ap.add_argument("--spec-lookup", type=int, default=0,
                     help="draft up to this many tokens per step from the sequence's own earlier text and verify them in the step (0 = off)")
     ap.add_argument("--device", type=int, default=0)
-    args = ap.parse_args(argv)
+    args, unknown = ap.parse_known_args(argv)
+    if unknown:  # other llama-server options a caller may pass: said once on stderr, then ignored
+        print("eidola_b200.server: ignoring options it does not know: %s" % " ".join(unknown), file=sys.stderr, flush=True)
     holder = {}
     loop = EngineLoop(None, args.ctx)
     loop.spec = max(0, min(args.spec_lookup, 5))  # the engine is created with max_q_len 6: one token and five drafts
