@@ -20,6 +20,8 @@
 #include <utility>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.h"
 #include "loader.h"
 
@@ -493,7 +495,19 @@ int32_t run_layers(eb_engine* e, int T, int n_seqs, const int32_t* d_tokens, con
   const bool prof = (c.debug & 2) != 0;
   size_t prof_used = 0;
   e->prof_cat.clear();
+  // EIDOLA_B200_NVTX=1: the same intervals as named NVTX ranges (no-ops unless a tool that reads them is attached)
+  static const bool nvtx_on = [] {
+    const char* v = getenv("EIDOLA_B200_NVTX");
+    return v && v[0] == '1';
+  }();
+  static const char* const kCatName[8] = {"attn_full", "attn_window", "dense_gemm", "expert_gemm", "lm_head", "collectives", "router", "quantisers"};
   auto mark = [&](int cat) {  // one event before and one after a call; cat < 0 closes the open interval
+    if (nvtx_on) {
+      if (cat >= 0 && cat < 8)
+        nvtxRangePushA(kCatName[cat]);
+      else
+        nvtxRangePop();
+    }
     if (!prof) return;
     if (prof_used == e->prof_ev.size()) {
       cudaEvent_t ev;
@@ -1316,7 +1330,13 @@ int32_t eb_engine_step_launch(eb_engine* e, const int32_t* h_slots, const int32_
   }
   for (int i = 0; i < n_seqs; ++i)  // (kept when the step is refused below: only ever too cautious)
     e->high_len[(size_t)h_slots[i]] = std::max(e->high_len[(size_t)h_slots[i]], old_len[(size_t)i] + h_q_lens[i]);
+  static const bool nvtx_step = [] {
+    const char* v = getenv("EIDOLA_B200_NVTX");
+    return v && v[0] == '1';
+  }();
+  if (nvtx_step) nvtxRangePushA("eb_engine_step_launch");
   const int32_t rc_body = step_launch_body(e, h_slots, h_q_lens, n_seqs, h_tokens, T, max_q);
+  if (nvtx_step) nvtxRangePop();
   if (rc_body != EB_OK) return rollback(rc_body);
   ++e->tick;
   for (int i = 0; i < n_seqs; ++i) eb_sched_touch(e->sched, h_slots[i], e->tick);

@@ -565,6 +565,8 @@ int32_t eb_engine_create(const eb_config* cfg, eb_engine** out);
  * EIDOLA_B200_TP_NCCL=1, the exchanges themselves as NCCL reduce-scatter / all-gather calls.  EIDOLA_B200_TP_WHOLE=0 and
  * EIDOLA_B200_EP_A2A=0|1 force one of the forms (A/B runs and tests).
  *
+ * EIDOLA_B200_NVTX=1 (any engine): NVTX ranges around every step and its phases, for timeline tools.
+ *
  * From four ranks on (peer-memory transport; EIDOLA_B200_TP_OGATHER=1|0 forces it on or off) the O projection has no
  * partial products at all: every rank keeps the whole W_o, quantises its heads' columns of the attention output straight
  * into the other ranks' copies of the operand (eb_quant_act_block128_to_peers: all rows to all ranks for steps of up to
