@@ -14,7 +14,11 @@ from tests.helpers import bf16_to_f32
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def test_two_gloo_ranks_reproduce_the_unsharded_layer(tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("c1", ["partial_sums", "gather"])
+def test_two_gloo_ranks_reproduce_the_unsharded_layer(tmp_path, c1):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
@@ -22,7 +26,7 @@ def test_two_gloo_ranks_reproduce_the_unsharded_layer(tmp_path):
     procs = []
     for r in range(2):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
-                   OMP_NUM_THREADS="2")
+                   OMP_NUM_THREADS="2", TP_GLOO_C1=c1)
         procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "tp_gloo_worker.py"), out], env=env,
                                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     logs = [p.communicate(timeout=600)[0] for p in procs]

@@ -6,7 +6,8 @@ Each rank computes its shard of every decoder layer with the CPU oracle's operat
 (with the 128-row K/V weight bands a rank shares with its neighbour when it holds a single KV head), its slice of
 the O projection's K dimension, its experts -- and the per-layer exchanges go through torch.distributed (gloo) in
 the engine's form: the two fp32 sums are reduce-scatters over token slices (gloo has no reduce-scatter: an
-all-reduce of which a rank keeps its slice), the slice's owner adds the residual, normalises and routes its tokens,
+all-reduce of which a rank keeps its slice; with TP_GLOO_C1=gather the first one is replaced by the gathered-operand
+form: the ranks' quantised attention bands are all-gathered and every rank multiplies full-K rows by the whole W_o), the slice's owner adds the residual, normalises and routes its tokens,
 and the rows and the routing are all-gathered.  The LM head is split over the vocabulary and the ranks' argmax
 candidates are merged.  Every layer starts from the unsharded oracle's input (teacher forcing); rank 0 saves the
 outputs.
@@ -102,10 +103,23 @@ def main():
         c0 = rank * hqd_l
         o_part = bf16_to_f32(orc.gemm_fp8_block(a8, sa, np.ascontiguousarray(wo[:, c0:c0 + hqd_l]),
                                                 np.ascontiguousarray(so[:, c0 // 128:(c0 + hqd_l) // 128]))).copy()
-        t_o = torch.from_numpy(o_part)
-        dist.all_reduce(t_o)                                   # C1: sum over the ranks' heads; this rank keeps rows [t0, t1)
         xs = np.ascontiguousarray(x[t0:t1])
-        orc.residual_add(xs, orc.bf16_encode(t_o.numpy()[t0:t1]))
+        if os.environ.get("TP_GLOO_C1") == "gather":
+            # C1 on the gathered operand: the ranks' code bands and scale columns side by side ARE the quantised whole
+            # attention output (scale blocks are 128 columns wide), and full-K rows of the projection are the unsharded ones
+            def all_cols(mine):
+                parts = [torch.zeros(mine.view(np.uint8).shape, dtype=torch.uint8) for _ in range(world)]
+                dist.all_gather(parts, torch.from_numpy(np.ascontiguousarray(mine).view(np.uint8)))
+                return np.concatenate([q.numpy().view(mine.dtype) for q in parts], axis=1)
+            a8_g, sa_g = all_cols(a8), all_cols(sa)
+            a8_w, sa_w = orc.quant_act_block128(all_cols(att))   # what one GPU quantises: the whole attention output
+            assert np.array_equal(a8_g, a8_w) and np.array_equal(sa_g, sa_w), "gathered bands differ from the whole operand"
+            o_full = orc.gemm_fp8_block(a8_g, sa_g, wo, so)     # hence the unsharded projection, bit for bit
+            orc.residual_add(xs, np.ascontiguousarray(o_full[t0:t1]))
+        else:
+            t_o = torch.from_numpy(o_part)
+            dist.all_reduce(t_o)                               # C1: sum over the ranks' heads; this rank keeps rows [t0, t1)
+            orc.residual_add(xs, orc.bf16_encode(t_o.numpy()[t0:t1]))
         # ---- expert half: the slice's owner normalises and routes, rows and routing are gathered
         h2s = orc.rmsnorm(xs, ones, cfg.rms_eps) if t1 > t0 else np.zeros((0, H), np.uint16)
         wr = orc.synth_normal_bf16(cfg.seed, sid(l, 3), 0, E * H, cfg.init_std).reshape(E, H)
