@@ -125,3 +125,11 @@ def test_engine_sampling_is_seeded_per_sequence_and_leaves_greedy_rows_alone(gpu
     with pytest.raises(eb.EbError):
         eng.sampling(s + 1, 1.0, 1.0, 0)  # not a live slot
     eng.sampling(s, 0.0)  # back to greedy is always fine
+
+
+def test_the_kernel_reproduces_the_committed_vectors(gpu):
+    from pathlib import Path
+    g = np.load(Path(__file__).with_name("golden") / "sampler.npz")
+    T, V = g["bits"].shape
+    got = _run(g["bits"], V, g["scales"], g["q24"], g["r32"], np.full(T, -1, np.int32))
+    assert np.array_equal(got, g["tokens"])

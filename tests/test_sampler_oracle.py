@@ -69,3 +69,16 @@ def test_draws_follow_the_distribution():
     live = p > 0
     chi2 = (((counts[live] - n * p[live]) ** 2) / (n * p[live])).sum()
     assert chi2 < 2.0 * live.sum() + 20, (chi2, live.sum())
+
+
+def test_the_restatement_reproduces_its_committed_vectors():
+    """tests/golden/sampler.npz (made by tests/golden/make_sampler_golden.py): inputs, thresholds, masses and tokens."""
+    from pathlib import Path
+    g = np.load(Path(__file__).with_name("golden") / "sampler.npz")
+    T = g["bits"].shape[0]
+    got = smp.sample(g["bits"], g["scales"], g["q24"], g["r32"], np.full(T, -1, np.int32))
+    assert np.array_equal(got, g["tokens"])
+    for t in range(T):
+        thr, mass, _, _ = smp.nucleus(g["bits"][t], g["scales"][t], int(g["q24"][t]))
+        assert thr == int(g["threshold_key"][t]) and mass == int(g["nucleus_mass"][t])
+    assert g["tokens"][0] == 77  # the dominant token of row 0
